@@ -1,0 +1,434 @@
+// Causal / sliding-window GQA attention backward on tcgen05 + TMEM, head_dim 128, key-owned.
+//
+// One CTA owns 128 keys of one (batch, kv head) and walks the 64-query tiles (of every query head
+// in the group) that can see them.  Everything is computed in the transposed frame so that the
+// thread <-> TMEM-lane mapping is "one key per thread":
+//     S^T  = K Q^T            P^T  = exp2(S^T * scale*log2e - lse2[q])
+//     dP^T = V dO^T           dS^T = P^T * (dP^T - delta[q]) * scale
+//     dV  += P^T dO           dK  += dS^T Q           dQ^T = K^T dS^T   (-> fp32 atomics)
+// dK / dV stay in TMEM for the whole CTA lifetime and are written once: no atomics on them and a
+// bit-reproducible result; only dQ uses floating-point atomics (the reference's key-owned TileLang
+// backward, src/archlab/architectures/tilelang_gqa.py:64-152, makes the same choice).
+#include "ptx.cuh"
+#include "host_util.h"
+#include "attention.h"
+#include <cuda.h>
+
+namespace nga {
+
+constexpr int AB_D = 128;
+constexpr int AB_BK = 128;   // keys per CTA
+constexpr int AB_BQ = 64;    // queries per inner step
+constexpr int AB_THREADS = 192;
+
+struct AttnBwdParams {
+  __nv_bfloat16* dqkv;   // [B*T, (Hq+2Hkv)*D]
+  float* dq_acc;         // [B*T, Hq*D] fp32, zeroed by the launcher
+  const float* lse2;     // [B, Hq, T]
+  const float* delta;    // [B, Hq, T]
+  int B, T, Hq, Hkv, window;
+  float scale, scale_log2;
+  int* status;
+};
+
+struct AttnBwdSmem {
+  static constexpr int kK = 0;                      // 32 KB
+  static constexpr int kV = 32768;                  // 32 KB
+  static constexpr int kQ = 65536;                  // 2 x 16 KB
+  static constexpr int kDO = kQ + 2 * 16384;        // 2 x 16 KB
+  static constexpr int kPT = kDO + 2 * 16384;       // 16 KB
+  static constexpr int kDST = kPT + 16384;          // 16 KB
+  static constexpr int kVec = kDST + 16384;         // per warp: lse2[2][64], delta[2][64]
+  static constexpr int kBar = kVec + 4 * 256 * 4;
+  static constexpr int kTotal = kBar + 16 * 8 + 16 + 1024;
+};
+
+// delta[b, h, t] = sum_d O * dO   (one warp per (token, head))
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out,
+                                  const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta,
+                                  int B, int T, int Hq) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)B * T * Hq) return;
+  const long long row = w / Hq;
+  const int h = int(w % Hq);
+  const long long off = row * (long long)(Hq * AB_D) + h * AB_D + lane * 4;
+  const uint2 a = *reinterpret_cast<const uint2*>(out + off);
+  const uint2 g = *reinterpret_cast<const uint2*>(dout + off);
+  const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    float2 x = __bfloat1622float2(ah[i]), y = __bfloat1622float2(gh[i]);
+    s += x.x * y.x + x.y * y.y;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) delta[((long long)(row / T) * Hq + h) * T + (row % T)] = s;
+}
+
+// dqkv[:, q columns] = bf16(dq_acc)
+__global__ void attn_dq_cast_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv,
+                                    long long rows, int qcols, int allcols) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= rows * qcols) return;
+  const long long row = i / qcols;
+  const int c = int(i % qcols);
+  const float4 v = *reinterpret_cast<const float4*>(dq_acc + i);
+  uint2 u;
+  u.x = pack_bf16(v.x, v.y);
+  u.y = pack_bf16(v.z, v.w);
+  *reinterpret_cast<uint2*>(dqkv + row * allcols + c) = u;
+}
+
+__global__ void __launch_bounds__(AB_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 128}
+                const __grid_constant__ CUtensorMap tm_q,    // qkv, box {64, 64}
+                const __grid_constant__ CUtensorMap tm_do,   // dout, box {64, 64}
+                const AttnBwdParams p) {
+  using S = AttnBwdSmem;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kBar);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* qdo_full = bars + 1;    // [2]
+  uint64_t* qdo_empty = bars + 3;   // [2]
+  uint64_t* st_full = bars + 5;
+  uint64_t* pds_full = bars + 6;
+  uint64_t* mma2_done = bars + 7;
+  uint64_t* dq_free = bars + 8;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* s_vec = reinterpret_cast<float*>(smem + S::kVec);       // [4 warps][lse 2x64 | delta 2x64]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int group = p.Hq / p.Hkv;
+  const int k0 = kt * AB_BK;
+  const int row_base = b * p.T;
+  const int qt_lo = k0 / AB_BQ;
+  const int q_last = (p.window < 0) ? (p.T - 1) : min(p.T - 1, k0 + AB_BK - 1 + p.window);
+  const int qt_hi = q_last / AB_BQ;
+  const int nq = qt_hi - qt_lo + 1;
+  const int niter = nq * group;
+  const int k_col = (p.Hq + hk) * AB_D;
+  const int v_col = (p.Hq + p.Hkv + hk) * AB_D;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qdo_full[i], 1);
+      mbar_init(&qdo_empty[i], 1);
+    }
+    mbar_init(st_full, 1);
+    mbar_init(pds_full, 4);
+    mbar_init(mma2_done, 1);
+    mbar_init(dq_free, 4);
+    *abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t t_ST = tmem_base;          // 64 cols
+  const uint32_t t_DPT = tmem_base + 64;    // 64 cols
+  const uint32_t t_DQT = tmem_base + 128;   // 64 cols
+  const uint32_t t_DV = tmem_base + 256;    // 128 cols
+  const uint32_t t_DK = tmem_base + 384;    // 128 cols
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_kv);
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_do);
+      mbar_expect_tx(kv_full, 65536);
+      tma_load_3d(smem + S::kK, &tm_kv, kv_full, k_col, row_base + k0, 0);
+      tma_load_3d(smem + S::kK + 16384, &tm_kv, kv_full, k_col + 64, row_base + k0, 0);
+      tma_load_3d(smem + S::kV, &tm_kv, kv_full, v_col, row_base + k0, 0);
+      tma_load_3d(smem + S::kV + 16384, &tm_kv, kv_full, v_col + 64, row_base + k0, 0);
+      bool ok = true;
+      for (int it = 0; it < niter && ok; ++it) {
+        const int st = it & 1;
+        ok = mbar_wait(&qdo_empty[st], ((it >> 1) & 1) ^ 1u, abort_word);
+        if (!ok) break;
+        const int h = hk * group + it / nq;
+        const int qrow = row_base + (qt_lo + it % nq) * AB_BQ;
+        uint8_t* sQ = smem + S::kQ + st * 16384;
+        uint8_t* sDO = smem + S::kDO + st * 16384;
+        mbar_expect_tx(&qdo_full[st], 32768);
+        tma_load_3d(sQ, &tm_q, &qdo_full[st], h * AB_D, qrow, 0);
+        tma_load_3d(sQ + 8192, &tm_q, &qdo_full[st], h * AB_D + 64, qrow, 0);
+        tma_load_3d(sDO, &tm_do, &qdo_full[st], h * AB_D, qrow, 0);
+        tma_load_3d(sDO + 8192, &tm_do, &qdo_full[st], h * AB_D + 64, qrow, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t id_st = umma_idesc_bf16(128, 64, 0, 0);    // K Q^T, V dO^T
+      constexpr uint32_t id_dv = umma_idesc_bf16(128, 128, 0, 1);   // P^T dO, dS^T Q
+      constexpr uint32_t id_dq = umma_idesc_bf16(128, 64, 1, 1);    // K^T dS^T
+      const uint32_t sK = smem_u32(smem + S::kK), sV = smem_u32(smem + S::kV);
+      const uint32_t sPT = smem_u32(smem + S::kPT), sDST = smem_u32(smem + S::kDST);
+      auto issue_mma1 = [&](int it) {
+        const uint32_t sQ = smem_u32(smem + S::kQ + (it & 1) * 16384);
+        const uint32_t sDO = smem_u32(smem + S::kDO + (it & 1) * 16384);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {   // contraction over d
+          const uint32_t offA = (k >> 2) * 16384 + (k & 3) * 32;   // K / V: 128-row blocks
+          const uint32_t offB = (k >> 2) * 8192 + (k & 3) * 32;    // Q / dO: 64-row blocks
+          umma_bf16_ss(t_ST, umma_smem_desc(sK + offA, 16, 1024), umma_smem_desc(sQ + offB, 16, 1024),
+                       id_st, k != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t offA = (k >> 2) * 16384 + (k & 3) * 32;
+          const uint32_t offB = (k >> 2) * 8192 + (k & 3) * 32;
+          umma_bf16_ss(t_DPT, umma_smem_desc(sV + offA, 16, 1024), umma_smem_desc(sDO + offB, 16, 1024),
+                       id_st, k != 0 ? 1u : 0u);
+        }
+        umma_commit(st_full);
+      };
+      bool ok = mbar_wait(kv_full, 0, abort_word);
+      if (ok) ok = mbar_wait(&qdo_full[0], 0, abort_word);
+      if (ok) {
+        tc_fence_after();
+        issue_mma1(0);
+      }
+      for (int it = 0; it < niter && ok; ++it) {
+        ok = mbar_wait(pds_full, it & 1, abort_word);
+        if (ok && it > 0) ok = mbar_wait(dq_free, (it - 1) & 1, abort_word);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sQ = smem_u32(smem + S::kQ + (it & 1) * 16384);
+        const uint32_t sDO = smem_u32(smem + S::kDO + (it & 1) * 16384);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {   // contraction over the 64 queries
+          // A: P^T / dS^T, K-major (q contiguous), one 64-wide block.  B: dO / Q, MN-major:
+          // rows are queries, d blocks 8 KB apart, 16 queries = 2048 B.
+          umma_bf16_ss(t_DV, umma_smem_desc(sPT + k * 32, 16, 1024),
+                       umma_smem_desc(sDO + k * 2048, 8192, 1024), id_dv, (it | k) != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          umma_bf16_ss(t_DK, umma_smem_desc(sDST + k * 32, 16, 1024),
+                       umma_smem_desc(sQ + k * 2048, 8192, 1024), id_dv, (it | k) != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {   // contraction over the 128 keys
+          // A: K^T, MN-major (rows are keys, d blocks 16 KB apart).  B: dS^T, MN-major (rows are
+          // keys, one 64-wide q block).
+          umma_bf16_ss(t_DQT, umma_smem_desc(sK + k * 2048, 16384, 1024),
+                       umma_smem_desc(sDST + k * 2048, 8192, 1024), id_dq, k != 0 ? 1u : 0u);
+        }
+        umma_commit(mma2_done);
+        umma_commit(&qdo_empty[it & 1]);
+        if (it + 1 < niter) {
+          ok = mbar_wait(&qdo_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_word);
+          if (!ok) break;
+          tc_fence_after();
+          issue_mma1(it + 1);
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- compute warps: thread = key
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int key = k0 + r;
+    const uint32_t lane_off = uint32_t(quarter * 32) << 16;
+    uint8_t* rowPT = smem + S::kPT + r * 128;
+    uint8_t* rowDST = smem + S::kDST + r * 128;
+    bool ok = true;
+    for (int it = 0; it < niter && ok; ++it) {
+      const int h = hk * group + it / nq;
+      const int q0 = (qt_lo + it % nq) * AB_BQ;
+      const bool need_mask = (q0 < k0 + AB_BK - 1) || (p.window >= 0 && q0 + AB_BQ - 1 - k0 > p.window) ||
+                             (q0 + AB_BQ > p.T);
+      // each warp keeps its own copy of the per-query vectors: no cross-warp barrier needed
+      float* lse_b = s_vec + quarter * 256 + (it & 1) * 64;
+      float* del_b = lse_b + 128;
+      for (int t = lane; t < 64; t += 32) {
+        const int q = q0 + t;
+        const long long vi = ((long long)b * p.Hq + h) * p.T + q;
+        lse_b[t] = q < p.T ? p.lse2[vi] : INFINITY;
+        del_b[t] = q < p.T ? p.delta[vi] : 0.f;
+      }
+      __syncwarp();
+      ok = __all_sync(0xffffffffu, mbar_wait(st_full, it & 1, abort_word));
+      if (!ok) break;
+      tc_fence_after();
+      float pr[64];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_ST + lane_off + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int qi = c * 32 + i;
+          float e = exp2f(__uint_as_float(v[i]) * p.scale_log2 - lse_b[qi]);
+          if (need_mask) {
+            const int q = q0 + qi;
+            if (key > q || q >= p.T || (p.window >= 0 && q - key > p.window)) e = 0.f;
+          }
+          pr[qi] = e;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = (c * 4 + g) ^ (r & 7);
+          uint4 u;
+          u.x = pack_bf16(pr[c * 32 + 8 * g + 0], pr[c * 32 + 8 * g + 1]);
+          u.y = pack_bf16(pr[c * 32 + 8 * g + 2], pr[c * 32 + 8 * g + 3]);
+          u.z = pack_bf16(pr[c * 32 + 8 * g + 4], pr[c * 32 + 8 * g + 5]);
+          u.w = pack_bf16(pr[c * 32 + 8 * g + 6], pr[c * 32 + 8 * g + 7]);
+          *reinterpret_cast<uint4*>(rowPT + chunk * 16) = u;
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_DPT + lane_off + c * 32, v);
+        tmem_ld_wait();
+        float ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int qi = c * 32 + i;
+          ds[i] = pr[qi] * (__uint_as_float(v[i]) - del_b[qi]) * p.scale;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = (c * 4 + g) ^ (r & 7);
+          uint4 u;
+          u.x = pack_bf16(ds[8 * g + 0], ds[8 * g + 1]);
+          u.y = pack_bf16(ds[8 * g + 2], ds[8 * g + 3]);
+          u.z = pack_bf16(ds[8 * g + 4], ds[8 * g + 5]);
+          u.w = pack_bf16(ds[8 * g + 6], ds[8 * g + 7]);
+          *reinterpret_cast<uint4*>(rowDST + chunk * 16) = u;
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+      // dQ^T of this step: lane = d, columns = the 64 queries
+      ok = __all_sync(0xffffffffu, mbar_wait(mma2_done, it & 1, abort_word));
+      if (!ok) break;
+      tc_fence_after();
+      float* dq_col = p.dq_acc + (long long)(row_base + q0) * (p.Hq * AB_D) + h * AB_D + r;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_DQT + lane_off + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int qi = c * 32 + i;
+          if (q0 + qi < p.T) atomicAdd(dq_col + (long long)qi * (p.Hq * AB_D), __uint_as_float(v[i]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_free);
+    }
+    // ---------------------------------------------------------------- dK / dV write-out
+    if (ok && niter > 0) {
+      tc_fence_after();
+      const bool key_ok = key < p.T;
+      const long long cols = (long long)(p.Hq + 2 * p.Hkv) * AB_D;
+      __nv_bfloat16* dk_row = p.dqkv + (long long)(row_base + key) * cols + k_col;
+      __nv_bfloat16* dv_row = p.dqkv + (long long)(row_base + key) * cols + v_col;
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32((c < 4 ? t_DK : t_DV) + lane_off + (c & 3) * 32, v);
+        tmem_ld_wait();
+        if (key_ok) {
+          __nv_bfloat16* dst = (c < 4 ? dk_row : dv_row) + (c & 3) * 32;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 u;
+            u.x = pack_bf16(__uint_as_float(v[8 * g + 0]), __uint_as_float(v[8 * g + 1]));
+            u.y = pack_bf16(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3]));
+            u.z = pack_bf16(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5]));
+            u.w = pack_bf16(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7]));
+            *reinterpret_cast<uint4*>(dst + g * 8) = u;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_word);
+}
+
+}  // namespace nga
+
+extern "C" int nga_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse2,
+                            void* dqkv, float* dq_acc, float* delta, int B, int T, int Hq, int Hkv,
+                            int D, int window, float scale, int* status, void* stream) {
+  using namespace nga;
+  if (D != AB_D || B <= 0 || T <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return -1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const long long rows = (long long)B * T;
+  const long long cols = (long long)(Hq + 2 * Hkv) * D;
+  const long long ocols = (long long)Hq * D;
+  CUtensorMap tm_kv, tm_q, tm_do;
+  int rc = make_tmap_3d(&tm_kv, qkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, cols, rows, 1, cols * 2,
+                        rows * cols * 2, 64, 128, true);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tm_q, qkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, cols, rows, 1, cols * 2,
+                    rows * cols * 2, 64, 64, true);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tm_do, dout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ocols, rows, 1, ocols * 2,
+                    rows * ocols * 2, 64, 64, true);
+  if (rc) return rc;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         AttnBwdSmem::kTotal);
+    if (e != cudaSuccess) return -1000 - (int)e;
+    attr_done = true;
+  }
+  {
+    const long long warps = rows * Hq;
+    attn_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout),
+        delta, B, T, Hq);
+    count_launch();
+  }
+  cudaMemsetAsync(dq_acc, 0, sizeof(float) * rows * ocols, st);
+  AttnBwdParams p;
+  p.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv);
+  p.dq_acc = dq_acc;
+  p.lse2 = lse2;
+  p.delta = delta;
+  p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.window = window;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  dim3 grid((T + AB_BK - 1) / AB_BK, Hkv, B);
+  attn_bwd_kernel<<<grid, AB_THREADS, AttnBwdSmem::kTotal, st>>>(tm_kv, tm_q, tm_do, p);
+  count_launch();
+  {
+    const long long n4 = rows * ocols / 4;
+    attn_dq_cast_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(
+        dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), rows, (int)ocols, (int)cols);
+    count_launch();
+  }
+  NGA_CHECK_LAUNCH();
+  return 0;
+}

@@ -1,0 +1,337 @@
+// Causal / sliding-window GQA attention forward on tcgen05 + TMEM, head_dim 128.
+//
+// Semantics are those of flash_attn_func(q, k, v, causal=True, window_size=(left, 0)) as used by
+// the reference trunk (src/archlab/architectures/base.py:325-333; mask rule in
+// src/archlab/speedrun/attention.py:175-181): key j is visible to query i iff j <= i and
+// (left < 0 or i - j <= left).  Softmax scale is 1/sqrt(D).
+//
+// One CTA owns a 128-query tile of one (batch, head).  Roles: warp 0 TMA producer (Q once, then a
+// two-stage K/V ring), warp 1 MMA issuer, warps 2..5 softmax (thread = query row = TMEM lane).
+// S = Q K^T is double-buffered in TMEM so the next tile's QK^T overlaps this tile's softmax; P goes
+// back to the tensor core through shared memory in the canonical 128-byte-swizzled K-major layout;
+// O accumulates in TMEM and is rescaled only when a row maximum grows by more than 2^8.
+#include "ptx.cuh"
+#include "host_util.h"
+#include "attention.h"
+#include <cuda.h>
+
+namespace nga {
+
+constexpr int AT_D = 128;
+constexpr int AT_BQ = 128;
+constexpr int AT_BK = 128;
+constexpr int AT_TILE_BYTES = 128 * 128 * 2;  // 32 KB: one 128 x 128 bf16 tile (two 64-wide blocks)
+constexpr int AT_THREADS = 192;
+
+struct AttnFwdParams {
+  __nv_bfloat16* out;   // [B*T, Hq*D]
+  float* lse2;          // [B, Hq, T]  log2-domain log-sum-exp of the scaled scores
+  int B, T, Hq, Hkv, window;
+  float scale_log2;
+  int* status;
+};
+
+struct AttnFwdSmem {
+  static constexpr int kQ = 0;
+  static constexpr int kK = AT_TILE_BYTES;                 // 2 stages
+  static constexpr int kV = kK + 2 * AT_TILE_BYTES;        // 2 stages
+  static constexpr int kP = kV + 2 * AT_TILE_BYTES;
+  static constexpr int kBar = kP + AT_TILE_BYTES;
+  static constexpr int kTotal = kBar + 16 * 8 + 16 + 1024;
+};
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
+  using S = AttnFwdSmem;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kBar);
+  uint64_t* q_full = bars + 0;
+  uint64_t* kv_full = bars + 1;    // [2]
+  uint64_t* kv_empty = bars + 3;   // [2]
+  uint64_t* s_full = bars + 5;     // [2]
+  uint64_t* s_free = bars + 7;     // [2]
+  uint64_t* p_full = bars + 9;
+  uint64_t* p_empty = bars + 10;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_qt = (p.T + AT_BQ - 1) / AT_BQ;
+  const int qt = num_qt - 1 - blockIdx.x;   // heavy (late) tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int q0 = qt * AT_BQ;
+  const int k_lo = (p.window < 0) ? 0 : max(0, q0 - p.window) / AT_BK;
+  const int k_hi = min(q0 + AT_BQ - 1, p.T - 1) / AT_BK;
+  const int ntiles = k_hi - k_lo + 1;
+  const int row_base = b * p.T;
+  const int q_col = h * AT_D;
+  const int k_col = (p.Hq + hk) * AT_D;
+  const int v_col = (p.Hq + p.Hkv + hk) * AT_D;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(p_empty, 1);
+    *abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_S0 = tmem_base;            // 2 x 128 columns
+  const uint32_t tmem_O = tmem_base + 256;       // 128 columns
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm);
+      mbar_expect_tx(q_full, AT_TILE_BYTES);
+      tma_load_3d(smem + S::kQ, &tm, q_full, q_col, row_base + q0, 0);
+      tma_load_3d(smem + S::kQ + 16384, &tm, q_full, q_col + 64, row_base + q0, 0);
+      bool ok = true;
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int st = j & 1;
+        ok = mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1u, abort_word);
+        if (!ok) break;
+        const int krow = row_base + (k_lo + j) * AT_BK;
+        uint8_t* sK = smem + S::kK + st * AT_TILE_BYTES;
+        uint8_t* sV = smem + S::kV + st * AT_TILE_BYTES;
+        mbar_expect_tx(&kv_full[st], 2 * AT_TILE_BYTES);
+        tma_load_3d(sK, &tm, &kv_full[st], k_col, krow, 0);
+        tma_load_3d(sK + 16384, &tm, &kv_full[st], k_col + 64, krow, 0);
+        tma_load_3d(sV, &tm, &kv_full[st], v_col, krow, 0);
+        tma_load_3d(sV + 16384, &tm, &kv_full[st], v_col + 64, krow, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, 1);
+      const uint32_t sQ = smem_u32(smem + S::kQ);
+      const uint32_t sP = smem_u32(smem + S::kP);
+      bool ok = mbar_wait(q_full, 0, abort_word);
+      auto issue_qk = [&](int j) {
+        const uint32_t sK = smem_u32(smem + S::kK + (j & 1) * AT_TILE_BYTES);
+        const uint32_t d = tmem_S0 + uint32_t((j & 1) * 128);
+#pragma unroll
+        for (int k = 0; k < AT_D / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_bf16_ss(d, umma_smem_desc(sQ + off, 16, 1024), umma_smem_desc(sK + off, 16, 1024),
+                       idesc_qk, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[j & 1]);
+      };
+      if (ok) ok = mbar_wait(&kv_full[0], 0, abort_word);
+      if (ok) {
+        tc_fence_after();
+        issue_qk(0);
+      }
+      for (int j = 0; j < ntiles && ok; ++j) {
+        if (j + 1 < ntiles) {
+          const int jn = j + 1;
+          ok = mbar_wait(&kv_full[jn & 1], (jn >> 1) & 1, abort_word);
+          if (ok) ok = mbar_wait(&s_free[jn & 1], ((jn >> 1) & 1) ^ 1u, abort_word);
+          if (!ok) break;
+          tc_fence_after();
+          issue_qk(jn);
+        }
+        ok = mbar_wait(p_full, j & 1, abort_word);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sV = smem_u32(smem + S::kV + (j & 1) * AT_TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < AT_BK / 16; ++k) {
+          // A = P: K-major, keys contiguous, two 64-key blocks of 16 KB.
+          // B = V: MN-major, rows are keys (128 B = 64 d), the two 64-wide d blocks 16 KB apart.
+          const uint64_t da = umma_smem_desc(sP + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+          const uint64_t db = umma_smem_desc(sV + k * 2048, 16384, 1024);
+          umma_bf16_ss(tmem_O, da, db, idesc_pv, (j | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[j & 1]);
+        umma_commit(p_empty);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax warps
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;           // query row inside the tile
+    const int q = q0 + r;
+    const uint32_t lane_off = uint32_t(quarter * 32) << 16;
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    uint8_t* sP = smem + S::kP;
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int k0 = (k_lo + j) * AT_BK;
+      const bool need_mask = (k0 + AT_BK - 1 > q0) || (p.window >= 0 && q0 + AT_BQ - 1 - k0 > p.window);
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_word));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tS = tmem_S0 + uint32_t((j & 1) * 128) + lane_off;
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tS + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]);
+          if (need_mask) {
+            const int key = k0 + c * 32 + i;
+            if (key > q || (p.window >= 0 && q - key > p.window)) s = -INFINITY;
+          }
+          mx = fmaxf(mx, s);
+        }
+      }
+      mx *= p.scale_log2;
+      // P buffer and O are free once the previous PV has completed
+      if (j > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(p_empty, (j - 1) & 1, abort_word));
+        if (!ok) break;
+        tc_fence_after();
+      }
+      const float m_new = fmaxf(m_ref, mx);
+      const bool grow = (m_new > m_ref + 8.f) || (m_ref == -INFINITY);
+      if (__any_sync(0xffffffffu, grow)) {
+        // rows of this warp rescale together (the TMEM accesses are warp-collective)
+        const float m_use = grow ? m_new : m_ref;
+        const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_use);
+        if (j > 0) {
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            uint32_t o[16];
+            tmem_ld_32x16(tmem_O + lane_off + c * 16, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x16(tmem_O + lane_off + c * 16, o);
+          }
+          tmem_st_wait();
+        }
+        l_sum *= alpha;
+        m_ref = m_use;
+      }
+      // pass 2: probabilities -> bf16 -> swizzled shared memory
+      float psum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tS + c * 32, v);
+        tmem_ld_wait();
+        float pr[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]);
+          float e = exp2f(s * p.scale_log2 - m_ref);
+          if (need_mask) {
+            const int key = k0 + c * 32 + i;
+            if (key > q || (p.window >= 0 && q - key > p.window)) e = 0.f;
+          }
+          pr[i] = e;
+          psum += e;
+        }
+        // 32 keys = 64 B = four 16-byte chunks of this row's 128-byte line in key block (c >> 1)
+        uint8_t* line = sP + (c >> 1) * 16384 + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = ((c & 1) * 4 + g) ^ (r & 7);
+          uint4 u;
+          u.x = pack_bf16(pr[8 * g + 0], pr[8 * g + 1]);
+          u.y = pack_bf16(pr[8 * g + 2], pr[8 * g + 3]);
+          u.z = pack_bf16(pr[8 * g + 4], pr[8 * g + 5]);
+          u.w = pack_bf16(pr[8 * g + 6], pr[8 * g + 7]);
+          *reinterpret_cast<uint4*>(line + chunk * 16) = u;
+        }
+      }
+      l_sum += psum;
+      // S buffer consumed; P written
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&s_free[j & 1]);
+        mbar_arrive(p_full);
+      }
+    }
+    // ---------------------------------------------------------------- epilogue
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(p_empty, (ntiles - 1) & 1, abort_word));
+    if (ok) {
+      tc_fence_after();
+      const float inv = 1.f / l_sum;
+      const bool q_ok = q < p.T;
+      __nv_bfloat16* orow = p.out + (long long)(row_base + q) * (p.Hq * AT_D) + q_col;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_O + lane_off + c * 32, v);
+        tmem_ld_wait();
+        if (q_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 u;
+            u.x = pack_bf16(__uint_as_float(v[8 * g + 0]) * inv, __uint_as_float(v[8 * g + 1]) * inv);
+            u.y = pack_bf16(__uint_as_float(v[8 * g + 2]) * inv, __uint_as_float(v[8 * g + 3]) * inv);
+            u.z = pack_bf16(__uint_as_float(v[8 * g + 4]) * inv, __uint_as_float(v[8 * g + 5]) * inv);
+            u.w = pack_bf16(__uint_as_float(v[8 * g + 6]) * inv, __uint_as_float(v[8 * g + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = u;
+          }
+        }
+      }
+      if (q_ok) p.lse2[((long long)b * p.Hq + h) * p.T + q] = m_ref + log2f(l_sum);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_word);
+}
+
+}  // namespace nga
+
+extern "C" int nga_attn_fwd(const void* qkv, void* out, float* lse2, int B, int T, int Hq, int Hkv,
+                            int D, int window, float scale, int* status, void* stream) {
+  using namespace nga;
+  if (D != AT_D || B <= 0 || T <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return -1;
+  const long long cols = (long long)(Hq + 2 * Hkv) * D;
+  CUtensorMap tm;
+  int rc = make_tmap_3d(&tm, qkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, cols, (long long)B * T, 1,
+                        cols * 2, (long long)B * T * cols * 2, 64, 128, true);
+  if (rc) return rc;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         AttnFwdSmem::kTotal);
+    if (e != cudaSuccess) return -1000 - (int)e;
+    attr_done = true;
+  }
+  AttnFwdParams p;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.lse2 = lse2;
+  p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.window = window;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  dim3 grid((T + AT_BQ - 1) / AT_BQ, Hq, B);
+  attn_fwd_kernel<<<grid, AT_THREADS, AttnFwdSmem::kTotal, reinterpret_cast<cudaStream_t>(stream)>>>(tm, p);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}

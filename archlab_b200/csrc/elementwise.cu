@@ -1,0 +1,622 @@
+// Memory-bound kernels of the speedrun GPT trunk, one warp per token row, 16-byte vector accesses.
+// They state the arithmetic of src/archlab/architectures/base.py (norm :147, smear :884-893,
+// resid/x0 mix :925, backout :981-984) as fused passes so each activation is read and written once.
+//
+// Layout: activations are [tokens, C] bf16 row-major, C a multiple of 8.
+#include "ptx.cuh"
+#include "host_util.h"
+#include "elementwise.h"
+
+namespace nga {
+
+constexpr float kRmsEps = 1.1920929e-07f;  // torch.finfo(float32).eps, F.rms_norm's default
+
+struct bf8 { uint4 u; };
+
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&f)[8]) {
+  uint4 u = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 v = __bfloat1622float2(h[i]);
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16(f[0], f[1]);
+  u.y = pack_bf16(f[2], f[3]);
+  u.z = pack_bf16(f[4], f[5]);
+  u.w = pack_bf16(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+
+// Per-block reduction of `n` per-warp partial scalars followed by one atomicAdd each.
+template <int N>
+__device__ __forceinline__ void block_atomic_add(float (&v)[N], float* const (&dst)[N]) {
+  __shared__ float red[N][32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    float s = warp_sum(v[i]);
+    if (lane == 0) red[i][warp] = s;
+  }
+  __syncthreads();
+  if (warp == 0) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      float s = lane < nw ? red[i][lane] : 0.f;
+      s = warp_sum(s);
+      if (lane == 0 && dst[i] != nullptr) atomicAdd(dst[i], s);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// x1 = a * x + b * x0 ; n = rmsnorm(x1).  a, b are read from device scalars (layer lambdas).
+// With x0 == nullptr the mix is skipped (x1 = x, not written) and only n is produced.
+// ------------------------------------------------------------------------------------------------
+__global__ void mix_norm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                    const __nv_bfloat16* __restrict__ x0, const float* a_ptr,
+                                    const float* b_ptr, float a_scale, float b_scale,
+                                    __nv_bfloat16* __restrict__ x1,
+                                    __nv_bfloat16* __restrict__ n, long long rows, int C) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float a = a_scale * (a_ptr ? *a_ptr : 1.f), b = b_scale * (b_ptr ? *b_ptr : 0.f);
+  const __nv_bfloat16* xr = x + row * C;
+  float ss = 0.f;
+  for (int c = lane * 8; c < C; c += 256) {
+    float v[8];
+    ld8(xr + c, v);
+    if (x0) {
+      float w[8];
+      ld8(x0 + row * C + c, w);
+      // round to bf16 first: the stored residual is what later layers and the backward see
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = __bfloat162float(__float2bfloat16(a * v[i] + b * w[i]));
+      st8(x1 + row * C + c, v);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / C + kRmsEps);
+  const __nv_bfloat16* src = (x0 ? x1 : x) + row * C;
+  for (int c = lane * 8; c < C; c += 256) {
+    float v[8];
+    ld8(src + c, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] *= rstd;
+    st8(n + row * C + c, v);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// RMSNorm backward, optionally fused with the residual add and the lambda mix backward.
+//   g   = dres + rstd * (dn - y * mean(dn * y)),  y = x * rstd
+//   mode 0 : dx = g
+//   mode 1 : dx = a * g ; dx0 += b * g ; da += <g, xprev> ; db += <g, x0>
+// dres may be nullptr (treated as zero).
+// ------------------------------------------------------------------------------------------------
+__global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                const __nv_bfloat16* __restrict__ dn,
+                                const __nv_bfloat16* __restrict__ dres,
+                                __nv_bfloat16* __restrict__ dx, int mode, const float* a_ptr,
+                                const float* b_ptr, float a_scale, float b_scale,
+                                const __nv_bfloat16* __restrict__ xprev,
+                                const __nv_bfloat16* __restrict__ x0, __nv_bfloat16* dx0,
+                                int dx0_init, float* da, float* db, long long rows, int C) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  float pa = 0.f, pb = 0.f;
+  if (row < rows) {
+    const long long off = row * C;
+    float ss = 0.f, dot = 0.f;
+    for (int c = lane * 8; c < C; c += 256) {
+      float v[8], g[8];
+      ld8(x + off + c, v);
+      ld8(dn + off + c, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { ss += v[i] * v[i]; dot += v[i] * g[i]; }
+    }
+    ss = warp_sum(ss);
+    dot = warp_sum(dot);
+    const float rstd = rsqrtf(ss / C + kRmsEps);
+    const float coef = dot * rstd * rstd / C;   // mean(dn * y) * rstd, applied to x
+    const float a = a_scale * ((mode == 1 && a_ptr) ? *a_ptr : 1.f);
+    const float b = b_scale * ((mode == 1 && b_ptr) ? *b_ptr : 0.f);
+    for (int c = lane * 8; c < C; c += 256) {
+      float v[8], g[8], r[8];
+      ld8(x + off + c, v);
+      ld8(dn + off + c, g);
+      if (dres) ld8(dres + off + c, r);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) g[i] = (dres ? r[i] : 0.f) + rstd * (g[i] - v[i] * coef);
+      if (mode == 1) {
+        float xp[8], xz[8], o[8];
+        ld8(xprev + off + c, xp);
+        ld8(x0 + off + c, xz);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { pa += g[i] * xp[i]; pb += g[i] * xz[i]; }
+        if (dx0_init) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = b * g[i];
+        } else {
+          ld8(dx0 + off + c, o);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += b * g[i];
+        }
+        st8(dx0 + off + c, o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) g[i] *= a;
+      }
+      st8(dx + off + c, g);
+    }
+  }
+  if (mode == 1) {
+    float v[2] = {pa, pb};
+    float* const dst[2] = {da, db};
+    block_atomic_add<2>(v, dst);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Embedding + RMSNorm + smear (base.py:876-893).
+//   e[t]  = rmsnorm(wte[idx[t]])
+//   x0[t] = e[t] + lam * sigmoid(<gate_w, e[t, :G]>) * e[t-1]      for t > 0 within a sequence
+// The gate pre-activation is kept per token for the backward.
+// ------------------------------------------------------------------------------------------------
+__global__ void embed_fwd_kernel(const long long* __restrict__ idx,
+                                 const __nv_bfloat16* __restrict__ wte,
+                                 const float* __restrict__ gate_w, const float* lam_ptr,
+                                 __nv_bfloat16* __restrict__ x0, float* __restrict__ gate_pre,
+                                 long long rows, int T, int C, int G) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int t = int(row % T);
+  const float lam = *lam_ptr;
+  const __nv_bfloat16* cur = wte + idx[row] * (long long)C;
+  const __nv_bfloat16* prv = t > 0 ? wte + idx[row - 1] * (long long)C : cur;
+  float ss = 0.f, sp = 0.f;
+  for (int c = lane * 8; c < C; c += 256) {
+    float v[8], w[8];
+    ld8(cur + c, v);
+    ld8(prv + c, w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { ss += v[i] * v[i]; sp += w[i] * w[i]; }
+  }
+  ss = warp_sum(ss);
+  sp = warp_sum(sp);
+  const float rs = rsqrtf(ss / C + kRmsEps), rp = rsqrtf(sp / C + kRmsEps);
+  // gate pre-activation over the first G channels of the (bf16-rounded) normalised embedding
+  float gp = 0.f;
+  for (int c = lane; c < G; c += 32)
+    gp += gate_w[c] * __bfloat162float(__float2bfloat16(__bfloat162float(cur[c]) * rs));
+  gp = warp_sum(gp);
+  const float gate = t > 0 ? lam * sigmoidf_(gp) : 0.f;
+  if (lane == 0) gate_pre[row] = gp;
+  for (int c = lane * 8; c < C; c += 256) {
+    float v[8], w[8];
+    ld8(cur + c, v);
+    ld8(prv + c, w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float e = __bfloat162float(__float2bfloat16(v[i] * rs));
+      const float ep = __bfloat162float(__float2bfloat16(w[i] * rp));
+      v[i] = e + gate * ep;
+    }
+    st8(x0 + row * C + c, v);
+  }
+}
+
+// Backward of the above.  g = d(x0).  With e = rmsnorm(w):
+//   de[t]   = g[t] + gate[t+1] * g[t+1]                (own + contribution as "previous" token)
+//             + (first G channels) dgp[t] * gate_w     where dgp = lam * s(1-s) * <g[t], e[t-1]>
+//   dlam   += s * <g[t], e[t-1]> ; dgate_w += dgp[t] * e[t, :G]
+//   dw      = rmsnorm_bwd(w, de)  accumulated into the fp32 table gradient with vector atomics.
+__global__ void embed_bwd_kernel(const long long* __restrict__ idx,
+                                 const __nv_bfloat16* __restrict__ wte,
+                                 const float* __restrict__ gate_w, const float* lam_ptr,
+                                 const float* __restrict__ gate_pre,
+                                 const __nv_bfloat16* __restrict__ g, float* __restrict__ dwte,
+                                 float* dgate_w, float* dlam, long long rows, int T, int C, int G) {
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  float p_lam = 0.f;
+  if (row < rows) {
+    const int t = int(row % T);
+    const float lam = *lam_ptr;
+    const bool has_prev = t > 0, has_next = t + 1 < T;
+    const __nv_bfloat16* cur = wte + idx[row] * (long long)C;
+    const __nv_bfloat16* prv = has_prev ? wte + idx[row - 1] * (long long)C : cur;
+    float ss = 0.f, sp = 0.f;
+    for (int c = lane * 8; c < C; c += 256) {
+      float v[8], w[8];
+      ld8(cur + c, v);
+      ld8(prv + c, w);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { ss += v[i] * v[i]; sp += w[i] * w[i]; }
+    }
+    ss = warp_sum(ss);
+    sp = warp_sum(sp);
+    const float rs = rsqrtf(ss / C + kRmsEps), rp = rsqrtf(sp / C + kRmsEps);
+    // <g[t], e[t-1]>
+    float gdot = 0.f;
+    if (has_prev) {
+      for (int c = lane * 8; c < C; c += 256) {
+        float gv[8], w[8];
+        ld8(g + row * C + c, gv);
+        ld8(prv + c, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) gdot += gv[i] * __bfloat162float(__float2bfloat16(w[i] * rp));
+      }
+    }
+    gdot = warp_sum(gdot);
+    const float s = sigmoidf_(gate_pre[row]);
+    const float dgp = has_prev ? lam * s * (1.f - s) * gdot : 0.f;
+    if (has_prev) p_lam = s * gdot / 32.f;   // every lane holds the full sum; divide before reduce
+    const float gate_next = has_next ? lam * sigmoidf_(gate_pre[row + 1]) : 0.f;
+    // de and its dot with e for the norm backward
+    float dot = 0.f;
+    for (int c = lane * 8; c < C; c += 256) {
+      float v[8], gv[8], gn[8];
+      ld8(cur + c, v);
+      ld8(g + row * C + c, gv);
+      if (has_next) ld8(g + (row + 1) * C + c, gn);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float de = gv[i] + (has_next ? gate_next * gn[i] : 0.f);
+        if (c + i < G) de += dgp * gate_w[c + i];
+        dot += de * v[i];
+      }
+    }
+    dot = warp_sum(dot);
+    const float coef = dot * rs * rs / C;
+    float* drow = dwte + idx[row] * (long long)C;
+    for (int c = lane * 8; c < C; c += 256) {
+      float v[8], gv[8], gn[8];
+      ld8(cur + c, v);
+      ld8(g + row * C + c, gv);
+      if (has_next) ld8(g + (row + 1) * C + c, gn);
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float de = gv[i] + (has_next ? gate_next * gn[i] : 0.f);
+        if (c + i < G) {
+          de += dgp * gate_w[c + i];
+          atomicAdd(dgate_w + c + i, dgp * __bfloat162float(__float2bfloat16(v[i] * rs)));
+        }
+        o[i] = rs * (de - v[i] * coef);
+      }
+      atomicAdd(reinterpret_cast<float4*>(drow + c), make_float4(o[0], o[1], o[2], o[3]));
+      atomicAdd(reinterpret_cast<float4*>(drow + c + 4), make_float4(o[4], o[5], o[6], o[7]));
+    }
+  }
+  float v[1] = {p_lam};
+  float* const dst[1] = {dlam};
+  block_atomic_add<1>(v, dst);
+}
+
+// ------------------------------------------------------------------------------------------------
+// In-place post-processing of the fused QKV projection (base.py:231-265, :316-323):
+//   q, k : half-split RoPE -> parameter-free RMSNorm over the head -> * gain
+//   v    : v + 3 * sigmoid(<gate_w[h], n[:, :GC]>) * ve_table[idx]      (layers with value embeds)
+// qkv is [tokens, (Hq + 2 Hkv) * D]; one warp per (token, head slot).  rstd [tokens, Hq + Hkv] and
+// the gate pre-activations [tokens, Hkv] are kept for the backward.  D is a multiple of 64.
+// ------------------------------------------------------------------------------------------------
+__global__ void qkv_post_fwd_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ cosT,
+                                    const float* __restrict__ sinT, float gain,
+                                    const long long* __restrict__ idx,
+                                    const __nv_bfloat16* __restrict__ ve_table,
+                                    const float* __restrict__ gate_w,
+                                    const __nv_bfloat16* __restrict__ n, int GC, int C,
+                                    float* __restrict__ rstd_out, float* __restrict__ gate_pre,
+                                    long long rows, int T, int Hq, int Hkv, int D) {
+  const int lane = threadIdx.x & 31;
+  const int slots = Hq + 2 * Hkv;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= rows * slots) return;
+  const long long row = w / slots;
+  const int slot = int(w % slots);
+  __nv_bfloat16* p = qkv + row * (long long)slots * D + (long long)slot * D;
+  const int half = D / 2;
+  if (slot < Hq + Hkv) {
+    const int t = int(row % T);
+    float ss = 0.f;
+    float y1[4], y2[4];
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const int j = lane + 32 * m;
+      if (j < half) {
+        const float c = cosT[t * half + j], s = sinT[t * half + j];
+        const float x1 = __bfloat162float(p[j]), x2 = __bfloat162float(p[j + half]);
+        // the reference rounds the rotated value to bf16 before normalising
+        y1[m] = __bfloat162float(__float2bfloat16(x1 * c + x2 * s));
+        y2[m] = __bfloat162float(__float2bfloat16(x2 * c - x1 * s));
+        ss += y1[m] * y1[m] + y2[m] * y2[m];
+      }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / D + kRmsEps);
+    if (lane == 0) rstd_out[row * (Hq + Hkv) + slot] = rstd;
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const int j = lane + 32 * m;
+      if (j < half) {
+        p[j] = __float2bfloat16(__bfloat162float(__float2bfloat16(y1[m] * rstd)) * gain);
+        p[j + half] = __float2bfloat16(__bfloat162float(__float2bfloat16(y2[m] * rstd)) * gain);
+      }
+    }
+  } else if (ve_table != nullptr) {
+    const int h = slot - Hq - Hkv;
+    float gp = 0.f;
+    for (int c = lane; c < GC; c += 32) gp += gate_w[h * GC + c] * __bfloat162float(n[row * C + c]);
+    gp = warp_sum(gp);
+    if (lane == 0) gate_pre[row * Hkv + h] = gp;
+    const float gate = 3.f * sigmoidf_(gp);
+    const __nv_bfloat16* ve = ve_table + idx[row] * (long long)(Hkv * D) + (long long)h * D;
+    for (int j = lane; j < D; j += 32)
+      p[j] = __float2bfloat16(__bfloat162float(p[j]) + gate * __bfloat162float(ve[j]));
+  }
+}
+
+// Backward, in place on dqkv (gradient w.r.t. the post-processed q', k', v').  qkv holds the saved
+// post-processed values.  Writes dgp [tokens, Hkv] (gradient of the gate pre-activation) and
+// accumulates the value-embedding table gradient with atomics.
+__global__ void qkv_post_bwd_kernel(__nv_bfloat16* __restrict__ dqkv,
+                                    const __nv_bfloat16* __restrict__ qkv,
+                                    const float* __restrict__ cosT, const float* __restrict__ sinT,
+                                    float gain, const long long* __restrict__ idx,
+                                    const __nv_bfloat16* __restrict__ ve_table,
+                                    const float* __restrict__ rstd_in,
+                                    const float* __restrict__ gate_pre, float* __restrict__ dgp_out,
+                                    float* __restrict__ dve_table, long long rows, int T, int Hq,
+                                    int Hkv, int D) {
+  const int lane = threadIdx.x & 31;
+  const int slots = Hq + 2 * Hkv;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= rows * slots) return;
+  const long long row = w / slots;
+  const int slot = int(w % slots);
+  const long long off = row * (long long)slots * D + (long long)slot * D;
+  __nv_bfloat16* dp = dqkv + off;
+  const __nv_bfloat16* p = qkv + off;
+  const int half = D / 2;
+  if (slot < Hq + Hkv) {
+    const int t = int(row % T);
+    const float rstd = rstd_in[row * (Hq + Hkv) + slot];
+    // y = q' / gain (normalised, rotated); dy = gain * dq'
+    float dot = 0.f;
+    for (int j = lane; j < D; j += 32)
+      dot += (__bfloat162float(dp[j]) * gain) * (__bfloat162float(p[j]) / gain);
+    dot = warp_sum(dot) / D;
+    for (int j = lane; j < half; j += 32) {
+      const float c = cosT[t * half + j], s = sinT[t * half + j];
+      const float y1 = __bfloat162float(p[j]) / gain, y2 = __bfloat162float(p[j + half]) / gain;
+      const float d1 = rstd * (__bfloat162float(dp[j]) * gain - y1 * dot);
+      const float d2 = rstd * (__bfloat162float(dp[j + half]) * gain - y2 * dot);
+      dp[j] = __float2bfloat16(d1 * c - d2 * s);
+      dp[j + half] = __float2bfloat16(d1 * s + d2 * c);
+    }
+  } else if (ve_table != nullptr) {
+    const int h = slot - Hq - Hkv;
+    const float s = sigmoidf_(gate_pre[row * Hkv + h]);
+    const __nv_bfloat16* ve = ve_table + idx[row] * (long long)(Hkv * D) + (long long)h * D;
+    float* dve = dve_table + idx[row] * (long long)(Hkv * D) + (long long)h * D;
+    float dot = 0.f;
+    for (int j = lane; j < D; j += 32) {
+      const float g = __bfloat162float(dp[j]);
+      dot += g * __bfloat162float(ve[j]);
+      atomicAdd(dve + j, 3.f * s * g);
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) dgp_out[row * Hkv + h] = 3.f * s * (1.f - s) * dot;
+  }
+}
+
+// dn[:, :GC] += sum_h dgp[:, h] * gate_w[h, :] ; dgate_w[h, c] += sum_rows dgp[row, h] * n[row, c]
+__global__ void gate_bwd_kernel(__nv_bfloat16* __restrict__ dn, const __nv_bfloat16* __restrict__ n,
+                                const float* __restrict__ dgp, const float* __restrict__ gate_w,
+                                float* __restrict__ dgate_w, long long rows, int C, int GC, int H) {
+  // one thread per (row, c); block-level reduction of dgate_w through shared memory
+  extern __shared__ float sh[];   // H * GC partial sums
+  for (int i = threadIdx.x; i < H * GC; i += blockDim.x) sh[i] = 0.f;
+  __syncthreads();
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gid / GC;
+  const int c = int(gid % GC);
+  if (row < rows) {
+    const float nv = __bfloat162float(n[row * C + c]);
+    float add = 0.f;
+    for (int h = 0; h < H; ++h) {
+      const float d = dgp[row * H + h];
+      add += d * gate_w[h * GC + c];
+      atomicAdd(&sh[h * GC + c], d * nv);
+    }
+    dn[row * C + c] = __float2bfloat16(__bfloat162float(dn[row * C + c]) + add);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < H * GC; i += blockDim.x) atomicAdd(dgate_w + i, sh[i]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Soft-capped cross entropy over a chunk of logits, forward and backward in one pass
+// (base.py:150-181 with the symmetric tanh cap of :991-996).  One block per row.
+//   z = cap * tanh(l / cap);  loss = log(sum exp z) - z[target];
+//   dl = gscale * (softmax(z) - onehot) * (1 - tanh^2)          written in place over the logits
+// |z| <= cap = 15, so exp(z) needs no running maximum in fp32.  target == -1 rows are ignored.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+softcap_ce_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
+                  float* __restrict__ loss_rows, float cap, float gscale, long long ld, int V) {
+  __shared__ float red[8];
+  __shared__ float total_s;
+  const long long row = blockIdx.x;
+  __nv_bfloat16* l = logits + row * ld;
+  const long long tgt = targets[row];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float inv_cap = 1.f / cap;
+  float sum = 0.f;
+  const int V8 = V & ~7;
+  for (int c = threadIdx.x * 8; c < V8; c += 256 * 8) {
+    float v[8];
+    ld8(l + c, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sum += __expf(cap * tanhf(v[i] * inv_cap));
+  }
+  for (int c = V8 + threadIdx.x; c < V; c += 256)
+    sum += __expf(cap * tanhf(__bfloat162float(l[c]) * inv_cap));
+  sum = warp_sum(sum);
+  if (lane == 0) red[warp] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += red[i];
+    total_s = t;
+    float loss = 0.f;
+    if (tgt >= 0) {
+      const float zt = cap * tanhf(__bfloat162float(l[tgt]) * inv_cap);
+      loss = __logf(t) - zt;
+    }
+    loss_rows[row] = loss;
+  }
+  __syncthreads();
+  const float inv_total = 1.f / total_s;
+  const float gs = tgt >= 0 ? gscale : 0.f;
+  for (int c = threadIdx.x * 8; c < V8; c += 256 * 8) {
+    float v[8];
+    ld8(l + c, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float th = tanhf(v[i] * inv_cap);
+      const float p = __expf(cap * th) * inv_total;
+      v[i] = gs * (p - ((long long)(c + i) == tgt ? 1.f : 0.f)) * (1.f - th * th);
+    }
+    st8(l + c, v);
+  }
+  for (int c = V8 + threadIdx.x; c < V; c += 256) {
+    const float th = tanhf(__bfloat162float(l[c]) * inv_cap);
+    const float p = __expf(cap * th) * inv_total;
+    l[c] = __float2bfloat16(gs * (p - ((long long)c == tgt ? 1.f : 0.f)) * (1.f - th * th));
+  }
+}
+
+}  // namespace nga
+
+// ------------------------------------------------------------------------------------------------
+// Launchers
+// ------------------------------------------------------------------------------------------------
+using namespace nga;
+#define BF(p) reinterpret_cast<const __nv_bfloat16*>(p)
+#define BFW(p) reinterpret_cast<__nv_bfloat16*>(p)
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+static inline unsigned warp_grid(long long warps, int warps_per_block) {
+  return (unsigned)((warps + warps_per_block - 1) / warps_per_block);
+}
+
+extern "C" int nga_mix_norm_fwd(const void* x, const void* x0, const float* a, const float* b,
+                                float a_scale, float b_scale, void* x1, void* n, long long rows,
+                                int C, void* stream) {
+  if (C % 8 || rows <= 0) return -1;
+  mix_norm_fwd_kernel<<<warp_grid(rows, 8), 256, 0, ST(stream)>>>(BF(x), BF(x0), a, b, a_scale,
+                                                                  b_scale, BFW(x1), BFW(n), rows, C);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int nga_norm_bwd(const void* x, const void* dn, const void* dres, void* dx, int mode,
+                            const float* a, const float* b, float a_scale, float b_scale,
+                            const void* xprev, const void* x0, void* dx0, int dx0_init, float* da,
+                            float* db, long long rows, int C, void* stream) {
+  if (C % 8 || rows <= 0) return -1;
+  norm_bwd_kernel<<<warp_grid(rows, 8), 256, 0, ST(stream)>>>(
+      BF(x), BF(dn), BF(dres), BFW(dx), mode, a, b, a_scale, b_scale, BF(xprev), BF(x0), BFW(dx0),
+      dx0_init, da, db, rows, C);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int nga_embed_fwd(const long long* idx, const void* wte, const float* gate_w,
+                             const float* lam, void* x0, float* gate_pre, long long rows, int T,
+                             int C, int G, void* stream) {
+  if (C % 8 || rows <= 0) return -1;
+  embed_fwd_kernel<<<warp_grid(rows, 8), 256, 0, ST(stream)>>>(idx, BF(wte), gate_w, lam, BFW(x0),
+                                                               gate_pre, rows, T, C, G);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int nga_embed_bwd(const long long* idx, const void* wte, const float* gate_w,
+                             const float* lam, const float* gate_pre, const void* g, float* dwte,
+                             float* dgate_w, float* dlam, long long rows, int T, int C, int G,
+                             void* stream) {
+  if (C % 8 || rows <= 0) return -1;
+  embed_bwd_kernel<<<warp_grid(rows, 8), 256, 0, ST(stream)>>>(
+      idx, BF(wte), gate_w, lam, gate_pre, BF(g), dwte, dgate_w, dlam, rows, T, C, G);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int nga_qkv_post_fwd(void* qkv, const float* cosT, const float* sinT, float gain,
+                                const long long* idx, const void* ve_table, const float* gate_w,
+                                const void* n, int GC, int C, float* rstd, float* gate_pre,
+                                long long rows, int T, int Hq, int Hkv, int D, void* stream) {
+  if (D % 64 || D > 256 || rows <= 0) return -1;
+  const long long warps = rows * (Hq + 2 * Hkv);
+  qkv_post_fwd_kernel<<<warp_grid(warps, 8), 256, 0, ST(stream)>>>(
+      BFW(qkv), cosT, sinT, gain, idx, BF(ve_table), gate_w, BF(n), GC, C, rstd, gate_pre, rows, T,
+      Hq, Hkv, D);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int nga_qkv_post_bwd(void* dqkv, const void* qkv, const float* cosT, const float* sinT,
+                                float gain, const long long* idx, const void* ve_table,
+                                const float* rstd, const float* gate_pre, float* dgp,
+                                float* dve_table, long long rows, int T, int Hq, int Hkv, int D,
+                                void* stream) {
+  if (D % 64 || D > 256 || rows <= 0) return -1;
+  const long long warps = rows * (Hq + 2 * Hkv);
+  qkv_post_bwd_kernel<<<warp_grid(warps, 8), 256, 0, ST(stream)>>>(
+      BFW(dqkv), BF(qkv), cosT, sinT, gain, idx, BF(ve_table), rstd, gate_pre, dgp, dve_table, rows,
+      T, Hq, Hkv, D);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int nga_gate_bwd(void* dn, const void* n, const float* dgp, const float* gate_w,
+                            float* dgate_w, long long rows, int C, int GC, int H, void* stream) {
+  if (rows <= 0) return -1;
+  const long long threads = rows * GC;
+  gate_bwd_kernel<<<(unsigned)((threads + 255) / 256), 256, H * GC * sizeof(float), ST(stream)>>>(
+      BFW(dn), BF(n), dgp, gate_w, dgate_w, rows, C, GC, H);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int nga_softcap_ce(void* logits, const long long* targets, float* loss_rows, float cap,
+                              float gscale, long long rows, long long ld, int V, void* stream) {
+  if (rows <= 0 || (ld % 8)) return -1;
+  softcap_ce_kernel<<<(unsigned)rows, 256, 0, ST(stream)>>>(BFW(logits), targets, loss_rows, cap,
+                                                            gscale, ld, V);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}

@@ -1,0 +1,382 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA-fed shared-memory ring, tcgen05.mma with
+// the accumulator double-buffered in TMEM, and a register epilogue that fuses the elementwise tail
+// (scale, residual/accumulate, ReLU^2, ReLU^2 backward) into the store.
+//
+//   D[b] = epi(alpha * A[b] * B[b]^T, Aux[b])        A: M x K, B: N x K  (logical shapes)
+//
+// Either operand may be stored K-major (K contiguous) or MN-major (its M/N index contiguous); the
+// three orientations of a linear layer (forward, dgrad, wgrad) are therefore all served without a
+// transposed copy.  This replaces the cuBLAS calls behind F.linear in the reference
+// (src/archlab/architectures/base.py:182-190) and the batched Newton-Schulz matmuls of
+// src/archlab/optimizers/speedrun.py:199-208.
+//
+// Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..5 =
+// epilogue (one 32-lane TMEM quarter each).
+#include "ptx.cuh"
+#include "gemm.h"
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <mutex>
+#include <unordered_map>
+#include <string>
+#include <cstring>
+#include <atomic>
+
+namespace nga {
+
+constexpr int BM = 128;
+constexpr int BK = 64;           // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kGemmThreads = 192;
+
+struct GemmParams {
+  int M, N, K, batch;
+  void* D;
+  const void* aux;
+  long long ldd, ldaux;          // row strides (elements)
+  long long sD, sAux;            // batch strides (elements)
+  int epi, out_fp32, aux_fp32;
+  float alpha, beta;
+  int* status;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  // full[S], empty[S], tmem_full[2], tmem_empty[2], then holder + abort word
+  static constexpr int kTotal = kBarOffset + (2 * kStages + 4) * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& b, int& mb, int& nb) {
+  const int per_batch = num_m * num_n;
+  b = tile / per_batch;
+  int r = tile - b * per_batch;
+  constexpr int kGroup = 16;
+  const int per_group = kGroup * num_n;
+  const int g = r / per_group;
+  r -= g * per_group;
+  const int first_m = g * kGroup;
+  const int gm = min(kGroup, num_m - first_m);
+  mb = first_m + r % gm;
+  nb = r / gm;
+}
+
+__device__ __forceinline__ float epi_apply(int epi, float acc, float aux, float alpha, float beta) {
+  switch (epi) {
+    case kEpiScale: return alpha * acc;
+    case kEpiAxpby: return alpha * acc + beta * aux;
+    case kEpiRelu2: { float r = fmaxf(alpha * acc, 0.f); return r * r; }
+    case kEpiMulDRelu2: return alpha * acc * 2.f * sqrtf(fmaxf(aux, 0.f));
+    default: return acc;
+  }
+}
+
+template <int BN, int A_MN, int B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  using S = GemmSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
+  uint64_t* empty_bar = full_bar + S::kStages;
+  uint64_t* tfull_bar = empty_bar + S::kStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int num_tiles = num_m * num_n * p.batch;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int b, mb, nb;
+        tile_coords(tile, num_m, num_n, b, mb, nb);
+        const int m0 = mb * BM, n0 = nb * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word);
+          if (!ok) break;
+          uint8_t* sA = smem + stage * S::kStageBytes;
+          uint8_t* sB = sA + S::kABytes;
+          mbar_expect_tx(&full_bar[stage], S::kStageBytes);
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_3d(sA + j * 8192, &tmA, &full_bar[stage], m0 + j * 64, kb * BK, b);
+          } else {
+            tma_load_3d(sA, &tmA, &full_bar[stage], kb * BK, m0, b);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(sB + j * 8192, &tmB, &full_bar[stage], n0 + j * 64, kb * BK, b);
+          } else {
+            tma_load_3d(sB, &tmB, &full_bar[stage], kb * BK, n0, b);
+          }
+          if (++stage == S::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_word);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + uint32_t(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_word);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + stage * S::kStageBytes);
+          const uint32_t sB = sA + S::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = A_MN ? umma_smem_desc(sA + k * (UMMA_K * 128), 8192, 1024)
+                                     : umma_smem_desc(sA + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t db = B_MN ? umma_smem_desc(sB + k * (UMMA_K * 128), 8192, 1024)
+                                     : umma_smem_desc(sB + k * (UMMA_K * 2), 16, 1024);
+            umma_bf16_ss(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == S::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    const bool vec_ok = p.out_fp32 ? ((p.ldd & 3) == 0 && (p.sD & 3) == 0 &&
+                                      (reinterpret_cast<uintptr_t>(p.D) & 15) == 0)
+                                   : ((p.ldd & 7) == 0 && (p.sD & 7) == 0 &&
+                                      (reinterpret_cast<uintptr_t>(p.D) & 15) == 0);
+    const bool need_aux = (p.epi == kEpiAxpby || p.epi == kEpiMulDRelu2);
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int b, mb, nb;
+      tile_coords(tile, num_m, num_n, b, mb, nb);
+      ok = __all_sync(0xffffffffu, mbar_wait(&tfull_bar[acc], acc_phase, abort_word));
+      if (!ok) break;
+      tc_fence_after();
+      const int row = mb * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + uint32_t(acc * BN) + (uint32_t(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = nb * BN + c * 32;
+        if (col0 >= p.N) break;   // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + uint32_t(c * 32), r);
+        tmem_ld_wait();
+        if (row_ok) {
+          const long long doff = (long long)b * p.sD + (long long)row * p.ldd + col0;
+          const long long aoff = (long long)b * p.sAux + (long long)row * p.ldaux + col0;
+          const int ncol = min(32, p.N - col0);
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (need_aux) {
+            if (p.aux_fp32) {
+              const float* ax = reinterpret_cast<const float*>(p.aux) + aoff;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                v[i] = epi_apply(p.epi, v[i], i < ncol ? ax[i] : 0.f, p.alpha, p.beta);
+            } else {
+              const __nv_bfloat16* ax = reinterpret_cast<const __nv_bfloat16*>(p.aux) + aoff;
+              if (ncol == 32 && (p.ldaux & 7) == 0 && (p.sAux & 7) == 0 &&
+                  (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  uint4 pk = reinterpret_cast<const uint4*>(ax)[q];
+                  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    float2 f = __bfloat1622float2(h[i]);
+                    v[q * 8 + 2 * i] = epi_apply(p.epi, v[q * 8 + 2 * i], f.x, p.alpha, p.beta);
+                    v[q * 8 + 2 * i + 1] = epi_apply(p.epi, v[q * 8 + 2 * i + 1], f.y, p.alpha, p.beta);
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  v[i] = epi_apply(p.epi, v[i], i < ncol ? __bfloat162float(ax[i]) : 0.f, p.alpha,
+                                   p.beta);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = epi_apply(p.epi, v[i], 0.f, p.alpha, p.beta);
+          }
+          if (p.out_fp32) {
+            float* d = reinterpret_cast<float*>(p.D) + doff;
+            if (ncol == 32 && vec_ok) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                reinterpret_cast<float4*>(d)[q] =
+                    make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < ncol) d[i] = v[i];
+            }
+          } else {
+            __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + doff;
+            if (ncol == 32 && vec_ok) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 pk;
+                pk.x = pack_bf16(v[8 * q], v[8 * q + 1]);
+                pk.y = pack_bf16(v[8 * q + 2], v[8 * q + 3]);
+                pk.z = pack_bf16(v[8 * q + 4], v[8 * q + 5]);
+                pk.w = pack_bf16(v[8 * q + 6], v[8 * q + 7]);
+                reinterpret_cast<uint4*>(d)[q] = pk;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < ncol) d[i] = __float2bfloat16(v[i]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ------------------------------------------------------------------ tear-down
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_word);
+}
+
+}  // namespace nga
+
+// ------------------------------------------------------------------------------------------------
+// Host launcher
+// ------------------------------------------------------------------------------------------------
+#include "host_util.h"
+
+namespace nga {
+
+template <int BN, int A_MN, int B_MN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                       cudaStream_t stream) {
+  using S = GemmSmem<BN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    if (e != cudaSuccess) return -1000 - (int)e;
+    attr_done = true;
+  }
+  const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
+  const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
+  kern<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, p);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}
+
+}  // namespace nga
+
+extern "C" int nga_gemm_bf16(const void* A, const void* B, void* D, const void* aux, int M, int N,
+                             int K, int batch, long long lda, long long ldb, long long ldd,
+                             long long ldaux, long long sA, long long sB, long long sD,
+                             long long sAux, int a_mn, int b_mn, int epi, int out_fp32,
+                             int aux_fp32, float alpha, float beta, int* status, void* stream) {
+  using namespace nga;
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -1;
+  if ((lda & 7) || (ldb & 7) || (sA & 7) || (sB & 7)) return -5;
+  // Tile width: 256 when that still fills the machine, else 128 (more, smaller tiles).
+  const long long tiles256 = (long long)((M + 127) / 128) * ((N + 255) / 256) * batch;
+  const bool bn256 = (N > 128) && tiles256 >= sm_count();
+  const int BNsel = bn256 ? 256 : 128;
+  CUtensorMap ta, tb;
+  int rc;
+  if (a_mn)
+    rc = make_tmap_3d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, batch, lda * 2,
+                      (batch > 1 ? sA : (long long)K * lda) * 2, 64, 64, true);
+  else
+    rc = make_tmap_3d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, batch, lda * 2,
+                      (batch > 1 ? sA : (long long)M * lda) * 2, 64, 128, true);
+  if (rc) return rc;
+  if (b_mn)
+    rc = make_tmap_3d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, batch, ldb * 2,
+                      (batch > 1 ? sB : (long long)K * ldb) * 2, 64, 64, true);
+  else
+    rc = make_tmap_3d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, batch, ldb * 2,
+                      (batch > 1 ? sB : (long long)N * ldb) * 2, 64, BNsel, true);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.batch = batch;
+  p.D = D; p.aux = aux; p.ldd = ldd; p.ldaux = ldaux; p.sD = sD; p.sAux = sAux;
+  p.epi = epi; p.out_fp32 = out_fp32; p.aux_fp32 = aux_fp32; p.alpha = alpha; p.beta = beta;
+  p.status = status;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define NGA_DISPATCH(BNV)                                                    \
+  if (a_mn && b_mn) return launch_gemm<BNV, 1, 1>(ta, tb, p, st);            \
+  if (a_mn && !b_mn) return launch_gemm<BNV, 1, 0>(ta, tb, p, st);           \
+  if (!a_mn && b_mn) return launch_gemm<BNV, 0, 1>(ta, tb, p, st);           \
+  return launch_gemm<BNV, 0, 0>(ta, tb, p, st);
+  if (bn256) { NGA_DISPATCH(256) }
+  NGA_DISPATCH(128)
+#undef NGA_DISPATCH
+}

@@ -1,0 +1,35 @@
+// C ABI of the native library (loaded with ctypes).  All pointers are device pointers unless a
+// comment says otherwise; `stream` is a cudaStream_t passed as void*.  Functions return 0 on
+// success or a negative number for a host-side error (bad shape / alignment / CUDA launch error).
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Epilogue selector of nga_gemm_bf16.
+enum {
+  kEpiScale = 0,      // D = alpha * acc
+  kEpiAxpby = 1,      // D = alpha * acc + beta * aux        (aux may alias D)
+  kEpiRelu2 = 2,      // D = relu(alpha * acc)^2
+  kEpiMulDRelu2 = 3,  // D = alpha * acc * 2 * sqrt(aux)     (aux = relu(h)^2 saved by kEpiRelu2)
+};
+
+// D[b] = epi(alpha * A[b] * B[b]^T).  A is M x K, B is N x K (logical).  a_mn / b_mn = 1 when the
+// operand is stored with its M (resp. N) index contiguous, i.e. as a K x M (K x N) row-major
+// array; lda / ldb are then the strides between consecutive K rows.  Strides are in elements;
+// lda, ldb and the batch strides must be multiples of 8 and the base pointers 16-byte aligned.
+int nga_gemm_bf16(const void* A, const void* B, void* D, const void* aux, int M, int N, int K,
+                  int batch, long long lda, long long ldb, long long ldd, long long ldaux,
+                  long long sA, long long sB, long long sD, long long sAux, int a_mn, int b_mn,
+                  int epi, int out_fp32, int aux_fp32, float alpha, float beta, int* status,
+                  void* stream);
+
+// Number of kernels this library has launched since load (every launcher increments it).
+long long nga_launch_count(void);
+void nga_launch_count_reset(void);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,105 @@
+"""bf16 GEMM with fused epilogues on the tcgen05 kernel (``csrc/gemm.cu``).
+
+``gemm(a, b, a_mn=…, b_mn=…)`` computes ``D = epi(alpha * A @ B^T, aux)`` where the logical A is
+``M x K`` and the logical B is ``N x K``:
+
+* ``a_mn=False``: ``a`` is stored ``[M, K]`` (K contiguous); ``a_mn=True``: stored ``[K, M]``.
+* ``b_mn=False``: ``b`` is stored ``[N, K]``; ``b_mn=True``: stored ``[K, N]``.
+
+So a linear layer ``y = x W^T`` uses ``gemm(x, W)``, its dgrad ``gemm(dy, W, b_mn=True)`` and its
+wgrad ``gemm(dy, x, a_mn=True, b_mn=True)``, none of which needs a transposed copy.  A leading
+batch dimension is supported on all operands.  CPU tensors take an fp32 PyTorch path (that path
+is the numerical oracle of the GPU tests); CUDA tensors always run the native kernel.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import native
+
+__all__ = ["gemm", "EPI_SCALE", "EPI_AXPBY", "EPI_RELU2", "EPI_MUL_DRELU2"]
+
+EPI_SCALE, EPI_AXPBY, EPI_RELU2, EPI_MUL_DRELU2 = 0, 1, 2, 3
+
+
+def _logical(a: torch.Tensor, mn: bool) -> torch.Tensor:
+    return a.transpose(-1, -2) if mn else a
+
+
+def gemm_reference(a, b, *, a_mn=False, b_mn=False, aux=None, epi=EPI_SCALE, alpha=1.0, beta=0.0,
+                   out_dtype=torch.bfloat16):
+    """fp32 PyTorch statement of the kernel's arithmetic."""
+    A = _logical(a, a_mn).float()
+    B = _logical(b, b_mn).float()
+    acc = alpha * (A @ B.transpose(-1, -2))
+    if epi == EPI_SCALE:
+        d = acc
+    elif epi == EPI_AXPBY:
+        d = acc + beta * aux.float()
+    elif epi == EPI_RELU2:
+        d = torch.relu(acc).square()
+    elif epi == EPI_MUL_DRELU2:
+        d = acc * 2.0 * aux.float().clamp_min(0).sqrt()
+    else:
+        raise ValueError(f"unknown epilogue {epi}")
+    return d.to(out_dtype)
+
+
+def _strides(t: torch.Tensor) -> tuple[int, int, int]:
+    """(batch, row stride, batch stride) of a 2-D / 3-D tensor with unit inner stride."""
+    if t.stride(-1) != 1:
+        raise ValueError("innermost dimension must be contiguous")
+    if t.dim() == 2:
+        return 1, t.stride(0), 0
+    if t.dim() == 3:
+        return t.size(0), t.stride(1), t.stride(0)
+    raise ValueError("expected a 2-D or 3-D tensor")
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: torch.Tensor | None = None, aux: torch.Tensor | None = None, epi: int = EPI_SCALE,
+         alpha: float = 1.0, beta: float = 0.0, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    if a.device.type != "cuda":
+        d = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, aux=aux, epi=epi, alpha=alpha, beta=beta,
+                           out_dtype=out.dtype if out is not None else out_dtype)
+        if out is not None:
+            out.copy_(d)
+            return out
+        return d
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("gemm operands must be bf16")
+    ba, lda, sa = _strides(a)
+    bb, ldb, sb = _strides(b)
+    K = a.size(-2) if a_mn else a.size(-1)
+    M = a.size(-1) if a_mn else a.size(-2)
+    Kb = b.size(-2) if b_mn else b.size(-1)
+    N = b.size(-1) if b_mn else b.size(-2)
+    if K != Kb:
+        raise ValueError(f"K mismatch: {K} vs {Kb}")
+    batch = max(ba, bb)
+    if ba != bb:
+        raise ValueError("batch mismatch (operands do not broadcast over the batch dimension)")
+    if out is None:
+        shape = (batch, M, N) if (a.dim() == 3 or b.dim() == 3) else (M, N)
+        out = torch.empty(shape, dtype=out_dtype, device=a.device)
+    bo, ldd, sd = _strides(out)
+    if out.size(-2) != M or out.size(-1) != N or bo != (batch if out.dim() == 3 else 1):
+        raise ValueError("output shape mismatch")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise TypeError("output must be bf16 or fp32")
+    ldaux = saux = 0
+    aux_fp32 = 0
+    if epi in (EPI_AXPBY, EPI_MUL_DRELU2):
+        if aux is None:
+            raise ValueError("this epilogue needs aux")
+        _, ldaux, saux = _strides(aux)
+        if aux.dtype not in (torch.bfloat16, torch.float32):
+            raise TypeError("aux must be bf16 or fp32")
+        aux_fp32 = int(aux.dtype == torch.float32)
+    rc = native.lib().nga_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), aux.data_ptr() if aux is not None else None,
+        M, N, K, batch, lda, ldb, ldd, ldaux, sa if ba > 1 else 0, sb if bb > 1 else 0, sd, saux,
+        int(a_mn), int(b_mn), epi, int(out.dtype == torch.float32), aux_fp32, float(alpha),
+        float(beta), native.status_word(a.device).data_ptr(), native.stream_ptr())
+    native.check(rc, "nga_gemm_bf16")
+    return out
