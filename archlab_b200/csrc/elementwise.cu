@@ -163,7 +163,7 @@ __global__ void norm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
     }
   }
   if (mode == 1) {
-    float v[2] = {pa, pb};
+    float v[2] = {pa * a_scale, pb * b_scale};
     float* const dst[2] = {da, db};
     block_atomic_add<2>(v, dst);
   }
@@ -511,6 +511,31 @@ softcap_ce_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restric
   }
 }
 
+// y = a * x + b * y over bf16 arrays (n a multiple of 8)
+__global__ void axpby_bf16_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                                  float a, float b, long long n) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i >= n) return;
+  float xv[8], yv[8];
+  ld8(x + i, xv);
+  ld8(y + i, yv);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) yv[k] = a * xv[k] + b * yv[k];
+  st8(y + i, yv);
+}
+
+// dst(bf16) = src(fp32), n a multiple of 4
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                     long long n) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  const float4 v = *reinterpret_cast<const float4*>(src + i);
+  uint2 u;
+  u.x = pack_bf16(v.x, v.y);
+  u.y = pack_bf16(v.z, v.w);
+  *reinterpret_cast<uint2*>(dst + i) = u;
+}
+
 }  // namespace nga
 
 // ------------------------------------------------------------------------------------------------
@@ -616,6 +641,22 @@ extern "C" int nga_softcap_ce(void* logits, const long long* targets, float* los
   if (rows <= 0 || (ld % 8)) return -1;
   softcap_ce_kernel<<<(unsigned)rows, 256, 0, ST(stream)>>>(BFW(logits), targets, loss_rows, cap,
                                                             gscale, ld, V);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int nga_axpby_bf16(const void* x, void* y, float a, float b, long long n, void* stream) {
+  if (n <= 0 || (n % 8)) return -1;
+  axpby_bf16_kernel<<<(unsigned)((n / 8 + 255) / 256), 256, 0, ST(stream)>>>(BF(x), BFW(y), a, b, n);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int nga_cast_f32_bf16(const float* src, void* dst, long long n, void* stream) {
+  if (n <= 0 || (n % 4)) return -1;
+  cast_f32_bf16_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, ST(stream)>>>(src, BFW(dst), n);
   count_launch();
   NGA_CHECK_LAUNCH();
   return 0;

@@ -25,6 +25,8 @@ int nga_gate_bwd(void* dn, const void* n, const float* dgp, const float* gate_w,
                  long long rows, int C, int GC, int H, void* stream);
 int nga_softcap_ce(void* logits, const long long* targets, float* loss_rows, float cap,
                    float gscale, long long rows, long long ld, int V, void* stream);
+int nga_axpby_bf16(const void* x, void* y, float a, float b, long long n, void* stream);
+int nga_cast_f32_bf16(const float* src, void* dst, long long n, void* stream);
 #ifdef __cplusplus
 }
 #endif

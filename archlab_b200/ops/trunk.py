@@ -32,6 +32,10 @@ native.register_signature("nga_attn_bwd", [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i
                                            _f, _vp, _vp])
 
 
+native.register_signature("nga_axpby_bf16", [_vp, _vp, _f, _f, _ll, _vp])
+native.register_signature("nga_cast_f32_bf16", [_vp, _vp, _ll, _vp])
+
+
 def _p(t):
     return None if t is None else t.data_ptr()
 
@@ -227,3 +231,17 @@ def attention_reference(q, k, v, window):
         mask = mask & ((i - j) <= window)
     s = s.masked_fill(~mask, float("-inf"))
     return (torch.softmax(s, dim=-1) @ vf).transpose(1, 2)
+
+
+def axpby_(y, x, a=1.0, b=1.0):
+    """y = a * x + b * y in place (bf16)."""
+    rc = native.lib().nga_axpby_bf16(_p(x), _p(y), a, b, y.numel(), _s())
+    native.check(rc, "nga_axpby_bf16")
+    return y
+
+
+def cast_to_bf16_(dst, src):
+    """dst (bf16) = src (fp32), same number of elements (a multiple of 4)."""
+    rc = native.lib().nga_cast_f32_bf16(_p(src), _p(dst), src.numel(), _s())
+    native.check(rc, "nga_cast_f32_bf16")
+    return dst

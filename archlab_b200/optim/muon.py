@@ -47,7 +47,8 @@ def _mm(a: Tensor, b: Tensor, *, b_mn: bool, a_mn: bool = False, aux: Tensor | N
         alpha: float = 1.0, beta: float = 0.0) -> Tensor:
     """alpha * op(a) @ op(b) + beta * aux on stacked matrices (``ops.gemm`` operand convention);
     tcgen05 kernel on CUDA bf16."""
-    if a.is_cuda and a.dtype == torch.bfloat16:
+    if (a.is_cuda and a.dtype == torch.bfloat16 and a.size(-1) % 8 == 0 and b.size(-1) % 8 == 0
+            and min(a.size(-1), a.size(-2), b.size(-1), b.size(-2)) >= 64):
         from ..ops.gemm import EPI_AXPBY, EPI_SCALE, gemm
 
         return gemm(a, b, a_mn=a_mn, b_mn=b_mn, aux=aux, epi=EPI_AXPBY if aux is not None else EPI_SCALE,
