@@ -7,6 +7,8 @@ extern "C" {
 #endif
 int nga_attn_fwd(const void* qkv, void* out, float* lse2, int B, int T, int Hq, int Hkv, int D,
                  int window, float scale, int* status, void* stream);
+void nga_attn_set_prof(long long* device_ptr);
+void nga_attn_bwd_set_prof(long long* device_ptr);
 // dqkv receives the gradient in the same fused layout.  `dq_acc` is fp32 scratch
 // [B*T, Hq*128] that the kernel accumulates dQ into (it is zeroed by the launcher) and `delta`
 // is fp32 scratch [B, Hq, T].

@@ -29,6 +29,7 @@ struct AttnBwdParams {
   int B, T, Hq, Hkv, window;
   float scale, scale_log2;
   int* status;
+  long long* prof;       // optional phase cycle counters written by CTA (0,0,0)
 };
 
 struct AttnBwdSmem {
@@ -246,6 +247,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
     uint8_t* rowPT = smem + S::kPT + r * 128;
     uint8_t* rowDST = smem + S::kDST + r * 128;
     bool ok = true;
+    const bool prof_on = p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64;
+    long long pc[6] = {0, 0, 0, 0, 0, 0};
+    long long tp = clock64();
+#define NGA_PROFB(i) do { if (prof_on) { long long tn = clock64(); pc[i] += tn - tp; tp = tn; } } while (0)
     for (int it = 0; it < niter && ok; ++it) {
       const int h = hk * group + it / nq;
       const int q0 = (qt_lo + it % nq) * AB_BQ;
@@ -261,58 +266,49 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
         del_b[t] = q < p.T ? p.delta[vi] : 0.f;
       }
       __syncwarp();
+      NGA_PROFB(0);
       ok = __all_sync(0xffffffffu, mbar_wait(st_full, it & 1, abort_word));
       if (!ok) break;
+      NGA_PROFB(1);
       tc_fence_after();
-      float pr[64];
+      // S^T and dP^T rows (64 + 64 columns) with back-to-back loads and one wait
+      uint32_t sv[2][32], dv[2][32];
+      tmem_ld_32x32(t_ST + lane_off, sv[0]);
+      tmem_ld_32x32(t_ST + lane_off + 32, sv[1]);
+      tmem_ld_32x32(t_DPT + lane_off, dv[0]);
+      tmem_ld_32x32(t_DPT + lane_off + 32, dv[1]);
+      tmem_ld_wait();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_ST + lane_off + c * 32, v);
-        tmem_ld_wait();
+        float pr[32], ds[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int qi = c * 32 + i;
-          float e = exp2f(__uint_as_float(v[i]) * p.scale_log2 - lse_b[qi]);
+          float e = exp2f(fmaf(__uint_as_float(sv[c][i]), p.scale_log2, -lse_b[qi]));
           if (need_mask) {
             const int q = q0 + qi;
             if (key > q || q >= p.T || (p.window >= 0 && q - key > p.window)) e = 0.f;
           }
-          pr[qi] = e;
+          pr[i] = e;
+          ds[i] = e * (__uint_as_float(dv[c][i]) - del_b[qi]) * p.scale;
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const int chunk = (c * 4 + g) ^ (r & 7);
-          uint4 u;
-          u.x = pack_bf16(pr[c * 32 + 8 * g + 0], pr[c * 32 + 8 * g + 1]);
-          u.y = pack_bf16(pr[c * 32 + 8 * g + 2], pr[c * 32 + 8 * g + 3]);
-          u.z = pack_bf16(pr[c * 32 + 8 * g + 4], pr[c * 32 + 8 * g + 5]);
-          u.w = pack_bf16(pr[c * 32 + 8 * g + 6], pr[c * 32 + 8 * g + 7]);
+          uint4 u, w;
+          u.x = pack_bf16(pr[8 * g + 0], pr[8 * g + 1]);
+          u.y = pack_bf16(pr[8 * g + 2], pr[8 * g + 3]);
+          u.z = pack_bf16(pr[8 * g + 4], pr[8 * g + 5]);
+          u.w = pack_bf16(pr[8 * g + 6], pr[8 * g + 7]);
+          w.x = pack_bf16(ds[8 * g + 0], ds[8 * g + 1]);
+          w.y = pack_bf16(ds[8 * g + 2], ds[8 * g + 3]);
+          w.z = pack_bf16(ds[8 * g + 4], ds[8 * g + 5]);
+          w.w = pack_bf16(ds[8 * g + 6], ds[8 * g + 7]);
           *reinterpret_cast<uint4*>(rowPT + chunk * 16) = u;
+          *reinterpret_cast<uint4*>(rowDST + chunk * 16) = w;
         }
       }
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_DPT + lane_off + c * 32, v);
-        tmem_ld_wait();
-        float ds[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int qi = c * 32 + i;
-          ds[i] = pr[qi] * (__uint_as_float(v[i]) - del_b[qi]) * p.scale;
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int chunk = (c * 4 + g) ^ (r & 7);
-          uint4 u;
-          u.x = pack_bf16(ds[8 * g + 0], ds[8 * g + 1]);
-          u.y = pack_bf16(ds[8 * g + 2], ds[8 * g + 3]);
-          u.z = pack_bf16(ds[8 * g + 4], ds[8 * g + 5]);
-          u.w = pack_bf16(ds[8 * g + 6], ds[8 * g + 7]);
-          *reinterpret_cast<uint4*>(rowDST + chunk * 16) = u;
-        }
-      }
+      NGA_PROFB(2);
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
@@ -320,23 +316,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
       // dQ^T of this step: lane = d, columns = the 64 queries
       ok = __all_sync(0xffffffffu, mbar_wait(mma2_done, it & 1, abort_word));
       if (!ok) break;
+      NGA_PROFB(3);
       tc_fence_after();
       float* dq_col = p.dq_acc + (long long)(row_base + q0) * (p.Hq * AB_D) + h * AB_D + r;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_DQT + lane_off + c * 32, v);
+      {
+        uint32_t v[2][32];
+        tmem_ld_32x32(t_DQT + lane_off, v[0]);
+        tmem_ld_32x32(t_DQT + lane_off + 32, v[1]);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int qi = c * 32 + i;
-          if (q0 + qi < p.T) atomicAdd(dq_col + (long long)qi * (p.Hq * AB_D), __uint_as_float(v[i]));
-        }
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int qi = c * 32 + i;
+            if (q0 + qi < p.T) atomicAdd(dq_col + (long long)qi * (p.Hq * AB_D), __uint_as_float(v[c][i]));
+          }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_free);
+      NGA_PROFB(4);
     }
+    if (prof_on) { for (int i = 0; i < 6; ++i) p.prof[i] = pc[i]; p.prof[6] = niter; }
     // ---------------------------------------------------------------- dK / dV write-out
     if (ok && niter > 0) {
       tc_fence_after();
@@ -376,6 +377,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
 }
 
 }  // namespace nga
+
+static long long* g_attn_bwd_prof = nullptr;
+extern "C" void nga_attn_bwd_set_prof(long long* device_ptr) { g_attn_bwd_prof = device_ptr; }
 
 extern "C" int nga_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse2,
                             void* dqkv, float* dq_acc, float* delta, int B, int T, int Hq, int Hkv,
@@ -420,6 +424,7 @@ extern "C" int nga_attn_bwd(const void* qkv, const void* out, const void* dout, 
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  p.prof = g_attn_bwd_prof;
   dim3 grid((T + AB_BK - 1) / AB_BK, Hkv, B);
   attn_bwd_kernel<<<grid, AB_THREADS, AttnBwdSmem::kTotal, st>>>(tm_kv, tm_q, tm_do, p);
   count_launch();

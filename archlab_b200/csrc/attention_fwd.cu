@@ -29,6 +29,7 @@ struct AttnFwdParams {
   int B, T, Hq, Hkv, window;
   float scale_log2;
   int* status;
+  long long* prof;      // optional: 16 cycle counters written by CTA (0,0,0) (phase timing for tuning)
 };
 
 struct AttnFwdSmem {
@@ -173,37 +174,48 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
     float m_ref = -INFINITY, l_sum = 0.f;
     bool ok = true;
     uint8_t* sP = smem + S::kP;
+    const bool prof_on = p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64;
+    long long pc[6] = {0, 0, 0, 0, 0, 0};
+    long long tp = clock64();
+#define NGA_PROF(i) do { if (prof_on) { long long tn = clock64(); pc[i] += tn - tp; tp = tn; } } while (0)
     for (int j = 0; j < ntiles && ok; ++j) {
       const int k0 = (k_lo + j) * AT_BK;
       const bool need_mask = (k0 + AT_BK - 1 > q0) || (p.window >= 0 && q0 + AT_BQ - 1 - k0 > p.window);
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_word));
       if (!ok) break;
+      NGA_PROF(0);
       tc_fence_after();
       const uint32_t tS = tmem_S0 + uint32_t((j & 1) * 128) + lane_off;
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + c * 32, v);
-        tmem_ld_wait();
+      // The whole 128-column row goes to registers with four back-to-back loads and ONE wait, so
+      // the TMEM read latency is paid once per tile instead of once per 32 columns.
+      uint32_t sv[4][32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]);
-          if (need_mask) {
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + c * 32, sv[c]);
+      tmem_ld_wait();
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
             const int key = k0 + c * 32 + i;
-            if (key > q || (p.window >= 0 && q - key > p.window)) s = -INFINITY;
+            if (key > q || (p.window >= 0 && q - key > p.window)) sv[c][i] = 0xff800000u;  // -inf
           }
-          mx = fmaxf(mx, s);
-        }
       }
-      mx *= p.scale_log2;
+      // row maximum with four independent chains
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx4[c] = fmaxf(mx4[c], __uint_as_float(sv[c][i]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+      NGA_PROF(1);
       // P buffer and O are free once the previous PV has completed
       if (j > 0) {
         ok = __all_sync(0xffffffffu, mbar_wait(p_empty, (j - 1) & 1, abort_word));
         if (!ok) break;
         tc_fence_after();
       }
+      NGA_PROF(2);
       const float m_new = fmaxf(m_ref, mx);
       const bool grow = (m_new > m_ref + 8.f) || (m_ref == -INFINITY);
       if (__any_sync(0xffffffffu, grow)) {
@@ -212,37 +224,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
         const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_use);
         if (j > 0) {
 #pragma unroll 1
-          for (int c = 0; c < 8; ++c) {
-            uint32_t o[16];
-            tmem_ld_32x16(tmem_O + lane_off + c * 16, o);
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32(tmem_O + lane_off + c * 32, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x16(tmem_O + lane_off + c * 16, o);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(tmem_O + lane_off + c * 32, o);
           }
           tmem_st_wait();
         }
         l_sum *= alpha;
         m_ref = m_use;
       }
-      // pass 2: probabilities -> bf16 -> swizzled shared memory
-      float psum = 0.f;
-#pragma unroll 1
+      NGA_PROF(3);
+      // probabilities -> bf16 -> swizzled shared memory (masked entries are exp2(-inf) = 0)
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      const float m_sub = (m_ref == -INFINITY) ? 0.f : m_ref;
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tS + c * 32, v);
-        tmem_ld_wait();
         float pr[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(v[i]);
-          float e = exp2f(s * p.scale_log2 - m_ref);
-          if (need_mask) {
-            const int key = k0 + c * 32 + i;
-            if (key > q || (p.window >= 0 && q - key > p.window)) e = 0.f;
-          }
-          pr[i] = e;
-          psum += e;
+          pr[i] = exp2f(fmaf(__uint_as_float(sv[c][i]), p.scale_log2, -m_sub));
+          ps4[i & 3] += pr[i];
         }
         // 32 keys = 64 B = four 16-byte chunks of this row's 128-byte line in key block (c >> 1)
         uint8_t* line = sP + (c >> 1) * 16384 + r * 128;
@@ -257,7 +262,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
           *reinterpret_cast<uint4*>(line + chunk * 16) = u;
         }
       }
+      const float psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
       l_sum += psum;
+      NGA_PROF(4);
       // S buffer consumed; P written
       tc_fence_before();
       fence_proxy_async_smem();
@@ -266,7 +273,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
         mbar_arrive(&s_free[j & 1]);
         mbar_arrive(p_full);
       }
+      NGA_PROF(5);
     }
+    if (prof_on) { for (int i = 0; i < 6; ++i) p.prof[i] = pc[i]; p.prof[6] = ntiles; }
     // ---------------------------------------------------------------- epilogue
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(p_empty, (ntiles - 1) & 1, abort_word));
     if (ok) {
@@ -307,6 +316,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
 
 }  // namespace nga
 
+static long long* g_attn_prof = nullptr;
+// Tuning aid: when set, CTA (0,0,0) of the next forward launches writes per-phase cycle counts there.
+extern "C" void nga_attn_set_prof(long long* device_ptr) { g_attn_prof = device_ptr; }
+
 extern "C" int nga_attn_fwd(const void* qkv, void* out, float* lse2, int B, int T, int Hq, int Hkv,
                             int D, int window, float scale, int* status, void* stream) {
   using namespace nga;
@@ -329,6 +342,7 @@ extern "C" int nga_attn_fwd(const void* qkv, void* out, float* lse2, int B, int 
   p.B = B; p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  p.prof = g_attn_prof;
   dim3 grid((T + AT_BQ - 1) / AT_BQ, Hq, B);
   attn_fwd_kernel<<<grid, AT_THREADS, AttnFwdSmem::kTotal, reinterpret_cast<cudaStream_t>(stream)>>>(tm, p);
   count_launch();

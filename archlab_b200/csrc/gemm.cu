@@ -212,12 +212,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + uint32_t(acc * BN) + (uint32_t(quarter * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c2 = 0; c2 < BN / 64; ++c2) {
+        if (nb * BN + c2 * 64 >= p.N) break;   // warp-uniform
+        // two 32-column chunks per TMEM round trip
+        uint32_t r2[2][32];
+        tmem_ld_32x32(taddr + uint32_t(c2 * 64), r2[0]);
+        tmem_ld_32x32(taddr + uint32_t(c2 * 64 + 32), r2[1]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int hc = 0; hc < 2; ++hc) {
+        const int c = c2 * 2 + hc;
         const int col0 = nb * BN + c * 32;
         if (col0 >= p.N) break;   // warp-uniform
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + uint32_t(c * 32), r);
-        tmem_ld_wait();
+        uint32_t (&r)[32] = r2[hc];
         if (row_ok) {
           const long long doff = (long long)b * p.sD + (long long)row * p.ldd + col0;
           const long long aoff = (long long)b * p.sAux + (long long)row * p.ldaux + col0;
@@ -288,6 +295,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
         }
+      }
       }
       tc_fence_before();
       __syncwarp();

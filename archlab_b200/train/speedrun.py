@@ -83,10 +83,10 @@ class Trainer:
         self._dev_tokens.copy_(tokens, non_blocking=True)
         return self._dev_tokens
 
-    def train_step(self, tokens: torch.Tensor) -> float:
-        """One optimizer step on this rank's ``[local_batch, T+1]`` token block."""
+    def train_step_device(self, tok: torch.Tensor) -> torch.Tensor:
+        """One optimizer step on a token block already resident on the device; returns the mean
+        loss as a 0-d device tensor (no host synchronisation)."""
         cfg = self.cfg
-        tok = self._to_device(tokens)
         x, y = tok[:, :-1], tok[:, 1:]
         nb = x.size(0)
         mb = min(cfg.micro_batch, nb)
@@ -114,7 +114,12 @@ class Trainer:
         if self.engine is not None:
             self.engine.refresh_shadows()
         self.step_index += 1
-        return float((loss_sum / n_valid).item())
+        return loss_sum / n_valid
+
+    def train_step(self, tokens: torch.Tensor) -> float:
+        """One optimizer step on this rank's ``[local_batch, T+1]`` host token block (pinned memory
+        makes the copy asynchronous); returns the mean loss as a Python float."""
+        return float(self.train_step_device(self._to_device(tokens)).item())
 
     # ------------------------------------------------------------------
     def tokens_per_step(self, local_batch: int) -> int:

@@ -1,0 +1,203 @@
+"""Headline benchmark: training throughput of the nanochat-style speedrun GPT d20.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched under torchrun)
+    python bench.py --impl reference ...                      (the reference arm)
+    python bench.py --impl eager ...                          (this repo's cuBLAS/SDPA/NCCL decomposition)
+
+Config (BASELINE.json, config 2): 20 layers, d_model 1280, 10 heads x 128, QK-norm, vocab 65536,
+seq 2048, bf16, Muon + AdamW, ZeRO-1 style gradient sync inside the optimizer.  Weak scaling:
+32 sequences (64 Ki tokens) per GPU per step, i.e. 512 Ki tokens per step on 8 GPUs.  Tokens are
+Zipf(1.1) ids from seed 0 and weights are random-init, since no dataset or checkpoint is reachable.
+
+Rank 0 prints ONE JSON line.  ``value`` is device-timed (CUDA events around K steps whose inputs are
+already on the device, max over ranks); ``e2e`` times K further steps through the public
+``Trainer.train_step`` call, which copies each step's tokens from pinned host memory and reads the
+loss back.  The step's working set (tens of GB of activations and weights) is far larger than the
+126 MB L2, so no explicit L2 flush is needed between iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+REFERENCE_UNAVAILABLE = (
+    "pip install --no-index of the reference fails: its build backend (hatchling) and its "
+    "dependencies omegaconf / hydra-core are not in the offline wheelhouse"
+)
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int, period: float = 0.2):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._halt = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = int(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            names = {
+                "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            }
+            get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self._halt.is_set():
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                mask = int(get_reasons(h))
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+                time.sleep(self.period)
+        except Exception as exc:  # pragma: no cover - NVML missing
+            self.reasons.add(f"nvml_unavailable:{type(exc).__name__}")
+
+    def stop(self) -> dict:
+        self._halt.set()
+        self.join(timeout=2.0)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference", "eager"])
+    ap.add_argument("--local-batch", type=int, default=32, help="sequences per GPU per step")
+    ap.add_argument("--micro-batch", type=int, default=16)
+    ap.add_argument("--depth", type=int, default=20)
+    ap.add_argument("--seq-len", type=int, default=2048)
+    ap.add_argument("--vocab", type=int, default=65536)
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    if args.warmup < 3:
+        raise SystemExit("at least 3 warm-up steps are required")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    from archlab_b200.data.synthetic import ZipfTokens
+    from archlab_b200.models.nanochat import GPTConfig
+    from archlab_b200.ops import native
+    from archlab_b200.train.speedrun import Trainer, TrainerConfig
+
+    mcfg = GPTConfig.from_depth(args.depth, sequence_len=args.seq_len, vocab_size=args.vocab,
+                                compute_dtype=torch.bfloat16, matrix_init_recipe="normal-0.02")
+    tcfg = TrainerConfig(model=mcfg, micro_batch=args.micro_batch, num_iterations=10000)
+    trainer = Trainer(tcfg, device=dev)
+    if args.impl == "eager":
+        trainer.engine = None   # cuBLAS + SDPA + autograd on the same parameters
+    data = ZipfTokens(args.vocab, args.seq_len, args.local_batch, s=1.1, seed=0, rank=rank, pin=True)
+    n_blocks = args.warmup + 2 * args.steps
+    host_blocks = [data.block(i) for i in range(n_blocks)]
+    dev_blocks = [b.to(dev) for b in host_blocks[: args.warmup + args.steps]]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up (untimed)
+    for i in range(args.warmup):
+        trainer.train_step_device(dev_blocks[i])
+    barrier()
+    if trainer.engine is not None:
+        native.check_status()
+
+    # ---- device-timed region
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = native.launch_count() if native.available() else 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        loss = trainer.train_step_device(dev_blocks[args.warmup + i])
+    e1.record()
+    barrier()
+    dev_ms = e0.elapsed_time(e1)
+    launches = (native.launch_count() - launches0) if native.available() else 0
+    last_loss = float(loss.item())
+
+    # ---- end-to-end region: public API, pinned host inputs, loss read back every step
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        last_loss = trainer.train_step(host_blocks[args.warmup + args.steps + i])
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    barrier()
+    clocks = sampler.stop()
+    if trainer.engine is not None:
+        native.check_status()
+
+    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = float(times[0]), float(times[1])
+    tokens_per_step = args.local_batch * args.seq_len * world
+    value = tokens_per_step * args.steps / (dev_ms / 1e3)
+    e2e_value = tokens_per_step * args.steps / (e2e_ms / 1e3)
+    h2d = host_blocks[0].numel() * host_blocks[0].element_size()
+    if rank == 0:
+        out = {
+            "metric": "train tokens/sec/box", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic: Zipf(1.1) token ids from seed 0, random-init weights",
+            "impl": args.impl,
+            "config": {
+                "model": f"nanochat-speedrun-d{args.depth} ({mcfg.n_layer}L, d_model {mcfg.n_embd}, "
+                         f"{mcfg.n_head}x{mcfg.head_dim} heads, vocab {args.vocab})",
+                "global_batch": tokens_per_step, "seq_len": args.seq_len,
+                "parallelism": f"dp{world} (ZeRO-1 Muon/AdamW inside the optimizer)",
+                "micro_batch_sequences": args.micro_batch,
+                "l2": "working set per step far exceeds the 126 MB L2; no explicit flush",
+            },
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                    "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": int(launches),
+            "final_loss": last_loss,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
