@@ -19,7 +19,7 @@ namespace nga {
 constexpr int AB_D = 128;
 constexpr int AB_BK = 128;   // keys per CTA
 constexpr int AB_BQ = 64;    // queries per inner step
-constexpr int AB_THREADS = 192;
+constexpr int AB_THREADS = 320;   // TMA warp, MMA warp, 8 compute warps
 
 struct AttnBwdParams {
   __nv_bfloat16* dqkv;   // [B*T, (Hq+2Hkv)*D]
@@ -39,8 +39,9 @@ struct AttnBwdSmem {
   static constexpr int kDO = kQ + 2 * 16384;        // 2 x 16 KB
   static constexpr int kPT = kDO + 2 * 16384;       // 16 KB
   static constexpr int kDST = kPT + 16384;          // 16 KB
-  static constexpr int kVec = kDST + 16384;         // per warp: lse2[2][64], delta[2][64]
-  static constexpr int kBar = kVec + 4 * 256 * 4;
+  static constexpr int kDQ = kDST + 16384;          // 32 KB: fp32 dQ staging tile [64 q][128 d]
+  static constexpr int kVec = kDQ + 32768;          // per compute warp: [2][lse 32 | delta 32]
+  static constexpr int kBar = kVec + 8 * 128 * 4;
   static constexpr int kTotal = kBar + 16 * 8 + 16 + 1024;
 };
 
@@ -87,6 +88,7 @@ __global__ void __launch_bounds__(AB_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 128}
                 const __grid_constant__ CUtensorMap tm_q,    // qkv, box {64, 64}
                 const __grid_constant__ CUtensorMap tm_do,   // dout, box {64, 64}
+                const __grid_constant__ CUtensorMap tm_dq,   // dq_acc fp32, box {128, 64}, no swizzle
                 const AttnBwdParams p) {
   using S = AttnBwdSmem;
   extern __shared__ uint8_t smem_raw[];
@@ -100,9 +102,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
   uint64_t* pds_full = bars + 6;
   uint64_t* mma2_done = bars + 7;
   uint64_t* dq_free = bars + 8;
+  uint64_t* dqs_full = bars + 9;    // dQ staging tile written by all compute warps
+  uint64_t* dqs_free = bars + 10;   // previous bulk reduction has finished reading the tile
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
-  float* s_vec = reinterpret_cast<float*>(smem + S::kVec);       // [4 warps][lse 2x64 | delta 2x64]
+  float* s_vec = reinterpret_cast<float*>(smem + S::kVec);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
@@ -124,9 +128,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
       mbar_init(&qdo_empty[i], 1);
     }
     mbar_init(st_full, 1);
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, 8);
     mbar_init(mma2_done, 1);
-    mbar_init(dq_free, 4);
+    mbar_init(dq_free, 8);
+    mbar_init(dqs_full, 8);
+    mbar_init(dqs_free, 1);
     *abort_word = 0;
     fence_mbar_init();
   }
@@ -239,62 +245,71 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
       }
     }
   } else {
-    // ---------------------------------------------------------------- compute warps: thread = key
+    // ---------------------------------------------------------------- compute warps 2..9
+    // thread = key row (TMEM lane); warps 2..5 own query columns 0..31 of the step, warps 6..9 own
+    // columns 32..63, so every scheduler has two warps to hide TMEM / MUFU latency behind.
+    const int cw = warp - 2;
     const int quarter = warp & 3;
+    const int chalf = cw >> 2;
     const int r = quarter * 32 + lane;
     const int key = k0 + r;
     const uint32_t lane_off = uint32_t(quarter * 32) << 16;
+    const uint32_t col_off = uint32_t(chalf * 32);
     uint8_t* rowPT = smem + S::kPT + r * 128;
     uint8_t* rowDST = smem + S::kDST + r * 128;
+    float* sDQ = reinterpret_cast<float*>(smem + S::kDQ);          // [64 q][128 d] fp32
+    float* my_vec = s_vec + cw * 128;                              // [2][lse 32 | delta 32]
+    const bool tma_thread = (warp == 2 && lane == 0);
     bool ok = true;
     const bool prof_on = p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64;
     long long pc[6] = {0, 0, 0, 0, 0, 0};
     long long tp = clock64();
 #define NGA_PROFB(i) do { if (prof_on) { long long tn = clock64(); pc[i] += tn - tp; tp = tn; } } while (0)
+    // per-query vectors of the first step; later steps are prefetched one step ahead
+    float nxt_l = INFINITY, nxt_d = 0.f;
+    auto fetch_vec = [&](int it) {
+      const int h = hk * group + it / nq;
+      const int q = (qt_lo + it % nq) * AB_BQ + chalf * 32 + lane;
+      const long long vi = ((long long)b * p.Hq + h) * p.T + q;
+      nxt_l = q < p.T ? p.lse2[vi] : INFINITY;
+      nxt_d = q < p.T ? p.delta[vi] : 0.f;
+    };
+    if (niter > 0) fetch_vec(0);
     for (int it = 0; it < niter && ok; ++it) {
       const int h = hk * group + it / nq;
       const int q0 = (qt_lo + it % nq) * AB_BQ;
       const bool need_mask = (q0 < k0 + AB_BK - 1) || (p.window >= 0 && q0 + AB_BQ - 1 - k0 > p.window) ||
                              (q0 + AB_BQ > p.T);
-      // each warp keeps its own copy of the per-query vectors: no cross-warp barrier needed
-      float* lse_b = s_vec + quarter * 256 + (it & 1) * 64;
-      float* del_b = lse_b + 128;
-      for (int t = lane; t < 64; t += 32) {
-        const int q = q0 + t;
-        const long long vi = ((long long)b * p.Hq + h) * p.T + q;
-        lse_b[t] = q < p.T ? p.lse2[vi] : INFINITY;
-        del_b[t] = q < p.T ? p.delta[vi] : 0.f;
-      }
+      float* lse_b = my_vec + (it & 1) * 64;
+      float* del_b = lse_b + 32;
+      lse_b[lane] = nxt_l;
+      del_b[lane] = nxt_d;
       __syncwarp();
+      if (it + 1 < niter) fetch_vec(it + 1);     // global loads in flight during this step
       NGA_PROFB(0);
       ok = __all_sync(0xffffffffu, mbar_wait(st_full, it & 1, abort_word));
       if (!ok) break;
       NGA_PROFB(1);
       tc_fence_after();
-      // S^T and dP^T rows (64 + 64 columns) with back-to-back loads and one wait
-      uint32_t sv[2][32], dv[2][32];
-      tmem_ld_32x32(t_ST + lane_off, sv[0]);
-      tmem_ld_32x32(t_ST + lane_off + 32, sv[1]);
-      tmem_ld_32x32(t_DPT + lane_off, dv[0]);
-      tmem_ld_32x32(t_DPT + lane_off + 32, dv[1]);
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32(t_ST + lane_off + col_off, sv);
+      tmem_ld_32x32(t_DPT + lane_off + col_off, dv);
       tmem_ld_wait();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      {
         float pr[32], ds[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int qi = c * 32 + i;
-          float e = exp2f(fmaf(__uint_as_float(sv[c][i]), p.scale_log2, -lse_b[qi]));
+          float e = exp2f(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_b[i]));
           if (need_mask) {
-            const int q = q0 + qi;
+            const int q = q0 + chalf * 32 + i;
             if (key > q || q >= p.T || (p.window >= 0 && q - key > p.window)) e = 0.f;
           }
           pr[i] = e;
-          ds[i] = e * (__uint_as_float(dv[c][i]) - del_b[qi]) * p.scale;
+          ds[i] = e * (__uint_as_float(dv[i]) - del_b[i]) * p.scale;
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const int chunk = (c * 4 + g) ^ (r & 7);
+          const int chunk = (chalf * 4 + g) ^ (r & 7);
           uint4 u, w;
           u.x = pack_bf16(pr[8 * g + 0], pr[8 * g + 1]);
           u.y = pack_bf16(pr[8 * g + 2], pr[8 * g + 3]);
@@ -313,53 +328,70 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
-      // dQ^T of this step: lane = d, columns = the 64 queries
+      // dQ^T of this step: lane = d, this warp's 32 query columns
       ok = __all_sync(0xffffffffu, mbar_wait(mma2_done, it & 1, abort_word));
       if (!ok) break;
       NGA_PROFB(3);
       tc_fence_after();
-      float* dq_col = p.dq_acc + (long long)(row_base + q0) * (p.Hq * AB_D) + h * AB_D + r;
-      {
-        uint32_t v[2][32];
-        tmem_ld_32x32(t_DQT + lane_off, v[0]);
-        tmem_ld_32x32(t_DQT + lane_off + 32, v[1]);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int qi = c * 32 + i;
-            if (q0 + qi < p.T) atomicAdd(dq_col + (long long)qi * (p.Hq * AB_D), __uint_as_float(v[c][i]));
-          }
-      }
+      uint32_t qv[32];
+      tmem_ld_32x32(t_DQT + lane_off + col_off, qv);
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_free);
+      // the staging tile is free once the previous step's bulk reduction has read it
+      if (it > 0) {
+        if (tma_thread) {
+          tma_store_wait_read0();
+          mbar_arrive(dqs_free);
+        }
+        ok = __all_sync(0xffffffffu, mbar_wait(dqs_free, (it - 1) & 1, abort_word));
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) sDQ[(chalf * 32 + i) * AB_D + r] = __uint_as_float(qv[i]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dqs_full);
+      if (tma_thread) {
+        // one bulk tensor reduction adds the 64 x 128 fp32 tile into dq_acc (rows past the
+        // sequence end carry exact zeros, rows past the tensor end are clipped by the copy engine)
+        if (mbar_wait(dqs_full, it & 1, abort_word)) {
+          tma_reduce_add_3d(&tm_dq, sDQ, h * AB_D, row_base + q0, 0);
+          tma_store_commit();
+        }
+      }
       NGA_PROFB(4);
     }
+    if (tma_thread) tma_store_wait0();
     if (prof_on) { for (int i = 0; i < 6; ++i) p.prof[i] = pc[i]; p.prof[6] = niter; }
     // ---------------------------------------------------------------- dK / dV write-out
+    // warps 2..5 write dK, warps 6..9 write dV (each thread: its key row, 128 columns)
     if (ok && niter > 0) {
       tc_fence_after();
       const bool key_ok = key < p.T;
       const long long cols = (long long)(p.Hq + 2 * p.Hkv) * AB_D;
-      __nv_bfloat16* dk_row = p.dqkv + (long long)(row_base + key) * cols + k_col;
-      __nv_bfloat16* dv_row = p.dqkv + (long long)(row_base + key) * cols + v_col;
+      __nv_bfloat16* dst_row = p.dqkv + (long long)(row_base + key) * cols + (chalf == 0 ? k_col : v_col);
+      const uint32_t src = (chalf == 0 ? t_DK : t_DV) + lane_off;
 #pragma unroll 1
-      for (int c = 0; c < 8; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32((c < 4 ? t_DK : t_DV) + lane_off + (c & 3) * 32, v);
+      for (int c2 = 0; c2 < 2; ++c2) {
+        uint32_t v2[2][32];
+        tmem_ld_32x32(src + c2 * 64, v2[0]);
+        tmem_ld_32x32(src + c2 * 64 + 32, v2[1]);
         tmem_ld_wait();
         if (key_ok) {
-          __nv_bfloat16* dst = (c < 4 ? dk_row : dv_row) + (c & 3) * 32;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 u;
-            u.x = pack_bf16(__uint_as_float(v[8 * g + 0]), __uint_as_float(v[8 * g + 1]));
-            u.y = pack_bf16(__uint_as_float(v[8 * g + 2]), __uint_as_float(v[8 * g + 3]));
-            u.z = pack_bf16(__uint_as_float(v[8 * g + 4]), __uint_as_float(v[8 * g + 5]));
-            u.w = pack_bf16(__uint_as_float(v[8 * g + 6]), __uint_as_float(v[8 * g + 7]));
-            *reinterpret_cast<uint4*>(dst + g * 8) = u;
+          for (int hc = 0; hc < 2; ++hc) {
+            __nv_bfloat16* dst = dst_row + c2 * 64 + hc * 32;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 u;
+              u.x = pack_bf16(__uint_as_float(v2[hc][8 * g + 0]), __uint_as_float(v2[hc][8 * g + 1]));
+              u.y = pack_bf16(__uint_as_float(v2[hc][8 * g + 2]), __uint_as_float(v2[hc][8 * g + 3]));
+              u.z = pack_bf16(__uint_as_float(v2[hc][8 * g + 4]), __uint_as_float(v2[hc][8 * g + 5]));
+              u.w = pack_bf16(__uint_as_float(v2[hc][8 * g + 6]), __uint_as_float(v2[hc][8 * g + 7]));
+              *reinterpret_cast<uint4*>(dst + g * 8) = u;
+            }
           }
         }
       }
@@ -400,6 +432,10 @@ extern "C" int nga_attn_bwd(const void* qkv, const void* out, const void* dout, 
   rc = make_tmap_3d(&tm_do, dout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ocols, rows, 1, ocols * 2,
                     rows * ocols * 2, 64, 64, true);
   if (rc) return rc;
+  CUtensorMap tm_dq;
+  rc = make_tmap_3d(&tm_dq, dq_acc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ocols, rows, 1, ocols * 4,
+                    rows * ocols * 4, 128, 64, false);
+  if (rc) return rc;
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -426,7 +462,7 @@ extern "C" int nga_attn_bwd(const void* qkv, const void* out, const void* dout, 
   p.status = status;
   p.prof = g_attn_bwd_prof;
   dim3 grid((T + AB_BK - 1) / AB_BK, Hkv, B);
-  attn_bwd_kernel<<<grid, AB_THREADS, AttnBwdSmem::kTotal, st>>>(tm_kv, tm_q, tm_do, p);
+  attn_bwd_kernel<<<grid, AB_THREADS, AttnBwdSmem::kTotal, st>>>(tm_kv, tm_q, tm_do, tm_dq, p);
   count_launch();
   {
     const long long n4 = rows * ocols / 4;

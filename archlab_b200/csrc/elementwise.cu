@@ -333,28 +333,39 @@ __global__ void qkv_post_fwd_kernel(__nv_bfloat16* __restrict__ qkv, const float
   if (slot < Hq + Hkv) {
     const int t = int(row % T);
     float ss = 0.f;
-    float y1[4], y2[4];
+    // lane owns element pairs (2j, 2j+1) of the first half and their partners in the second half
+    float2 y1[2], y2[2];
+    const __nv_bfloat162* p1 = reinterpret_cast<const __nv_bfloat162*>(p);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(p + half);
+    const float2* c2 = reinterpret_cast<const float2*>(cosT + (long long)t * half);
+    const float2* s2 = reinterpret_cast<const float2*>(sinT + (long long)t * half);
 #pragma unroll
-    for (int m = 0; m < 4; ++m) {
-      const int j = lane + 32 * m;
-      if (j < half) {
-        const float c = cosT[t * half + j], s = sinT[t * half + j];
-        const float x1 = __bfloat162float(p[j]), x2 = __bfloat162float(p[j + half]);
+    for (int m = 0; m < 2; ++m) {
+      const int j = lane + 32 * m;          // pair index within the half (half / 2 pairs)
+      if (2 * j < half) {
+        const float2 c = c2[j], sn = s2[j];
+        const float2 x1 = __bfloat1622float2(p1[j]), x2 = __bfloat1622float2(p2[j]);
         // the reference rounds the rotated value to bf16 before normalising
-        y1[m] = __bfloat162float(__float2bfloat16(x1 * c + x2 * s));
-        y2[m] = __bfloat162float(__float2bfloat16(x2 * c - x1 * s));
-        ss += y1[m] * y1[m] + y2[m] * y2[m];
+        y1[m].x = __bfloat162float(__float2bfloat16(x1.x * c.x + x2.x * sn.x));
+        y1[m].y = __bfloat162float(__float2bfloat16(x1.y * c.y + x2.y * sn.y));
+        y2[m].x = __bfloat162float(__float2bfloat16(x2.x * c.x - x1.x * sn.x));
+        y2[m].y = __bfloat162float(__float2bfloat16(x2.y * c.y - x1.y * sn.y));
+        ss += y1[m].x * y1[m].x + y1[m].y * y1[m].y + y2[m].x * y2[m].x + y2[m].y * y2[m].y;
       }
     }
     ss = warp_sum(ss);
     const float rstd = rsqrtf(ss / D + kRmsEps);
     if (lane == 0) rstd_out[row * (Hq + Hkv) + slot] = rstd;
+    __nv_bfloat162* o1 = reinterpret_cast<__nv_bfloat162*>(p);
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(p + half);
 #pragma unroll
-    for (int m = 0; m < 4; ++m) {
+    for (int m = 0; m < 2; ++m) {
       const int j = lane + 32 * m;
-      if (j < half) {
-        p[j] = __float2bfloat16(__bfloat162float(__float2bfloat16(y1[m] * rstd)) * gain);
-        p[j + half] = __float2bfloat16(__bfloat162float(__float2bfloat16(y2[m] * rstd)) * gain);
+      if (2 * j < half) {
+        o1[j] = __floats2bfloat162_rn(__bfloat162float(__float2bfloat16(y1[m].x * rstd)) * gain,
+                                      __bfloat162float(__float2bfloat16(y1[m].y * rstd)) * gain);
+        o2[j] = __floats2bfloat162_rn(__bfloat162float(__float2bfloat16(y2[m].x * rstd)) * gain,
+                                      __bfloat162float(__float2bfloat16(y2[m].y * rstd)) * gain);
       }
     }
   } else if (ve_table != nullptr) {
@@ -365,8 +376,12 @@ __global__ void qkv_post_fwd_kernel(__nv_bfloat16* __restrict__ qkv, const float
     if (lane == 0) gate_pre[row * Hkv + h] = gp;
     const float gate = 3.f * sigmoidf_(gp);
     const __nv_bfloat16* ve = ve_table + idx[row] * (long long)(Hkv * D) + (long long)h * D;
-    for (int j = lane; j < D; j += 32)
-      p[j] = __float2bfloat16(__bfloat162float(p[j]) + gate * __bfloat162float(ve[j]));
+    __nv_bfloat162* pv = reinterpret_cast<__nv_bfloat162*>(p);
+    const __nv_bfloat162* vv = reinterpret_cast<const __nv_bfloat162*>(ve);
+    for (int j = lane; j < D / 2; j += 32) {
+      const float2 a = __bfloat1622float2(pv[j]), e = __bfloat1622float2(vv[j]);
+      pv[j] = __floats2bfloat162_rn(a.x + gate * e.x, a.y + gate * e.y);
+    }
   }
 }
 
@@ -396,17 +411,39 @@ __global__ void qkv_post_bwd_kernel(__nv_bfloat16* __restrict__ dqkv,
     const int t = int(row % T);
     const float rstd = rstd_in[row * (Hq + Hkv) + slot];
     // y = q' / gain (normalised, rotated); dy = gain * dq'
+    const __nv_bfloat162* p1 = reinterpret_cast<const __nv_bfloat162*>(p);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(p + half);
+    __nv_bfloat162* d1p = reinterpret_cast<__nv_bfloat162*>(dp);
+    __nv_bfloat162* d2p = reinterpret_cast<__nv_bfloat162*>(dp + half);
+    const float2* c2 = reinterpret_cast<const float2*>(cosT + (long long)t * half);
+    const float2* s2 = reinterpret_cast<const float2*>(sinT + (long long)t * half);
+    float2 ya[2], yb[2], ga[2], gb[2];
     float dot = 0.f;
-    for (int j = lane; j < D; j += 32)
-      dot += (__bfloat162float(dp[j]) * gain) * (__bfloat162float(p[j]) / gain);
+    const float inv_gain = 1.f / gain;
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+      const int j = lane + 32 * m;
+      if (2 * j < half) {
+        ya[m] = __bfloat1622float2(p1[j]);
+        yb[m] = __bfloat1622float2(p2[j]);
+        ga[m] = __bfloat1622float2(d1p[j]);
+        gb[m] = __bfloat1622float2(d2p[j]);
+        ya[m].x *= inv_gain; ya[m].y *= inv_gain; yb[m].x *= inv_gain; yb[m].y *= inv_gain;
+        ga[m].x *= gain; ga[m].y *= gain; gb[m].x *= gain; gb[m].y *= gain;
+        dot += ga[m].x * ya[m].x + ga[m].y * ya[m].y + gb[m].x * yb[m].x + gb[m].y * yb[m].y;
+      }
+    }
     dot = warp_sum(dot) / D;
-    for (int j = lane; j < half; j += 32) {
-      const float c = cosT[t * half + j], s = sinT[t * half + j];
-      const float y1 = __bfloat162float(p[j]) / gain, y2 = __bfloat162float(p[j + half]) / gain;
-      const float d1 = rstd * (__bfloat162float(dp[j]) * gain - y1 * dot);
-      const float d2 = rstd * (__bfloat162float(dp[j + half]) * gain - y2 * dot);
-      dp[j] = __float2bfloat16(d1 * c - d2 * s);
-      dp[j + half] = __float2bfloat16(d1 * s + d2 * c);
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+      const int j = lane + 32 * m;
+      if (2 * j < half) {
+        const float2 c = c2[j], sn = s2[j];
+        const float a1 = rstd * (ga[m].x - ya[m].x * dot), a2 = rstd * (ga[m].y - ya[m].y * dot);
+        const float b1 = rstd * (gb[m].x - yb[m].x * dot), b2 = rstd * (gb[m].y - yb[m].y * dot);
+        d1p[j] = __floats2bfloat162_rn(a1 * c.x - b1 * sn.x, a2 * c.y - b2 * sn.y);
+        d2p[j] = __floats2bfloat162_rn(a1 * sn.x + b1 * c.x, a2 * sn.y + b2 * c.y);
+      }
     }
   } else if (ve_table != nullptr) {
     const int h = slot - Hq - Hkv;

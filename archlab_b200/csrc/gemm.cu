@@ -12,8 +12,7 @@
 //
 // Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..5 =
 // epilogue (one 32-lane TMEM quarter each).
-#include "ptx.cuh"
-#include "gemm.h"
+#include "gemm_common.cuh"
 #include <cuda.h>
 #include <cudaTypedefs.h>
 #include <mutex>
@@ -24,21 +23,7 @@
 
 namespace nga {
 
-constexpr int BM = 128;
-constexpr int BK = 64;           // 64 bf16 = one 128-byte swizzle row
-constexpr int UMMA_K = 16;
 constexpr int kGemmThreads = 192;
-
-struct GemmParams {
-  int M, N, K, batch;
-  void* D;
-  const void* aux;
-  long long ldd, ldaux;          // row strides (elements)
-  long long sD, sAux;            // batch strides (elements)
-  int epi, out_fp32, aux_fp32;
-  float alpha, beta;
-  int* status;
-};
 
 template <int BN>
 struct GemmSmem {
@@ -50,30 +35,6 @@ struct GemmSmem {
   // full[S], empty[S], tmem_full[2], tmem_empty[2], then holder + abort word
   static constexpr int kTotal = kBarOffset + (2 * kStages + 4) * 8 + 16 + 1024;
 };
-
-__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& b, int& mb, int& nb) {
-  const int per_batch = num_m * num_n;
-  b = tile / per_batch;
-  int r = tile - b * per_batch;
-  constexpr int kGroup = 16;
-  const int per_group = kGroup * num_n;
-  const int g = r / per_group;
-  r -= g * per_group;
-  const int first_m = g * kGroup;
-  const int gm = min(kGroup, num_m - first_m);
-  mb = first_m + r % gm;
-  nb = r / gm;
-}
-
-__device__ __forceinline__ float epi_apply(int epi, float acc, float aux, float alpha, float beta) {
-  switch (epi) {
-    case kEpiScale: return alpha * acc;
-    case kEpiAxpby: return alpha * acc + beta * aux;
-    case kEpiRelu2: { float r = fmaxf(alpha * acc, 0.f); return r * r; }
-    case kEpiMulDRelu2: return alpha * acc * 2.f * sqrtf(fmaxf(aux, 0.f));
-    default: return acc;
-  }
-}
 
 template <int BN, int A_MN, int B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -197,10 +158,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    const bool vec_ok = p.out_fp32 ? ((p.ldd & 3) == 0 && (p.sD & 3) == 0 &&
-                                      (reinterpret_cast<uintptr_t>(p.D) & 15) == 0)
-                                   : ((p.ldd & 7) == 0 && (p.sD & 7) == 0 &&
-                                      (reinterpret_cast<uintptr_t>(p.D) & 15) == 0);
+    const bool vec_ok = epilogue_vec_ok(p);
     const bool need_aux = (p.epi == kEpiAxpby || p.epi == kEpiMulDRelu2);
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int b, mb, nb;
@@ -209,7 +167,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const int row = mb * BM + quarter * 32 + lane;
-      const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + uint32_t(acc * BN) + (uint32_t(quarter * 32) << 16);
 #pragma unroll 1
       for (int c2 = 0; c2 < BN / 64; ++c2) {
@@ -225,77 +182,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int col0 = nb * BN + c * 32;
         if (col0 >= p.N) break;   // warp-uniform
         uint32_t (&r)[32] = r2[hc];
-        if (row_ok) {
-          const long long doff = (long long)b * p.sD + (long long)row * p.ldd + col0;
-          const long long aoff = (long long)b * p.sAux + (long long)row * p.ldaux + col0;
-          const int ncol = min(32, p.N - col0);
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          if (need_aux) {
-            if (p.aux_fp32) {
-              const float* ax = reinterpret_cast<const float*>(p.aux) + aoff;
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                v[i] = epi_apply(p.epi, v[i], i < ncol ? ax[i] : 0.f, p.alpha, p.beta);
-            } else {
-              const __nv_bfloat16* ax = reinterpret_cast<const __nv_bfloat16*>(p.aux) + aoff;
-              if (ncol == 32 && (p.ldaux & 7) == 0 && (p.sAux & 7) == 0 &&
-                  (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0) {
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  uint4 pk = reinterpret_cast<const uint4*>(ax)[q];
-                  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) {
-                    float2 f = __bfloat1622float2(h[i]);
-                    v[q * 8 + 2 * i] = epi_apply(p.epi, v[q * 8 + 2 * i], f.x, p.alpha, p.beta);
-                    v[q * 8 + 2 * i + 1] = epi_apply(p.epi, v[q * 8 + 2 * i + 1], f.y, p.alpha, p.beta);
-                  }
-                }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                  v[i] = epi_apply(p.epi, v[i], i < ncol ? __bfloat162float(ax[i]) : 0.f, p.alpha,
-                                   p.beta);
-              }
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = epi_apply(p.epi, v[i], 0.f, p.alpha, p.beta);
-          }
-          if (p.out_fp32) {
-            float* d = reinterpret_cast<float*>(p.D) + doff;
-            if (ncol == 32 && vec_ok) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                reinterpret_cast<float4*>(d)[q] =
-                    make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (i < ncol) d[i] = v[i];
-            }
-          } else {
-            __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + doff;
-            if (ncol == 32 && vec_ok) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                uint4 pk;
-                pk.x = pack_bf16(v[8 * q], v[8 * q + 1]);
-                pk.y = pack_bf16(v[8 * q + 2], v[8 * q + 3]);
-                pk.z = pack_bf16(v[8 * q + 4], v[8 * q + 5]);
-                pk.w = pack_bf16(v[8 * q + 6], v[8 * q + 7]);
-                reinterpret_cast<uint4*>(d)[q] = pk;
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (i < ncol) d[i] = __float2bfloat16(v[i]);
-            }
-          }
+        epilogue_store_chunk(p, r, row, col0, b, vec_ok, need_aux);
         }
-      }
       }
       tc_fence_before();
       __syncwarp();

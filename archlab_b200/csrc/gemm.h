@@ -26,6 +26,13 @@ int nga_gemm_bf16(const void* A, const void* B, void* D, const void* aux, int M,
                   int epi, int out_fp32, int aux_fp32, float alpha, float beta, int* status,
                   void* stream);
 
+// CTA-pair (cta_group::2, 256 x 256 tile) variant with the same contract; best for large problems.
+int nga_gemm2_bf16(const void* A, const void* B, void* D, const void* aux, int M, int N, int K,
+                   int batch, long long lda, long long ldb, long long ldd, long long ldaux,
+                   long long sA, long long sB, long long sD, long long sAux, int a_mn, int b_mn,
+                   int epi, int out_fp32, int aux_fp32, float alpha, float beta, int* status,
+                   void* stream);
+
 // Number of kernels this library has launched since load (every launcher increments it).
 long long nga_launch_count(void);
 void nga_launch_count_reset(void);

@@ -1,0 +1,130 @@
+// Pieces shared by the single-CTA and the CTA-pair GEMM kernels: parameter block, tile order and the
+// register epilogue (scale / axpby / ReLU^2 / ReLU^2-backward, bf16 or fp32 output).
+#pragma once
+#include "ptx.cuh"
+#include "gemm.h"
+
+namespace nga {
+
+constexpr int BM = 128;
+constexpr int BK = 64;           // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+
+struct GemmParams {
+  int M, N, K, batch;
+  void* D;
+  const void* aux;
+  long long ldd, ldaux;          // row strides (elements)
+  long long sD, sAux;            // batch strides (elements)
+  int epi, out_fp32, aux_fp32;
+  float alpha, beta;
+  int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& b, int& mb, int& nb) {
+  const int per_batch = num_m * num_n;
+  b = tile / per_batch;
+  int r = tile - b * per_batch;
+  constexpr int kGroup = 16;
+  const int per_group = kGroup * num_n;
+  const int g = r / per_group;
+  r -= g * per_group;
+  const int first_m = g * kGroup;
+  const int gm = min(kGroup, num_m - first_m);
+  mb = first_m + r % gm;
+  nb = r / gm;
+}
+
+__device__ __forceinline__ float epi_apply(int epi, float acc, float aux, float alpha, float beta) {
+  switch (epi) {
+    case kEpiScale: return alpha * acc;
+    case kEpiAxpby: return alpha * acc + beta * aux;
+    case kEpiRelu2: { float r = fmaxf(alpha * acc, 0.f); return r * r; }
+    case kEpiMulDRelu2: return alpha * acc * 2.f * sqrtf(fmaxf(aux, 0.f));
+    default: return acc;
+  }
+}
+
+// Applies the epilogue to one 32-column chunk of one accumulator row and stores it.
+// r: the 32 fp32 accumulator values of (row, col0 .. col0+31); b: batch index.
+__device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const uint32_t (&r)[32], int row,
+                                                     int col0, int b, bool vec_ok, bool need_aux) {
+  const bool row_ok = row < p.M;
+  if (row_ok) {
+    const long long doff = (long long)b * p.sD + (long long)row * p.ldd + col0;
+    const long long aoff = (long long)b * p.sAux + (long long)row * p.ldaux + col0;
+    const int ncol = min(32, p.N - col0);
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    if (need_aux) {
+      if (p.aux_fp32) {
+        const float* ax = reinterpret_cast<const float*>(p.aux) + aoff;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          v[i] = epi_apply(p.epi, v[i], i < ncol ? ax[i] : 0.f, p.alpha, p.beta);
+      } else {
+        const __nv_bfloat16* ax = reinterpret_cast<const __nv_bfloat16*>(p.aux) + aoff;
+        if (ncol == 32 && (p.ldaux & 7) == 0 && (p.sAux & 7) == 0 &&
+            (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 pk = reinterpret_cast<const uint4*>(ax)[q];
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float2 f = __bfloat1622float2(h[i]);
+              v[q * 8 + 2 * i] = epi_apply(p.epi, v[q * 8 + 2 * i], f.x, p.alpha, p.beta);
+              v[q * 8 + 2 * i + 1] = epi_apply(p.epi, v[q * 8 + 2 * i + 1], f.y, p.alpha, p.beta);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            v[i] = epi_apply(p.epi, v[i], i < ncol ? __bfloat162float(ax[i]) : 0.f, p.alpha,
+                             p.beta);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = epi_apply(p.epi, v[i], 0.f, p.alpha, p.beta);
+    }
+    if (p.out_fp32) {
+      float* d = reinterpret_cast<float*>(p.D) + doff;
+      if (ncol == 32 && vec_ok) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          reinterpret_cast<float4*>(d)[q] =
+              make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < ncol) d[i] = v[i];
+      }
+    } else {
+      __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + doff;
+      if (ncol == 32 && vec_ok) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 pk;
+          pk.x = pack_bf16(v[8 * q], v[8 * q + 1]);
+          pk.y = pack_bf16(v[8 * q + 2], v[8 * q + 3]);
+          pk.z = pack_bf16(v[8 * q + 4], v[8 * q + 5]);
+          pk.w = pack_bf16(v[8 * q + 6], v[8 * q + 7]);
+          reinterpret_cast<uint4*>(d)[q] = pk;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < ncol) d[i] = __float2bfloat16(v[i]);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ bool epilogue_vec_ok(const GemmParams& p) {
+  return p.out_fp32 ? ((p.ldd & 3) == 0 && (p.sD & 3) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0)
+                    : ((p.ldd & 7) == 0 && (p.sD & 7) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0);
+}
+
+}  // namespace nga

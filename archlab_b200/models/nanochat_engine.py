@@ -43,9 +43,12 @@ class StackedGroup:
 class ParamStore:
     """Re-homes the module's parameters into stacked / flat buffers (see module docstring)."""
 
-    def __init__(self, model: GPT):
+    def __init__(self, model: GPT, world: int = 1):
+        """``world`` pads every stacked group to a multiple of the data-parallel world size so that
+        whole matrices can be reduce-scattered / all-gathered without staging copies."""
         cfg = model.config
         dev = model.lm_head.weight.device
+        self.world = world
         self.groups: dict[tuple[int, int], StackedGroup] = {}
         order: dict[tuple[int, int], list] = {}
         for block in model.transformer.h:
@@ -57,8 +60,8 @@ class ParamStore:
             for p in mats:
                 order.setdefault(tuple(p.shape), []).append(p)
         for shape, plist in order.items():
-            K = len(plist)
-            master = torch.empty(K, *shape, dtype=torch.float32, device=dev)
+            K = (len(plist) + world - 1) // world * world
+            master = torch.zeros(K, *shape, dtype=torch.float32, device=dev)
             for i, p in enumerate(plist):
                 master[i].copy_(p.data)
                 p.data = master[i]
@@ -125,7 +128,7 @@ class FusedGPTEngine:
     the optimizer has changed the master weights.
     """
 
-    def __init__(self, model: GPT, *, head_chunk: int = 8192):
+    def __init__(self, model: GPT, *, head_chunk: int = 8192, world: int = 1):
         cfg = model.config
         if cfg.head_dim != 128:
             raise ValueError("the fused engine supports head_dim 128")
@@ -137,7 +140,7 @@ class FusedGPTEngine:
             raise ValueError("the fused engine needs CUDA parameters")
         native.lib()   # fail loudly if the native library is missing
         self.model, self.cfg = model, cfg
-        self.store = ParamStore(model)
+        self.store = ParamStore(model, world)
         self.head_chunk = head_chunk
         dev = model.lm_head.weight.device
         self.dev = dev

@@ -13,6 +13,8 @@ is the numerical oracle of the GPU tests); CUDA tensors always run the native ke
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import native
@@ -20,6 +22,10 @@ from . import native
 __all__ = ["gemm", "EPI_SCALE", "EPI_AXPBY", "EPI_RELU2", "EPI_MUL_DRELU2"]
 
 EPI_SCALE, EPI_AXPBY, EPI_RELU2, EPI_MUL_DRELU2 = 0, 1, 2, 3
+
+# "auto": CTA-pair kernel (cta_group::2, 256 x 256 tiles) when the problem has enough such tiles to
+# fill the machine, otherwise the single-CTA 128 x {128, 256} kernel.  "single" / "pair" force one.
+DEFAULT_IMPL = os.environ.get("NGA_GEMM_IMPL", "auto")
 
 
 def _logical(a: torch.Tensor, mn: bool) -> torch.Tensor:
@@ -58,7 +64,8 @@ def _strides(t: torch.Tensor) -> tuple[int, int, int]:
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: torch.Tensor | None = None, aux: torch.Tensor | None = None, epi: int = EPI_SCALE,
-         alpha: float = 1.0, beta: float = 0.0, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+         alpha: float = 1.0, beta: float = 0.0, out_dtype: torch.dtype = torch.bfloat16,
+         impl: str | None = None) -> torch.Tensor:
     if a.device.type != "cuda":
         d = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, aux=aux, epi=epi, alpha=alpha, beta=beta,
                            out_dtype=out.dtype if out is not None else out_dtype)
@@ -96,7 +103,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         if aux.dtype not in (torch.bfloat16, torch.float32):
             raise TypeError("aux must be bf16 or fp32")
         aux_fp32 = int(aux.dtype == torch.float32)
-    rc = native.lib().nga_gemm_bf16(
+    impl = impl or DEFAULT_IMPL
+    tiles_pair = ((M + 255) // 256) * ((N + 255) // 256) * batch
+    use_pair = impl == "pair" or (impl == "auto" and M >= 256 and N >= 256 and tiles_pair >= 64)
+    fn = native.lib().nga_gemm2_bf16 if use_pair else native.lib().nga_gemm_bf16
+    rc = fn(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), aux.data_ptr() if aux is not None else None,
         M, N, K, batch, lda, ldb, ldd, ldaux, sa if ba > 1 else 0, sb if bb > 1 else 0, sd, saux,
         int(a_mn), int(b_mn), epi, int(out.dtype == torch.float32), aux_fp32, float(alpha),

@@ -46,6 +46,8 @@ def _declare(L: ctypes.CDLL) -> None:
     L.nga_gemm_bf16.argtypes = [vp, vp, vp, vp, i, i, i, i, ll, ll, ll, ll, ll, ll, ll, ll,
                                 i, i, i, i, i, f, f, vp, vp]
     L.nga_gemm_bf16.restype = i
+    L.nga_gemm2_bf16.argtypes = L.nga_gemm_bf16.argtypes
+    L.nga_gemm2_bf16.restype = i
     L.nga_launch_count.restype = ll
     L.nga_launch_count_reset.restype = None
     for name, sig in _EXTRA_SIGNATURES.items():

@@ -56,7 +56,7 @@ class Trainer:
         if self.device.type == "cuda" and not cfg.model.simplicial_layers:
             from ..models.nanochat_engine import FusedGPTEngine
 
-            self.engine = FusedGPTEngine(model, head_chunk=cfg.head_chunk)
+            self.engine = FusedGPTEngine(model, head_chunk=cfg.head_chunk, world=coll.world_size())
         self.world = coll.world_size()
         if self.world > 1:
             # identical parameters on every rank (seeded init makes them equal already; this is the
@@ -65,10 +65,19 @@ class Trainer:
                 dist.broadcast(p.data, src=0)
             if self.engine is not None:
                 self.engine.refresh_shadows()
-        self.optimizer = setup_model_optimizer(
-            model, unembedding_lr=cfg.unembedding_lr, embedding_lr=cfg.embedding_lr, matrix_lr=cfg.matrix_lr,
-            weight_decay=cfg.weight_decay, scalar_lr=cfg.scalar_lr, matrix_optimizer=cfg.matrix_optimizer,
-            distributed=self.world > 1)
+        if self.engine is not None and cfg.matrix_optimizer == "normuon":
+            from ..optim.fused import FusedMuonAdamW
+
+            self.optimizer = FusedMuonAdamW(
+                model, self.engine.store, unembedding_lr=cfg.unembedding_lr, embedding_lr=cfg.embedding_lr,
+                matrix_lr=cfg.matrix_lr, weight_decay=cfg.weight_decay, scalar_lr=cfg.scalar_lr)
+            self.fused_optimizer = True
+        else:
+            self.fused_optimizer = False
+            self.optimizer = setup_model_optimizer(
+                model, unembedding_lr=cfg.unembedding_lr, embedding_lr=cfg.embedding_lr, matrix_lr=cfg.matrix_lr,
+                weight_decay=cfg.weight_decay, scalar_lr=cfg.scalar_lr, matrix_optimizer=cfg.matrix_optimizer,
+                distributed=self.world > 1)
         self.schedule = Schedule(cfg.num_iterations, cfg.warmup_steps, cfg.warmdown_ratio, cfg.final_lr_frac,
                                  cfg.weight_decay)
         self.step_index = 0
@@ -111,8 +120,8 @@ class Trainer:
                 loss_sum = ls.detach() if loss_sum is None else loss_sum + ls.detach()
         self.schedule.apply(self.optimizer, self.step_index)
         self.optimizer.step()
-        if self.engine is not None:
-            self.engine.refresh_shadows()
+        if self.engine is not None and not self.fused_optimizer:
+            self.engine.refresh_shadows()   # the fused optimizer writes the bf16 shadows itself
         self.step_index += 1
         return loss_sum / n_valid
 
