@@ -57,7 +57,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_m = (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int num_tiles = num_m * num_n * p.batch;
+  const int num_tiles = num_m * num_n * p.batch * p.splits;   // work items (tile x k-split)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::kStages; ++s) {
@@ -89,10 +89,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int b, mb, nb;
-        tile_coords(tile, num_m, num_n, b, mb, nb);
+        int b, mb, nb, otile, kb0, kb1;
+        split_range(tile, p.splits, num_kb, otile, kb0, kb1);
+        tile_coords(otile, num_m, num_n, b, mb, nb);
         const int m0 = mb * BM, n0 = nb * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word);
           if (!ok) break;
           uint8_t* sA = smem + stage * S::kStageBytes;
@@ -130,7 +131,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + uint32_t(acc * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int otile, kb0, kb1;
+        split_range(tile, p.splits, num_kb, otile, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_word);
           if (!ok) break;
           tc_fence_after();
@@ -142,7 +145,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                      : umma_smem_desc(sA + k * (UMMA_K * 2), 16, 1024);
             const uint64_t db = B_MN ? umma_smem_desc(sB + k * (UMMA_K * 128), 8192, 1024)
                                      : umma_smem_desc(sB + k * (UMMA_K * 2), 16, 1024);
-            umma_bf16_ss(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16_ss(tmem_d, da, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
           if (++stage == S::kStages) { stage = 0; phase ^= 1u; }
@@ -160,17 +163,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     bool ok = true;
     const bool vec_ok = epilogue_vec_ok(p);
     const bool need_aux = (p.epi == kEpiAxpby || p.epi == kEpiMulDRelu2);
+    const bool aux_fast = aux_prefetchable(p);
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      int b, mb, nb;
-      tile_coords(tile, num_m, num_n, b, mb, nb);
+      int b, mb, nb, otile, kb0, kb1;
+      split_range(tile, p.splits, num_kb, otile, kb0, kb1);
+      tile_coords(otile, num_m, num_n, b, mb, nb);
+      const int row = mb * BM + quarter * 32 + lane;
+      AuxPre nxt;
+      aux_prefetch(p, nxt, row, nb * BN, b, aux_fast);      // in flight while the main loop finishes
       ok = __all_sync(0xffffffffu, mbar_wait(&tfull_bar[acc], acc_phase, abort_word));
       if (!ok) break;
       tc_fence_after();
-      const int row = mb * BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + uint32_t(acc * BN) + (uint32_t(quarter * 32) << 16);
 #pragma unroll 1
       for (int c2 = 0; c2 < BN / 64; ++c2) {
         if (nb * BN + c2 * 64 >= p.N) break;   // warp-uniform
+        const AuxPre cur = nxt;
+        if (c2 + 1 < BN / 64) aux_prefetch(p, nxt, row, nb * BN + (c2 + 1) * 64, b, aux_fast);
         // two 32-column chunks per TMEM round trip
         uint32_t r2[2][32];
         tmem_ld_32x32(taddr + uint32_t(c2 * 64), r2[0]);
@@ -178,11 +187,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_ld_wait();
 #pragma unroll
         for (int hc = 0; hc < 2; ++hc) {
-        const int c = c2 * 2 + hc;
-        const int col0 = nb * BN + c * 32;
-        if (col0 >= p.N) break;   // warp-uniform
-        uint32_t (&r)[32] = r2[hc];
-        epilogue_store_chunk(p, r, row, col0, b, vec_ok, need_aux);
+          const int col0 = nb * BN + (c2 * 2 + hc) * 32;
+          if (col0 >= p.N) break;   // warp-uniform
+          epilogue_store_chunk(p, r2[hc], row, col0, b, vec_ok, need_aux, cur.valid[hc] ? cur.v[hc] : nullptr);
         }
       }
       tc_fence_before();
@@ -223,7 +230,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     if (e != cudaSuccess) return -1000 - (int)e;
     attr_done = true;
   }
-  const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
+  const int num_tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch * p.splits;
   const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
   kern<<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, p);
   count_launch();
@@ -237,7 +244,7 @@ extern "C" int nga_gemm_bf16(const void* A, const void* B, void* D, const void* 
                              int K, int batch, long long lda, long long ldb, long long ldd,
                              long long ldaux, long long sA, long long sB, long long sD,
                              long long sAux, int a_mn, int b_mn, int epi, int out_fp32,
-                             int aux_fp32, float alpha, float beta, int* status, void* stream) {
+                             int aux_fp32, float alpha, float beta, int splits, int* status, void* stream) {
   using namespace nga;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -1;
   if ((lda & 7) || (ldb & 7) || (sA & 7) || (sB & 7)) return -5;
@@ -265,6 +272,13 @@ extern "C" int nga_gemm_bf16(const void* A, const void* B, void* D, const void* 
   p.M = M; p.N = N; p.K = K; p.batch = batch;
   p.D = D; p.aux = aux; p.ldd = ldd; p.ldaux = ldaux; p.sD = sD; p.sAux = sAux;
   p.epi = epi; p.out_fp32 = out_fp32; p.aux_fp32 = aux_fp32; p.alpha = alpha; p.beta = beta;
+  {
+    const int num_kb = (K + BK - 1) / BK;
+    int sp = (epi == kEpiAtomicAdd && splits > 1) ? (splits < num_kb ? splits : num_kb) : 1;
+    const int per = (num_kb + sp - 1) / sp;
+    p.splits = (num_kb + per - 1) / per;       // every split is non-empty
+  }
+  if (epi == kEpiAtomicAdd && !out_fp32) return -8;
   p.status = status;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 #define NGA_DISPATCH(BNV)                                                    \

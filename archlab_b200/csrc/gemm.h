@@ -14,6 +14,7 @@ enum {
   kEpiAxpby = 1,      // D = alpha * acc + beta * aux        (aux may alias D)
   kEpiRelu2 = 2,      // D = relu(alpha * acc)^2
   kEpiMulDRelu2 = 3,  // D = alpha * acc * 2 * sqrt(aux)     (aux = relu(h)^2 saved by kEpiRelu2)
+  kEpiAtomicAdd = 4,  // D(fp32) += alpha * acc with vector atomics; allows split-K (splits > 1)
 };
 
 // D[b] = epi(alpha * A[b] * B[b]^T).  A is M x K, B is N x K (logical).  a_mn / b_mn = 1 when the
@@ -23,15 +24,15 @@ enum {
 int nga_gemm_bf16(const void* A, const void* B, void* D, const void* aux, int M, int N, int K,
                   int batch, long long lda, long long ldb, long long ldd, long long ldaux,
                   long long sA, long long sB, long long sD, long long sAux, int a_mn, int b_mn,
-                  int epi, int out_fp32, int aux_fp32, float alpha, float beta, int* status,
-                  void* stream);
+                  int epi, int out_fp32, int aux_fp32, float alpha, float beta, int splits,
+                  int* status, void* stream);
 
 // CTA-pair (cta_group::2, 256 x 256 tile) variant with the same contract; best for large problems.
 int nga_gemm2_bf16(const void* A, const void* B, void* D, const void* aux, int M, int N, int K,
                    int batch, long long lda, long long ldb, long long ldd, long long ldaux,
                    long long sA, long long sB, long long sD, long long sAux, int a_mn, int b_mn,
-                   int epi, int out_fp32, int aux_fp32, float alpha, float beta, int* status,
-                   void* stream);
+                   int epi, int out_fp32, int aux_fp32, float alpha, float beta, int splits,
+                   int* status, void* stream);
 
 // Number of kernels this library has launched since load (every launcher increments it).
 long long nga_launch_count(void);

@@ -108,7 +108,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int num_m = (p.M + 2 * BM - 1) / (2 * BM);   // 256-row tiles
   const int num_n = (p.N + G2_BN - 1) / G2_BN;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int num_tiles = num_m * num_n * p.batch;
+  const int num_tiles = num_m * num_n * p.batch * p.splits;   // work items (tile x k-split)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < G2_STAGES; ++s) {
@@ -141,11 +141,12 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        int b, mb, nb;
-        tile_coords(tile, num_m, num_n, b, mb, nb);
+        int b, mb, nb, otile, kb0, kb1;
+        split_range(tile, p.splits, num_kb, otile, kb0, kb1);
+        tile_coords(otile, num_m, num_n, b, mb, nb);
         const int m0 = mb * 2 * BM + int(rank) * BM;       // this CTA's 128 rows of A
         const int n0 = nb * G2_BN + int(rank) * 128;       // this CTA's 128 N-rows of B
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word);
           if (!ok) break;
           uint8_t* sA = smem + stage * G2_STAGE_BYTES;
@@ -184,7 +185,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + uint32_t(acc * G2_BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        int otile, kb0, kb1;
+        split_range(tile, p.splits, num_kb, otile, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_word);
           if (!ok) break;
           tc_fence_after();
@@ -196,7 +199,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                                      : umma_smem_desc(sA + k * (UMMA_K * 2), 16, 1024);
             const uint64_t db = B_MN ? umma_smem_desc(sB + k * (UMMA_K * 128), 8192, 1024)
                                      : umma_smem_desc(sB + k * (UMMA_K * 2), 16, 1024);
-            umma2_bf16_ss(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma2_bf16_ss(tmem_d, da, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
           }
           umma2_commit_multicast(&empty_bar[stage], 3);
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1u; }
@@ -214,17 +217,23 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     bool ok = true;
     const bool vec_ok = epilogue_vec_ok(p);
     const bool need_aux = (p.epi == kEpiAxpby || p.epi == kEpiMulDRelu2);
+    const bool aux_fast = aux_prefetchable(p);
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-      int b, mb, nb;
-      tile_coords(tile, num_m, num_n, b, mb, nb);
+      int b, mb, nb, otile, kb0, kb1;
+      split_range(tile, p.splits, num_kb, otile, kb0, kb1);
+      tile_coords(otile, num_m, num_n, b, mb, nb);
+      const int row = mb * 2 * BM + int(rank) * BM + quarter * 32 + lane;
+      AuxPre nxt;
+      aux_prefetch(p, nxt, row, nb * G2_BN, b, aux_fast);   // in flight while the main loop finishes
       ok = __all_sync(0xffffffffu, mbar_wait(&tfull_bar[acc], acc_phase, abort_word));
       if (!ok) break;
       tc_fence_after();
-      const int row = mb * 2 * BM + int(rank) * BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + uint32_t(acc * G2_BN) + (uint32_t(quarter * 32) << 16);
 #pragma unroll 1
       for (int c2 = 0; c2 < G2_BN / 64; ++c2) {
         if (nb * G2_BN + c2 * 64 >= p.N) break;   // warp-uniform
+        const AuxPre cur = nxt;
+        if (c2 + 1 < G2_BN / 64) aux_prefetch(p, nxt, row, nb * G2_BN + (c2 + 1) * 64, b, aux_fast);
         uint32_t r2[2][32];
         tmem_ld_32x32(taddr + uint32_t(c2 * 64), r2[0]);
         tmem_ld_32x32(taddr + uint32_t(c2 * 64 + 32), r2[1]);
@@ -233,7 +242,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         for (int hc = 0; hc < 2; ++hc) {
           const int col0 = nb * G2_BN + (c2 * 2 + hc) * 32;
           if (col0 >= p.N) break;   // warp-uniform
-          epilogue_store_chunk(p, r2[hc], row, col0, b, vec_ok, need_aux);
+          epilogue_store_chunk(p, r2[hc], row, col0, b, vec_ok, need_aux, cur.valid[hc] ? cur.v[hc] : nullptr);
         }
       }
       tc_fence_before();
@@ -280,7 +289,7 @@ static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
     if (e != cudaSuccess || n <= 0) return -1000 - (int)e;
     max_clusters = n;
   }
-  const int num_tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch;
+  const int num_tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch * p.splits;
   const int clusters = num_tiles < max_clusters ? num_tiles : max_clusters;
   cfg.gridDim = dim3(2 * clusters);
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
@@ -296,8 +305,8 @@ static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
 extern "C" int nga_gemm2_bf16(const void* A, const void* B, void* D, const void* aux, int M, int N, int K,
                               int batch, long long lda, long long ldb, long long ldd, long long ldaux,
                               long long sA, long long sB, long long sD, long long sAux, int a_mn, int b_mn,
-                              int epi, int out_fp32, int aux_fp32, float alpha, float beta, int* status,
-                              void* stream) {
+                              int epi, int out_fp32, int aux_fp32, float alpha, float beta, int splits,
+                              int* status, void* stream) {
   using namespace nga;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -1;
   if ((lda & 7) || (ldb & 7) || (sA & 7) || (sB & 7)) return -5;
@@ -321,6 +330,13 @@ extern "C" int nga_gemm2_bf16(const void* A, const void* B, void* D, const void*
   p.M = M; p.N = N; p.K = K; p.batch = batch;
   p.D = D; p.aux = aux; p.ldd = ldd; p.ldaux = ldaux; p.sD = sD; p.sAux = sAux;
   p.epi = epi; p.out_fp32 = out_fp32; p.aux_fp32 = aux_fp32; p.alpha = alpha; p.beta = beta;
+  {
+    const int num_kb = (K + BK - 1) / BK;
+    int sp = (epi == kEpiAtomicAdd && splits > 1) ? (splits < num_kb ? splits : num_kb) : 1;
+    const int per = (num_kb + sp - 1) / sp;
+    p.splits = (num_kb + per - 1) / per;
+  }
+  if (epi == kEpiAtomicAdd && !out_fp32) return -8;
   p.status = status;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (a_mn && b_mn) return launch_gemm2<1, 1>(ta, tb, p, st);

@@ -18,6 +18,7 @@ struct GemmParams {
   long long sD, sAux;            // batch strides (elements)
   int epi, out_fp32, aux_fp32;
   float alpha, beta;
+  int splits;                    // split-K factor (> 1 only with kEpiAtomicAdd)
   int* status;
 };
 
@@ -35,20 +36,57 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
   nb = r / gm;
 }
 
+// Work item -> (output tile index, k-block range) under split-K.
+__device__ __forceinline__ void split_range(int item, int splits, int num_kb, int& tile, int& kb0, int& kb1) {
+  const int sidx = item % splits;
+  tile = item / splits;
+  const int per = (num_kb + splits - 1) / splits;
+  kb0 = sidx * per;
+  kb1 = min(num_kb, kb0 + per);
+}
+
 __device__ __forceinline__ float epi_apply(int epi, float acc, float aux, float alpha, float beta) {
   switch (epi) {
     case kEpiScale: return alpha * acc;
     case kEpiAxpby: return alpha * acc + beta * aux;
     case kEpiRelu2: { float r = fmaxf(alpha * acc, 0.f); return r * r; }
     case kEpiMulDRelu2: return alpha * acc * 2.f * sqrtf(fmaxf(aux, 0.f));
+    case kEpiAtomicAdd: return alpha * acc;
     default: return acc;
   }
 }
 
 // Applies the epilogue to one 32-column chunk of one accumulator row and stores it.
 // r: the 32 fp32 accumulator values of (row, col0 .. col0+31); b: batch index.
+// Register prefetch of the bf16 aux operand for two adjacent 32-column chunks of one row.  Issued
+// before the accumulator is read, so the global-load latency overlaps the main loop / TMEM reads
+// instead of serialising the epilogue (which made K <= 1280 GEMMs with an aux epilogue-bound).
+struct AuxPre {
+  uint4 v[2][4];
+  bool valid[2];
+};
+__device__ __forceinline__ void aux_prefetch(const GemmParams& p, AuxPre& a, int row, int col_pair0, int b,
+                                             bool fast) {
+#pragma unroll
+  for (int hc = 0; hc < 2; ++hc) {
+    const int col0 = col_pair0 + hc * 32;
+    a.valid[hc] = fast && row < p.M && col0 + 32 <= p.N;
+    if (a.valid[hc]) {
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.aux) +
+                                                        (long long)b * p.sAux + (long long)row * p.ldaux + col0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) a.v[hc][q] = src[q];
+    }
+  }
+}
+__device__ __forceinline__ bool aux_prefetchable(const GemmParams& p) {
+  return (p.epi == kEpiAxpby || p.epi == kEpiMulDRelu2) && !p.aux_fp32 && (p.ldaux & 7) == 0 &&
+         (p.sAux & 7) == 0 && (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0;
+}
+
 __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const uint32_t (&r)[32], int row,
-                                                     int col0, int b, bool vec_ok, bool need_aux) {
+                                                     int col0, int b, bool vec_ok, bool need_aux,
+                                                     const uint4* pre = nullptr) {
   const bool row_ok = row < p.M;
   if (row_ok) {
     const long long doff = (long long)b * p.sD + (long long)row * p.ldd + col0;
@@ -69,7 +107,7 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const 
             (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            uint4 pk = reinterpret_cast<const uint4*>(ax)[q];
+            uint4 pk = pre ? pre[q] : reinterpret_cast<const uint4*>(ax)[q];
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -89,7 +127,19 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const 
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = epi_apply(p.epi, v[i], 0.f, p.alpha, p.beta);
     }
-    if (p.out_fp32) {
+    if (p.epi == kEpiAtomicAdd) {
+      // split-K partial sums: fp32 vector reductions into the (pre-existing) output
+      float* d = reinterpret_cast<float*>(p.D) + doff;
+      if (ncol == 32 && vec_ok) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          atomicAdd(reinterpret_cast<float4*>(d) + q, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i < ncol) atomicAdd(d + i, v[i]);
+      }
+    } else if (p.out_fp32) {
       float* d = reinterpret_cast<float*>(p.D) + doff;
       if (ncol == 32 && vec_ok) {
 #pragma unroll

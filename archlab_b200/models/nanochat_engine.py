@@ -26,7 +26,7 @@ from dataclasses import dataclass
 import torch
 
 from ..ops import native, trunk
-from ..ops.gemm import EPI_AXPBY, EPI_MUL_DRELU2, EPI_RELU2, EPI_SCALE, gemm
+from ..ops.gemm import EPI_ATOMIC_ADD, EPI_AXPBY, EPI_MUL_DRELU2, EPI_RELU2, EPI_SCALE, gemm
 from .nanochat import GPT, GPTConfig, has_ve
 
 
@@ -43,12 +43,26 @@ class StackedGroup:
 class ParamStore:
     """Re-homes the module's parameters into stacked / flat buffers (see module docstring)."""
 
-    def __init__(self, model: GPT, world: int = 1):
-        """``world`` pads every stacked group to a multiple of the data-parallel world size so that
+    def __init__(self, model: GPT, world: int = 1, symmetric: bool = False, group=None):
+        """``symmetric`` places gradient and shadow buffers in NVLink symmetric memory (same offset on
+        every rank, peer-mapped) for the fused collective kernels.  ``world`` pads every stacked group to a multiple of the data-parallel world size so that
         whole matrices can be reduce-scattered / all-gathered without staging copies."""
         cfg = model.config
         dev = model.lm_head.weight.device
         self.world = world
+        self.symmetric = symmetric
+        self.sym_group_grad, self.sym_group_shadow = {}, {}
+        self.sym_table_grad, self.sym_table_shadow = {}, {}
+        if symmetric:
+            from ..parallel.symm import symm_zeros
+
+        def alloc(shape, dtype, registry, key):
+            if not symmetric:
+                return torch.zeros(shape, dtype=dtype, device=dev)
+            st = symm_zeros(tuple(shape), dtype, dev, group)
+            registry[key] = st
+            return st.tensor
+
         self.groups: dict[tuple[int, int], StackedGroup] = {}
         order: dict[tuple[int, int], list] = {}
         for block in model.transformer.h:
@@ -65,18 +79,21 @@ class ParamStore:
             for i, p in enumerate(plist):
                 master[i].copy_(p.data)
                 p.data = master[i]
-            grad = torch.zeros_like(master)
+            grad = alloc(master.shape, torch.float32, self.sym_group_grad, shape)
             for i, p in enumerate(plist):
                 p.grad = grad[i]
-            shadow = master.to(torch.bfloat16)
+            shadow = alloc(master.shape, torch.bfloat16, self.sym_group_shadow, shape)
+            shadow.copy_(master)
             self.groups[shape] = StackedGroup(shape, master, grad, shadow, plist)
         # embedding-like tables: fp32 master + fp32 grad + bf16 shadow each
         self.tables: dict[str, tuple[torch.nn.Parameter, torch.Tensor]] = {}
         names = [("wte", model.transformer.wte.weight), ("lm_head", model.lm_head.weight)]
         names += [(f"ve{i}", ve.weight) for i, ve in model.value_embeds.items()]
         for name, p in names:
-            p.grad = torch.zeros_like(p.data)
-            self.tables[name] = (p, p.data.to(torch.bfloat16))
+            p.grad = alloc(p.data.shape, torch.float32, self.sym_table_grad, name)
+            sh = alloc(p.data.shape, torch.bfloat16, self.sym_table_shadow, name)
+            sh.copy_(p.data)
+            self.tables[name] = (p, sh)
         # scalars stay fp32 and are read by the kernels directly
         self.scalars = [model.resid_lambdas, model.x0_lambdas, model.smear_gate.weight, model.smear_lambda,
                         model.backout_lambda]
@@ -128,7 +145,8 @@ class FusedGPTEngine:
     the optimizer has changed the master weights.
     """
 
-    def __init__(self, model: GPT, *, head_chunk: int = 8192, world: int = 1):
+    def __init__(self, model: GPT, *, head_chunk: int = 8192, world: int = 1, symmetric: bool = False,
+                 group=None):
         cfg = model.config
         if cfg.head_dim != 128:
             raise ValueError("the fused engine supports head_dim 128")
@@ -140,7 +158,7 @@ class FusedGPTEngine:
             raise ValueError("the fused engine needs CUDA parameters")
         native.lib()   # fail loudly if the native library is missing
         self.model, self.cfg = model, cfg
-        self.store = ParamStore(model, world)
+        self.store = ParamStore(model, world, symmetric, group)
         self.head_chunk = head_chunk
         dev = model.lm_head.weight.device
         self.dev = dev
@@ -259,7 +277,7 @@ class FusedGPTEngine:
             logits = gemm(nf[s:e], wlm)
             losses[s:e] = trunk.softcap_ce_(logits, tflat[s:e], gscale, cfg.logit_softcap)
             gemm(logits, wlm, b_mn=True, out=dnf[s:e])
-            gemm(logits, nf[s:e], a_mn=True, b_mn=True, out=glm, aux=glm, epi=EPI_AXPBY, alpha=1.0, beta=1.0)
+            gemm(logits, nf[s:e], a_mn=True, b_mn=True, out=glm, epi=EPI_ATOMIC_ADD)
         return losses.sum(), dnf
 
     # ------------------------------------------------------------------ backward
@@ -288,14 +306,14 @@ class FusedGPTEngine:
             act, n2, x2, y = sv["act"][i], sv["n2"][i], sv["x2"][i], sv["y"][i]
             # ---- MLP
             dh = gemm(dx, w_p2, b_mn=True, aux=act, epi=EPI_MUL_DRELU2)
-            gemm(dx, act, a_mn=True, b_mn=True, out=g_p2, aux=g_p2, epi=EPI_AXPBY, alpha=1.0, beta=1.0)
+            gemm(dx, act, a_mn=True, b_mn=True, out=g_p2, epi=EPI_ATOMIC_ADD)
             dn2 = gemm(dh, w_fc, b_mn=True)
-            gemm(dh, n2, a_mn=True, b_mn=True, out=g_fc, aux=g_fc, epi=EPI_AXPBY, alpha=1.0, beta=1.0)
+            gemm(dh, n2, a_mn=True, b_mn=True, out=g_fc, epi=EPI_ATOMIC_ADD)
             del dh
             dx2 = trunk.norm_bwd(x2, dn2, dx)
             # ---- attention
             dy = gemm(dx2, w_o, b_mn=True)
-            gemm(dx2, y, a_mn=True, b_mn=True, out=g_o, aux=g_o, epi=EPI_AXPBY, alpha=1.0, beta=1.0)
+            gemm(dx2, y, a_mn=True, b_mn=True, out=g_o, epi=EPI_ATOMIC_ADD)
             window = m.window_sizes[i]
             qkv = sv["qkv"][i]
             dqkv = trunk.attn_bwd(qkv, y, dy, sv["lse"][i], B, T, H, Hkv, D, -1 if window >= T else window,
@@ -309,7 +327,7 @@ class FusedGPTEngine:
             wqkv, gqkv = self._wqkv(i)
             n1 = sv["n1"][i]
             dn1 = gemm(dqkv, wqkv, b_mn=True)
-            gemm(dqkv, n1, a_mn=True, b_mn=True, out=gqkv, aux=gqkv, epi=EPI_AXPBY, alpha=1.0, beta=1.0)
+            gemm(dqkv, n1, a_mn=True, b_mn=True, out=gqkv, epi=EPI_ATOMIC_ADD)
             if has:
                 trunk.gate_bwd(dn1, n1, dgp, block.attn.ve_gate.weight.data, st.grad_of(block.attn.ve_gate.weight))
             dx = trunk.norm_bwd_mix(sv["x1"][i], dn1, dx2, m.resid_lambdas.data[i:i + 1],

@@ -19,9 +19,12 @@ import torch
 
 from . import native
 
-__all__ = ["gemm", "EPI_SCALE", "EPI_AXPBY", "EPI_RELU2", "EPI_MUL_DRELU2"]
+__all__ = ["gemm", "EPI_SCALE", "EPI_AXPBY", "EPI_RELU2", "EPI_MUL_DRELU2", "EPI_ATOMIC_ADD"]
 
-EPI_SCALE, EPI_AXPBY, EPI_RELU2, EPI_MUL_DRELU2 = 0, 1, 2, 3
+# EPI_ATOMIC_ADD: out (fp32, must already hold valid data) += alpha * A @ B^T through vector atomics;
+# the contraction may then be split over K (``splits``) so that few-tile / long-K problems such as
+# weight gradients still fill the machine.
+EPI_SCALE, EPI_AXPBY, EPI_RELU2, EPI_MUL_DRELU2, EPI_ATOMIC_ADD = 0, 1, 2, 3, 4
 
 # "auto": CTA-pair kernel (cta_group::2, 256 x 256 tiles) when the problem has enough such tiles to
 # fill the machine, otherwise the single-CTA 128 x {128, 256} kernel.  "single" / "pair" force one.
@@ -46,6 +49,8 @@ def gemm_reference(a, b, *, a_mn=False, b_mn=False, aux=None, epi=EPI_SCALE, alp
         d = torch.relu(acc).square()
     elif epi == EPI_MUL_DRELU2:
         d = acc * 2.0 * aux.float().clamp_min(0).sqrt()
+    elif epi == EPI_ATOMIC_ADD:
+        d = acc + aux.float()
     else:
         raise ValueError(f"unknown epilogue {epi}")
     return d.to(out_dtype)
@@ -65,8 +70,10 @@ def _strides(t: torch.Tensor) -> tuple[int, int, int]:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: torch.Tensor | None = None, aux: torch.Tensor | None = None, epi: int = EPI_SCALE,
          alpha: float = 1.0, beta: float = 0.0, out_dtype: torch.dtype = torch.bfloat16,
-         impl: str | None = None) -> torch.Tensor:
+         impl: str | None = None, splits: int = 0) -> torch.Tensor:
     if a.device.type != "cuda":
+        if epi == EPI_ATOMIC_ADD:
+            aux = out
         d = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, aux=aux, epi=epi, alpha=alpha, beta=beta,
                            out_dtype=out.dtype if out is not None else out_dtype)
         if out is not None:
@@ -87,6 +94,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if ba != bb:
         raise ValueError("batch mismatch (operands do not broadcast over the batch dimension)")
     if out is None:
+        if epi == EPI_ATOMIC_ADD:
+            raise ValueError("EPI_ATOMIC_ADD accumulates into an existing output")
         shape = (batch, M, N) if (a.dim() == 3 or b.dim() == 3) else (M, N)
         out = torch.empty(shape, dtype=out_dtype, device=a.device)
     bo, ldd, sd = _strides(out)
@@ -105,12 +114,21 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         aux_fp32 = int(aux.dtype == torch.float32)
     impl = impl or DEFAULT_IMPL
     tiles_pair = ((M + 255) // 256) * ((N + 255) // 256) * batch
-    use_pair = impl == "pair" or (impl == "auto" and M >= 256 and N >= 256 and tiles_pair >= 64)
+    if epi == EPI_ATOMIC_ADD:
+        if out.dtype != torch.float32:
+            raise TypeError("EPI_ATOMIC_ADD needs an fp32 output")
+        if splits <= 0:
+            # aim for >= 4 waves of work items; keep at least 8 k-blocks (512 deep) per split
+            tiles = tiles_pair if (M >= 256 and N >= 256) else ((M + 127) // 128) * ((N + 255) // 256) * batch
+            splits = max(1, min(-(-296 // max(tiles, 1)), (K // 64) // 8))
+    else:
+        splits = 1
+    use_pair = impl == "pair" or (impl == "auto" and M >= 256 and N >= 256 and tiles_pair * splits >= 64)
     fn = native.lib().nga_gemm2_bf16 if use_pair else native.lib().nga_gemm_bf16
     rc = fn(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), aux.data_ptr() if aux is not None else None,
         M, N, K, batch, lda, ldb, ldd, ldaux, sa if ba > 1 else 0, sb if bb > 1 else 0, sd, saux,
         int(a_mn), int(b_mn), epi, int(out.dtype == torch.float32), aux_fp32, float(alpha),
-        float(beta), native.status_word(a.device).data_ptr(), native.stream_ptr())
+        float(beta), int(splits), native.status_word(a.device).data_ptr(), native.stream_ptr())
     native.check(rc, "nga_gemm_bf16")
     return out

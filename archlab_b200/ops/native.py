@@ -16,7 +16,7 @@ _LIB_PATH = Path(__file__).resolve().parent.parent / "libnga_b200.so"
 _lib = None
 _status = {}
 
-EPI_SCALE, EPI_AXPBY, EPI_RELU2, EPI_MUL_DRELU2 = 0, 1, 2, 3
+EPI_SCALE, EPI_AXPBY, EPI_RELU2, EPI_MUL_DRELU2, EPI_ATOMIC_ADD = 0, 1, 2, 3, 4
 
 
 class NativeError(RuntimeError):
@@ -44,7 +44,7 @@ def _declare(L: ctypes.CDLL) -> None:
     c = ctypes
     vp, i, ll, f = c.c_void_p, c.c_int, c.c_longlong, c.c_float
     L.nga_gemm_bf16.argtypes = [vp, vp, vp, vp, i, i, i, i, ll, ll, ll, ll, ll, ll, ll, ll,
-                                i, i, i, i, i, f, f, vp, vp]
+                                i, i, i, i, i, f, f, i, vp, vp]
     L.nga_gemm_bf16.restype = i
     L.nga_gemm2_bf16.argtypes = L.nga_gemm_bf16.argtypes
     L.nga_gemm2_bf16.restype = i

@@ -56,7 +56,9 @@ class Trainer:
         if self.device.type == "cuda" and not cfg.model.simplicial_layers:
             from ..models.nanochat_engine import FusedGPTEngine
 
-            self.engine = FusedGPTEngine(model, head_chunk=cfg.head_chunk, world=coll.world_size())
+            ws = coll.world_size()
+            self.use_peer = ws > 1 and cfg.zero_impl in ("auto", "fused") and cfg.matrix_optimizer == "normuon"
+            self.engine = FusedGPTEngine(model, head_chunk=cfg.head_chunk, world=ws, symmetric=self.use_peer)
         self.world = coll.world_size()
         if self.world > 1:
             # identical parameters on every rank (seeded init makes them equal already; this is the
@@ -67,8 +69,9 @@ class Trainer:
                 self.engine.refresh_shadows()
         if self.engine is not None and cfg.matrix_optimizer == "normuon":
             from ..optim.fused import FusedMuonAdamW
+            from ..optim.fused_peer import PeerMuonAdamW
 
-            self.optimizer = FusedMuonAdamW(
+            self.optimizer = (PeerMuonAdamW if self.use_peer else FusedMuonAdamW)(
                 model, self.engine.store, unembedding_lr=cfg.unembedding_lr, embedding_lr=cfg.embedding_lr,
                 matrix_lr=cfg.matrix_lr, weight_decay=cfg.weight_decay, scalar_lr=cfg.scalar_lr)
             self.fused_optimizer = True

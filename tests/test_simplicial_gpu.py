@@ -1,0 +1,28 @@
+"""sm_100a 2-simplicial attention kernel against the fp32 PyTorch statement (the ladder of window
+shapes follows the reference's preflight, src/archlab/qualification/simplicial_attention.py:196-215)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("B,N,Hq,Hkv,w1,w2", [(1, 64, 1, 1, 8, 8), (1, 130, 2, 1, 16, 64), (2, 300, 2, 2, 32, 128),
+                                               (1, 529, 2, 1, 32, 512), (1, 257, 4, 2, 16, 128)])
+def test_simplicial_forward(B, N, Hq, Hkv, w1, w2):
+    from archlab_b200.ops import native
+    from archlab_b200.ops.simplicial import simplicial_attention_reference
+    from archlab_b200.ops.simplicial_cuda import simplicial_fwd
+
+    torch.manual_seed(0)
+    D = 128
+    mk = lambda H: (torch.randn(B, N, H, D, device="cuda") * 0.7).bfloat16()
+    q, k1, k2, v1, v2 = mk(Hq), mk(Hkv), mk(Hkv), mk(Hkv), mk(Hkv)
+    scale = D ** -0.5
+    out, lse2 = simplicial_fwd(q, k1, k2, v1, v2, w1, w2, scale)
+    torch.cuda.synchronize()
+    native.check_status()
+    ref = simplicial_attention_reference(q.float(), k1.float(), k2.float(), v1.float(), v2.float(), w1, w2,
+                                         scale=scale)
+    rel = ((out.float() - ref).norm() / ref.norm()).item()
+    assert rel < 2.5e-2, rel
+    assert not torch.isnan(out.float()).any()
