@@ -1,0 +1,121 @@
+"""Delta-rule linear-attention recurrences: gated delta net (GDN) and Kimi delta attention (KDA).
+
+State ``S_t`` is a ``[key_dim, value_dim]`` matrix per (batch, head):
+
+    S_t = decay_t * S_{t-1} ;  S_t += k_t (beta_t (v_t - k_t^T S_t))^T ;  o_t = S_t^T q_t
+
+GDN uses one scalar log-decay per (token, head); KDA one per key channel.  q and k are L2
+normalised, q additionally scaled by ``1/sqrt(K)``.  The O(T) recurrent functions are the oracles
+(src/archlab/architectures/qwen38_flash_next_full.py:535-554, kimi.py:154-178; the reference's
+kernels are fla-core Triton ``chunk_gated_delta_rule`` / ``chunk_kda``).  ``chunk_*`` are the
+chunk-parallel forms (chunk 64: intra-chunk triangular solve + inter-chunk state passing) that the
+sm_100a kernels follow; they are differentiable and serve as the CPU / fallback path.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+
+def _prep(q, k, v, g, beta):
+    K = q.size(-1)
+    q = F.normalize(q.float(), p=2, dim=-1) * K ** -0.5
+    k = F.normalize(k.float(), p=2, dim=-1)
+    return q, k, v.float(), g.float(), beta.float()
+
+
+def gated_delta_reference(q, k, v, decay, beta):
+    """[B, T, H, K] q/k, [B, T, H, V] v, [B, T, H] log-decay (<= 0) and beta -> [B, T, H, V]."""
+    q, k, v, decay, beta = _prep(q, k, v, decay, beta)
+    B, T, H, K = q.shape
+    state = q.new_zeros(B, H, K, v.size(-1))
+    outs = []
+    for t in range(T):
+        state = state * decay[:, t].exp()[..., None, None]
+        pred = torch.einsum("bhk,bhkv->bhv", k[:, t], state)
+        upd = beta[:, t, :, None] * (v[:, t] - pred)
+        state = state + k[:, t, :, :, None] * upd[:, :, None, :]
+        outs.append(torch.einsum("bhkv,bhk->bhv", state, q[:, t]))
+    return torch.stack(outs, dim=1)
+
+
+def kda_recurrent_reference(q, k, v, g, beta):
+    """As above with a per-channel log-decay ``g`` of shape [B, T, H, K]."""
+    q, k, v, g, beta = _prep(q, k, v, g, beta)
+    B, T, H, K = q.shape
+    state = q.new_zeros(B, H, K, v.size(-1))
+    outs = []
+    for t in range(T):
+        state = state * g[:, t].exp()[..., None]
+        pred = torch.einsum("bhk,bhkv->bhv", k[:, t], state)
+        upd = beta[:, t, :, None] * (v[:, t] - pred)
+        state = state + k[:, t, :, :, None] * upd[:, :, None, :]
+        outs.append(torch.einsum("bhkv,bhk->bhv", state, q[:, t]))
+    return torch.stack(outs, dim=1)
+
+
+def chunk_kda(q, k, v, g, beta, chunk: int = 64, initial_state=None, output_final_state: bool = False):
+    """Chunk-parallel KDA (per-channel decay); GDN is the special case of a channel-constant ``g``.
+
+    Within a chunk with cumulative log-decay ``G_t = sum_{s<=t} g_s`` (per channel), define
+    ``kd_t = k_t * exp(G_t)``, ``ku_t = k_t * exp(-G_t)``, ``qd_t = q_t * exp(G_t)``.  The corrected
+    values ``u`` solve the unit-lower-triangular system
+        (I + tril(diag(beta) (kd ku^T), -1)) u = beta * (v - kd S_0)
+    and  o = qd S_0 + tril(qd ku^T) u ,   S_C = exp(G_C) * S_0 + (ku * exp(G_C))^T u.
+    """
+    q, k, v, g, beta = _prep(q, k, v, g, beta)
+    B, T, H, K = q.shape
+    V = v.size(-1)
+    pad = (-T) % chunk
+    if pad:
+        q, k, v, g = (F.pad(x, (0, 0, 0, 0, 0, pad)) for x in (q, k, v, g))
+        beta = F.pad(beta, (0, 0, 0, pad))
+    n = (T + pad) // chunk
+    rs = lambda x: x.view(B, n, chunk, H, -1).permute(0, 1, 3, 2, 4)      # [B, n, H, C, *]
+    q, k, v, g = rs(q), rs(k), rs(v), rs(g)
+    beta = beta.view(B, n, chunk, H).permute(0, 1, 3, 2)                  # [B, n, H, C]
+    G = g.cumsum(dim=-2)
+    kd, ku, qd = k * G.exp(), k * (-G).exp(), q * G.exp()
+    eye = torch.eye(chunk, device=q.device, dtype=q.dtype)
+    A = torch.tril(beta[..., None] * (kd @ ku.transpose(-1, -2)), -1) + eye
+    Aq = torch.tril(qd @ ku.transpose(-1, -2))
+    state = q.new_zeros(B, H, K, V) if initial_state is None else initial_state.float()
+    outs = []
+    for c in range(n):
+        rhs = beta[:, c, ..., None] * (v[:, c] - kd[:, c] @ state)
+        u = torch.linalg.solve_triangular(A[:, c], rhs, upper=False, unitriangular=True)
+        outs.append(qd[:, c] @ state + Aq[:, c] @ u)
+        Gc = G[:, c, :, -1, :]                                             # [B, H, K]
+        state = Gc.exp()[..., None] * state + (ku[:, c] * Gc.exp()[:, :, None, :]).transpose(-1, -2) @ u
+    o = torch.stack(outs, dim=1).permute(0, 1, 3, 2, 4).reshape(B, n * chunk, H, V)[:, :T]
+    return (o, state) if output_final_state else o
+
+
+def chunk_gated_delta_rule(q, k, v, decay, beta, chunk: int = 64, **kw):
+    """GDN: scalar log-decay per (token, head) broadcast over the key channels."""
+    return chunk_kda(q, k, v, decay[..., None].expand(*decay.shape, q.size(-1)), beta, chunk, **kw)
+
+
+def fused_kda_gate(raw_gate: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor | None = None):
+    """Per-channel log-decay ``g = -exp(A_log) * softplus(raw + dt_bias)`` (<= 0); ``a_log`` is per head."""
+    x = raw_gate.float()
+    if dt_bias is not None:
+        x = x + dt_bias.float().view(*([1] * (x.dim() - 2)), *x.shape[-2:]) if dt_bias.dim() == 2 else x + dt_bias.float()
+    return -a_log.float().exp().view(*([1] * (x.dim() - 2)), -1, 1) * F.softplus(x)
+
+
+def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+                  activation: str | None = "silu", dilation: int = 1) -> torch.Tensor:
+    """Depthwise causal convolution over [B, T, C] with weight [C, k] (k = 4 in every reference
+    model; src/archlab/architectures/qwen38_flash_next_full.py:491-532), optional SiLU."""
+    B, T, Cc = x.shape
+    kk = weight.size(1)
+    y = F.conv1d(F.pad(x.transpose(1, 2), ((kk - 1) * dilation, 0)), weight.unsqueeze(1).to(x.dtype), bias,
+                 groups=Cc, dilation=dilation).transpose(1, 2)
+    if activation == "silu":
+        y = F.silu(y)
+    elif activation is not None:
+        raise ValueError(f"unsupported activation {activation!r}")
+    return y

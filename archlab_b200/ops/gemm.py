@@ -56,6 +56,23 @@ def gemm_reference(a, b, *, a_mn=False, b_mn=False, aux=None, epi=EPI_SCALE, alp
     return d.to(out_dtype)
 
 
+def _choose_splits(M: int, N: int, K: int, batch: int, slots: int = 74) -> int:
+    """Split-K factor for an atomically accumulated GEMM from a two-term cost model fitted on B200:
+    tensor time = (time of one full-K 256 x 256 tile on a CTA pair) * waves / splits, plus one fp32
+    reduction pass over the output per split at ~1.3 TB/s of L2 atomic throughput."""
+    tiles = ((M + 255) // 256) * ((N + 255) // 256) * batch
+    t_tile = 2.0 * 256 * 256 * K / 19.6e12
+    t_red = 4.0 * M * N * batch / 1.3e12
+    best, best_cost = 1, float("inf")
+    for s in range(1, 17):
+        if s > 1 and (K // 64) // s < 16:
+            break
+        cost = t_tile * (-(-tiles * s // slots)) / s + t_red * s
+        if cost < best_cost * (1 - 1e-6):
+            best, best_cost = s, cost
+    return best
+
+
 def _strides(t: torch.Tensor) -> tuple[int, int, int]:
     """(batch, row stride, batch stride) of a 2-D / 3-D tensor with unit inner stride."""
     if t.stride(-1) != 1:
@@ -118,9 +135,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         if out.dtype != torch.float32:
             raise TypeError("EPI_ATOMIC_ADD needs an fp32 output")
         if splits <= 0:
-            # aim for >= 4 waves of work items; keep at least 8 k-blocks (512 deep) per split
-            tiles = tiles_pair if (M >= 256 and N >= 256) else ((M + 127) // 128) * ((N + 255) // 256) * batch
-            splits = max(1, min(-(-296 // max(tiles, 1)), (K // 64) // 8))
+            splits = _choose_splits(M, N, K, batch)
     else:
         splits = 1
     use_pair = impl == "pair" or (impl == "auto" and M >= 256 and N >= 256 and tiles_pair * splits >= 64)
