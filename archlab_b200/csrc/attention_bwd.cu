@@ -13,6 +13,7 @@
 #include "host_util.h"
 #include "attention.h"
 #include <cuda.h>
+#include <mutex>
 
 namespace nga {
 
@@ -472,4 +473,60 @@ extern "C" int nga_attn_bwd(const void* qkv, const void* out, const void* dout, 
   }
   NGA_CHECK_LAUNCH();
   return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free attention backward.
+//
+// Some callers cannot hand over scratch buffers: a host runtime that drives the kernels straight
+// through the C ABI with no tensor library behind it, a serving loop that has frozen its memory
+// pool, or code that runs where a device allocation would synchronise the whole GPU.  For them the
+// fp32 dQ accumulator and the delta rows live in the two fixed device arrays below, which are part
+// of the loaded module, so no cudaMalloc / cudaFree / allocator call happens on any call.
+//
+// Limits (rejected with -20 beyond them):  B*T*Hq*128 <= kStaticDqElems (16 MiB of fp32) and
+// B*Hq*T <= kStaticDeltaElems.  The arrays are shared by every call on a device: two calls whose
+// execution can overlap (different streams, or different host threads on different streams) race
+// on them and must be ordered by the caller.  The accumulator is cleared by the launcher on each
+// call, so nothing has to be zeroed by the caller.
+//
+// The first call on each device looks the arrays' addresses up (cudaGetSymbolAddress, with that
+// device current) and caches them; make that first call outside of any stream capture.
+namespace nga {
+constexpr long long kStaticDqElems = 4ll * 1024 * 1024;
+constexpr long long kStaticDeltaElems = kStaticDqElems / AB_D;
+constexpr int kStaticMaxDevices = 64;
+static __device__ __align__(256) float g_static_dq_acc[kStaticDqElems];
+static __device__ __align__(256) float g_static_delta[kStaticDeltaElems];
+static float* g_static_dq_ptr[kStaticMaxDevices] = {};
+static float* g_static_delta_ptr[kStaticMaxDevices] = {};
+static std::mutex g_static_mu;
+}  // namespace nga
+
+extern "C" long long nga_attn_bwd_static_max_elems(void) { return nga::kStaticDqElems; }
+
+extern "C" int nga_attn_bwd_static(const void* qkv, const void* out, const void* dout, const float* lse2,
+                                   void* dqkv, int B, int T, int Hq, int Hkv, int D, int window,
+                                   float scale, int* status, void* stream) {
+  using namespace nga;
+  if (D != AB_D || B <= 0 || T <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return -1;
+  if ((long long)B * T * Hq * D > kStaticDqElems || (long long)B * Hq * T > kStaticDeltaElems) return -20;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices) return -21;
+  float *dq = nullptr, *dl = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (g_static_dq_ptr[dev] == nullptr) {
+      float *a = nullptr, *b = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&a), g_static_dq_acc);
+      if (e != cudaSuccess || a == nullptr) return -1000 - (int)e;
+      e = cudaGetSymbolAddress(reinterpret_cast<void**>(&b), g_static_delta);
+      if (e != cudaSuccess || b == nullptr) return -1000 - (int)e;
+      g_static_delta_ptr[dev] = b;
+      g_static_dq_ptr[dev] = a;
+    }
+    dq = g_static_dq_ptr[dev];
+    dl = g_static_delta_ptr[dev];
+  }
+  return nga_attn_bwd(qkv, out, dout, lse2, dqkv, dq, dl, B, T, Hq, Hkv, D, window, scale, status, stream);
 }
