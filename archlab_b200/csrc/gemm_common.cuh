@@ -45,15 +45,18 @@ __device__ __forceinline__ void split_range(int item, int splits, int num_kb, in
   kb1 = min(num_kb, kb0 + per);
 }
 
-__device__ __forceinline__ float epi_apply(int epi, float acc, float aux, float alpha, float beta) {
-  switch (epi) {
-    case kEpiScale: return alpha * acc;
-    case kEpiAxpby: return alpha * acc + beta * aux;
-    case kEpiRelu2: { float r = fmaxf(alpha * acc, 0.f); return r * r; }
-    case kEpiMulDRelu2: return alpha * acc * 2.f * sqrtf(fmaxf(aux, 0.f));
-    case kEpiAtomicAdd: return alpha * acc;
-    default: return acc;
+template <int EPI>
+__device__ __forceinline__ float epi_apply(float acc, float aux, float alpha, float beta) {
+  if constexpr (EPI == kEpiAxpby) return alpha * acc + beta * aux;
+  if constexpr (EPI == kEpiRelu2) { float r = fmaxf(alpha * acc, 0.f); return r * r; }
+  if constexpr (EPI == kEpiMulDRelu2) {
+    // d/dh relu(h)^2 = 2 relu(h) = 2 sqrt(aux); one MUFU op (the IEEE sqrt sequence costs ~30
+    // instructions per element and made this epilogue issue-bound), bf16 output hides the 1-ulp error
+    float rt;
+    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(rt) : "f"(fmaxf(aux, 0.f)));
+    return alpha * acc * 2.f * rt;
   }
+  return alpha * acc;   // kEpiScale, kEpiAtomicAdd
 }
 
 // Applies the epilogue to one 32-column chunk of one accumulator row and stores it.
@@ -84,91 +87,113 @@ __device__ __forceinline__ bool aux_prefetchable(const GemmParams& p) {
          (p.sAux & 7) == 0 && (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0;
 }
 
-__device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const uint32_t (&r)[32], int row,
-                                                     int col0, int b, bool vec_ok, bool need_aux,
-                                                     const uint4* pre = nullptr) {
-  const bool row_ok = row < p.M;
-  if (row_ok) {
-    const long long doff = (long long)b * p.sD + (long long)row * p.ldd + col0;
+// The epilogue mode is a template parameter: the per-element arithmetic must not branch on it (a
+// run-time switch per element made every K <= 1280 GEMM epilogue-bound).
+template <int EPI>
+__device__ __forceinline__ void epilogue_chunk_t(const GemmParams& p, const uint32_t (&r)[32], int row, int col0,
+                                                 int b, bool vec_ok, const uint4* pre) {
+  constexpr bool kNeedAux = (EPI == kEpiAxpby || EPI == kEpiMulDRelu2);
+  if (row >= p.M) return;
+  const long long doff = (long long)b * p.sD + (long long)row * p.ldd + col0;
+  const int ncol = min(32, p.N - col0);
+  const float alpha = p.alpha, beta = p.beta;
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+  if constexpr (kNeedAux) {
     const long long aoff = (long long)b * p.sAux + (long long)row * p.ldaux + col0;
-    const int ncol = min(32, p.N - col0);
-    float v[32];
+    if (p.aux_fp32) {
+      const float* ax = reinterpret_cast<const float*>(p.aux) + aoff;
+      if (ncol == 32 && (p.ldaux & 3) == 0 && (p.sAux & 3) == 0 && (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-    if (need_aux) {
-      if (p.aux_fp32) {
-        const float* ax = reinterpret_cast<const float*>(p.aux) + aoff;
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          v[i] = epi_apply(p.epi, v[i], i < ncol ? ax[i] : 0.f, p.alpha, p.beta);
-      } else {
-        const __nv_bfloat16* ax = reinterpret_cast<const __nv_bfloat16*>(p.aux) + aoff;
-        if (ncol == 32 && (p.ldaux & 7) == 0 && (p.sAux & 7) == 0 &&
-            (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 pk = pre ? pre[q] : reinterpret_cast<const uint4*>(ax)[q];
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              float2 f = __bfloat1622float2(h[i]);
-              v[q * 8 + 2 * i] = epi_apply(p.epi, v[q * 8 + 2 * i], f.x, p.alpha, p.beta);
-              v[q * 8 + 2 * i + 1] = epi_apply(p.epi, v[q * 8 + 2 * i + 1], f.y, p.alpha, p.beta);
-            }
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            v[i] = epi_apply(p.epi, v[i], i < ncol ? __bfloat162float(ax[i]) : 0.f, p.alpha,
-                             p.beta);
+        for (int q = 0; q < 8; ++q) {
+          const float4 f = reinterpret_cast<const float4*>(ax)[q];
+          v[4 * q] = epi_apply<EPI>(v[4 * q], f.x, alpha, beta);
+          v[4 * q + 1] = epi_apply<EPI>(v[4 * q + 1], f.y, alpha, beta);
+          v[4 * q + 2] = epi_apply<EPI>(v[4 * q + 2], f.z, alpha, beta);
+          v[4 * q + 3] = epi_apply<EPI>(v[4 * q + 3], f.w, alpha, beta);
         }
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = epi_apply(p.epi, v[i], 0.f, p.alpha, p.beta);
-    }
-    if (p.epi == kEpiAtomicAdd) {
-      // split-K partial sums: fp32 vector reductions into the (pre-existing) output
-      float* d = reinterpret_cast<float*>(p.D) + doff;
-      if (ncol == 32 && vec_ok) {
-#pragma unroll
-        for (int q = 0; q < 8; ++q)
-          atomicAdd(reinterpret_cast<float4*>(d) + q, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (i < ncol) atomicAdd(d + i, v[i]);
-      }
-    } else if (p.out_fp32) {
-      float* d = reinterpret_cast<float*>(p.D) + doff;
-      if (ncol == 32 && vec_ok) {
-#pragma unroll
-        for (int q = 0; q < 8; ++q)
-          reinterpret_cast<float4*>(d)[q] =
-              make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (i < ncol) d[i] = v[i];
+        for (int i = 0; i < 32; ++i) v[i] = epi_apply<EPI>(v[i], i < ncol ? ax[i] : 0.f, alpha, beta);
       }
     } else {
-      __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + doff;
-      if (ncol == 32 && vec_ok) {
+      const __nv_bfloat16* ax = reinterpret_cast<const __nv_bfloat16*>(p.aux) + aoff;
+      if (pre != nullptr || (ncol == 32 && (p.ldaux & 7) == 0 && (p.sAux & 7) == 0 &&
+                             (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0)) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          uint4 pk;
-          pk.x = pack_bf16(v[8 * q], v[8 * q + 1]);
-          pk.y = pack_bf16(v[8 * q + 2], v[8 * q + 3]);
-          pk.z = pack_bf16(v[8 * q + 4], v[8 * q + 5]);
-          pk.w = pack_bf16(v[8 * q + 6], v[8 * q + 7]);
-          reinterpret_cast<uint4*>(d)[q] = pk;
+          uint4 pk = pre ? pre[q] : reinterpret_cast<const uint4*>(ax)[q];
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float2 f = __bfloat1622float2(h[i]);
+            v[q * 8 + 2 * i] = epi_apply<EPI>(v[q * 8 + 2 * i], f.x, alpha, beta);
+            v[q * 8 + 2 * i + 1] = epi_apply<EPI>(v[q * 8 + 2 * i + 1], f.y, alpha, beta);
+          }
         }
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i)
-          if (i < ncol) d[i] = __float2bfloat16(v[i]);
+          v[i] = epi_apply<EPI>(v[i], i < ncol ? __bfloat162float(ax[i]) : 0.f, alpha, beta);
       }
     }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = epi_apply<EPI>(v[i], 0.f, alpha, beta);
+  }
+  if constexpr (EPI == kEpiAtomicAdd) {
+    // split-K partial sums: fp32 vector reductions into the (pre-existing) output
+    float* d = reinterpret_cast<float*>(p.D) + doff;
+    if (ncol == 32 && vec_ok) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        atomicAdd(reinterpret_cast<float4*>(d) + q, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < ncol) atomicAdd(d + i, v[i]);
+    }
+  } else if (p.out_fp32) {
+    float* d = reinterpret_cast<float*>(p.D) + doff;
+    if (ncol == 32 && vec_ok) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        reinterpret_cast<float4*>(d)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < ncol) d[i] = v[i];
+    }
+  } else {
+    __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(p.D) + doff;
+    if (ncol == 32 && vec_ok) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint4 pk;
+        pk.x = pack_bf16(v[8 * q], v[8 * q + 1]);
+        pk.y = pack_bf16(v[8 * q + 2], v[8 * q + 3]);
+        pk.z = pack_bf16(v[8 * q + 4], v[8 * q + 5]);
+        pk.w = pack_bf16(v[8 * q + 6], v[8 * q + 7]);
+        reinterpret_cast<uint4*>(d)[q] = pk;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < ncol) d[i] = __float2bfloat16(v[i]);
+    }
+  }
+}
+
+__device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const uint32_t (&r)[32], int row,
+                                                     int col0, int b, bool vec_ok, bool /*need_aux*/,
+                                                     const uint4* pre = nullptr) {
+  switch (p.epi) {
+    case kEpiAxpby: epilogue_chunk_t<kEpiAxpby>(p, r, row, col0, b, vec_ok, pre); break;
+    case kEpiRelu2: epilogue_chunk_t<kEpiRelu2>(p, r, row, col0, b, vec_ok, pre); break;
+    case kEpiMulDRelu2: epilogue_chunk_t<kEpiMulDRelu2>(p, r, row, col0, b, vec_ok, pre); break;
+    case kEpiAtomicAdd: epilogue_chunk_t<kEpiAtomicAdd>(p, r, row, col0, b, vec_ok, pre); break;
+    default: epilogue_chunk_t<kEpiScale>(p, r, row, col0, b, vec_ok, pre); break;
   }
 }
 
