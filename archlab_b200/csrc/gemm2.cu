@@ -6,7 +6,7 @@
 //
 // Protocol (per CTA: warp 0 TMA producer, warp 1 MMA issuer in the leader, warps 2..5 epilogue):
 //   * every TMA load of either CTA completes its bytes on the LEADER's full[stage] barrier
-//     (cp.async.bulk.tensor with .cta_group::2, no multicast);
+//     (cp.async.bulk.tensor with .cta_group::2; each CTA loads its own tiles);
 //   * the leader's MMA thread waits on full[stage], issues the pair MMA, and releases the stage with
 //     a tcgen05.commit multicast to empty[stage] of BOTH CTAs;
 //   * accumulator hand-off uses tmem_full[acc] (commit multicast, one arrival per CTA) and the

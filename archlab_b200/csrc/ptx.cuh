@@ -97,7 +97,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 // ----------------------------------------------------------------------------------------------
-// TMA (cp.async.bulk.tensor), tiled mode, no multicast anywhere.
+// TMA (cp.async.bulk.tensor), tiled mode; every CTA issues its own loads.
 // ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

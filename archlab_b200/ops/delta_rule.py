@@ -56,15 +56,35 @@ def kda_recurrent_reference(q, k, v, g, beta):
     return torch.stack(outs, dim=1)
 
 
+def _decayed_gram(a: torch.Tensor, b: torch.Tensor, G: torch.Tensor, sub: int = 16) -> torch.Tensor:
+    """M[t, s] = sum_c a[t, c] b[s, c] exp(G[t, c] - G[s, c]) for s <= t, else 0, over the last two dims
+    ``[C, K]``.  Every exponent that is evaluated is <= 0 (G is non-increasing in t): blocks below the
+    diagonal factor through the cumulative decay at the first row of the row block, diagonal
+    ``sub x sub`` blocks are evaluated pairwise."""
+    C = a.size(-2)
+    out = a.new_zeros(*a.shape[:-2], C, C)
+    for i0 in range(0, C, sub):
+        i1 = min(C, i0 + sub)
+        ref = G[..., i0:i0 + 1, :]
+        left = a[..., i0:i1, :] * (G[..., i0:i1, :] - ref).exp()
+        if i0:
+            right = b[..., :i0, :] * (ref - G[..., :i0, :]).clamp_max(0).exp()
+            out[..., i0:i1, :i0] = left @ right.transpose(-1, -2)
+        diff = (G[..., i0:i1, None, :] - G[..., None, i0:i1, :]).clamp_max(0).exp()       # [sub, sub, K]
+        blk = torch.einsum("...tc,...sc,...tsc->...ts", a[..., i0:i1, :], b[..., i0:i1, :], diff)
+        out[..., i0:i1, i0:i1] = torch.tril(blk)
+    return out
+
+
 def chunk_kda(q, k, v, g, beta, chunk: int = 64, initial_state=None, output_final_state: bool = False):
     """Chunk-parallel KDA (per-channel decay); GDN is the special case of a channel-constant ``g``.
 
-    Within a chunk with cumulative log-decay ``G_t = sum_{s<=t} g_s`` (per channel), define
-    ``kd_t = k_t * exp(G_t)``, ``ku_t = k_t * exp(-G_t)``, ``qd_t = q_t * exp(G_t)``.  The corrected
+    Within a chunk with cumulative log-decay ``G_t = sum_{s<=t} g_s`` (per channel) the corrected
     values ``u`` solve the unit-lower-triangular system
-        (I + tril(diag(beta) (kd ku^T), -1)) u = beta * (v - kd S_0)
-    and  o = qd S_0 + tril(qd ku^T) u ,   S_C = exp(G_C) * S_0 + (ku * exp(G_C))^T u.
-    """
+        (I + strict_tril(diag(beta) P)) u = beta * (v - (k exp(G)) S_0),  P[t,s] = sum_c k_t k_s exp(G_t - G_s)
+    and  o = (q exp(G)) S_0 + tril(Q) u  with Q[t,s] = sum_c q_t k_s exp(G_t - G_s),
+         S_C = exp(G_C) * S_0 + (k exp(G_C - G))^T u.
+    All exponentials are of non-positive numbers, so strong decays cannot overflow."""
     q, k, v, g, beta = _prep(q, k, v, g, beta)
     B, T, H, K = q.shape
     V = v.size(-1)
@@ -77,18 +97,19 @@ def chunk_kda(q, k, v, g, beta, chunk: int = 64, initial_state=None, output_fina
     q, k, v, g = rs(q), rs(k), rs(v), rs(g)
     beta = beta.view(B, n, chunk, H).permute(0, 1, 3, 2)                  # [B, n, H, C]
     G = g.cumsum(dim=-2)
-    kd, ku, qd = k * G.exp(), k * (-G).exp(), q * G.exp()
+    kd, qd = k * G.exp(), q * G.exp()
     eye = torch.eye(chunk, device=q.device, dtype=q.dtype)
-    A = torch.tril(beta[..., None] * (kd @ ku.transpose(-1, -2)), -1) + eye
-    Aq = torch.tril(qd @ ku.transpose(-1, -2))
+    A = torch.tril(beta[..., None] * _decayed_gram(k, k, G), -1) + eye
+    Aq = _decayed_gram(q, k, G)
+    Gend = G[..., -1:, :]
+    kend = k * (Gend - G).exp()                                            # k_s exp(G_C - G_s)
     state = q.new_zeros(B, H, K, V) if initial_state is None else initial_state.float()
     outs = []
     for c in range(n):
         rhs = beta[:, c, ..., None] * (v[:, c] - kd[:, c] @ state)
         u = torch.linalg.solve_triangular(A[:, c], rhs, upper=False, unitriangular=True)
         outs.append(qd[:, c] @ state + Aq[:, c] @ u)
-        Gc = G[:, c, :, -1, :]                                             # [B, H, K]
-        state = Gc.exp()[..., None] * state + (ku[:, c] * Gc.exp()[:, :, None, :]).transpose(-1, -2) @ u
+        state = Gend[:, c].transpose(-1, -2).exp() * state + kend[:, c].transpose(-1, -2) @ u
     o = torch.stack(outs, dim=1).permute(0, 1, 3, 2, 4).reshape(B, n * chunk, H, V)[:, :T]
     return (o, state) if output_final_state else o
 

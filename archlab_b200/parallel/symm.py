@@ -10,12 +10,18 @@ release / acquire at system scope, bounded wait reporting through the device sta
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 
 import torch
 import torch.distributed as dist
 
 from ..ops import native
+
+# The kernels here use plain peer loads / stores only, so the buffers are not bound to an NVSwitch
+# multicast object (a rank that dies while bound can fault its peers' GPUs); opt in by setting the
+# variable to 0 before import.
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 _vp, _i, _ll, _f = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 native.register_signature("nga_peer_barrier", [_vp, _i, _i, _i, _vp, _vp])

@@ -206,3 +206,12 @@ def test_replicated_global_batch_pads_with_ignored_targets():
         parts.append(replicated_global_batch(p, r, 3))
     ys = torch.cat([y for _, y, _ in parts])
     assert ys.shape[0] == 6 and (ys[4:] == -1).all() and (ys[:4] >= 0).all()
+
+
+def test_chunk_forms_survive_strong_decay():
+    q, k, v, g, beta = _delta_inputs(B=1, T=130, H=2, K=8, V=8, per_channel=True, seed=3)
+    g = g * 80.0                                    # cumulative log-decay far below exp() underflow
+    ref = dr.kda_recurrent_reference(q, k, v, g, beta)
+    out = dr.chunk_kda(q, k, v, g, beta)
+    assert torch.isfinite(out).all()
+    torch.testing.assert_close(out, ref, atol=2e-5, rtol=1e-4)
