@@ -34,6 +34,16 @@ int nga_gemm2_bf16(const void* A, const void* B, void* D, const void* aux, int M
                    int epi, int out_fp32, int aux_fp32, float alpha, float beta, int splits,
                    int* status, void* stream);
 
+// Tensor-parallel GEMM fused with its collective over NVLink peer memory (CTA-pair kernel).
+// mode 1: all-gather of A row shards -> GEMM; mode 2: GEMM -> reduce-scatter of D row blocks into the
+// owners' staging slots, summed by nga_tp_reduce_slots after a cross-rank barrier.  See gemm2.cu.
+int nga_tp_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long ldb, long long ldd,
+                     int b_mn, int mode, int rank, int world, int rows_per_rank, const long long* src_ptrs,
+                     void* gathered, int* flags, int epoch, int copy_clusters, const long long* dst_ptrs,
+                     int* status, void* stream);
+int nga_tp_reduce_slots(const void* stage, const void* resid, void* out, int world, long long rows, int N,
+                        long long ld_stage, long long ld_resid, long long ld_out, void* stream);
+
 // Number of kernels this library has launched since load (every launcher increments it).
 long long nga_launch_count(void);
 void nga_launch_count_reset(void);

@@ -25,7 +25,9 @@ constexpr int G2_STAGES = 6;
 constexpr int G2_A_BYTES = BM * BK * 2;     // 16 KB: this CTA's 128 rows of A
 constexpr int G2_B_BYTES = 128 * BK * 2;    // 16 KB: this CTA's half of B
 constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
-constexpr int G2_BAR_OFFSET = G2_STAGES * G2_STAGE_BYTES;
+constexpr int G2_OUT_OFFSET = G2_STAGES * G2_STAGE_BYTES;      // 4 warps x 2 staging tiles of 32 rows x 128 B
+constexpr int G2_OUT_BYTES = 4 * 2 * 4096;
+constexpr int G2_BAR_OFFSET = G2_OUT_OFFSET + G2_OUT_BYTES;
 constexpr int G2_SMEM = G2_BAR_OFFSET + (2 * G2_STAGES + 4) * 8 + 16 + 1024;
 constexpr int G2_THREADS = 192;
 
@@ -87,10 +89,98 @@ __device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 
-template <int A_MN, int B_MN>
+// Untiled bulk copies (TMA engine) used by the all-gather clusters: peer global -> shared -> local global.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ void st_release_gpu(int* addr, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* addr, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+// Bounded wait for a gathered 128-row block; false (and the abort word set) when the budget runs out.
+__device__ __forceinline__ bool wait_block_ready(const int* flag, int epoch, volatile int* abort_word) {
+  if (ld_acquire_gpu(flag) >= epoch) return true;
+  const long long t0 = clock64();
+  while (ld_acquire_gpu(flag) < epoch) {
+    if (*abort_word != 0) return false;
+    if (clock64() - t0 > kWaitBudgetCycles) {
+      *abort_word = kErrPeerTimeout;
+      return false;
+    }
+  }
+  return true;
+}
+
+
+// All-gather role of one CTA: pulls its share of the 128-row blocks into `tp.gathered` (remote shards in
+// ring order, this rank's own rows last so that the gathered matrix is complete for the weight-gradient
+// GEMM).  One thread drives a ring of G2_STAGES bulk copies of up to G2_STAGE_BYTES each.
+__device__ __forceinline__ void tp_copy_role(const TpParams& tp, int K, uint8_t* smem, uint64_t* full_bar,
+                                             int copy_cta, int num_copy_ctas, volatile int* abort_word) {
+  const int blocks_per_rank = tp.rows_per_rank / BM;
+  const int items = tp.world * blocks_per_rank;
+  const long long block_bytes = (long long)BM * K * 2;
+  const int chunks = int((block_bytes + G2_STAGE_BYTES - 1) / G2_STAGE_BYTES);
+  uint32_t use = 0;                                   // global chunk counter -> slot and parity
+  for (int it = copy_cta; it < items; it += num_copy_ctas) {
+    const int src_rank = (tp.rank + 1 + it / blocks_per_rank) % tp.world;
+    const int blk = it % blocks_per_rank;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(tp.peer_src[src_rank]) + (long long)blk * block_bytes;
+    const long long grow = (long long)src_rank * tp.rows_per_rank + (long long)blk * BM;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(tp.gathered) + grow * K * 2;
+    const int ahead = chunks < G2_STAGES ? chunks : G2_STAGES;
+    for (int c = 0; c < ahead; ++c) {
+      const uint32_t slot = (use + c) % G2_STAGES;
+      const uint32_t bytes = uint32_t(min((long long)G2_STAGE_BYTES, block_bytes - (long long)c * G2_STAGE_BYTES));
+      mbar_expect_tx(&full_bar[slot], bytes);
+      bulk_load(smem + slot * G2_STAGE_BYTES, src + (long long)c * G2_STAGE_BYTES, bytes, &full_bar[slot]);
+    }
+    for (int c = 0; c < chunks; ++c) {
+      const uint32_t u = use + c;
+      const uint32_t slot = u % G2_STAGES;
+      const uint32_t bytes = uint32_t(min((long long)G2_STAGE_BYTES, block_bytes - (long long)c * G2_STAGE_BYTES));
+      if (!mbar_wait(&full_bar[slot], (u / G2_STAGES) & 1u, abort_word)) return;
+      bulk_store(dst + (long long)c * G2_STAGE_BYTES, smem + slot * G2_STAGE_BYTES, bytes);
+      tma_store_commit();
+      const int nx = c + G2_STAGES;
+      if (nx < chunks) {
+        tma_store_wait_read0();                         // the slot's bytes have left shared memory
+        const uint32_t nb = uint32_t(min((long long)G2_STAGE_BYTES, block_bytes - (long long)nx * G2_STAGE_BYTES));
+        mbar_expect_tx(&full_bar[slot], nb);
+        bulk_load(smem + slot * G2_STAGE_BYTES, src + (long long)nx * G2_STAGE_BYTES, nb, &full_bar[slot]);
+      }
+    }
+    use += chunks;
+    tma_store_wait0();                                  // the block is written
+    fence_proxy_async_all();
+    __threadfence();
+    st_release_gpu(tp.flags + grow / BM, tp.epoch);
+  }
+}
+
+template <int A_MN, int B_MN, int TP>
 __global__ void __launch_bounds__(G2_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const GemmParams p) {
+                  const GemmParams p, const __grid_constant__ CUtensorMap tmA2, const TpParams tp,
+                  const __grid_constant__ TpMaps tpm) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + G2_BAR_OFFSET);
@@ -102,8 +192,11 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();          // 0 = leader
-  const int cluster_id = blockIdx.x >> 1;
-  const int num_clusters = gridDim.x >> 1;
+  // With the all-gather fused in, the first `copy_clusters` clusters only move data.
+  const int copy_clusters = (TP && (tp.mode & kTpGather)) ? tp.copy_clusters : 0;
+  const bool copy_role = TP && int(blockIdx.x >> 1) < copy_clusters;
+  const int cluster_id = int(blockIdx.x >> 1) - copy_clusters;
+  const int num_clusters = int(gridDim.x >> 1) - copy_clusters;
 
   const int num_m = (p.M + 2 * BM - 1) / (2 * BM);   // 256-row tiles
   const int num_n = (p.N + G2_BN - 1) / G2_BN;
@@ -132,11 +225,15 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 0) {
+  if (copy_role) {
+    if (threadIdx.x == 0)
+      tp_copy_role(tp, p.K, smem, full_bar, int(blockIdx.x), 2 * copy_clusters, abort_word);
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
+      if (TP) tma_prefetch_desc(&tmA2);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -144,8 +241,21 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         int b, mb, nb, otile, kb0, kb1;
         split_range(tile, p.splits, num_kb, otile, kb0, kb1);
         tile_coords(otile, num_m, num_n, b, mb, nb);
-        const int m0 = mb * 2 * BM + int(rank) * BM;       // this CTA's 128 rows of A
+        if (TP) mb = tp_remap_mb(tp, mb, num_m);
+        int m0 = mb * 2 * BM + int(rank) * BM;             // this CTA's 128 rows of A
         const int n0 = nb * G2_BN + int(rank) * 128;       // this CTA's 128 N-rows of B
+        const CUtensorMap* mapA = &tmA;
+        if (TP && (tp.mode & kTpGather)) {
+          const int owner = m0 / tp.rows_per_rank;
+          if (owner == tp.rank) {                          // own rows: straight from the local shard
+            mapA = &tmA2;
+            m0 -= owner * tp.rows_per_rank;
+          } else {
+            ok = wait_block_ready(tp.flags + m0 / BM, tp.epoch, abort_word);
+            if (!ok) break;
+            fence_proxy_async_all();
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word);
           if (!ok) break;
@@ -156,9 +266,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (A_MN) {
 #pragma unroll
             for (int j = 0; j < 2; ++j)
-              tma_load_3d_pair(sA + j * 8192, &tmA, leader_full, m0 + j * 64, kb * BK, b);
+              tma_load_3d_pair(sA + j * 8192, mapA, leader_full, m0 + j * 64, kb * BK, b);
           } else {
-            tma_load_3d_pair(sA, &tmA, leader_full, kb * BK, m0, b);
+            tma_load_3d_pair(sA, mapA, leader_full, kb * BK, m0, b);
           }
           if (B_MN) {
 #pragma unroll
@@ -218,17 +328,59 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const bool vec_ok = epilogue_vec_ok(p);
     const bool need_aux = (p.epi == kEpiAxpby || p.epi == kEpiMulDRelu2);
     const bool aux_fast = aux_prefetchable(p);
+    uint32_t out_cnt = 0;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int b, mb, nb, otile, kb0, kb1;
       split_range(tile, p.splits, num_kb, otile, kb0, kb1);
       tile_coords(otile, num_m, num_n, b, mb, nb);
+      if (TP) mb = tp_remap_mb(tp, mb, num_m);
       const int row = mb * 2 * BM + int(rank) * BM + quarter * 32 + lane;
+      GemmParams pt = p;
+      if (TP && (tp.mode & kTpScatter)) {                   // this tile's rows live on rank `owner`
+        const int owner = (mb * 2 * BM) / tp.rows_per_rank;
+        pt.D = tp.peer_dst[owner];
+        pt.row_shift = (long long)(tp.rank - owner) * tp.rows_per_rank;
+      }
       AuxPre nxt;
       aux_prefetch(p, nxt, row, nb * G2_BN, b, aux_fast);   // in flight while the main loop finishes
       ok = __all_sync(0xffffffffu, mbar_wait(&tfull_bar[acc], acc_phase, abort_word));
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + uint32_t(acc * G2_BN) + (uint32_t(quarter * 32) << 16);
+      if (TP && (tp.mode & kTpScatter)) {
+        // reduce-scatter: bf16 tile -> swizzled staging tile -> one TMA store into the owner's slot
+        const int owner = (mb * 2 * BM) / tp.rows_per_rank;
+        const int row0 = mb * 2 * BM + int(rank) * BM + quarter * 32 + int(pt.row_shift);
+#pragma unroll 1
+        for (int c2 = 0; c2 < G2_BN / 64; ++c2) {
+          const int col0 = nb * G2_BN + c2 * 64;
+          if (col0 >= p.N) break;   // warp-uniform
+          uint32_t r2[2][32];
+          tmem_ld_32x32(taddr + uint32_t(c2 * 64), r2[0]);
+          tmem_ld_32x32(taddr + uint32_t(c2 * 64 + 32), r2[1]);
+          tmem_ld_wait();
+          uint8_t* buf = smem + G2_OUT_OFFSET + (quarter * 2 + int(out_cnt & 1u)) * 4096;
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t* v = &r2[q >> 2][(q & 3) * 8];
+            uint4 pk;
+            pk.x = pack_bf16(p.alpha * __uint_as_float(v[0]), p.alpha * __uint_as_float(v[1]));
+            pk.y = pack_bf16(p.alpha * __uint_as_float(v[2]), p.alpha * __uint_as_float(v[3]));
+            pk.z = pack_bf16(p.alpha * __uint_as_float(v[4]), p.alpha * __uint_as_float(v[5]));
+            pk.w = pack_bf16(p.alpha * __uint_as_float(v[6]), p.alpha * __uint_as_float(v[7]));
+            *reinterpret_cast<uint4*>(buf + lane * 128 + ((q ^ (lane & 7)) * 16)) = pk;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&tpm.d[owner], buf, col0, row0, 0);
+            tma_store_commit();
+          }
+          ++out_cnt;
+        }
+      } else
 #pragma unroll 1
       for (int c2 = 0; c2 < G2_BN / 64; ++c2) {
         if (nb * G2_BN + c2 * 64 >= p.N) break;   // warp-uniform
@@ -242,7 +394,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         for (int hc = 0; hc < 2; ++hc) {
           const int col0 = nb * G2_BN + (c2 * 2 + hc) * 32;
           if (col0 >= p.N) break;   // warp-uniform
-          epilogue_store_chunk(p, r2[hc], row, col0, b, vec_ok, need_aux, cur.valid[hc] ? cur.v[hc] : nullptr);
+          epilogue_store_chunk(pt, r2[hc], row, col0, b, vec_ok, need_aux, cur.valid[hc] ? cur.v[hc] : nullptr);
         }
       }
       tc_fence_before();
@@ -250,6 +402,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty_bar[acc]), 0));
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
+    if (TP && (tp.mode & kTpScatter) && lane == 0) tma_store_wait0();   // every tile has reached its owner
   }
 
   // ------------------------------------------------------------------ tear-down
@@ -265,9 +418,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_word);
 }
 
-template <int A_MN, int B_MN>
-static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
-  auto kern = gemm2_bf16_kernel<A_MN, B_MN>;
+template <int A_MN, int B_MN, int TP>
+static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream,
+                        const CUtensorMap& ta2, const TpParams& tp, const TpMaps& tpm) {
+  auto kern = gemm2_bf16_kernel<A_MN, B_MN, TP>;
   static int max_clusters = 0;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
@@ -290,12 +444,49 @@ static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
     max_clusters = n;
   }
   const int num_tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch * p.splits;
-  const int clusters = num_tiles < max_clusters ? num_tiles : max_clusters;
+  int clusters = num_tiles < max_clusters ? num_tiles : max_clusters;
+  if (TP && (tp.mode & kTpGather)) {
+    // every cluster must be resident at once: the GEMM clusters wait for the copy clusters
+    if (tp.copy_clusters < 1 || tp.copy_clusters >= max_clusters) return -9;
+    const int gemm_clusters = num_tiles < max_clusters - tp.copy_clusters ? num_tiles : max_clusters - tp.copy_clusters;
+    clusters = gemm_clusters + tp.copy_clusters;
+  }
   cfg.gridDim = dim3(2 * clusters);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, p, ta2, tp, tpm);
   count_launch();
   if (e != cudaSuccess) return -1000 - (int)e;
   return 0;
+}
+
+// out[r, c] = (resid ? resid[r, c] : 0) + sum_s stage[s * rows + r, c]   (fp32 accumulation, bf16 in/out)
+__global__ void tp_reduce_slots_kernel(const __nv_bfloat16* __restrict__ stage, const __nv_bfloat16* __restrict__ resid,
+                                       __nv_bfloat16* __restrict__ out, int world, long long rows, int N,
+                                       long long ld_stage, long long ld_resid, long long ld_out) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i >= rows * N) return;
+  const long long r = i / N;
+  const int c = int(i - r * N);
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  auto add = [&](const __nv_bfloat16* src) {
+    const uint4 v = *reinterpret_cast<const uint4*>(src);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]);
+      acc[2 * k] += f.x;
+      acc[2 * k + 1] += f.y;
+    }
+  };
+  if (resid != nullptr) add(resid + r * ld_resid + c);
+  for (int s = 0; s < world; ++s) add(stage + ((long long)s * rows + r) * ld_stage + c);
+  uint4 o;
+  o.x = pack_bf16(acc[0], acc[1]);
+  o.y = pack_bf16(acc[2], acc[3]);
+  o.z = pack_bf16(acc[4], acc[5]);
+  o.w = pack_bf16(acc[6], acc[7]);
+  *reinterpret_cast<uint4*>(out + r * ld_out + c) = o;
 }
 
 }  // namespace nga
@@ -338,9 +529,84 @@ extern "C" int nga_gemm2_bf16(const void* A, const void* B, void* D, const void*
   }
   if (epi == kEpiAtomicAdd && !out_fp32) return -8;
   p.status = status;
+  p.row_shift = 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (a_mn && b_mn) return launch_gemm2<1, 1>(ta, tb, p, st);
-  if (a_mn && !b_mn) return launch_gemm2<1, 0>(ta, tb, p, st);
-  if (!a_mn && b_mn) return launch_gemm2<0, 1>(ta, tb, p, st);
-  return launch_gemm2<0, 0>(ta, tb, p, st);
+  TpParams tp = {};
+  static const TpMaps no_maps = {};
+  if (a_mn && b_mn) return launch_gemm2<1, 1, 0>(ta, tb, p, st, ta, tp, no_maps);
+  if (a_mn && !b_mn) return launch_gemm2<1, 0, 0>(ta, tb, p, st, ta, tp, no_maps);
+  if (!a_mn && b_mn) return launch_gemm2<0, 1, 0>(ta, tb, p, st, ta, tp, no_maps);
+  return launch_gemm2<0, 0, 0>(ta, tb, p, st, ta, tp, no_maps);
+}
+
+// Tensor-parallel GEMM fused with its collective (see TpParams).  A is K-major; B is K-major (b_mn = 0)
+// or MN-major (b_mn = 1); D is bf16.
+//   mode = 1 (all-gather -> GEMM): `src_ptrs[r]` is rank r's row shard [rows_per_rank, K] (contiguous,
+//     symmetric memory), `gathered` a local [world * rows_per_rank, K] buffer, `flags` a local int array
+//     with one entry per 128 gathered rows (zero-initialised once; `epoch` must grow by one per call).
+//     D [M = world * rows_per_rank, N] is local.
+//   mode = 2 (GEMM -> reduce-scatter): A [M, K] is local; `dst_ptrs[r]` is rank r's staging buffer
+//     [world, rows_per_rank, ldd]; this rank's partial sums for rank r's rows land in slot `rank` there.
+//     The owner sums the slots with nga_tp_reduce_slots after a cross-rank barrier.
+extern "C" int nga_tp_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, long long ldb,
+                                long long ldd, int b_mn, int mode, int rank, int world, int rows_per_rank,
+                                const long long* src_ptrs, void* gathered, int* flags, int epoch,
+                                int copy_clusters, const long long* dst_ptrs, int* status, void* stream) {
+  using namespace nga;
+  if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > kTpMaxWorld || rank < 0 || rank >= world) return -1;
+  if (rows_per_rank <= 0 || rows_per_rank % 256 || M != world * rows_per_rank) return -2;
+  if ((K & 63) || (ldb & 7) || (ldd & 7)) return -5;
+  if (mode != kTpGather && mode != kTpScatter) return -3;
+  TpParams tp = {};
+  tp.mode = mode; tp.rank = rank; tp.world = world; tp.rows_per_rank = rows_per_rank;
+  tp.copy_clusters = copy_clusters; tp.epoch = epoch; tp.flags = flags; tp.gathered = gathered;
+  for (int r = 0; r < world; ++r) {
+    tp.peer_src[r] = (mode == kTpGather) ? reinterpret_cast<const void*>(src_ptrs[r]) : nullptr;
+    tp.peer_dst[r] = (mode == kTpScatter) ? reinterpret_cast<void*>(dst_ptrs[r]) : nullptr;
+  }
+  const void* a_full = (mode == kTpGather) ? gathered : A;
+  const void* a_own = (mode == kTpGather) ? tp.peer_src[rank] : A;
+  if (a_full == nullptr || a_own == nullptr) return -4;
+  CUtensorMap ta, ta2, tb;
+  int rc = make_tmap_3d(&ta, a_full, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, 1, (long long)K * 2,
+                        (long long)M * K * 2, 64, 128, true);
+  if (rc) return rc;
+  const long long own_rows = (mode == kTpGather) ? rows_per_rank : M;
+  rc = make_tmap_3d(&ta2, a_own, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, own_rows, 1, (long long)K * 2,
+                    own_rows * K * 2, 64, 128, true);
+  if (rc) return rc;
+  if (b_mn)
+    rc = make_tmap_3d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, 1, ldb * 2, (long long)K * ldb * 2, 64, 64, true);
+  else
+    rc = make_tmap_3d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, 1, ldb * 2, (long long)N * ldb * 2, 64, 128, true);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.batch = 1;
+  p.D = D; p.aux = nullptr; p.ldd = ldd; p.ldaux = 0; p.sD = 0; p.sAux = 0;
+  p.epi = kEpiScale; p.out_fp32 = 0; p.aux_fp32 = 0; p.alpha = 1.f; p.beta = 0.f; p.splits = 1;
+  p.status = status; p.row_shift = 0;
+  TpMaps tpm = {};
+  if (mode == kTpScatter) {
+    for (int r = 0; r < world; ++r) {
+      rc = make_tmap_3d(&tpm.d[r], tp.peer_dst[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, (long long)world * rows_per_rank,
+                        1, ldd * 2, (long long)world * rows_per_rank * ldd * 2, 64, 32, true);
+      if (rc) return rc;
+    }
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (b_mn) return launch_gemm2<0, 1, 1>(ta, tb, p, st, ta2, tp, tpm);
+  return launch_gemm2<0, 0, 1>(ta, tb, p, st, ta2, tp, tpm);
+}
+
+extern "C" int nga_tp_reduce_slots(const void* stage, const void* resid, void* out, int world, long long rows, int N,
+                                   long long ld_stage, long long ld_resid, long long ld_out, void* stream) {
+  using namespace nga;
+  if (world < 1 || rows <= 0 || N <= 0 || (N & 7) || (ld_stage & 7) || (ld_resid & 7) || (ld_out & 7)) return -1;
+  const long long n8 = rows * N / 8;
+  tp_reduce_slots_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(stage), reinterpret_cast<const __nv_bfloat16*>(resid),
+      reinterpret_cast<__nv_bfloat16*>(out), world, rows, N, ld_stage, ld_resid, ld_out);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
 }

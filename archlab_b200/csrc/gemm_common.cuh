@@ -1,6 +1,7 @@
 // Pieces shared by the single-CTA and the CTA-pair GEMM kernels: parameter block, tile order and the
 // register epilogue (scale / axpby / ReLU^2 / ReLU^2-backward, bf16 or fp32 output).
 #pragma once
+#include <cuda.h>
 #include "ptx.cuh"
 #include "gemm.h"
 
@@ -20,7 +21,45 @@ struct GemmParams {
   float alpha, beta;
   int splits;                    // split-K factor (> 1 only with kEpiAtomicAdd)
   int* status;
+  long long row_shift;           // added to the row index when addressing D (tensor-parallel staging slots)
 };
+
+// Tensor-parallel fusion of the CTA-pair GEMM with its collective over NVLink peer memory.
+//   kTpGather : A = concatenation over ranks of row shards [rows_per_rank, K].  `copy_clusters`
+//               clusters pull the remote shards into the local `gathered` buffer with bulk copies (each
+//               remote byte crosses NVLink once; one SM sustains ~17 GB/s of such copies, so about two
+//               dozen CTAs are needed to keep a link busy) and publish 128-row blocks through `flags`;
+//               the GEMM clusters start on this rank's own rows (read straight from the shard) and wait
+//               (bounded) for a block before loading it.
+//   kTpScatter: D row blocks belong to the rank that owns those rows; tiles are stored straight into
+//               that rank's staging buffer at slot `rank` ([world][rows_per_rank, ldd]), remote owners
+//               first, so the reduce-scatter traffic overlaps the remaining tiles.
+constexpr int kTpMaxWorld = 8;
+constexpr int kTpGather = 1;
+constexpr int kTpScatter = 2;
+struct TpParams {
+  int mode, rank, world, rows_per_rank;
+  int copy_clusters, epoch;
+  int* flags;                          // one per 128-row block of the gathered matrix; value = epoch when ready
+  const void* peer_src[kTpMaxWorld];   // row shard of every rank (bf16, contiguous rows of K elements, symmetric)
+  void* gathered;                      // local [world * rows_per_rank, K] bf16
+  void* peer_dst[kTpMaxWorld];         // reduce-scatter staging buffer of every rank
+};
+
+// Tensor maps of the reduce-scatter staging buffer on every rank ([world * rows_per_rank, ldd] bf16,
+// box 64 columns x 32 rows, 128-byte swizzle): output tiles leave through TMA stores, so the NVLink
+// write stream consists of full 128-byte lines.
+struct TpMaps {
+  CUtensorMap d[kTpMaxWorld];
+};
+
+__device__ __forceinline__ int tp_remap_mb(const TpParams& tp, int mb, int num_m) {
+  if (tp.mode == 0) return mb;
+  const int per = tp.rows_per_rank / (2 * BM);
+  const int first = (tp.mode & kTpGather) ? tp.rank * per : ((tp.rank + 1) % tp.world) * per;
+  int r = mb + first;
+  return r >= num_m ? r - num_m : r;
+}
 
 __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& b, int& mb, int& nb) {
   const int per_batch = num_m * num_n;
@@ -94,7 +133,7 @@ __device__ __forceinline__ void epilogue_chunk_t(const GemmParams& p, const uint
                                                  int b, bool vec_ok, const uint4* pre) {
   constexpr bool kNeedAux = (EPI == kEpiAxpby || EPI == kEpiMulDRelu2);
   if (row >= p.M) return;
-  const long long doff = (long long)b * p.sD + (long long)row * p.ldd + col0;
+  const long long doff = (long long)b * p.sD + ((long long)row + p.row_shift) * p.ldd + col0;
   const int ncol = min(32, p.N - col0);
   const float alpha = p.alpha, beta = p.beta;
   float v[32];

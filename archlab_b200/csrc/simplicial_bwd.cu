@@ -1,0 +1,820 @@
+// 2-simplicial (trilinear) windowed attention, backward, on tcgen05 + TMEM.  head_dim 128,
+// w1 in {8, 16, 32}.  With rows r = (query i, short key j), A_r = q_i * k1_j, G_r = dO_i * v1_j:
+//     S  = A K2^T                 P  = exp2(S * scale*log2e - lse2[i])          (joint softmax)
+//     dP = G V2^T                 dS = P * (dP - delta[i]) * scale,   delta[i] = dO_i . O_i
+//     dA = dS K2   -> dq_i = sum_j dA_(i,j) * k1_j ,  dk1_j += sum_i dA_(i,j) * q_i
+//     Op = P  V2   -> dv1_j += sum_i Op_(i,j) * dO_i
+//     dK2 = dS^T A ,  dV2 = P^T G
+// (oracle: autograd through src/archlab/architectures/simplicial_attention.py:49-74; incumbents:
+// Triton simplicial_kernels.py:56-177, TileLang tilelang_attention.py:143-378.)
+//
+// Two kernels, each keeping its accumulators in TMEM for the CTA lifetime:
+//   * query-owned (this file, part 1): CTA = 128 rows (128 / w1 queries), walks 64-key tiles of the
+//     long window; dA and Op accumulate in TMEM; dq is written directly, dk1 / dv1 are added to fp32
+//     buffers with vector atomics (rows of neighbouring CTAs and of the query heads of a KV group
+//     overlap).
+//   * key-owned (part 2): CTA = 128 long keys, walks the 64-row groups that can see them in the
+//     transposed frame (thread = key); dK2 / dV2 accumulate in TMEM and are added once per CTA.
+#include "ptx.cuh"
+#include "host_util.h"
+#include "simplicial.h"
+#include <cuda.h>
+
+namespace nga {
+
+constexpr int SB_D = 128;
+constexpr int SB_BK = 64;            // long keys per tile (query-owned kernel)
+constexpr int SB_THREADS = 192;
+
+struct SimpBwdParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k1;
+  const __nv_bfloat16* v1;
+  const __nv_bfloat16* dout;   // [B*N, lddo]
+  const float* lse2;           // [B, Hq, N]
+  const float* delta;          // [B, Hq, N]
+  __nv_bfloat16* dq;           // [B*N, lddq]
+  float* dk1;                  // [B*N, Hkv*D] fp32, zeroed by the launcher
+  float* dv1;                  // [B*N, Hkv*D] fp32, zeroed by the launcher
+  float* dk2;                  // [B*N, Hkv*D] fp32, zeroed by the launcher
+  float* dv2;
+  long long ldq, ldk1, ldv1, lddo, lddq;
+  int B, N, Hq, Hkv, w1, w2;
+  float scale, scale_log2;
+  int* status;
+};
+
+// delta[b, h, i] = sum_d out * dout   (one warp per (token, head)); strided rows.
+__global__ void simp_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
+                                  float* __restrict__ delta, long long ldo, long long lddo, int B, int N, int Hq) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)B * N * Hq) return;
+  const long long row = w / Hq;
+  const int h = int(w % Hq);
+  const uint2 a = *reinterpret_cast<const uint2*>(out + row * ldo + h * SB_D + lane * 4);
+  const uint2 g = *reinterpret_cast<const uint2*>(dout + row * lddo + h * SB_D + lane * 4);
+  const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float2 x = __bfloat1622float2(ah[i]), y = __bfloat1622float2(gh[i]);
+    s += x.x * y.x + x.y * y.y;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) delta[((row / N) * Hq + h) * N + (row % N)] = s;
+}
+
+// out[row, c] = bf16(acc[row, c]) for an fp32 [rows, cols] buffer into a strided bf16 destination.
+__global__ void simp_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dst, long long rows,
+                                 int cols, long long ld) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= rows * cols) return;
+  const long long row = i / cols;
+  const int c = int(i % cols);
+  const float4 v = *reinterpret_cast<const float4*>(acc + i);
+  uint2 u;
+  u.x = pack_bf16(v.x, v.y);
+  u.y = pack_bf16(v.z, v.w);
+  *reinterpret_cast<uint2*>(dst + row * ld + c) = u;
+}
+
+// Row r of a [128 x 128] K-major operand tile (two 64-column halves of 16 KB, 128-byte swizzle):
+// element-wise product of two bf16 rows, zero when the row is masked.
+__device__ __forceinline__ void build_product_row(uint8_t* tile, int r, const __nv_bfloat16* x, const __nv_bfloat16* y,
+                                                  bool valid) {
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {
+    const uint4 xa = *reinterpret_cast<const uint4*>(x + c * 8);
+    const uint4 ya = *reinterpret_cast<const uint4*>(y + c * 8);
+    const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xa);
+    const __nv_bfloat162* yh = reinterpret_cast<const __nv_bfloat162*>(&ya);
+    uint4 o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(xh[e]), b = __bfloat1622float2(yh[e]);
+      ow[e] = valid ? pack_bf16(a.x * b.x, a.y * b.y) : 0u;
+    }
+    const int chunk = (c & 7) ^ (r & 7);
+    *reinterpret_cast<uint4*>(tile + (c >> 3) * 16384 + r * 128 + chunk * 16) = o;
+  }
+}
+
+__device__ __forceinline__ float segsum(float v, int w1) {
+  for (int o = 1; o < w1; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+struct SimpBwdQSmem {
+  static constexpr int kA = 0;                    // 32 KB  q * k1 rows
+  static constexpr int kG = 32768;                // 32 KB  dO * v1 rows
+  static constexpr int kK = 65536;                // 2 x 16 KB  K2 tiles [64 keys][128 d]
+  static constexpr int kV = kK + 2 * 16384;       // 2 x 16 KB  V2 tiles
+  static constexpr int kP = kV + 2 * 16384;       // 16 KB  P  [128 rows][64 keys]
+  static constexpr int kDS = kP + 16384;          // 16 KB  dS
+  static constexpr int kBar = kDS + 16384;
+  static constexpr int kTotal = kBar + 16 * 8 + 16 + 1024;
+};
+
+__global__ void __launch_bounds__(SB_THREADS, 1)
+simplicial_bwd_q_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_constant__ CUtensorMap tm_v2,
+                        const SimpBwdParams p) {
+  using S = SimpBwdQSmem;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kBar);
+  uint64_t* ag_full = bars + 0;
+  uint64_t* kv_full = bars + 1;     // [2]
+  uint64_t* kv_empty = bars + 3;    // [2]
+  uint64_t* s_full = bars + 5;      // [2]
+  uint64_t* s_free = bars + 7;      // [2]
+  uint64_t* p_full = bars + 9;
+  uint64_t* p_empty = bars + 10;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int BQ = 128 / p.w1;
+  const int i0 = blockIdx.x * BQ;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int row_base = b * p.N;
+  const int i_last = min(i0 + BQ - 1, p.N - 1);
+  const int t_lo = max(0, i0 - p.w2 + 1) / SB_BK;
+  const int t_hi = i_last / SB_BK;
+  const int ntiles = t_hi - t_lo + 1;
+  const int kv_col = hk * SB_D;
+
+  if (threadIdx.x == 0) {
+    mbar_init(ag_full, 4);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(p_empty, 1);
+    *abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_S = tmem_base;            // 2 x 64 columns
+  const uint32_t tmem_dP = tmem_base + 128;     // 2 x 64 columns
+  const uint32_t tmem_dA = tmem_base + 256;     // 128 columns
+  const uint32_t tmem_Op = tmem_base + 384;     // 128 columns
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_k2);
+      tma_prefetch_desc(&tm_v2);
+      bool ok = true;
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int st = j & 1;
+        ok = mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1u, abort_word);
+        if (!ok) break;
+        const int krow = row_base + (t_lo + j) * SB_BK;
+        uint8_t* sK = smem + S::kK + st * 16384;
+        uint8_t* sV = smem + S::kV + st * 16384;
+        mbar_expect_tx(&kv_full[st], 2 * 16384);
+        tma_load_3d(sK, &tm_k2, &kv_full[st], kv_col, krow, 0);
+        tma_load_3d(sK + 8192, &tm_k2, &kv_full[st], kv_col + 64, krow, 0);
+        tma_load_3d(sV, &tm_v2, &kv_full[st], kv_col, krow, 0);
+        tma_load_3d(sV + 8192, &tm_v2, &kv_full[st], kv_col + 64, krow, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, 0, 0);      // [128 rows] x [64 keys], K = d
+      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, 128, 0, 1);   // [128 rows] x [128 d],   K = keys
+      const uint32_t sA = smem_u32(smem + S::kA);
+      const uint32_t sG = smem_u32(smem + S::kG);
+      const uint32_t sP = smem_u32(smem + S::kP);
+      const uint32_t sDS = smem_u32(smem + S::kDS);
+      bool ok = mbar_wait(ag_full, 0, abort_word);
+      auto issue_scores = [&](int j) {
+        const uint32_t sK = smem_u32(smem + S::kK + (j & 1) * 16384);
+        const uint32_t sV = smem_u32(smem + S::kV + (j & 1) * 16384);
+        const uint32_t dS_ = tmem_S + uint32_t((j & 1) * 64);
+        const uint32_t dP_ = tmem_dP + uint32_t((j & 1) * 64);
+#pragma unroll
+        for (int k = 0; k < SB_D / 16; ++k) {
+          const uint32_t offa = (k >> 2) * 16384 + (k & 3) * 32;
+          const uint32_t offb = (k >> 2) * 8192 + (k & 3) * 32;
+          umma_bf16_ss(dS_, umma_smem_desc(sA + offa, 16, 1024), umma_smem_desc(sK + offb, 16, 1024), idesc_s,
+                       k != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < SB_D / 16; ++k) {
+          const uint32_t offa = (k >> 2) * 16384 + (k & 3) * 32;
+          const uint32_t offb = (k >> 2) * 8192 + (k & 3) * 32;
+          umma_bf16_ss(dP_, umma_smem_desc(sG + offa, 16, 1024), umma_smem_desc(sV + offb, 16, 1024), idesc_s,
+                       k != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[j & 1]);
+      };
+      if (ok) ok = mbar_wait(&kv_full[0], 0, abort_word);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(0);
+      }
+      for (int j = 0; j < ntiles && ok; ++j) {
+        if (j + 1 < ntiles) {
+          const int jn = j + 1;
+          ok = mbar_wait(&kv_full[jn & 1], (jn >> 1) & 1, abort_word);
+          if (ok) ok = mbar_wait(&s_free[jn & 1], ((jn >> 1) & 1) ^ 1u, abort_word);
+          if (!ok) break;
+          tc_fence_after();
+          issue_scores(jn);
+        }
+        ok = mbar_wait(p_full, j & 1, abort_word);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sK = smem_u32(smem + S::kK + (j & 1) * 16384);
+        const uint32_t sV = smem_u32(smem + S::kV + (j & 1) * 16384);
+#pragma unroll
+        for (int k = 0; k < SB_BK / 16; ++k) {
+          umma_bf16_ss(tmem_dA, umma_smem_desc(sDS + k * 32, 16, 1024), umma_smem_desc(sK + k * 2048, 8192, 1024),
+                       idesc_acc, (j | k) != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < SB_BK / 16; ++k) {
+          umma_bf16_ss(tmem_Op, umma_smem_desc(sP + k * 32, 16, 1024), umma_smem_desc(sV + k * 2048, 8192, 1024),
+                       idesc_acc, (j | k) != 0 ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[j & 1]);
+        umma_commit(p_empty);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- compute warps: row = (query, short key)
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int qi = r / p.w1, jj = r % p.w1;
+    const int i = i0 + qi;
+    const int p1 = i - p.w1 + 1 + jj;
+    const bool row_valid = (i < p.N) && (p1 >= 0);
+    const uint32_t lane_off = uint32_t(quarter * 32) << 16;
+    const long long qrow_idx = row_base + min(i, p.N - 1);
+    const long long krow_idx = row_base + max(p1, 0);
+    const __nv_bfloat16* qrow = p.q + qrow_idx * p.ldq + h * SB_D;
+    const __nv_bfloat16* k1row = p.k1 + krow_idx * p.ldk1 + hk * SB_D;
+    const __nv_bfloat16* v1row = p.v1 + krow_idx * p.ldv1 + hk * SB_D;
+    const __nv_bfloat16* dorow = p.dout + qrow_idx * p.lddo + h * SB_D;
+    build_product_row(smem + S::kA, r, qrow, k1row, row_valid);
+    build_product_row(smem + S::kG, r, dorow, v1row, row_valid);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(ag_full);
+    const long long stat = ((long long)b * p.Hq + h) * p.N + min(i, p.N - 1);
+    const float lse = p.lse2[stat];
+    const float dlt = p.delta[stat];
+    bool ok = true;
+    uint8_t* sP = smem + S::kP;
+    uint8_t* sDS = smem + S::kDS;
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int k0 = (t_lo + j) * SB_BK;
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_word));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sv[2][32], dv[2][32];
+      const uint32_t tS = tmem_S + uint32_t((j & 1) * 64) + lane_off;
+      const uint32_t tP = tmem_dP + uint32_t((j & 1) * 64) + lane_off;
+      tmem_ld_32x32(tS, sv[0]);
+      tmem_ld_32x32(tS + 32, sv[1]);
+      tmem_ld_32x32(tP, dv[0]);
+      tmem_ld_32x32(tP + 32, dv[1]);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[j & 1]);          // the score buffers can be overwritten
+      const int lo = i - p.w2 + 1 - k0, hi = i - k0;      // valid columns are [lo, hi]
+      if (j > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(p_empty, (j - 1) & 1, abort_word));
+        if (!ok) break;
+      }
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float pr[32], ds[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int col = c * 32 + e;
+          const bool v = row_valid && col >= lo && col <= hi;
+          const float pv = v ? exp2f(fmaf(__uint_as_float(sv[c][e]), p.scale_log2, -lse)) : 0.f;
+          pr[e] = pv;
+          ds[e] = pv * (__uint_as_float(dv[c][e]) - dlt) * p.scale;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = (c * 4 + g) ^ (r & 7);
+          uint4 u, w;
+          u.x = pack_bf16(pr[8 * g + 0], pr[8 * g + 1]);
+          u.y = pack_bf16(pr[8 * g + 2], pr[8 * g + 3]);
+          u.z = pack_bf16(pr[8 * g + 4], pr[8 * g + 5]);
+          u.w = pack_bf16(pr[8 * g + 6], pr[8 * g + 7]);
+          w.x = pack_bf16(ds[8 * g + 0], ds[8 * g + 1]);
+          w.y = pack_bf16(ds[8 * g + 2], ds[8 * g + 3]);
+          w.z = pack_bf16(ds[8 * g + 4], ds[8 * g + 5]);
+          w.w = pack_bf16(ds[8 * g + 6], ds[8 * g + 7]);
+          *reinterpret_cast<uint4*>(sP + r * 128 + chunk * 16) = u;
+          *reinterpret_cast<uint4*>(sDS + r * 128 + chunk * 16) = w;
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    // ---------------------------------------------------------------- epilogue
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(p_empty, (ntiles - 1) & 1, abort_word));
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* dqrow = p.dq + qrow_idx * p.lddq + h * SB_D;
+      float* dk1row = p.dk1 + krow_idx * ((long long)p.Hkv * SB_D) + hk * SB_D;
+      float* dv1row = p.dv1 + krow_idx * ((long long)p.Hkv * SB_D) + hk * SB_D;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t da[32], op[32];
+        tmem_ld_32x32(tmem_dA + lane_off + c * 32, da);
+        tmem_ld_32x32(tmem_Op + lane_off + c * 32, op);
+        tmem_ld_wait();
+        float dqv[32];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const uint4 kk = *reinterpret_cast<const uint4*>(k1row + c * 32 + g * 8);
+          const uint4 qq = *reinterpret_cast<const uint4*>(qrow + c * 32 + g * 8);
+          const uint4 gg = *reinterpret_cast<const uint4*>(dorow + c * 32 + g * 8);
+          const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&kk);
+          const __nv_bfloat162* qh = reinterpret_cast<const __nv_bfloat162*>(&qq);
+          const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gg);
+          float dk[8], dvv[8];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 kf = __bfloat1622float2(kh[e]), qf = __bfloat1622float2(qh[e]), gf = __bfloat1622float2(gh[e]);
+            const float a0 = __uint_as_float(da[g * 8 + 2 * e]), a1 = __uint_as_float(da[g * 8 + 2 * e + 1]);
+            const float o0 = __uint_as_float(op[g * 8 + 2 * e]), o1 = __uint_as_float(op[g * 8 + 2 * e + 1]);
+            dqv[g * 8 + 2 * e] = row_valid ? a0 * kf.x : 0.f;
+            dqv[g * 8 + 2 * e + 1] = row_valid ? a1 * kf.y : 0.f;
+            dk[2 * e] = a0 * qf.x;
+            dk[2 * e + 1] = a1 * qf.y;
+            dvv[2 * e] = o0 * gf.x;
+            dvv[2 * e + 1] = o1 * gf.y;
+          }
+          if (row_valid) {
+            atomicAdd(reinterpret_cast<float4*>(dk1row + c * 32 + g * 8), make_float4(dk[0], dk[1], dk[2], dk[3]));
+            atomicAdd(reinterpret_cast<float4*>(dk1row + c * 32 + g * 8 + 4), make_float4(dk[4], dk[5], dk[6], dk[7]));
+            atomicAdd(reinterpret_cast<float4*>(dv1row + c * 32 + g * 8), make_float4(dvv[0], dvv[1], dvv[2], dvv[3]));
+            atomicAdd(reinterpret_cast<float4*>(dv1row + c * 32 + g * 8 + 4), make_float4(dvv[4], dvv[5], dvv[6], dvv[7]));
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 32; ++e) dqv[e] = segsum(dqv[e], p.w1);
+        if (jj == 0 && i < p.N) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 u;
+            u.x = pack_bf16(dqv[8 * g + 0], dqv[8 * g + 1]);
+            u.y = pack_bf16(dqv[8 * g + 2], dqv[8 * g + 3]);
+            u.z = pack_bf16(dqv[8 * g + 4], dqv[8 * g + 5]);
+            u.w = pack_bf16(dqv[8 * g + 6], dqv[8 * g + 7]);
+            *reinterpret_cast<uint4*>(dqrow + c * 32 + g * 8) = u;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_word);
+}
+
+
+// ================================================================================================
+// Part 2: key-owned kernel.  CTA = 128 long keys of one (batch, kv head); thread t of the compute
+// warps owns key k0 + t.  Walks, for every query head of the group, the 64-row groups (64 / w1
+// queries x w1 short keys) whose long window reaches these keys, in the transposed frame:
+//     S^T = K2 A^T    dP^T = V2 G^T    dK2 += dS^T A    dV2 += P^T G
+// The A / G row groups are rebuilt by two builder warps (double-buffered) while the tensor core and
+// the compute warps work on the previous group.  dK2 / dV2 never leave TMEM until the end: plain
+// stores, no atomics, bit-reproducible.
+// ================================================================================================
+constexpr int SK_BK = 128;           // keys per CTA
+constexpr int SK_ROWS = 64;          // rows (query, short key) per inner step
+constexpr int SK_THREADS = 256;      // TMA warp, MMA warp, 4 compute warps, 2 builder warps
+
+struct SimpBwdKParams {
+  SimpBwdParams c;
+  __nv_bfloat16* dk2;          // [B*N, lddk2] bf16
+  __nv_bfloat16* dv2;
+  long long lddk2, lddv2;
+};
+
+struct SimpBwdKSmem {
+  static constexpr int kK = 0;                    // 32 KB K2 [128 keys][128 d]
+  static constexpr int kV = 32768;                // 32 KB V2
+  static constexpr int kA = 65536;                // 2 x 16 KB A row groups [64 rows][128 d]
+  static constexpr int kG = kA + 2 * 16384;       // 2 x 16 KB G row groups
+  static constexpr int kPT = kG + 2 * 16384;      // 16 KB P^T  [128 keys][64 rows]
+  static constexpr int kDST = kPT + 16384;        // 16 KB dS^T
+  static constexpr int kVec = kDST + 16384;       // [2 buffers][lse 64 | delta 64] floats
+  static constexpr int kBar = kVec + 2 * 128 * 4;
+  static constexpr int kTotal = kBar + 16 * 8 + 16 + 1024;
+};
+
+__global__ void __launch_bounds__(SK_THREADS, 1)
+simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_constant__ CUtensorMap tm_v2,
+                        const SimpBwdKParams pk) {
+  using S = SimpBwdKSmem;
+  const SimpBwdParams& p = pk.c;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kBar);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* ag_full = bars + 1;     // [2] builders -> MMA / compute
+  uint64_t* ag_empty = bars + 3;    // [2] accumulation MMAs done with the row group
+  uint64_t* st_full = bars + 5;     // [2] S^T / dP^T ready in TMEM
+  uint64_t* st_free = bars + 7;     // [2] compute warps have read them
+  uint64_t* pds_full = bars + 9;    // P^T / dS^T written to shared memory
+  uint64_t* pds_empty = bars + 10;  // accumulation MMAs have consumed them
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* s_vec = reinterpret_cast<float*>(smem + S::kVec);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int group = p.Hq / p.Hkv;
+  const int k0 = kt * SK_BK;
+  const int row_base = b * p.N;
+  const int sh = (p.w1 == 8) ? 3 : (p.w1 == 16 ? 4 : 5);
+  const int QS = SK_ROWS >> sh;                               // queries per row group
+  const int q_lo = (k0 / QS) * QS;
+  const int q_last = min(p.N - 1, k0 + SK_BK - 1 + p.w2 - 1);
+  const int nsub = (q_last - q_lo) / QS + 1;
+  const int total = group * nsub;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&ag_full[i], 2);
+      mbar_init(&ag_empty[i], 1);
+      mbar_init(&st_full[i], 1);
+      mbar_init(&st_free[i], 4);
+    }
+    mbar_init(pds_full, 4);
+    mbar_init(pds_empty, 1);
+    *abort_word = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_ST = tmem_base;            // 2 x 64 columns
+  const uint32_t tmem_dPT = tmem_base + 128;     // 2 x 64 columns
+  const uint32_t tmem_dK = tmem_base + 256;      // 128 columns
+  const uint32_t tmem_dV = tmem_base + 384;      // 128 columns
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_k2);
+      tma_prefetch_desc(&tm_v2);
+      mbar_expect_tx(kv_full, 2 * 32768);
+      const int kv_col = hk * SB_D;
+      tma_load_3d(smem + S::kK, &tm_k2, kv_full, kv_col, row_base + k0, 0);
+      tma_load_3d(smem + S::kK + 16384, &tm_k2, kv_full, kv_col + 64, row_base + k0, 0);
+      tma_load_3d(smem + S::kV, &tm_v2, kv_full, kv_col, row_base + k0, 0);
+      tma_load_3d(smem + S::kV + 16384, &tm_v2, kv_full, kv_col + 64, row_base + k0, 0);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 64, 0, 0);      // [128 keys] x [64 rows], K = d
+      constexpr uint32_t idesc_acc = umma_idesc_bf16(128, 128, 0, 1);   // [128 keys] x [128 d],   K = rows
+      const uint32_t sK = smem_u32(smem + S::kK);
+      const uint32_t sV = smem_u32(smem + S::kV);
+      const uint32_t sPT = smem_u32(smem + S::kPT);
+      const uint32_t sDST = smem_u32(smem + S::kDST);
+      bool ok = mbar_wait(kv_full, 0, abort_word);
+      auto issue_scores = [&](int it) {
+        const uint32_t sA = smem_u32(smem + S::kA + (it & 1) * 16384);
+        const uint32_t sG = smem_u32(smem + S::kG + (it & 1) * 16384);
+        const uint32_t dS_ = tmem_ST + uint32_t((it & 1) * 64);
+        const uint32_t dP_ = tmem_dPT + uint32_t((it & 1) * 64);
+#pragma unroll
+        for (int k = 0; k < SB_D / 16; ++k) {
+          const uint32_t offa = (k >> 2) * 16384 + (k & 3) * 32;
+          const uint32_t offb = (k >> 2) * 8192 + (k & 3) * 32;
+          umma_bf16_ss(dS_, umma_smem_desc(sK + offa, 16, 1024), umma_smem_desc(sA + offb, 16, 1024), idesc_s,
+                       k != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < SB_D / 16; ++k) {
+          const uint32_t offa = (k >> 2) * 16384 + (k & 3) * 32;
+          const uint32_t offb = (k >> 2) * 8192 + (k & 3) * 32;
+          umma_bf16_ss(dP_, umma_smem_desc(sV + offa, 16, 1024), umma_smem_desc(sG + offb, 16, 1024), idesc_s,
+                       k != 0 ? 1u : 0u);
+        }
+        umma_commit(&st_full[it & 1]);
+      };
+      if (ok) ok = mbar_wait(&ag_full[0], 0, abort_word);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(0);
+      }
+      for (int it = 0; it < total && ok; ++it) {
+        if (it + 1 < total) {
+          const int n = it + 1;
+          ok = mbar_wait(&ag_full[n & 1], (n >> 1) & 1, abort_word);
+          if (ok) ok = mbar_wait(&st_free[n & 1], ((n >> 1) & 1) ^ 1u, abort_word);
+          if (!ok) break;
+          tc_fence_after();
+          issue_scores(n);
+        }
+        ok = mbar_wait(pds_full, it & 1, abort_word);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t sA = smem_u32(smem + S::kA + (it & 1) * 16384);
+        const uint32_t sG = smem_u32(smem + S::kG + (it & 1) * 16384);
+#pragma unroll
+        for (int k = 0; k < SK_ROWS / 16; ++k)
+          umma_bf16_ss(tmem_dK, umma_smem_desc(sDST + k * 32, 16, 1024), umma_smem_desc(sA + k * 2048, 8192, 1024),
+                       idesc_acc, (it | k) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < SK_ROWS / 16; ++k)
+          umma_bf16_ss(tmem_dV, umma_smem_desc(sPT + k * 32, 16, 1024), umma_smem_desc(sG + k * 2048, 8192, 1024),
+                       idesc_acc, (it | k) != 0 ? 1u : 0u);
+        umma_commit(&ag_empty[it & 1]);
+        umma_commit(pds_empty);
+      }
+    }
+  } else if (warp >= 6) {
+    // ---------------------------------------------------------------- builder warps: one row each
+    const int c = (warp - 6) * 32 + lane;                 // row of the group
+    const int qi = c >> sh, jj = c & (p.w1 - 1);
+    bool ok = true;
+    for (int it = 0; it < total && ok; ++it) {
+      const int buf = it & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&ag_empty[buf], ((it >> 1) & 1) ^ 1u, abort_word));
+      if (!ok) break;
+      const int g = it / nsub, s = it - g * nsub;
+      const int h = hk * group + g;
+      const int i = q_lo + s * QS + qi;
+      const int p1 = i - p.w1 + 1 + jj;
+      const bool valid = (i <= q_last) && (p1 >= 0);
+      const long long qrow_idx = row_base + min(i, p.N - 1);
+      const long long krow_idx = row_base + max(p1, 0);
+      // a [64 x 128] group is two 64-column halves of 8 KB
+      uint8_t* tA = smem + S::kA + buf * 16384;
+      uint8_t* tG = smem + S::kG + buf * 16384;
+      const __nv_bfloat16* qrow = p.q + qrow_idx * p.ldq + h * SB_D;
+      const __nv_bfloat16* k1row = p.k1 + krow_idx * p.ldk1 + hk * SB_D;
+      const __nv_bfloat16* v1row = p.v1 + krow_idx * p.ldv1 + hk * SB_D;
+      const __nv_bfloat16* dorow = p.dout + qrow_idx * p.lddo + h * SB_D;
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {
+        const uint4 qa = *reinterpret_cast<const uint4*>(qrow + ch * 8);
+        const uint4 ka = *reinterpret_cast<const uint4*>(k1row + ch * 8);
+        const uint4 ga = *reinterpret_cast<const uint4*>(dorow + ch * 8);
+        const uint4 va = *reinterpret_cast<const uint4*>(v1row + ch * 8);
+        const __nv_bfloat162* qh = reinterpret_cast<const __nv_bfloat162*>(&qa);
+        const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&ka);
+        const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&ga);
+        const __nv_bfloat162* vh = reinterpret_cast<const __nv_bfloat162*>(&va);
+        uint4 oa, og;
+        uint32_t* wa = reinterpret_cast<uint32_t*>(&oa);
+        uint32_t* wg = reinterpret_cast<uint32_t*>(&og);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 x = __bfloat1622float2(qh[e]), y = __bfloat1622float2(kh[e]);
+          const float2 u = __bfloat1622float2(gh[e]), w = __bfloat1622float2(vh[e]);
+          wa[e] = valid ? pack_bf16(x.x * y.x, x.y * y.y) : 0u;
+          wg[e] = valid ? pack_bf16(u.x * w.x, u.y * w.y) : 0u;
+        }
+        const int off = (ch >> 3) * 8192 + c * 128 + (((ch & 7) ^ (c & 7)) * 16);
+        *reinterpret_cast<uint4*>(tA + off) = oa;
+        *reinterpret_cast<uint4*>(tG + off) = og;
+      }
+      const long long stat = ((long long)b * p.Hq + h) * p.N + min(i, p.N - 1);
+      s_vec[buf * 128 + c] = valid ? p.lse2[stat] : INFINITY;
+      s_vec[buf * 128 + 64 + c] = valid ? p.delta[stat] : 0.f;
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ag_full[buf]);
+    }
+  } else {
+    // ---------------------------------------------------------------- compute warps: thread = key
+    const int quarter = warp & 3;
+    const int t = quarter * 32 + lane;
+    const int kp = k0 + t;
+    const uint32_t lane_off = uint32_t(quarter * 32) << 16;
+    uint8_t* sPT = smem + S::kPT;
+    uint8_t* sDST = smem + S::kDST;
+    bool ok = true;
+    for (int it = 0; it < total && ok; ++it) {
+      const int buf = it & 1;
+      const int g = it / nsub, s = it - g * nsub;
+      const int i_start = q_lo + s * QS;
+      ok = __all_sync(0xffffffffu, mbar_wait(&ag_full[buf], (it >> 1) & 1, abort_word));   // stats visible
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&st_full[buf], (it >> 1) & 1, abort_word));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sv[2][32], dv[2][32];
+      tmem_ld_32x32(tmem_ST + uint32_t(buf * 64) + lane_off, sv[0]);
+      tmem_ld_32x32(tmem_ST + uint32_t(buf * 64 + 32) + lane_off, sv[1]);
+      tmem_ld_32x32(tmem_dPT + uint32_t(buf * 64) + lane_off, dv[0]);
+      tmem_ld_32x32(tmem_dPT + uint32_t(buf * 64 + 32) + lane_off, dv[1]);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&st_free[buf]);
+      if (it > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(pds_empty, (it - 1) & 1, abort_word));
+        if (!ok) break;
+      }
+      const float* lse = s_vec + buf * 128;
+      const float* dlt = lse + 64;
+#pragma unroll
+      for (int c2 = 0; c2 < 2; ++c2) {
+        float pr[32], ds[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int col = c2 * 32 + e;
+          const int i = i_start + (col >> sh);
+          const bool v = (kp <= i) && (kp > i - p.w2);
+          const float pv = v ? exp2f(fmaf(__uint_as_float(sv[c2][e]), p.scale_log2, -lse[col])) : 0.f;
+          pr[e] = pv;
+          ds[e] = pv * (__uint_as_float(dv[c2][e]) - dlt[col]) * p.scale;
+        }
+#pragma unroll
+        for (int gq = 0; gq < 4; ++gq) {
+          const int chunk = (c2 * 4 + gq) ^ (t & 7);
+          uint4 u, w;
+          u.x = pack_bf16(pr[8 * gq + 0], pr[8 * gq + 1]);
+          u.y = pack_bf16(pr[8 * gq + 2], pr[8 * gq + 3]);
+          u.z = pack_bf16(pr[8 * gq + 4], pr[8 * gq + 5]);
+          u.w = pack_bf16(pr[8 * gq + 6], pr[8 * gq + 7]);
+          w.x = pack_bf16(ds[8 * gq + 0], ds[8 * gq + 1]);
+          w.y = pack_bf16(ds[8 * gq + 2], ds[8 * gq + 3]);
+          w.z = pack_bf16(ds[8 * gq + 4], ds[8 * gq + 5]);
+          w.w = pack_bf16(ds[8 * gq + 6], ds[8 * gq + 7]);
+          *reinterpret_cast<uint4*>(sPT + t * 128 + chunk * 16) = u;
+          *reinterpret_cast<uint4*>(sDST + t * 128 + chunk * 16) = w;
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+    }
+    // ---------------------------------------------------------------- epilogue: plain stores
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pds_empty, (total - 1) & 1, abort_word));
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* dkrow = pk.dk2 + (long long)(row_base + min(kp, p.N - 1)) * pk.lddk2 + hk * SB_D;
+      __nv_bfloat16* dvrow = pk.dv2 + (long long)(row_base + min(kp, p.N - 1)) * pk.lddv2 + hk * SB_D;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t a[32], v[32];
+        tmem_ld_32x32(tmem_dK + lane_off + c * 32, a);
+        tmem_ld_32x32(tmem_dV + lane_off + c * 32, v);
+        tmem_ld_wait();
+        if (kp < p.N) {
+#pragma unroll
+          for (int gq = 0; gq < 4; ++gq) {
+            uint4 u, w;
+            u.x = pack_bf16(__uint_as_float(a[8 * gq + 0]), __uint_as_float(a[8 * gq + 1]));
+            u.y = pack_bf16(__uint_as_float(a[8 * gq + 2]), __uint_as_float(a[8 * gq + 3]));
+            u.z = pack_bf16(__uint_as_float(a[8 * gq + 4]), __uint_as_float(a[8 * gq + 5]));
+            u.w = pack_bf16(__uint_as_float(a[8 * gq + 6]), __uint_as_float(a[8 * gq + 7]));
+            w.x = pack_bf16(__uint_as_float(v[8 * gq + 0]), __uint_as_float(v[8 * gq + 1]));
+            w.y = pack_bf16(__uint_as_float(v[8 * gq + 2]), __uint_as_float(v[8 * gq + 3]));
+            w.z = pack_bf16(__uint_as_float(v[8 * gq + 4]), __uint_as_float(v[8 * gq + 5]));
+            w.w = pack_bf16(__uint_as_float(v[8 * gq + 6]), __uint_as_float(v[8 * gq + 7]));
+            *reinterpret_cast<uint4*>(dkrow + c * 32 + gq * 8) = u;
+            *reinterpret_cast<uint4*>(dvrow + c * 32 + gq * 8) = w;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_word);
+}
+
+}  // namespace nga
+
+// Backward of nga_simplicial_fwd.  `out`, `lse2` come from the forward pass.  dq / dk2 / dv2 are
+// written as bf16 (strided like their inputs); dk1 / dv1 are accumulated in the fp32 scratch
+// buffers `dk1_acc` / `dv1_acc` ([B*N, Hkv*128], zeroed here) and cast into dk1 / dv1; `delta` is
+// fp32 scratch [B, Hq, N].
+extern "C" int nga_simplicial_bwd(const void* q, const void* k1, const void* k2, const void* v1, const void* v2,
+                                  const void* out, const void* dout, const float* lse2, void* dq, void* dk1,
+                                  void* dk2, void* dv1, void* dv2, float* dk1_acc, float* dv1_acc, float* delta,
+                                  long long ldq, long long ldk1, long long ldk2, long long ldv1, long long ldv2,
+                                  long long ldo, long long lddo, long long lddq, long long lddk1, long long lddk2,
+                                  long long lddv1, long long lddv2, int B, int N, int Hq, int Hkv, int D, int w1,
+                                  int w2, float scale, int* status, void* stream) {
+  using namespace nga;
+  if (D != SB_D || B <= 0 || N <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return -1;
+  if (!(w1 == 8 || w1 == 16 || w1 == 32) || w2 < w1) return -6;
+  if ((ldq | ldk1 | ldk2 | ldv1 | ldv2 | ldo | lddo | lddq | lddk1 | lddk2 | lddv1 | lddv2) & 7) return -5;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const long long rows = (long long)B * N;
+  const long long kvcols = (long long)Hkv * D;
+  CUtensorMap tk64, tv64, tk128, tv128;
+  int rc = make_tmap_3d(&tk64, k2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, kvcols, rows, 1, ldk2 * 2, rows * ldk2 * 2, 64, 64, true);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tv64, v2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, kvcols, rows, 1, ldv2 * 2, rows * ldv2 * 2, 64, 64, true);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tk128, k2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, kvcols, rows, 1, ldk2 * 2, rows * ldk2 * 2, 64, 128, true);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tv128, v2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, kvcols, rows, 1, ldv2 * 2, rows * ldv2 * 2, 64, 128, true);
+  if (rc) return rc;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(simplicial_bwd_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SimpBwdQSmem::kTotal);
+    if (e != cudaSuccess) return -1000 - (int)e;
+    e = cudaFuncSetAttribute(simplicial_bwd_k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SimpBwdKSmem::kTotal);
+    if (e != cudaSuccess) return -1000 - (int)e;
+    attr_done = true;
+  }
+  {
+    const long long warps = rows * Hq;
+    simp_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), delta, ldo, lddo, B,
+        N, Hq);
+    count_launch();
+  }
+  cudaMemsetAsync(dk1_acc, 0, sizeof(float) * rows * kvcols, st);
+  cudaMemsetAsync(dv1_acc, 0, sizeof(float) * rows * kvcols, st);
+  SimpBwdParams p;
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q);
+  p.k1 = reinterpret_cast<const __nv_bfloat16*>(k1);
+  p.v1 = reinterpret_cast<const __nv_bfloat16*>(v1);
+  p.dout = reinterpret_cast<const __nv_bfloat16*>(dout);
+  p.lse2 = lse2;
+  p.delta = delta;
+  p.dq = reinterpret_cast<__nv_bfloat16*>(dq);
+  p.dk1 = dk1_acc;
+  p.dv1 = dv1_acc;
+  p.dk2 = nullptr;
+  p.dv2 = nullptr;
+  p.ldq = ldq; p.ldk1 = ldk1; p.ldv1 = ldv1; p.lddo = lddo; p.lddq = lddq;
+  p.B = B; p.N = N; p.Hq = Hq; p.Hkv = Hkv; p.w1 = w1; p.w2 = w2;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  {
+    const int BQ = 128 / w1;
+    dim3 grid((N + BQ - 1) / BQ, Hq, B);
+    simplicial_bwd_q_kernel<<<grid, SB_THREADS, SimpBwdQSmem::kTotal, st>>>(tk64, tv64, p);
+    count_launch();
+  }
+  {
+    SimpBwdKParams pk;
+    pk.c = p;
+    pk.dk2 = reinterpret_cast<__nv_bfloat16*>(dk2);
+    pk.dv2 = reinterpret_cast<__nv_bfloat16*>(dv2);
+    pk.lddk2 = lddk2; pk.lddv2 = lddv2;
+    dim3 grid((N + SK_BK - 1) / SK_BK, Hkv, B);
+    simplicial_bwd_k_kernel<<<grid, SK_THREADS, SimpBwdKSmem::kTotal, st>>>(tk128, tv128, pk);
+    count_launch();
+  }
+  {
+    const long long n4 = rows * kvcols / 4;
+    simp_cast_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dk1_acc, reinterpret_cast<__nv_bfloat16*>(dk1), rows,
+                                                                  (int)kvcols, lddk1);
+    count_launch();
+    simp_cast_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dv1_acc, reinterpret_cast<__nv_bfloat16*>(dv1), rows,
+                                                                  (int)kvcols, lddv1);
+    count_launch();
+  }
+  NGA_CHECK_LAUNCH();
+  return 0;
+}

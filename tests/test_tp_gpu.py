@@ -1,0 +1,71 @@
+"""Fused tensor-parallel GEMMs (all-gather -> GEMM, GEMM -> reduce-scatter) over peer memory against
+the decomposed NCCL + fp32 matmul oracle.  Child processes, one per GPU; needs two GPUs."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    from archlab_b200.ops import native
+    from archlab_b200.parallel import tp as T
+
+    dev = torch.device("cuda", rank)
+    rows, K, N = 512, 320, 384
+    grp = T.TPGroup(rows, max_k=512, max_n=512, device=dev, copy_clusters=2)
+    res = {}
+    for it in range(3):                               # several epochs: flags, double buffering, slot reuse
+        g = torch.Generator(device=dev).manual_seed(100 * it + rank)
+        x = (torch.randn(rows, K, device=dev, generator=g) * 0.5).bfloat16()
+        gw = torch.Generator(device=dev).manual_seed(7 + it)
+        w = (torch.randn(N, K, device=dev, generator=gw) * 0.1).bfloat16()
+        y = T.ag_gemm(grp, x, w)
+        ref = T.ag_gemm_reference(x, w)
+        res[f"ag{it}"] = ((y.float() - ref.float()).norm() / ref.float().norm()).item()
+        wt = w.t().contiguous()                       # [K, N] MN-major operand
+        y2 = T.ag_gemm(grp, x, wt, w_mn=True)
+        res[f"ag_mn{it}"] = ((y2.float() - ref.float()).norm() / ref.float().norm()).item()
+        gathered = grp.gathered_view(K)
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x)
+        res[f"gathered{it}"] = float((gathered.float() - torch.cat(parts).float()).abs().max())   # own rows included
+        a = (torch.randn(world * rows, K, device=dev, generator=g) * 0.5).bfloat16()
+        resid = (torch.randn(rows, N, device=dev, generator=g)).bfloat16()
+        z = T.gemm_rs(grp, a, w, resid=resid)
+        zref = T.gemm_rs_reference(a, w, resid=resid)
+        res[f"rs{it}"] = ((z.float() - zref.float()).norm() / zref.float().norm()).item()
+    torch.cuda.synchronize()
+    native.check_status()
+    torch.save(res, os.path.join(out_dir, f"tp_rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_tp_gemms_match_decomposed(tmp_path):
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_worker, args=(r, 2, 29631, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=600)
+        if p.is_alive():
+            p.terminate()
+            pytest.fail("worker timed out")
+        assert p.exitcode == 0
+    for r in range(2):
+        res = torch.load(tmp_path / f"tp_rank{r}.pt")
+        for k, v in res.items():
+            assert v < (1e-6 if k.startswith("gathered") else 1e-2), (r, k, v)
