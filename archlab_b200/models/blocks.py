@@ -88,7 +88,8 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, *, style: 
 
 
 def so3_chunk_rope(x: torch.Tensor, positions: torch.Tensor, base: float = 10000.0) -> torch.Tensor:
-    """Rotates consecutive channel triples about the (1,1,1)/sqrt(3) axis by a per-triple angle
+    """``positions`` must broadcast against ``x.shape[:-1]`` (e.g. ``[1, T, 1]`` for ``[B, T, H, D]``).
+    Rotates consecutive channel triples about the (1,1,1)/sqrt(3) axis by a per-triple angle
     ``pos * base^(-i/n)``.  Every rotation has determinant 1, so a 3x3 determinant of three vectors
     rotated at the SAME position is unchanged while vectors at different positions pick up a relative
     rotation (the position signal of the determinant simplicial switch;
@@ -97,9 +98,7 @@ def so3_chunk_rope(x: torch.Tensor, positions: torch.Tensor, base: float = 10000
     n = D // 3
     v = x[..., : 3 * n].float().unflatten(-1, (n, 3))
     inv = base ** (-torch.arange(n, device=x.device, dtype=torch.float32) / max(n, 1))
-    ang = positions.float()[..., None] * inv                                  # [..., T, n]
-    while ang.dim() < v.dim() - 1:
-        ang = ang.unsqueeze(-2)                                                 # broadcast over heads
+    ang = positions.float()[..., None] * inv              # positions broadcast against x.shape[:-1]
     c, s = ang.cos()[..., None], ang.sin()[..., None]
     mean = v.mean(-1, keepdim=True)                                             # projection on the axis
     cross = (torch.roll(v, -1, -1) - torch.roll(v, 1, -1)) / math.sqrt(3.0)     # axis x v
