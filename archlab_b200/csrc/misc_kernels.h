@@ -1,0 +1,22 @@
+// C ABI of the single-pass model-zoo kernels (see misc_kernels.cu).  bf16 tensors unless noted.
+#pragma once
+#ifdef __cplusplus
+extern "C" {
+#endif
+int nga_rmsnorm(const void* x, const float* weight, void* y, long long rows, int groups, int width, float eps,
+                int zero_centered, void* stream);
+int nga_rope(void* x, const float* cos_t, const float* sin_t, long long rows, int T, int H, int D, int rot, int interleaved,
+             void* stream);
+int nga_router_topk(const void* x, const void* w, const float* bias, float* out_w, int* out_idx, float* out_scores, int T,
+                    int C, int E, int k, int score_fn, float route_scale, int renorm, void* stream);
+int nga_causal_conv1d(const void* x, const float* w, const float* bias, void* y, int B, int T, int Cc, int K, int dil,
+                      int silu, void* stream);
+int nga_ngram_hash(const long long* tok, const int* seg_start, const long long* mult, const long long* sizes,
+                   const long long* offsets, long long* ids, int B, int T, int n, int heads_per_order, long long eos,
+                   void* stream);
+int nga_fp8_block_quant(const void* x, void* q, float* scales, long long n, int block, int pow2, void* stream);
+int nga_nvfp4_quant(const void* x, void* vals, void* bscale, float tensor_scale, long long n, void* stream);
+int nga_stochastic_bf16(const float* x, void* y, long long n, unsigned long long seed, void* stream);
+#ifdef __cplusplus
+}
+#endif

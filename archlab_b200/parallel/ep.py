@@ -1,0 +1,196 @@
+"""Expert parallelism whose all-to-all is fused with the token permutation in kernels that read and
+write peer memory directly (``csrc/moe.cu``).
+
+Forward of one MoE layer on every rank:
+  route -> counts exchanged (tiny all-gather) -> prefix sums give every (token, slot) its row in the
+  owner's receive buffer -> ``push_rows`` writes the token rows straight into the owners' buffers
+  (dispatch = all-to-all + permute, one kernel) -> device barrier -> per-expert tcgen05 GEMMs + clamped
+  SwiGLU on contiguous expert segments -> device barrier -> ``pull_combine`` reads every token's k
+  expert rows back from the owners and sums them, weighted, in ascending expert id (combine =
+  all-to-all + un-permute + ordered fp32 sum, one kernel).
+Backward uses the same two kernels as each other's adjoint.  The NCCL all-to-all form
+(``models.moe.ExpertParallelMoE``; src/archlab/automodel/deepseek_v41_parallel.py:16-111) is the
+baseline and the oracle.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..models.moe import GroupedExperts, SwiGLU, route
+from ..ops import native
+from ..ops.linear import linear
+
+_vp, _i, _ll, _f = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+native.register_signature("nga_moe_push_rows", [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp])
+native.register_signature("nga_moe_pull_combine", [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp])
+native.register_signature("nga_swiglu_clamped", [_vp, _vp, _vp, _ll, _i, _f, _vp])
+
+
+class EPBuffers:
+    """Symmetric buffers of one expert-parallel group: token rows in, expert rows out, and the two
+    gradient buffers of the backward pass; ``capacity`` rows of ``dim`` bf16 each."""
+
+    def __init__(self, capacity: int, dim: int, device, group=None):
+        from .symm import PeerBarrier, symm_empty
+
+        self.group = group or dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.capacity, self.dim = capacity, dim
+        mk = lambda: symm_empty((capacity * dim,), torch.bfloat16, device, self.group)
+        self.recv_x, self.y, self.g_y, self.g_x = mk(), mk(), mk(), mk()
+        self.barrier = PeerBarrier(device, self.group)
+
+    def view(self, sym, n):
+        return sym.tensor[: n * self.dim].view(n, self.dim)
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def push_rows(rows, dst_rank, dst_row, sym, buf: EPBuffers, scale=None, src_row=None):
+    n = dst_rank.numel()
+    rc = native.lib().nga_moe_push_rows(_p(rows), _p(src_row), _p(dst_rank), _p(dst_row), _p(scale), sym.ptr_array(), buf.world,
+                                        n, buf.dim, native.stream_ptr())
+    native.check(rc, "nga_moe_push_rows")
+
+
+def pull_combine(sym, buf: EPBuffers, rank, row, weight, T, k, gout=None, want_dweight=False, fp32_out=False):
+    out = None if fp32_out else torch.empty(T, buf.dim, dtype=torch.bfloat16, device=rank.device)
+    out32 = torch.empty(T, buf.dim, dtype=torch.float32, device=rank.device) if fp32_out else None
+    dw = torch.empty(T, k, dtype=torch.float32, device=rank.device) if want_dweight else None
+    rc = native.lib().nga_moe_pull_combine(sym.ptr_array(), buf.world, _p(rank), _p(row), _p(weight), _p(gout), _p(out), _p(out32),
+                                           _p(dw), T, k, buf.dim, native.stream_ptr())
+    native.check(rc, "nga_moe_pull_combine")
+    return (out32 if fp32_out else out), dw
+
+
+class _Dispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, src_row, dst_rank, dst_row, n_recv, k, buf):
+        ctx.meta = (dst_rank, dst_row, x.size(0), k, buf, n_recv)
+        buf.barrier()                                           # receive buffers are free everywhere
+        push_rows(x, dst_rank, dst_row, buf.recv_x, buf, src_row=src_row)
+        buf.barrier()                                           # every row has landed
+        return buf.view(buf.recv_x, n_recv).clone()
+
+    @staticmethod
+    def backward(ctx, g_recv):
+        dst_rank, dst_row, T, k, buf, n_recv = ctx.meta
+        buf.barrier()
+        buf.view(buf.g_x, n_recv).copy_(g_recv)
+        buf.barrier()
+        dx, _ = pull_combine(buf.g_x, buf, dst_rank, dst_row, None, T, k)      # slots of a token are adjacent
+        return dx, None, None, None, None, None, None
+
+
+class _Combine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y_local, weight, rank_sorted, row_sorted, T, k, buf):
+        n = y_local.size(0)
+        buf.barrier()
+        buf.view(buf.y, n).copy_(y_local)
+        buf.barrier()
+        out, _ = pull_combine(buf.y, buf, rank_sorted, row_sorted, weight, T, k)
+        ctx.save_for_backward(y_local, weight, rank_sorted, row_sorted)
+        ctx.meta = (T, k, buf)
+        return out
+
+    @staticmethod
+    def backward(ctx, gout):
+        y_local, weight, rank_sorted, row_sorted = ctx.saved_tensors
+        T, k, buf = ctx.meta
+        n = y_local.size(0)
+        gout = gout.contiguous()
+        buf.barrier()
+        buf.view(buf.y, n).copy_(y_local)                        # expert rows again, for d(weight)
+        buf.barrier()
+        _, dw = pull_combine(buf.y, buf, rank_sorted, row_sorted, None, T, k, gout=gout, want_dweight=True, fp32_out=True)
+        src_row = torch.arange(T, device=gout.device, dtype=torch.int32).repeat_interleave(k)
+        push_rows(gout, rank_sorted.flatten(), row_sorted.flatten(), buf.g_y, buf, scale=weight.flatten().contiguous(),
+                  src_row=src_row)
+        buf.barrier()
+        gy = buf.view(buf.g_y, n).clone()
+        return gy, dw, None, None, None, None, None
+
+
+class FusedExpertParallelMoE(nn.Module):
+    """Same parameters and semantics as ``models.moe.ExpertParallelMoE``; bf16 CUDA only."""
+
+    def __init__(self, dim, inter, n_experts, top_k, buffers: EPBuffers, *, score="sqrt_softplus", route_scale=1.0,
+                 swiglu_limit=None, n_shared=1):
+        super().__init__()
+        self.buf = buffers
+        self.size, self.rank = buffers.world, buffers.rank
+        if n_experts % self.size:
+            raise ValueError("expert count must divide EP size")
+        self.dim, self.n_experts, self.top_k, self.score, self.route_scale = dim, n_experts, top_k, score, route_scale
+        self.local_experts = n_experts // self.size
+        self.first = self.rank * self.local_experts
+        self.limit = swiglu_limit
+        self.router = nn.Parameter(torch.empty(n_experts, dim))
+        self.register_buffer("e_score_correction_bias", torch.zeros(n_experts, dtype=torch.float32))
+        self.experts = GroupedExperts(self.local_experts, dim, inter, swiglu_limit=swiglu_limit)
+        self.shared = SwiGLU(dim, inter * n_shared, swiglu_limit) if n_shared else None
+        self._cumulative_expert_load = None
+
+    def plan(self, idx: torch.Tensor):
+        """Routing indices [T, k] -> where every slot lives in its owner's buffer, and this rank's segments."""
+        T, k = idx.shape
+        E, El, W = self.n_experts, self.local_experts, self.size
+        flat = idx.flatten()
+        counts = torch.bincount(flat, minlength=E)
+        allc = torch.empty(W, E, dtype=counts.dtype, device=idx.device)
+        dist.all_gather_into_tensor(allc, counts, group=self.buf.group)
+        per_e = allc.sum(0)                                                     # rows of expert e on its owner
+        seg_start = per_e.view(W, El).cumsum(1) - per_e.view(W, El)            # start of e's segment on its owner
+        before_me = allc[: self.rank].sum(0)                                    # rows of e from lower source ranks
+        base = seg_start.flatten() + before_me
+        sorted_e, order = flat.sort(stable=True)
+        group_start = (counts.cumsum(0) - counts)[sorted_e]
+        within = torch.arange(flat.numel(), device=idx.device) - group_start
+        dst_row = torch.empty_like(flat)
+        dst_row[order] = base[sorted_e] + within
+        dst_rank = flat // El
+        mine = per_e[self.first:self.first + El]
+        return dst_rank.int(), dst_row.int(), mine, counts
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        x2 = x.reshape(-1, self.dim).contiguous()
+        T, k = x2.size(0), self.top_k
+        w, idx, _ = route(x2, self.router, self.e_score_correction_bias, top_k=k, score=self.score, route_scale=self.route_scale)
+        dst_rank, dst_row, mine, counts = self.plan(idx)
+        load = counts.float()
+        self._cumulative_expert_load = load if self._cumulative_expert_load is None else self._cumulative_expert_load + load
+        seg = mine.tolist()                                                       # host needs the GEMM extents
+        n_recv = sum(seg)
+        if n_recv > self.buf.capacity:
+            raise RuntimeError(f"expert receive buffer too small: {n_recv} rows > capacity {self.buf.capacity}")
+        src_row = torch.arange(T, device=x.device, dtype=torch.int32).repeat_interleave(k)
+        recv = _Dispatch.apply(x2, src_row, dst_rank, dst_row, n_recv, k, self.buf)
+        outs, s0 = [], 0
+        for le, n in enumerate(seg):
+            if n == 0:
+                continue
+            h = linear(recv[s0:s0 + n], self.experts.gate_up[le].to(recv.dtype))
+            g, u = h[:, : self.experts.inter].float(), h[:, self.experts.inter:].float()
+            if self.limit is not None:
+                g, u = g.clamp(max=self.limit), u.clamp(-self.limit, self.limit)
+            a = (F.silu(g) * u).to(recv.dtype)
+            outs.append(linear(a, self.experts.down[le].to(recv.dtype)))
+            s0 += n
+        y_local = torch.cat(outs, 0) if outs else recv.new_zeros(0, self.dim)
+        # ascending expert id per token: deterministic summation order
+        eo = idx.argsort(dim=-1)
+        slots = (torch.arange(T, device=x.device) * k).unsqueeze(1) + eo
+        rank_s, row_s, w_s = dst_rank[slots].contiguous(), dst_row[slots].contiguous(), w.gather(1, eo).float().contiguous()
+        out = _Combine.apply(y_local, w_s, rank_s, row_s, T, k, self.buf)
+        if self.shared is not None:
+            out = out + self.shared(x2).to(out.dtype)
+        return out.reshape(shape)

@@ -1,0 +1,77 @@
+"""Fused expert-parallel MoE (peer-memory dispatch / combine) against the NCCL all-to-all form, 2 GPUs."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    from archlab_b200.models import moe
+    from archlab_b200.ops import native
+    from archlab_b200.parallel import ep
+
+    dev = torch.device("cuda", rank)
+    dim, inter, E, k, T = 256, 128, 8, 2, 96
+    torch.manual_seed(0)
+    ref = moe.ExpertParallelMoE(dim, inter, E, k, dist.group.WORLD, swiglu_limit=7.0, n_shared=1).to(dev)
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.normal_(std=0.05)
+    ref = ref.bfloat16()
+    ref.e_score_correction_bias = ref.e_score_correction_bias.float()
+    buf = ep.EPBuffers(capacity=T * k * world, dim=dim, device=dev)
+    fused = ep.FusedExpertParallelMoE(dim, inter, E, k, buf, swiglu_limit=7.0, n_shared=1).to(dev).bfloat16()
+    fused.e_score_correction_bias = fused.e_score_correction_bias.float()
+    fused.load_state_dict(ref.state_dict())
+    res = {}
+    for it in range(2):
+        g = torch.Generator(device=dev).manual_seed(10 * it + rank)
+        x = torch.randn(T, dim, device=dev, generator=g).bfloat16()
+        xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+        ya, yb = ref(xa), fused(xb)
+        res[f"out{it}"] = ((ya.float() - yb.float()).norm() / ya.float().norm()).item()
+        go = torch.randn(T, dim, device=dev, generator=g).bfloat16()
+        for m in (ref, fused):
+            m.zero_grad()
+        ya.backward(go)
+        yb.backward(go)
+        rel = lambda a, b: ((a.float() - b.float()).norm() / a.float().norm().clamp_min(1e-9)).item()
+        res[f"dx{it}"] = rel(xa.grad, xb.grad)
+        res[f"drouter{it}"] = rel(ref.router.grad, fused.router.grad)
+        res[f"ddown{it}"] = rel(ref.experts.down.grad, fused.experts.down.grad)
+        res[f"dgate_up{it}"] = rel(ref.experts.gate_up.grad, fused.experts.gate_up.grad)
+    torch.cuda.synchronize()
+    native.check_status()
+    torch.save(res, os.path.join(out_dir, f"ep_rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_ep_moe_matches_all_to_all(tmp_path):
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_worker, args=(r, 2, 29641, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=600)
+        if p.is_alive():
+            p.terminate()
+            pytest.fail("worker timed out")
+        assert p.exitcode == 0
+    for r in range(2):
+        res = torch.load(tmp_path / f"ep_rank{r}.pt")
+        for key, v in res.items():
+            assert v < 3e-2, (r, key, v)
