@@ -1,0 +1,84 @@
+"""Evaluation in the training loop: bits-per-byte on held-out tokens (tokenizer independent), a
+multiple-choice scorer (the CORE-style "lowest mean loss over the continuation" rule) and batched
+sampling (src/archlab/speedrun/loss_eval.py:20-64, core_eval.py:160-270, engine.py)."""
+from __future__ import annotations
+
+import math
+from collections.abc import Iterable
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+
+@torch.no_grad()
+def evaluate_bpb(model, batches: Iterable[tuple[torch.Tensor, torch.Tensor]], token_bytes: torch.Tensor, *, group=None) -> float:
+    """``token_bytes[v]`` = UTF-8 length of token v (0 for special tokens, which are excluded from both sums).
+    bpb = sum(nats) / (ln 2 * sum(bytes)), reduced over all ranks."""
+    total_nats = torch.zeros((), dtype=torch.float64, device=token_bytes.device)
+    total_bytes = torch.zeros((), dtype=torch.int64, device=token_bytes.device)
+    was_training = model.training
+    model.eval()
+    for x, y in batches:
+        loss = model(x, y, loss_reduction="none") if _takes_reduction(model) else _per_token(model, x, y)
+        valid = y >= 0
+        nbytes = torch.where(valid, token_bytes[y.clamp_min(0)], torch.zeros_like(y))
+        counted = nbytes > 0
+        total_nats += (loss.double() * counted).sum()
+        total_bytes += nbytes.sum()
+    if dist.is_available() and dist.is_initialized():
+        dist.all_reduce(total_nats, group=group)
+        dist.all_reduce(total_bytes, group=group)
+    model.train(was_training)
+    return float("inf") if int(total_bytes) == 0 else float(total_nats) / (math.log(2) * int(total_bytes))
+
+
+def _takes_reduction(model) -> bool:
+    import inspect
+
+    return "loss_reduction" in inspect.signature(model.forward).parameters
+
+
+def _per_token(model, x, y):
+    logits = model(x).float()
+    return F.cross_entropy(logits.flatten(0, 1), y.flatten(), ignore_index=-1, reduction="none").view_as(y)
+
+
+@torch.no_grad()
+def score_multiple_choice(model, prefix: list[int], continuations: list[list[int]]) -> int:
+    """Index of the continuation with the lowest mean token loss given the shared prefix."""
+    dev = next(model.parameters()).device
+    losses = []
+    for cont in continuations:
+        ids = torch.tensor([prefix + cont], device=dev)
+        lp = _per_token(model, ids[:, :-1], ids[:, 1:])[0, len(prefix) - 1:]
+        losses.append(float(lp.mean()))
+    return min(range(len(losses)), key=losses.__getitem__)
+
+
+@torch.no_grad()
+def generate_batch(model, prompts: list[list[int]], max_tokens: int, *, temperature: float = 0.0, top_k: int | None = None,
+                   seed: int = 0, eos: int | None = None) -> list[list[int]]:
+    """Greedy / sampled continuation of several prompts at once (right-aligned, left-padded with the first
+    token; the padding never influences a causal model's later positions beyond the prompt itself)."""
+    dev = next(model.parameters()).device
+    width = max(len(p) for p in prompts)
+    ids = torch.tensor([[p[0]] * (width - len(p)) + p for p in prompts], device=dev)
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    done = torch.zeros(len(prompts), dtype=torch.bool, device=dev)
+    outs: list[list[int]] = [[] for _ in prompts]
+    for _ in range(max_tokens):
+        logits = model(ids)[:, -1, :].float()
+        if top_k:
+            kth = logits.topk(min(top_k, logits.size(-1))).values[:, -1:]
+            logits = logits.masked_fill(logits < kth, float("-inf"))
+        nxt = torch.multinomial((logits / temperature).softmax(-1), 1, generator=gen) if temperature > 0 else logits.argmax(-1, keepdim=True)
+        for i, t in enumerate(nxt[:, 0].tolist()):
+            if not done[i]:
+                outs[i].append(t)
+        if eos is not None:
+            done |= nxt[:, 0] == eos
+            if bool(done.all()):
+                break
+        ids = torch.cat([ids, nxt], 1)
+    return outs
