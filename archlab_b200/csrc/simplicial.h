@@ -11,10 +11,12 @@ int nga_simplicial_fwd(const void* q, const void* k1, const void* k2, const void
                        int* status, void* stream);
 // Backward.  `out` / `lse2` are the forward results, `dout` the incoming gradient [B*N, Hq*128].
 // dq, dk1, dk2, dv1, dv2 receive bf16 gradients with the given row strides.  Scratch (fp32):
-// dk1_acc, dv1_acc [B*N, Hkv*128] (zeroed inside) and delta [B, Hq, N].
+// dk1_acc, dv1_acc [B*N, Hkv*128] (zeroed inside), dk2_acc, dv2_acc (same shape; needed only when
+// Hq > Hkv, may be null otherwise) and delta [B, Hq, N].
 int nga_simplicial_bwd(const void* q, const void* k1, const void* k2, const void* v1, const void* v2,
                        const void* out, const void* dout, const float* lse2, void* dq, void* dk1, void* dk2,
-                       void* dv1, void* dv2, float* dk1_acc, float* dv1_acc, float* delta, long long ldq,
+                       void* dv1, void* dv2, float* dk1_acc, float* dv1_acc, float* dk2_acc, float* dv2_acc, float* delta,
+                       long long ldq,
                        long long ldk1, long long ldk2, long long ldv1, long long ldv2, long long ldo, long long lddo,
                        long long lddq, long long lddk1, long long lddk2, long long lddv1, long long lddv2, int B,
                        int N, int Hq, int Hkv, int D, int w1, int w2, float scale, int* status, void* stream);

@@ -83,24 +83,43 @@ __global__ void simp_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* _
 
 // Row r of a [128 x 128] K-major operand tile (two 64-column halves of 16 KB, 128-byte swizzle):
 // element-wise product of two bf16 rows, zero when the row is masked.
+// bf16 x bf16 rounded to bf16 equals the fp32 product rounded once, so the packed multiply is exact enough
+// and five times cheaper than unpack / multiply / repack.
+__device__ __forceinline__ uint4 mul_bf16x8(const uint4& a, const uint4& b) {
+  uint4 o;
+  const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* y = reinterpret_cast<const __nv_bfloat162*>(&b);
+  __nv_bfloat162* z = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) z[e] = __hmul2(x[e], y[e]);
+  return o;
+}
+
+// All sixteen chunks of both rows are loaded before any product is stored: a store through a generic
+// pointer between two global loads keeps the compiler from hoisting the loads, which serialises every
+// chunk on the L2 latency.
 __device__ __forceinline__ void build_product_row(uint8_t* tile, int r, const __nv_bfloat16* x, const __nv_bfloat16* y,
                                                   bool valid) {
 #pragma unroll
-  for (int c = 0; c < 16; ++c) {
-    const uint4 xa = *reinterpret_cast<const uint4*>(x + c * 8);
-    const uint4 ya = *reinterpret_cast<const uint4*>(y + c * 8);
-    const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xa);
-    const __nv_bfloat162* yh = reinterpret_cast<const __nv_bfloat162*>(&ya);
-    uint4 o;
-    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+  for (int hb = 0; hb < 2; ++hb) {
+    uint4 xa[8], ya[8];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 a = __bfloat1622float2(xh[e]), b = __bfloat1622float2(yh[e]);
-      ow[e] = valid ? pack_bf16(a.x * b.x, a.y * b.y) : 0u;
+    for (int c = 0; c < 8; ++c) {
+      xa[c] = valid ? *reinterpret_cast<const uint4*>(x + (hb * 8 + c) * 8) : make_uint4(0u, 0u, 0u, 0u);
+      ya[c] = valid ? *reinterpret_cast<const uint4*>(y + (hb * 8 + c) * 8) : make_uint4(0u, 0u, 0u, 0u);
     }
-    const int chunk = (c & 7) ^ (r & 7);
-    *reinterpret_cast<uint4*>(tile + (c >> 3) * 16384 + r * 128 + chunk * 16) = o;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int chunk = c ^ (r & 7);
+      *reinterpret_cast<uint4*>(tile + hb * 16384 + r * 128 + chunk * 16) = mul_bf16x8(xa[c], ya[c]);
+    }
   }
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {   // one MUFU op; exp2(-inf) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ float segsum(float v, int w1) {
@@ -303,29 +322,32 @@ simplicial_bwd_q_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
         ok = __all_sync(0xffffffffu, mbar_wait(p_empty, (j - 1) & 1, abort_word));
         if (!ok) break;
       }
+      // rows whose whole 64-key tile is visible skip the per-element window test
+      const bool full = row_valid && lo <= 0 && hi >= SB_BK - 1;
+      const float lse_row = row_valid ? lse : INFINITY;          // exp2(-inf) = 0 for padded rows
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        float pr[32], ds[32];
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int col = c * 32 + e;
-          const bool v = row_valid && col >= lo && col <= hi;
-          const float pv = v ? exp2f(fmaf(__uint_as_float(sv[c][e]), p.scale_log2, -lse)) : 0.f;
-          pr[e] = pv;
-          ds[e] = pv * (__uint_as_float(dv[c][e]) - dlt) * p.scale;
-        }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
+          float pr[8], ds[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int col = c * 32 + g * 8 + e;
+            const float l = (full || (col >= lo && col <= hi)) ? lse_row : INFINITY;
+            const float pv = ex2_approx(fmaf(__uint_as_float(sv[c][g * 8 + e]), p.scale_log2, -l));
+            pr[e] = pv;
+            ds[e] = (pv * p.scale) * (__uint_as_float(dv[c][g * 8 + e]) - dlt);
+          }
           const int chunk = (c * 4 + g) ^ (r & 7);
           uint4 u, w;
-          u.x = pack_bf16(pr[8 * g + 0], pr[8 * g + 1]);
-          u.y = pack_bf16(pr[8 * g + 2], pr[8 * g + 3]);
-          u.z = pack_bf16(pr[8 * g + 4], pr[8 * g + 5]);
-          u.w = pack_bf16(pr[8 * g + 6], pr[8 * g + 7]);
-          w.x = pack_bf16(ds[8 * g + 0], ds[8 * g + 1]);
-          w.y = pack_bf16(ds[8 * g + 2], ds[8 * g + 3]);
-          w.z = pack_bf16(ds[8 * g + 4], ds[8 * g + 5]);
-          w.w = pack_bf16(ds[8 * g + 6], ds[8 * g + 7]);
+          u.x = pack_bf16(pr[0], pr[1]);
+          u.y = pack_bf16(pr[2], pr[3]);
+          u.z = pack_bf16(pr[4], pr[5]);
+          u.w = pack_bf16(pr[6], pr[7]);
+          w.x = pack_bf16(ds[0], ds[1]);
+          w.y = pack_bf16(ds[2], ds[3]);
+          w.z = pack_bf16(ds[4], ds[5]);
+          w.w = pack_bf16(ds[6], ds[7]);
           *reinterpret_cast<uint4*>(sP + r * 128 + chunk * 16) = u;
           *reinterpret_cast<uint4*>(sDS + r * 128 + chunk * 16) = w;
         }
@@ -343,6 +365,13 @@ simplicial_bwd_q_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
       float* dv1row = p.dv1 + krow_idx * ((long long)p.Hkv * SB_D) + hk * SB_D;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
+        uint4 kk[4], qq[4], gg[4];                         // loads first: the atomics below would pin them in place
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          kk[g] = *reinterpret_cast<const uint4*>(k1row + c * 32 + g * 8);
+          qq[g] = *reinterpret_cast<const uint4*>(qrow + c * 32 + g * 8);
+          gg[g] = *reinterpret_cast<const uint4*>(dorow + c * 32 + g * 8);
+        }
         uint32_t da[32], op[32];
         tmem_ld_32x32(tmem_dA + lane_off + c * 32, da);
         tmem_ld_32x32(tmem_Op + lane_off + c * 32, op);
@@ -350,12 +379,9 @@ simplicial_bwd_q_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
         float dqv[32];
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const uint4 kk = *reinterpret_cast<const uint4*>(k1row + c * 32 + g * 8);
-          const uint4 qq = *reinterpret_cast<const uint4*>(qrow + c * 32 + g * 8);
-          const uint4 gg = *reinterpret_cast<const uint4*>(dorow + c * 32 + g * 8);
-          const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&kk);
-          const __nv_bfloat162* qh = reinterpret_cast<const __nv_bfloat162*>(&qq);
-          const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gg);
+          const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&kk[g]);
+          const __nv_bfloat162* qh = reinterpret_cast<const __nv_bfloat162*>(&qq[g]);
+          const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gg[g]);
           float dk[8], dvv[8];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -415,14 +441,20 @@ simplicial_bwd_q_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
 // ================================================================================================
 constexpr int SK_BK = 128;           // keys per CTA
 constexpr int SK_ROWS = 64;          // rows (query, short key) per inner step
-constexpr int SK_THREADS = 256;      // TMA warp, MMA warp, 4 compute warps, 2 builder warps
+constexpr int SK_THREADS = 320;      // TMA warp, MMA warp, 4 compute warps, 4 builder warps
 
 struct SimpBwdKParams {
   SimpBwdParams c;
-  __nv_bfloat16* dk2;          // [B*N, lddk2] bf16
+  long long* prof;             // optional phase cycle counters
+  __nv_bfloat16* dk2;          // [B*N, lddk2] bf16 (written directly when every KV head has one query head)
   __nv_bfloat16* dv2;
   long long lddk2, lddv2;
+  float* dk2_acc;              // [B*N, Hkv*D] fp32, zeroed by the launcher: target of the per-query-head CTAs'
+  float* dv2_acc;              //   vector atomics when a KV head serves several query heads
 };
+
+// Optional phase cycle counters (16 slots), written by CTA (0,0,0) of the key-owned kernel.
+static long long* g_simp_prof = nullptr;
 
 struct SimpBwdKSmem {
   static constexpr int kK = 0;                    // 32 KB K2 [128 keys][128 d]
@@ -436,6 +468,7 @@ struct SimpBwdKSmem {
   static constexpr int kTotal = kBar + 16 * 8 + 16 + 1024;
 };
 
+template <int W1>
 __global__ void __launch_bounds__(SK_THREADS, 1)
 simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_constant__ CUtensorMap tm_v2,
                         const SimpBwdKParams pk) {
@@ -456,21 +489,22 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
   float* s_vec = reinterpret_cast<float*>(smem + S::kVec);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int kt = blockIdx.x, hq = blockIdx.y, b = blockIdx.z;     // one CTA per (key tile, QUERY head)
   const int group = p.Hq / p.Hkv;
+  const int hk = hq / group;
   const int k0 = kt * SK_BK;
   const int row_base = b * p.N;
-  const int sh = (p.w1 == 8) ? 3 : (p.w1 == 16 ? 4 : 5);
-  const int QS = SK_ROWS >> sh;                               // queries per row group
+  constexpr int sh = (W1 == 8) ? 3 : (W1 == 16 ? 4 : 5);
+  constexpr int QS = SK_ROWS >> sh;                           // queries per row group
   const int q_lo = (k0 / QS) * QS;
   const int q_last = min(p.N - 1, k0 + SK_BK - 1 + p.w2 - 1);
   const int nsub = (q_last - q_lo) / QS + 1;
-  const int total = group * nsub;
+  const int total = nsub;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&ag_full[i], 2);
+      mbar_init(&ag_full[i], 4);
       mbar_init(&ag_empty[i], 1);
       mbar_init(&st_full[i], 1);
       mbar_init(&st_free[i], 4);
@@ -566,59 +600,56 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
       }
     }
   } else if (warp >= 6) {
-    // ---------------------------------------------------------------- builder warps: one row each
-    const int c = (warp - 6) * 32 + lane;                 // row of the group
-    const int qi = c >> sh, jj = c & (p.w1 - 1);
+    // ---------------------------------------------------------------- builder warps: half a row each
+    const int tid = (warp - 6) * 32 + lane;               // 0..127
+    const int c = tid >> 1, half = tid & 1;               // row of the group, 64-column half
+    const int qi = c >> sh, jj = c & (W1 - 1);
     bool ok = true;
+    const bool prof = pk.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 6 && lane == 0;
+    long long bw = 0, bb = 0;
     for (int it = 0; it < total && ok; ++it) {
       const int buf = it & 1;
+      const long long b0 = clock64();
       ok = __all_sync(0xffffffffu, mbar_wait(&ag_empty[buf], ((it >> 1) & 1) ^ 1u, abort_word));
       if (!ok) break;
-      const int g = it / nsub, s = it - g * nsub;
-      const int h = hk * group + g;
-      const int i = q_lo + s * QS + qi;
-      const int p1 = i - p.w1 + 1 + jj;
+      const long long b1 = clock64();
+      const int i = q_lo + it * QS + qi;
+      const int p1 = i - W1 + 1 + jj;
       const bool valid = (i <= q_last) && (p1 >= 0);
       const long long qrow_idx = row_base + min(i, p.N - 1);
       const long long krow_idx = row_base + max(p1, 0);
-      // a [64 x 128] group is two 64-column halves of 8 KB
-      uint8_t* tA = smem + S::kA + buf * 16384;
-      uint8_t* tG = smem + S::kG + buf * 16384;
-      const __nv_bfloat16* qrow = p.q + qrow_idx * p.ldq + h * SB_D;
-      const __nv_bfloat16* k1row = p.k1 + krow_idx * p.ldk1 + hk * SB_D;
-      const __nv_bfloat16* v1row = p.v1 + krow_idx * p.ldv1 + hk * SB_D;
-      const __nv_bfloat16* dorow = p.dout + qrow_idx * p.lddo + h * SB_D;
+      uint8_t* tA = smem + S::kA + buf * 16384 + half * 8192 + c * 128;     // a [64 x 128] group: two 8 KB halves
+      uint8_t* tG = smem + S::kG + buf * 16384 + half * 8192 + c * 128;
+      const __nv_bfloat16* qrow = p.q + qrow_idx * p.ldq + hq * SB_D + half * 64;
+      const __nv_bfloat16* k1row = p.k1 + krow_idx * p.ldk1 + hk * SB_D + half * 64;
+      const __nv_bfloat16* v1row = p.v1 + krow_idx * p.ldv1 + hk * SB_D + half * 64;
+      const __nv_bfloat16* dorow = p.dout + qrow_idx * p.lddo + hq * SB_D + half * 64;
+      uint4 qv[8], kv[8], gv[8], vv[8];
+      const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {
-        const uint4 qa = *reinterpret_cast<const uint4*>(qrow + ch * 8);
-        const uint4 ka = *reinterpret_cast<const uint4*>(k1row + ch * 8);
-        const uint4 ga = *reinterpret_cast<const uint4*>(dorow + ch * 8);
-        const uint4 va = *reinterpret_cast<const uint4*>(v1row + ch * 8);
-        const __nv_bfloat162* qh = reinterpret_cast<const __nv_bfloat162*>(&qa);
-        const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&ka);
-        const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&ga);
-        const __nv_bfloat162* vh = reinterpret_cast<const __nv_bfloat162*>(&va);
-        uint4 oa, og;
-        uint32_t* wa = reinterpret_cast<uint32_t*>(&oa);
-        uint32_t* wg = reinterpret_cast<uint32_t*>(&og);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 x = __bfloat1622float2(qh[e]), y = __bfloat1622float2(kh[e]);
-          const float2 u = __bfloat1622float2(gh[e]), w = __bfloat1622float2(vh[e]);
-          wa[e] = valid ? pack_bf16(x.x * y.x, x.y * y.y) : 0u;
-          wg[e] = valid ? pack_bf16(u.x * w.x, u.y * w.y) : 0u;
-        }
-        const int off = (ch >> 3) * 8192 + c * 128 + (((ch & 7) ^ (c & 7)) * 16);
-        *reinterpret_cast<uint4*>(tA + off) = oa;
-        *reinterpret_cast<uint4*>(tG + off) = og;
+      for (int ch = 0; ch < 8; ++ch) {                    // all loads first (see build_product_row)
+        qv[ch] = valid ? *reinterpret_cast<const uint4*>(qrow + ch * 8) : zero4;
+        kv[ch] = valid ? *reinterpret_cast<const uint4*>(k1row + ch * 8) : zero4;
+        gv[ch] = valid ? *reinterpret_cast<const uint4*>(dorow + ch * 8) : zero4;
+        vv[ch] = valid ? *reinterpret_cast<const uint4*>(v1row + ch * 8) : zero4;
       }
-      const long long stat = ((long long)b * p.Hq + h) * p.N + min(i, p.N - 1);
-      s_vec[buf * 128 + c] = valid ? p.lse2[stat] : INFINITY;
-      s_vec[buf * 128 + 64 + c] = valid ? p.delta[stat] : 0.f;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        const int off = (ch ^ (c & 7)) * 16;
+        *reinterpret_cast<uint4*>(tA + off) = mul_bf16x8(qv[ch], kv[ch]);
+        *reinterpret_cast<uint4*>(tG + off) = mul_bf16x8(gv[ch], vv[ch]);
+      }
+      if (half == 0) {
+        const long long stat = ((long long)b * p.Hq + hq) * p.N + min(i, p.N - 1);
+        s_vec[buf * 128 + c] = valid ? p.lse2[stat] : INFINITY;
+        s_vec[buf * 128 + 64 + c] = valid ? p.delta[stat] : 0.f;
+      }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ag_full[buf]);
+      if (prof) { bw += b1 - b0; bb += clock64() - b1; }
     }
+    if (prof) { pk.prof[8] = bw; pk.prof[9] = bb; }
   } else {
     // ---------------------------------------------------------------- compute warps: thread = key
     const int quarter = warp & 3;
@@ -628,20 +659,24 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
     uint8_t* sPT = smem + S::kPT;
     uint8_t* sDST = smem + S::kDST;
     bool ok = true;
+    const bool prof = pk.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 2 && lane == 0;
+    long long pc[5] = {0, 0, 0, 0, 0};
     for (int it = 0; it < total && ok; ++it) {
       const int buf = it & 1;
-      const int g = it / nsub, s = it - g * nsub;
-      const int i_start = q_lo + s * QS;
+      const int i_start = q_lo + it * QS;
+      const long long c0 = clock64();
       ok = __all_sync(0xffffffffu, mbar_wait(&ag_full[buf], (it >> 1) & 1, abort_word));   // stats visible
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&st_full[buf], (it >> 1) & 1, abort_word));
       if (!ok) break;
       tc_fence_after();
+      const long long c1 = clock64();
       uint32_t sv[2][32], dv[2][32];
       tmem_ld_32x32(tmem_ST + uint32_t(buf * 64) + lane_off, sv[0]);
       tmem_ld_32x32(tmem_ST + uint32_t(buf * 64 + 32) + lane_off, sv[1]);
       tmem_ld_32x32(tmem_dPT + uint32_t(buf * 64) + lane_off, dv[0]);
       tmem_ld_32x32(tmem_dPT + uint32_t(buf * 64 + 32) + lane_off, dv[1]);
       tmem_ld_wait();
+      const long long c2 = clock64();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&st_free[buf]);
@@ -649,32 +684,43 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
         ok = __all_sync(0xffffffffu, mbar_wait(pds_empty, (it - 1) & 1, abort_word));
         if (!ok) break;
       }
-      const float* lse = s_vec + buf * 128;
-      const float* dlt = lse + 64;
+      const long long c3 = clock64();
+      const float4* lse4 = reinterpret_cast<const float4*>(s_vec + buf * 128);
+      const float4* dlt4 = lse4 + 16;
+      bool qmask[QS];                                      // this key is inside query qq's long window
+#pragma unroll
+      for (int qq = 0; qq < QS; ++qq) {
+        const int i = i_start + qq;
+        qmask[qq] = (kp <= i) && (kp > i - p.w2);
+      }
 #pragma unroll
       for (int c2 = 0; c2 < 2; ++c2) {
-        float pr[32], ds[32];
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int col = c2 * 32 + e;
-          const int i = i_start + (col >> sh);
-          const bool v = (kp <= i) && (kp > i - p.w2);
-          const float pv = v ? exp2f(fmaf(__uint_as_float(sv[c2][e]), p.scale_log2, -lse[col])) : 0.f;
-          pr[e] = pv;
-          ds[e] = pv * (__uint_as_float(dv[c2][e]) - dlt[col]) * p.scale;
-        }
 #pragma unroll
         for (int gq = 0; gq < 4; ++gq) {
+          float ls[8], dl[8];
+          *reinterpret_cast<float4*>(&ls[0]) = lse4[c2 * 8 + gq * 2];
+          *reinterpret_cast<float4*>(&ls[4]) = lse4[c2 * 8 + gq * 2 + 1];
+          *reinterpret_cast<float4*>(&dl[0]) = dlt4[c2 * 8 + gq * 2];
+          *reinterpret_cast<float4*>(&dl[4]) = dlt4[c2 * 8 + gq * 2 + 1];
+          float pr[8], ds[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int col = c2 * 32 + gq * 8 + e;
+            const float l = qmask[col >> sh] ? ls[e] : INFINITY;        // masked or padded row: exp2(-inf) = 0
+            const float pv = ex2_approx(fmaf(__uint_as_float(sv[c2][gq * 8 + e]), p.scale_log2, -l));
+            pr[e] = pv;
+            ds[e] = (pv * p.scale) * (__uint_as_float(dv[c2][gq * 8 + e]) - dl[e]);
+          }
           const int chunk = (c2 * 4 + gq) ^ (t & 7);
           uint4 u, w;
-          u.x = pack_bf16(pr[8 * gq + 0], pr[8 * gq + 1]);
-          u.y = pack_bf16(pr[8 * gq + 2], pr[8 * gq + 3]);
-          u.z = pack_bf16(pr[8 * gq + 4], pr[8 * gq + 5]);
-          u.w = pack_bf16(pr[8 * gq + 6], pr[8 * gq + 7]);
-          w.x = pack_bf16(ds[8 * gq + 0], ds[8 * gq + 1]);
-          w.y = pack_bf16(ds[8 * gq + 2], ds[8 * gq + 3]);
-          w.z = pack_bf16(ds[8 * gq + 4], ds[8 * gq + 5]);
-          w.w = pack_bf16(ds[8 * gq + 6], ds[8 * gq + 7]);
+          u.x = pack_bf16(pr[0], pr[1]);
+          u.y = pack_bf16(pr[2], pr[3]);
+          u.z = pack_bf16(pr[4], pr[5]);
+          u.w = pack_bf16(pr[6], pr[7]);
+          w.x = pack_bf16(ds[0], ds[1]);
+          w.y = pack_bf16(ds[2], ds[3]);
+          w.z = pack_bf16(ds[4], ds[5]);
+          w.w = pack_bf16(ds[6], ds[7]);
           *reinterpret_cast<uint4*>(sPT + t * 128 + chunk * 16) = u;
           *reinterpret_cast<uint4*>(sDST + t * 128 + chunk * 16) = w;
         }
@@ -682,13 +728,23 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
+      if (prof) {
+        const long long c4 = clock64();
+        pc[0] += c1 - c0; pc[1] += c2 - c1; pc[2] += c3 - c2; pc[3] += c4 - c3; pc[4] += 1;
+      }
+    }
+    if (prof) {
+      for (int i = 0; i < 5; ++i) pk.prof[i] = pc[i];
     }
     // ---------------------------------------------------------------- epilogue: plain stores
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pds_empty, (total - 1) & 1, abort_word));
     if (ok) {
       tc_fence_after();
-      __nv_bfloat16* dkrow = pk.dk2 + (long long)(row_base + min(kp, p.N - 1)) * pk.lddk2 + hk * SB_D;
-      __nv_bfloat16* dvrow = pk.dv2 + (long long)(row_base + min(kp, p.N - 1)) * pk.lddv2 + hk * SB_D;
+      const long long krow = row_base + min(kp, p.N - 1);
+      __nv_bfloat16* dkrow = pk.dk2 + krow * pk.lddk2 + hk * SB_D;
+      __nv_bfloat16* dvrow = pk.dv2 + krow * pk.lddv2 + hk * SB_D;
+      float* dkacc = pk.dk2_acc + krow * ((long long)p.Hkv * SB_D) + hk * SB_D;
+      float* dvacc = pk.dv2_acc + krow * ((long long)p.Hkv * SB_D) + hk * SB_D;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t a[32], v[32];
@@ -696,19 +752,31 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
         tmem_ld_32x32(tmem_dV + lane_off + c * 32, v);
         tmem_ld_wait();
         if (kp < p.N) {
+          if (group == 1) {
 #pragma unroll
-          for (int gq = 0; gq < 4; ++gq) {
-            uint4 u, w;
-            u.x = pack_bf16(__uint_as_float(a[8 * gq + 0]), __uint_as_float(a[8 * gq + 1]));
-            u.y = pack_bf16(__uint_as_float(a[8 * gq + 2]), __uint_as_float(a[8 * gq + 3]));
-            u.z = pack_bf16(__uint_as_float(a[8 * gq + 4]), __uint_as_float(a[8 * gq + 5]));
-            u.w = pack_bf16(__uint_as_float(a[8 * gq + 6]), __uint_as_float(a[8 * gq + 7]));
-            w.x = pack_bf16(__uint_as_float(v[8 * gq + 0]), __uint_as_float(v[8 * gq + 1]));
-            w.y = pack_bf16(__uint_as_float(v[8 * gq + 2]), __uint_as_float(v[8 * gq + 3]));
-            w.z = pack_bf16(__uint_as_float(v[8 * gq + 4]), __uint_as_float(v[8 * gq + 5]));
-            w.w = pack_bf16(__uint_as_float(v[8 * gq + 6]), __uint_as_float(v[8 * gq + 7]));
-            *reinterpret_cast<uint4*>(dkrow + c * 32 + gq * 8) = u;
-            *reinterpret_cast<uint4*>(dvrow + c * 32 + gq * 8) = w;
+            for (int gq = 0; gq < 4; ++gq) {
+              uint4 u, w;
+              u.x = pack_bf16(__uint_as_float(a[8 * gq + 0]), __uint_as_float(a[8 * gq + 1]));
+              u.y = pack_bf16(__uint_as_float(a[8 * gq + 2]), __uint_as_float(a[8 * gq + 3]));
+              u.z = pack_bf16(__uint_as_float(a[8 * gq + 4]), __uint_as_float(a[8 * gq + 5]));
+              u.w = pack_bf16(__uint_as_float(a[8 * gq + 6]), __uint_as_float(a[8 * gq + 7]));
+              w.x = pack_bf16(__uint_as_float(v[8 * gq + 0]), __uint_as_float(v[8 * gq + 1]));
+              w.y = pack_bf16(__uint_as_float(v[8 * gq + 2]), __uint_as_float(v[8 * gq + 3]));
+              w.z = pack_bf16(__uint_as_float(v[8 * gq + 4]), __uint_as_float(v[8 * gq + 5]));
+              w.w = pack_bf16(__uint_as_float(v[8 * gq + 6]), __uint_as_float(v[8 * gq + 7]));
+              *reinterpret_cast<uint4*>(dkrow + c * 32 + gq * 8) = u;
+              *reinterpret_cast<uint4*>(dvrow + c * 32 + gq * 8) = w;
+            }
+          } else {
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4) {
+              atomicAdd(reinterpret_cast<float4*>(dkacc + c * 32 + q4 * 4),
+                        make_float4(__uint_as_float(a[4 * q4]), __uint_as_float(a[4 * q4 + 1]), __uint_as_float(a[4 * q4 + 2]),
+                                    __uint_as_float(a[4 * q4 + 3])));
+              atomicAdd(reinterpret_cast<float4*>(dvacc + c * 32 + q4 * 4),
+                        make_float4(__uint_as_float(v[4 * q4]), __uint_as_float(v[4 * q4 + 1]), __uint_as_float(v[4 * q4 + 2]),
+                                    __uint_as_float(v[4 * q4 + 3])));
+            }
           }
         }
       }
@@ -727,13 +795,17 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
 
 }  // namespace nga
 
+extern "C" void nga_simplicial_bwd_set_prof(long long* device_ptr) { nga::g_simp_prof = device_ptr; }
+
 // Backward of nga_simplicial_fwd.  `out`, `lse2` come from the forward pass.  dq / dk2 / dv2 are
 // written as bf16 (strided like their inputs); dk1 / dv1 are accumulated in the fp32 scratch
-// buffers `dk1_acc` / `dv1_acc` ([B*N, Hkv*128], zeroed here) and cast into dk1 / dv1; `delta` is
-// fp32 scratch [B, Hq, N].
+// buffers `dk1_acc` / `dv1_acc` ([B*N, Hkv*128], zeroed here) and cast into dk1 / dv1; `dk2_acc` /
+// `dv2_acc` (same shape) are needed only when Hq > Hkv (may be null otherwise); `delta` is fp32
+// scratch [B, Hq, N].
 extern "C" int nga_simplicial_bwd(const void* q, const void* k1, const void* k2, const void* v1, const void* v2,
                                   const void* out, const void* dout, const float* lse2, void* dq, void* dk1,
-                                  void* dk2, void* dv1, void* dv2, float* dk1_acc, float* dv1_acc, float* delta,
+                                  void* dk2, void* dv1, void* dv2, float* dk1_acc, float* dv1_acc, float* dk2_acc,
+                                  float* dv2_acc, float* delta,
                                   long long ldq, long long ldk1, long long ldk2, long long ldv1, long long ldv2,
                                   long long ldo, long long lddo, long long lddq, long long lddk1, long long lddk2,
                                   long long lddv1, long long lddv2, int B, int N, int Hq, int Hkv, int D, int w1,
@@ -759,9 +831,10 @@ extern "C" int nga_simplicial_bwd(const void* q, const void* k1, const void* k2,
     cudaError_t e = cudaFuncSetAttribute(simplicial_bwd_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SimpBwdQSmem::kTotal);
     if (e != cudaSuccess) return -1000 - (int)e;
-    e = cudaFuncSetAttribute(simplicial_bwd_k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             SimpBwdKSmem::kTotal);
-    if (e != cudaSuccess) return -1000 - (int)e;
+    for (auto kern : {simplicial_bwd_k_kernel<8>, simplicial_bwd_k_kernel<16>, simplicial_bwd_k_kernel<32>}) {
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SimpBwdKSmem::kTotal);
+      if (e != cudaSuccess) return -1000 - (int)e;
+    }
     attr_done = true;
   }
   {
@@ -802,9 +875,26 @@ extern "C" int nga_simplicial_bwd(const void* q, const void* k1, const void* k2,
     pk.dk2 = reinterpret_cast<__nv_bfloat16*>(dk2);
     pk.dv2 = reinterpret_cast<__nv_bfloat16*>(dv2);
     pk.lddk2 = lddk2; pk.lddv2 = lddv2;
-    dim3 grid((N + SK_BK - 1) / SK_BK, Hkv, B);
-    simplicial_bwd_k_kernel<<<grid, SK_THREADS, SimpBwdKSmem::kTotal, st>>>(tk128, tv128, pk);
+    pk.dk2_acc = dk2_acc; pk.dv2_acc = dv2_acc;
+    pk.prof = g_simp_prof;
+    if (Hq != Hkv) {
+      if (dk2_acc == nullptr || dv2_acc == nullptr) return -7;
+      cudaMemsetAsync(dk2_acc, 0, sizeof(float) * rows * kvcols, st);
+      cudaMemsetAsync(dv2_acc, 0, sizeof(float) * rows * kvcols, st);
+    }
+    dim3 grid((N + SK_BK - 1) / SK_BK, Hq, B);
+    auto kern = w1 == 8 ? simplicial_bwd_k_kernel<8> : (w1 == 16 ? simplicial_bwd_k_kernel<16> : simplicial_bwd_k_kernel<32>);
+    kern<<<grid, SK_THREADS, SimpBwdKSmem::kTotal, st>>>(tk128, tv128, pk);
     count_launch();
+    if (Hq != Hkv) {
+      const long long n4 = rows * kvcols / 4;
+      simp_cast_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dk2_acc, reinterpret_cast<__nv_bfloat16*>(dk2), rows,
+                                                                    (int)kvcols, lddk2);
+      count_launch();
+      simp_cast_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dv2_acc, reinterpret_cast<__nv_bfloat16*>(dv2), rows,
+                                                                    (int)kvcols, lddv2);
+      count_launch();
+    }
   }
   {
     const long long n4 = rows * kvcols / 4;

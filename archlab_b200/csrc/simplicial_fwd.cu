@@ -188,21 +188,27 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
       const __nv_bfloat16* qrow = p.q + (long long)(row_base + min(i, p.N - 1)) * p.ldq + h * SX_D;
       const __nv_bfloat16* krow = p.k1 + (long long)(row_base + max(p1, 0)) * p.ldk1 + hk * SX_D;
       uint8_t* sA = smem + S::kA;
+      // loads of a half row first, then the packed products (bf16 x bf16 rounded to bf16 equals the fp32
+      // product rounded once): a generic shared store between two global loads would serialise every
+      // chunk on the L2 latency
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {            // sixteen 16-byte chunks of 8 bf16
-        uint4 qa = *reinterpret_cast<const uint4*>(qrow + c * 8);
-        uint4 ka = *reinterpret_cast<const uint4*>(krow + c * 8);
-        const __nv_bfloat162* qh = reinterpret_cast<const __nv_bfloat162*>(&qa);
-        const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&ka);
-        uint4 o;
-        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+      for (int hb = 0; hb < 2; ++hb) {
+        uint4 qa[8], ka[8];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 a = __bfloat1622float2(qh[e]), k = __bfloat1622float2(kh[e]);
-          ow[e] = row_valid ? pack_bf16(a.x * k.x, a.y * k.y) : 0u;
+        for (int c = 0; c < 8; ++c) {
+          qa[c] = row_valid ? *reinterpret_cast<const uint4*>(qrow + (hb * 8 + c) * 8) : make_uint4(0u, 0u, 0u, 0u);
+          ka[c] = row_valid ? *reinterpret_cast<const uint4*>(krow + (hb * 8 + c) * 8) : make_uint4(0u, 0u, 0u, 0u);
         }
-        const int chunk = (c & 7) ^ (r & 7);
-        *reinterpret_cast<uint4*>(sA + (c >> 3) * 16384 + r * 128 + chunk * 16) = o;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint4 o;
+          const __nv_bfloat162* qh = reinterpret_cast<const __nv_bfloat162*>(&qa[c]);
+          const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&ka[c]);
+          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) oh[e] = __hmul2(qh[e], kh[e]);
+          *reinterpret_cast<uint4*>(sA + hb * 16384 + r * 128 + ((c ^ (r & 7)) * 16)) = o;
+        }
       }
       fence_proxy_async_smem();
       __syncwarp();
@@ -272,7 +278,7 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
         float pr[32];
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          pr[e] = exp2f(fmaf(__uint_as_float(sv[c][e]), p.scale_log2, -m_sub));
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pr[e]) : "f"(fmaf(__uint_as_float(sv[c][e]), p.scale_log2, -m_sub)));
           ps4[e & 3] += pr[e];
         }
         uint8_t* line = sP + (c >> 1) * 16384 + r * 128;

@@ -18,11 +18,14 @@ def simplicial_bwd(q, k1, k2, v1, v2, out, dout, lse2, w1: int, w2: int, scale: 
     dk1, dk2, dv1, dv2 = (torch.empty(B, N, Hkv, D, dtype=torch.bfloat16, device=dev) for _ in range(4))
     dk1_acc = torch.empty(B * N, Hkv * D, dtype=torch.float32, device=dev)
     dv1_acc = torch.empty_like(dk1_acc)
+    dk2_acc = torch.empty_like(dk1_acc) if Hq != Hkv else None
+    dv2_acc = torch.empty_like(dk1_acc) if Hq != Hkv else None
     delta = torch.empty(B, Hq, N, dtype=torch.float32, device=dev)
     rc = native.lib().nga_simplicial_bwd(
         q.data_ptr(), k1.data_ptr(), k2.data_ptr(), v1.data_ptr(), v2.data_ptr(), out.data_ptr(), dout.data_ptr(),
         lse2.data_ptr(), dq.data_ptr(), dk1.data_ptr(), dk2.data_ptr(), dv1.data_ptr(), dv2.data_ptr(),
-        dk1_acc.data_ptr(), dv1_acc.data_ptr(), delta.data_ptr(), ldq, ldk1, ldk2, ldv1, ldv2, ldo, lddo,
+        dk1_acc.data_ptr(), dv1_acc.data_ptr(), None if dk2_acc is None else dk2_acc.data_ptr(),
+        None if dv2_acc is None else dv2_acc.data_ptr(), delta.data_ptr(), ldq, ldk1, ldk2, ldv1, ldv2, ldo, lddo,
         Hq * D, Hkv * D, Hkv * D, Hkv * D, Hkv * D, B, N, Hq, Hkv, D, w1, w2, scale,
         native.status_word(dev).data_ptr(), native.stream_ptr())
     native.check(rc, "nga_simplicial_bwd")

@@ -10,7 +10,7 @@ from . import native
 
 _vp, _i, _ll, _f = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 native.register_signature("nga_simplicial_fwd", [_vp] * 7 + [_ll] * 6 + [_i] * 7 + [_f, _vp, _vp])
-native.register_signature("nga_simplicial_bwd", [_vp] * 16 + [_ll] * 12 + [_i] * 7 + [_f, _vp, _vp])
+native.register_signature("nga_simplicial_bwd", [_vp] * 18 + [_ll] * 12 + [_i] * 7 + [_f, _vp, _vp])
 
 
 def kernel_supports(q, k1, v1, w1: int, w2: int) -> bool:
