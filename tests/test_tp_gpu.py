@@ -69,3 +69,62 @@ def test_fused_tp_gemms_match_decomposed(tmp_path):
         res = torch.load(tmp_path / f"tp_rank{r}.pt")
         for k, v in res.items():
             assert v < (1e-6 if k.startswith("gathered") else 1e-2), (r, k, v)
+
+
+def _mlp_worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    from archlab_b200.ops import native
+    from archlab_b200.parallel import tp as T
+    from archlab_b200.parallel.tp_layers import TPMLP
+
+    dev = torch.device("cuda", rank)
+    H, I, rows = 256, 512, 256
+    grp = T.TPGroup(rows, max_k=512, max_n=512, device=dev, copy_clusters=2)
+    torch.manual_seed(0)
+    Wg, Wu, Wd = (torch.randn(I, H, device=dev) * 0.05), (torch.randn(I, H, device=dev) * 0.05), (torch.randn(H, I, device=dev) * 0.05)
+    X = torch.randn(world * rows, H, device=dev)
+    Il = I // world
+    fused, plain = TPMLP(H, I, grp, world).to(dev).bfloat16(), TPMLP(H, I, None, world).to(dev)
+    with torch.no_grad():
+        for m in (fused, plain):
+            m.gate_up.weight.copy_(torch.cat([Wg[rank * Il:(rank + 1) * Il], Wu[rank * Il:(rank + 1) * Il]]))
+            m.down.weight.copy_(Wd[:, rank * Il:(rank + 1) * Il])
+    xs = X[rank * rows:(rank + 1) * rows]
+    xa = xs.bfloat16().clone().requires_grad_(True)
+    xb = xs.bfloat16().float().clone().requires_grad_(True)
+    resid = torch.randn(rows, H, device=dev).bfloat16()
+    ya, yb = fused(xa, resid), plain(xb, resid.float())
+    go = torch.randn(rows, H, device=dev)
+    ya.backward(go.bfloat16())
+    yb.backward(go)
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-9)).item()
+    res = {"out": rel(ya, yb), "dx": rel(xa.grad, xb.grad), "dgate_up": rel(fused.gate_up.weight.grad, plain.gate_up.weight.grad),
+           "ddown": rel(fused.down.weight.grad, plain.down.weight.grad)}
+    torch.cuda.synchronize()
+    native.check_status()
+    torch.save(res, os.path.join(out_dir, f"mlp_rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp_mlp_fused_forward_backward(tmp_path):
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_mlp_worker, args=(r, 2, 29633, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=600)
+        if p.is_alive():
+            p.terminate()
+            pytest.fail("worker timed out")
+        assert p.exitcode == 0
+    for r in range(2):
+        for k, v in torch.load(tmp_path / f"mlp_rank{r}.pt").items():
+            assert v < 2e-2, (r, k, v)
