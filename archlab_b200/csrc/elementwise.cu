@@ -36,6 +36,10 @@ __device__ __forceinline__ float warp_sum(float v) {
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
 
 // Per-block reduction of `n` per-warp partial scalars followed by one atomicAdd each.
@@ -321,7 +325,7 @@ __global__ void qkv_post_fwd_kernel(__nv_bfloat16* __restrict__ qkv, const float
                                     const float* __restrict__ gate_w,
                                     const __nv_bfloat16* __restrict__ n, int GC, int C,
                                     float* __restrict__ rstd_out, float* __restrict__ gate_pre,
-                                    long long rows, int T, int Hq, int Hkv, int D) {
+                                    long long rows, int T, int Hq, int Hkv, int D, int skip_qk) {
   const int lane = threadIdx.x & 31;
   const int slots = Hq + 2 * Hkv;
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -331,6 +335,7 @@ __global__ void qkv_post_fwd_kernel(__nv_bfloat16* __restrict__ qkv, const float
   __nv_bfloat16* p = qkv + row * (long long)slots * D + (long long)slot * D;
   const int half = D / 2;
   if (slot < Hq + Hkv) {
+    if (skip_qk) return;                 // handled by the vectorised kernel
     const int t = int(row % T);
     float ss = 0.f;
     // lane owns element pairs (2j, 2j+1) of the first half and their partners in the second half
@@ -385,6 +390,132 @@ __global__ void qkv_post_fwd_kernel(__nv_bfloat16* __restrict__ qkv, const float
   }
 }
 
+// Vectorised q / k path of the post-processing: D / 16 lanes per (token, head), each lane owning 8
+// elements of the first half and their rotation partners (16-byte loads; four times the bytes in flight of
+// the pair-per-lane form, which left these memory-bound kernels at a third of the HBM rate).
+template <int LPH>
+__global__ void qk_rope_norm_fwd_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ cosT,
+                                        const float* __restrict__ sinT, float gain, float* __restrict__ rstd_out,
+                                        long long rows, int T, int Hq, int Hkv) {
+  constexpr int D = LPH * 16, half = D / 2;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int sub = int(gid % LPH);
+  const long long item = gid / LPH;
+  const int nh = Hq + Hkv, slots = Hq + 2 * Hkv;
+  const bool active = item < rows * nh;
+  const long long row = active ? item / nh : 0;
+  const int slot = active ? int(item % nh) : 0;
+  __nv_bfloat16* p = qkv + row * (long long)slots * D + (long long)slot * D + sub * 8;
+  const int t = int(row % T);
+  float y1[8], y2[8], ss = 0.f;
+  if (active) {
+    const uint4 a = *reinterpret_cast<const uint4*>(p);
+    const uint4 b = *reinterpret_cast<const uint4*>(p + half);
+    const float4* c4 = reinterpret_cast<const float4*>(cosT + (long long)t * half + sub * 8);
+    const float4* s4 = reinterpret_cast<const float4*>(sinT + (long long)t * half + sub * 8);
+    const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x1 = __bfloat1622float2(ah[i]), x2 = __bfloat1622float2(bh[i]);
+      // the rotated value is rounded to bf16 before normalising (the eager model's order of operations)
+      y1[2 * i] = __bfloat162float(__float2bfloat16(x1.x * c[2 * i] + x2.x * sn[2 * i]));
+      y1[2 * i + 1] = __bfloat162float(__float2bfloat16(x1.y * c[2 * i + 1] + x2.y * sn[2 * i + 1]));
+      y2[2 * i] = __bfloat162float(__float2bfloat16(x2.x * c[2 * i] - x1.x * sn[2 * i]));
+      y2[2 * i + 1] = __bfloat162float(__float2bfloat16(x2.y * c[2 * i + 1] - x1.y * sn[2 * i + 1]));
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += y1[i] * y1[i] + y2[i] * y2[i];
+  }
+#pragma unroll
+  for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (!active) return;
+  const float rstd = rsqrtf(ss / D + kRmsEps);
+  if (sub == 0) rstd_out[row * nh + slot] = rstd;
+  uint4 o1, o2;
+  uint32_t* w1 = reinterpret_cast<uint32_t*>(&o1);
+  uint32_t* w2 = reinterpret_cast<uint32_t*>(&o2);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    w1[i] = pack2(__bfloat162float(__float2bfloat16(y1[2 * i] * rstd)) * gain,
+                  __bfloat162float(__float2bfloat16(y1[2 * i + 1] * rstd)) * gain);
+    w2[i] = pack2(__bfloat162float(__float2bfloat16(y2[2 * i] * rstd)) * gain,
+                  __bfloat162float(__float2bfloat16(y2[2 * i + 1] * rstd)) * gain);
+  }
+  *reinterpret_cast<uint4*>(p) = o1;
+  *reinterpret_cast<uint4*>(p + half) = o2;
+}
+
+template <int LPH>
+__global__ void qk_rope_norm_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __restrict__ qkv,
+                                        const float* __restrict__ cosT, const float* __restrict__ sinT, float gain,
+                                        const float* __restrict__ rstd_in, long long rows, int T, int Hq, int Hkv) {
+  constexpr int D = LPH * 16, half = D / 2;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int sub = int(gid % LPH);
+  const long long item = gid / LPH;
+  const int nh = Hq + Hkv, slots = Hq + 2 * Hkv;
+  const bool active = item < rows * nh;
+  const long long row = active ? item / nh : 0;
+  const int slot = active ? int(item % nh) : 0;
+  const long long off = row * (long long)slots * D + (long long)slot * D + sub * 8;
+  const int t = int(row % T);
+  float ya[8], yb[8], ga[8], gb[8], dot = 0.f;
+  if (active) {
+    const uint4 a = *reinterpret_cast<const uint4*>(qkv + off);
+    const uint4 b = *reinterpret_cast<const uint4*>(qkv + off + half);
+    const uint4 da = *reinterpret_cast<const uint4*>(dqkv + off);
+    const uint4 db = *reinterpret_cast<const uint4*>(dqkv + off + half);
+    const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&b);
+    const __nv_bfloat162* dah = reinterpret_cast<const __nv_bfloat162*>(&da);
+    const __nv_bfloat162* dbh = reinterpret_cast<const __nv_bfloat162*>(&db);
+    const float inv_gain = 1.f / gain;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 u = __bfloat1622float2(ah[i]), v = __bfloat1622float2(bh[i]);
+      const float2 gu = __bfloat1622float2(dah[i]), gv = __bfloat1622float2(dbh[i]);
+      ya[2 * i] = u.x * inv_gain; ya[2 * i + 1] = u.y * inv_gain;
+      yb[2 * i] = v.x * inv_gain; yb[2 * i + 1] = v.y * inv_gain;
+      ga[2 * i] = gu.x * gain; ga[2 * i + 1] = gu.y * gain;
+      gb[2 * i] = gv.x * gain; gb[2 * i + 1] = gv.y * gain;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dot += ga[i] * ya[i] + gb[i] * yb[i];
+  }
+#pragma unroll
+  for (int o = LPH / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  if (!active) return;
+  dot /= D;
+  const float rstd = rstd_in[row * nh + slot];
+  const float4* c4 = reinterpret_cast<const float4*>(cosT + (long long)t * half + sub * 8);
+  const float4* s4 = reinterpret_cast<const float4*>(sinT + (long long)t * half + sub * 8);
+  const float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
+  const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  uint4 o1, o2;
+  uint32_t* w1 = reinterpret_cast<uint32_t*>(&o1);
+  uint32_t* w2 = reinterpret_cast<uint32_t*>(&o2);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float r1[2], r2[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int k = 2 * i + e;
+      const float a1 = rstd * (ga[k] - ya[k] * dot), b1 = rstd * (gb[k] - yb[k] * dot);
+      r1[e] = a1 * c[k] - b1 * sn[k];
+      r2[e] = a1 * sn[k] + b1 * c[k];
+    }
+    w1[i] = pack2(r1[0], r1[1]);
+    w2[i] = pack2(r2[0], r2[1]);
+  }
+  *reinterpret_cast<uint4*>(dqkv + off) = o1;
+  *reinterpret_cast<uint4*>(dqkv + off + half) = o2;
+}
+
 // Backward, in place on dqkv (gradient w.r.t. the post-processed q', k', v').  qkv holds the saved
 // post-processed values.  Writes dgp [tokens, Hkv] (gradient of the gate pre-activation) and
 // accumulates the value-embedding table gradient with atomics.
@@ -396,7 +527,7 @@ __global__ void qkv_post_bwd_kernel(__nv_bfloat16* __restrict__ dqkv,
                                     const float* __restrict__ rstd_in,
                                     const float* __restrict__ gate_pre, float* __restrict__ dgp_out,
                                     float* __restrict__ dve_table, long long rows, int T, int Hq,
-                                    int Hkv, int D) {
+                                    int Hkv, int D, int skip_qk) {
   const int lane = threadIdx.x & 31;
   const int slots = Hq + 2 * Hkv;
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -408,6 +539,7 @@ __global__ void qkv_post_bwd_kernel(__nv_bfloat16* __restrict__ dqkv,
   const __nv_bfloat16* p = qkv + off;
   const int half = D / 2;
   if (slot < Hq + Hkv) {
+    if (skip_qk) return;
     const int t = int(row % T);
     const float rstd = rstd_in[row * (Hq + Hkv) + slot];
     // y = q' / gain (normalised, rotated); dy = gain * dq'
@@ -451,10 +583,16 @@ __global__ void qkv_post_bwd_kernel(__nv_bfloat16* __restrict__ dqkv,
     const __nv_bfloat16* ve = ve_table + idx[row] * (long long)(Hkv * D) + (long long)h * D;
     float* dve = dve_table + idx[row] * (long long)(Hkv * D) + (long long)h * D;
     float dot = 0.f;
-    for (int j = lane; j < D; j += 32) {
-      const float g = __bfloat162float(dp[j]);
-      dot += g * __bfloat162float(ve[j]);
-      atomicAdd(dve + j, 3.f * s * g);
+    const float sc = 3.f * s;
+    for (int j = lane * 4; j < D; j += 128) {            // four elements per lane: one vector atomic instead of four
+      const uint2 gv = *reinterpret_cast<const uint2*>(dp + j);
+      const uint2 ev = *reinterpret_cast<const uint2*>(ve + j);
+      const float2 g0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv.x));
+      const float2 g1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv.y));
+      const float2 e0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ev.x));
+      const float2 e1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ev.y));
+      dot += g0.x * e0.x + g0.y * e0.y + g1.x * e1.x + g1.y * e1.y;
+      atomicAdd(reinterpret_cast<float4*>(dve + j), make_float4(sc * g0.x, sc * g0.y, sc * g1.x, sc * g1.y));
     }
     dot = warp_sum(dot);
     if (lane == 0) dgp_out[row * Hkv + h] = 3.f * s * (1.f - s) * dot;
@@ -639,10 +777,21 @@ extern "C" int nga_qkv_post_fwd(void* qkv, const float* cosT, const float* sinT,
                                 long long rows, int T, int Hq, int Hkv, int D, void* stream) {
   if (D % 64 || D > 256 || rows <= 0) return -1;
   const long long warps = rows * (Hq + 2 * Hkv);
-  qkv_post_fwd_kernel<<<warp_grid(warps, 8), 256, 0, ST(stream)>>>(
-      BFW(qkv), cosT, sinT, gain, idx, BF(ve_table), gate_w, BF(n), GC, C, rstd, gate_pre, rows, T,
-      Hq, Hkv, D);
-  count_launch();
+  const bool vec = (D == 64 || D == 128 || D == 256);
+  if (vec) {
+    const long long threads = rows * (Hq + Hkv) * (D / 16);
+    const unsigned grid = (unsigned)((threads + 255) / 256);
+    if (D == 64) qk_rope_norm_fwd_kernel<4><<<grid, 256, 0, ST(stream)>>>(BFW(qkv), cosT, sinT, gain, rstd, rows, T, Hq, Hkv);
+    else if (D == 128) qk_rope_norm_fwd_kernel<8><<<grid, 256, 0, ST(stream)>>>(BFW(qkv), cosT, sinT, gain, rstd, rows, T, Hq, Hkv);
+    else qk_rope_norm_fwd_kernel<16><<<grid, 256, 0, ST(stream)>>>(BFW(qkv), cosT, sinT, gain, rstd, rows, T, Hq, Hkv);
+    count_launch();
+  }
+  if (!vec || ve_table != nullptr) {
+    qkv_post_fwd_kernel<<<warp_grid(warps, 8), 256, 0, ST(stream)>>>(
+        BFW(qkv), cosT, sinT, gain, idx, BF(ve_table), gate_w, BF(n), GC, C, rstd, gate_pre, rows, T,
+        Hq, Hkv, D, vec ? 1 : 0);
+    count_launch();
+  }
   NGA_CHECK_LAUNCH();
   return 0;
 }
@@ -654,10 +803,21 @@ extern "C" int nga_qkv_post_bwd(void* dqkv, const void* qkv, const float* cosT, 
                                 void* stream) {
   if (D % 64 || D > 256 || rows <= 0) return -1;
   const long long warps = rows * (Hq + 2 * Hkv);
-  qkv_post_bwd_kernel<<<warp_grid(warps, 8), 256, 0, ST(stream)>>>(
-      BFW(dqkv), BF(qkv), cosT, sinT, gain, idx, BF(ve_table), rstd, gate_pre, dgp, dve_table, rows,
-      T, Hq, Hkv, D);
-  count_launch();
+  const bool vec = (D == 64 || D == 128 || D == 256);
+  if (vec) {
+    const long long threads = rows * (Hq + Hkv) * (D / 16);
+    const unsigned grid = (unsigned)((threads + 255) / 256);
+    if (D == 64) qk_rope_norm_bwd_kernel<4><<<grid, 256, 0, ST(stream)>>>(BFW(dqkv), BF(qkv), cosT, sinT, gain, rstd, rows, T, Hq, Hkv);
+    else if (D == 128) qk_rope_norm_bwd_kernel<8><<<grid, 256, 0, ST(stream)>>>(BFW(dqkv), BF(qkv), cosT, sinT, gain, rstd, rows, T, Hq, Hkv);
+    else qk_rope_norm_bwd_kernel<16><<<grid, 256, 0, ST(stream)>>>(BFW(dqkv), BF(qkv), cosT, sinT, gain, rstd, rows, T, Hq, Hkv);
+    count_launch();
+  }
+  if (!vec || ve_table != nullptr) {
+    qkv_post_bwd_kernel<<<warp_grid(warps, 8), 256, 0, ST(stream)>>>(
+        BFW(dqkv), BF(qkv), cosT, sinT, gain, idx, BF(ve_table), rstd, gate_pre, dgp, dve_table, rows,
+        T, Hq, Hkv, D, vec ? 1 : 0);
+    count_launch();
+  }
   NGA_CHECK_LAUNCH();
   return 0;
 }

@@ -28,7 +28,7 @@ constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
 constexpr int G2_OUT_OFFSET = G2_STAGES * G2_STAGE_BYTES;      // 4 warps x 2 staging tiles of 32 rows x 128 B
 constexpr int G2_OUT_BYTES = 4 * 2 * 4096;
 constexpr int G2_BAR_OFFSET = G2_OUT_OFFSET + G2_OUT_BYTES;
-constexpr int G2_SMEM = G2_BAR_OFFSET + (2 * G2_STAGES + 4) * 8 + 16 + 1024;
+constexpr int G2_SMEM = G2_BAR_OFFSET + (2 * G2_STAGES + 4 + 8) * 8 + 16 + 1024;
 constexpr int G2_THREADS = 192;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -180,14 +180,15 @@ template <int A_MN, int B_MN, int TP>
 __global__ void __launch_bounds__(G2_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const GemmParams p, const __grid_constant__ CUtensorMap tmA2, const TpParams tp,
-                  const __grid_constant__ TpMaps tpm) {
+                  const __grid_constant__ TpMaps tpm, const __grid_constant__ CUtensorMap tmAux) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + G2_BAR_OFFSET);
   uint64_t* empty_bar = full_bar + G2_STAGES;
   uint64_t* tfull_bar = empty_bar + G2_STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* aux_bar = tempty_bar + 2;                   // [4 epilogue warps][2 staging buffers]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(aux_bar + 8);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -212,6 +213,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       mbar_init(&tfull_bar[a], 1);
       mbar_init(&tempty_bar[a], 8);
     }
+    for (int a = 0; a < 8; ++a) mbar_init(&aux_bar[a], 1);
     *abort_word = 0;
     fence_mbar_init();
   }
@@ -327,7 +329,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     bool ok = true;
     const bool vec_ok = epilogue_vec_ok(p);
     const bool need_aux = (p.epi == kEpiAxpby || p.epi == kEpiMulDRelu2);
-    const bool aux_fast = aux_prefetchable(p);
+    // With aux_tma the residual / activation operand of the epilogue arrives through TMA into this warp's
+    // two staging tiles (32 rows x 64 columns, 128-byte swizzle), two chunks ahead of its use: coalesced,
+    // asynchronous, and off the load/store unit, instead of one 16-byte row-strided load per lane.
+    const bool aux_tma = p.aux_tma != 0 && need_aux && !(TP && (tp.mode & kTpScatter));
+    const bool aux_fast = aux_prefetchable(p) && !aux_tma;
+    uint64_t* abar = aux_bar + quarter * 2;
+    uint8_t* abuf = smem + G2_OUT_OFFSET + quarter * 8192;
+    uint32_t aux_phase = 0;                               // bit i: parity of staging buffer i
     uint32_t out_cnt = 0;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int b, mb, nb, otile, kb0, kb1;
@@ -343,6 +352,16 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       }
       AuxPre nxt;
       aux_prefetch(p, nxt, row, nb * G2_BN, b, aux_fast);   // in flight while the main loop finishes
+      const int arow0 = mb * 2 * BM + int(rank) * BM + quarter * 32;
+      if (aux_tma && lane == 0) {
+#pragma unroll
+        for (int pre = 0; pre < 2; ++pre) {
+          if (nb * G2_BN + pre * 64 < p.N) {
+            mbar_expect_tx(&abar[pre], 4096);
+            tma_load_3d(abuf + pre * 4096, &tmAux, &abar[pre], nb * G2_BN + pre * 64, arow0, b);
+          }
+        }
+      }
       ok = __all_sync(0xffffffffu, mbar_wait(&tfull_bar[acc], acc_phase, abort_word));
       if (!ok) break;
       tc_fence_after();
@@ -389,12 +408,32 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         uint32_t r2[2][32];
         tmem_ld_32x32(taddr + uint32_t(c2 * 64), r2[0]);
         tmem_ld_32x32(taddr + uint32_t(c2 * 64 + 32), r2[1]);
+        uint4 av[8];
+        if (aux_tma) {
+          const int bi = c2 & 1;
+          ok = __all_sync(0xffffffffu, mbar_wait(&abar[bi], (aux_phase >> bi) & 1u, abort_word));
+          if (!ok) break;
+          aux_phase ^= 1u << bi;
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            av[q] = *reinterpret_cast<const uint4*>(abuf + bi * 4096 + lane * 128 + ((q ^ (lane & 7)) * 16));
+          const int ncol = nb * G2_BN + (c2 + 2) * 64;
+          if (c2 + 2 < G2_BN / 64 && ncol < p.N) {           // refill this buffer for the chunk after next
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              mbar_expect_tx(&abar[bi], 4096);
+              tma_load_3d(abuf + bi * 4096, &tmAux, &abar[bi], ncol, arow0, b);
+            }
+          }
+        }
         tmem_ld_wait();
 #pragma unroll
         for (int hc = 0; hc < 2; ++hc) {
           const int col0 = nb * G2_BN + (c2 * 2 + hc) * 32;
           if (col0 >= p.N) break;   // warp-uniform
-          epilogue_store_chunk(pt, r2[hc], row, col0, b, vec_ok, need_aux, cur.valid[hc] ? cur.v[hc] : nullptr);
+          const uint4* pre = aux_tma ? &av[hc * 4] : (cur.valid[hc] ? cur.v[hc] : nullptr);
+          epilogue_store_chunk(pt, r2[hc], row, col0, b, vec_ok, need_aux, pre);
         }
       }
       tc_fence_before();
@@ -420,7 +459,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
 template <int A_MN, int B_MN, int TP>
 static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream,
-                        const CUtensorMap& ta2, const TpParams& tp, const TpMaps& tpm) {
+                        const CUtensorMap& ta2, const TpParams& tp, const TpMaps& tpm, const CUtensorMap& taux) {
   auto kern = gemm2_bf16_kernel<A_MN, B_MN, TP>;
   static int max_clusters = 0;
   cudaLaunchConfig_t cfg = {};
@@ -452,7 +491,7 @@ static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
     clusters = gemm_clusters + tp.copy_clusters;
   }
   cfg.gridDim = dim3(2 * clusters);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, p, ta2, tp, tpm);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, p, ta2, tp, tpm, taux);
   count_launch();
   if (e != cudaSuccess) return -1000 - (int)e;
   return 0;
@@ -533,10 +572,18 @@ extern "C" int nga_gemm2_bf16(const void* A, const void* B, void* D, const void*
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   TpParams tp = {};
   static const TpMaps no_maps = {};
-  if (a_mn && b_mn) return launch_gemm2<1, 1, 0>(ta, tb, p, st, ta, tp, no_maps);
-  if (a_mn && !b_mn) return launch_gemm2<1, 0, 0>(ta, tb, p, st, ta, tp, no_maps);
-  if (!a_mn && b_mn) return launch_gemm2<0, 1, 0>(ta, tb, p, st, ta, tp, no_maps);
-  return launch_gemm2<0, 0, 0>(ta, tb, p, st, ta, tp, no_maps);
+  CUtensorMap taux = ta;
+  p.aux_tma = 0;
+  if ((epi == kEpiAxpby || epi == kEpiMulDRelu2) && !aux_fp32 && aux != nullptr && (ldaux & 7) == 0 && (sAux & 7) == 0 &&
+      (reinterpret_cast<uintptr_t>(aux) & 15) == 0 && N >= 64) {
+    rc = make_tmap_3d(&taux, aux, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, M, batch, ldaux * 2,
+                      (batch > 1 ? sAux : (long long)M * ldaux) * 2, 64, 32, true);
+    if (rc == 0) p.aux_tma = 1;
+  }
+  if (a_mn && b_mn) return launch_gemm2<1, 1, 0>(ta, tb, p, st, ta, tp, no_maps, taux);
+  if (a_mn && !b_mn) return launch_gemm2<1, 0, 0>(ta, tb, p, st, ta, tp, no_maps, taux);
+  if (!a_mn && b_mn) return launch_gemm2<0, 1, 0>(ta, tb, p, st, ta, tp, no_maps, taux);
+  return launch_gemm2<0, 0, 0>(ta, tb, p, st, ta, tp, no_maps, taux);
 }
 
 // Tensor-parallel GEMM fused with its collective (see TpParams).  A is K-major; B is K-major (b_mn = 0)
@@ -594,8 +641,9 @@ extern "C" int nga_tp_gemm_bf16(const void* A, const void* B, void* D, int M, in
     }
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (b_mn) return launch_gemm2<0, 1, 1>(ta, tb, p, st, ta2, tp, tpm);
-  return launch_gemm2<0, 0, 1>(ta, tb, p, st, ta2, tp, tpm);
+  p.aux_tma = 0;
+  if (b_mn) return launch_gemm2<0, 1, 1>(ta, tb, p, st, ta2, tp, tpm, ta);
+  return launch_gemm2<0, 0, 1>(ta, tb, p, st, ta2, tp, tpm, ta);
 }
 
 extern "C" int nga_tp_reduce_slots(const void* stage, const void* resid, void* out, int world, long long rows, int N,
