@@ -300,7 +300,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
         float pr[32], ds[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float e = exp2f(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_b[i]));
+          float e = ex2_fast(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_b[i]));
           if (need_mask) {
             const int q = q0 + chalf * 32 + i;
             if (key > q || q >= p.T || (p.window >= 0 && q - key > p.window)) e = 0.f;

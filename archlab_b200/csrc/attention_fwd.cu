@@ -246,7 +246,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
         float pr[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          pr[i] = exp2f(fmaf(__uint_as_float(sv[c][i]), p.scale_log2, -m_sub));
+          pr[i] = ex2_fast(fmaf(__uint_as_float(sv[c][i]), p.scale_log2, -m_sub));
           ps4[i & 3] += pr[i];
         }
         // 32 keys = 64 B = four 16-byte chunks of this row's 128-byte line in key block (c >> 1)

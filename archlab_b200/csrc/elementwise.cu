@@ -631,6 +631,19 @@ __global__ void gate_bwd_kernel(__nv_bfloat16* __restrict__ dn, const __nv_bfloa
 //   dl = gscale * (softmax(z) - onehot) * (1 - tanh^2)          written in place over the logits
 // |z| <= cap = 15, so exp(z) needs no running maximum in fp32.  target == -1 rows are ignored.
 // ------------------------------------------------------------------------------------------------
+// tanh through one ex2 and one rcp (about 1e-6 relative error); the libm tanhf / expf sequences made this
+// memory-sized kernel instruction-bound (two passes x 65536 columns x ~80 instructions per element).
+__device__ __forceinline__ float fast_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_tanh(float x) {
+  const float e = fast_ex2(x * 2.885390081777927f);      // exp(2x)
+  return 1.f - __fdividef(2.f, e + 1.f);
+}
+__device__ __forceinline__ float fast_exp(float x) { return fast_ex2(x * 1.4426950408889634f); }
+
 __global__ void __launch_bounds__(256)
 softcap_ce_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ targets,
                   float* __restrict__ loss_rows, float cap, float gscale, long long ld, int V) {
@@ -647,10 +660,10 @@ softcap_ce_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restric
     float v[8];
     ld8(l + c, v);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) sum += __expf(cap * tanhf(v[i] * inv_cap));
+    for (int i = 0; i < 8; ++i) sum += fast_exp(cap * fast_tanh(v[i] * inv_cap));
   }
   for (int c = V8 + threadIdx.x; c < V; c += 256)
-    sum += __expf(cap * tanhf(__bfloat162float(l[c]) * inv_cap));
+    sum += fast_exp(cap * fast_tanh(__bfloat162float(l[c]) * inv_cap));
   sum = warp_sum(sum);
   if (lane == 0) red[warp] = sum;
   __syncthreads();
@@ -673,15 +686,15 @@ softcap_ce_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restric
     ld8(l + c, v);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float th = tanhf(v[i] * inv_cap);
-      const float p = __expf(cap * th) * inv_total;
+      const float th = fast_tanh(v[i] * inv_cap);
+      const float p = fast_exp(cap * th) * inv_total;
       v[i] = gs * (p - ((long long)(c + i) == tgt ? 1.f : 0.f)) * (1.f - th * th);
     }
     st8(l + c, v);
   }
   for (int c = V8 + threadIdx.x; c < V; c += 256) {
-    const float th = tanhf(__bfloat162float(l[c]) * inv_cap);
-    const float p = __expf(cap * th) * inv_total;
+    const float th = fast_tanh(__bfloat162float(l[c]) * inv_cap);
+    const float p = fast_exp(cap * th) * inv_total;
     l[c] = __float2bfloat16(gs * (p - ((long long)c == tgt ? 1.f : 0.f)) * (1.f - th * th));
   }
 }

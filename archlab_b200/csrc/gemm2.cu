@@ -26,10 +26,10 @@ constexpr int G2_A_BYTES = BM * BK * 2;     // 16 KB: this CTA's 128 rows of A
 constexpr int G2_B_BYTES = 128 * BK * 2;    // 16 KB: this CTA's half of B
 constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
 constexpr int G2_OUT_OFFSET = G2_STAGES * G2_STAGE_BYTES;      // 4 warps x 2 staging tiles of 32 rows x 128 B
-constexpr int G2_OUT_BYTES = 4 * 2 * 4096;
+constexpr int G2_OUT_BYTES = 8 * 4096;    // 8 epilogue warps x one 32 x 64 staging tile (see below)
 constexpr int G2_BAR_OFFSET = G2_OUT_OFFSET + G2_OUT_BYTES;
-constexpr int G2_SMEM = G2_BAR_OFFSET + (2 * G2_STAGES + 4 + 8) * 8 + 16 + 1024;
-constexpr int G2_THREADS = 192;
+constexpr int G2_SMEM = G2_BAR_OFFSET + (2 * G2_STAGES + 4) * 8 + 16 + 1024;
+constexpr int G2_THREADS = 320;          // TMA warp, MMA warp, 8 epilogue warps
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -180,15 +180,14 @@ template <int A_MN, int B_MN, int TP>
 __global__ void __launch_bounds__(G2_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const GemmParams p, const __grid_constant__ CUtensorMap tmA2, const TpParams tp,
-                  const __grid_constant__ TpMaps tpm, const __grid_constant__ CUtensorMap tmAux) {
+                  const __grid_constant__ TpMaps tpm) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + G2_BAR_OFFSET);
   uint64_t* empty_bar = full_bar + G2_STAGES;
   uint64_t* tfull_bar = empty_bar + G2_STAGES;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint64_t* aux_bar = tempty_bar + 2;                   // [4 epilogue warps][2 staging buffers]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(aux_bar + 8);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty_bar + 2);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -211,9 +210,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 8);
+      mbar_init(&tempty_bar[a], 16);
     }
-    for (int a = 0; a < 8; ++a) mbar_init(&aux_bar[a], 1);
     *abort_word = 0;
     fence_mbar_init();
   }
@@ -323,20 +321,16 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------------ epilogue warps (both CTAs)
+    // eight epilogue warps: TMEM lane quarter = warp % 4 (hardware rule), and the two warps of a quarter
+    // split the 256 accumulator columns (the aux epilogues were issue-bound with four warps)
     const int quarter = warp & 3;
+    const int chalf = (warp - 2) >> 2;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     const bool vec_ok = epilogue_vec_ok(p);
     const bool need_aux = (p.epi == kEpiAxpby || p.epi == kEpiMulDRelu2);
-    // With aux_tma the residual / activation operand of the epilogue arrives through TMA into this warp's
-    // two staging tiles (32 rows x 64 columns, 128-byte swizzle), two chunks ahead of its use: coalesced,
-    // asynchronous, and off the load/store unit, instead of one 16-byte row-strided load per lane.
-    const bool aux_tma = p.aux_tma != 0 && need_aux && !(TP && (tp.mode & kTpScatter));
-    const bool aux_fast = aux_prefetchable(p) && !aux_tma;
-    uint64_t* abar = aux_bar + quarter * 2;
-    uint8_t* abuf = smem + G2_OUT_OFFSET + quarter * 8192;
-    uint32_t aux_phase = 0;                               // bit i: parity of staging buffer i
+    const bool aux_fast = aux_prefetchable(p);
     uint32_t out_cnt = 0;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int b, mb, nb, otile, kb0, kb1;
@@ -351,17 +345,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         pt.row_shift = (long long)(tp.rank - owner) * tp.rows_per_rank;
       }
       AuxPre nxt;
-      aux_prefetch(p, nxt, row, nb * G2_BN, b, aux_fast);   // in flight while the main loop finishes
-      const int arow0 = mb * 2 * BM + int(rank) * BM + quarter * 32;
-      if (aux_tma && lane == 0) {
-#pragma unroll
-        for (int pre = 0; pre < 2; ++pre) {
-          if (nb * G2_BN + pre * 64 < p.N) {
-            mbar_expect_tx(&abar[pre], 4096);
-            tma_load_3d(abuf + pre * 4096, &tmAux, &abar[pre], nb * G2_BN + pre * 64, arow0, b);
-          }
-        }
-      }
+      aux_prefetch(p, nxt, row, nb * G2_BN + chalf * 128, b, aux_fast);   // in flight while the main loop finishes
       ok = __all_sync(0xffffffffu, mbar_wait(&tfull_bar[acc], acc_phase, abort_word));
       if (!ok) break;
       tc_fence_after();
@@ -371,15 +355,15 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int owner = (mb * 2 * BM) / tp.rows_per_rank;
         const int row0 = mb * 2 * BM + int(rank) * BM + quarter * 32 + int(pt.row_shift);
 #pragma unroll 1
-        for (int c2 = 0; c2 < G2_BN / 64; ++c2) {
+        for (int c2 = chalf * 2; c2 < chalf * 2 + 2; ++c2) {
           const int col0 = nb * G2_BN + c2 * 64;
           if (col0 >= p.N) break;   // warp-uniform
           uint32_t r2[2][32];
           tmem_ld_32x32(taddr + uint32_t(c2 * 64), r2[0]);
           tmem_ld_32x32(taddr + uint32_t(c2 * 64 + 32), r2[1]);
           tmem_ld_wait();
-          uint8_t* buf = smem + G2_OUT_OFFSET + (quarter * 2 + int(out_cnt & 1u)) * 4096;
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          uint8_t* buf = smem + G2_OUT_OFFSET + (chalf * 4 + quarter) * 4096;      // one staging tile per warp
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           __syncwarp();
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
@@ -401,39 +385,19 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
       } else
 #pragma unroll 1
-      for (int c2 = 0; c2 < G2_BN / 64; ++c2) {
+      for (int c2 = chalf * 2; c2 < chalf * 2 + 2; ++c2) {
         if (nb * G2_BN + c2 * 64 >= p.N) break;   // warp-uniform
         const AuxPre cur = nxt;
-        if (c2 + 1 < G2_BN / 64) aux_prefetch(p, nxt, row, nb * G2_BN + (c2 + 1) * 64, b, aux_fast);
+        if (c2 + 1 < chalf * 2 + 2) aux_prefetch(p, nxt, row, nb * G2_BN + (c2 + 1) * 64, b, aux_fast);
         uint32_t r2[2][32];
         tmem_ld_32x32(taddr + uint32_t(c2 * 64), r2[0]);
         tmem_ld_32x32(taddr + uint32_t(c2 * 64 + 32), r2[1]);
-        uint4 av[8];
-        if (aux_tma) {
-          const int bi = c2 & 1;
-          ok = __all_sync(0xffffffffu, mbar_wait(&abar[bi], (aux_phase >> bi) & 1u, abort_word));
-          if (!ok) break;
-          aux_phase ^= 1u << bi;
-#pragma unroll
-          for (int q = 0; q < 8; ++q)
-            av[q] = *reinterpret_cast<const uint4*>(abuf + bi * 4096 + lane * 128 + ((q ^ (lane & 7)) * 16));
-          const int ncol = nb * G2_BN + (c2 + 2) * 64;
-          if (c2 + 2 < G2_BN / 64 && ncol < p.N) {           // refill this buffer for the chunk after next
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              mbar_expect_tx(&abar[bi], 4096);
-              tma_load_3d(abuf + bi * 4096, &tmAux, &abar[bi], ncol, arow0, b);
-            }
-          }
-        }
         tmem_ld_wait();
 #pragma unroll
         for (int hc = 0; hc < 2; ++hc) {
           const int col0 = nb * G2_BN + (c2 * 2 + hc) * 32;
           if (col0 >= p.N) break;   // warp-uniform
-          const uint4* pre = aux_tma ? &av[hc * 4] : (cur.valid[hc] ? cur.v[hc] : nullptr);
-          epilogue_store_chunk(pt, r2[hc], row, col0, b, vec_ok, need_aux, pre);
+          epilogue_store_chunk(pt, r2[hc], row, col0, b, vec_ok, need_aux, cur.valid[hc] ? cur.v[hc] : nullptr);
         }
       }
       tc_fence_before();
@@ -459,7 +423,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
 template <int A_MN, int B_MN, int TP>
 static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream,
-                        const CUtensorMap& ta2, const TpParams& tp, const TpMaps& tpm, const CUtensorMap& taux) {
+                        const CUtensorMap& ta2, const TpParams& tp, const TpMaps& tpm) {
   auto kern = gemm2_bf16_kernel<A_MN, B_MN, TP>;
   static int max_clusters = 0;
   cudaLaunchConfig_t cfg = {};
@@ -491,7 +455,7 @@ static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
     clusters = gemm_clusters + tp.copy_clusters;
   }
   cfg.gridDim = dim3(2 * clusters);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, p, ta2, tp, tpm, taux);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, p, ta2, tp, tpm);
   count_launch();
   if (e != cudaSuccess) return -1000 - (int)e;
   return 0;
@@ -572,18 +536,10 @@ extern "C" int nga_gemm2_bf16(const void* A, const void* B, void* D, const void*
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   TpParams tp = {};
   static const TpMaps no_maps = {};
-  CUtensorMap taux = ta;
-  p.aux_tma = 0;
-  if ((epi == kEpiAxpby || epi == kEpiMulDRelu2) && !aux_fp32 && aux != nullptr && (ldaux & 7) == 0 && (sAux & 7) == 0 &&
-      (reinterpret_cast<uintptr_t>(aux) & 15) == 0 && N >= 64) {
-    rc = make_tmap_3d(&taux, aux, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, M, batch, ldaux * 2,
-                      (batch > 1 ? sAux : (long long)M * ldaux) * 2, 64, 32, true);
-    if (rc == 0) p.aux_tma = 1;
-  }
-  if (a_mn && b_mn) return launch_gemm2<1, 1, 0>(ta, tb, p, st, ta, tp, no_maps, taux);
-  if (a_mn && !b_mn) return launch_gemm2<1, 0, 0>(ta, tb, p, st, ta, tp, no_maps, taux);
-  if (!a_mn && b_mn) return launch_gemm2<0, 1, 0>(ta, tb, p, st, ta, tp, no_maps, taux);
-  return launch_gemm2<0, 0, 0>(ta, tb, p, st, ta, tp, no_maps, taux);
+  if (a_mn && b_mn) return launch_gemm2<1, 1, 0>(ta, tb, p, st, ta, tp, no_maps);
+  if (a_mn && !b_mn) return launch_gemm2<1, 0, 0>(ta, tb, p, st, ta, tp, no_maps);
+  if (!a_mn && b_mn) return launch_gemm2<0, 1, 0>(ta, tb, p, st, ta, tp, no_maps);
+  return launch_gemm2<0, 0, 0>(ta, tb, p, st, ta, tp, no_maps);
 }
 
 // Tensor-parallel GEMM fused with its collective (see TpParams).  A is K-major; B is K-major (b_mn = 0)
@@ -641,9 +597,8 @@ extern "C" int nga_tp_gemm_bf16(const void* A, const void* B, void* D, int M, in
     }
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  p.aux_tma = 0;
-  if (b_mn) return launch_gemm2<0, 1, 1>(ta, tb, p, st, ta2, tp, tpm, ta);
-  return launch_gemm2<0, 0, 1>(ta, tb, p, st, ta2, tp, tpm, ta);
+  if (b_mn) return launch_gemm2<0, 1, 1>(ta, tb, p, st, ta2, tp, tpm);
+  return launch_gemm2<0, 0, 1>(ta, tb, p, st, ta2, tp, tpm);
 }
 
 extern "C" int nga_tp_reduce_slots(const void* stage, const void* resid, void* out, int world, long long rows, int N,

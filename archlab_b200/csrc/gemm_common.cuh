@@ -22,7 +22,6 @@ struct GemmParams {
   int splits;                    // split-K factor (> 1 only with kEpiAtomicAdd)
   int* status;
   long long row_shift;           // added to the row index when addressing D (tensor-parallel staging slots)
-  int aux_tma;                   // pair kernel: the bf16 aux operand is staged through shared memory by TMA
 };
 
 // Tensor-parallel fusion of the CTA-pair GEMM with its collective over NVLink peer memory.
