@@ -1,0 +1,378 @@
+"""Mesh training entry: ``torchrun -m archlab_b200.train.mesh_train --model qwen35_4b --tp 2 ...``.
+
+Ranks form a (pipeline, data, context, tensor) mesh with the tensor index fastest, so that a tensor
+group sits on neighbouring GPUs.  Qwen3.5-family models run as ``Qwen35TP`` (tensor + sequence
+parallel layers over the fused all-gather->GEMM / GEMM->reduce-scatter kernels, zig-zag context
+parallel attention, layer-range pipeline stages under the 1F1B schedule); DeepSeek-V4.1-family models
+run with their routed experts split over the expert group (which spans the data x context ranks).
+Gradients are averaged over the data group (and summed over tensor / context groups for replicated
+parameters) and applied with fp32-master AdamW.  One JSON line per step goes to
+``<run-dir>/metrics_rank0.jsonl``.
+
+Plays the role of the reference's Megatron launches (``src/archlab/megatron/qwen38_flash_next_config.py:
+140-260`` renders the parallel sizes; ``training/backends.py`` hands them to the trainer).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import time
+import zlib
+from dataclasses import dataclass
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+from ..parallel import pp as ppar
+
+
+@dataclass(frozen=True)
+class Mesh:
+    rank: int
+    world: int
+    tp: int
+    cp: int
+    dp: int
+    pp: int
+
+    @property
+    def tp_i(self):
+        return self.rank % self.tp
+
+    @property
+    def cp_i(self):
+        return self.rank // self.tp % self.cp
+
+    @property
+    def dp_i(self):
+        return self.rank // (self.tp * self.cp) % self.dp
+
+    @property
+    def pp_i(self):
+        return self.rank // (self.tp * self.cp * self.dp)
+
+    def rank_of(self, *, tp_i=None, cp_i=None, dp_i=None, pp_i=None) -> int:
+        t = self.tp_i if tp_i is None else tp_i
+        c = self.cp_i if cp_i is None else cp_i
+        d = self.dp_i if dp_i is None else dp_i
+        p = self.pp_i if pp_i is None else pp_i
+        return ((p * self.dp + d) * self.cp + c) * self.tp + t
+
+    def axis_ranks(self, axis: str) -> list[list[int]]:
+        """Every group along ``axis`` (all ranks must create all groups, in this order)."""
+        sizes = {"tp": self.tp, "cp": self.cp, "dp": self.dp, "pp": self.pp}
+        others = [a for a in ("pp", "dp", "cp", "tp") if a != axis]
+        groups = []
+
+        def rec(fixed, rest):
+            if not rest:
+                groups.append([Mesh.rank_of(self, **{f"{axis}_i": i}, **{f"{k}_i": v for k, v in fixed.items()})
+                               for i in range(sizes[axis])])
+                return
+            for v in range(sizes[rest[0]]):
+                rec({**fixed, rest[0]: v}, rest[1:])
+
+        rec({}, others)
+        return groups
+
+    def dpcp_ranks(self) -> list[list[int]]:
+        """Groups over data x context (the expert-parallel / gradient-averaging span for experts)."""
+        return [[self.rank_of(tp_i=t, pp_i=p, dp_i=d, cp_i=c) for d in range(self.dp) for c in range(self.cp)]
+                for p in range(self.pp) for t in range(self.tp)]
+
+
+def build_mesh(rank: int, world: int, tp: int, pp: int, cp: int) -> Mesh:
+    mp = tp * pp * cp
+    if world % mp:
+        raise ValueError("world size must be divisible by tp x pp x cp")
+    return Mesh(rank, world, tp, cp, world // mp, pp)
+
+
+def make_groups(mesh: Mesh) -> dict:
+    out = {}
+    for axis in ("tp", "cp", "dp", "pp"):
+        for ranks in mesh.axis_ranks(axis):
+            g = dist.new_group(ranks) if len(ranks) > 1 else None
+            if mesh.rank in ranks:
+                out[axis] = g
+    for ranks in mesh.dpcp_ranks():
+        g = dist.new_group(ranks) if len(ranks) > 1 else None
+        if mesh.rank in ranks:
+            out["dpcp"] = g
+    return out
+
+
+def parse_args(argv=None):
+    ap = argparse.ArgumentParser(description="tensor / pipeline / context / expert / data parallel training")
+    ap.add_argument("--model", default="qwen35_tiny")
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--pp", type=int, default=1)
+    ap.add_argument("--cp", type=int, default=1)
+    ap.add_argument("--ep", type=int, default=1)
+    ap.add_argument("--sequence-parallel", action="store_true")
+    ap.add_argument("--micro-batch", type=int, default=1)
+    ap.add_argument("--global-batch", type=int, default=8)
+    ap.add_argument("--seq-len", type=int, default=8192)
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8_block", "nvfp4"])
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--lr", type=float, default=3e-4)
+    ap.add_argument("--weight-decay", type=float, default=0.1)
+    ap.add_argument("--grad-clip", type=float, default=1.0)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--run-dir", default="runs/mesh")
+    ap.add_argument("--n-layer", type=int, default=0, help="override the preset's depth (0 keeps it)")
+    return ap.parse_args(argv)
+
+
+# ------------------------------------------------------------------------------------------------
+# models
+# ------------------------------------------------------------------------------------------------
+def _qwen35_config(name: str, a):
+    from ..models.qwen35 import Qwen35Config
+
+    kw = {"sequence_len": a.seq_len}
+    if a.n_layer:
+        kw["n_layer"] = a.n_layer
+    if name == "qwen35_tiny":
+        return Qwen35Config.tiny(**kw)
+    if name == "qwen35_tiny_dense":
+        return Qwen35Config.tiny(simplicial_every=0, **kw)
+    if name == "qwen35_4b":
+        return Qwen35Config(**kw)
+    if name == "qwen35_4b_dense":
+        return Qwen35Config(simplicial_every=0, **kw)
+    raise ValueError(f"unknown model {name}")
+
+
+class _Job:
+    """Model + how one micro-batch runs on this rank.  ``stage(x, (ids, labels))`` follows the contract
+    of ``parallel.pp.run_1f1b``."""
+
+    def __init__(self, a, mesh: Mesh, groups: dict, device):
+        self.mesh, self.groups, self.device = mesh, groups, device
+        fam = a.model.split("_")[0]
+        if fam == "qwen35":
+            from ..models.qwen35_tp import Qwen35TP
+
+            cfg = _qwen35_config(a.model, a)
+            tpg = None
+            if mesh.tp > 1 and device.type == "cuda":
+                from ..parallel.tp import TPGroup
+
+                rows = a.seq_len // mesh.cp // mesh.tp
+                widest = max(cfg.intermediate_size * 2 // mesh.tp, (cfg.n_heads + 4 * cfg.n_kv_heads) * cfg.head_dim // mesh.tp,
+                             cfg.hidden_size)
+                tpg = TPGroup(rows, max(cfg.hidden_size, cfg.intermediate_size // mesh.tp), widest, device, groups["tp"])
+            stage_layers = ppar.split_layers(cfg.n_layer, mesh.pp)[mesh.pp_i]
+            torch.manual_seed(a.seed)                         # same init stream on every rank of a stage
+            self.model = Qwen35TP(cfg, tpg, world=mesh.tp, rank=mesh.tp_i, group=groups["tp"], layer_range=stage_layers,
+                                  cp=(mesh.cp, mesh.cp_i, groups["cp"])).to(device)
+            self._init_qwen(a.seed)
+            self.act_shape = self.model.act_shape(a.seq_len)
+            self.vocab = cfg.vocab_size
+            self.kind = "tp"
+        elif fam == "v41":
+            from ..models.deepseek_v41 import V41Config, V41LM
+
+            if mesh.tp > 1 or mesh.pp > 1 or mesh.cp > 1:
+                raise ValueError("the V4.1 family runs under data + expert parallelism here")
+            kw = {"sequence_len": a.seq_len, **({"n_layer": a.n_layer} if a.n_layer else {})}
+            cfg = V41Config.tiny(**kw) if a.model == "v41_tiny" else V41Config(**kw)
+            ep_group = groups["dp"] if a.ep > 1 else None
+            if a.ep > 1 and a.ep != mesh.dp:
+                raise ValueError("expert parallel size must equal the data parallel size in this trainer")
+            torch.manual_seed(a.seed)
+            self.model = V41LM(cfg, ep_group).to(device)
+            self.model.init_weights()
+            if ep_group is not None:                          # shared weights agree; every rank keeps its own experts
+                for n, p in self.model.named_parameters():
+                    if ".experts." not in n:
+                        dist.broadcast(p.data, mesh.rank_of(dp_i=0), group=ep_group)
+            self.act_shape, self.vocab, self.kind = None, cfg.vocab_size, "ep"
+        else:
+            raise ValueError(f"unknown model family {fam}")
+        if device.type == "cuda":
+            self.model.to(torch.bfloat16)
+
+    def _init_qwen(self, seed: int) -> None:
+        g = torch.Generator().manual_seed(seed)
+        for name, p in self.model.named_parameters():
+            if p.dim() < 2:
+                continue
+            # tensor-parallel shards of one matrix draw from different streams; replicated ones agree
+            shard = self.mesh.tp_i if getattr(p, "tensor_model_parallel", False) else 0
+            g.manual_seed(zlib.crc32(f"{seed}/{name}/{shard}".encode()))
+            p.data.copy_(torch.randn(p.shape, generator=g).mul_(0.02).to(p.dtype))
+
+    def expert_params(self) -> set:
+        if self.kind != "ep" or not hasattr(self.model.layers[0].ffn, "local_experts"):
+            return set()
+        return {p for n, p in self.model.named_parameters() if ".experts." in n}
+
+    def stage(self, x, mb):
+        ids, labels = mb
+        if self.kind == "tp":
+            return self.model(ids, labels, x)
+        return self.model(ids, labels)
+
+
+class MasterAdamW:
+    """AdamW on fp32 master copies; the model keeps its compute dtype."""
+
+    def __init__(self, params, lr, weight_decay, betas=(0.9, 0.95), eps=1e-8):
+        self.params = [p for p in params if p.requires_grad]
+        self.master = [p.detach().float().clone() for p in self.params]
+        self.m = [torch.zeros_like(w) for w in self.master]
+        self.v = [torch.zeros_like(w) for w in self.master]
+        self.lr, self.wd, self.betas, self.eps, self.t = lr, weight_decay, betas, eps, 0
+
+    @torch.no_grad()
+    def step(self, lr_scale: float = 1.0, grad_scale: float = 1.0):
+        self.t += 1
+        b1, b2 = self.betas
+        grads = [(p.grad if p.grad is not None else torch.zeros_like(p)).float() * grad_scale for p in self.params]
+        torch._foreach_mul_(self.m, b1)
+        torch._foreach_add_(self.m, grads, alpha=1 - b1)
+        torch._foreach_mul_(self.v, b2)
+        torch._foreach_addcmul_(self.v, grads, grads, value=1 - b2)
+        lr = self.lr * lr_scale
+        c1, c2 = 1 - b1 ** self.t, 1 - b2 ** self.t
+        decay = [w for w, p in zip(self.master, self.params) if p.dim() >= 2]
+        if decay and self.wd:
+            torch._foreach_mul_(decay, 1 - lr * self.wd)
+        den = torch._foreach_sqrt(self.v)
+        torch._foreach_div_(den, c2 ** 0.5)
+        torch._foreach_add_(den, self.eps)
+        torch._foreach_addcdiv_(self.master, self.m, den, value=-lr / c1)
+        for p, w in zip(self.params, self.master):
+            p.copy_(w)
+            p.grad = None
+
+
+# ------------------------------------------------------------------------------------------------
+# step
+# ------------------------------------------------------------------------------------------------
+def _allreduce(t, group, op=dist.ReduceOp.SUM):
+    if group is not None:
+        dist.all_reduce(t, op=op, group=group)
+
+
+def reduce_gradients(job: _Job, scale: float) -> float:
+    """Sum partial gradients over the mesh, then return the global gradient norm (after ``scale``)."""
+    mesh, g = job.mesh, job.groups
+    experts = job.expert_params()
+    sq_sharded = torch.zeros((), device=job.device)
+    sq_repl = torch.zeros((), device=job.device)
+    for p in job.model.parameters():
+        if p.grad is None:
+            continue
+        sharded = getattr(p, "tensor_model_parallel", False)
+        if job.kind == "tp":
+            if not sharded:
+                _allreduce(p.grad, g["tp"])
+            _allreduce(p.grad, g["cp"])
+            _allreduce(p.grad, g["dp"])
+        elif p not in experts:
+            _allreduce(p.grad, g["dp"])
+        n2 = p.grad.float().pow(2).sum()
+        if sharded or p in experts:
+            sq_sharded += n2
+        else:
+            sq_repl += n2
+    _allreduce(sq_sharded, g["tp"] if job.kind == "tp" else (g["dp"] if experts else None))
+    total = sq_sharded + sq_repl
+    _allreduce(total, g["pp"])
+    return float(total.sqrt()) * scale
+
+
+def train(a, *, on_step=None) -> list[float]:
+    rank, world, device = _init_distributed()
+    mesh = build_mesh(rank, world, a.tp, a.pp, a.cp)
+    if a.global_batch % (a.micro_batch * mesh.dp):
+        raise SystemExit("global batch must be a multiple of micro batch x data parallel size")
+    if a.micro_batch != 1 and a.model.startswith("qwen35"):
+        raise SystemExit("sequence-parallel models take one sequence per micro-batch")
+    accum = a.global_batch // (a.micro_batch * mesh.dp)
+    groups = make_groups(mesh) if world > 1 else {k: None for k in ("tp", "cp", "dp", "pp", "dpcp")}
+    job = _Job(a, mesh, groups, device)
+    opt = MasterAdamW(job.model.parameters(), a.lr, a.weight_decay)
+    links = ppar.StageLinks(mesh.pp_i, mesh.pp, mesh.rank_of(pp_i=mesh.pp_i - 1) if mesh.pp_i else None,
+                            mesh.rank_of(pp_i=mesh.pp_i + 1) if mesh.pp_i + 1 < mesh.pp else None)
+    run_dir = Path(os.environ.get(a.run_dir[4:], "runs/mesh") if a.run_dir.startswith("env:") else a.run_dir)
+    log = None
+    if rank == 0:
+        run_dir.mkdir(parents=True, exist_ok=True)
+        (run_dir / "config.json").write_text(json.dumps({"args": vars(a), "world_size": world, "data_parallel": mesh.dp,
+                                                         "grad_accum_steps": accum}, indent=2))
+        log = open(run_dir / "metrics_rank0.jsonl", "a")
+    from ..data.synthetic import ZipfTokens
+
+    # every rank of a (tensor, context, pipeline) slice reads the data of its data-parallel index
+    gen = ZipfTokens(job.vocab, a.seq_len, a.micro_batch * accum, seed=a.seed, rank=mesh.dp_i, pin=False)
+    act_dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
+    losses = []
+    scale = 1.0 / (accum * mesh.dp)
+    for step in range(a.steps):
+        t0 = time.perf_counter()
+        block = gen.block(step).to(device).long()              # [micro*accum, T+1]
+        mbs = [(block[i * a.micro_batch:(i + 1) * a.micro_batch, :-1], block[i * a.micro_batch:(i + 1) * a.micro_batch, 1:])
+               for i in range(accum)]
+        if mesh.pp > 1:
+            loss = ppar.run_1f1b(links, job.stage, mbs, act_shape=job.act_shape, act_dtype=act_dtype, device=device)
+        else:
+            loss = torch.zeros((), device=device)
+            for mb in mbs:
+                l = job.stage(None, mb)
+                l.backward()
+                loss = loss + l.detach()
+        gnorm = reduce_gradients(job, scale)
+        clip = min(1.0, a.grad_clip / (gnorm + 1e-6)) if a.grad_clip > 0 else 1.0
+        warm = min(1.0, (step + 1) / max(1, min(10, a.steps // 10)))
+        opt.step(lr_scale=warm, grad_scale=scale * clip)
+        # mean loss of the step: partial sums live on the last stage's tensor/context ranks
+        loss = loss.float() * scale
+        if job.kind == "tp":
+            _allreduce(loss, groups["tp"])
+            _allreduce(loss, groups["cp"])
+        _allreduce(loss, groups["dp"])
+        _allreduce(loss, groups["pp"])
+        if device.type == "cuda":
+            torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        losses.append(float(loss))
+        if log is not None:
+            log.write(json.dumps({"step": step + 1, "loss": losses[-1], "grad_norm": gnorm, "step_seconds": dt,
+                                  "tokens_per_second": a.global_batch * a.seq_len / dt,
+                                  "parallelism": f"tp{mesh.tp} pp{mesh.pp} cp{mesh.cp} ep{a.ep} dp{mesh.dp}"}) + "\n")
+            log.flush()
+        if on_step is not None:
+            on_step(step, losses[-1])
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return losses
+
+
+def _init_distributed():
+    if "RANK" not in os.environ:
+        return 0, 1, torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    rank, local = int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", 0))
+    if torch.cuda.is_available():
+        torch.cuda.set_device(local)
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return rank, dist.get_world_size(), torch.device("cuda", local)
+    if not dist.is_initialized():
+        dist.init_process_group("gloo")
+    return rank, dist.get_world_size(), torch.device("cpu")
+
+
+def main(argv=None) -> int:
+    train(parse_args(argv))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
