@@ -16,6 +16,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops.attention import causal_attention
 from ..ops import delta_rule
 from .blocks import rms_norm
 
@@ -121,8 +122,8 @@ class GlobalGatedAttention(nn.Module):
         B, T, E = x.shape
         q, k, v = self.qkv(x).view(B, T, 3, self.h, self.d).unbind(2)
         q, k = rms_norm(q), rms_norm(k)
-        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
-        return self.o_proj(o.transpose(1, 2).reshape(B, T, E) * torch.sigmoid(self.gate(x)))
+        o = causal_attention(q, k, v)
+        return self.o_proj(o.reshape(B, T, E) * torch.sigmoid(self.gate(x)))
 
 
 class AttnResRead(nn.Module):

@@ -21,6 +21,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import local_attention as la
+from ..ops.attention import causal_attention
 from ..ops import simplicial as sx
 from .blocks import GroupRMSNorm, RMSNorm, apply_rope, rope_tables, so3_chunk_rope
 
@@ -86,9 +87,7 @@ class DenseAttention(nn.Module):
             k2 = apply_rope(self.k2_norm(kv[2]), cos, sin)
             o = sx.simplicial_attention(q, k1, k2, kv[1], kv[3], c.simplicial_w1, c.simplicial_w2)
         else:
-            rep = c.n_heads // c.n_kv_heads
-            o = F.scaled_dot_product_attention(q.transpose(1, 2), k1.repeat_interleave(rep, 2).transpose(1, 2),
-                                               kv[1].repeat_interleave(rep, 2).transpose(1, 2), is_causal=True).transpose(1, 2)
+            o = causal_attention(q, k1, kv[1])
         return self.o(o.reshape(B, T, q_w).to(x.dtype))
 
 

@@ -16,6 +16,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops import simplicial as sx
+from ..ops.attention import causal_attention
 from ..parallel import cp as cpar
 from ..parallel.tp_layers import ColumnParallelLinear, RowParallelLinear, TPMLP
 from .blocks import RMSNorm, apply_rope, rope_tables
@@ -53,9 +54,7 @@ class TPAttention(nn.Module):
         elif self.cp_world > 1:
             o = cpar.cp_causal_attention(q, k1, kvs[1], rank=self.cp_rank, world=self.cp_world, group=self.cp_group)
         else:
-            rep = self.h // self.kv
-            o = F.scaled_dot_product_attention(q.transpose(1, 2), k1.repeat_interleave(rep, 2).transpose(1, 2),
-                                               kvs[1].repeat_interleave(rep, 2).transpose(1, 2), is_causal=True).transpose(1, 2)
+            o = causal_attention(q, k1, kvs[1])
         return self.o(o.reshape(T, self.h * D).to(y.dtype), resid)
 
 

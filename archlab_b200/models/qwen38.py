@@ -15,6 +15,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops.attention import causal_attention
 from ..ops import delta_rule
 from . import moe
 from .blocks import NgramHash, OwnerShardedEmbedding, RMSNorm, apply_rope, rope_tables
@@ -186,14 +187,14 @@ class GatedAttention(nn.Module):
         v = self.v(x).view(B, T, self.kv, self.d)
         q = apply_rope(self.q_norm(q), cos, sin, rot_dim=self.rot)
         k = apply_rope(self.k_norm(k), cos, sin, rot_dim=self.rot)
-        rep = self.h // self.kv
-        k, v = k.repeat_interleave(rep, 2), v.repeat_interleave(rep, 2)
         if self.indexer is not None and T > self.indexer.top_k:
+            rep = self.h // self.kv
+            k, v = k.repeat_interleave(rep, 2), v.repeat_interleave(rep, 2)
             mask = self.indexer(x.detach()).unsqueeze(1)
-            o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=mask)
+            o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=mask).transpose(1, 2)
         else:
-            o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=True)
-        o = o.transpose(1, 2) * torch.sigmoid(gate)
+            o = causal_attention(q, k, v)
+        o = o * torch.sigmoid(gate)
         return self.out(o.reshape(B, T, self.h * self.d))
 
 

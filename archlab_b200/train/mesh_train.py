@@ -139,6 +139,9 @@ def _qwen35_config(name: str, a):
         return Qwen35Config.tiny(**kw)
     if name == "qwen35_tiny_dense":
         return Qwen35Config.tiny(simplicial_every=0, **kw)
+    if name == "qwen35_small":
+        return Qwen35Config(**{**dict(vocab_size=32768, n_layer=4, hidden_size=1024, n_heads=8, n_kv_heads=4, intermediate_size=3072,
+                                      simplicial_w1=16, simplicial_w2=64), **kw})
     if name == "qwen35_4b":
         return Qwen35Config(**kw)
     if name == "qwen35_4b_dense":
@@ -162,9 +165,8 @@ class _Job:
                 from ..parallel.tp import TPGroup
 
                 rows = a.seq_len // mesh.cp // mesh.tp
-                widest = max(cfg.intermediate_size * 2 // mesh.tp, (cfg.n_heads + 4 * cfg.n_kv_heads) * cfg.head_dim // mesh.tp,
-                             cfg.hidden_size)
-                tpg = TPGroup(rows, max(cfg.hidden_size, cfg.intermediate_size // mesh.tp), widest, device, groups["tp"])
+                # gathered operands and reduce-scattered outputs are always ``hidden_size`` wide
+                tpg = TPGroup(rows, cfg.hidden_size, cfg.hidden_size, device, groups["tp"])
             stage_layers = ppar.split_layers(cfg.n_layer, mesh.pp)[mesh.pp_i]
             torch.manual_seed(a.seed)                         # same init stream on every rank of a stage
             self.model = Qwen35TP(cfg, tpg, world=mesh.tp, rank=mesh.tp_i, group=groups["tp"], layer_range=stage_layers,
