@@ -261,32 +261,51 @@ def _allreduce(t, group, op=dist.ReduceOp.SUM):
         dist.all_reduce(t, op=op, group=group)
 
 
-def reduce_gradients(job: _Job, scale: float) -> float:
-    """Sum partial gradients over the mesh, then return the global gradient norm (after ``scale``)."""
-    mesh, g = job.mesh, job.groups
-    experts = job.expert_params()
-    sq_sharded = torch.zeros((), device=job.device)
-    sq_repl = torch.zeros((), device=job.device)
-    for p in job.model.parameters():
-        if p.grad is None:
-            continue
-        sharded = getattr(p, "tensor_model_parallel", False)
+class MeshOptimizer:
+    """ZeRO-sharded AdamW over the data group for everything that is averaged over it, plus a local
+    AdamW for routed experts (each data rank owns different experts)."""
+
+    def __init__(self, job: _Job, lr: float, weight_decay: float):
+        from ..optim.zero import ZeroAdamW
+
+        self.job = job
+        experts = job.expert_params()
+        shared = [p for p in job.model.parameters() if p not in experts and p.requires_grad]
+        is_repl = lambda p: not getattr(p, "tensor_model_parallel", False)
+        shared.sort(key=lambda p: (p.dim() < 2, not is_repl(p)))      # decayed replicated | decayed sharded | plain
+        self.zero = ZeroAdamW(shared, lr=lr, weight_decay=weight_decay, group=job.groups["dp"])
+        self.experts = MasterAdamW(list(experts), lr, weight_decay) if experts else None
+        repl = [p for p in shared if is_repl(p)]
+        dec = [p for p in repl if p.dim() >= 2]
+        plain = [p for p in repl if p.dim() < 2]
+        self.repl_ranges = [self.zero.range_of(g) for g in (dec, plain) if g]
+        self.zero.zero_grad()
+
+    def reduce_and_norm(self, scale: float) -> float:
+        job, g, z = self.job, self.job.groups, self.zero
         if job.kind == "tp":
-            if not sharded:
-                _allreduce(p.grad, g["tp"])
-            _allreduce(p.grad, g["cp"])
-            _allreduce(p.grad, g["dp"])
-        elif p not in experts:
-            _allreduce(p.grad, g["dp"])
-        n2 = p.grad.float().pow(2).sum()
-        if sharded or p in experts:
-            sq_sharded += n2
-        else:
-            sq_repl += n2
-    _allreduce(sq_sharded, g["tp"] if job.kind == "tp" else (g["dp"] if experts else None))
-    total = sq_sharded + sq_repl
-    _allreduce(total, g["pp"])
-    return float(total.sqrt()) * scale
+            for a, b in self.repl_ranges:                              # every tensor rank saw different rows
+                _allreduce(z.flat_g[a:b], g["tp"])
+            _allreduce(z.flat_g, g["cp"])
+        z.reduce_gradients()
+        sq_all, sq_repl = z.grad_sq_norm(), z.grad_sq_norm(self.repl_ranges)
+        both = torch.stack([sq_all, sq_repl])
+        _allreduce(both, g["dp"])
+        sharded = both[0] - both[1]
+        if self.experts is not None:
+            e = torch.stack([p.grad.float().pow(2).sum() for p in self.experts.params if p.grad is not None]).sum()
+            _allreduce(e, g["dp"])
+            sharded = sharded + e
+        if job.kind == "tp":
+            _allreduce(sharded, g["tp"])
+        total = sharded + both[1]
+        _allreduce(total, g["pp"])
+        return float(total.sqrt()) * scale
+
+    def step(self, lr_scale: float, grad_scale: float) -> None:
+        self.zero.step(lr_scale=lr_scale, grad_scale=grad_scale)
+        if self.experts is not None:
+            self.experts.step(lr_scale=lr_scale, grad_scale=grad_scale)
 
 
 def train(a, *, on_step=None) -> list[float]:
@@ -299,7 +318,7 @@ def train(a, *, on_step=None) -> list[float]:
     accum = a.global_batch // (a.micro_batch * mesh.dp)
     groups = make_groups(mesh) if world > 1 else {k: None for k in ("tp", "cp", "dp", "pp", "dpcp")}
     job = _Job(a, mesh, groups, device)
-    opt = MasterAdamW(job.model.parameters(), a.lr, a.weight_decay)
+    opt = MeshOptimizer(job, a.lr, a.weight_decay)
     links = ppar.StageLinks(mesh.pp_i, mesh.pp, mesh.rank_of(pp_i=mesh.pp_i - 1) if mesh.pp_i else None,
                             mesh.rank_of(pp_i=mesh.pp_i + 1) if mesh.pp_i + 1 < mesh.pp else None)
     run_dir = Path(os.environ.get(a.run_dir[4:], "runs/mesh") if a.run_dir.startswith("env:") else a.run_dir)
@@ -316,8 +335,12 @@ def train(a, *, on_step=None) -> list[float]:
     act_dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
     losses = []
     scale = 1.0 / (accum * mesh.dp)
+    cuda = device.type == "cuda"
     for step in range(a.steps):
         t0 = time.perf_counter()
+        if cuda:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
         block = gen.block(step).to(device).long()              # [micro*accum, T+1]
         mbs = [(block[i * a.micro_batch:(i + 1) * a.micro_batch, :-1], block[i * a.micro_batch:(i + 1) * a.micro_batch, 1:])
                for i in range(accum)]
@@ -329,10 +352,10 @@ def train(a, *, on_step=None) -> list[float]:
                 l = job.stage(None, mb)
                 l.backward()
                 loss = loss + l.detach()
-        gnorm = reduce_gradients(job, scale)
+        gnorm = opt.reduce_and_norm(scale)
         clip = min(1.0, a.grad_clip / (gnorm + 1e-6)) if a.grad_clip > 0 else 1.0
         warm = min(1.0, (step + 1) / max(1, min(10, a.steps // 10)))
-        opt.step(lr_scale=warm, grad_scale=scale * clip)
+        opt.step(warm, scale * clip)
         # mean loss of the step: partial sums live on the last stage's tensor/context ranks
         loss = loss.float() * scale
         if job.kind == "tp":
@@ -340,13 +363,21 @@ def train(a, *, on_step=None) -> list[float]:
             _allreduce(loss, groups["cp"])
         _allreduce(loss, groups["dp"])
         _allreduce(loss, groups["pp"])
-        if device.type == "cuda":
+        if cuda:                                                 # device time of the step, max over ranks
+            ev1.record()
             torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
+            ms = torch.tensor([ev0.elapsed_time(ev1)], device=device)
+            if world > 1:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            dt = float(ms) / 1e3
+        else:
+            dt = time.perf_counter() - t0
         losses.append(float(loss))
         if log is not None:
             log.write(json.dumps({"step": step + 1, "loss": losses[-1], "grad_norm": gnorm, "step_seconds": dt,
                                   "tokens_per_second": a.global_batch * a.seq_len / dt,
+                                  "timing": "cuda events, max over ranks" if cuda else "host clock",
+                                  "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 2) if cuda else 0.0,
                                   "parallelism": f"tp{mesh.tp} pp{mesh.pp} cp{mesh.cp} ep{a.ep} dp{mesh.dp}"}) + "\n")
             log.flush()
         if on_step is not None:

@@ -43,6 +43,7 @@ def test_mesh_axes():
     (4, ["--model=qwen35_tiny", "--tp=2", "--pp=2", "--sequence-parallel"]),
     (4, ["--model=qwen35_tiny_dense", "--tp=2", "--cp=2", "--sequence-parallel"]),
     (2, ["--model=v41_tiny", "--ep=2"]),
+    (4, ["--model=qwen35_tiny", "--tp=2", "--sequence-parallel"]),          # tp2 x dp2 with ZeRO-sharded optimizer state
 ])
 def test_mesh_train_steps(tmp_path, world, extra):
     argv = extra + ["--seq-len=32", "--global-batch=4", "--steps=6", "--lr=3e-3", f"--run-dir={tmp_path}"]
@@ -52,3 +53,29 @@ def test_mesh_train_steps(tmp_path, world, extra):
     assert ref[-1] < ref[0]
     rows = [json.loads(l) for l in open(tmp_path / "metrics_rank0.jsonl")]
     assert len(rows) == 6 and rows[-1]["grad_norm"] > 0
+
+
+def test_zero_adamw_matches_torch_adamw():
+    import torch
+
+    from archlab_b200.optim.zero import ZeroAdamW
+
+    torch.manual_seed(0)
+    a = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.LayerNorm(5), torch.nn.Linear(5, 3))
+    b = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.LayerNorm(5), torch.nn.Linear(5, 3))
+    b.load_state_dict(a.state_dict())
+    decay = [p for p in b.parameters() if p.dim() >= 2]
+    rest = [p for p in b.parameters() if p.dim() < 2]
+    ref = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": rest, "weight_decay": 0.0}], lr=1e-2, betas=(0.9, 0.95))
+    opt = ZeroAdamW(a.parameters(), lr=1e-2, weight_decay=0.1)
+    opt.zero_grad()
+    for i in range(4):
+        x = torch.randn(7, 6)
+        a(x).pow(2).sum().backward()
+        opt.reduce_gradients()
+        opt.step()
+        ref.zero_grad()
+        b(x).pow(2).sum().backward()
+        ref.step()
+    for p, q in zip(a.parameters(), b.parameters()):
+        assert torch.allclose(p, q, atol=1e-5, rtol=1e-4)
