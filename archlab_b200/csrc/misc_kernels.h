@@ -20,3 +20,15 @@ int nga_stochastic_bf16(const float* x, void* y, long long n, unsigned long long
 #ifdef __cplusplus
 }
 #endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+int nga_rmsnorm_bwd(const void* x, const float* weight, const void* dy, void* dx, float* dw, long long rows, int groups,
+                    int width, float eps, int zero_centered, void* stream);
+int nga_swiglu_bwd(const void* h, const void* dout, void* dh, long long rows, int inter, float limit, void* stream);
+int nga_ce_inplace(void* logits, const long long* targets, float* loss_rows, float gscale, long long rows, long long ld,
+                   int V, long long ignore_index, void* stream);
+#ifdef __cplusplus
+}
+#endif

@@ -22,7 +22,13 @@ import torch.nn.functional as F
 # ------------------------------------------------------------------------------------------------
 def rms_norm(x: torch.Tensor, weight: torch.Tensor | None = None, *, eps: float = 1e-6,
              zero_centered: bool = False) -> torch.Tensor:
-    """fp32 statistics; ``zero_centered`` scales by ``1 + weight`` (weights initialised to 0)."""
+    """fp32 statistics; ``zero_centered`` scales by ``1 + weight`` (weights initialised to 0).
+    bf16 CUDA inputs run the fused forward / backward kernels."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.size(-1) % 8 == 0 and x.size(-1) <= 8192:
+        from ..ops import block_ops
+
+        if block_ops.usable(x):
+            return block_ops.rms_norm(x, weight, eps=eps, zero_centered=zero_centered)
     xf = x.float()
     y = xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)
     if weight is not None:
@@ -74,6 +80,12 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, *, style: 
     ``half``: pairs (i, i + rot/2) (nanochat, Qwen); ``interleaved``: pairs (2i, 2i + 1)."""
     D = x.size(-1)
     r = D if rot_dim is None else rot_dim
+    if (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 4 and style in ("half", "interleaved") and r % 2 == 0
+            and cos.size(0) == x.size(1)):
+        from ..ops import block_ops
+
+        if block_ops.usable(x):
+            return block_ops.rope(x, cos, sin, rot_dim=r, interleaved=style == "interleaved")
     xr, xp = x[..., :r].float(), x[..., r:]
     c, s = cos[None, :, None, :], sin[None, :, None, :]
     if style == "half":

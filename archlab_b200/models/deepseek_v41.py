@@ -169,11 +169,17 @@ class HyperConnectionMix(nn.Module):
 
 
 class V41Block(nn.Module):
-    def __init__(self, c: V41Config, ep_group=None):
+    def __init__(self, c: V41Config, ep_group=None, ep_buffers=None):
         super().__init__()
         self.attn_norm, self.ffn_norm = RMSNorm(c.hidden_size, c.rms_eps), RMSNorm(c.hidden_size, c.rms_eps)
         self.attn = SparseLatentAttention(c)
-        if ep_group is not None:
+        if ep_buffers is not None:                      # dispatch / combine kernels over peer memory
+            from ..parallel.ep import FusedExpertParallelMoE
+
+            self.ffn = FusedExpertParallelMoE(c.hidden_size, c.moe_inter, c.n_routed_experts, c.experts_top_k, ep_buffers,
+                                              score=c.router_score, route_scale=c.route_scale, swiglu_limit=c.swiglu_limit,
+                                              n_shared=c.n_shared_experts)
+        elif ep_group is not None:
             self.ffn = moe.ExpertParallelMoE(c.hidden_size, c.moe_inter, c.n_routed_experts, c.experts_top_k, ep_group,
                                              score=c.router_score, route_scale=c.route_scale, swiglu_limit=c.swiglu_limit,
                                              n_shared=c.n_shared_experts)
@@ -189,11 +195,11 @@ class V41Block(nn.Module):
 
 
 class V41LM(nn.Module):
-    def __init__(self, config: V41Config, ep_group=None):
+    def __init__(self, config: V41Config, ep_group=None, ep_buffers=None):
         super().__init__()
         c = self.config = config
         self.embed = nn.Embedding(c.vocab_size, c.hidden_size)
-        self.layers = nn.ModuleList(V41Block(c, ep_group) for _ in range(c.n_layer))
+        self.layers = nn.ModuleList(V41Block(c, ep_group, ep_buffers) for _ in range(c.n_layer))
         self.head_mix = nn.Parameter(torch.zeros(c.hc_streams))
         self.norm = RMSNorm(c.hidden_size, c.rms_eps)
         self.lm_head = nn.Linear(c.hidden_size, c.vocab_size, bias=False)

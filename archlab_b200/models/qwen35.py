@@ -20,6 +20,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops import block_ops
 from ..ops import local_attention as la
 from ..ops.attention import causal_attention
 from ..ops import simplicial as sx
@@ -102,8 +103,7 @@ class DenseBlock(nn.Module):
 
     def forward(self, x, cos=None, sin=None, **_):
         x = x + self.attn(self.input_norm(x), cos, sin)
-        g, u = self.gate_up(self.post_norm(x)).chunk(2, -1)
-        return x + self.down(F.silu(g) * u)
+        return x + self.down(block_ops.swiglu(self.gate_up(self.post_norm(x))))
 
 
 class Qwen35LM(nn.Module):
@@ -138,10 +138,11 @@ class Qwen35LM(nn.Module):
         with torch.autocast(ids.device.type, dtype=dt, enabled=dt != torch.float32):
             for blk in self.layers:
                 x = blk(x, cos=cos, sin=sin)
-            logits = self.lm_head(self.norm(x)).float()
+            logits = self.lm_head(self.norm(x))
         if labels is None:
-            return logits
-        return F.cross_entropy(logits.flatten(0, 1), labels.flatten(), ignore_index=-1)
+            return logits.float()
+        flat = labels.flatten()
+        return block_ops.cross_entropy_sum(logits.flatten(0, 1), flat) / flat.ne(-1).sum().clamp_min(1)
 
 
 # ------------------------------------------------------------------------------------------------

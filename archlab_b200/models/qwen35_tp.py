@@ -15,6 +15,7 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
+from ..ops import block_ops
 from ..ops import simplicial as sx
 from ..ops.attention import causal_attention
 from ..parallel import cp as cpar
@@ -153,8 +154,8 @@ class Qwen35TP(nn.Module):
             x = blk(x, cos, sin)
         if not self.last:
             return x
-        logits = self.lm_head(self.norm(x).to(self.lm_head.weight.dtype)).float()
+        logits = self.lm_head(self.norm(x).to(self.lm_head.weight.dtype))
         if labels is None:
-            return logits
-        loss_sum = F.cross_entropy(logits, labels[0, pos[sl]], ignore_index=-1, reduction="sum")
+            return logits.float()
+        loss_sum = block_ops.cross_entropy_sum(logits, labels[0, pos[sl]])
         return loss_sum / labels.ne(-1).sum().clamp_min(1)

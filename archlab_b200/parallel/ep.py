@@ -22,6 +22,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..models.moe import GroupedExperts, SwiGLU, route
+from ..ops import block_ops
 from ..ops import native
 from ..ops.linear import linear
 
@@ -179,10 +180,7 @@ class FusedExpertParallelMoE(nn.Module):
             if n == 0:
                 continue
             h = linear(recv[s0:s0 + n], self.experts.gate_up[le].to(recv.dtype))
-            g, u = h[:, : self.experts.inter].float(), h[:, self.experts.inter:].float()
-            if self.limit is not None:
-                g, u = g.clamp(max=self.limit), u.clamp(-self.limit, self.limit)
-            a = (F.silu(g) * u).to(recv.dtype)
+            a = block_ops.swiglu(h, self.limit)
             outs.append(linear(a, self.experts.down[le].to(recv.dtype)))
             s0 += n
         y_local = torch.cat(outs, 0) if outs else recv.new_zeros(0, self.dim)

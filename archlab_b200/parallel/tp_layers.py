@@ -14,6 +14,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
+from ..ops import block_ops
 from ..ops import gemm as G
 from . import tp as T
 
@@ -161,6 +162,4 @@ class TPMLP(nn.Module):
 
     def forward(self, x_shard, resid=None):
         h = self.gate_up(x_shard)
-        g, u = h[:, : self.inter_local], h[:, self.inter_local:]
-        a = (torch.nn.functional.silu(g.float()) * u.float()).to(h.dtype)
-        return self.down(a, resid)
+        return self.down(block_ops.swiglu(h), resid)

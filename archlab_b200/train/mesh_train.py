@@ -181,12 +181,21 @@ class _Job:
             if mesh.tp > 1 or mesh.pp > 1 or mesh.cp > 1:
                 raise ValueError("the V4.1 family runs under data + expert parallelism here")
             kw = {"sequence_len": a.seq_len, **({"n_layer": a.n_layer} if a.n_layer else {})}
-            cfg = V41Config.tiny(**kw) if a.model == "v41_tiny" else V41Config(**kw)
+            presets = {"v41_tiny": V41Config.tiny, "v41_moe": V41Config,
+                       "v41_small": lambda **k: V41Config(**{**dict(vocab_size=32768, n_layer=2, hidden_size=1024, n_heads=8,
+                                                                    n_routed_experts=16, moe_inter=512, index_top_k=256), **k})}
+            cfg = presets[a.model](**kw)
             ep_group = groups["dp"] if a.ep > 1 else None
             if a.ep > 1 and a.ep != mesh.dp:
                 raise ValueError("expert parallel size must equal the data parallel size in this trainer")
             torch.manual_seed(a.seed)
-            self.model = V41LM(cfg, ep_group).to(device)
+            ep_buffers = None
+            if ep_group is not None and device.type == "cuda":
+                from ..parallel.ep import EPBuffers
+
+                slots = a.micro_batch * a.seq_len * cfg.experts_top_k
+                ep_buffers = EPBuffers(2 * slots, cfg.hidden_size, device, ep_group)
+            self.model = V41LM(cfg, ep_group, ep_buffers).to(device)
             self.model.init_weights()
             if ep_group is not None:                          # shared weights agree; every rank keeps its own experts
                 for n, p in self.model.named_parameters():
