@@ -32,3 +32,13 @@ int nga_ce_inplace(void* logits, const long long* targets, float* loss_rows, flo
 #ifdef __cplusplus
 }
 #endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+long long nga_gdn_workspace_bytes(int B, int T, int H);
+int nga_gdn_fwd(const void* q, const void* k, const void* v, const float* g, const float* beta, void* o, const float* s0,
+                float* s_out, void* workspace, int B, int T, int H, int D, int* status, void* stream);
+#ifdef __cplusplus
+}
+#endif

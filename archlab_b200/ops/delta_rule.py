@@ -140,3 +140,70 @@ def causal_conv1d(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | No
     elif activation is not None:
         raise ValueError(f"unsupported activation {activation!r}")
     return y
+
+
+# ------------------------------------------------------------------------------------------------
+# sm_100a kernel path (gated delta rule, scalar decay, width 128)
+# ------------------------------------------------------------------------------------------------
+def _native():
+    import ctypes as C
+
+    from . import native
+
+    vp, i = C.c_void_p, C.c_int
+    native.register_signature("nga_gdn_workspace_bytes", [i, i, i], C.c_longlong)
+    native.register_signature("nga_gdn_fwd", [vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, vp, vp])
+    return native
+
+
+def gdn_kernel_supports(q, k, v) -> bool:
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.size(-1) == 128 and v.size(-1) == 128 and k.shape == q.shape
+            and v.shape[:3] == q.shape[:3])
+
+
+def gdn_forward_cuda(q, k, v, decay, beta, initial_state=None, output_final_state: bool = False):
+    """Forward of the gated delta rule on the tcgen05 kernels: q/k/v [B, T, H, 128] bf16 (un-normalised),
+    decay/beta [B, T, H].  Returns o [B, T, H, 128] bf16 (and the final fp32 state [B, H, 128, 128])."""
+    native = _native()
+    B, T, H, D = q.shape
+    pad = (-T) % 64
+    if pad:                                              # zero k, v, beta and zero log-decay leave the state untouched
+        q, k, v = (F.pad(x, (0, 0, 0, 0, 0, pad)) for x in (q, k, v))
+        decay, beta = F.pad(decay, (0, 0, 0, pad)), F.pad(beta, (0, 0, 0, pad))
+    Tp = T + pad
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    g32, b32 = decay.float().contiguous(), beta.float().contiguous()
+    o = torch.empty(B, Tp, H, D, dtype=torch.bfloat16, device=q.device)
+    ws = torch.empty(native.lib().nga_gdn_workspace_bytes(B, Tp, H), dtype=torch.uint8, device=q.device)
+    s0 = None if initial_state is None else initial_state.float().contiguous()
+    s_out = torch.empty(B, H, D, D, dtype=torch.float32, device=q.device) if output_final_state else None
+    ptr = lambda t: None if t is None else t.data_ptr()
+    rc = native.lib().nga_gdn_fwd(ptr(q), ptr(k), ptr(v), ptr(g32), ptr(b32), ptr(o), ptr(s0), ptr(s_out), ptr(ws), B, Tp, H, D,
+                                  native.status_word(q.device).data_ptr(), native.stream_ptr())
+    native.check(rc, "nga_gdn_fwd")
+    o = o[:, :T]
+    return (o, s_out) if output_final_state else o
+
+
+class _GatedDeltaFn(torch.autograd.Function):
+    """Kernel forward; the backward differentiates the chunk-parallel PyTorch form on the saved inputs."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, decay, beta):
+        ctx.save_for_backward(q, k, v, decay, beta)
+        return gdn_forward_cuda(q, k, v, decay, beta)
+
+    @staticmethod
+    def backward(ctx, do):
+        saved = [t.detach().requires_grad_(True) for t in ctx.saved_tensors]
+        with torch.enable_grad():
+            o = chunk_gated_delta_rule(*saved)
+        grads = torch.autograd.grad(o, saved, do.float())
+        return tuple(g.to(t.dtype) for g, t in zip(grads, ctx.saved_tensors))
+
+
+def gated_delta_rule(q, k, v, decay, beta):
+    """Dispatch: tcgen05 forward for bf16 CUDA inputs of width 128, else the chunk-parallel PyTorch form."""
+    if gdn_kernel_supports(q, k, v):
+        return _GatedDeltaFn.apply(q, k, v, decay, beta)
+    return chunk_gated_delta_rule(q, k, v, decay, beta).to(q.dtype)
