@@ -128,6 +128,22 @@ def bench_simplicial(t: Timer, small: bool):
         _emit(f"simplicial_fwd_bwd_N{N}_H{Hq}_{w1}x{w2}", ms_f + ms_b, flops=14.0 * D * triples)
 
 
+def bench_delta(t: Timer, small: bool):
+    """Gated delta rule forward; FLOPs counted as the chunked algorithm's tensor-core products
+    (per 64-token chunk and head: gram 2*128*64*128, W/U 2*2*128*64*64, scan 2*128*64*(128+128+64+128))."""
+    from .ops import delta_rule as dr
+
+    cases = [(1, 8192, 16), (4, 8192, 16), (8, 2048, 32)] if not small else [(2, 4096, 16)]
+    for B, T, H in cases:
+        q, k, v = ((torch.randn(B, T, H, 128, device="cuda")).bfloat16() for _ in range(3))
+        decay = -torch.rand(B, T, H, device="cuda") * 0.1
+        beta = torch.rand(B, T, H, device="cuda")
+        ms = t(lambda: dr.gdn_forward_cuda(q, k, v, decay, beta))
+        per_chunk = 2 * 128 * 64 * 128 + 4 * 128 * 64 * 64 + 2 * 128 * 64 * (128 + 128 + 64 + 128)
+        _emit(f"gdn_fwd_B{B}_T{T}_H{H}", ms, flops=float(per_chunk) * B * H * (T // 64),
+              bytes_=B * T * H * 128 * 2 * 4, extra={"tokens_per_s": round(B * T / ms * 1e3)})
+
+
 def bench_trunk(t: Timer, small: bool):
     from .ops import trunk
 
@@ -146,14 +162,14 @@ def bench_trunk(t: Timer, small: bool):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "attention", "simplicial", "trunk", "all"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "attention", "simplicial", "trunk", "delta", "all"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
     from .ops import native
 
     t = Timer(a.iters)
-    ops = {"gemm": bench_gemm, "attention": bench_attention, "simplicial": bench_simplicial, "trunk": bench_trunk}
+    ops = {"gemm": bench_gemm, "attention": bench_attention, "simplicial": bench_simplicial, "trunk": bench_trunk, "delta": bench_delta}
     for name, fn in ops.items():
         if a.op in (name, "all"):
             fn(t, a.small)

@@ -126,6 +126,19 @@ __device__ __forceinline__ float segsum(float v, int w1) {
   for (int o = 1; o < w1; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
+// Barrier of the 128 compute threads of the query-owned kernel that ANDs a predicate.
+__device__ __forceinline__ bool sb_bar_and(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "barrier.cta.red.and.pred q, 1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
 
 struct SimpBwdQSmem {
   static constexpr int kA = 0;                    // 32 KB  q * k1 rows
@@ -360,7 +373,7 @@ simplicial_bwd_q_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(p_empty, (ntiles - 1) & 1, abort_word));
     if (ok) {
       tc_fence_after();
-      __nv_bfloat16* dqrow = p.dq + qrow_idx * p.lddq + h * SB_D;
+      float* red = reinterpret_cast<float*>(smem + S::kK);
       float* dk1row = p.dk1 + krow_idx * ((long long)p.Hkv * SB_D) + hk * SB_D;
       float* dv1row = p.dv1 + krow_idx * ((long long)p.Hkv * SB_D) + hk * SB_D;
 #pragma unroll 1
@@ -402,19 +415,27 @@ simplicial_bwd_q_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
             atomicAdd(reinterpret_cast<float4*>(dv1row + c * 32 + g * 8 + 4), make_float4(dvv[4], dvv[5], dvv[6], dvv[7]));
           }
         }
+        // dq partials of this row go to shared memory (the K2 / V2 / P / dS buffers are idle now); the
+        // sum over a query's w1 rows is done per column below instead of by 160 dependent shuffles
 #pragma unroll
-        for (int e = 0; e < 32; ++e) dqv[e] = segsum(dqv[e], p.w1);
-        if (jj == 0 && i < p.N) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 u;
-            u.x = pack_bf16(dqv[8 * g + 0], dqv[8 * g + 1]);
-            u.y = pack_bf16(dqv[8 * g + 2], dqv[8 * g + 3]);
-            u.z = pack_bf16(dqv[8 * g + 4], dqv[8 * g + 5]);
-            u.w = pack_bf16(dqv[8 * g + 6], dqv[8 * g + 7]);
-            *reinterpret_cast<uint4*>(dqrow + c * 32 + g * 8) = u;
-          }
+        for (int g = 0; g < 8; ++g)
+          *reinterpret_cast<float4*>(red + r * 132 + c * 32 + g * 4) =
+              make_float4(dqv[4 * g], dqv[4 * g + 1], dqv[4 * g + 2], dqv[4 * g + 3]);
+      }
+    }
+    ok = sb_bar_and(ok);                            // all four compute warps, whatever happened above
+    if (ok) {
+      const float* red = reinterpret_cast<const float*>(smem + S::kK);
+      for (int qq = 0; qq < BQ; ++qq) {
+        const int iq = i0 + qq;
+        if (iq >= p.N) break;
+        float a0 = 0.f, a1 = 0.f;
+        const float* col = red + (qq * p.w1) * 132 + r;
+        for (int x = 0; x < p.w1; x += 2) {
+          a0 += col[x * 132];
+          a1 += col[(x + 1) * 132];
         }
+        p.dq[(long long)(row_base + iq) * p.lddq + h * SB_D + r] = __float2bfloat16(a0 + a1);
       }
     }
   }

@@ -36,6 +36,7 @@ struct SimpFwdParams {
   int B, N, Hq, Hkv, w1, w2;
   float scale_log2;
   int* status;
+  long long* prof;           // optional phase cycle counters written by one mid-grid CTA (tuning aid)
 };
 
 struct SimpFwdSmem {
@@ -47,6 +48,19 @@ struct SimpFwdSmem {
   static constexpr int kTotal = kBar + 16 * 8 + 16 + 1024;
 };
 
+// Barrier of the 128 softmax threads that ANDs a predicate.
+__device__ __forceinline__ bool sx_bar_and(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "barrier.cta.red.and.pred q, 1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
 __device__ __forceinline__ float seg_max(float v, int w1) {
   for (int o = 1; o < w1; o <<= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
@@ -74,6 +88,10 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool prof = p.prof != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && blockIdx.z == 0 &&
+                    warp == 2 && lane == 0;
+  long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const long long pt0 = prof ? clock64() : 0;
   const int BQ = 128 / p.w1;
   const int i0 = blockIdx.x * BQ;
   const int h = blockIdx.y, b = blockIdx.z;
@@ -183,6 +201,8 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
     const int p1 = i - p.w1 + 1 + jj;            // short-key position of this row
     const bool row_valid = (i < p.N) && (p1 >= 0);
     const uint32_t lane_off = uint32_t(quarter * 32) << 16;
+    if (prof) pc[0] = clock64() - pt0;             // setup (barriers, TMEM allocation)
+    long long pt = prof ? clock64() : 0;
     // ---- build this row of A = q[i] * k1[p1] into the swizzled tile
     {
       const __nv_bfloat16* qrow = p.q + (long long)(row_base + min(i, p.N - 1)) * p.ldq + h * SX_D;
@@ -191,29 +211,27 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
       // loads of a half row first, then the packed products (bf16 x bf16 rounded to bf16 equals the fp32
       // product rounded once): a generic shared store between two global loads would serialise every
       // chunk on the L2 latency
+      uint4 qa[16], ka[16];
 #pragma unroll
-      for (int hb = 0; hb < 2; ++hb) {
-        uint4 qa[8], ka[8];
+      for (int c = 0; c < 16; ++c) {
+        qa[c] = row_valid ? *reinterpret_cast<const uint4*>(qrow + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+        ka[c] = row_valid ? *reinterpret_cast<const uint4*>(krow + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+      }
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          qa[c] = row_valid ? *reinterpret_cast<const uint4*>(qrow + (hb * 8 + c) * 8) : make_uint4(0u, 0u, 0u, 0u);
-          ka[c] = row_valid ? *reinterpret_cast<const uint4*>(krow + (hb * 8 + c) * 8) : make_uint4(0u, 0u, 0u, 0u);
-        }
+      for (int c = 0; c < 16; ++c) {
+        uint4 o;
+        const __nv_bfloat162* qh = reinterpret_cast<const __nv_bfloat162*>(&qa[c]);
+        const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&ka[c]);
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint4 o;
-          const __nv_bfloat162* qh = reinterpret_cast<const __nv_bfloat162*>(&qa[c]);
-          const __nv_bfloat162* kh = reinterpret_cast<const __nv_bfloat162*>(&ka[c]);
-          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) oh[e] = __hmul2(qh[e], kh[e]);
-          *reinterpret_cast<uint4*>(sA + hb * 16384 + r * 128 + ((c ^ (r & 7)) * 16)) = o;
-        }
+        for (int e = 0; e < 4; ++e) oh[e] = __hmul2(qh[e], kh[e]);
+        *reinterpret_cast<uint4*>(sA + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) * 16)) = o;
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(a_full);
     }
+    if (prof) { const long long n = clock64(); pc[1] = n - pt; pt = n; }   // A build
     float m_ref = -INFINITY, l_row = 0.f;
     bool ok = true;
     uint8_t* sP = smem + S::kP;
@@ -222,11 +240,13 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_word));
       if (!ok) break;
       tc_fence_after();
+      if (prof) { const long long n = clock64(); pc[2] += n - pt; pt = n; }   // wait for S
       const uint32_t tS = tmem_S0 + uint32_t((j & 1) * 128) + lane_off;
       uint32_t sv[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(tS + c * 32, sv[c]);
       tmem_ld_wait();
+      if (prof) { const long long n = clock64(); pc[3] += n - pt; pt = n; }   // TMEM load
       // visibility of long key pos2 = k0 + col for this row: i - w2 < pos2 <= i
       const int lo = i - p.w2 + 1 - k0, hi = i - k0;      // valid columns are [lo, hi]
       const bool full = row_valid && lo <= 0 && hi >= SX_BK - 1;
@@ -251,6 +271,7 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
         if (!ok) break;
         tc_fence_after();
       }
+      if (prof) { const long long n = clock64(); pc[4] += n - pt; pt = n; }   // mask + max + wait for the P buffer
       const float m_new = fmaxf(m_ref, mx);
       const bool grow = (m_new > m_ref + 8.f) || (m_ref == -INFINITY && m_new != -INFINITY);
       if (__any_sync(0xffffffffu, grow)) {
@@ -301,47 +322,70 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
         mbar_arrive(&s_free[j & 1]);
         mbar_arrive(p_full);
       }
+      if (prof) { const long long n = clock64(); pc[5] += n - pt; pt = n; }   // rescale + exp + P store
     }
     // ---------------------------------------------------------------- epilogue
+    // this row's v1 values are fetched while the last P V2 product is still running
+    const __nv_bfloat16* v1row = p.v1 + (long long)(row_base + max(p1, 0)) * p.ldv1 + hk * SX_D;
+    uint4 vv[16];
+#pragma unroll
+    for (int g = 0; g < 16; ++g)
+      vv[g] = row_valid ? *reinterpret_cast<const uint4*>(v1row + g * 8) : make_uint4(0u, 0u, 0u, 0u);
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(p_empty, (ntiles - 1) & 1, abort_word));
+    ok = sx_bar_and(ok);                        // the four softmax warps agree before sharing a barrier
     if (ok) {
       tc_fence_after();
       const float l_q = seg_sum(l_row, p.w1);
       const float inv = l_q > 0.f ? 1.f / l_q : 0.f;
-      const __nv_bfloat16* v1row = p.v1 + (long long)(row_base + max(p1, 0)) * p.ldv1 + hk * SX_D;
-      __nv_bfloat16* orow = p.out + (long long)(row_base + min(i, p.N - 1)) * p.ldo + h * SX_D;
-#pragma unroll 1
+      // The K2 / V2 / P buffers are idle now: each row leaves inv * O_pair[row] * v1[row] there in fp32
+      // (row stride 132 floats keeps the 16-byte stores of a quarter warp on distinct banks), then thread t
+      // adds the w1 rows of every query for column t.  (A shuffle reduction would serialise 640 dependent
+      // shuffles per thread.)
+      float* red = reinterpret_cast<float*>(smem + S::kK);
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
         tmem_ld_32x32(tmem_O + lane_off + c * 32, v);
         tmem_ld_wait();
-        float acc[32];
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          uint4 vv = *reinterpret_cast<const uint4*>(v1row + c * 32 + g * 8);
-          const __nv_bfloat162* vh = reinterpret_cast<const __nv_bfloat162*>(&vv);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(vh[e]);
-            acc[g * 8 + 2 * e] = row_valid ? __uint_as_float(v[g * 8 + 2 * e]) * f.x : 0.f;
-            acc[g * 8 + 2 * e + 1] = row_valid ? __uint_as_float(v[g * 8 + 2 * e + 1]) * f.y : 0.f;
-          }
-        }
-#pragma unroll
-        for (int e = 0; e < 32; ++e) acc[e] = seg_sum(acc[e], p.w1) * inv;
-        if (jj == 0 && i < p.N) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 u;
-            u.x = pack_bf16(acc[8 * g + 0], acc[8 * g + 1]);
-            u.y = pack_bf16(acc[8 * g + 2], acc[8 * g + 3]);
-            u.z = pack_bf16(acc[8 * g + 4], acc[8 * g + 5]);
-            u.w = pack_bf16(acc[8 * g + 6], acc[8 * g + 7]);
-            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = u;
-          }
+          const __nv_bfloat162* vh = reinterpret_cast<const __nv_bfloat162*>(&vv[c * 4 + g]);
+          float4 lo, hi;
+          float2 f = __bfloat1622float2(vh[0]);
+          lo.x = __uint_as_float(v[g * 8 + 0]) * f.x * inv;
+          lo.y = __uint_as_float(v[g * 8 + 1]) * f.y * inv;
+          f = __bfloat1622float2(vh[1]);
+          lo.z = __uint_as_float(v[g * 8 + 2]) * f.x * inv;
+          lo.w = __uint_as_float(v[g * 8 + 3]) * f.y * inv;
+          f = __bfloat1622float2(vh[2]);
+          hi.x = __uint_as_float(v[g * 8 + 4]) * f.x * inv;
+          hi.y = __uint_as_float(v[g * 8 + 5]) * f.y * inv;
+          f = __bfloat1622float2(vh[3]);
+          hi.z = __uint_as_float(v[g * 8 + 6]) * f.x * inv;
+          hi.w = __uint_as_float(v[g * 8 + 7]) * f.y * inv;
+          *reinterpret_cast<float4*>(red + r * 132 + c * 32 + g * 8) = lo;
+          *reinterpret_cast<float4*>(red + r * 132 + c * 32 + g * 8 + 4) = hi;
         }
       }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int qq = 0; qq < BQ; ++qq) {
+        const int iq = i0 + qq;
+        if (iq >= p.N) break;
+        float a0 = 0.f, a1 = 0.f;
+        const float* col = red + (qq * p.w1) * 132 + r;
+        for (int x = 0; x < p.w1; x += 2) {
+          a0 += col[x * 132];
+          a1 += col[(x + 1) * 132];
+        }
+        p.out[(long long)(row_base + iq) * p.ldo + h * SX_D + r] = __float2bfloat16(a0 + a1);
+      }
       if (jj == 0 && i < p.N) p.lse2[((long long)b * p.Hq + h) * p.N + i] = m_ref + log2f(l_q);
+    }
+    if (prof) {
+      pc[6] = clock64() - pt;                      // last PV wait + epilogue
+      pc[7] = ntiles;
+      for (int x = 0; x < 8; ++x) p.prof[x] = pc[x];
+      p.prof[8] = clock64() - pt0;
     }
   }
 
@@ -356,6 +400,9 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
 }
 
 }  // namespace nga
+
+static long long* g_simp_fwd_prof = nullptr;
+extern "C" void nga_simplicial_fwd_set_prof(long long* device_ptr) { g_simp_fwd_prof = device_ptr; }
 
 extern "C" int nga_simplicial_fwd(const void* q, const void* k1, const void* k2, const void* v1, const void* v2,
                                   void* out, float* lse2, long long ldq, long long ldk1, long long ldk2,
@@ -390,6 +437,7 @@ extern "C" int nga_simplicial_fwd(const void* q, const void* k1, const void* k2,
   p.B = B; p.N = N; p.Hq = Hq; p.Hkv = Hkv; p.w1 = w1; p.w2 = w2;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  p.prof = g_simp_fwd_prof;
   const int BQ = 128 / w1;
   dim3 grid((N + BQ - 1) / BQ, Hq, B);
   simplicial_fwd_kernel<<<grid, SX_THREADS, SimpFwdSmem::kTotal, reinterpret_cast<cudaStream_t>(stream)>>>(tk, tv, p);

@@ -129,7 +129,7 @@ class GatedDeltaNet(nn.Module):
         rep = self.vh // self.qh
         q = q.view(B, T, self.qh, self.kd).repeat_interleave(rep, 2)
         k = k.view(B, T, self.qh, self.kd).repeat_interleave(rep, 2)
-        o = delta_rule.chunk_gated_delta_rule(q, k, v.view(B, T, self.vh, self.vd), decay, b_logit.sigmoid())
+        o = delta_rule.gated_delta_rule(q, k, v.view(B, T, self.vh, self.vd), decay, b_logit.sigmoid())
         o = self.output_norm(o.to(x.dtype)) * F.silu(self.z(x).view(B, T, self.vh, self.vd))
         return self.out(o.flatten(-2))
 
