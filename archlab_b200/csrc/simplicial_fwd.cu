@@ -37,6 +37,10 @@ struct SimpFwdParams {
   float scale_log2;
   int* status;
   long long* prof;           // optional phase cycle counters written by one mid-grid CTA (tuning aid)
+  // decode mode: one new token per sequence against paged caches (page = 128 positions = one key tile)
+  const int* block_table;    // [B, max_pages] physical page of every logical page
+  const int* seq_lens;       // [B] tokens in the cache including the new one
+  int max_pages;
 };
 
 struct SimpFwdSmem {
@@ -70,6 +74,10 @@ __device__ __forceinline__ float seg_sum(float v, int w1) {
   return v;
 }
 
+// DECODE = false: a CTA owns 128 / w1 consecutive queries of one head (prefill / training forward).
+// DECODE = true : a CTA owns the newest token of one sequence for the Hq / Hkv query heads that share a
+//                 KV head; its rows are (query head, short key), keys come from paged caches.
+template <bool DECODE>
 __global__ void __launch_bounds__(SX_THREADS, 1)
 simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_constant__ CUtensorMap tm_v2,
                       const SimpFwdParams p) {
@@ -92,12 +100,16 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
                     warp == 2 && lane == 0;
   long long pc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   const long long pt0 = prof ? clock64() : 0;
-  const int BQ = 128 / p.w1;
-  const int i0 = blockIdx.x * BQ;
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int hk = h / (p.Hq / p.Hkv);
-  const int row_base = b * p.N;
-  const int i_last = min(i0 + BQ - 1, p.N - 1);
+  const int G = p.Hq / p.Hkv;
+  const int BQ = DECODE ? G : 128 / p.w1;
+  const int b = blockIdx.z;
+  const int pos_last = DECODE ? p.seq_lens[b] - 1 : 0;
+  const int i0 = DECODE ? pos_last : blockIdx.x * BQ;
+  const int h = blockIdx.y;                       // query head (prefill) or KV head (decode)
+  const int hk = DECODE ? h : h / G;
+  const int row_base = DECODE ? 0 : b * p.N;
+  const int i_last = DECODE ? pos_last : min(i0 + BQ - 1, p.N - 1);
+  const int* pages = DECODE ? p.block_table + (long long)b * p.max_pages : nullptr;
   const int t_lo = max(0, i0 - p.w2 + 1) / SX_BK;
   const int t_hi = i_last / SX_BK;
   const int ntiles = t_hi - t_lo + 1;
@@ -136,7 +148,7 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
         const int st = j & 1;
         ok = mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1u, abort_word);
         if (!ok) break;
-        const int krow = row_base + (t_lo + j) * SX_BK;
+        const int krow = DECODE ? pages[t_lo + j] * SX_BK : row_base + (t_lo + j) * SX_BK;
         uint8_t* sK = smem + S::kK + st * SX_TILE;
         uint8_t* sV = smem + S::kV + st * SX_TILE;
         mbar_expect_tx(&kv_full[st], 2 * SX_TILE);
@@ -197,16 +209,21 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const int qi = r / p.w1, jj = r % p.w1;
-    const int i = i0 + qi;                       // query position
+    const int i = DECODE ? pos_last : i0 + qi;   // query position
+    const int head = DECODE ? hk * G + qi : h;   // query head of this row
     const int p1 = i - p.w1 + 1 + jj;            // short-key position of this row
-    const bool row_valid = (i < p.N) && (p1 >= 0);
+    const bool row_valid = DECODE ? (qi < G && p1 >= 0) : ((i < p.N) && (p1 >= 0));
+    // row of the short key / value in its tensor (paged in decode mode)
+    const long long short_row = DECODE ? (long long)pages[max(p1, 0) >> 7] * SX_BK + (max(p1, 0) & 127)
+                                       : (long long)(row_base + max(p1, 0));
     const uint32_t lane_off = uint32_t(quarter * 32) << 16;
     if (prof) pc[0] = clock64() - pt0;             // setup (barriers, TMEM allocation)
     long long pt = prof ? clock64() : 0;
     // ---- build this row of A = q[i] * k1[p1] into the swizzled tile
     {
-      const __nv_bfloat16* qrow = p.q + (long long)(row_base + min(i, p.N - 1)) * p.ldq + h * SX_D;
-      const __nv_bfloat16* krow = p.k1 + (long long)(row_base + max(p1, 0)) * p.ldk1 + hk * SX_D;
+      const __nv_bfloat16* qrow = DECODE ? p.q + (long long)b * p.ldq + min(head, p.Hq - 1) * SX_D
+                                         : p.q + (long long)(row_base + min(i, p.N - 1)) * p.ldq + h * SX_D;
+      const __nv_bfloat16* krow = p.k1 + short_row * p.ldk1 + hk * SX_D;
       uint8_t* sA = smem + S::kA;
       // loads of a half row first, then the packed products (bf16 x bf16 rounded to bf16 equals the fp32
       // product rounded once): a generic shared store between two global loads would serialise every
@@ -326,7 +343,7 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
     }
     // ---------------------------------------------------------------- epilogue
     // this row's v1 values are fetched while the last P V2 product is still running
-    const __nv_bfloat16* v1row = p.v1 + (long long)(row_base + max(p1, 0)) * p.ldv1 + hk * SX_D;
+    const __nv_bfloat16* v1row = p.v1 + short_row * p.ldv1 + hk * SX_D;
     uint4 vv[16];
 #pragma unroll
     for (int g = 0; g < 16; ++g)
@@ -368,18 +385,24 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
         }
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      for (int qq = 0; qq < BQ; ++qq) {
+      for (int qq = 0; qq < BQ && (qq + 1) * p.w1 <= 128; ++qq) {
         const int iq = i0 + qq;
-        if (iq >= p.N) break;
+        if (!DECODE && iq >= p.N) break;
         float a0 = 0.f, a1 = 0.f;
         const float* col = red + (qq * p.w1) * 132 + r;
         for (int x = 0; x < p.w1; x += 2) {
           a0 += col[x * 132];
           a1 += col[(x + 1) * 132];
         }
-        p.out[(long long)(row_base + iq) * p.ldo + h * SX_D + r] = __float2bfloat16(a0 + a1);
+        const long long o = DECODE ? (long long)b * p.ldo + (hk * G + qq) * SX_D + r
+                                   : (long long)(row_base + iq) * p.ldo + h * SX_D + r;
+        p.out[o] = __float2bfloat16(a0 + a1);
       }
-      if (jj == 0 && i < p.N) p.lse2[((long long)b * p.Hq + h) * p.N + i] = m_ref + log2f(l_q);
+      if (DECODE) {
+        if (jj == 0 && qi < G) p.lse2[(long long)b * p.Hq + head] = m_ref + log2f(l_q);
+      } else if (jj == 0 && i < p.N) {
+        p.lse2[((long long)b * p.Hq + h) * p.N + i] = m_ref + log2f(l_q);
+      }
     }
     if (prof) {
       pc[6] = clock64() - pt;                      // last PV wait + epilogue
@@ -422,7 +445,7 @@ extern "C" int nga_simplicial_fwd(const void* q, const void* k1, const void* k2,
   if (rc) return rc;
   static bool attr_done = false;
   if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(simplicial_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(simplicial_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SimpFwdSmem::kTotal);
     if (e != cudaSuccess) return -1000 - (int)e;
     attr_done = true;
@@ -438,9 +461,55 @@ extern "C" int nga_simplicial_fwd(const void* q, const void* k1, const void* k2,
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
   p.prof = g_simp_fwd_prof;
+  p.block_table = nullptr; p.seq_lens = nullptr; p.max_pages = 0;
   const int BQ = 128 / w1;
   dim3 grid((N + BQ - 1) / BQ, Hq, B);
-  simplicial_fwd_kernel<<<grid, SX_THREADS, SimpFwdSmem::kTotal, reinterpret_cast<cudaStream_t>(stream)>>>(tk, tv, p);
+  simplicial_fwd_kernel<false><<<grid, SX_THREADS, SimpFwdSmem::kTotal, reinterpret_cast<cudaStream_t>(stream)>>>(tk, tv, p);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}
+
+// One new token per sequence against paged caches.  q: [B, Hq*D]; caches: [num_pages * 128, Hkv*D] bf16 (page p
+// holds rows p*128 .. p*128+127); block_table [B, max_pages] int32; seq_lens [B] int32 (cache length including
+// the new token, whose k1/k2/v1/v2 are already written); out [B, Hq*D]; lse2 [B, Hq].
+// Requires (Hq / Hkv) * w1 <= 128.
+extern "C" int nga_simplicial_decode(const void* q, const void* k1c, const void* k2c, const void* v1c, const void* v2c,
+                                     void* out, float* lse2, const int* block_table, const int* seq_lens, long long ldq,
+                                     long long ldc, long long ldo, int B, int Hq, int Hkv, int D, int w1, int w2,
+                                     int max_pages, int num_pages, float scale, int* status, void* stream) {
+  using namespace nga;
+  if (D != SX_D || B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || num_pages <= 0 || max_pages <= 0) return -1;
+  if (!(w1 == 8 || w1 == 16 || w1 == 32) || w2 < w1 || (Hq / Hkv) * w1 > 128) return -6;
+  if ((ldq | ldc | ldo) & 7) return -5;
+  const long long rows = (long long)num_pages * SX_BK;
+  CUtensorMap tk, tv;
+  int rc = make_tmap_3d(&tk, k2c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)Hkv * D, rows, 1, ldc * 2, rows * ldc * 2,
+                        64, 128, true);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tv, v2c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)Hkv * D, rows, 1, ldc * 2, rows * ldc * 2, 64, 128,
+                    true);
+  if (rc) return rc;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(simplicial_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SimpFwdSmem::kTotal);
+    if (e != cudaSuccess) return -1000 - (int)e;
+    attr_done = true;
+  }
+  SimpFwdParams p;
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q);
+  p.k1 = reinterpret_cast<const __nv_bfloat16*>(k1c);
+  p.v1 = reinterpret_cast<const __nv_bfloat16*>(v1c);
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.lse2 = lse2;
+  p.ldq = ldq; p.ldk1 = ldc; p.ldv1 = ldc; p.ldo = ldo;
+  p.B = B; p.N = 1; p.Hq = Hq; p.Hkv = Hkv; p.w1 = w1; p.w2 = w2;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  p.prof = nullptr;
+  p.block_table = block_table; p.seq_lens = seq_lens; p.max_pages = max_pages;
+  simplicial_fwd_kernel<true><<<dim3(1, Hkv, B), SX_THREADS, SimpFwdSmem::kTotal, reinterpret_cast<cudaStream_t>(stream)>>>(tk, tv, p);
   count_launch();
   NGA_CHECK_LAUNCH();
   return 0;
