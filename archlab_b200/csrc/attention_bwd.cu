@@ -31,6 +31,7 @@ struct AttnBwdParams {
   float scale, scale_log2;
   int* status;
   long long* prof;       // optional phase cycle counters written by CTA (0,0,0)
+  const uint32_t* selT;  // optional key-major selection bits [B, T(key), T/32] (bit q of row k)
 };
 
 struct AttnBwdSmem {
@@ -268,9 +269,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
 #define NGA_PROFB(i) do { if (prof_on) { long long tn = clock64(); pc[i] += tn - tp; tp = tn; } } while (0)
     // per-query vectors of the first step; later steps are prefetched one step ahead
     float nxt_l = INFINITY, nxt_d = 0.f;
+    uint32_t nxt_sel = ~0u;
     auto fetch_vec = [&](int it) {
       const int h = hk * group + it / nq;
       const int q = (qt_lo + it % nq) * AB_BQ + chalf * 32 + lane;
+      if (p.selT != nullptr && key < p.T)
+        nxt_sel = p.selT[((long long)b * p.T + key) * (p.T >> 5) + (((qt_lo + it % nq) * AB_BQ + chalf * 32) >> 5)];
       const long long vi = ((long long)b * p.Hq + h) * p.T + q;
       nxt_l = q < p.T ? p.lse2[vi] : INFINITY;
       nxt_d = q < p.T ? p.delta[vi] : 0.f;
@@ -285,6 +289,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
       float* del_b = lse_b + 32;
       lse_b[lane] = nxt_l;
       del_b[lane] = nxt_d;
+      const uint32_t selw = nxt_sel;
       __syncwarp();
       if (it + 1 < niter) fetch_vec(it + 1);     // global loads in flight during this step
       NGA_PROFB(0);
@@ -305,6 +310,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
             const int q = q0 + chalf * 32 + i;
             if (key > q || q >= p.T || (p.window >= 0 && q - key > p.window)) e = 0.f;
           }
+          if (!((selw >> i) & 1u)) e = 0.f;
           pr[i] = e;
           ds[i] = e * (__uint_as_float(dv[i]) - del_b[i]) * p.scale;
         }
@@ -412,6 +418,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
 }  // namespace nga
 
 static long long* g_attn_bwd_prof = nullptr;
+static const uint32_t* g_attn_bwd_selT = nullptr;
+// Key-major selection bits for the NEXT backward launch only (consumed by it).
+extern "C" void nga_attn_bwd_set_extras(const uint32_t* sel_bits_key_major) { g_attn_bwd_selT = sel_bits_key_major; }
 extern "C" void nga_attn_bwd_set_prof(long long* device_ptr) { g_attn_bwd_prof = device_ptr; }
 
 extern "C" int nga_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse2,
@@ -462,6 +471,9 @@ extern "C" int nga_attn_bwd(const void* qkv, const void* out, const void* dout, 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
   p.prof = g_attn_bwd_prof;
+  p.selT = g_attn_bwd_selT;
+  g_attn_bwd_selT = nullptr;
+  if (p.selT != nullptr && (T % 64)) return -7;
   dim3 grid((T + AB_BK - 1) / AB_BK, Hkv, B);
   attn_bwd_kernel<<<grid, AB_THREADS, AttnBwdSmem::kTotal, st>>>(tm_kv, tm_q, tm_do, tm_dq, p);
   count_launch();

@@ -30,6 +30,8 @@ struct AttnFwdParams {
   float scale_log2;
   int* status;
   long long* prof;      // optional: 16 cycle counters written by CTA (0,0,0) (phase timing for tuning)
+  const uint32_t* sel;  // optional key-selection bits [B, T, T/32] (bit k of row q: query q may see key k)
+  const float* sink;    // optional per-head sink logit: adds exp(sink) to every row's softmax denominator
 };
 
 struct AttnFwdSmem {
@@ -181,6 +183,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
     for (int j = 0; j < ntiles && ok; ++j) {
       const int k0 = (k_lo + j) * AT_BK;
       const bool need_mask = (k0 + AT_BK - 1 > q0) || (p.window >= 0 && q0 + AT_BQ - 1 - k0 > p.window);
+      uint4 selw = make_uint4(~0u, ~0u, ~0u, ~0u);            // fetched before the wait for S
+      if (p.sel != nullptr && q < p.T)
+        selw = *reinterpret_cast<const uint4*>(p.sel + ((long long)b * p.T + q) * (p.T >> 5) + (k0 >> 5));
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_word));
       if (!ok) break;
       NGA_PROF(0);
@@ -200,6 +205,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
             const int key = k0 + c * 32 + i;
             if (key > q || (p.window >= 0 && q - key > p.window)) sv[c][i] = 0xff800000u;  // -inf
           }
+      }
+      if (p.sel != nullptr) {
+        const uint32_t w4[4] = {selw.x, selw.y, selw.z, selw.w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (!((w4[c] >> i) & 1u)) sv[c][i] = 0xff800000u;
       }
       // row maximum with four independent chains
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -280,6 +293,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(p_empty, (ntiles - 1) & 1, abort_word));
     if (ok) {
       tc_fence_after();
+      if (p.sink != nullptr) {                       // the sink takes probability mass but carries no value
+        const float s2 = p.sink[h] * 1.4426950408889634f;
+        if (m_ref == -INFINITY) {
+          m_ref = s2;
+          l_sum = 1.f;
+        } else {
+          l_sum += exp2f(s2 - m_ref);
+        }
+      }
       const float inv = 1.f / l_sum;
       const bool q_ok = q < p.T;
       __nv_bfloat16* orow = p.out + (long long)(row_base + q) * (p.Hq * AT_D) + q_col;
@@ -317,6 +339,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
 }  // namespace nga
 
 static long long* g_attn_prof = nullptr;
+static const uint32_t* g_attn_sel = nullptr;
+static const float* g_attn_sink = nullptr;
+// Key-selection bits and sink logits for the NEXT forward launch only (consumed by it).
+extern "C" void nga_attn_fwd_set_extras(const uint32_t* sel_bits, const float* sink) {
+  g_attn_sel = sel_bits;
+  g_attn_sink = sink;
+}
 // Tuning aid: when set, CTA (0,0,0) of the next forward launches writes per-phase cycle counts there.
 extern "C" void nga_attn_set_prof(long long* device_ptr) { g_attn_prof = device_ptr; }
 
@@ -343,6 +372,11 @@ extern "C" int nga_attn_fwd(const void* qkv, void* out, float* lse2, int B, int 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
   p.prof = g_attn_prof;
+  p.sel = g_attn_sel;
+  p.sink = g_attn_sink;
+  g_attn_sel = nullptr;
+  g_attn_sink = nullptr;
+  if (p.sel != nullptr && (T % 128)) return -7;     // rows of selection words are read 16 bytes at a time
   dim3 grid((T + AT_BQ - 1) / AT_BQ, Hq, B);
   attn_fwd_kernel<<<grid, AT_THREADS, AttnFwdSmem::kTotal, reinterpret_cast<cudaStream_t>(stream)>>>(tm, p);
   count_launch();

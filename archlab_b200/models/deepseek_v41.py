@@ -18,7 +18,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops import dsa, quant
+from ..ops import dsa, dsa_cuda, quant
 from . import moe
 from .blocks import RMSNorm, apply_rope, hc_split_sinkhorn, rms_norm, rope_tables
 
@@ -134,7 +134,10 @@ class SparseLatentAttention(nn.Module):
         if self.training and self.c.indexer_kl_weight > 0:
             target = dsa.main_attention_target(q, kv, scale)
             self.last_kl = dsa.indexer_kl(target, scores, torch.isfinite(scores))
-        if dense or S <= self.c.index_top_k:
+        use_dense = dense or S <= self.c.index_top_k
+        if dsa_cuda.kernel_supports(q, kv):                  # flash kernels with selection bits and sink
+            o = dsa_cuda.selected_sink_attention(q, kv, self.sink, None if use_dense else idx)
+        elif use_dense:
             o = dsa.dense_sink_attention(q, kv, self.sink, scale)
         else:
             o = dsa.sparse_attention(q, kv, self.sink, idx, scale)

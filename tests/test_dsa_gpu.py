@@ -1,0 +1,32 @@
+"""Selected-key sink attention on the flash kernels against the gather-based fp32 statement."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("top_k", [None, 96])
+def test_selected_sink_attention_forward_backward(top_k):
+    from archlab_b200.ops import dsa, dsa_cuda, native
+
+    torch.manual_seed(0)
+    B, T, H, D = 2, 256, 4, 128
+    q = (torch.randn(B, T, H, D, device="cuda") * 0.6).bfloat16().requires_grad_(True)
+    kv = (torch.randn(B, T, D, device="cuda") * 0.6).bfloat16().requires_grad_(True)
+    sink = (torch.randn(H, device="cuda") * 0.5).requires_grad_(True)
+    idx = None
+    if top_k is not None:
+        scores = torch.randn(B, T, T, device="cuda")
+        scores = scores.masked_fill(torch.arange(T, device="cuda")[None, :] > torch.arange(T, device="cuda")[:, None], float("-inf"))
+        idx, _ = dsa.select_topk(scores, top_k)
+    w = torch.randn(B, T, H, D, device="cuda")
+    o = dsa_cuda.selected_sink_attention(q, kv, sink, idx)
+    (o.float() * w).sum().backward()
+    native.check_status()
+    qf, kvf, sf = (t.detach().float().requires_grad_(True) for t in (q, kv, sink))
+    scale = D ** -0.5
+    ref = dsa.dense_sink_attention(qf, kvf, sf, scale) if idx is None else dsa.sparse_attention(qf, kvf, sf, idx, scale, recompute=False)
+    (ref * w).sum().backward()
+    rel = lambda a, b: ((a.float() - b).norm() / b.norm()).item()
+    assert rel(o, ref) < 2e-2
+    assert rel(q.grad, qf.grad) < 3e-2 and rel(kv.grad, kvf.grad) < 3e-2 and rel(sink.grad, sf.grad) < 3e-2
