@@ -42,3 +42,14 @@ int nga_gdn_fwd(const void* q, const void* k, const void* v, const float* g, con
 #ifdef __cplusplus
 }
 #endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+int nga_token_mix(const void* in_a, const void* in_b, const float* W, void* out, long long tokens, int na, int nb, int n_out, int C,
+                  int transpose_w, void* stream);
+int nga_token_mix_dw(const void* dout, const void* in_a, const void* in_b, float* dW, long long tokens, int na, int nb, int n_out,
+                     int C, void* stream);
+#ifdef __cplusplus
+}
+#endif

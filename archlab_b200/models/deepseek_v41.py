@@ -18,7 +18,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops import dsa, dsa_cuda, quant
+from ..ops import dsa, dsa_cuda, quant, stream_mix
 from . import moe
 from .blocks import RMSNorm, apply_rope, hc_split_sinkhorn, rms_norm, rope_tables
 
@@ -165,10 +165,9 @@ class HyperConnectionMix(nn.Module):
 
     def forward(self, streams: torch.Tensor, sublayer):
         pre, post, comb = self.coefficients(streams)
-        x = (streams.float() * pre.unsqueeze(-1)).sum(-2).to(streams.dtype)
+        x = stream_mix.hyper_connection_read(pre, streams)       # one fused pass on bf16 CUDA, einsum elsewhere
         y = sublayer(x)
-        out = comb.transpose(-1, -2) @ streams.float() + post.unsqueeze(-1) * y.float().unsqueeze(-2)
-        return out.to(streams.dtype)
+        return stream_mix.hyper_connection_write(comb, post, streams, y.to(streams.dtype))
 
 
 class V41Block(nn.Module):
