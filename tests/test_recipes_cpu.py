@@ -1,0 +1,40 @@
+"""Every shipped recipe loads through the loader of its schema."""
+from pathlib import Path
+
+import pytest
+
+from archlab_b200.contracts import experiment as E
+from archlab_b200.contracts.recipe import read_recipe
+from archlab_b200.contracts.spec import load_experiment
+
+ROOT = Path(__file__).resolve().parents[1] / "recipes"
+
+
+@pytest.mark.parametrize("ref,backend", [("reference/speedrun.yaml#d20", "speedrun"), ("reference/speedrun.yaml#d20-simplicial", "speedrun"),
+                                         ("reference/speedrun.yaml#d4-cpu", "speedrun"), ("reference/mesh.yaml#qwen35-4b-simplicial", "megatron"),
+                                         ("reference/mesh.yaml#v41-moe-ep8", "megatron"), ("reference/mesh.yaml#qwen38-flash-next", "megatron")])
+def test_layered_specs(ref, backend):
+    s = load_experiment(ROOT / ref)
+    assert s.backend == backend and s.parallelism["gpus_per_node"] >= 1 and s.training["sequence_length"] >= 256
+    assert set(s.config["paths"]) == {"data_root", "run_dir"}
+
+
+def test_inheritance_overrides_only_what_it_names():
+    base, child = load_experiment(ROOT / "reference/speedrun.yaml#d20"), load_experiment(ROOT / "reference/speedrun.yaml#d20-simplicial")
+    assert child.model["depth"] == base.model["depth"] == 20 and child.variant == "simplicial" and "simplicial_layers" in child.model
+
+
+def test_rl_recipes_and_overlay(monkeypatch):
+    monkeypatch.setenv("ARCHLAB_PARENT_CHECKPOINT", "/ckpt")
+    monkeypatch.setenv("ARCHLAB_DATA_MANIFEST", "/m.json")
+    e = E.read_experiment(ROOT / "rl/limite_code.yaml", [], overlays=[ROOT / "rl/limite_code_local.yaml"])
+    assert e.execution == "sync" and e.settings["data.train_batch_size"] == 8 and e.settings["actor_rollout_ref.rollout.n"] == 8
+    assert E.read_experiment(ROOT / "rl/qwen35_code.yaml", []).engine == "dp"
+
+
+def test_launch_catalog_and_study_contract():
+    cat = read_recipe(f"{ROOT / 'qwen/launches.yaml'}#flash-next-quarter-fp4")
+    assert cat["family"] == "flash-next" and cat["environment"]["NGA_PRECISION"] == "fp4"
+    with pytest.raises(ValueError):
+        read_recipe(ROOT / "qwen/launches.yaml")
+    assert read_recipe(ROOT / "deepseek_v41/scratch_w640_d20.yaml")["parallelism"]["expert"] == 8
