@@ -51,3 +51,13 @@ void nga_launch_count_reset(void);
 #ifdef __cplusplus
 }
 #endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+int nga_gemm2_fp8(const void* A, const void* B, void* D, const void* aux, int M, int N, int K, long long lda, long long ldb,
+                  long long ldd, long long ldaux, int a_e5m2, int b_e5m2, int epi, int out_fp32, int aux_fp32, float alpha,
+                  float beta, int* status, void* stream);
+#ifdef __cplusplus
+}
+#endif

@@ -68,6 +68,22 @@ __device__ __forceinline__ void umma2_bf16_ss(uint32_t tmem_d, uint64_t desc_a, 
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same with 8-bit floating-point operands (e4m3 / e5m2 selected in the instruction descriptor), K = 32.
+__device__ __forceinline__ void umma2_f8_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Instruction descriptor for kind::f8f6f4, fp32 accumulator, K-major operands; format 0 = e4m3, 1 = e5m2.
+__host__ __device__ constexpr uint32_t umma_idesc_f8(int m, int n, int a_fmt, int b_fmt) {
+  return (1u << 4) | (uint32_t(a_fmt & 7) << 7) | (uint32_t(b_fmt & 7) << 10) | (uint32_t(n >> 3) << 17) |
+         (uint32_t(m >> 4) << 24);
+}
 // One arrival on the barrier at this shared-memory offset in every CTA of `mask`, when all MMAs
 // issued so far have completed.
 __device__ __forceinline__ void umma2_commit_multicast(uint64_t* bar, uint16_t mask) {
@@ -176,7 +192,8 @@ __device__ __forceinline__ void tp_copy_role(const TpParams& tp, int K, uint8_t*
   }
 }
 
-template <int A_MN, int B_MN, int TP>
+// F8: 0 = bf16 operands; 1 + 2 * (A is e5m2) + 4 * (B is e5m2) = 8-bit operands (K-major only, 128 per k-block).
+template <int A_MN, int B_MN, int TP, int F8 = 0>
 __global__ void __launch_bounds__(G2_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const GemmParams p, const __grid_constant__ CUtensorMap tmA2, const TpParams tp,
@@ -200,7 +217,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
   const int num_m = (p.M + 2 * BM - 1) / (2 * BM);   // 256-row tiles
   const int num_n = (p.N + G2_BN - 1) / G2_BN;
-  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr int BKE = F8 ? 2 * BK : BK;             // elements per 128-byte k-block row
+  const int num_kb = (p.K + BKE - 1) / BKE;
   const int num_tiles = num_m * num_n * p.batch * p.splits;   // work items (tile x k-split)
 
   if (threadIdx.x == 0) {
@@ -268,14 +286,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             for (int j = 0; j < 2; ++j)
               tma_load_3d_pair(sA + j * 8192, mapA, leader_full, m0 + j * 64, kb * BK, b);
           } else {
-            tma_load_3d_pair(sA, mapA, leader_full, kb * BK, m0, b);
+            tma_load_3d_pair(sA, mapA, leader_full, kb * BKE, m0, b);
           }
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < 2; ++j)
               tma_load_3d_pair(sB + j * 8192, &tmB, leader_full, n0 + j * 64, kb * BK, b);
           } else {
-            tma_load_3d_pair(sB, &tmB, leader_full, kb * BK, n0, b);
+            tma_load_3d_pair(sB, &tmB, leader_full, kb * BKE, n0, b);
           }
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -284,7 +302,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader only)
     if (rank == 0 && lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, G2_BN, A_MN, B_MN);
+      constexpr uint32_t idesc = F8 ? umma_idesc_f8(2 * BM, G2_BN, (F8 >> 1) & 1, (F8 >> 2) & 1)
+                                    : umma_idesc_bf16(2 * BM, G2_BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -309,7 +328,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                                      : umma_smem_desc(sA + k * (UMMA_K * 2), 16, 1024);
             const uint64_t db = B_MN ? umma_smem_desc(sB + k * (UMMA_K * 128), 8192, 1024)
                                      : umma_smem_desc(sB + k * (UMMA_K * 2), 16, 1024);
-            umma2_bf16_ss(tmem_d, da, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
+            if (F8) umma2_f8_ss(tmem_d, da, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
+            else umma2_bf16_ss(tmem_d, da, db, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
           }
           umma2_commit_multicast(&empty_bar[stage], 3);
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1u; }
@@ -421,10 +441,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) atomicCAS(p.status, 0, *abort_word);
 }
 
-template <int A_MN, int B_MN, int TP>
+template <int A_MN, int B_MN, int TP, int F8 = 0>
 static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream,
                         const CUtensorMap& ta2, const TpParams& tp, const TpMaps& tpm) {
-  auto kern = gemm2_bf16_kernel<A_MN, B_MN, TP>;
+  auto kern = gemm2_bf16_kernel<A_MN, B_MN, TP, F8>;
   static int max_clusters = 0;
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
@@ -540,6 +560,40 @@ extern "C" int nga_gemm2_bf16(const void* A, const void* B, void* D, const void*
   if (a_mn && !b_mn) return launch_gemm2<1, 0, 0>(ta, tb, p, st, ta, tp, no_maps);
   if (!a_mn && b_mn) return launch_gemm2<0, 1, 0>(ta, tb, p, st, ta, tp, no_maps);
   return launch_gemm2<0, 0, 0>(ta, tb, p, st, ta, tp, no_maps);
+}
+
+// D[M, N] (bf16 or fp32) = alpha * A[M, K] B[N, K]^T with 8-bit floating-point operands (row-major, K contiguous,
+// K a multiple of 16 bytes); a_e5m2 / b_e5m2 select e5m2 instead of e4m3.  `alpha` carries the product of the two
+// tensor scales; epilogues as in nga_gemm2_bf16 (aux in bf16 / fp32).
+extern "C" int nga_gemm2_fp8(const void* A, const void* B, void* D, const void* aux, int M, int N, int K, long long lda,
+                             long long ldb, long long ldd, long long ldaux, int a_e5m2, int b_e5m2, int epi, int out_fp32,
+                             int aux_fp32, float alpha, float beta, int* status, void* stream) {
+  using namespace nga;
+  if (M <= 0 || N <= 0 || K <= 0) return -1;
+  if ((lda & 15) || (ldb & 15)) return -5;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_3d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, M, 1, lda, (long long)M * lda, 128, 128, true);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, K, N, 1, ldb, (long long)N * ldb, 128, 128, true);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.batch = 1;
+  p.D = D; p.aux = aux; p.ldd = ldd; p.ldaux = ldaux; p.sD = 0; p.sAux = 0;
+  p.epi = epi; p.out_fp32 = out_fp32; p.aux_fp32 = aux_fp32; p.alpha = alpha; p.beta = beta;
+  p.splits = 1;
+  if (epi == kEpiAtomicAdd) return -8;
+  p.status = status;
+  p.row_shift = 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  TpParams tp = {};
+  static const TpMaps no_maps = {};
+  const int f = 1 + 2 * (a_e5m2 ? 1 : 0) + 4 * (b_e5m2 ? 1 : 0);
+  switch (f) {
+    case 1: return launch_gemm2<0, 0, 0, 1>(ta, tb, p, st, ta, tp, no_maps);
+    case 3: return launch_gemm2<0, 0, 0, 3>(ta, tb, p, st, ta, tp, no_maps);
+    case 5: return launch_gemm2<0, 0, 0, 5>(ta, tb, p, st, ta, tp, no_maps);
+    default: return launch_gemm2<0, 0, 0, 7>(ta, tb, p, st, ta, tp, no_maps);
+  }
 }
 
 // Tensor-parallel GEMM fused with its collective (see TpParams).  A is K-major; B is K-major (b_mn = 0)
