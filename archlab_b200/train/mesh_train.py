@@ -123,6 +123,8 @@ def parse_args(argv=None):
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--run-dir", default="runs/mesh")
     ap.add_argument("--n-layer", type=int, default=0, help="override the preset's depth (0 keeps it)")
+    ap.add_argument("--save-every", type=int, default=0, help="write a per-rank checkpoint every N steps (0: never)")
+    ap.add_argument("--resume", action="store_true", help="continue from the newest checkpoint in --run-dir")
     return ap.parse_args(argv)
 
 
@@ -156,6 +158,8 @@ class _Job:
     def __init__(self, a, mesh: Mesh, groups: dict, device):
         self.mesh, self.groups, self.device = mesh, groups, device
         fam = a.model.split("_")[0]
+        if a.model.startswith("factory:"):
+            fam = "factory"
         if fam == "qwen35":
             from ..models.qwen35_tp import Qwen35TP
 
@@ -202,6 +206,17 @@ class _Job:
                     if ".experts." not in n:
                         dist.broadcast(p.data, mesh.rank_of(dp_i=0), group=ep_group)
             self.act_shape, self.vocab, self.kind = None, cfg.vocab_size, "ep"
+        elif a.model.startswith("factory:"):
+            # any registered architecture family under data parallelism (model(ids, labels) -> loss)
+            from ..models.factory import build_model
+
+            if mesh.tp > 1 or mesh.pp > 1 or mesh.cp > 1 or a.ep > 1:
+                raise ValueError("factory models run under data parallelism in this trainer")
+            torch.manual_seed(a.seed)
+            extra = {"sequence_len": a.seq_len}
+            self.model = build_model(a.model.split(":", 1)[1], extra, device=device)
+            self.act_shape, self.kind = None, "dp"
+            self.vocab = int(getattr(self.model.config, "vocab_size"))
         else:
             raise ValueError(f"unknown model family {fam}")
         if device.type == "cuda":
@@ -260,6 +275,79 @@ class MasterAdamW:
         for p, w in zip(self.params, self.master):
             p.copy_(w)
             p.grad = None
+
+
+# ------------------------------------------------------------------------------------------------
+# run contract, checkpoints
+# ------------------------------------------------------------------------------------------------
+CONTRACT_KEYS = ("model", "tp", "pp", "cp", "ep", "micro_batch", "global_batch", "seq_len", "precision", "seed", "n_layer")
+
+
+def run_contract(a, world: int) -> dict:
+    """What must not change between the attempts of one run (a resume under a different contract is refused)."""
+    return {"format": "archlab-mesh-run-v1", "world_size": world, **{k: getattr(a, k) for k in CONTRACT_KEYS}}
+
+
+def check_contract(run_dir: Path, contract: dict, resume: bool) -> int:
+    """Writes RUN_CONTRACT.json on the first attempt, contracts/attempt-N.json on every attempt and
+    LATEST_CONTRACT.json; returns the attempt number."""
+    path = run_dir / "RUN_CONTRACT.json"
+    (run_dir / "contracts").mkdir(parents=True, exist_ok=True)
+    if path.exists():
+        old = json.loads(path.read_text())
+        if not resume:
+            raise FileExistsError(f"{run_dir} already holds a run; pass --resume or choose a new directory")
+        diff = sorted(k for k in set(old) | set(contract) if old.get(k) != contract.get(k))
+        if diff:
+            raise ValueError(f"resume contract differs in {diff}")
+    else:
+        if resume:
+            raise FileNotFoundError("nothing to resume: no RUN_CONTRACT.json")
+        path.write_text(json.dumps(contract, indent=2, sort_keys=True))
+    attempt = len(list((run_dir / "contracts").glob("attempt-*.json"))) + 1
+    (run_dir / "contracts" / f"attempt-{attempt}.json").write_text(json.dumps({**contract, "attempt": attempt, "time": time.time()},
+                                                                              indent=2, sort_keys=True))
+    (run_dir / "LATEST_CONTRACT.json").write_text(json.dumps({**contract, "attempt": attempt}, indent=2, sort_keys=True))
+    return attempt
+
+
+def save_checkpoint(run_dir: Path, step: int, rank: int, job, opt) -> None:
+    """Every rank writes its own model shard and optimizer slice; rank 0 writes the step marker LAST."""
+    d = run_dir / "checkpoints" / f"step_{step:07d}"
+    d.mkdir(parents=True, exist_ok=True)
+    state = {"step": step, "model": job.model.state_dict(), "zero": opt.zero.state_dict(),
+             "experts": None if opt.experts is None else {"t": opt.experts.t, "master": opt.experts.master, "m": opt.experts.m,
+                                                          "v": opt.experts.v},
+             "rng": torch.get_rng_state()}
+    tmp = d / f".rank{rank:03d}.pt.tmp"
+    torch.save(state, tmp)
+    os.replace(tmp, d / f"rank{rank:03d}.pt")
+    if dist.is_initialized():
+        dist.barrier()
+    if rank == 0:
+        (run_dir / "checkpoints" / "latest_checkpointed_iteration.txt").write_text(f"{step}\n")
+
+
+def load_checkpoint(run_dir: Path, rank: int, job, opt) -> int:
+    marker = run_dir / "checkpoints" / "latest_checkpointed_iteration.txt"
+    if not marker.exists():
+        return 0
+    step = int(marker.read_text().strip())
+    state = torch.load(run_dir / "checkpoints" / f"step_{step:07d}" / f"rank{rank:03d}.pt", map_location="cpu", weights_only=False)
+    opt.zero.load_state_dict(state["zero"])
+    with torch.no_grad():                                    # parameters are views of the flat buffer: copy in place
+        for name, p in job.model.named_parameters():
+            p.copy_(state["model"][name])
+        for name, b in job.model.named_buffers():
+            if name in state["model"]:
+                b.copy_(state["model"][name])
+    if opt.experts is not None and state["experts"] is not None:
+        e = state["experts"]
+        opt.experts.t = e["t"]
+        for dst, src in zip(opt.experts.master + opt.experts.m + opt.experts.v, e["master"] + e["m"] + e["v"]):
+            dst.copy_(src)
+    torch.set_rng_state(state["rng"])
+    return step
 
 
 # ------------------------------------------------------------------------------------------------
@@ -331,12 +419,23 @@ def train(a, *, on_step=None) -> list[float]:
     links = ppar.StageLinks(mesh.pp_i, mesh.pp, mesh.rank_of(pp_i=mesh.pp_i - 1) if mesh.pp_i else None,
                             mesh.rank_of(pp_i=mesh.pp_i + 1) if mesh.pp_i + 1 < mesh.pp else None)
     run_dir = Path(os.environ.get(a.run_dir[4:], "runs/mesh") if a.run_dir.startswith("env:") else a.run_dir)
-    log = None
+    log, receipts = None, None
     if rank == 0:
+        from ..ckpt.formats import RunReceipts
+
         run_dir.mkdir(parents=True, exist_ok=True)
+        attempt = check_contract(run_dir, run_contract(a, world), a.resume)
         (run_dir / "config.json").write_text(json.dumps({"args": vars(a), "world_size": world, "data_parallel": mesh.dp,
-                                                         "grad_accum_steps": accum}, indent=2))
+                                                         "grad_accum_steps": accum, "attempt": attempt}, indent=2))
+        (run_dir / "PARALLELISM.json").write_text(json.dumps({"tensor": mesh.tp, "pipeline": mesh.pp, "context": mesh.cp,
+                                                              "expert": a.ep, "data": mesh.dp, "world_size": world,
+                                                              "order": "tensor fastest, then context, data, pipeline"}, indent=2))
+        (run_dir / "MODEL_SHAPES.json").write_text(json.dumps({n: list(p.shape) for n, p in job.model.named_parameters()}, indent=1))
+        receipts = RunReceipts(run_dir, {"args": vars(a), "world_size": world})
         log = open(run_dir / "metrics_rank0.jsonl", "a")
+    if world > 1:
+        dist.barrier()                                           # a refused contract stops every rank at the next collective
+    start = load_checkpoint(run_dir, rank, job, opt) if a.resume else 0
     from ..data.synthetic import ZipfTokens
 
     # every rank of a (tensor, context, pipeline) slice reads the data of its data-parallel index
@@ -345,7 +444,7 @@ def train(a, *, on_step=None) -> list[float]:
     losses = []
     scale = 1.0 / (accum * mesh.dp)
     cuda = device.type == "cuda"
-    for step in range(a.steps):
+    for step in range(start, a.steps):
         t0 = time.perf_counter()
         if cuda:
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -391,6 +490,10 @@ def train(a, *, on_step=None) -> list[float]:
             log.flush()
         if on_step is not None:
             on_step(step, losses[-1])
+        if a.save_every and ((step + 1) % a.save_every == 0 or step + 1 == a.steps):
+            save_checkpoint(run_dir, step + 1, rank, job, opt)
+    if receipts is not None:
+        receipts.finish({"final_loss": losses[-1] if losses else None, "steps": a.steps})
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -79,3 +79,36 @@ def test_zero_adamw_matches_torch_adamw():
         ref.step()
     for p, q in zip(a.parameters(), b.parameters()):
         assert torch.allclose(p, q, atol=1e-5, rtol=1e-4)
+
+
+def test_resume_reproduces_the_uninterrupted_run_and_contract_is_enforced(tmp_path, monkeypatch):
+    from archlab_b200.train import mesh_train
+
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(k, raising=False)
+    base = ["--model=qwen35_tiny_dense", "--seq-len=32", "--global-batch=2", "--lr=3e-3", "--save-every=2"]
+    full = mesh_train.train(mesh_train.parse_args(base + ["--steps=4", f"--run-dir={tmp_path / 'a'}"]))
+    mesh_train.train(mesh_train.parse_args(base + ["--steps=2", f"--run-dir={tmp_path / 'b'}"]))
+    # the contract pins everything but the step budget; a finished run directory is closed for good
+    with pytest.raises(FileExistsError):
+        mesh_train.train(mesh_train.parse_args(base + ["--steps=4", f"--run-dir={tmp_path / 'b'}"]))
+    (tmp_path / "b" / "COMPLETE.json").unlink()
+    with pytest.raises(ValueError):
+        mesh_train.train(mesh_train.parse_args(base[:1] + ["--seq-len=64"] + base[2:] + ["--steps=4", "--resume", f"--run-dir={tmp_path / 'b'}"]))
+    rest = mesh_train.train(mesh_train.parse_args(base + ["--steps=4", "--resume", f"--run-dir={tmp_path / 'b'}"]))
+    assert len(rest) == 2 and rest == pytest.approx(full[2:], abs=1e-6)
+    assert (tmp_path / "b" / "PARALLELISM.json").exists() and (tmp_path / "b" / "COMPLETE.json").exists()
+    assert len(list((tmp_path / "b" / "contracts").glob("attempt-*.json"))) == 2
+
+
+def test_factory_family_under_data_parallelism(tmp_path, monkeypatch):
+    from archlab_b200.train import mesh_train
+
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(k, raising=False)
+    from archlab_b200.models.factory import families
+
+    fam = "nanochat" if "nanochat" in families() else families()[0]
+    losses = mesh_train.train(mesh_train.parse_args([f"--model=factory:{fam}", "--seq-len=32", "--global-batch=2", "--micro-batch=2",
+                                                     "--steps=3", f"--run-dir={tmp_path}"]))
+    assert len(losses) == 3 and all(l == l for l in losses)
