@@ -10,7 +10,7 @@ import torch
 
 
 def _registry() -> dict[str, tuple[type, type]]:
-    from . import deepseek_v41, kimi, nanochat, qwen35, qwen38
+    from . import deepseek_v41, frontier, kimi, limite, nanochat, qwen35, qwen38, sota
 
     return {
         "nanochat": (nanochat.GPTConfig, nanochat.GPT),
@@ -24,7 +24,14 @@ def _registry() -> dict[str, tuple[type, type]]:
         "qwen38_flash_next_quarter": (qwen38.Qwen38Config, qwen38.Qwen38LM),
         "qwen38_tiny": (qwen38.Qwen38Config, qwen38.Qwen38LM),
         "deepseek_v41": (deepseek_v41.V41Config, deepseek_v41.V41LM),
+        "frontier": (frontier.FrontierConfig, frontier.FrontierLM),
+        "sota": (sota.SotaConfig, sota.SotaLM),
+        "fog": (sota.SotaConfig, sota.SotaLM),
+        "limite": (limite.LimiteConfig, limite.LimiteLM),
     }
+
+
+_EAGER_FAMILIES = frozenset({"frontier", "sota", "fog", "limite"})
 
 
 def families() -> list[str]:
@@ -63,9 +70,13 @@ def build_model(arch_family: str, config: dict[str, Any] | None = None, *, devic
     kw = patch_config(arch_family, dict(config or {}))
     kw.pop("__dropped__", None)
     cfg = cfg_cls(**kw)
-    with torch.device("meta"):
-        model = model_cls(cfg, **model_kwargs)
-    model.to_empty(device=device)
+    if arch_family in _EAGER_FAMILIES:
+        # constructors of these families set scalar gains, biases and fixed feature banks themselves
+        model = model_cls(cfg, **model_kwargs).to(device)
+    else:
+        with torch.device("meta"):
+            model = model_cls(cfg, **model_kwargs)
+        model.to_empty(device=device)
     if init and hasattr(model, "init_weights"):
         model.init_weights()
     return model
