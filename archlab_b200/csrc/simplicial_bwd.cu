@@ -628,32 +628,43 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
     bool ok = true;
     const bool prof = pk.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 6 && lane == 0;
     long long bw = 0, bb = 0;
+    // The rows of step it + 1 are fetched into registers BEFORE waiting for their buffer: the L2 latency of
+    // the 32 loads per thread overlaps the wait instead of following it.
+    uint4 qv[8], kv[8], gv[8], vv[8];
+    float n_lse = INFINITY, n_del = 0.f;
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    auto fetch = [&](int it) {
+      const int i = q_lo + it * QS + qi;
+      const int p1 = i - W1 + 1 + jj;
+      const bool valid = (i <= q_last) && (p1 >= 0);
+      const long long qrow_idx = row_base + min(i, p.N - 1);
+      const long long krow_idx = row_base + max(p1, 0);
+      const __nv_bfloat16* qrow = p.q + qrow_idx * p.ldq + hq * SB_D + half * 64;
+      const __nv_bfloat16* k1row = p.k1 + krow_idx * p.ldk1 + hk * SB_D + half * 64;
+      const __nv_bfloat16* v1row = p.v1 + krow_idx * p.ldv1 + hk * SB_D + half * 64;
+      const __nv_bfloat16* dorow = p.dout + qrow_idx * p.lddo + hq * SB_D + half * 64;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        qv[ch] = valid ? *reinterpret_cast<const uint4*>(qrow + ch * 8) : zero4;
+        kv[ch] = valid ? *reinterpret_cast<const uint4*>(k1row + ch * 8) : zero4;
+        gv[ch] = valid ? *reinterpret_cast<const uint4*>(dorow + ch * 8) : zero4;
+        vv[ch] = valid ? *reinterpret_cast<const uint4*>(v1row + ch * 8) : zero4;
+      }
+      if (half == 0) {
+        const long long stat = ((long long)b * p.Hq + hq) * p.N + min(i, p.N - 1);
+        n_lse = valid ? p.lse2[stat] : INFINITY;
+        n_del = valid ? p.delta[stat] : 0.f;
+      }
+    };
+    if (total > 0) fetch(0);
     for (int it = 0; it < total && ok; ++it) {
       const int buf = it & 1;
       const long long b0 = clock64();
       ok = __all_sync(0xffffffffu, mbar_wait(&ag_empty[buf], ((it >> 1) & 1) ^ 1u, abort_word));
       if (!ok) break;
       const long long b1 = clock64();
-      const int i = q_lo + it * QS + qi;
-      const int p1 = i - W1 + 1 + jj;
-      const bool valid = (i <= q_last) && (p1 >= 0);
-      const long long qrow_idx = row_base + min(i, p.N - 1);
-      const long long krow_idx = row_base + max(p1, 0);
       uint8_t* tA = smem + S::kA + buf * 16384 + half * 8192 + c * 128;     // a [64 x 128] group: two 8 KB halves
       uint8_t* tG = smem + S::kG + buf * 16384 + half * 8192 + c * 128;
-      const __nv_bfloat16* qrow = p.q + qrow_idx * p.ldq + hq * SB_D + half * 64;
-      const __nv_bfloat16* k1row = p.k1 + krow_idx * p.ldk1 + hk * SB_D + half * 64;
-      const __nv_bfloat16* v1row = p.v1 + krow_idx * p.ldv1 + hk * SB_D + half * 64;
-      const __nv_bfloat16* dorow = p.dout + qrow_idx * p.lddo + hq * SB_D + half * 64;
-      uint4 qv[8], kv[8], gv[8], vv[8];
-      const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {                    // all loads first (see build_product_row)
-        qv[ch] = valid ? *reinterpret_cast<const uint4*>(qrow + ch * 8) : zero4;
-        kv[ch] = valid ? *reinterpret_cast<const uint4*>(k1row + ch * 8) : zero4;
-        gv[ch] = valid ? *reinterpret_cast<const uint4*>(dorow + ch * 8) : zero4;
-        vv[ch] = valid ? *reinterpret_cast<const uint4*>(v1row + ch * 8) : zero4;
-      }
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
         const int off = (ch ^ (c & 7)) * 16;
@@ -661,13 +672,13 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
         *reinterpret_cast<uint4*>(tG + off) = mul_bf16x8(gv[ch], vv[ch]);
       }
       if (half == 0) {
-        const long long stat = ((long long)b * p.Hq + hq) * p.N + min(i, p.N - 1);
-        s_vec[buf * 128 + c] = valid ? p.lse2[stat] : INFINITY;
-        s_vec[buf * 128 + 64 + c] = valid ? p.delta[stat] : 0.f;
+        s_vec[buf * 128 + c] = n_lse;
+        s_vec[buf * 128 + 64 + c] = n_del;
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ag_full[buf]);
+      if (it + 1 < total) fetch(it + 1);
       if (prof) { bw += b1 - b0; bb += clock64() - b1; }
     }
     if (prof) { pk.prof[8] = bw; pk.prof[9] = bb; }
