@@ -87,6 +87,20 @@ def bench_gemm(t: Timer, small: bool):
             _emit(f"gemm_{name}_cublas", ms, flops=2.0 * M * N * K)
 
 
+def bench_fp8(t: Timer, small: bool):
+    """8-bit tensor-core GEMM (tensor scales); the roofline fraction is against the bf16 peak (dense fp8 is twice that)."""
+    from .ops import fp8
+
+    cases = [("nt_fc_fwd", 32768, 5120, 1280), ("nt_8192", 8192, 8192, 8192), ("nt_dgrad", 32768, 1280, 5120)]
+    if small:
+        cases = [("nt_small", 8192, 5120, 1280)]
+    for name, M, N, K in cases:
+        a = torch.randn(M, K, device="cuda").to(fp8.E4M3)
+        b = torch.randn(N, K, device="cuda").to(fp8.E4M3)
+        ms = t(lambda: fp8.fp8_gemm(a, b, 1.0))
+        _emit(f"fp8_gemm_{name}", ms, flops=2.0 * M * N * K, extra={"M": M, "N": N, "K": K})
+
+
 def bench_attention(t: Timer, small: bool):
     from .ops import trunk
 
@@ -162,14 +176,14 @@ def bench_trunk(t: Timer, small: bool):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "attention", "simplicial", "trunk", "delta", "all"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "fp8", "attention", "simplicial", "trunk", "delta", "all"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
     from .ops import native
 
     t = Timer(a.iters)
-    ops = {"gemm": bench_gemm, "attention": bench_attention, "simplicial": bench_simplicial, "trunk": bench_trunk, "delta": bench_delta}
+    ops = {"gemm": bench_gemm, "fp8": bench_fp8, "attention": bench_attention, "simplicial": bench_simplicial, "trunk": bench_trunk, "delta": bench_delta}
     for name, fn in ops.items():
         if a.op in (name, "all"):
             fn(t, a.small)

@@ -462,7 +462,7 @@ simplicial_bwd_q_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
 // ================================================================================================
 constexpr int SK_BK = 128;           // keys per CTA
 constexpr int SK_ROWS = 64;          // rows (query, short key) per inner step
-constexpr int SK_THREADS = 320;      // TMA warp, MMA warp, 4 compute warps, 4 builder warps
+constexpr int SK_THREADS = 448;      // TMA warp, MMA warp, 8 compute warps (two per scheduler), 4 builder warps
 
 struct SimpBwdKParams {
   SimpBwdParams c;
@@ -528,9 +528,9 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
       mbar_init(&ag_full[i], 4);
       mbar_init(&ag_empty[i], 1);
       mbar_init(&st_full[i], 1);
-      mbar_init(&st_free[i], 4);
+      mbar_init(&st_free[i], 8);
     }
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, 8);
     mbar_init(pds_empty, 1);
     *abort_word = 0;
     fence_mbar_init();
@@ -620,17 +620,22 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
         umma_commit(pds_empty);
       }
     }
-  } else if (warp >= 6) {
+  } else if (warp >= 10) {
     // ---------------------------------------------------------------- builder warps: half a row each
-    const int tid = (warp - 6) * 32 + lane;               // 0..127
+    const int tid = (warp - 10) * 32 + lane;              // 0..127
     const int c = tid >> 1, half = tid & 1;               // row of the group, 64-column half
     const int qi = c >> sh, jj = c & (W1 - 1);
     bool ok = true;
-    const bool prof = pk.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 6 && lane == 0;
+    const bool prof = pk.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && warp == 10 && lane == 0;
     long long bw = 0, bb = 0;
     // The rows of step it + 1 are fetched into registers BEFORE waiting for their buffer: the L2 latency of
     // the 32 loads per thread overlaps the wait instead of following it.
-    uint4 qv[8], kv[8], gv[8], vv[8];
+    // (k1 / v1 rows only: the q / dO rows are shared by the w1 rows of a query and hit in L1, they are read after
+    // the wait so that 64 instead of 128 registers stay live across it)
+    uint4 kv[8], vv[8];
+    const __nv_bfloat16* n_qrow = p.q;
+    const __nv_bfloat16* n_dorow = p.dout;
+    bool n_valid = false;
     float n_lse = INFINITY, n_del = 0.f;
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
     auto fetch = [&](int it) {
@@ -639,15 +644,14 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
       const bool valid = (i <= q_last) && (p1 >= 0);
       const long long qrow_idx = row_base + min(i, p.N - 1);
       const long long krow_idx = row_base + max(p1, 0);
-      const __nv_bfloat16* qrow = p.q + qrow_idx * p.ldq + hq * SB_D + half * 64;
+      n_qrow = p.q + qrow_idx * p.ldq + hq * SB_D + half * 64;
+      n_dorow = p.dout + qrow_idx * p.lddo + hq * SB_D + half * 64;
+      n_valid = valid;
       const __nv_bfloat16* k1row = p.k1 + krow_idx * p.ldk1 + hk * SB_D + half * 64;
       const __nv_bfloat16* v1row = p.v1 + krow_idx * p.ldv1 + hk * SB_D + half * 64;
-      const __nv_bfloat16* dorow = p.dout + qrow_idx * p.lddo + hq * SB_D + half * 64;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
-        qv[ch] = valid ? *reinterpret_cast<const uint4*>(qrow + ch * 8) : zero4;
         kv[ch] = valid ? *reinterpret_cast<const uint4*>(k1row + ch * 8) : zero4;
-        gv[ch] = valid ? *reinterpret_cast<const uint4*>(dorow + ch * 8) : zero4;
         vv[ch] = valid ? *reinterpret_cast<const uint4*>(v1row + ch * 8) : zero4;
       }
       if (half == 0) {
@@ -665,11 +669,18 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
       const long long b1 = clock64();
       uint8_t* tA = smem + S::kA + buf * 16384 + half * 8192 + c * 128;     // a [64 x 128] group: two 8 KB halves
       uint8_t* tG = smem + S::kG + buf * 16384 + half * 8192 + c * 128;
+      {
+        uint4 qv[8];
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        const int off = (ch ^ (c & 7)) * 16;
-        *reinterpret_cast<uint4*>(tA + off) = mul_bf16x8(qv[ch], kv[ch]);
-        *reinterpret_cast<uint4*>(tG + off) = mul_bf16x8(gv[ch], vv[ch]);
+        for (int ch = 0; ch < 8; ++ch) qv[ch] = n_valid ? *reinterpret_cast<const uint4*>(n_qrow + ch * 8) : zero4;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch)
+          *reinterpret_cast<uint4*>(tA + (ch ^ (c & 7)) * 16) = mul_bf16x8(qv[ch], kv[ch]);
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) qv[ch] = n_valid ? *reinterpret_cast<const uint4*>(n_dorow + ch * 8) : zero4;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch)
+          *reinterpret_cast<uint4*>(tG + (ch ^ (c & 7)) * 16) = mul_bf16x8(qv[ch], vv[ch]);
       }
       if (half == 0) {
         s_vec[buf * 128 + c] = n_lse;
@@ -683,8 +694,10 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
     }
     if (prof) { pk.prof[8] = bw; pk.prof[9] = bb; }
   } else {
-    // ---------------------------------------------------------------- compute warps: thread = key
+    // ---------------------------------------------------------------- compute warps: thread = key; warps 2..5 own
+    // columns 0..31 of the 64-row step, warps 6..9 columns 32..63, so that every scheduler has two of them
     const int quarter = warp & 3;
+    const int chalf = (warp - 2) >> 2;
     const int t = quarter * 32 + lane;
     const int kp = k0 + t;
     const uint32_t lane_off = uint32_t(quarter * 32) << 16;
@@ -702,11 +715,9 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
       if (!ok) break;
       tc_fence_after();
       const long long c1 = clock64();
-      uint32_t sv[2][32], dv[2][32];
-      tmem_ld_32x32(tmem_ST + uint32_t(buf * 64) + lane_off, sv[0]);
-      tmem_ld_32x32(tmem_ST + uint32_t(buf * 64 + 32) + lane_off, sv[1]);
-      tmem_ld_32x32(tmem_dPT + uint32_t(buf * 64) + lane_off, dv[0]);
-      tmem_ld_32x32(tmem_dPT + uint32_t(buf * 64 + 32) + lane_off, dv[1]);
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32(tmem_ST + uint32_t(buf * 64 + chalf * 32) + lane_off, sv);
+      tmem_ld_32x32(tmem_dPT + uint32_t(buf * 64 + chalf * 32) + lane_off, dv);
       tmem_ld_wait();
       const long long c2 = clock64();
       tc_fence_before();
@@ -725,8 +736,8 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
         const int i = i_start + qq;
         qmask[qq] = (kp <= i) && (kp > i - p.w2);
       }
-#pragma unroll
-      for (int c2 = 0; c2 < 2; ++c2) {
+      {
+        const int c2 = chalf;
 #pragma unroll
         for (int gq = 0; gq < 4; ++gq) {
           float ls[8], dl[8];
@@ -739,9 +750,9 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
           for (int e = 0; e < 8; ++e) {
             const int col = c2 * 32 + gq * 8 + e;
             const float l = qmask[col >> sh] ? ls[e] : INFINITY;        // masked or padded row: exp2(-inf) = 0
-            const float pv = ex2_approx(fmaf(__uint_as_float(sv[c2][gq * 8 + e]), p.scale_log2, -l));
+            const float pv = ex2_approx(fmaf(__uint_as_float(sv[gq * 8 + e]), p.scale_log2, -l));
             pr[e] = pv;
-            ds[e] = (pv * p.scale) * (__uint_as_float(dv[c2][gq * 8 + e]) - dl[e]);
+            ds[e] = (pv * p.scale) * (__uint_as_float(dv[gq * 8 + e]) - dl[e]);
           }
           const int chunk = (c2 * 4 + gq) ^ (t & 7);
           uint4 u, w;
@@ -778,7 +789,7 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
       float* dkacc = pk.dk2_acc + krow * ((long long)p.Hkv * SB_D) + hk * SB_D;
       float* dvacc = pk.dv2_acc + krow * ((long long)p.Hkv * SB_D) + hk * SB_D;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = chalf * 2; c < chalf * 2 + 2; ++c) {          // each warp of a lane quarter stores half the channels
         uint32_t a[32], v[32];
         tmem_ld_32x32(tmem_dK + lane_off + c * 32, a);
         tmem_ld_32x32(tmem_dV + lane_off + c * 32, v);

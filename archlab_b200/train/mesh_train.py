@@ -436,6 +436,13 @@ def train(a, *, on_step=None) -> list[float]:
     if world > 1:
         dist.barrier()                                           # a refused contract stops every rank at the next collective
     start = load_checkpoint(run_dir, rank, job, opt) if a.resume else 0
+    from . import health
+
+    if world > 1:
+        health.collective_probe(device, timeout_seconds=300.0)   # an absent rank fails here, not in the first step
+    guard = health.FiniteGuard(device)
+    stop = health.StopConsensus(run_dir, device)
+    beat = health.Heartbeat(run_dir, rank=rank)
     from ..data.synthetic import ZipfTokens
 
     # every rank of a (tensor, context, pipeline) slice reads the data of its data-parallel index
@@ -481,6 +488,8 @@ def train(a, *, on_step=None) -> list[float]:
         else:
             dt = time.perf_counter() - t0
         losses.append(float(loss))
+        guard.check(step + 1, losses[-1], gnorm)
+        beat.beat(step=step + 1, loss=losses[-1])
         if log is not None:
             log.write(json.dumps({"step": step + 1, "loss": losses[-1], "grad_norm": gnorm, "step_seconds": dt,
                                   "tokens_per_second": a.global_batch * a.seq_len / dt,
@@ -490,8 +499,12 @@ def train(a, *, on_step=None) -> list[float]:
             log.flush()
         if on_step is not None:
             on_step(step, losses[-1])
-        if a.save_every and ((step + 1) % a.save_every == 0 or step + 1 == a.steps):
+        stopping = stop.should_stop()
+        if (a.save_every and ((step + 1) % a.save_every == 0 or step + 1 == a.steps)) or stopping:
             save_checkpoint(run_dir, step + 1, rank, job, opt)
+        if stopping:                                             # every rank leaves at the same step, after the checkpoint
+            stop.acknowledge(step + 1, rank)
+            break
     if receipts is not None:
         receipts.finish({"final_loss": losses[-1] if losses else None, "steps": a.steps})
     if world > 1:

@@ -112,3 +112,23 @@ def test_factory_family_under_data_parallelism(tmp_path, monkeypatch):
     losses = mesh_train.train(mesh_train.parse_args([f"--model=factory:{fam}", "--seq-len=32", "--global-batch=2", "--micro-batch=2",
                                                      "--steps=3", f"--run-dir={tmp_path}"]))
     assert len(losses) == 3 and all(l == l for l in losses)
+
+
+def test_stop_request_checkpoints_and_leaves_cleanly(tmp_path, monkeypatch):
+    from archlab_b200.train import mesh_train
+
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(k, raising=False)
+    run = tmp_path / "r"
+    run.mkdir()
+
+    def on_step(step, loss):
+        if step == 1:
+            (run / "STOP_REQUESTED.json").write_text("{}")
+
+    argv = ["--model=qwen35_tiny_dense", "--seq-len=32", "--global-batch=2", "--steps=6", f"--run-dir={run}"]
+    (run / "placeholder").write_text("")                          # a non-empty directory without a contract is a fresh run
+    losses = mesh_train.train(mesh_train.parse_args(argv), on_step=on_step)
+    assert len(losses) == 2
+    assert json.loads((run / "STOPPED.json").read_text())["step"] == 2
+    assert (run / "checkpoints" / "latest_checkpointed_iteration.txt").read_text().strip() == "2" and (run / "HEARTBEAT.json").exists()
