@@ -14,6 +14,7 @@
 #include "host_util.h"
 #include "attention.h"
 #include <cuda.h>
+#include <cstdlib>
 
 namespace nga {
 
@@ -32,6 +33,7 @@ struct AttnFwdParams {
   long long* prof;      // optional: 16 cycle counters written by CTA (0,0,0) (phase timing for tuning)
   const uint32_t* sel;  // optional key-selection bits [B, T, T/32] (bit k of row q: query q may see key k)
   const float* sink;    // optional per-head sink logit: adds exp(sink) to every row's softmax denominator
+  int p_tmem;           // 1: P goes back to the tensor core through TMEM (A operand of P V), not shared memory
 };
 
 struct AttnFwdSmem {
@@ -157,11 +159,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
         const uint32_t sV = smem_u32(smem + S::kV + (j & 1) * AT_TILE_BYTES);
 #pragma unroll
         for (int k = 0; k < AT_BK / 16; ++k) {
-          // A = P: K-major, keys contiguous, two 64-key blocks of 16 KB.
+          // A = P: K-major, keys contiguous, two 64-key blocks of 16 KB (or, in TMEM, 8 columns of bf16 pairs
+          // per 16 keys inside the S buffer of this tile).
           // B = V: MN-major, rows are keys (128 B = 64 d), the two 64-wide d blocks 16 KB apart.
-          const uint64_t da = umma_smem_desc(sP + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
           const uint64_t db = umma_smem_desc(sV + k * 2048, 16384, 1024);
-          umma_bf16_ss(tmem_O, da, db, idesc_pv, (j | k) != 0 ? 1u : 0u);
+          if (p.p_tmem) {
+            umma_bf16_ts(tmem_O, tmem_S0 + uint32_t((j & 1) * 128 + k * 8), db, idesc_pv, (j | k) != 0 ? 1u : 0u);
+          } else {
+            const uint64_t da = umma_smem_desc(sP + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+            umma_bf16_ss(tmem_O, da, db, idesc_pv, (j | k) != 0 ? 1u : 0u);
+          }
         }
         umma_commit(&kv_empty[j & 1]);
         umma_commit(p_empty);
@@ -262,19 +269,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm, const AttnFwdParams p) {
           pr[i] = ex2_fast(fmaf(__uint_as_float(sv[c][i]), p.scale_log2, -m_sub));
           ps4[i & 3] += pr[i];
         }
-        // 32 keys = 64 B = four 16-byte chunks of this row's 128-byte line in key block (c >> 1)
-        uint8_t* line = sP + (c >> 1) * 16384 + r * 128;
+        if (p.p_tmem) {
+          // 32 keys = 16 columns of packed pairs, written over the (already consumed) scores of this tile
+          uint32_t pk[16];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int chunk = ((c & 1) * 4 + g) ^ (r & 7);
-          uint4 u;
-          u.x = pack_bf16(pr[8 * g + 0], pr[8 * g + 1]);
-          u.y = pack_bf16(pr[8 * g + 2], pr[8 * g + 3]);
-          u.z = pack_bf16(pr[8 * g + 4], pr[8 * g + 5]);
-          u.w = pack_bf16(pr[8 * g + 6], pr[8 * g + 7]);
-          *reinterpret_cast<uint4*>(line + chunk * 16) = u;
+          for (int g = 0; g < 16; ++g) pk[g] = pack_bf16(pr[2 * g], pr[2 * g + 1]);
+          tmem_st_32x16(tS + c * 16, pk);
+        } else {
+          // 32 keys = 64 B = four 16-byte chunks of this row's 128-byte line in key block (c >> 1)
+          uint8_t* line = sP + (c >> 1) * 16384 + r * 128;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int chunk = ((c & 1) * 4 + g) ^ (r & 7);
+            uint4 u;
+            u.x = pack_bf16(pr[8 * g + 0], pr[8 * g + 1]);
+            u.y = pack_bf16(pr[8 * g + 2], pr[8 * g + 3]);
+            u.z = pack_bf16(pr[8 * g + 4], pr[8 * g + 5]);
+            u.w = pack_bf16(pr[8 * g + 6], pr[8 * g + 7]);
+            *reinterpret_cast<uint4*>(line + chunk * 16) = u;
+          }
         }
       }
+      if (p.p_tmem) tmem_st_wait();
       const float psum = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
       l_sum += psum;
       NGA_PROF(4);
@@ -374,6 +390,14 @@ extern "C" int nga_attn_fwd(const void* qkv, void* out, float* lse2, int B, int 
   p.prof = g_attn_prof;
   p.sel = g_attn_sel;
   p.sink = g_attn_sink;
+  {
+    static int p_tmem = -1;                        // NGA_ATTN_P_TMEM=1 selects the TMEM route for P
+    if (p_tmem < 0) {
+      const char* e = getenv("NGA_ATTN_P_TMEM");
+      p_tmem = (e != nullptr && e[0] == '1') ? 1 : 0;
+    }
+    p.p_tmem = p_tmem;
+  }
   g_attn_sel = nullptr;
   g_attn_sink = nullptr;
   if (p.sel != nullptr && (T % 128)) return -7;     // rows of selection words are read 16 bytes at a time

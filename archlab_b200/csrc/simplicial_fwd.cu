@@ -18,6 +18,7 @@
 #include "host_util.h"
 #include "simplicial.h"
 #include <cuda.h>
+#include <cstdlib>
 
 namespace nga {
 
@@ -41,6 +42,7 @@ struct SimpFwdParams {
   const int* block_table;    // [B, max_pages] physical page of every logical page
   const int* seq_lens;       // [B] tokens in the cache including the new one
   int max_pages;
+  int p_tmem;                // 1: P returns to the tensor core through TMEM (A operand of P V2)
 };
 
 struct SimpFwdSmem {
@@ -196,9 +198,13 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
         const uint32_t sV = smem_u32(smem + S::kV + (j & 1) * SX_TILE);
 #pragma unroll
         for (int k = 0; k < SX_BK / 16; ++k) {
-          const uint64_t da = umma_smem_desc(sP + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
           const uint64_t db = umma_smem_desc(sV + k * 2048, 16384, 1024);
-          umma_bf16_ss(tmem_O, da, db, idesc_pv, (j | k) != 0 ? 1u : 0u);
+          if (p.p_tmem) {
+            umma_bf16_ts(tmem_O, tmem_S0 + uint32_t((j & 1) * 128 + k * 8), db, idesc_pv, (j | k) != 0 ? 1u : 0u);
+          } else {
+            const uint64_t da = umma_smem_desc(sP + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+            umma_bf16_ss(tmem_O, da, db, idesc_pv, (j | k) != 0 ? 1u : 0u);
+          }
         }
         umma_commit(&kv_empty[j & 1]);
         umma_commit(p_empty);
@@ -319,18 +325,26 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
           asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pr[e]) : "f"(fmaf(__uint_as_float(sv[c][e]), p.scale_log2, -m_sub)));
           ps4[e & 3] += pr[e];
         }
-        uint8_t* line = sP + (c >> 1) * 16384 + r * 128;
+        if (p.p_tmem) {
+          uint32_t pk[16];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int chunk = ((c & 1) * 4 + g) ^ (r & 7);
-          uint4 u;
-          u.x = pack_bf16(pr[8 * g + 0], pr[8 * g + 1]);
-          u.y = pack_bf16(pr[8 * g + 2], pr[8 * g + 3]);
-          u.z = pack_bf16(pr[8 * g + 4], pr[8 * g + 5]);
-          u.w = pack_bf16(pr[8 * g + 6], pr[8 * g + 7]);
-          *reinterpret_cast<uint4*>(line + chunk * 16) = u;
+          for (int g = 0; g < 16; ++g) pk[g] = pack_bf16(pr[2 * g], pr[2 * g + 1]);
+          tmem_st_32x16(tS + c * 16, pk);
+        } else {
+          uint8_t* line = sP + (c >> 1) * 16384 + r * 128;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int chunk = ((c & 1) * 4 + g) ^ (r & 7);
+            uint4 u;
+            u.x = pack_bf16(pr[8 * g + 0], pr[8 * g + 1]);
+            u.y = pack_bf16(pr[8 * g + 2], pr[8 * g + 3]);
+            u.z = pack_bf16(pr[8 * g + 4], pr[8 * g + 5]);
+            u.w = pack_bf16(pr[8 * g + 6], pr[8 * g + 7]);
+            *reinterpret_cast<uint4*>(line + chunk * 16) = u;
+          }
         }
       }
+      if (p.p_tmem) tmem_st_wait();
       l_row += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
       tc_fence_before();
       fence_proxy_async_smem();
@@ -424,6 +438,14 @@ simplicial_fwd_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_co
 
 }  // namespace nga
 
+static int simp_p_tmem() {                         // NGA_SIMP_P_TMEM=1 selects the TMEM route for P
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("NGA_SIMP_P_TMEM");
+    v = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  return v;
+}
 static long long* g_simp_fwd_prof = nullptr;
 extern "C" void nga_simplicial_fwd_set_prof(long long* device_ptr) { g_simp_fwd_prof = device_ptr; }
 
@@ -462,6 +484,7 @@ extern "C" int nga_simplicial_fwd(const void* q, const void* k1, const void* k2,
   p.status = status;
   p.prof = g_simp_fwd_prof;
   p.block_table = nullptr; p.seq_lens = nullptr; p.max_pages = 0;
+  p.p_tmem = simp_p_tmem();
   const int BQ = 128 / w1;
   dim3 grid((N + BQ - 1) / BQ, Hq, B);
   simplicial_fwd_kernel<false><<<grid, SX_THREADS, SimpFwdSmem::kTotal, reinterpret_cast<cudaStream_t>(stream)>>>(tk, tv, p);
@@ -509,6 +532,7 @@ extern "C" int nga_simplicial_decode(const void* q, const void* k1c, const void*
   p.status = status;
   p.prof = nullptr;
   p.block_table = block_table; p.seq_lens = seq_lens; p.max_pages = max_pages;
+  p.p_tmem = simp_p_tmem();
   simplicial_fwd_kernel<true><<<dim3(1, Hkv, B), SX_THREADS, SimpFwdSmem::kTotal, reinterpret_cast<cudaStream_t>(stream)>>>(tk, tv, p);
   count_launch();
   NGA_CHECK_LAUNCH();

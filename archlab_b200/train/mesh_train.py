@@ -197,8 +197,10 @@ class _Job:
             if ep_group is not None and device.type == "cuda":
                 from ..parallel.ep import EPBuffers
 
+                # worst case: every rank routes all of its slots to the experts of ONE rank (an untrained router can
+                # come close); at 2 bytes x hidden per row the four buffers stay in the low GB range
                 slots = a.micro_batch * a.seq_len * cfg.experts_top_k
-                ep_buffers = EPBuffers(2 * slots, cfg.hidden_size, device, ep_group)
+                ep_buffers = EPBuffers(mesh.dp * slots, cfg.hidden_size, device, ep_group)
             self.model = V41LM(cfg, ep_group, ep_buffers).to(device)
             self.model.init_weights()
             if ep_group is not None:                          # shared weights agree; every rank keeps its own experts
