@@ -61,3 +61,12 @@ int nga_gemm2_fp8(const void* A, const void* B, void* D, const void* aux, int M,
 #ifdef __cplusplus
 }
 #endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+int nga_gemm2_grouped_bf16(const void* A, const void* B, void* D, const int* group_of_mtile, int groups, int M, int N, int K,
+                           long long lda, long long ldb, long long ldd, int b_mn, int* status, void* stream);
+#ifdef __cplusplus
+}
+#endif

@@ -262,6 +262,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (TP) mb = tp_remap_mb(tp, mb, num_m);
         int m0 = mb * 2 * BM + int(rank) * BM;             // this CTA's 128 rows of A
         const int n0 = nb * G2_BN + int(rank) * 128;       // this CTA's 128 N-rows of B
+        const int grp_off = p.group_of_mtile ? p.group_of_mtile[mb] * p.group_rows : 0;   // rows of B before this tile's group
         const CUtensorMap* mapA = &tmA;
         if (TP && (tp.mode & kTpGather)) {
           const int owner = m0 / tp.rows_per_rank;
@@ -291,9 +292,9 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < 2; ++j)
-              tma_load_3d_pair(sB + j * 8192, &tmB, leader_full, n0 + j * 64, kb * BK, b);
+              tma_load_3d_pair(sB + j * 8192, &tmB, leader_full, n0 + j * 64, kb * BK + grp_off, b);
           } else {
-            tma_load_3d_pair(sB, &tmB, leader_full, kb * BKE, n0, b);
+            tma_load_3d_pair(sB, &tmB, leader_full, kb * BKE, n0 + grp_off, b);
           }
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -553,12 +554,48 @@ extern "C" int nga_gemm2_bf16(const void* A, const void* B, void* D, const void*
   if (epi == kEpiAtomicAdd && !out_fp32) return -8;
   p.status = status;
   p.row_shift = 0;
+  p.group_of_mtile = nullptr; p.group_rows = 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   TpParams tp = {};
   static const TpMaps no_maps = {};
   if (a_mn && b_mn) return launch_gemm2<1, 1, 0>(ta, tb, p, st, ta, tp, no_maps);
   if (a_mn && !b_mn) return launch_gemm2<1, 0, 0>(ta, tb, p, st, ta, tp, no_maps);
   if (!a_mn && b_mn) return launch_gemm2<0, 1, 0>(ta, tb, p, st, ta, tp, no_maps);
+  return launch_gemm2<0, 0, 0>(ta, tb, p, st, ta, tp, no_maps);
+}
+
+// Grouped GEMM for expert layers: D[M, N] = A[M, K] . B_g^T (b_mn = 0: B is the stack [G * N, K] of K-major matrices)
+// or A[M, K] . B_g (b_mn = 1: B is the stack [G * K, N] of MN-major matrices), where g = group_of_mtile[m / 256] for
+// every 256-row tile (device int array of ceil(M / 256) entries; segments are padded to multiples of 256 rows).
+extern "C" int nga_gemm2_grouped_bf16(const void* A, const void* B, void* D, const int* group_of_mtile, int groups, int M, int N,
+                                      int K, long long lda, long long ldb, long long ldd, int b_mn, int* status, void* stream) {
+  using namespace nga;
+  if (M <= 0 || N <= 0 || K <= 0 || groups <= 0 || group_of_mtile == nullptr) return -1;
+  if ((lda & 7) || (ldb & 7)) return -5;
+  if (b_mn && (K % BK)) return -6;                 // a k-block must not straddle two groups' matrices
+  CUtensorMap ta, tb;
+  int rc = make_tmap_3d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, 1, lda * 2, (long long)M * lda * 2, 64, 128, true);
+  if (rc) return rc;
+  if (b_mn)
+    rc = make_tmap_3d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, (long long)groups * K, 1, ldb * 2,
+                      (long long)groups * K * ldb * 2, 64, 64, true);
+  else
+    rc = make_tmap_3d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, (long long)groups * N, 1, ldb * 2,
+                      (long long)groups * N * ldb * 2, 64, 128, true);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.batch = 1;
+  p.D = D; p.aux = nullptr; p.ldd = ldd; p.ldaux = 0; p.sD = 0; p.sAux = 0;
+  p.epi = kEpiScale; p.out_fp32 = 0; p.aux_fp32 = 0; p.alpha = 1.f; p.beta = 0.f;
+  p.splits = 1;
+  p.status = status;
+  p.row_shift = 0;
+  p.group_of_mtile = group_of_mtile;
+  p.group_rows = b_mn ? K : N;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  TpParams tp = {};
+  static const TpMaps no_maps = {};
+  if (b_mn) return launch_gemm2<0, 1, 0>(ta, tb, p, st, ta, tp, no_maps);
   return launch_gemm2<0, 0, 0>(ta, tb, p, st, ta, tp, no_maps);
 }
 
@@ -584,6 +621,7 @@ extern "C" int nga_gemm2_fp8(const void* A, const void* B, void* D, const void* 
   if (epi == kEpiAtomicAdd) return -8;
   p.status = status;
   p.row_shift = 0;
+  p.group_of_mtile = nullptr; p.group_rows = 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   TpParams tp = {};
   static const TpMaps no_maps = {};
@@ -642,6 +680,7 @@ extern "C" int nga_tp_gemm_bf16(const void* A, const void* B, void* D, int M, in
   p.D = D; p.aux = nullptr; p.ldd = ldd; p.ldaux = 0; p.sD = 0; p.sAux = 0;
   p.epi = kEpiScale; p.out_fp32 = 0; p.aux_fp32 = 0; p.alpha = 1.f; p.beta = 0.f; p.splits = 1;
   p.status = status; p.row_shift = 0;
+  p.group_of_mtile = nullptr; p.group_rows = 0;
   TpMaps tpm = {};
   if (mode == kTpScatter) {
     for (int r = 0; r < world; ++r) {

@@ -22,6 +22,10 @@ struct GemmParams {
   int splits;                    // split-K factor (> 1 only with kEpiAtomicAdd)
   int* status;
   long long row_shift;           // added to the row index when addressing D (tensor-parallel staging slots)
+  // grouped form (expert GEMMs in one launch): rows are sorted by group and every 256-row tile belongs to one
+  // group; `group_of_mtile[mb]` names it and B is the stack of the groups' matrices, `group_rows` rows each
+  const int* group_of_mtile;
+  int group_rows;
 };
 
 // Tensor-parallel fusion of the CTA-pair GEMM with its collective over NVLink peer memory.

@@ -1,0 +1,77 @@
+"""Grouped linear layer: one tcgen05 GEMM launch for all experts of a rank.
+
+Rows are sorted by expert and every expert's segment is padded to a multiple of 256 rows, so that each
+256-row tile of the pair-CTA GEMM belongs to one expert; a small int table names the expert of every
+tile and the kernel offsets its B coordinate into the stacked weights.  Forward and input gradient are
+one launch each; weight gradients are per-expert ``dY_e^T X_e`` products on the same kernel (their
+reduction lengths differ per expert).  Replaces a per-expert loop of 2 * E launches per layer; the
+reference reaches TE ``GroupedLinear`` for this (src/archlab/architectures/qwen38_flash_next.py:184-202).
+Off the GPU the per-expert loop runs.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import gemm as G
+from . import native
+
+TILE = 256
+_vp, _i, _ll = C.c_void_p, C.c_int, C.c_longlong
+native.register_signature("nga_gemm2_grouped_bf16", [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp])
+
+
+def padded_sizes(counts: torch.Tensor) -> torch.Tensor:
+    return (counts + TILE - 1) // TILE * TILE
+
+
+def _launch(a, w_stack, tile_group, groups, n_out, k_red, b_mn):
+    out = torch.empty(a.size(0), n_out, dtype=torch.bfloat16, device=a.device)
+    rc = native.lib().nga_gemm2_grouped_bf16(a.data_ptr(), w_stack.data_ptr(), out.data_ptr(), tile_group.data_ptr(), groups, a.size(0),
+                                             n_out, k_red, a.stride(0), w_stack.stride(0), out.stride(0), int(b_mn),
+                                             native.status_word(a.device).data_ptr(), native.stream_ptr())
+    native.check(rc, "nga_gemm2_grouped_bf16")
+    return out
+
+
+class _GroupedLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, tile_group, real, padded):
+        E, N, K = w.shape
+        ctx.save_for_backward(x, w, tile_group)
+        ctx.seg = (real, padded)
+        return _launch(x, w.view(E * N, K), tile_group, E, N, K, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, tile_group = ctx.saved_tensors
+        real, padded = ctx.seg
+        E, N, K = w.shape
+        dy = dy.contiguous()
+        dx = _launch(dy, w.view(E * N, K), tile_group, E, K, N, True)          # dY W_e: B read MN-major, reduction over N
+        dw = torch.zeros_like(w)
+        s0 = 0
+        for e, (n, npad) in enumerate(zip(real, padded)):
+            if n:
+                dw[e] = G.gemm(dy[s0:s0 + n], x[s0:s0 + n], a_mn=True, b_mn=True)     # dY_e^T X_e
+            s0 += npad
+        return dx, dw, None, None, None
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, real: list[int], padded: list[int]) -> torch.Tensor:
+    """x [sum(padded), K] (rows sorted by expert, segments padded to 256), w [E, N, K] -> [sum(padded), N].
+    Rows in the padding produce unspecified values."""
+    E, N, K = w.shape
+    if x.is_cuda and x.dtype == torch.bfloat16 and native.available() and K % 8 == 0 and N % 64 == 0 and K % 64 == 0:
+        return _GroupedLinear.apply(x.contiguous(), w.to(x.dtype).contiguous(), tile_group, real, padded)
+    outs, s0 = [], 0
+    for e, npad in enumerate(padded):
+        outs.append(x[s0:s0 + npad] @ w[e].to(x.dtype).t())
+        s0 += npad
+    return torch.cat(outs, 0) if outs else x.new_zeros(0, N)
+
+
+def tile_groups(padded: list[int], device) -> torch.Tensor:
+    reps = torch.tensor([p // TILE for p in padded], device=device)
+    return torch.repeat_interleave(torch.arange(len(padded), device=device, dtype=torch.int32), reps).contiguous()

@@ -22,7 +22,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..models.moe import GroupedExperts, SwiGLU, route
-from ..ops import block_ops
+from ..ops import block_ops, grouped
 from ..ops import native
 from ..ops.linear import linear
 
@@ -41,6 +41,8 @@ class EPBuffers:
 
         self.group = group or dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        # `capacity` counts routed rows; every local expert's segment is padded to a 256-row tile on top of that
+        capacity = capacity + 256 * 64
         self.capacity, self.dim = capacity, dim
         mk = lambda: symm_empty((capacity * dim,), torch.bfloat16, device, self.group)
         self.recv_x, self.y, self.g_y, self.g_x = mk(), mk(), mk(), mk()
@@ -149,7 +151,8 @@ class FusedExpertParallelMoE(nn.Module):
         allc = torch.empty(W, E, dtype=counts.dtype, device=idx.device)
         dist.all_gather_into_tensor(allc, counts, group=self.buf.group)
         per_e = allc.sum(0)                                                     # rows of expert e on its owner
-        seg_start = per_e.view(W, El).cumsum(1) - per_e.view(W, El)            # start of e's segment on its owner
+        pad_e = grouped.padded_sizes(per_e)                                     # segments start on 256-row tiles
+        seg_start = pad_e.view(W, El).cumsum(1) - pad_e.view(W, El)            # start of e's segment on its owner
         before_me = allc[: self.rank].sum(0)                                    # rows of e from lower source ranks
         base = seg_start.flatten() + before_me
         sorted_e, order = flat.sort(stable=True)
@@ -158,7 +161,7 @@ class FusedExpertParallelMoE(nn.Module):
         dst_row = torch.empty_like(flat)
         dst_row[order] = base[sorted_e] + within
         dst_rank = flat // El
-        mine = per_e[self.first:self.first + El]
+        mine = torch.stack([per_e[self.first:self.first + El], pad_e[self.first:self.first + El]])
         return dst_rank.int(), dst_row.int(), mine, counts
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -169,21 +172,16 @@ class FusedExpertParallelMoE(nn.Module):
         dst_rank, dst_row, mine, counts = self.plan(idx)
         load = counts.float()
         self._cumulative_expert_load = load if self._cumulative_expert_load is None else self._cumulative_expert_load + load
-        seg = mine.tolist()                                                       # host needs the GEMM extents
-        n_recv = sum(seg)
+        seg, seg_pad = mine.tolist()                                              # host needs the GEMM extents
+        n_recv = sum(seg_pad)
         if n_recv > self.buf.capacity:
             raise RuntimeError(f"expert receive buffer too small: {n_recv} rows > capacity {self.buf.capacity}")
         src_row = torch.arange(T, device=x.device, dtype=torch.int32).repeat_interleave(k)
         recv = _Dispatch.apply(x2, src_row, dst_rank, dst_row, n_recv, k, self.buf)
-        outs, s0 = [], 0
-        for le, n in enumerate(seg):
-            if n == 0:
-                continue
-            h = linear(recv[s0:s0 + n], self.experts.gate_up[le].to(recv.dtype))
-            a = block_ops.swiglu(h, self.limit)
-            outs.append(linear(a, self.experts.down[le].to(recv.dtype)))
-            s0 += n
-        y_local = torch.cat(outs, 0) if outs else recv.new_zeros(0, self.dim)
+        # all local experts in ONE grouped GEMM per projection (rows in the 256-row padding are never read back)
+        tiles = grouped.tile_groups(seg_pad, x.device)
+        h = grouped.grouped_linear(recv, self.experts.gate_up, tiles, seg, seg_pad)
+        y_local = grouped.grouped_linear(block_ops.swiglu(h, self.limit), self.experts.down, tiles, seg, seg_pad)
         # ascending expert id per token: deterministic summation order
         eo = idx.argsort(dim=-1)
         slots = (torch.arange(T, device=x.device) * k).unsqueeze(1) + eo
