@@ -63,6 +63,8 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, r
     """x [sum(padded), K] (rows sorted by expert, segments padded to 256), w [E, N, K] -> [sum(padded), N].
     Rows in the padding produce unspecified values."""
     E, N, K = w.shape
+    if x.size(0) == 0:
+        return x.new_zeros(0, N) + 0 * w.sum().to(x.dtype)            # keeps the weights in the graph
     if x.is_cuda and x.dtype == torch.bfloat16 and native.available() and K % 8 == 0 and N % 64 == 0 and K % 64 == 0:
         return _GroupedLinear.apply(x.contiguous(), w.to(x.dtype).contiguous(), tile_group, real, padded)
     outs, s0 = [], 0
