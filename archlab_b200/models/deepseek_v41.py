@@ -39,6 +39,7 @@ class V41Config:
     index_top_k: int = 2048
     dense_warmup_steps: int = 0
     indexer_kl_weight: float = 1.0
+    indexer_kl_rows: int = 512            # query rows per sequence on which the KL target is evaluated (0: all)
     n_routed_experts: int = 64
     n_shared_experts: int = 2
     experts_top_k: int = 6
@@ -102,7 +103,8 @@ class LightningIndexer(nn.Module):
         k = apply_rope(k, cos, sin, rot_dim=self.rope).squeeze(2)
         w = self.weights_proj(x).float() * self.h ** -0.5
         scores = dsa.indexer_scores(q, k, w)
-        idx, _ = dsa.select_topk(scores, self.top_k)
+        idx, vals = dsa.select_topk(scores, self.top_k)
+        self.kth = vals[..., -1:].detach()                 # threshold form of the same selection (for the bit-mask kernels)
         return scores, idx
 
 
@@ -123,6 +125,7 @@ class SparseLatentAttention(nn.Module):
         self.o_proj = mk(self.h * self.d, c.hidden_size)
         self.indexer = LightningIndexer(c)
         self.last_kl = None
+        self.kl_step = 0
 
     def forward(self, x, cos, sin, *, dense: bool = False):
         B, S, _ = x.shape
@@ -132,11 +135,19 @@ class SparseLatentAttention(nn.Module):
         icos, isin = cos[:, : self.c.index_rope_dim // 2], sin[:, : self.c.index_rope_dim // 2]
         scores, idx = self.indexer(x, icos, isin)
         if self.training and self.c.indexer_kl_weight > 0:
-            target = dsa.main_attention_target(q, kv, scale)
-            self.last_kl = dsa.indexer_kl(target, scores, torch.isfinite(scores))
+            rows = dsa.kl_rows(S, self.c.indexer_kl_rows, self.kl_step, x.device)
+            self.kl_step += 1
+            if rows is None:
+                target = dsa.main_attention_target(q, kv, scale)
+                self.last_kl = dsa.indexer_kl(target, scores, torch.isfinite(scores))
+            else:                                        # the [heads, S, S] target is the costliest tensor of the layer
+                target = dsa.main_attention_target(q[:, rows], kv, scale, rows)
+                sub = scores[:, rows]
+                self.last_kl = dsa.indexer_kl(target, sub, torch.isfinite(sub))
         use_dense = dense or S <= self.c.index_top_k
         if dsa_cuda.kernel_supports(q, kv):                  # flash kernels with selection bits and sink
-            o = dsa_cuda.selected_sink_attention(q, kv, self.sink, None if use_dense else idx)
+            o = (dsa_cuda.selected_sink_attention(q, kv, self.sink) if use_dense else
+                 dsa_cuda.selected_sink_attention(q, kv, self.sink, scores=scores.detach(), kth=self.indexer.kth))
         elif use_dense:
             o = dsa.dense_sink_attention(q, kv, self.sink, scale)
         else:

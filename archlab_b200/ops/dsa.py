@@ -104,9 +104,20 @@ def indexer_kl(target: torch.Tensor, index_scores: torch.Tensor, valid: torch.Te
     return (terms.sum(-1) * has).sum() / has.sum().clamp_min(1)
 
 
-def main_attention_target(main_q: torch.Tensor, kv: torch.Tensor, scale: float) -> torch.Tensor:
-    """Head-averaged causal softmax of the main attention (detached) -> [B,S,K]."""
+def main_attention_target(main_q: torch.Tensor, kv: torch.Tensor, scale: float, positions: torch.Tensor | None = None) -> torch.Tensor:
+    """Head-averaged causal softmax of the main attention (detached) -> [B,S,K].  ``positions`` [S] gives the
+    absolute position of every query row when only a subset of the rows is passed."""
     S, K = main_q.size(1), kv.size(1)
     s = torch.einsum("bshd,bkd->bhsk", main_q.detach().float(), kv.detach().float()) * scale
-    mask = torch.arange(K, device=s.device)[None, :] > (torch.arange(S, device=s.device)[:, None] + (K - S))
+    qpos = torch.arange(S, device=s.device) + (K - S) if positions is None else positions
+    mask = torch.arange(K, device=s.device)[None, :] > qpos[:, None]
     return s.masked_fill(mask, float("-inf")).softmax(-1).mean(1)
+
+
+def kl_rows(S: int, max_rows: int, step: int, device) -> torch.Tensor | None:
+    """Query rows on which the indexer's KL is evaluated: all of them up to ``max_rows``, else a strided subset whose
+    offset moves with the training step so that every row is visited."""
+    if max_rows <= 0 or S <= max_rows:
+        return None
+    stride = (S + max_rows - 1) // max_rows
+    return torch.arange(step % stride, S, stride, device=device)

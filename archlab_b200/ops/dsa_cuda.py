@@ -32,8 +32,9 @@ def kernel_supports(q: torch.Tensor, kv: torch.Tensor) -> bool:
 def _pack_bits(mask: torch.Tensor) -> torch.Tensor:
     """bool [..., T] -> int32 [..., T/32], bit i of word w = mask[..., 32 w + i]."""
     T = mask.size(-1)
-    w = (mask.view(*mask.shape[:-1], T // 32, 32).long() << torch.arange(32, device=mask.device)).sum(-1)
-    return torch.where(w >= 2 ** 31, w - 2 ** 32, w).to(torch.int32).contiguous()
+    weights = (1 << torch.arange(8, device=mask.device)).to(torch.uint8)
+    by = (mask.view(*mask.shape[:-1], T // 8, 8).to(torch.uint8) * weights).sum(-1, dtype=torch.uint8)     # byte j = bits 8j .. 8j+7
+    return by.contiguous().view(torch.int32)                                                               # little-endian words
 
 
 def selection_bits(indices: torch.Tensor, T: int):
@@ -74,9 +75,19 @@ class _SelectedAttention(torch.autograd.Function):
         return dq.reshape(B, T, H, D), (dk + dv).reshape(B, T, D), dsink.to(sink32.dtype), None, None
 
 
-def selected_sink_attention(q, kv, sink, indices=None):
-    """q [B, T, H, 128], kv [B, T, 128] (key = value), sink [H], indices [B, T, K] or None (all causal keys)."""
+def selection_bits_from_scores(scores: torch.Tensor, kth: torch.Tensor):
+    """scores [B, T, T] (-inf on non-causal pairs), kth [B, T, 1] the k-th largest score of every row (-inf when the
+    row has fewer than k candidates): keys scoring at least the threshold are selected - no index scatter."""
+    mask = (scores >= kth) & torch.isfinite(scores)
+    return _pack_bits(mask), _pack_bits(mask.transpose(1, 2).contiguous())
+
+
+def selected_sink_attention(q, kv, sink, indices=None, *, scores=None, kth=None):
+    """q [B, T, H, 128], kv [B, T, 128] (key = value), sink [H]; the selection is given either by ``indices``
+    [B, T, K] or by the indexer ``scores`` with their per-row threshold ``kth``; neither: all causal keys."""
     bits = bits_t = None
-    if indices is not None:
+    if scores is not None and kth is not None:
+        bits, bits_t = selection_bits_from_scores(scores, kth)
+    elif indices is not None:
         bits, bits_t = selection_bits(indices, q.size(1))
     return _SelectedAttention.apply(q, kv.to(q.dtype), sink, bits, bits_t)
