@@ -53,3 +53,12 @@ int nga_token_mix_dw(const void* dout, const void* in_a, const void* in_b, float
 #ifdef __cplusplus
 }
 #endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+int nga_indexer_select(const void* q, const void* k, const float* w, void* bits, int B, int S, int heads, int dim, int top_k,
+                       float scale, void* stream);
+#ifdef __cplusplus
+}
+#endif

@@ -92,9 +92,10 @@ class LightningIndexer(nn.Module):
         self.k_norm = nn.LayerNorm(self.d, eps=1e-6)
         self.weights_proj = nn.Linear(c.hidden_size, self.h, bias=False)
 
-    def forward(self, x: torch.Tensor, cos, sin):
-        """-> (scores [B,S,S] fp32 causal, indices [B,S,k] with -1 padding).  Inputs are detached:
-        the indexer learns only from its KL objective."""
+    def forward(self, x: torch.Tensor, cos, sin, fused: bool = False):
+        """-> (scores [B,S,S] fp32 causal, indices [B,S,k] with -1 padding), or (None, None) with ``self.bits`` set
+        when ``fused`` and the selection kernel applies.  Inputs are detached: the indexer learns only from its
+        KL objective."""
         x = x.detach()
         B, S, _ = x.shape
         q = self.q_proj(x).view(B, S, self.h, self.d)
@@ -102,10 +103,21 @@ class LightningIndexer(nn.Module):
         q = apply_rope(q, cos, sin, rot_dim=self.rope)
         k = apply_rope(k, cos, sin, rot_dim=self.rope).squeeze(2)
         w = self.weights_proj(x).float() * self.h ** -0.5
+        self.qkw = (q, k, w)                               # for the objective on a subset of rows
+        if fused and dsa_cuda.indexer_kernel_supports(q, k):
+            # selection kernel: scores, top-k threshold and one bit per key without the [S, S] score matrix
+            self.bits = dsa_cuda.indexer_select(q, k, w, self.top_k) if S > self.top_k else None
+            return None, None
+        self.bits = None
         scores = dsa.indexer_scores(q, k, w)
         idx, vals = dsa.select_topk(scores, self.top_k)
         self.kth = vals[..., -1:].detach()                 # threshold form of the same selection (for the bit-mask kernels)
         return scores, idx
+
+    def scores_for_rows(self, rows: torch.Tensor) -> torch.Tensor:
+        """Differentiable scores of the given query rows against all keys (the rows the objective looks at)."""
+        q, k, w = self.qkw
+        return dsa.indexer_scores(q[:, rows], k, w[:, rows], positions=rows)
 
 
 class SparseLatentAttention(nn.Module):
@@ -133,21 +145,28 @@ class SparseLatentAttention(nn.Module):
         kv = apply_rope(self.kv_norm(self.kv_proj(x)).unsqueeze(2), cos, sin, rot_dim=self.c.rope_dim).squeeze(2)
         scale = self.d ** -0.5
         icos, isin = cos[:, : self.c.index_rope_dim // 2], sin[:, : self.c.index_rope_dim // 2]
-        scores, idx = self.indexer(x, icos, isin)
+        flash = dsa_cuda.kernel_supports(q, kv)
+        scores, idx = self.indexer(x, icos, isin, fused=flash)
         if self.training and self.c.indexer_kl_weight > 0:
             rows = dsa.kl_rows(S, self.c.indexer_kl_rows, self.kl_step, x.device)
             self.kl_step += 1
+            if rows is None and scores is None:
+                rows = torch.arange(S, device=x.device)
             if rows is None:
                 target = dsa.main_attention_target(q, kv, scale)
                 self.last_kl = dsa.indexer_kl(target, scores, torch.isfinite(scores))
             else:                                        # the [heads, S, S] target is the costliest tensor of the layer
                 target = dsa.main_attention_target(q[:, rows], kv, scale, rows)
-                sub = scores[:, rows]
+                sub = scores[:, rows] if scores is not None else self.indexer.scores_for_rows(rows)
                 self.last_kl = dsa.indexer_kl(target, sub, torch.isfinite(sub))
         use_dense = dense or S <= self.c.index_top_k
-        if dsa_cuda.kernel_supports(q, kv):                  # flash kernels with selection bits and sink
-            o = (dsa_cuda.selected_sink_attention(q, kv, self.sink) if use_dense else
-                 dsa_cuda.selected_sink_attention(q, kv, self.sink, scores=scores.detach(), kth=self.indexer.kth))
+        if flash:                                            # flash kernels with selection bits and sink
+            if use_dense:
+                o = dsa_cuda.selected_sink_attention(q, kv, self.sink)
+            elif scores is None:
+                o = dsa_cuda.selected_sink_attention(q, kv, self.sink, bits_pair=self.indexer.bits)
+            else:
+                o = dsa_cuda.selected_sink_attention(q, kv, self.sink, scores=scores.detach(), kth=self.indexer.kth)
         elif use_dense:
             o = dsa.dense_sink_attention(q, kv, self.sink, scale)
         else:

@@ -20,13 +20,13 @@ from torch.utils.checkpoint import checkpoint
 
 
 def indexer_scores(q: torch.Tensor, k: torch.Tensor, weights: torch.Tensor, scale: float | None = None,
-                   *, query_offset: int = 0) -> torch.Tensor:
+                   *, query_offset: int = 0, positions: torch.Tensor | None = None) -> torch.Tensor:
     """q [B,S,Hi,Di], k [B,K,Di], weights [B,S,Hi] -> scores [B,S,K] (fp32, -inf above the diagonal).
-    Query i sits at absolute position ``query_offset + i``."""
+    Query i sits at absolute position ``query_offset + i`` (or ``positions[i]`` when given)."""
     scale = q.size(-1) ** -0.5 if scale is None else scale
     per_head = torch.einsum("bqhd,bkd->bqhk", q.float(), k.float()).relu()
     s = (per_head * weights.float().unsqueeze(-1)).sum(2) * scale
-    qpos = torch.arange(q.size(1), device=q.device) + query_offset
+    qpos = torch.arange(q.size(1), device=q.device) + query_offset if positions is None else positions
     kpos = torch.arange(k.size(1), device=q.device)
     return s.masked_fill(kpos[None, None, :] > qpos[None, :, None], float("-inf"))
 

@@ -21,6 +21,8 @@ from . import native, trunk
 
 native.register_signature("nga_attn_fwd_set_extras", [C.c_void_p, C.c_void_p], None)
 native.register_signature("nga_attn_bwd_set_extras", [C.c_void_p], None)
+native.register_signature("nga_indexer_select", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                 C.c_int, C.c_float, C.c_void_p])
 LOG2E = 1.4426950408889634
 
 
@@ -75,6 +77,31 @@ class _SelectedAttention(torch.autograd.Function):
         return dq.reshape(B, T, H, D), (dk + dv).reshape(B, T, D), dsink.to(sink32.dtype), None, None
 
 
+def indexer_kernel_supports(q: torch.Tensor, k: torch.Tensor) -> bool:
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.size(2) == 4 and q.size(3) == 64 and q.size(1) % 32 == 0
+            and q.size(1) <= 8192 and native.available())
+
+
+def transpose_bits(bits: torch.Tensor, T: int) -> torch.Tensor:
+    """[B, T, T/32] query-major selection words -> key-major words."""
+    by = bits.contiguous().view(torch.uint8)                                   # [B, T, T/8]
+    mask = ((by.unsqueeze(-1) >> torch.arange(8, device=bits.device, dtype=torch.uint8)) & 1).bool().view(bits.size(0), T, T)
+    return _pack_bits(mask.transpose(1, 2).contiguous())
+
+
+@torch.no_grad()
+def indexer_select(q, k, w, top_k: int, scale: float | None = None):
+    """q [B, S, 4, 64] bf16, k [B, S, 64] bf16, w [B, S, 4] -> (bits, key-major bits) of the causal top-k keys per
+    query (threshold semantics: every key scoring at least the k-th largest score)."""
+    B, S, H, D = q.shape
+    bits = torch.empty(B, S, S // 32, dtype=torch.int32, device=q.device)
+    rc = native.lib().nga_indexer_select(q.contiguous().data_ptr(), k.contiguous().data_ptr(), w.float().contiguous().data_ptr(),
+                                         bits.data_ptr(), B, S, H, D, int(top_k), float(D ** -0.5 if scale is None else scale),
+                                         native.stream_ptr())
+    native.check(rc, "nga_indexer_select")
+    return bits, transpose_bits(bits, S)
+
+
 def selection_bits_from_scores(scores: torch.Tensor, kth: torch.Tensor):
     """scores [B, T, T] (-inf on non-causal pairs), kth [B, T, 1] the k-th largest score of every row (-inf when the
     row has fewer than k candidates): keys scoring at least the threshold are selected - no index scatter."""
@@ -82,11 +109,14 @@ def selection_bits_from_scores(scores: torch.Tensor, kth: torch.Tensor):
     return _pack_bits(mask), _pack_bits(mask.transpose(1, 2).contiguous())
 
 
-def selected_sink_attention(q, kv, sink, indices=None, *, scores=None, kth=None):
-    """q [B, T, H, 128], kv [B, T, 128] (key = value), sink [H]; the selection is given either by ``indices``
-    [B, T, K] or by the indexer ``scores`` with their per-row threshold ``kth``; neither: all causal keys."""
+def selected_sink_attention(q, kv, sink, indices=None, *, scores=None, kth=None, bits_pair=None):
+    """q [B, T, H, 128], kv [B, T, 128] (key = value), sink [H]; the selection is given by ready ``bits_pair``
+    (query-major, key-major), by ``indices`` [B, T, K], or by the indexer ``scores`` with their per-row threshold
+    ``kth``; none of them: all causal keys."""
     bits = bits_t = None
-    if scores is not None and kth is not None:
+    if bits_pair is not None:
+        bits, bits_t = bits_pair
+    elif scores is not None and kth is not None:
         bits, bits_t = selection_bits_from_scores(scores, kth)
     elif indices is not None:
         bits, bits_t = selection_bits(indices, q.size(1))
