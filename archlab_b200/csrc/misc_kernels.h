@@ -62,3 +62,15 @@ int nga_indexer_select(const void* q, const void* k, const float* w, void* bits,
 #ifdef __cplusplus
 }
 #endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+int nga_hc_coeff_fwd(const float* mixes, const float* scale, const float* base, float* pre, float* post, float* comb, long long T,
+                     int streams, int iters, float eps, void* stream);
+int nga_hc_coeff_bwd(const float* mixes, const float* scale, const float* base, const float* dpre, const float* dpost,
+                     const float* dcomb, float* dmixes, float* dscale, float* dbase, long long T, int streams, int iters, float eps,
+                     void* stream);
+#ifdef __cplusplus
+}
+#endif

@@ -141,6 +141,11 @@ def hc_split_sinkhorn(mixes: torch.Tensor, scale: torch.Tensor, base: torch.Tens
         raise ValueError("wrong mHC projection width")
     if scale.shape != (3,) or base.shape != (mixes.shape[-1],):
         raise ValueError("wrong mHC scale/base shape")
+    if mixes.is_cuda and streams == 4:
+        from ..ops import stream_mix
+
+        if stream_mix.hc_coefficients_usable(mixes, streams, iterations):
+            return stream_mix.hc_coefficients(mixes, scale, base, iterations, eps)
     dt = torch.float64 if mixes.dtype == torch.float64 else torch.float32
     mixes, scale, base = mixes.to(dt), scale.to(dt), base.to(dt)
     n = streams

@@ -85,3 +85,51 @@ def hyper_connection_write(comb: torch.Tensor, post: torch.Tensor, streams: torc
     """new_streams = comb^T streams + post (x) y.  comb [..., n, n], post [..., n], y [..., C]."""
     W = torch.cat([comb.transpose(-1, -2), post.unsqueeze(-1)], -1)
     return token_mix(W, streams, y.unsqueeze(-2))
+
+
+# ------------------------------------------------------------------------------------------------
+# hyper-connection coefficients (sigmoid read / write weights, Sinkhorn-balanced mixing matrix), n = 4
+# ------------------------------------------------------------------------------------------------
+_f = C.c_float
+native.register_signature("nga_hc_coeff_fwd", [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _f, _vp])
+native.register_signature("nga_hc_coeff_bwd", [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _f, _vp])
+
+
+class _HCCoeff(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, mixes, scale, base, iters, eps):
+        lead = mixes.shape[:-1]
+        m = mixes.float().contiguous().view(-1, 24)
+        T = m.size(0)
+        sc, bs = scale.detach().float().contiguous(), base.detach().float().contiguous()
+        pre = torch.empty(T, 4, dtype=torch.float32, device=m.device)
+        post = torch.empty_like(pre)
+        comb = torch.empty(T, 16, dtype=torch.float32, device=m.device)
+        native.check(native.lib().nga_hc_coeff_fwd(_p(m), _p(sc), _p(bs), _p(pre), _p(post), _p(comb), T, 4, iters, eps,
+                                                   native.stream_ptr()), "nga_hc_coeff_fwd")
+        ctx.save_for_backward(m, sc, bs)
+        ctx.meta = (lead, iters, eps, mixes.dtype, scale.dtype, base.dtype)
+        return pre.view(*lead, 4), post.view(*lead, 4), comb.view(*lead, 4, 4)
+
+    @staticmethod
+    def backward(ctx, dpre, dpost, dcomb):
+        m, sc, bs = ctx.saved_tensors
+        lead, iters, eps, mdt, sdt, bdt = ctx.meta
+        T = m.size(0)
+        z = lambda g, n: (torch.zeros(T, n, dtype=torch.float32, device=m.device) if g is None else g.float().contiguous().view(T, n))
+        dpre, dpost, dcomb = z(dpre, 4), z(dpost, 4), z(dcomb, 16)
+        dm = torch.empty_like(m)
+        dscale = torch.zeros(3, dtype=torch.float32, device=m.device)
+        dbase = torch.zeros(24, dtype=torch.float32, device=m.device)
+        native.check(native.lib().nga_hc_coeff_bwd(_p(m), _p(sc), _p(bs), _p(dpre), _p(dpost), _p(dcomb), _p(dm), _p(dscale), _p(dbase),
+                                                   T, 4, iters, eps, native.stream_ptr()), "nga_hc_coeff_bwd")
+        return dm.view(*lead, 24).to(mdt), dscale.to(sdt), dbase.to(bdt), None, None
+
+
+def hc_coefficients_usable(mixes: torch.Tensor, streams: int, iterations: int) -> bool:
+    return mixes.is_cuda and streams == 4 and 1 <= iterations <= 32 and mixes.dtype != torch.float64 and native.available()
+
+
+def hc_coefficients(mixes, scale, base, iterations: int, eps: float):
+    """mixes [..., 24] -> (pre [..., 4], post [..., 4], comb [..., 4, 4]) in fp32, one kernel each way."""
+    return _HCCoeff.apply(mixes, scale, base, int(iterations), float(eps))

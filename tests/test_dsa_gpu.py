@@ -48,10 +48,13 @@ def test_indexer_selection_kernel_matches_topk_threshold(S, top_k):
     idx, vals = dsa.select_topk(scores, top_k)
     want, want_t = dsa_cuda.selection_bits_from_scores(scores, vals[..., -1:])
     # scores are recomputed in a different summation order: allow the few keys that sit on the threshold to differ
-    diff = (bits ^ want).view(torch.uint8)
-    flipped = sum(int((diff >> i & 1).sum()) for i in range(8))
-    assert flipped <= 0.002 * B * S * S
-    assert torch.equal(bits_t, dsa_cuda.transpose_bits(bits, S))
+    # (exact ties, e.g. keys whose four head products are all negative and score 0, are selected together by both)
+    unpack = lambda t: torch.stack([(t.view(torch.uint8) >> i) & 1 for i in range(8)], -1).flatten(-2)[..., :S].bool()
+    got, ref = unpack(bits), unpack(want)
+    flipped = int((got ^ ref).sum())
+    assert flipped <= 0.002 * B * S * S, flipped
+    assert torch.equal(bits_t, dsa_cuda.transpose_bits(bits, S)) and torch.equal(unpack(bits_t), got.transpose(1, 2))
     rows = torch.arange(S, device="cuda")
-    per_row = sum(((bits.view(torch.uint8) >> i) & 1).sum(-1) for i in range(8))
-    assert torch.all(per_row >= torch.clamp(rows + 1, max=top_k)[None, :]) and torch.all(per_row <= torch.clamp(rows + 1, max=top_k)[None, :] + 2)
+    assert not (got & (rows[None, :] > rows[:, None])[None]).any()                    # nothing above the diagonal
+    assert torch.all(got.sum(-1) >= torch.clamp(rows + 1, max=top_k)[None, :])        # at least k (all, when fewer exist)
+    assert (got.sum(-1) - ref.sum(-1)).abs().max() <= 4
