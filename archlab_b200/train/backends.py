@@ -77,8 +77,8 @@ class MeshBackend:
             sequence_parallel = False
         if global_batch % (micro_batch * dp):
             raise ValueError("global batch must be a multiple of micro batch x data parallel size")
-        if precision not in ("bf16", "fp8_block", "nvfp4"):
-            raise ValueError("precision must be bf16, fp8_block or nvfp4")
+        if precision not in ("bf16", "fp8_block", "fp8_tensor", "nvfp4"):
+            raise ValueError("precision must be bf16, fp8_block, fp8_tensor or nvfp4")
         argv = _torchrun(topology) + ["-m", "archlab_b200.train.mesh_train", f"--model={model}", f"--tp={tp}", f"--pp={pp}",
                                       f"--cp={cp}", f"--ep={ep}", f"--micro-batch={micro_batch}",
                                       f"--global-batch={global_batch}", f"--seq-len={seq_len}", f"--precision={precision}",

@@ -115,7 +115,9 @@ def parse_args(argv=None):
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--global-batch", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=8192)
-    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8_block", "nvfp4"])
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8_block", "fp8_tensor", "nvfp4"],
+                    help="fp8_block: 1x128 / 128x128 block rounding with straight-through gradients (bf16 GEMMs); "
+                         "fp8_tensor: tensor-scaled e4m3 / e5m2 GEMMs on the 8-bit tensor-core path")
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--weight-decay", type=float, default=0.1)
@@ -184,7 +186,8 @@ class _Job:
 
             if mesh.tp > 1 or mesh.pp > 1 or mesh.cp > 1:
                 raise ValueError("the V4.1 family runs under data + expert parallelism here")
-            kw = {"sequence_len": a.seq_len, **({"n_layer": a.n_layer} if a.n_layer else {})}
+            kw = {"sequence_len": a.seq_len, **({"n_layer": a.n_layer} if a.n_layer else {}),
+                  **({"fp8": True} if a.precision == "fp8_block" else {})}
             presets = {"v41_tiny": V41Config.tiny, "v41_moe": V41Config,
                        "v41_small": lambda **k: V41Config(**{**dict(vocab_size=32768, n_layer=2, hidden_size=1024, n_heads=8,
                                                                     n_routed_experts=16, moe_inter=512, index_top_k=256), **k})}
@@ -223,6 +226,10 @@ class _Job:
             raise ValueError(f"unknown model family {fam}")
         if device.type == "cuda":
             self.model.to(torch.bfloat16)
+        if a.precision == "fp8_tensor":
+            from ..ops.fp8 import convert_linears
+
+            self.fp8_layers = convert_linears(self.model)        # dense nn.Linear layers; expert and TP GEMMs stay bf16
 
     def _init_qwen(self, seed: int) -> None:
         g = torch.Generator().manual_seed(seed)
