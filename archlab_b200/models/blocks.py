@@ -28,7 +28,13 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor | None = None, *, eps: float 
         from ..ops import block_ops
 
         if block_ops.usable(x):
-            return block_ops.rms_norm(x, weight, eps=eps, zero_centered=zero_centered)
+            if weight is None or (weight.dim() == 1 and weight.numel() == x.size(-1)):
+                return block_ops.rms_norm(x, weight, eps=eps, zero_centered=zero_centered)
+            if weight.dim() == 2 and x.dim() >= 2 and tuple(x.shape[-2:]) == tuple(weight.shape):
+                # one gain row per slice of the second-to-last dimension: the grouped form of the kernel
+                y = block_ops.rms_norm(x.flatten(-2), weight.reshape(-1), eps=eps, zero_centered=zero_centered,
+                                       groups=weight.size(0))
+                return y.view(x.shape)
     xf = x.float()
     y = xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)
     if weight is not None:

@@ -18,9 +18,16 @@ def test_rmsnorm_variants():
     for groups, zc in ((1, False), (4, True), (4, False)):
         width = x.size(-1) // groups
         got = fm.rmsnorm(x, w, groups=groups, zero_centered=zc)
-        want = rms_norm(x.unflatten(-1, (groups, width)), w.view(groups, width), zero_centered=zc).flatten(-2)
+        xf = x.float().unflatten(-1, (groups, width))                      # plain fp32 statement of the op
+        gain = (1.0 + w.view(groups, width)) if zc else w.view(groups, width)
+        want = (xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + 1e-6) * gain).flatten(-2)
         assert _rel(got, want) < 6e-3
-    assert _rel(fm.rmsnorm(x), rms_norm(x)) < 6e-3
+        # the model-level function routes [.., groups, width] inputs with a [groups, width] gain to the same kernel
+        via = rms_norm(x.unflatten(-1, (groups, width)), w.view(groups, width), zero_centered=zc).flatten(-2)
+        assert _rel(via, want) < 6e-3
+    xf = x.float()
+    assert _rel(fm.rmsnorm(x), xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + 1e-6)) < 6e-3
+    assert _rel(rms_norm(x), xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + 1e-6)) < 6e-3
 
 
 def test_rope_styles():
@@ -30,7 +37,7 @@ def test_rope_styles():
     x = torch.randn(2, 33, 3, 64, device="cuda").bfloat16()
     cos, sin = rope_tables(33, 32, device="cuda")
     for inter in (False, True):
-        want = apply_rope(x, cos, sin, style="interleaved" if inter else "half", rot_dim=32)
+        want = apply_rope(x.float(), cos, sin, style="interleaved" if inter else "half", rot_dim=32)   # fp32 PyTorch path
         got = fm.rope_(x.clone(), cos, sin, rot_dim=32, interleaved=inter)
         assert _rel(got, want) < 6e-3 and torch.equal(got[..., 32:], x[..., 32:])
 
