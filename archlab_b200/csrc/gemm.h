@@ -41,6 +41,11 @@ int nga_tp_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K,
                      int b_mn, int mode, int rank, int world, int rows_per_rank, const long long* src_ptrs,
                      void* gathered, int* flags, int epoch, int copy_clusters, const long long* dst_ptrs,
                      int* status, void* stream);
+// Fully-sharded weight [w_rows, w_cols] in row shards on the ranks of a group: D = A . W^T (transposed = 0) or
+// D = A . W (transposed = 1), with the gather done by copy clusters of the same kernel (see gemm2.cu).
+int nga_fsdp_gemm_bf16(const void* A, void* D, int M, int w_rows, int w_cols, long long lda, long long ldd, int transposed,
+                       int rank, int world, int rows_per_rank, const long long* src_ptrs, void* gathered, int* flags,
+                       int epoch, int copy_clusters, int* status, void* stream);
 int nga_tp_reduce_slots(const void* stage, const void* resid, void* out, int world, long long rows, int N,
                         long long ld_stage, long long ld_resid, long long ld_out, void* stream);
 

@@ -210,7 +210,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();          // 0 = leader
   // With the all-gather fused in, the first `copy_clusters` clusters only move data.
-  const int copy_clusters = (TP && (tp.mode & kTpGather)) ? tp.copy_clusters : 0;
+  const int copy_clusters = (TP && (tp.mode & kTpGatherAny)) ? tp.copy_clusters : 0;
   const bool copy_role = TP && int(blockIdx.x >> 1) < copy_clusters;
   const int cluster_id = int(blockIdx.x >> 1) - copy_clusters;
   const int num_clusters = int(gridDim.x >> 1) - copy_clusters;
@@ -245,7 +245,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
   if (copy_role) {
     if (threadIdx.x == 0)
-      tp_copy_role(tp, p.K, smem, full_bar, int(blockIdx.x), 2 * copy_clusters, abort_word);
+      tp_copy_role(tp, tp.row_elems, smem, full_bar, int(blockIdx.x), 2 * copy_clusters, abort_word);
   } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
@@ -255,13 +255,14 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      bool gathered_seen = false;                          // every block of the gathered B has been waited for once
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         int b, mb, nb, otile, kb0, kb1;
         split_range(tile, p.splits, num_kb, otile, kb0, kb1);
         tile_coords(otile, num_m, num_n, b, mb, nb);
-        if (TP) mb = tp_remap_mb(tp, mb, num_m);
+        if (TP) { mb = tp_remap_mb(tp, mb, num_m); nb = tp_remap_nb(tp, nb, num_n); }
         int m0 = mb * 2 * BM + int(rank) * BM;             // this CTA's 128 rows of A
-        const int n0 = nb * G2_BN + int(rank) * 128;       // this CTA's 128 N-rows of B
+        int n0 = nb * G2_BN + int(rank) * 128;             // this CTA's 128 N-rows of B
         const int grp_off = p.group_of_mtile ? p.group_of_mtile[mb] * p.group_rows : 0;   // rows of B before this tile's group
         const CUtensorMap* mapA = &tmA;
         if (TP && (tp.mode & kTpGather)) {
@@ -275,7 +276,35 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             fence_proxy_async_all();
           }
         }
-        for (int kb = kb0; kb < kb1; ++kb) {
+        const CUtensorMap* mapB = &tmB;
+        if (TP && (tp.mode & kTpGatherB)) {
+          const int owner = n0 / tp.rows_per_rank;
+          if (owner == tp.rank) {                          // own weight rows: straight from the local shard
+            mapB = &tmA2;
+            n0 -= owner * tp.rows_per_rank;
+          } else {
+            ok = wait_block_ready(tp.flags + n0 / 128, tp.epoch, abort_word);
+            if (!ok) break;
+            fence_proxy_async_all();
+          }
+        }
+        for (int kbi = kb0; kbi < kb1; ++kbi) {
+          int kb = kbi;
+          int brow = kb * BK;                              // first reduction row of an MN-major B block
+          const CUtensorMap* mapBk = mapB;
+          if (TP && B_MN && (tp.mode & kTpGatherBk)) {
+            kb = kbi + tp.rank * (tp.rows_per_rank / BK);  // start at this rank's own rows
+            if (kb >= num_kb) kb -= num_kb;
+            brow = kb * BK;
+            if (brow / tp.rows_per_rank == tp.rank) {
+              mapBk = &tmA2;
+              brow -= tp.rank * tp.rows_per_rank;
+            } else if (!gathered_seen) {
+              ok = wait_block_ready(tp.flags + brow / 128, tp.epoch, abort_word);
+              if (!ok) break;
+              fence_proxy_async_all();
+            }
+          }
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word);
           if (!ok) break;
           uint8_t* sA = smem + stage * G2_STAGE_BYTES;
@@ -292,12 +321,13 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < 2; ++j)
-              tma_load_3d_pair(sB + j * 8192, &tmB, leader_full, n0 + j * 64, kb * BK + grp_off, b);
+              tma_load_3d_pair(sB + j * 8192, mapBk, leader_full, n0 + j * 64, brow + grp_off, b);
           } else {
-            tma_load_3d_pair(sB, &tmB, leader_full, kb * BKE, n0 + grp_off, b);
+            tma_load_3d_pair(sB, mapB, leader_full, kb * BKE, n0 + grp_off, b);
           }
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1u; }
         }
+        if (TP && (tp.mode & kTpGatherBk) && ok) gathered_seen = true;
       }
     }
   } else if (warp == 1) {
@@ -357,7 +387,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int b, mb, nb, otile, kb0, kb1;
       split_range(tile, p.splits, num_kb, otile, kb0, kb1);
       tile_coords(otile, num_m, num_n, b, mb, nb);
-      if (TP) mb = tp_remap_mb(tp, mb, num_m);
+      if (TP) { mb = tp_remap_mb(tp, mb, num_m); nb = tp_remap_nb(tp, nb, num_n); }
       const int row = mb * 2 * BM + int(rank) * BM + quarter * 32 + lane;
       GemmParams pt = p;
       if (TP && (tp.mode & kTpScatter)) {                   // this tile's rows live on rank `owner`
@@ -469,7 +499,7 @@ static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
   }
   const int num_tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch * p.splits;
   int clusters = num_tiles < max_clusters ? num_tiles : max_clusters;
-  if (TP && (tp.mode & kTpGather)) {
+  if (TP && (tp.mode & kTpGatherAny)) {
     // every cluster must be resident at once: the GEMM clusters wait for the copy clusters
     if (tp.copy_clusters < 1 || tp.copy_clusters >= max_clusters) return -9;
     const int gemm_clusters = num_tiles < max_clusters - tp.copy_clusters ? num_tiles : max_clusters - tp.copy_clusters;
@@ -655,6 +685,7 @@ extern "C" int nga_tp_gemm_bf16(const void* A, const void* B, void* D, int M, in
   TpParams tp = {};
   tp.mode = mode; tp.rank = rank; tp.world = world; tp.rows_per_rank = rows_per_rank;
   tp.copy_clusters = copy_clusters; tp.epoch = epoch; tp.flags = flags; tp.gathered = gathered;
+  tp.row_elems = K;
   for (int r = 0; r < world; ++r) {
     tp.peer_src[r] = (mode == kTpGather) ? reinterpret_cast<const void*>(src_ptrs[r]) : nullptr;
     tp.peer_dst[r] = (mode == kTpScatter) ? reinterpret_cast<void*>(dst_ptrs[r]) : nullptr;
@@ -692,6 +723,55 @@ extern "C" int nga_tp_gemm_bf16(const void* A, const void* B, void* D, int M, in
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (b_mn) return launch_gemm2<0, 1, 1>(ta, tb, p, st, ta2, tp, tpm);
   return launch_gemm2<0, 0, 1>(ta, tb, p, st, ta2, tp, tpm);
+}
+
+// GEMMs against a fully-sharded weight W [w_rows = world * rows_per_rank, w_cols] that lives as row shards on the
+// ranks of a data-parallel group: `src_ptrs[r]` is rank r's shard [rows_per_rank, w_cols] (contiguous, symmetric
+// memory), `gathered` a local [w_rows, w_cols] buffer that holds the whole weight afterwards, `flags` a local int
+// array with one entry per 128 weight rows (zero-initialised once; `epoch` grows by one per call on the same
+// flags).  A and D are local bf16 with row pitches lda, ldd.
+//   transposed = 0 (forward):        D [M, w_rows] = A [M, w_cols] . W^T
+//   transposed = 1 (data gradient):  D [M, w_cols] = A [M, w_rows] . W
+extern "C" int nga_fsdp_gemm_bf16(const void* A, void* D, int M, int w_rows, int w_cols, long long lda, long long ldd,
+                                  int transposed, int rank, int world, int rows_per_rank, const long long* src_ptrs,
+                                  void* gathered, int* flags, int epoch, int copy_clusters, int* status, void* stream) {
+  using namespace nga;
+  if (M <= 0 || w_rows <= 0 || w_cols <= 0 || world < 1 || world > kTpMaxWorld || rank < 0 || rank >= world) return -1;
+  if (rows_per_rank <= 0 || rows_per_rank % 256 || w_rows != world * rows_per_rank) return -2;
+  if ((w_cols & 63) || (lda & 7) || (ldd & 7)) return -5;
+  if (A == nullptr || D == nullptr || gathered == nullptr || flags == nullptr || src_ptrs == nullptr) return -4;
+  TpParams tp = {};
+  tp.mode = transposed ? kTpGatherBk : kTpGatherB;
+  tp.rank = rank; tp.world = world; tp.rows_per_rank = rows_per_rank;
+  tp.copy_clusters = copy_clusters; tp.epoch = epoch; tp.flags = flags; tp.gathered = gathered;
+  tp.row_elems = w_cols;
+  for (int r = 0; r < world; ++r) {
+    tp.peer_src[r] = reinterpret_cast<const void*>(src_ptrs[r]);
+    tp.peer_dst[r] = nullptr;
+    if (tp.peer_src[r] == nullptr) return -4;
+  }
+  const int N = transposed ? w_cols : w_rows;
+  const int K = transposed ? w_rows : w_cols;
+  CUtensorMap ta, tb, tb_own;
+  int rc = make_tmap_3d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, 1, lda * 2, (long long)M * lda * 2, 64, 128, true);
+  if (rc) return rc;
+  const int box_rows = transposed ? 64 : 128;     // MN-major B: 64 output columns x 64 reduction rows per load
+  rc = make_tmap_3d(&tb, gathered, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w_cols, w_rows, 1, (long long)w_cols * 2,
+                    (long long)w_rows * w_cols * 2, 64, box_rows, true);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tb_own, tp.peer_src[rank], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, w_cols, rows_per_rank, 1,
+                    (long long)w_cols * 2, (long long)rows_per_rank * w_cols * 2, 64, box_rows, true);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.batch = 1;
+  p.D = D; p.aux = nullptr; p.ldd = ldd; p.ldaux = 0; p.sD = 0; p.sAux = 0;
+  p.epi = kEpiScale; p.out_fp32 = 0; p.aux_fp32 = 0; p.alpha = 1.f; p.beta = 0.f; p.splits = 1;
+  p.status = status; p.row_shift = 0;
+  p.group_of_mtile = nullptr; p.group_rows = 0;
+  TpMaps tpm = {};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (transposed) return launch_gemm2<0, 1, 1>(ta, tb, p, st, tb_own, tp, tpm);
+  return launch_gemm2<0, 0, 1>(ta, tb, p, st, tb_own, tp, tpm);
 }
 
 extern "C" int nga_tp_reduce_slots(const void* stage, const void* resid, void* out, int world, long long rows, int N,

@@ -41,9 +41,20 @@ struct GemmParams {
 constexpr int kTpMaxWorld = 8;
 constexpr int kTpGather = 1;
 constexpr int kTpScatter = 2;
+// kTpGatherB: the B operand (a weight [N, K] whose row shards live on the ranks of a data-parallel group)
+//               is gathered by the copy clusters exactly as kTpGather gathers A; the GEMM clusters start on
+//               the output columns of this rank's own shard (read straight from it) and wait (bounded) for
+//               the 128-row blocks of the other shards.  A [M, K] and D [M, N] are local.
+constexpr int kTpGatherB = 4;
+// kTpGatherBk: the same gather for an MN-major B whose rows are the reduction dimension (the data gradient
+//               dX = dY . W of a fully-sharded weight): every tile walks the k-blocks starting at this rank's
+//               own shard and waits (bounded) for each block of the others the first time it needs it.
+constexpr int kTpGatherBk = 8;
+constexpr int kTpGatherAny = kTpGather | kTpGatherB | kTpGatherBk;
 struct TpParams {
   int mode, rank, world, rows_per_rank;
   int copy_clusters, epoch;
+  int row_elems;                       // elements per row of the gathered matrix
   int* flags;                          // one per 128-row block of the gathered matrix; value = epoch when ready
   const void* peer_src[kTpMaxWorld];   // row shard of every rank (bf16, contiguous rows of K elements, symmetric)
   void* gathered;                      // local [world * rows_per_rank, K] bf16
@@ -58,11 +69,19 @@ struct TpMaps {
 };
 
 __device__ __forceinline__ int tp_remap_mb(const TpParams& tp, int mb, int num_m) {
-  if (tp.mode == 0) return mb;
+  if (tp.mode == 0 || (tp.mode & (kTpGatherB | kTpGatherBk))) return mb;
   const int per = tp.rows_per_rank / (2 * BM);
   const int first = (tp.mode & kTpGather) ? tp.rank * per : ((tp.rank + 1) % tp.world) * per;
   int r = mb + first;
   return r >= num_m ? r - num_m : r;
+}
+
+// Column-tile order under kTpGatherB: this rank's own shard first, then the shards in the order the copy
+// clusters fetch them (rank + 1, rank + 2, ...).
+__device__ __forceinline__ int tp_remap_nb(const TpParams& tp, int nb, int num_n) {
+  if (!(tp.mode & kTpGatherB)) return nb;
+  const int r = nb + tp.rank * (tp.rows_per_rank / 256);
+  return r >= num_n ? r - num_n : r;
 }
 
 __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& b, int& mb, int& nb) {

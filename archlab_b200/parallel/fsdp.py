@@ -1,0 +1,216 @@
+"""Fully-sharded linear weights whose all-gather runs inside the consuming GEMM kernel.
+
+Every weight ``[out, in]`` is stored as one row shard per rank of a data-parallel group, all shards
+of a model in one symmetric (peer-mapped) buffer.  The forward GEMM ``y = x W^T`` and the
+data-gradient GEMM ``dx = dy W`` are launched on the *sharded* weight: a few clusters of the GEMM
+kernel pull the other ranks' shards over NVLink into a local scratch buffer and flag 128-row blocks
+as they land, while the tensor cores start on the tiles (forward) or k-blocks (data gradient) that
+need only this rank's own rows and then follow the arrival order.  No separate all-gather kernel is
+launched and no barrier is needed per layer: shards only change in the optimizer step, which is
+bracketed by ``FsdpGroup.sync()``.  The weight gradient is a local GEMM followed by a
+reduce-scatter to the shard owners.
+
+This is the role of Megatron's ``--overlap-param-gather`` distributed optimizer
+(src/archlab/megatron/qwen38_flash_next_config.py:216-221) and of FSDP2 in the RL trainer
+(src/archlab/training/config.py), where the gather is an NCCL call on a side stream.  On CPU (gloo)
+or without the native library the same classes run gather + matmul, which is also the test oracle.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..ops import native
+
+_vp, _i, _ll = C.c_void_p, C.c_int, C.c_longlong
+native.register_signature("nga_fsdp_gemm_bf16", [_vp, _vp, _i, _i, _i, _ll, _ll, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i,
+                                                 _vp, _vp])
+
+
+def _round_up(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
+class FsdpGroup:
+    """Shard storage, gather scratch and arrival flags shared by the sharded linears of one model."""
+
+    def __init__(self, device, group=None, copy_clusters: int = 12):
+        self.group = group or dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.device = torch.device(device)
+        self.copy_clusters = copy_clusters
+        self.layers: list["FsdpLinear"] = []
+        self.flat = None                # SymmTensor (CUDA) or a plain tensor (CPU)
+        self.fused = False
+        self.epoch = 0
+
+    # -- construction ------------------------------------------------------------------------------
+    def register(self, layer: "FsdpLinear") -> None:
+        if self.flat is not None:
+            raise RuntimeError("the group is already materialised")
+        self.layers.append(layer)
+
+    def materialize(self) -> None:
+        """Allocates the shard buffer (symmetric memory on CUDA) and binds every layer's parameter to its slice."""
+        total, biggest = 0, 0
+        for layer in self.layers:
+            layer.offset = total
+            total += layer.rows_per_rank * layer.in_features
+            biggest = max(biggest, layer.padded_out * layer.in_features)
+        self.fused = self.device.type == "cuda" and native.available() and self.world <= 8
+        if self.fused:
+            from .symm import PeerBarrier, symm_zeros
+
+            self.flat = symm_zeros((total,), torch.bfloat16, self.device, self.group)
+            flat = self.flat.tensor
+            self.gathered = torch.empty(biggest, dtype=torch.bfloat16, device=self.device)
+            rows = max(layer.padded_out for layer in self.layers)
+            self.flags = torch.zeros(rows // 128, dtype=torch.int32, device=self.device)
+            self.barrier = PeerBarrier(self.device, self.group)
+        else:
+            self.flat = torch.zeros(total, dtype=torch.bfloat16 if self.device.type == "cuda" else torch.float32,
+                                    device=self.device)
+            flat = self.flat
+        for layer in self.layers:
+            n = layer.rows_per_rank * layer.in_features
+            layer.weight = nn.Parameter(flat[layer.offset: layer.offset + n].view(layer.rows_per_rank, layer.in_features))
+            layer._ptrs = self.flat.ptr_array(layer.offset) if self.fused else None
+
+    def sync(self) -> None:
+        """Orders shard writes (optimizer step, weight loading) against the peers' reads: call it before and
+        after anything that writes the shards."""
+        if self.fused:
+            self.barrier()
+        else:
+            dist.barrier(self.group)
+
+    # -- the two GEMMs against a sharded weight ------------------------------------------------------
+    def full_weight(self, layer: "FsdpLinear") -> torch.Tensor:
+        """[padded_out, in] by a plain all-gather (decomposed path, checkpoints, tests)."""
+        full = torch.empty(layer.padded_out, layer.in_features, dtype=layer.weight.dtype, device=layer.weight.device)
+        dist.all_gather_into_tensor(full, layer.weight.detach().contiguous(), group=self.group)
+        return full
+
+    def gemm(self, a: torch.Tensor, layer: "FsdpLinear", transposed: bool) -> torch.Tensor:
+        """``a @ W^T`` (``transposed=False``: a [M, in] -> [M, padded_out]) or ``a @ W`` (a [M, padded_out] -> [M, in])."""
+        if not self.fused:
+            w = self.full_weight(layer)
+            return a @ (w if transposed else w.t())
+        M = a.size(0)
+        n_out = layer.in_features if transposed else layer.padded_out
+        out = torch.empty(M, n_out, dtype=torch.bfloat16, device=a.device)
+        self.epoch += 1
+        rc = native.lib().nga_fsdp_gemm_bf16(
+            a.data_ptr(), out.data_ptr(), M, layer.padded_out, layer.in_features, a.stride(0), out.stride(0),
+            int(transposed), self.rank, self.world, layer.rows_per_rank, layer._ptrs, self.gathered.data_ptr(),
+            self.flags.data_ptr(), self.epoch, self.copy_clusters, native.status_word(a.device).data_ptr(),
+            native.stream_ptr())
+        native.check(rc, "nga_fsdp_gemm_bf16")
+        return out
+
+    def gathered_view(self, layer: "FsdpLinear") -> torch.Tensor:
+        """The whole weight as left in the scratch buffer by the last fused GEMM on ``layer``."""
+        return self.gathered[: layer.padded_out * layer.in_features].view(layer.padded_out, layer.in_features)
+
+    def reduce_scatter_grad(self, full_grad: torch.Tensor, layer: "FsdpLinear") -> torch.Tensor:
+        """Mean over the group of a [padded_out, in] gradient, returned as this rank's row shard."""
+        out = torch.empty(layer.rows_per_rank, layer.in_features, dtype=full_grad.dtype, device=full_grad.device)
+        if full_grad.is_cuda:
+            dist.reduce_scatter_tensor(out, full_grad, op=dist.ReduceOp.AVG, group=self.group)
+        else:
+            total = full_grad.clone()                       # gloo has no reduce-scatter
+            dist.all_reduce(total, group=self.group)
+            out.copy_(total.chunk(self.world, 0)[self.rank] / self.world)
+        return out
+
+
+class _FsdpLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, shard, layer):
+        g = layer.group
+        x2 = x.reshape(-1, layer.in_features)
+        if g.fused:
+            x2 = x2.to(torch.bfloat16).contiguous()
+        y = g.gemm(x2, layer, transposed=False)
+        ctx.save_for_backward(x2)
+        ctx.layer, ctx.lead = layer, x.shape[:-1]
+        if layer.padded_out != layer.out_features:
+            y = y[:, : layer.out_features]
+        return y.reshape(*x.shape[:-1], layer.out_features).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x2,) = ctx.saved_tensors
+        layer = ctx.layer
+        g = layer.group
+        dy2 = dy.reshape(-1, layer.out_features)
+        if layer.padded_out != layer.out_features:
+            pad = dy2.new_zeros(dy2.size(0), layer.padded_out)
+            pad[:, : layer.out_features] = dy2
+            dy2 = pad
+        if g.fused:
+            from ..ops import gemm as G
+
+            dy2 = dy2.to(torch.bfloat16).contiguous()
+            dx = g.gemm(dy2, layer, transposed=True) if ctx.needs_input_grad[0] else None
+            dw = G.gemm(dy2, x2, a_mn=True, b_mn=True)                      # [padded_out, in] = dy^T x
+        else:
+            dx = g.gemm(dy2, layer, transposed=True) if ctx.needs_input_grad[0] else None
+            dw = dy2.t() @ x2
+        dshard = g.reduce_scatter_grad(dw, layer).to(layer.weight.dtype)
+        if dx is not None:
+            dx = dx.reshape(*ctx.lead, layer.in_features).to(dy.dtype)
+        return dx, dshard, None
+
+
+class FsdpLinear(nn.Module):
+    """``y = x W^T`` with W [out, in] sharded by rows over the ranks of ``group`` (no bias).
+
+    ``in_features`` must be a multiple of 64; ``out_features`` is padded (with zero rows that stay zero) to a
+    multiple of ``256 * world`` so that every rank owns whole 256-row tiles."""
+
+    def __init__(self, group: FsdpGroup, in_features: int, out_features: int):
+        super().__init__()
+        if in_features % 64:
+            raise ValueError("in_features must be a multiple of 64")
+        self.group, self.in_features, self.out_features = group, in_features, out_features
+        self.padded_out = _round_up(out_features, 256 * group.world)
+        self.rows_per_rank = self.padded_out // group.world
+        self.offset = 0
+        self.weight = None
+        self._ptrs = None
+        group.register(self)
+
+    def load_full(self, w: torch.Tensor) -> None:
+        """Copies this rank's rows of a full [out, in] weight into the shard (call ``group.sync()`` afterwards)."""
+        r0 = self.group.rank * self.rows_per_rank
+        with torch.no_grad():
+            self.weight.zero_()
+            n = max(0, min(self.out_features, r0 + self.rows_per_rank) - r0)
+            if n:
+                self.weight[:n].copy_(w[r0: r0 + n])
+
+    def forward(self, x):
+        if self.weight is None:
+            raise RuntimeError("FsdpGroup.materialize() has not been called")
+        return _FsdpLinearFn.apply(x, self.weight, self)
+
+
+def shard_linears(module: nn.Module, group: FsdpGroup, *, min_features: int = 256) -> nn.Module:
+    """Replaces every bias-free ``nn.Linear`` whose sides are at least ``min_features`` (and whose input width is
+    a multiple of 64) by an ``FsdpLinear`` holding the same values, then materialises the group."""
+    swaps = []
+    for parent in module.modules():
+        for name, child in parent.named_children():
+            if (isinstance(child, nn.Linear) and child.bias is None and child.in_features % 64 == 0
+                    and min(child.in_features, child.out_features) >= min_features):
+                swaps.append((parent, name, child, FsdpLinear(group, child.in_features, child.out_features)))
+    group.materialize()
+    for parent, name, old, new in swaps:
+        new.load_full(old.weight.detach().to(new.weight.dtype))
+        setattr(parent, name, new)
+    group.sync()
+    return module

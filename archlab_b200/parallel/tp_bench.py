@@ -43,6 +43,7 @@ def main(argv=None):
     ap.add_argument("--gemm-peak-tflops", type=float, default=1684.0)
     ap.add_argument("--link-gbs", type=float, default=770.0)
     ap.add_argument("--copy-clusters", type=int, default=12)
+    ap.add_argument("--fsdp", action="store_true", help="also time the fused weight-gather GEMMs of a sharded linear")
     ap.add_argument("--sweep", type=int, nargs="*", default=[], help="extra copy-cluster counts to time")
     a = ap.parse_args(argv)
     rank = int(os.environ.get("LOCAL_RANK", 0))
@@ -98,6 +99,38 @@ def main(argv=None):
     for name, fn in (("gemm_rs_fused", lambda: T.gemm_rs(grp, act, w2, out=ys)), ("gemm_rs_nccl", nccl_rs)):
         ms = _time(fn, a.iters, flush)
         rows.append({"op": name, "ms": ms, "tflops": flops2 / ms / 1e9, "roofline_ms": roof2, "of_roofline": roof2 / ms})
+    if a.fsdp:
+        # fully-sharded weight [n, k] (row shards on the ranks): forward x W^T and data gradient dy W with the
+        # weight gather inside the GEMM kernel, against an NCCL all-gather of the weight followed by the GEMM
+        from .fsdp import FsdpGroup, FsdpLinear
+
+        fg = FsdpGroup(dev, copy_clusters=a.copy_clusters)
+        lay = FsdpLinear(fg, a.k, a.n)
+        fg.materialize()
+        lay.weight.data.normal_(0, 0.02)
+        fg.sync()
+        xm = torch.randn(M, a.k, device=dev).bfloat16()
+        dym = torch.randn(M, lay.padded_out, device=dev).bfloat16()
+        wfull = torch.empty(lay.padded_out, a.k, device=dev, dtype=torch.bfloat16)
+        yo = torch.empty(M, lay.padded_out, device=dev, dtype=torch.bfloat16)
+        dxo = torch.empty(M, a.k, device=dev, dtype=torch.bfloat16)
+
+        def nccl_fwd():
+            dist.all_gather_into_tensor(wfull, lay.weight.data)
+            G.gemm(xm, wfull, out=yo)
+
+        def nccl_dgrad():
+            dist.all_gather_into_tensor(wfull, lay.weight.data)
+            G.gemm(dym, wfull, b_mn=True, out=dxo)
+
+        flops3 = 2.0 * M * lay.padded_out * a.k
+        link3 = (world - 1) * lay.rows_per_rank * a.k * 2
+        roof3 = max(flops3 / (a.gemm_peak_tflops * 1e12), link3 / (a.link_gbs * 1e9)) * 1e3
+        for name, fn in (("fsdp_fwd_fused", lambda: fg.gemm(xm, lay, False)), ("fsdp_fwd_nccl", nccl_fwd),
+                         ("fsdp_dgrad_fused", lambda: fg.gemm(dym, lay, True)), ("fsdp_dgrad_nccl", nccl_dgrad),
+                         ("fsdp_gemm_only", lambda: G.gemm(xm, wfull, out=yo))):
+            ms = _time(fn, a.iters, flush)
+            rows.append({"op": name, "ms": ms, "tflops": flops3 / ms / 1e9, "roofline_ms": roof3, "of_roofline": roof3 / ms})
     if rank == 0:
         for r in rows:
             r.update(world=world, rows_per_rank=a.rows, k=a.k, n=a.n, peaks="measured cuBLAS bf16 burst / peer copy")

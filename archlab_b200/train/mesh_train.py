@@ -118,6 +118,12 @@ def parse_args(argv=None):
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8_block", "fp8_tensor", "nvfp4"],
                     help="fp8_block: 1x128 / 128x128 block rounding with straight-through gradients (bf16 GEMMs); "
                          "fp8_tensor: tensor-scaled e4m3 / e5m2 GEMMs on the 8-bit tensor-core path")
+    ap.add_argument("--model-set", action="append", default=[], metavar="KEY=VALUE",
+                    help="factory models: override a field of the family's config (repeatable; values parse as JSON)")
+    ap.add_argument("--fsdp", action="store_true",
+                    help="factory models: shard the linear weights over the data group; the all-gather of a weight runs "
+                         "inside the GEMM that consumes it")
+    ap.add_argument("--fsdp-min-features", type=int, default=256, help="smallest linear side that is sharded")
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--weight-decay", type=float, default=0.1)
@@ -218,7 +224,10 @@ class _Job:
             if mesh.tp > 1 or mesh.pp > 1 or mesh.cp > 1 or a.ep > 1:
                 raise ValueError("factory models run under data parallelism in this trainer")
             torch.manual_seed(a.seed)
-            extra = {"sequence_len": a.seq_len}
+            extra = {"sequence_len": a.seq_len, **({"n_layer": a.n_layer} if a.n_layer else {})}
+            for item in getattr(a, "model_set", None) or []:            # KEY=VALUE overrides of the family's config
+                key, _, val = item.partition("=")
+                extra[key] = json.loads(val) if val and (val[0] in "[{\"-" or val[0].isdigit() or val in ("true", "false", "null")) else val
             self.model = build_model(a.model.split(":", 1)[1], extra, device=device)
             self.act_shape, self.kind = None, "dp"
             self.vocab = int(getattr(self.model.config, "vocab_size"))
@@ -230,6 +239,15 @@ class _Job:
             from ..ops.fp8 import convert_linears
 
             self.fp8_layers = convert_linears(self.model)        # dense nn.Linear layers; expert and TP GEMMs stay bf16
+        self.fsdp = None
+        if getattr(a, "fsdp", False):
+            # fully-sharded linear weights over the data group: the gather runs inside the consuming GEMM kernel
+            if self.kind != "dp" or mesh.dp < 2:
+                raise ValueError("--fsdp shards the linears of a factory model over a data group of at least two ranks")
+            from ..parallel.fsdp import FsdpGroup, shard_linears
+
+            self.fsdp = FsdpGroup(device, groups["dp"])
+            shard_linears(self.model, self.fsdp, min_features=a.fsdp_min_features)
 
     def _init_qwen(self, seed: int) -> None:
         g = torch.Generator().manual_seed(seed)
@@ -242,6 +260,10 @@ class _Job:
             p.data.copy_(torch.randn(p.shape, generator=g).mul_(0.02).to(p.dtype))
 
     def expert_params(self) -> set:
+        """Parameters that every data rank owns a different part of (updated locally, never reduced over the group):
+        routed experts under expert parallelism, row shards of fully-sharded linears."""
+        if self.fsdp is not None:
+            return {layer.weight for layer in self.fsdp.layers}
         if self.kind != "ep" or not hasattr(self.model.layers[0].ffn, "local_experts"):
             return set()
         return {p for n, p in self.model.named_parameters() if ".experts." in n}
@@ -409,9 +431,14 @@ class MeshOptimizer:
         return float(total.sqrt()) * scale
 
     def step(self, lr_scale: float, grad_scale: float) -> None:
+        fsdp = getattr(self.job, "fsdp", None)
+        if fsdp is not None:
+            fsdp.sync()                                   # no peer still reads the shards this step rewrites
         self.zero.step(lr_scale=lr_scale, grad_scale=grad_scale)
         if self.experts is not None:
             self.experts.step(lr_scale=lr_scale, grad_scale=grad_scale)
+        if fsdp is not None:
+            fsdp.sync()                                   # the new shards are visible before the next forward
 
 
 def train(a, *, on_step=None) -> list[float]:

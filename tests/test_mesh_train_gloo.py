@@ -132,3 +132,19 @@ def test_stop_request_checkpoints_and_leaves_cleanly(tmp_path, monkeypatch):
     assert len(losses) == 2
     assert json.loads((run / "STOPPED.json").read_text())["step"] == 2
     assert (run / "checkpoints" / "latest_checkpointed_iteration.txt").read_text().strip() == "2" and (run / "HEARTBEAT.json").exists()
+
+
+def test_fully_sharded_linears_follow_the_replicated_run(tmp_path):
+    """The same data-parallel job with replicated weights and with row-sharded linears: equal loss curves."""
+    from archlab_b200.models.factory import families
+
+    fam = "nanochat" if "nanochat" in families() else families()[0]
+    base = [f"--model=factory:{fam}", "--seq-len=32", "--global-batch=4", "--micro-batch=2", "--steps=4", "--lr=3e-3"]
+    if fam == "nanochat":
+        base += ["--n-layer=2", "--model-set=n_embd=128", "--model-set=n_head=2", "--model-set=n_kv_head=2",
+                 "--model-set=vocab_size=512"]
+    plain = _run(2, base + [f"--run-dir={tmp_path / 'plain'}"])
+    shard = _run(2, base + ["--fsdp", "--fsdp-min-features=64", f"--run-dir={tmp_path / 'fsdp'}"])
+    assert all(abs(a - b) < 2e-3 * abs(a) for a, b in zip(plain[0], shard[0])), (plain[0], shard[0])
+    assert shard[0][-1] < shard[0][0]
+    assert all(abs(a - b) < 1e-6 for a, b in zip(shard[0], shard[1]))
