@@ -27,6 +27,14 @@ int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, 
                  uint64_t stride2_bytes, uint32_t b0, uint32_t b1, bool swizzle128) {
   auto fn = encode_fn();
   if (!fn) return -2;
+  // The encode call is a driver entry point and needs a context bound to the calling thread.  A thread that has
+  // only inherited the default device (an autograd worker before its first launch) has none yet: one runtime
+  // call binds the primary context of the thread's current device.
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
   if ((reinterpret_cast<uintptr_t>(base) & 15) || (stride1_bytes & 15) || (stride2_bytes & 15)) return -3;
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};

@@ -1,7 +1,7 @@
 """Times the fused tensor-parallel GEMMs against their roofline and their NCCL-decomposed form.
 
 Launch: ``python -m torch.distributed.run --nproc-per-node W --master-addr 127.0.0.1 -m
-archlab_b200.parallel.tp_bench [--rows R --k K --n N]``.  Rank 0 prints one JSON line per op:
+archlab_b200.parallel.tp_bench [--rows R --k K --cols N] [--fsdp]``.  Rank 0 prints one JSON line per op:
 device time (max over ranks, CUDA events, L2 flushed between iterations), achieved TFLOP/s, the
 roofline time = max(FLOPs / GEMM peak, NVLink bytes / link bandwidth) and achieved / roofline.
 """
@@ -38,7 +38,8 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--rows", type=int, default=4096)
     ap.add_argument("--k", type=int, default=2560)
-    ap.add_argument("--n", type=int, default=3072)
+    ap.add_argument("--n", "--cols", dest="n", type=int, default=3072,
+                    help="output width (use --cols under torch.distributed.run, whose own options start with --n)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--gemm-peak-tflops", type=float, default=1684.0)
     ap.add_argument("--link-gbs", type=float, default=770.0)

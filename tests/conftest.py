@@ -22,3 +22,18 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def join_ranks(procs, timeout: float = 600.0) -> None:
+    """Waits for the child processes of a multi-rank test; a rank whose peer failed must not outlive the test
+    (it would sit in a collective until the process-group timeout), so stragglers are terminated."""
+    try:
+        for p in procs:
+            p.join(timeout=timeout)
+            assert not p.is_alive(), "worker timed out"
+            assert p.exitcode == 0, f"worker exited with code {p.exitcode}"
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=30)

@@ -65,12 +65,9 @@ def test_fused_ep_moe_matches_all_to_all(tmp_path):
     procs = [ctx.Process(target=_worker, args=(r, 2, 29641, str(tmp_path))) for r in range(2)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(timeout=600)
-        if p.is_alive():
-            p.terminate()
-            pytest.fail("worker timed out")
-        assert p.exitcode == 0
+    from conftest import join_ranks
+
+    join_ranks(procs)
     for r in range(2):
         res = torch.load(tmp_path / f"ep_rank{r}.pt")
         for key, v in res.items():

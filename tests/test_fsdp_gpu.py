@@ -70,15 +70,12 @@ def _worker(rank, world, port, out_dir):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_fused_weight_gather_gemms(tmp_path):
     ctx = mp.get_context("spawn")
-    procs = [ctx.Process(target=_worker, args=(r, 2, 29641, str(tmp_path))) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, 29661, str(tmp_path))) for r in range(2)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(timeout=600)
-        if p.is_alive():
-            p.terminate()
-            pytest.fail("worker timed out")
-        assert p.exitcode == 0
+    from conftest import join_ranks
+
+    join_ranks(procs, timeout=300)
     for r in range(2):
         res = torch.load(tmp_path / f"fsdp_rank{r}.pt")
         for k, v in res.items():

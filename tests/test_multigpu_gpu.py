@@ -48,12 +48,9 @@ def _run(tmp_path, zero_impl, port):
     procs = [ctx.Process(target=_worker, args=(r, 2, port, str(tmp_path), zero_impl)) for r in range(2)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(timeout=600)
-        if p.is_alive():
-            p.terminate()
-            pytest.fail("multi-GPU worker timed out")
-        assert p.exitcode == 0
+    from conftest import join_ranks
+
+    join_ranks(procs)
     return [torch.load(tmp_path / f"{zero_impl}_rank{r}.pt") for r in range(2)]
 
 

@@ -59,12 +59,9 @@ def test_fused_tp_gemms_match_decomposed(tmp_path):
     procs = [ctx.Process(target=_worker, args=(r, 2, 29631, str(tmp_path))) for r in range(2)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(timeout=600)
-        if p.is_alive():
-            p.terminate()
-            pytest.fail("worker timed out")
-        assert p.exitcode == 0
+    from conftest import join_ranks
+
+    join_ranks(procs)
     for r in range(2):
         res = torch.load(tmp_path / f"tp_rank{r}.pt")
         for k, v in res.items():
@@ -119,12 +116,9 @@ def test_tp_mlp_fused_forward_backward(tmp_path):
     procs = [ctx.Process(target=_mlp_worker, args=(r, 2, 29633, str(tmp_path))) for r in range(2)]
     for p in procs:
         p.start()
-    for p in procs:
-        p.join(timeout=600)
-        if p.is_alive():
-            p.terminate()
-            pytest.fail("worker timed out")
-        assert p.exitcode == 0
+    from conftest import join_ranks
+
+    join_ranks(procs)
     for r in range(2):
         for k, v in torch.load(tmp_path / f"mlp_rank{r}.pt").items():
             assert v < 2e-2, (r, k, v)
