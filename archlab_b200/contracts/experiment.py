@@ -161,6 +161,11 @@ def read_experiment(path: str | Path, overrides: list[str] | tuple[str, ...] = (
             data.setdefault("settings", {})[key[len("settings."):]] = value
         else:
             _set_dotted(data, key, value, struct=False)
+    # experiment fields interpolate environment variables like the trainer tree does; a variable that is not set
+    # (and has no default) stays as written, so a recipe can be read and checked without its deployment environment
+    for key in list(data):
+        if key != "settings":
+            data[key] = _resolve_env(data[key], os.environ, strict=False)
     exp = _build_dataclass(Experiment, data, "")
     for req in ("name", "parent_checkpoint", "data_manifest"):
         if getattr(exp, req) == MISSING:
@@ -239,17 +244,19 @@ class Tree(dict):
 _INTERP = re.compile(r"\$\{oc\.env:([A-Za-z_][A-Za-z0-9_]*)(?:,([^}]*))?\}")
 
 
-def _resolve_env(value: Any, environ) -> Any:
+def _resolve_env(value: Any, environ, strict: bool = True) -> Any:
     if isinstance(value, dict):
-        return {k: _resolve_env(v, environ) for k, v in value.items()}
+        return {k: _resolve_env(v, environ, strict) for k, v in value.items()}
     if isinstance(value, list):
-        return [_resolve_env(v, environ) for v in value]
+        return [_resolve_env(v, environ, strict) for v in value]
     if isinstance(value, str):
         whole = _INTERP.fullmatch(value)
 
         def sub(m):
             got = environ.get(m.group(1), m.group(2))
             if got is None:
+                if not strict:
+                    return m.group(0)
                 raise ValueError(f"environment variable {m.group(1)} is not set and has no default")
             return str(got)
 

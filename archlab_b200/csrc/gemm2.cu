@@ -13,6 +13,8 @@
 //     leader's tmem_empty[acc] (8 arrivals: 4 epilogue warps of each CTA, the peer's via remote
 //     mbarrier arrive).
 // All waits are bounded; the two CTAs rendezvous on the hardware cluster barrier at start and end.
+#include <cmath>
+#include <cstdlib>
 #include "gemm_common.cuh"
 #include "host_util.h"
 #include <cuda.h>
@@ -243,10 +245,32 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
+  TileSeq seq = {cluster_id, 0x3fffffff, num_clusters, 0, 1};
+  if (TP && copy_clusters > 0) {
+    if (tp.early_rounds < 0) {
+      if (copy_role) seq = {0, 0, 1, num_tiles, 1};                    // copy only
+    } else {
+      const int t1 = tp.early_rounds * num_clusters;
+      if (copy_role) seq = {0, 0, 1, t1 + num_clusters + int(blockIdx.x >> 1), num_clusters + copy_clusters};
+      else seq = {cluster_id, tp.early_rounds, num_clusters, t1 + cluster_id, num_clusters + copy_clusters};
+    }
+  }
   if (copy_role) {
     if (threadIdx.x == 0)
       tp_copy_role(tp, tp.row_elems, smem, full_bar, int(blockIdx.x), 2 * copy_clusters, abort_word);
-  } else if (warp == 0) {
+    __syncthreads();
+    if (threadIdx.x == 0) {            // the copies used the load barriers with their own phases: start them afresh
+      for (int s = 0; s < G2_STAGES; ++s) {
+        mbar_inval(&full_bar[s]);
+        mbar_init(&full_bar[s], 1);
+      }
+      fence_mbar_init();
+    }
+    __syncthreads();
+    cluster_sync_all();                // both CTAs of the pair are done copying before either loads a GEMM stage
+    if (*abort_word != 0) seq = {0, 0, 1, num_tiles, 1};   // a copy gave up: no tiles for this CTA (its pair times out)
+  }
+  if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       tma_prefetch_desc(&tmA);
@@ -256,7 +280,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       bool gathered_seen = false;                          // every block of the gathered B has been waited for once
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      for (int it = 0, tile = seq.at(0); tile < num_tiles && ok; tile = seq.at(++it)) {
         int b, mb, nb, otile, kb0, kb1;
         split_range(tile, p.splits, num_kb, otile, kb0, kb1);
         tile_coords(otile, num_m, num_n, b, mb, nb);
@@ -340,7 +364,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      for (int it = 0, tile = seq.at(0); tile < num_tiles && ok; tile = seq.at(++it)) {
         ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_word);
         if (!ok) break;
         tc_fence_after();
@@ -383,7 +407,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const bool need_aux = (p.epi == kEpiAxpby || p.epi == kEpiMulDRelu2);
     const bool aux_fast = aux_prefetchable(p);
     uint32_t out_cnt = 0;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+    for (int it = 0, tile = seq.at(0); tile < num_tiles && ok; tile = seq.at(++it)) {
       int b, mb, nb, otile, kb0, kb1;
       split_range(tile, p.splits, num_kb, otile, kb0, kb1);
       tile_coords(otile, num_m, num_n, b, mb, nb);
@@ -664,6 +688,25 @@ extern "C" int nga_gemm2_fp8(const void* A, const void* B, void* D, const void* 
   }
 }
 
+// Rounds of tiles that the GEMM clusters work through alone while the copy clusters are busy: the estimated copy
+// time (remote bytes at the slower of the NVLink rate and the copy CTAs' own rate, then the local shard) over the
+// time of one 256 x 256 x K tile on a CTA pair.  NGA_TP_EARLY_ROUNDS overrides it (-1: copy clusters never compute).
+static int tp_early_rounds(double remote_bytes, double own_bytes, int copy_ctas, int K, bool whole_k_per_tile) {
+  static int forced = -2;
+  if (forced == -2) {
+    const char* e = getenv("NGA_TP_EARLY_ROUNDS");
+    forced = e ? atoi(e) : -3;
+  }
+  if (copy_ctas <= 0) return 0;
+  if (forced >= -1) return forced;
+  if (whole_k_per_tile) return 1;                       // every tile waits for the whole gather anyway
+  const double remote_rate = fmin(650e9, 55e9 * copy_ctas), local_rate = fmin(2000e9, 100e9 * copy_ctas);
+  const double copy_s = remote_bytes / remote_rate + own_bytes / local_rate;
+  const double tile_s = 2.0 * 256 * 256 * K / (1.45e15 / 74);
+  int r = int(copy_s / tile_s + 0.999);
+  return r < 1 ? 1 : (r > 64 ? 64 : r);
+}
+
 // Tensor-parallel GEMM fused with its collective (see TpParams).  A is K-major; B is K-major (b_mn = 0)
 // or MN-major (b_mn = 1); D is bf16.
 //   mode = 1 (all-gather -> GEMM): `src_ptrs[r]` is rank r's row shard [rows_per_rank, K] (contiguous,
@@ -686,6 +729,8 @@ extern "C" int nga_tp_gemm_bf16(const void* A, const void* B, void* D, int M, in
   tp.mode = mode; tp.rank = rank; tp.world = world; tp.rows_per_rank = rows_per_rank;
   tp.copy_clusters = copy_clusters; tp.epoch = epoch; tp.flags = flags; tp.gathered = gathered;
   tp.row_elems = K;
+  tp.early_rounds = tp_early_rounds(double(world - 1) * rows_per_rank * K * 2, double(rows_per_rank) * K * 2,
+                                    2 * copy_clusters, K, false);
   for (int r = 0; r < world; ++r) {
     tp.peer_src[r] = (mode == kTpGather) ? reinterpret_cast<const void*>(src_ptrs[r]) : nullptr;
     tp.peer_dst[r] = (mode == kTpScatter) ? reinterpret_cast<void*>(dst_ptrs[r]) : nullptr;
@@ -745,6 +790,8 @@ extern "C" int nga_fsdp_gemm_bf16(const void* A, void* D, int M, int w_rows, int
   tp.rank = rank; tp.world = world; tp.rows_per_rank = rows_per_rank;
   tp.copy_clusters = copy_clusters; tp.epoch = epoch; tp.flags = flags; tp.gathered = gathered;
   tp.row_elems = w_cols;
+  tp.early_rounds = tp_early_rounds(double(world - 1) * rows_per_rank * w_cols * 2, double(rows_per_rank) * w_cols * 2,
+                                    2 * copy_clusters, transposed ? w_rows : w_cols, transposed != 0);
   for (int r = 0; r < world; ++r) {
     tp.peer_src[r] = reinterpret_cast<const void*>(src_ptrs[r]);
     tp.peer_dst[r] = nullptr;

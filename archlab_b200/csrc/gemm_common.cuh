@@ -55,6 +55,8 @@ struct TpParams {
   int mode, rank, world, rows_per_rank;
   int copy_clusters, epoch;
   int row_elems;                       // elements per row of the gathered matrix
+  int early_rounds;                    // >= 0: the copy clusters compute tiles too once their copies are done; the first
+                                       // early_rounds rounds of tiles belong to the GEMM clusters alone.  < 0: copy only
   int* flags;                          // one per 128-row block of the gathered matrix; value = epoch when ready
   const void* peer_src[kTpMaxWorld];   // row shard of every rank (bf16, contiguous rows of K elements, symmetric)
   void* gathered;                      // local [world * rows_per_rank, K] bf16
@@ -66,6 +68,16 @@ struct TpParams {
 // write stream consists of full 128-byte lines.
 struct TpMaps {
   CUtensorMap d[kTpMaxWorld];
+};
+
+// The tiles of one cluster in launch order.  Without a gather every cluster strides through the tile list.  With
+// copy clusters that join late, the first `early_n` rounds are dealt to the GEMM clusters only and the rest to all
+// clusters, so that the copy clusters (which start on tiles when their copies are done) finish with the others.
+struct TileSeq {
+  int first, early_n, early_step, late_first, late_step;
+  __device__ __forceinline__ int at(int i) const {
+    return i < early_n ? first + i * early_step : late_first + (i - early_n) * late_step;
+  }
 };
 
 __device__ __forceinline__ int tp_remap_mb(const TpParams& tp, int mb, int num_m) {

@@ -28,7 +28,8 @@ def test_rl_recipes_and_overlay(monkeypatch):
     monkeypatch.setenv("ARCHLAB_PARENT_CHECKPOINT", "/ckpt")
     monkeypatch.setenv("ARCHLAB_DATA_MANIFEST", "/m.json")
     e = E.read_experiment(ROOT / "rl/limite_code.yaml", [], overlays=[ROOT / "rl/limite_code_local.yaml"])
-    assert e.execution == "sync" and e.settings["data.train_batch_size"] == 8 and e.settings["actor_rollout_ref.rollout.n"] == 8
+    assert e.execution == "colocate_async" and e.parent_checkpoint == "/ckpt"
+    assert e.settings["data.train_batch_size"] == 8 and e.settings["actor_rollout_ref.rollout.n"] == 8
     assert E.read_experiment(ROOT / "rl/qwen35_code.yaml", []).engine == "dp"
 
 
@@ -38,3 +39,23 @@ def test_launch_catalog_and_study_contract():
     with pytest.raises(ValueError):
         read_recipe(ROOT / "qwen/launches.yaml")
     assert read_recipe(ROOT / "deepseek_v41/scratch_w640_d20.yaml")["parallelism"]["expert"] == 8
+
+
+@pytest.mark.parametrize("recipe,overlays", [("rl/limite_code.yaml", []), ("rl/limite_code.yaml", ["rl/limite_code_local.yaml"]),
+                                             ("rl/qwen35_code.yaml", [])])
+def test_rl_recipes_compose_and_pass_the_science_validators(monkeypatch, recipe, overlays):
+    """The shipped RL recipes resolve against the packaged trainer tree: every settings path exists, the
+    environment interpolations are filled in and the fail-closed pilot rules hold."""
+    monkeypatch.setenv("ARCHLAB_PARENT_CHECKPOINT", "/ckpt/parent")
+    monkeypatch.setenv("ARCHLAB_DATA_MANIFEST", "/data/manifest.json")
+    exp = E.read_experiment(ROOT / recipe, overlays=[ROOT / o for o in overlays])
+    assert exp.parent_checkpoint == "/ckpt/parent"
+    tree = E.compose_trainer(exp)
+    assert tree["trainer"]["experiment_name"] == exp.name
+    assert tree["actor_rollout_ref"]["rollout"]["n"] == 8
+    if overlays:
+        assert tree["data"]["train_batch_size"] == 8 and tree["trainer"]["total_training_steps"] == 20
+    # a broken rule is refused with its message
+    exp.settings["actor_rollout_ref.rollout.n"] = 1
+    with pytest.raises(ValueError):
+        E.compose_trainer(exp)
