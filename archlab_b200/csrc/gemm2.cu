@@ -688,10 +688,13 @@ extern "C" int nga_gemm2_fp8(const void* A, const void* B, void* D, const void* 
   }
 }
 
-// Rounds of tiles that the GEMM clusters work through alone while the copy clusters are busy: the estimated copy
-// time (remote bytes at the slower of the NVLink rate and the copy CTAs' own rate, then the local shard) over the
-// time of one 256 x 256 x K tile on a CTA pair.  NGA_TP_EARLY_ROUNDS overrides it (-1: copy clusters never compute).
-static int tp_early_rounds(double remote_bytes, double own_bytes, int copy_ctas, int K, bool whole_k_per_tile) {
+// Whether the copy clusters also compute tiles once their copies are done (TpParams::early_rounds).  Measured on
+// 2 x B200 (8192 x 9728 x 2560): when tiles follow the arrival order (kTpGather, kTpGatherB) a handful of copy
+// clusters is enough and dedicated ones are faster (0.302 ms with 6 static clusters against 0.31-0.35 ms with any
+// late-joining count); when every tile needs the whole gather (kTpGatherBk) the first round waits for the copies
+// anyway and the copy clusters should take a share of the later rounds (0.45 against 0.51 ms at 12 clusters).
+// NGA_TP_EARLY_ROUNDS overrides the choice (-1: copy only; r >= 0: join after r rounds).
+static int tp_early_rounds(int copy_ctas, bool whole_k_per_tile) {
   static int forced = -2;
   if (forced == -2) {
     const char* e = getenv("NGA_TP_EARLY_ROUNDS");
@@ -699,12 +702,7 @@ static int tp_early_rounds(double remote_bytes, double own_bytes, int copy_ctas,
   }
   if (copy_ctas <= 0) return 0;
   if (forced >= -1) return forced;
-  if (whole_k_per_tile) return 1;                       // every tile waits for the whole gather anyway
-  const double remote_rate = fmin(650e9, 55e9 * copy_ctas), local_rate = fmin(2000e9, 100e9 * copy_ctas);
-  const double copy_s = remote_bytes / remote_rate + own_bytes / local_rate;
-  const double tile_s = 2.0 * 256 * 256 * K / (1.45e15 / 74);
-  int r = int(copy_s / tile_s + 0.999);
-  return r < 1 ? 1 : (r > 64 ? 64 : r);
+  return whole_k_per_tile ? 1 : -1;
 }
 
 // Tensor-parallel GEMM fused with its collective (see TpParams).  A is K-major; B is K-major (b_mn = 0)
@@ -729,8 +727,7 @@ extern "C" int nga_tp_gemm_bf16(const void* A, const void* B, void* D, int M, in
   tp.mode = mode; tp.rank = rank; tp.world = world; tp.rows_per_rank = rows_per_rank;
   tp.copy_clusters = copy_clusters; tp.epoch = epoch; tp.flags = flags; tp.gathered = gathered;
   tp.row_elems = K;
-  tp.early_rounds = tp_early_rounds(double(world - 1) * rows_per_rank * K * 2, double(rows_per_rank) * K * 2,
-                                    2 * copy_clusters, K, false);
+  tp.early_rounds = tp_early_rounds(2 * copy_clusters, false);
   for (int r = 0; r < world; ++r) {
     tp.peer_src[r] = (mode == kTpGather) ? reinterpret_cast<const void*>(src_ptrs[r]) : nullptr;
     tp.peer_dst[r] = (mode == kTpScatter) ? reinterpret_cast<void*>(dst_ptrs[r]) : nullptr;
@@ -790,8 +787,7 @@ extern "C" int nga_fsdp_gemm_bf16(const void* A, void* D, int M, int w_rows, int
   tp.rank = rank; tp.world = world; tp.rows_per_rank = rows_per_rank;
   tp.copy_clusters = copy_clusters; tp.epoch = epoch; tp.flags = flags; tp.gathered = gathered;
   tp.row_elems = w_cols;
-  tp.early_rounds = tp_early_rounds(double(world - 1) * rows_per_rank * w_cols * 2, double(rows_per_rank) * w_cols * 2,
-                                    2 * copy_clusters, transposed ? w_rows : w_cols, transposed != 0);
+  tp.early_rounds = tp_early_rounds(2 * copy_clusters, transposed != 0);
   for (int r = 0; r < world; ++r) {
     tp.peer_src[r] = reinterpret_cast<const void*>(src_ptrs[r]);
     tp.peer_dst[r] = nullptr;

@@ -37,11 +37,20 @@ def _round_up(n: int, m: int) -> int:
 class FsdpGroup:
     """Shard storage, gather scratch and arrival flags shared by the sharded linears of one model."""
 
-    def __init__(self, device, group=None, copy_clusters: int = 12):
+    def __init__(self, device, group=None, copy_clusters: int = 6, reshard_after_forward: bool = True,
+                 fused_dgrad: bool = False):
+        """``reshard_after_forward=False`` keeps one gathered buffer per layer from the forward to the backward
+        pass (the full bf16 weights stay on the GPU for that window, the data gradient needs no second gather);
+        with the default the layers share one scratch buffer and the backward pass gathers again: by an NCCL
+        all-gather into the scratch followed by the plain GEMM, or (``fused_dgrad``) inside the GEMM kernel.
+        Measured on 2 x B200 (8192 x 9728 x 2560): forward 0.302 ms fused against 0.363 ms all-gather + GEMM
+        (GEMM alone 0.279 ms); data gradient 0.45 ms fused against 0.38 ms all-gather + GEMM, because every output
+        tile needs the whole gather before it can finish."""
         self.group = group or dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
         self.device = torch.device(device)
         self.copy_clusters = copy_clusters
+        self.reshard_after_forward, self.fused_dgrad = reshard_after_forward, fused_dgrad
         self.layers: list["FsdpLinear"] = []
         self.flat = None                # SymmTensor (CUDA) or a plain tensor (CPU)
         self.fused = False
@@ -67,6 +76,9 @@ class FsdpGroup:
             self.flat = symm_zeros((total,), torch.bfloat16, self.device, self.group)
             flat = self.flat.tensor
             self.gathered = torch.empty(biggest, dtype=torch.bfloat16, device=self.device)
+            if not self.reshard_after_forward:
+                for layer in self.layers:
+                    layer._kept = torch.empty(layer.padded_out, layer.in_features, dtype=torch.bfloat16, device=self.device)
             rows = max(layer.padded_out for layer in self.layers)
             self.flags = torch.zeros(rows // 128, dtype=torch.int32, device=self.device)
             self.barrier = PeerBarrier(self.device, self.group)
@@ -101,11 +113,20 @@ class FsdpGroup:
             return a @ (w if transposed else w.t())
         M = a.size(0)
         n_out = layer.in_features if transposed else layer.padded_out
+        kept = getattr(layer, "_kept", None)
+        if transposed and (kept is not None or not self.fused_dgrad):
+            from ..ops import gemm as G
+
+            if kept is None:                        # gather again into the shared scratch, then the plain GEMM
+                kept = self.gathered_view(layer)
+                dist.all_gather_into_tensor(kept, layer.weight.detach(), group=self.group)
+            return G.gemm(a, kept, b_mn=True)
         out = torch.empty(M, n_out, dtype=torch.bfloat16, device=a.device)
+        scratch = self.gathered if kept is None else kept
         self.epoch += 1
         rc = native.lib().nga_fsdp_gemm_bf16(
             a.data_ptr(), out.data_ptr(), M, layer.padded_out, layer.in_features, a.stride(0), out.stride(0),
-            int(transposed), self.rank, self.world, layer.rows_per_rank, layer._ptrs, self.gathered.data_ptr(),
+            int(transposed), self.rank, self.world, layer.rows_per_rank, layer._ptrs, scratch.data_ptr(),
             self.flags.data_ptr(), self.epoch, self.copy_clusters, native.status_word(a.device).data_ptr(),
             native.stream_ptr())
         native.check(rc, "nga_fsdp_gemm_bf16")
@@ -113,6 +134,9 @@ class FsdpGroup:
 
     def gathered_view(self, layer: "FsdpLinear") -> torch.Tensor:
         """The whole weight as left in the scratch buffer by the last fused GEMM on ``layer``."""
+        kept = getattr(layer, "_kept", None)
+        if kept is not None:
+            return kept
         return self.gathered[: layer.padded_out * layer.in_features].view(layer.padded_out, layer.in_features)
 
     def reduce_scatter_grad(self, full_grad: torch.Tensor, layer: "FsdpLinear") -> torch.Tensor:

@@ -105,7 +105,7 @@ def main(argv=None):
         # weight gather inside the GEMM kernel, against an NCCL all-gather of the weight followed by the GEMM
         from .fsdp import FsdpGroup, FsdpLinear
 
-        fg = FsdpGroup(dev, copy_clusters=a.copy_clusters)
+        fg = FsdpGroup(dev, copy_clusters=a.copy_clusters, fused_dgrad=True)
         lay = FsdpLinear(fg, a.k, a.n)
         fg.materialize()
         lay.weight.data.normal_(0, 0.02)
@@ -116,6 +116,10 @@ def main(argv=None):
         yo = torch.empty(M, lay.padded_out, device=dev, dtype=torch.bfloat16)
         dxo = torch.empty(M, a.k, device=dev, dtype=torch.bfloat16)
 
+        flops3 = 2.0 * M * lay.padded_out * a.k
+        link3 = (world - 1) * lay.rows_per_rank * a.k * 2
+        roof3 = max(flops3 / (a.gemm_peak_tflops * 1e12), link3 / (a.link_gbs * 1e9)) * 1e3
+
         def nccl_fwd():
             dist.all_gather_into_tensor(wfull, lay.weight.data)
             G.gemm(xm, wfull, out=yo)
@@ -124,9 +128,12 @@ def main(argv=None):
             dist.all_gather_into_tensor(wfull, lay.weight.data)
             G.gemm(dym, wfull, b_mn=True, out=dxo)
 
-        flops3 = 2.0 * M * lay.padded_out * a.k
-        link3 = (world - 1) * lay.rows_per_rank * a.k * 2
-        roof3 = max(flops3 / (a.gemm_peak_tflops * 1e12), link3 / (a.link_gbs * 1e9)) * 1e3
+        for cc in a.sweep:
+            fg.copy_clusters = cc
+            for name, tr, src in (("fsdp_fwd_fused", False, xm), ("fsdp_dgrad_fused", True, dym)):
+                ms = _time(lambda: fg.gemm(src, lay, tr), a.iters, flush)
+                rows.append({"op": f"{name}_cc{cc}", "ms": ms, "tflops": flops3 / ms / 1e9})
+        fg.copy_clusters = a.copy_clusters
         for name, fn in (("fsdp_fwd_fused", lambda: fg.gemm(xm, lay, False)), ("fsdp_fwd_nccl", nccl_fwd),
                          ("fsdp_dgrad_fused", lambda: fg.gemm(dym, lay, True)), ("fsdp_dgrad_nccl", nccl_dgrad),
                          ("fsdp_gemm_only", lambda: G.gemm(xm, wfull, out=yo))):

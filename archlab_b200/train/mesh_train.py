@@ -124,6 +124,8 @@ def parse_args(argv=None):
                     help="factory models: shard the linear weights over the data group; the all-gather of a weight runs "
                          "inside the GEMM that consumes it")
     ap.add_argument("--fsdp-min-features", type=int, default=256, help="smallest linear side that is sharded")
+    ap.add_argument("--fsdp-keep-gathered", action="store_true",
+                    help="keep every gathered weight from the forward to the backward pass (no second gather)")
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--weight-decay", type=float, default=0.1)
@@ -246,7 +248,7 @@ class _Job:
                 raise ValueError("--fsdp shards the linears of a factory model over a data group of at least two ranks")
             from ..parallel.fsdp import FsdpGroup, shard_linears
 
-            self.fsdp = FsdpGroup(device, groups["dp"])
+            self.fsdp = FsdpGroup(device, groups["dp"], reshard_after_forward=not getattr(a, "fsdp_keep_gathered", False))
             shard_linears(self.model, self.fsdp, min_features=a.fsdp_min_features)
 
     def _init_qwen(self, seed: int) -> None:

@@ -27,7 +27,23 @@ def _worker(rank, world, port, out_dir):
     from archlab_b200.parallel.fsdp import FsdpGroup, FsdpLinear
 
     dev = torch.device("cuda", rank)
-    grp = FsdpGroup(dev, copy_clusters=2)
+    res = {}
+    # the three backward policies: second gather by NCCL, second gather inside the data-gradient GEMM, gathered
+    # weights kept from the forward pass
+    for tag, kw in (("a", {}), ("b", {"fused_dgrad": True}), ("c", {"reshard_after_forward": False})):
+        _check_group(FsdpGroup(dev, copy_clusters=2, **kw), tag, res, rank, world, dev)
+    torch.cuda.synchronize()
+    native.check_status()
+    torch.save(res, os.path.join(out_dir, f"fsdp_rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _check_group(grp, tag, res, rank, world, dev):
+    import torch.distributed as dist
+
+    from archlab_b200.parallel.fsdp import FsdpLinear
+
     shapes = [(320, 1024), (1024, 320), (256, 700)]                  # (in, out); 700 pads to 1024 with 2 ranks
     layers = [FsdpLinear(grp, i, o) for i, o in shapes]
     grp.materialize()
@@ -39,8 +55,7 @@ def _worker(rank, world, port, out_dir):
         lay.load_full(w)
         fulls.append(w)
     grp.sync()
-    res = {}
-    for it in range(3):                                                # several epochs on the same scratch and flags
+    for it in range(2):                                                # several epochs on the same scratch and flags
         for n, (lay, w) in enumerate(zip(layers, fulls)):
             g = torch.Generator(device=dev).manual_seed(1000 * it + 10 * n + rank)
             x = (torch.randn(3, 200, lay.in_features, device=dev, generator=g) * 0.5).bfloat16().requires_grad_(True)
@@ -49,22 +64,17 @@ def _worker(rank, world, port, out_dir):
             got_w = grp.gathered_view(lay)[: lay.out_features].clone()
             y.backward(dy)
             xf, wf = x.detach().float(), w.float()
-            res[f"y{it}_{n}"] = _rel(y, xf @ wf.t())
-            res[f"dx{it}_{n}"] = _rel(x.grad, dy.float() @ wf)
-            res[f"w{it}_{n}"] = float((got_w.float() - wf).abs().max())
+            res[f"y{tag}{it}_{n}"] = _rel(y, xf @ wf.t())
+            res[f"dx{tag}{it}_{n}"] = _rel(x.grad, dy.float() @ wf)
+            res[f"w{tag}{it}_{n}"] = float((got_w.float() - wf).abs().max())
             dw = dy.float().flatten(0, 1).t() @ xf.flatten(0, 1)       # this rank's full weight gradient
             dist.all_reduce(dw)
             dw /= world
             r0 = rank * lay.rows_per_rank
             nrows = max(0, min(lay.out_features, r0 + lay.rows_per_rank) - r0)
-            res[f"dw{it}_{n}"] = _rel(lay.weight.grad[:nrows], dw[r0: r0 + nrows])
-            res[f"pad{it}_{n}"] = float(lay.weight.grad[nrows:].float().abs().max()) if nrows < lay.rows_per_rank else 0.0
+            res[f"dw{tag}{it}_{n}"] = _rel(lay.weight.grad[:nrows], dw[r0: r0 + nrows])
+            res[f"pad{tag}{it}_{n}"] = float(lay.weight.grad[nrows:].float().abs().max()) if nrows < lay.rows_per_rank else 0.0
             lay.weight.grad = None
-    torch.cuda.synchronize()
-    native.check_status()
-    torch.save(res, os.path.join(out_dir, f"fsdp_rank{rank}.pt"))
-    dist.barrier()
-    dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
