@@ -425,9 +425,10 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + uint32_t(acc * G2_BN) + (uint32_t(quarter * 32) << 16);
-      if (TP && (tp.mode & kTpScatter)) {
-        // reduce-scatter: bf16 tile -> swizzled staging tile -> one TMA store into the owner's slot
-        const int owner = (mb * 2 * BM) / tp.rows_per_rank;
+      const bool scatter = TP && (tp.mode & kTpScatter);
+      if (scatter || p.tma_store) {
+        // bf16 tile -> swizzled staging tile -> one TMA store: into the owner's slot (reduce-scatter) or into D
+        const int owner = scatter ? (mb * 2 * BM) / tp.rows_per_rank : 0;
         const int row0 = mb * 2 * BM + int(rank) * BM + quarter * 32 + int(pt.row_shift);
 #pragma unroll 1
         for (int c2 = chalf * 2; c2 < chalf * 2 + 2; ++c2) {
@@ -453,7 +454,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_3d(&tpm.d[owner], buf, col0, row0, 0);
+            tma_store_3d(&tpm.d[owner], buf, col0, row0, scatter ? 0 : b);
             tma_store_commit();
           }
           ++out_cnt;
@@ -480,7 +481,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty_bar[acc]), 0));
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
-    if (TP && (tp.mode & kTpScatter) && lane == 0) tma_store_wait0();   // every tile has reached its owner
+    if (((TP && (tp.mode & kTpScatter)) || p.tma_store) && lane == 0) tma_store_wait0();   // every tile has landed
   }
 
   // ------------------------------------------------------------------ tear-down
@@ -521,6 +522,23 @@ static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
     if (e != cudaSuccess || n <= 0) return -1000 - (int)e;
     max_clusters = n;
   }
+  // plain bf16 output: hand the tiles to the TMA engine (full 128-byte lines) instead of per-thread row stores
+  GemmParams pp = p;
+  TpMaps maps = tpm;
+  pp.tma_store = 0;
+  static int tma_store_on = -1;
+  if (tma_store_on < 0) {
+    const char* e = getenv("NGA_GEMM_TMA_STORE");
+    tma_store_on = (e && e[0] == '0') ? 0 : 1;
+  }
+  if (tma_store_on && !(TP && (tp.mode & kTpScatter)) && p.epi == kEpiScale && !p.out_fp32 && p.splits == 1 &&
+      p.row_shift == 0 && p.D != nullptr && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0 && (p.ldd & 7) == 0 &&
+      (p.batch == 1 || (p.sD & 7) == 0)) {
+    const long long bstride = p.batch > 1 ? p.sD : (long long)p.M * p.ldd;
+    if (make_tmap_3d(&maps.d[0], p.D, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.N, p.M, p.batch, p.ldd * 2, bstride * 2, 64, 32,
+                     true) == 0)
+      pp.tma_store = 1;
+  }
   const int num_tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch * p.splits;
   int clusters = num_tiles < max_clusters ? num_tiles : max_clusters;
   if (TP && (tp.mode & kTpGatherAny)) {
@@ -530,7 +548,7 @@ static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
     clusters = gemm_clusters + tp.copy_clusters;
   }
   cfg.gridDim = dim3(2 * clusters);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, p, ta2, tp, tpm);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ta, tb, pp, ta2, tp, maps);
   count_launch();
   if (e != cudaSuccess) return -1000 - (int)e;
   return 0;

@@ -26,6 +26,7 @@ struct GemmParams {
   // group; `group_of_mtile[mb]` names it and B is the stack of the groups' matrices, `group_rows` rows each
   const int* group_of_mtile;
   int group_rows;
+  int tma_store;                 // pair kernel, plain bf16 output: tiles leave through swizzled staging + TMA stores
 };
 
 // Tensor-parallel fusion of the CTA-pair GEMM with its collective over NVLink peer memory.
