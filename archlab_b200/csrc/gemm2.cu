@@ -434,6 +434,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         for (int c2 = chalf * 2; c2 < chalf * 2 + 2; ++c2) {
           const int col0 = nb * G2_BN + c2 * 64;
           if (col0 >= p.N) break;   // warp-uniform
+          const AuxPre cur = nxt;
+          if (c2 + 1 < chalf * 2 + 2) aux_prefetch(p, nxt, row, nb * G2_BN + (c2 + 1) * 64, b, aux_fast);
           uint32_t r2[2][32];
           tmem_ld_32x32(taddr + uint32_t(c2 * 64), r2[0]);
           tmem_ld_32x32(taddr + uint32_t(c2 * 64 + 32), r2[1]);
@@ -442,15 +444,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           __syncwarp();
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const uint32_t* v = &r2[q >> 2][(q & 3) * 8];
-            uint4 pk;
-            pk.x = pack_bf16(p.alpha * __uint_as_float(v[0]), p.alpha * __uint_as_float(v[1]));
-            pk.y = pack_bf16(p.alpha * __uint_as_float(v[2]), p.alpha * __uint_as_float(v[3]));
-            pk.z = pack_bf16(p.alpha * __uint_as_float(v[4]), p.alpha * __uint_as_float(v[5]));
-            pk.w = pack_bf16(p.alpha * __uint_as_float(v[6]), p.alpha * __uint_as_float(v[7]));
-            *reinterpret_cast<uint4*>(buf + lane * 128 + ((q ^ (lane & 7)) * 16)) = pk;
-          }
+          for (int hc = 0; hc < 2; ++hc)
+            epilogue_stage_chunk(p, r2[hc], cur.valid[hc] ? cur.v[hc] : nullptr, buf, lane, hc);
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
@@ -529,9 +524,14 @@ static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
   static int tma_store_on = -1;
   if (tma_store_on < 0) {
     const char* e = getenv("NGA_GEMM_TMA_STORE");
-    tma_store_on = (e && e[0] == '0') ? 0 : 1;
+    tma_store_on = e ? atoi(e) : 1;              // 0: off; 1: every bf16 epilogue; 2: only those without aux
   }
-  if (tma_store_on && !(TP && (tp.mode & kTpScatter)) && p.epi == kEpiScale && !p.out_fp32 && p.splits == 1 &&
+  const bool aux_epi = (p.epi == kEpiAxpby || p.epi == kEpiMulDRelu2);
+  // aux epilogues take the row's aux values from the register prefetch, which covers whole 32-column chunks only
+  const bool epi_ok = p.epi == kEpiScale || p.epi == kEpiRelu2 ||
+                      (aux_epi && !p.aux_fp32 && p.aux != nullptr && (p.N & 31) == 0 && (p.ldaux & 7) == 0 &&
+                       (p.sAux & 7) == 0 && (reinterpret_cast<uintptr_t>(p.aux) & 15) == 0);
+  if (tma_store_on && !(tma_store_on == 2 && aux_epi) && !(TP && (tp.mode & kTpScatter)) && epi_ok && !p.out_fp32 && p.splits == 1 &&
       p.row_shift == 0 && p.D != nullptr && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0 && (p.ldd & 7) == 0 &&
       (p.batch == 1 || (p.sD & 7) == 0)) {
     const long long bstride = p.batch > 1 ? p.sD : (long long)p.M * p.ldd;

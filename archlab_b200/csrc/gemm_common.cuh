@@ -260,6 +260,53 @@ __device__ __forceinline__ void epilogue_chunk_t(const GemmParams& p, const uint
   }
 }
 
+// Staging form of the epilogue for TMA stores: applies the epilogue to one 32-column chunk of one accumulator row
+// and writes the bf16 result into this lane's 128-byte row of a 32 x 64 staging tile (128-byte swizzle; `half`
+// selects columns 0..31 or 32..63 of the tile).  `pre` holds the row's 32 bf16 aux values (nullptr: zeros; the
+// caller only uses this form when every chunk inside the matrix has them).
+template <int EPI>
+__device__ __forceinline__ void epilogue_stage_t(const GemmParams& p, const uint32_t (&r)[32], const uint4* pre,
+                                                 uint8_t* buf, int lane, int half) {
+  constexpr bool kNeedAux = (EPI == kEpiAxpby || EPI == kEpiMulDRelu2);
+  const float alpha = p.alpha, beta = p.beta;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float a[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] = 0.f;
+    if constexpr (kNeedAux) {
+      if (pre != nullptr) {
+        const uint4 pk = pre[q];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h[i]);
+          a[2 * i] = f.x;
+          a[2 * i + 1] = f.y;
+        }
+      }
+    }
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = epi_apply<EPI>(__uint_as_float(r[q * 8 + i]), a[i], alpha, beta);
+    uint4 o;
+    o.x = pack_bf16(v[0], v[1]);
+    o.y = pack_bf16(v[2], v[3]);
+    o.z = pack_bf16(v[4], v[5]);
+    o.w = pack_bf16(v[6], v[7]);
+    *reinterpret_cast<uint4*>(buf + lane * 128 + (((half * 4 + q) ^ (lane & 7)) * 16)) = o;
+  }
+}
+__device__ __forceinline__ void epilogue_stage_chunk(const GemmParams& p, const uint32_t (&r)[32], const uint4* pre,
+                                                     uint8_t* buf, int lane, int half) {
+  switch (p.epi) {
+    case kEpiAxpby: epilogue_stage_t<kEpiAxpby>(p, r, pre, buf, lane, half); break;
+    case kEpiRelu2: epilogue_stage_t<kEpiRelu2>(p, r, pre, buf, lane, half); break;
+    case kEpiMulDRelu2: epilogue_stage_t<kEpiMulDRelu2>(p, r, pre, buf, lane, half); break;
+    default: epilogue_stage_t<kEpiScale>(p, r, pre, buf, lane, half); break;
+  }
+}
+
 __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const uint32_t (&r)[32], int row,
                                                      int col0, int b, bool vec_ok, bool /*need_aux*/,
                                                      const uint4* pre = nullptr) {
