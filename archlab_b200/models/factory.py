@@ -87,3 +87,56 @@ def build_from_meta(meta: dict[str, Any], *, device="cpu"):
     cfg = dict(meta["model_config"])
     family = cfg.get("arch_family", meta.get("arch_family", "nanochat"))
     return build_model(family, cfg, device=device, init=False)
+
+
+# ------------------------------------------------------------------------------------------------
+# campaign arms -> this package's families
+# ------------------------------------------------------------------------------------------------
+_ARM_FAMILY = {"sota_pool": "sota", "pareto_combo": "sota", "combo_search": "sota", "frontier_pool": "frontier",
+               "kimi_kda": "kimi_kda", "kimi_attnres": "kimi_attnres", "nanochat": "nanochat"}
+_FRONTIER_NAMES = {"glm_mla_muon_split": "glm_mla"}
+
+
+def campaign_arm_config(kwargs: dict[str, Any]) -> tuple[str, dict[str, Any]]:
+    """Translates the model arguments of a frozen campaign arm (``contracts.campaigns.*_model_config_kwargs``:
+    depth / aspect ratio / head width plus one mechanism, src/archlab/model_factory.py:243-350) into a family of
+    this package and the fields of its config class.  Arms whose mechanism has no model here (Engram memory,
+    multi-stream hyper-connections and the small DSA model as nanochat-sized families, gated attention) are
+    refused by name rather than silently built as the baseline."""
+    kw = dict(kwargs)
+    arm = kw.pop("arch_family", "nanochat")
+    if arm not in _ARM_FAMILY:
+        raise NotImplementedError(f"campaign family {arm!r} has no nanochat-sized model in this package")
+    depth, head_dim = int(kw.pop("depth")), int(kw.pop("head_dim"))
+    width = -(-depth * int(kw.pop("aspect_ratio")) // head_dim) * head_dim
+    cfg: dict[str, Any] = {"n_layer": depth, "n_embd": width, "n_head": width // head_dim,
+                           "sequence_len": int(kw.pop("max_seq_len", 2048)), "vocab_size": int(kw.pop("vocab_size", 32768))}
+    family = _ARM_FAMILY[arm]
+    if family == "sota":
+        variant = kw.pop("sota_variant", None) or kw.pop("search_mlp", None) or "baseline"
+        if variant not in ("baseline", "xielu", "colu", "dyt", "canon", "bov", "diff_attn", "gated_relu", "qat"):
+            raise NotImplementedError(f"mechanism {variant!r} is not part of the SoTA pool of this package")
+        cfg["mechanisms"] = () if variant == "baseline" else (variant,)
+        if "colu_dim" in kw:
+            cfg["colu_dim"] = kw.pop("colu_dim")
+        if "bov_target_fraction" in kw:
+            cfg["bov_fraction"] = kw.pop("bov_target_fraction")
+        if kw.get("fog_variant") and arm == "fog":
+            cfg["fog_variant"] = kw["fog_variant"]
+    elif family == "frontier":
+        v = kw.pop("frontier_variant", "baseline")
+        cfg["variant"] = _FRONTIER_NAMES.get(v, v)
+        cfg["relative_dim"] = kw.pop("relative_dim", 16)
+    elif family == "kimi_kda":
+        cfg.update(kda_pattern=kw.pop("kda_pattern", "KKKG"), kda_variant=kw.pop("kda_variant", "kimi_linear"),
+                   kda_force_final_global=kw.pop("kda_force_final_global", True))
+    elif family == "kimi_attnres":
+        cfg.update(attnres_block=kw.pop("attn_res_block_size", 2), attnres_heads=kw.pop("attn_res_heads", 1))
+    elif family == "nanochat":
+        cfg.update(n_kv_head=cfg["n_head"], window_pattern=kw.pop("window_pattern", "L"))
+    return family, cfg
+
+
+def build_campaign_arm(kwargs: dict[str, Any], *, device="cpu"):
+    family, cfg = campaign_arm_config(kwargs)
+    return build_model(family, cfg, device=device)
