@@ -243,11 +243,21 @@ class V41LM(nn.Module):
         for n, p in self.named_parameters():
             if p.ndim >= 2:
                 nn.init.normal_(p, std=std)
-        for m in self.modules():
+        self.head_mix.zero_()
+        for m in self.modules():                     # gains, sinks and biases too: a meta-built model has no defaults
             if isinstance(m, HyperConnectionMix):
                 nn.init.normal_(m.proj.weight, std=std)
+                m.scale.fill_(0.01)
+                m.base.zero_()
+                m.base[2 * m.n:] = (torch.eye(m.n, device=m.base.device, dtype=m.base.dtype) * 4.0).flatten()   # near-identity mixing
             if isinstance(m, nn.LayerNorm):
                 m.reset_parameters()
+            if isinstance(m, RMSNorm):
+                m.weight.fill_(0.0 if m.zero_centered else 1.0)
+            if isinstance(m, SparseLatentAttention):
+                m.sink.zero_()
+            if isinstance(m, nn.Linear) and m.bias is not None:
+                m.bias.zero_()
 
     def routers(self):
         return [b.ffn for b in self.layers]

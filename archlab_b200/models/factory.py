@@ -10,12 +10,12 @@ import torch
 
 
 def _registry() -> dict[str, tuple[type, type]]:
-    from . import deepseek_v41, frontier, kimi, limite, nanochat, qwen35, qwen38, sota
+    from . import deepseek_v41, frontier, kimi, limite, nanochat, nanochat_variants, qwen35, qwen38, sota
 
     return {
         "nanochat": (nanochat.GPTConfig, nanochat.GPT),
-        "engram": (nanochat.GPTConfig, nanochat.GPT),
-        "mhc": (nanochat.GPTConfig, nanochat.GPT),
+        "engram": (nanochat_variants.EngramGPTConfig, nanochat_variants.EngramGPT),
+        "mhc": (nanochat_variants.MhcGPTConfig, nanochat_variants.MhcGPT),
         "kimi_kda": (kimi.KimiConfig, kimi.KimiLM),
         "kimi_attnres": (kimi.KimiConfig, kimi.KimiLM),
         "qwen35": (qwen35.Qwen35Config, qwen35.Qwen35LM),
@@ -31,7 +31,7 @@ def _registry() -> dict[str, tuple[type, type]]:
     }
 
 
-_EAGER_FAMILIES = frozenset({"frontier", "sota", "fog", "limite"})
+_EAGER_FAMILIES = frozenset({"frontier", "sota", "fog", "limite", "engram"})   # engram: hash tables are built from data
 
 
 def families() -> list[str]:
@@ -92,7 +92,7 @@ def build_from_meta(meta: dict[str, Any], *, device="cpu"):
 # ------------------------------------------------------------------------------------------------
 # campaign arms -> this package's families
 # ------------------------------------------------------------------------------------------------
-_ARM_FAMILY = {"sota_pool": "sota", "pareto_combo": "sota", "combo_search": "sota", "frontier_pool": "frontier",
+_ARM_FAMILY = {"engram": "engram", "mhc": "mhc", "sota_pool": "sota", "pareto_combo": "sota", "combo_search": "sota", "frontier_pool": "frontier",
                "kimi_kda": "kimi_kda", "kimi_attnres": "kimi_attnres", "nanochat": "nanochat"}
 _FRONTIER_NAMES = {"glm_mla_muon_split": "glm_mla"}
 
@@ -132,8 +132,10 @@ def campaign_arm_config(kwargs: dict[str, Any]) -> tuple[str, dict[str, Any]]:
                    kda_force_final_global=kw.pop("kda_force_final_global", True))
     elif family == "kimi_attnres":
         cfg.update(attnres_block=kw.pop("attn_res_block_size", 2), attnres_heads=kw.pop("attn_res_heads", 1))
-    elif family == "nanochat":
+    elif family in ("nanochat", "engram", "mhc"):
         cfg.update(n_kv_head=cfg["n_head"], window_pattern=kw.pop("window_pattern", "L"))
+        prefix = "engram_" if family == "engram" else "mhc_"
+        cfg.update({k: kw.pop(k) for k in list(kw) if k.startswith(prefix)})
     return family, cfg
 
 

@@ -185,6 +185,8 @@ class KimiLM(nn.Module):
             if p.ndim >= 2:
                 nn.init.normal_(p, std=std)
         for m in self.modules():
+            if isinstance(m, nn.Linear) and m.bias is not None:
+                m.bias.zero_()                       # a model built on the meta device has no defaults to fall back on
             if isinstance(m, KimiDeltaAttention):
                 m.a_log.copy_(torch.empty_like(m.a_log).uniform_(1.0, 16.0).log())
                 m.dt_bias.copy_(torch.empty_like(m.dt_bias).uniform_(-4.0, -1.0))

@@ -122,6 +122,11 @@ class Qwen35LM(nn.Module):
         for _, p in self.named_parameters():
             if p.ndim >= 2:
                 nn.init.normal_(p, std=std)
+        for m in self.modules():                     # gains and biases too: a meta-built model has no defaults
+            if isinstance(m, RMSNorm):
+                m.weight.fill_(0.0 if m.zero_centered else 1.0)
+            elif isinstance(m, nn.Linear) and m.bias is not None:
+                m.bias.zero_()
 
     def layer_types(self) -> list[str]:
         return [b.layer_type for b in self.layers]

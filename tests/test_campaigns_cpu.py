@@ -33,7 +33,7 @@ def test_fineweb_templates_scale_their_mechanisms():
     assert C.fineweb_token_budget("10m", 10_000_000) == 120_000_000
 
 
-@pytest.mark.parametrize("arm", ["baseline", "xielu", "kda", "attnres", "glm-mla", "partial-rope-25", "qwen-gdn"])
+@pytest.mark.parametrize("arm", ["baseline", "xielu", "kda", "attnres", "glm-mla", "partial-rope-25", "qwen-gdn", "engram", "mhc"])
 def test_ten_m_arms_build_and_step(arm):
     import torch
 
@@ -54,6 +54,6 @@ def test_ten_m_arms_build_and_step(arm):
 def test_unbuilt_arms_are_refused_by_name():
     from archlab_b200.models.factory import campaign_arm_config
 
-    for arm in ("engram", "mhc", "dsa", "gated-attention"):
+    for arm in ("dsa", "gated-attention"):
         with pytest.raises(NotImplementedError):
             campaign_arm_config(C.ten_m_model_config_kwargs(C.get_ten_m_variant(arm)))
