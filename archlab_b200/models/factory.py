@@ -16,6 +16,7 @@ def _registry() -> dict[str, tuple[type, type]]:
         "nanochat": (nanochat.GPTConfig, nanochat.GPT),
         "engram": (nanochat_variants.EngramGPTConfig, nanochat_variants.EngramGPT),
         "mhc": (nanochat_variants.MhcGPTConfig, nanochat_variants.MhcGPT),
+        "deepseek_dsa": (nanochat_variants.DsaGPTConfig, nanochat_variants.DsaGPT),
         "kimi_kda": (kimi.KimiConfig, kimi.KimiLM),
         "kimi_attnres": (kimi.KimiConfig, kimi.KimiLM),
         "qwen35": (qwen35.Qwen35Config, qwen35.Qwen35LM),
@@ -92,7 +93,7 @@ def build_from_meta(meta: dict[str, Any], *, device="cpu"):
 # ------------------------------------------------------------------------------------------------
 # campaign arms -> this package's families
 # ------------------------------------------------------------------------------------------------
-_ARM_FAMILY = {"engram": "engram", "mhc": "mhc", "sota_pool": "sota", "pareto_combo": "sota", "combo_search": "sota", "frontier_pool": "frontier",
+_ARM_FAMILY = {"engram": "engram", "mhc": "mhc", "deepseek_dsa": "deepseek_dsa", "sota_pool": "sota", "pareto_combo": "sota", "combo_search": "sota", "frontier_pool": "frontier",
                "kimi_kda": "kimi_kda", "kimi_attnres": "kimi_attnres", "nanochat": "nanochat"}
 _FRONTIER_NAMES = {"glm_mla_muon_split": "glm_mla"}
 
@@ -114,7 +115,9 @@ def campaign_arm_config(kwargs: dict[str, Any]) -> tuple[str, dict[str, Any]]:
     family = _ARM_FAMILY[arm]
     if family == "sota":
         variant = kw.pop("sota_variant", None) or kw.pop("search_mlp", None) or "baseline"
-        if variant not in ("baseline", "xielu", "colu", "dyt", "canon", "bov", "diff_attn", "gated_relu", "qat"):
+        variant = {"bank_of_values": "bov", "differential_attention": "diff_attn", "dynamic_tanh": "dyt"}.get(variant, variant)
+        if variant not in ("baseline", "xielu", "colu", "dyt", "canon", "bov", "diff_attn", "gated_relu", "qat",
+                           "gated_attention", "exclusive_attention"):
             raise NotImplementedError(f"mechanism {variant!r} is not part of the SoTA pool of this package")
         cfg["mechanisms"] = () if variant == "baseline" else (variant,)
         if "colu_dim" in kw:
@@ -132,9 +135,9 @@ def campaign_arm_config(kwargs: dict[str, Any]) -> tuple[str, dict[str, Any]]:
                    kda_force_final_global=kw.pop("kda_force_final_global", True))
     elif family == "kimi_attnres":
         cfg.update(attnres_block=kw.pop("attn_res_block_size", 2), attnres_heads=kw.pop("attn_res_heads", 1))
-    elif family in ("nanochat", "engram", "mhc"):
+    elif family in ("nanochat", "engram", "mhc", "deepseek_dsa"):
         cfg.update(n_kv_head=cfg["n_head"], window_pattern=kw.pop("window_pattern", "L"))
-        prefix = "engram_" if family == "engram" else "mhc_"
+        prefix = {"engram": "engram_", "mhc": "mhc_", "deepseek_dsa": "dsa_"}.get(family, "\0")
         cfg.update({k: kw.pop(k) for k in list(kw) if k.startswith(prefix)})
     return family, cfg
 

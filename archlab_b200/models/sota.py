@@ -28,7 +28,8 @@ import torch.nn.functional as F
 from ..ops.attention import causal_attention
 from .blocks import apply_rope, rms_norm, rope_tables
 
-MECHANISMS = frozenset({"dyt", "xielu", "canon", "bov", "diff_attn", "gated_relu", "colu", "qat"})
+MECHANISMS = frozenset({"dyt", "xielu", "canon", "bov", "diff_attn", "gated_relu", "colu", "qat", "gated_attention",
+                        "exclusive_attention"})
 
 
 @dataclass(frozen=True)
@@ -208,6 +209,9 @@ class PoolAttention(nn.Module):
             self.value_table = nn.Embedding(c.vocab_size, c.n_embd)
         else:
             self.v = lin(c.n_embd, c.n_embd)
+        if c.has("gated_attention"):
+            # query-dependent head-wise sigmoid gate on the attention output (src/archlab/architectures/sota.py:162-163, 299-301)
+            self.output_gate = nn.Linear(c.n_embd, c.n_head, bias=False)
         if c.has("diff_attn"):
             half = c.head_dim // 2
             self.lambda_init = 0.8 - 0.6 * math.exp(-0.3 * layer)
@@ -251,6 +255,12 @@ class PoolAttention(nn.Module):
                 monitor.record(f"layer{self.layer}/q", q)
                 monitor.record(f"layer{self.layer}/k", k)
             y = causal_attention(q, k, v)
+            if c.has("gated_attention"):
+                y = y * torch.sigmoid(self.output_gate(x)).unsqueeze(-1).to(y.dtype)
+            elif c.has("exclusive_attention"):
+                # the output keeps only what is orthogonal to the token's own value (sota.py:302-304)
+                vd = F.normalize(v, dim=-1)
+                y = y - (y * vd).sum(-1, keepdim=True) * vd
         return self.o(y.reshape(B, T, -1))
 
 

@@ -33,7 +33,7 @@ def test_fineweb_templates_scale_their_mechanisms():
     assert C.fineweb_token_budget("10m", 10_000_000) == 120_000_000
 
 
-@pytest.mark.parametrize("arm", ["baseline", "xielu", "kda", "attnres", "glm-mla", "partial-rope-25", "qwen-gdn", "engram", "mhc"])
+@pytest.mark.parametrize("arm", ["baseline", "xielu", "kda", "attnres", "glm-mla", "partial-rope-25", "qwen-gdn", "engram", "mhc", "gated-attention", "dsa"])
 def test_ten_m_arms_build_and_step(arm):
     import torch
 
@@ -51,9 +51,27 @@ def test_ten_m_arms_build_and_step(arm):
     assert torch.isfinite(loss)
 
 
-def test_unbuilt_arms_are_refused_by_name():
+def test_unknown_family_is_refused_by_name():
     from archlab_b200.models.factory import campaign_arm_config
 
-    for arm in ("dsa", "gated-attention"):
-        with pytest.raises(NotImplementedError):
-            campaign_arm_config(C.ten_m_model_config_kwargs(C.get_ten_m_variant(arm)))
+    with pytest.raises(NotImplementedError):
+        campaign_arm_config({"arch_family": "made_up", "depth": 2, "aspect_ratio": 8, "head_dim": 8})
+
+
+def test_dsa_stages():
+    import torch
+
+    from archlab_b200.models.factory import build_campaign_arm
+
+    kw = C.ten_m_model_config_kwargs(C.get_ten_m_variant("dsa"))
+    kw["vocab_size"], kw["max_seq_len"] = 512, 64
+    model = build_campaign_arm(kw)
+    ids = torch.randint(0, 512, (2, 64))
+    dense = model(ids, ids)
+    model.set_stage("sparse")
+    sparse = model(ids, ids)
+    sparse.backward()
+    assert torch.isfinite(dense) and torch.isfinite(sparse) and dense.item() != sparse.item()
+    assert all(p.grad is not None for p in model.indexer_parameters())
+    model.eval()
+    assert model(ids).shape == (2, 64, 512)
