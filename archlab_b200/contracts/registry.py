@@ -54,24 +54,30 @@ def capability_rows() -> list[dict[str, object]]:
 # ------------------------------------------------------------------------------------------------
 # campaign variants: flags appended to the training command
 # ------------------------------------------------------------------------------------------------
-VARIANTS: dict[str, tuple[str, ...]] = {
-    "baseline": ("--arch-family=nanochat",),
-    "attnres": ("--arch-family=kimi_attnres", "--attnres-block=4"),
-    "dsa": ("--arch-family=dsa", "--dsa-top-k=32", "--dsa-warmup-steps=40"),
-    "engram": ("--arch-family=engram", "--engram-orders=2,3"),
-    "gated-attention": ("--arch-family=frontier", "--mixer=gated_attention"),
-    "glm-mla": ("--arch-family=frontier", "--mixer=glm_mla"),
-    "inkling-relative-attention": ("--arch-family=frontier", "--mixer=inkling_relative"),
-    "inkling-sconv-kv": ("--arch-family=frontier", "--mixer=inkling_sconv_kv"),
-    "inkling-sconv-residual": ("--arch-family=frontier", "--mixer=inkling_sconv_residual"),
-    "kda": ("--arch-family=kimi_kda", "--kda-pattern=KKKG"),
-    "kimi-k3-kda-update": ("--arch-family=kimi_kda", "--kda-variant=kimi_k3"),
-    "mhc": ("--arch-family=mhc", "--mhc-num-streams=4"),
-    "partial-rope-25": ("--arch-family=nanochat", "--rope-fraction=0.25"),
-    "qwen-gdn": ("--arch-family=frontier", "--mixer=qwen_gdn"),
-    "situ-glu": ("--arch-family=frontier", "--mlp=situ_glu"),
-    "xielu": ("--arch-family=sota", "--activation=xielu"),
-}
+def arm_flags(model_kwargs: dict[str, Any]) -> tuple[str, ...]:
+    """Model arguments of a campaign arm as trainer flags: ``--kda-pattern=KKKG``, tuples comma-separated, true
+    booleans as bare flags (false ones are the trainer's defaults and are left out)."""
+    out = []
+    for key, value in model_kwargs.items():
+        flag = "--" + key.replace("_", "-")
+        if isinstance(value, bool):
+            if value:
+                out.append(flag)
+        elif isinstance(value, (tuple, list)):
+            out.append(f"{flag}={','.join(str(v) for v in value)}")
+        else:
+            out.append(f"{flag}={value}")
+    return tuple(out)
+
+
+def _variants() -> dict[str, tuple[str, ...]]:
+    from .campaigns import TEN_M_VARIANTS
+
+    return {v.name: arm_flags(v.model_kwargs()) for v in TEN_M_VARIANTS}
+
+
+# the sixteen arms of the frozen campaign tables, as flags of ``archlab_b200.train.base_train``
+VARIANTS: dict[str, tuple[str, ...]] = _variants()
 SIZES = {"100m": dict(depth=12, aspect_ratio=64, head_dim=128), "300m": dict(depth=20, aspect_ratio=64, head_dim=128),
          "1b": dict(depth=28, aspect_ratio=80, head_dim=128)}
 SEEDS = (0, 1, 2)

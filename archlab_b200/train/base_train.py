@@ -47,7 +47,82 @@ def parse_args(argv=None):
     ap.add_argument("--save-every", type=int, default=-1)
     ap.add_argument("--resume-from-step", type=int, default=-1)
     ap.add_argument("--seed", type=int, default=0)
+    # architecture arms of the frozen campaigns (contracts/campaigns.py): any family other than the fused nanochat
+    # engine is built by the model factory and trained by the mesh trainer's sharded AdamW under data parallelism
+    ap.add_argument("--arch-family", default=None, help="campaign family (sota_pool, frontier_pool, kimi_kda, engram, ...)")
+    ap.add_argument("--aspect-ratio", type=int, default=64)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--window-pattern", default="L")
+    ap.add_argument("--per-head-muon", action="store_true")
+    ap.add_argument("--arm-lr", type=float, default=3e-4, help="AdamW learning rate of the architecture-arm path")
+    ap.add_argument("--scalar-lr", type=float, default=0.5)
+    ap.add_argument("--final-lr-frac", type=float, default=0.05)
+    ap.add_argument("--eval-every", type=int, default=-1)
+    ap.add_argument("--eval-tokens", type=int, default=0)
+    ap.add_argument("--finite-check-every", type=int, default=1)
+    ap.add_argument("--run", default="dummy", help="tracking run name (dummy: no tracker)")
+    ap.add_argument("--model-tag", default=None, help="names the run directory under --run-dir")
+    _add_arm_flags(ap)
     return ap.parse_args(argv)
+
+
+def _arm_knobs() -> dict[str, object]:
+    """Every model argument that appears in the campaign tables, with a sample value that fixes its type."""
+    from ..contracts import campaigns as C
+
+    knobs: dict[str, object] = {}
+    for table in (C.TEN_M_VARIANTS, *[tuple(v.values()) for v in C.FINEWEB_CAMPAIGN_VARIANTS.values()]):
+        for arm in table:
+            for key, value in arm.model_kwargs().items():
+                if key != "arch_family":
+                    knobs.setdefault(key, value)
+    return knobs
+
+
+def _add_arm_flags(ap) -> None:
+    for key, sample in _arm_knobs().items():
+        flag = "--" + key.replace("_", "-")
+        if isinstance(sample, bool):
+            ap.add_argument(flag, action="store_true", default=None)
+        elif isinstance(sample, (tuple, list)):
+            ap.add_argument(flag, type=lambda s: tuple(int(v) for v in s.split(",") if v), default=None)
+        else:
+            ap.add_argument(flag, type=type(sample), default=None)
+
+
+def arm_model_kwargs(a) -> dict:
+    """The campaign-style model arguments named by the command line (geometry + family + the knobs that were given)."""
+    kw = {"arch_family": a.arch_family, "depth": a.depth, "aspect_ratio": a.aspect_ratio, "head_dim": a.head_dim,
+          "max_seq_len": a.max_seq_len, "vocab_size": a.vocab_size, "window_pattern": a.window_pattern}
+    for key in _arm_knobs():
+        value = getattr(a, key, None)
+        if value is not None:
+            kw[key] = value
+    return kw
+
+
+def run_arm(a) -> int:
+    """Trains one campaign arm: the model factory builds the family, the mesh trainer steps it (ZeRO-sharded AdamW
+    over the data group, run contract, checkpoints, health checks)."""
+    from ..models.factory import campaign_arm_config
+    from . import mesh_train
+
+    family, cfg = campaign_arm_config(arm_model_kwargs(a))
+    if a.total_batch_size % a.max_seq_len:
+        raise SystemExit("total batch must be a multiple of the sequence length")
+    if a.num_iterations <= 0:
+        raise SystemExit("architecture arms take their frozen step count: pass --num-iterations")
+    run_dir = Path(a.run_dir) / (a.model_tag or family)
+    argv = [f"--model=factory:{family}", f"--seq-len={a.max_seq_len}", f"--global-batch={a.total_batch_size // a.max_seq_len}",
+            f"--micro-batch={a.device_batch_size}", f"--steps={a.num_iterations}", f"--lr={a.arm_lr}",
+            f"--weight-decay={a.weight_decay}", f"--seed={a.seed}", f"--run-dir={run_dir}"]
+    if a.save_every > 0:
+        argv.append(f"--save-every={a.save_every}")
+    for key, value in cfg.items():
+        if key != "sequence_len":
+            argv.append(f"--model-set={key}={json.dumps(list(value) if isinstance(value, tuple) else value)}")
+    mesh_train.train(mesh_train.parse_args(argv))
+    return 0
 
 
 def _init_distributed():
@@ -64,6 +139,8 @@ def _init_distributed():
 
 def main(argv=None) -> int:
     a = parse_args(argv)
+    if a.arch_family not in (None, "nanochat"):
+        return run_arm(a)
     rank, world, device = _init_distributed()
     model_cfg = GPTConfig.from_depth(a.depth, sequence_len=a.max_seq_len, vocab_size=a.vocab_size)
     tokens_per_micro = a.device_batch_size * a.max_seq_len * world

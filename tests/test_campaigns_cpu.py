@@ -75,3 +75,36 @@ def test_dsa_stages():
     assert all(p.grad is not None for p in model.indexer_parameters())
     model.eval()
     assert model(ids).shape == (2, 64, 512)
+
+
+def test_every_frozen_run_command_parses_and_names_a_buildable_arm():
+    from archlab_b200.contracts.registry import campaign_grid
+    from archlab_b200.models.factory import campaign_arm_config
+    from archlab_b200.train import base_train
+
+    seen = set()
+    for run in campaign_grid():
+        if run.variant_id in seen:
+            continue
+        seen.add(run.variant_id)
+        argv = run.command()[3:]                                   # after "python -m archlab_b200.train.base_train"
+        a = base_train.parse_args(argv)
+        assert a.depth == run.depth and a.num_iterations == run.steps
+        family, cfg = campaign_arm_config(base_train.arm_model_kwargs(a))
+        assert cfg["n_layer"] == run.depth
+    assert len(seen) == 16
+
+
+def test_arm_path_trains_through_the_mesh_trainer(tmp_path, monkeypatch):
+    import json
+
+    from archlab_b200.train import base_train
+
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(k, raising=False)
+    rc = base_train.main(["--arch-family=kimi_kda", "--depth=2", "--aspect-ratio=16", "--head-dim=8", "--max-seq-len=32",
+                          "--vocab-size=256", "--device-batch-size=2", "--total-batch-size=128", "--num-iterations=3",
+                          "--kda-pattern=KG", "--kda-force-final-global", "--model-tag=arm", f"--run-dir={tmp_path}"])
+    assert rc == 0
+    rows = [json.loads(l) for l in open(tmp_path / "arm" / "metrics_rank0.jsonl")]
+    assert len(rows) == 3 and all(r["loss"] == r["loss"] for r in rows)
