@@ -72,7 +72,7 @@ def test_campaign_grid_is_complete_and_commands_are_exact(tmp_path):
     runs = rg.load_runs(path)
     run = rg.find_run(runs, "100m", "kda", 1)
     cmd = run.command(run_name="r")
-    assert cmd[:3] == ["python", "-m", "archlab_b200.train.base_train"] and "--seed=1" in cmd and cmd[-1] == "--kda-pattern=KKKG"
+    assert cmd[:3] == ["python", "-m", "archlab_b200.train.base_train"] and "--seed=1" in cmd and "--kda-pattern=KKKG" in cmd and "--arch-family=kimi_kda" in cmd
     data = json.loads(path.read_text())
     data["runs"].pop()
     path.write_text(json.dumps(data))
