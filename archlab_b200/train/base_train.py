@@ -62,6 +62,17 @@ def parse_args(argv=None):
     ap.add_argument("--finite-check-every", type=int, default=1)
     ap.add_argument("--run", default="dummy", help="tracking run name (dummy: no tracker)")
     ap.add_argument("--model-tag", default=None, help="names the run directory under --run-dir")
+    ap.add_argument("--checkpoint-dir", default=None, help="checkpoint bundle directory (default: <run-dir>/checkpoints)")
+    ap.add_argument("--metrics-path", default=None, help="per-step JSON lines of rank 0 (default: <run-dir>/metrics_rank0.jsonl)")
+    ap.add_argument("--metrics-every", type=int, default=1)
+    ap.add_argument("--no-final-checkpoint", dest="save_final_checkpoint", action="store_false")
+    ap.add_argument("--save-final-checkpoint", dest="save_final_checkpoint", action="store_true", default=True)
+    ap.add_argument("--max-parameters", type=int, default=0, help="refuse a model with more scaling parameters than this")
+    ap.add_argument("--max-training-tokens", type=int, default=0, help="refuse a horizon longer than this many tokens")
+    ap.add_argument("--initialization-hash", default=None,
+                    help="sha256 over the initial weights (contracts.provenance.hash_named_tensors); a mismatch is refused")
+    ap.add_argument("--throughput-warmup-steps", type=int, default=10)
+    ap.add_argument("--throughput-measurement-steps", type=int, default=0)
     _add_arm_flags(ap)
     return ap.parse_args(argv)
 
@@ -160,8 +171,20 @@ def main(argv=None) -> int:
         n_params = scaling["total"] if isinstance(scaling, dict) else int(scaling)
         iters = max(1, int(a.target_param_data_ratio * n_params) // a.total_batch_size)
         trainer.schedule.num_iterations = iters
+    n_scaling = trainer.model.num_scaling_params()
+    n_scaling = n_scaling["total"] if isinstance(n_scaling, dict) else int(n_scaling)
+    if a.max_parameters and n_scaling > a.max_parameters:
+        raise SystemExit(f"model has {n_scaling} scaling parameters, more than --max-parameters={a.max_parameters}")
+    if a.max_training_tokens and iters * a.total_batch_size > a.max_training_tokens:
+        raise SystemExit(f"{iters} steps of {a.total_batch_size} tokens exceed --max-training-tokens={a.max_training_tokens}")
+    if a.initialization_hash and a.resume_from_step < 0:
+        from ..contracts.provenance import hash_named_tensors
+
+        got = hash_named_tensors(trainer.model.state_dict().items())
+        if got != a.initialization_hash:
+            raise SystemExit(f"initial weights hash to {got}, not to the declared {a.initialization_hash}")
     run_dir = Path(a.run_dir)
-    ckpt_dir = run_dir / "checkpoints"
+    ckpt_dir = Path(a.checkpoint_dir) if a.checkpoint_dir else run_dir / "checkpoints"
     if rank == 0:
         run_dir.mkdir(parents=True, exist_ok=True)
         (run_dir / "config.json").write_text(json.dumps({"args": vars(a), "world_size": world, "grad_accum_steps": accum,
@@ -180,19 +203,32 @@ def main(argv=None) -> int:
         gen = ZipfTokens(a.vocab_size, a.max_seq_len, local_batch, seed=a.seed, rank=rank, pin=device.type == "cuda")
         next_block = gen.block
         data_tag = "synthetic-zipf"
-    log = open(run_dir / f"metrics_rank{rank}.jsonl", "a") if rank == 0 else None
+    log = open(a.metrics_path or run_dir / f"metrics_rank{rank}.jsonl", "a") if rank == 0 else None
     t_last = time.perf_counter()
+    stamps, paused = [t_last], 0.0
     for step in range(start, iters):
         loss = trainer.train_step(next_block(step))
-        if log is not None:
-            now = time.perf_counter()
+        if a.finite_check_every > 0 and (step + 1) % a.finite_check_every == 0 and loss != loss:
+            raise FloatingPointError(f"non-finite loss at step {step + 1}")        # classified as a numerical failure
+        now = time.perf_counter()
+        stamps.append(now - paused)
+        if log is not None and (a.metrics_every <= 1 or (step + 1) % a.metrics_every == 0 or step + 1 == iters):
             log.write(json.dumps({"step": step + 1, "loss": loss, "tokens_per_second": a.total_batch_size / (now - t_last),
                                   "data": data_tag}) + "\n")
             log.flush()
-            t_last = now
+        t_last = now
         last = step + 1 == iters
-        if (a.save_every > 0 and (step + 1) % a.save_every == 0) or last:
+        if (a.save_every > 0 and (step + 1) % a.save_every == 0) or (last and a.save_final_checkpoint):
             save(trainer, ckpt_dir, step + 1, rank, model_cfg, a)
+            paused += time.perf_counter() - now                                  # a checkpoint is not a training interval
+            t_last = time.perf_counter()
+    if rank == 0 and len(stamps) > 1:
+        from ..contracts.performance import ThroughputProtocol, summarize_step_timestamps
+        from ..contracts.substrate import atomic_write_json
+
+        proto = ThroughputProtocol(warmup_steps=a.throughput_warmup_steps, measurement_steps=a.throughput_measurement_steps)
+        atomic_write_json(run_dir / "throughput.json", summarize_step_timestamps(stamps, tokens_per_step=a.total_batch_size,
+                                                                                  protocol=proto))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
