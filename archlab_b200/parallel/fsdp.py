@@ -238,3 +238,19 @@ def shard_linears(module: nn.Module, group: FsdpGroup, *, min_features: int = 25
         setattr(parent, name, new)
     group.sync()
     return module
+
+
+def full_state_dict(module: nn.Module, group: FsdpGroup) -> dict[str, torch.Tensor]:
+    """State of ``module`` with every sharded linear gathered back to its full ``[out, in]`` weight (padding rows
+    dropped) under the name an unsharded ``nn.Linear`` would use: what an export or a single-process evaluation
+    loads.  A collective call: every rank of the group must make it."""
+    sharded = {name: m for name, m in module.named_modules() if isinstance(m, FsdpLinear)}
+    out = {}
+    for key, value in module.state_dict().items():
+        owner = key.rsplit(".", 1)[0] if "." in key else ""
+        if owner in sharded and key.endswith("weight"):
+            layer = sharded[owner]
+            out[key] = group.full_weight(layer)[: layer.out_features].clone()
+        else:
+            out[key] = value.detach().clone()
+    return out

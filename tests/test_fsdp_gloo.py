@@ -60,6 +60,12 @@ def _worker(rank, world, port, out):
             model[0].group.sync()
         full = model[0].group.full_weight(layers[0])[:320]
         errs.append((full - ref[0].weight).abs().max().item())
+        from archlab_b200.parallel.fsdp import full_state_dict
+
+        state = full_state_dict(model, model[0].group)                 # loads into the unsharded model as is
+        fresh = _model()
+        fresh.load_state_dict(state)
+        errs.append(max((a - b).abs().max().item() for a, b in zip(fresh.parameters(), ref.parameters())))
         torch.save(errs, os.path.join(out, f"fsdp{rank}.pt"))
     finally:
         dist.destroy_process_group()
