@@ -1,0 +1,55 @@
+"""KV-cache engine of the speedrun GPT: cached logits equal the full forward pass; sampling API."""
+import pytest
+import torch
+
+from archlab_b200.models.nanochat import GPT, GPTConfig
+from archlab_b200.serve.kv_engine import Engine, KVCache, forward_cached
+
+
+def _model(pattern="SL"):
+    torch.manual_seed(0)
+    cfg = GPTConfig(sequence_len=512, vocab_size=300, n_layer=4, n_head=4, n_kv_head=2, n_embd=64, window_pattern=pattern)
+    m = GPT(cfg)
+    m.init_weights()
+    with torch.no_grad():                                   # make the gates and gains matter
+        m.smear_lambda.fill_(0.7)
+        m.x0_lambdas.uniform_(-0.2, 0.2)
+        for p in m.parameters():
+            if p.dim() >= 2 and float(p.abs().max()) == 0:
+                p.normal_(std=0.05)
+    return m.eval()
+
+
+@pytest.mark.parametrize("split", [(200,), (1, 199), (150, 1, 1, 48), (64, 64, 72)])
+def test_cached_logits_equal_full_forward(split):
+    m = _model()
+    ids = torch.randint(0, 300, (2, sum(split)))
+    want = m(ids)
+    cache = KVCache(m, 2, 256)
+    got, s = [], 0
+    for n in split:
+        got.append(forward_cached(m, ids[:, s: s + n], cache))
+        s += n
+    torch.testing.assert_close(torch.cat(got, 1), want, atol=2e-4, rtol=1e-4)
+    assert cache.pos == sum(split)
+
+
+def test_greedy_generation_matches_the_uncached_sampler_and_samples_share_the_prefill():
+    m = _model("L")
+    prompt = [5, 17, 200, 3]
+    eng = Engine(m)
+    cached = eng.generate_batch(prompt, max_tokens=12, temperature=0.0)[0]
+    naive = prompt + list(m.generate(prompt, 12, temperature=0.0))
+    assert cached == naive
+    outs = eng.generate_batch(prompt, num_samples=3, max_tokens=8, temperature=1.0, top_k=20, seed=1)
+    assert len(outs) == 3 and all(o[:4] == prompt and len(o) == 12 for o in outs) and len({tuple(o) for o in outs}) > 1
+    stopped = eng.generate_batch(prompt, max_tokens=12, temperature=0.0, stop_tokens=(cached[6],))[0]
+    assert stopped == cached[:6]
+
+
+def test_engine_refuses_families_with_their_own_trunk():
+    from archlab_b200.models.nanochat_variants import MhcGPT, MhcGPTConfig
+
+    m = MhcGPT(MhcGPTConfig(sequence_len=64, vocab_size=64, n_layer=2, n_head=2, n_kv_head=2, n_embd=32))
+    with pytest.raises(TypeError):
+        Engine(m)
