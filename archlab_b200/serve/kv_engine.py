@@ -154,3 +154,50 @@ class Engine:
                 if t is not None and t not in stops:
                     out[r].append(t)
         return out
+
+
+# ------------------------------------------------------------------------------------------------
+# chat: conversation -> tokens, and the worker that answers the tickets of the HTTP front
+# ------------------------------------------------------------------------------------------------
+def render_chat(tokenizer, messages: list[dict]) -> list[int]:
+    """``<|bos|>`` then every turn between its role markers (a system message is folded into the first user turn),
+    ending with ``<|assistant_start|>`` so that the model writes the reply (speedrun chat format,
+    src/archlab/speedrun/tokenizer.py ``render_for_completion``)."""
+    sp = tokenizer.special
+    ids = [sp["<|bos|>"]]
+    pending = ""
+    for m in messages:
+        if m["role"] == "system":
+            pending += m["content"] + "\n\n"
+            continue
+        role = "user" if m["role"] == "user" else "assistant"
+        text = (pending + m["content"]) if role == "user" else m["content"]
+        pending = "" if role == "user" else pending
+        ids += [sp[f"<|{role}_start|>"], *tokenizer.encode(text), sp[f"<|{role}_end|>"]]
+    return ids + [sp["<|assistant_start|>"]]
+
+
+def answer_tickets(front, engine: "Engine", tokenizer, *, stop=None, idle_timeout: float = 0.2, top_k: int | None = 50) -> int:
+    """Drains the chat front's ticket queue on the thread that owns the model until ``stop()`` is true: one
+    generation per ticket, reply text = decoded tokens up to ``<|assistant_end|>``.  Returns the tickets served."""
+    served = 0
+    end = tokenizer.special["<|assistant_end|>"]
+    while not (stop and stop()):
+        ticket = front.next_ticket(timeout=idle_timeout)
+        if ticket is None:
+            continue
+        req = ticket.request
+        try:
+            front.set_state("generating", id=ticket.id)
+            prompt = render_chat(tokenizer, req["messages"])
+            room = engine.model.cos.size(0) - len(prompt)
+            if room < 1:
+                raise ValueError("the conversation does not fit the model's context")
+            out = engine.generate_batch(prompt, max_tokens=min(req["max_tokens"], room), temperature=req["temperature"],
+                                        top_k=top_k, seed=req["seed"] % (2 ** 63), stop_tokens=(end,))[0]
+            ticket.finish(text=tokenizer.decode(out[len(prompt):]))
+        except Exception as e:                                     # the front reports it as a 500 with this message
+            ticket.finish(error=f"{type(e).__name__}: {e}")
+        served += 1
+        front.set_state("serving")
+    return served

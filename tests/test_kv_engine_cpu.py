@@ -53,3 +53,40 @@ def test_engine_refuses_families_with_their_own_trunk():
     m = MhcGPT(MhcGPTConfig(sequence_len=64, vocab_size=64, n_layer=2, n_head=2, n_kv_head=2, n_embd=32))
     with pytest.raises(TypeError):
         Engine(m)
+
+
+def test_chat_front_is_answered_by_the_engine():
+    import json
+    import threading
+    import urllib.request
+
+    from archlab_b200.data.tokenizer import BPETokenizer
+    from archlab_b200.serve.kv_engine import answer_tickets, render_chat
+    from archlab_b200.services.chat import ChatFront
+
+    tok = BPETokenizer.train(["hello world, hello there. the quick brown fox"] * 4, vocab_size=280)
+    ids = render_chat(tok, [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hello"}])
+    assert ids[0] == tok.special["<|bos|>"] and ids[-1] == tok.special["<|assistant_start|>"]
+    assert tok.decode(ids[2:-2]) == "be brief\n\nhello"
+    torch.manual_seed(0)
+    m = GPT(GPTConfig(sequence_len=128, vocab_size=300, n_layer=2, n_head=2, n_kv_head=2, n_embd=32, window_pattern="L"))
+    m.init_weights()
+    front = ChatFront("127.0.0.1", 0, "tok", {"tiny": "normal"})
+    port = front.server.server_address[1]
+    stop = threading.Event()
+    result = {}
+
+    def client():
+        body = json.dumps({"model": "tiny", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 6}).encode()
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/chat/completions", data=body,
+                                     headers={"Authorization": "Bearer tok", "Content-Type": "application/json"})
+        result["reply"] = json.loads(urllib.request.urlopen(req, timeout=30).read())
+        stop.set()
+
+    t = threading.Thread(target=client)
+    t.start()
+    served = answer_tickets(front, Engine(m), tok, stop=stop.is_set)
+    t.join(10)
+    front.server.shutdown()
+    assert served == 1 and result["reply"]["object"] == "chat.completion"
+    assert isinstance(result["reply"]["choices"][0]["message"]["content"], str)
