@@ -248,7 +248,8 @@ class _Job:
                 raise ValueError("--fsdp shards the linears of a factory model over a data group of at least two ranks")
             from ..parallel.fsdp import FsdpGroup, shard_linears
 
-            self.fsdp = FsdpGroup(device, groups["dp"], reshard_after_forward=not getattr(a, "fsdp_keep_gathered", False))
+            self.fsdp = FsdpGroup(device, groups["dp"], reshard_after_forward=not getattr(a, "fsdp_keep_gathered", False),
+                                  grad_reduce="sum")      # the step scales every gradient by 1 / (accumulation x data ranks)
             shard_linears(self.model, self.fsdp, min_features=a.fsdp_min_features)
 
     def _init_qwen(self, seed: int) -> None:

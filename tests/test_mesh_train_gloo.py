@@ -147,4 +147,6 @@ def test_fully_sharded_linears_follow_the_replicated_run(tmp_path):
     shard = _run(2, base + ["--fsdp", "--fsdp-min-features=64", f"--run-dir={tmp_path / 'fsdp'}"])
     assert all(abs(a - b) < 2e-3 * abs(a) for a, b in zip(plain[0], shard[0])), (plain[0], shard[0])
     assert shard[0][-1] < shard[0][0]
+    norms = [[json.loads(l)["grad_norm"] for l in open(tmp_path / d / "metrics_rank0.jsonl")] for d in ("plain", "fsdp")]
+    assert all(abs(a - b) < 2e-2 * a for a, b in zip(*norms)), norms        # same gradient scale, not only the same direction
     assert all(abs(a - b) < 1e-6 for a, b in zip(shard[0], shard[1]))
