@@ -120,6 +120,8 @@ def parse_args(argv=None):
                          "fp8_tensor: tensor-scaled e4m3 / e5m2 GEMMs on the 8-bit tensor-core path")
     ap.add_argument("--model-set", action="append", default=[], metavar="KEY=VALUE",
                     help="factory models: override a field of the family's config (repeatable; values parse as JSON)")
+    ap.add_argument("--native-linears", action="store_true",
+                    help="run the bias-free nn.Linear layers of the model on the hand-written GEMM kernels")
     ap.add_argument("--fsdp", action="store_true",
                     help="factory models: shard the linear weights over the data group; the all-gather of a weight runs "
                          "inside the GEMM that consumes it")
@@ -241,6 +243,10 @@ class _Job:
             from ..ops.fp8 import convert_linears
 
             self.fp8_layers = convert_linears(self.model)        # dense nn.Linear layers; expert and TP GEMMs stay bf16
+        if getattr(a, "native_linears", False) and not getattr(a, "fsdp", False):
+            from ..ops.native_linear import convert_linears as to_native
+
+            self.native_layers = to_native(self.model)           # nn.Linear layers onto the pair GEMM kernels
         self.fsdp = None
         if getattr(a, "fsdp", False):
             # fully-sharded linear weights over the data group: the gather runs inside the consuming GEMM kernel
