@@ -186,9 +186,15 @@ _EXPERT_SUFFIXES = (".ffn.experts.gate_and_up_projs", ".ffn.experts.down_projs")
 
 
 def shard_extent(size: int, pieces: int, index: int) -> tuple[int, int]:
-    """(offset, length) of piece ``index`` when ``size`` is cut into ``pieces`` near-equal parts."""
-    base, extra = divmod(size, pieces)
-    return index * base + min(index, extra), base + (1 if index < extra else 0)
+    """(offset, length) of piece ``index`` of an axis of ``size`` cut into ``pieces``.
+
+    The on-disk layout fixes the rule (src/archlab/serving/v41_checkpoint_inventory.py:20-23): every
+    piece is ``ceil(size / pieces)`` wide, the last non-empty one takes what is left and pieces past
+    the end are empty (offset = size, length 0).  10 rows over 4 pieces: (0,3) (3,3) (6,3) (9,1).
+    """
+    width = -(-size // pieces)
+    offset = min(index * width, size)
+    return offset, min(width, size - offset)
 
 
 def _placement(name: str, shape: list[int], rank: int, world: int, ep: int, fsdp: int):
@@ -375,7 +381,8 @@ def export_v41_released(out_dir, tensors, *, engram_row_block: int = 0) -> dict:
 # run receipts
 # ------------------------------------------------------------------------------------------------
 class RunReceipts:
-    """RUNNING.json while the run is alive; exactly one of COMPLETE.json / FAILED.json afterwards."""
+    """RUNNING.json while the run is alive; afterwards COMPLETE.json, FAILED.json, or neither when the
+    run was stopped on request (``stopped``)."""
 
     def __init__(self, run_dir, resolved: dict):
         self.dir = Path(run_dir)
@@ -389,6 +396,12 @@ class RunReceipts:
     def log(self, record: dict) -> None:
         with open(self.dir / "metrics.jsonl", "a") as f:
             f.write(json.dumps(record) + "\n")
+
+    def stopped(self, result: dict | None = None) -> None:
+        """A requested stop before the step budget was used up: the partial result is recorded and
+        RUNNING.json goes away, but no COMPLETE.json is written, so the directory can be resumed."""
+        atomic_write_json(self.dir / "result.json", {**(result or {}), "outcome": "stopped"})
+        (self.dir / "RUNNING.json").unlink(missing_ok=True)
 
     def finish(self, result: dict | None = None, error: BaseException | None = None) -> None:
         from ..contracts.substrate import classify_failure

@@ -465,21 +465,38 @@ def train(a, *, on_step=None) -> list[float]:
                             mesh.rank_of(pp_i=mesh.pp_i + 1) if mesh.pp_i + 1 < mesh.pp else None)
     run_dir = Path(os.environ.get(a.run_dir[4:], "runs/mesh") if a.run_dir.startswith("env:") else a.run_dir)
     log, receipts = None, None
+    refusal = None
     if rank == 0:
         from ..ckpt.formats import RunReceipts
 
-        run_dir.mkdir(parents=True, exist_ok=True)
-        attempt = check_contract(run_dir, run_contract(a, world), a.resume)
-        (run_dir / "config.json").write_text(json.dumps({"args": vars(a), "world_size": world, "data_parallel": mesh.dp,
-                                                         "grad_accum_steps": accum, "attempt": attempt}, indent=2))
-        (run_dir / "PARALLELISM.json").write_text(json.dumps({"tensor": mesh.tp, "pipeline": mesh.pp, "context": mesh.cp,
-                                                              "expert": a.ep, "data": mesh.dp, "world_size": world,
-                                                              "order": "tensor fastest, then context, data, pipeline"}, indent=2))
-        (run_dir / "MODEL_SHAPES.json").write_text(json.dumps({n: list(p.shape) for n, p in job.model.named_parameters()}, indent=1))
-        receipts = RunReceipts(run_dir, {"args": vars(a), "world_size": world})
-        log = open(run_dir / "metrics_rank0.jsonl", "a")
+        try:
+            run_dir.mkdir(parents=True, exist_ok=True)
+            attempt = check_contract(run_dir, run_contract(a, world), a.resume)
+            (run_dir / "config.json").write_text(json.dumps({"args": vars(a), "world_size": world, "data_parallel": mesh.dp,
+                                                             "grad_accum_steps": accum, "attempt": attempt}, indent=2))
+            (run_dir / "PARALLELISM.json").write_text(json.dumps({"tensor": mesh.tp, "pipeline": mesh.pp, "context": mesh.cp,
+                                                                  "expert": a.ep, "data": mesh.dp, "world_size": world,
+                                                                  "order": "tensor fastest, then context, data, pipeline"}, indent=2))
+            (run_dir / "MODEL_SHAPES.json").write_text(json.dumps({n: list(p.shape) for n, p in job.model.named_parameters()}, indent=1))
+            receipts = RunReceipts(run_dir, {"args": vars(a), "world_size": world})
+            if a.resume:                                         # the stop that ended the previous attempt is consumed
+                (run_dir / "STOP_REQUESTED.json").unlink(missing_ok=True)
+                (run_dir / "STOPPED.json").unlink(missing_ok=True)
+            log = open(run_dir / "metrics_rank0.jsonl", "a")
+        except Exception as exc:                                 # told to the other ranks below, then raised here
+            refusal = exc
     if world > 1:
-        dist.barrier()                                           # a refused contract stops every rank at the next collective
+        # rank 0's verdict on the run directory reaches every rank: a refused contract or a closed
+        # directory ends all of them here instead of leaving the others in a collective until it times out
+        verdict = [None if refusal is None else f"{type(refusal).__name__}: {refusal}"]
+        dist.broadcast_object_list(verdict, src=0)
+        if rank != 0 and verdict[0] is not None:
+            dist.destroy_process_group()
+            raise RuntimeError(f"rank 0 refused the run directory: {verdict[0]}")
+    if refusal is not None:
+        if world > 1:
+            dist.destroy_process_group()
+        raise refusal
     start = load_checkpoint(run_dir, rank, job, opt) if a.resume else 0
     from . import health
 
@@ -496,6 +513,7 @@ def train(a, *, on_step=None) -> list[float]:
     losses = []
     scale = 1.0 / (accum * mesh.dp)
     cuda = device.type == "cuda"
+    reached, stopped_early = start, False
     for step in range(start, a.steps):
         t0 = time.perf_counter()
         if cuda:
@@ -547,11 +565,19 @@ def train(a, *, on_step=None) -> list[float]:
         stopping = stop.should_stop()
         if (a.save_every and ((step + 1) % a.save_every == 0 or step + 1 == a.steps)) or stopping:
             save_checkpoint(run_dir, step + 1, rank, job, opt)
+        reached = step + 1
         if stopping:                                             # every rank leaves at the same step, after the checkpoint
             stop.acknowledge(step + 1, rank)
+            stopped_early = reached < a.steps
             break
     if receipts is not None:
-        receipts.finish({"final_loss": losses[-1] if losses else None, "steps": a.steps})
+        outcome = {"final_loss": losses[-1] if losses else None, "steps": reached, "step_budget": a.steps}
+        if stopped_early:
+            # a graceful stop leaves STOPPED.json + the checkpoint and no completion marker, so that
+            # --resume can continue it (src/archlab/megatron/simplicial_pilot.py:457-460)
+            receipts.stopped(outcome)
+        else:
+            receipts.finish(outcome)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -1,0 +1,252 @@
+"""Reference arm of ``bench.py``: the reference project's own speedrun stack on the same step.
+
+What runs here is the unmodified ``archlab`` package of the reference (a file copy of its
+``src/archlab`` tree under ``baseline/_ref``, which is what its wheel would install) driven through
+its public pieces in the order its training script uses them
+(src/archlab/speedrun/base_train.py:979-1044, 1238-1242, 1330-1340, 1812-1870):
+
+    compute_init -> build_model_config -> instantiate_model on "meta" -> to_empty -> init_weights
+    -> torch.compile(model, dynamic=False) -> setup_model_optimizer (DistMuonAdamW when ranks > 1)
+    -> per step: loss = model(x, y); loss.backward(); schedules; optimizer.step(); zero_grad
+
+Nothing of this repository's package is imported and its native library is not loaded.  Attention
+goes through the reference's own backend selection (src/archlab/speedrun/attention.py:82-104): FA4
+when ``flash_attn.cute`` imports, else its SDPA fallback; the choice is reported in the JSON line.
+The training script itself cannot be executed as is because it opens FineWeb shards and a
+tokenizer that are not reachable offline; the token blocks are therefore the same synthetic
+Zipf(1.1) ids the other arm uses.
+"""
+from __future__ import annotations
+
+import math
+import os
+import sys
+import time
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF_ROOT = os.path.join(HERE, "_ref")
+
+
+def ensure_reference_tree() -> str | None:
+    """Returns None when ``baseline/_ref/archlab`` is importable, else a one-line reason.  When the
+    tree is missing and the reference checkout is mounted, the package directory is copied over
+    (the reference's build backend, hatchling, is not installable offline, so ``pip install
+    --target`` cannot produce it)."""
+    pkg = os.path.join(REF_ROOT, "archlab")
+    if not os.path.isdir(pkg):
+        src = os.environ.get("ARCHLAB_REFERENCE_SRC", "/root/reference/src/archlab")
+        if os.path.isdir(src):
+            import shutil
+
+            os.makedirs(REF_ROOT, exist_ok=True)
+            shutil.copytree(src, pkg)
+        else:
+            return "baseline/_ref/archlab is absent and no reference checkout is mounted to copy it from"
+    return None
+
+
+def zipf_block(cdf: np.ndarray, vocab: int, batch: int, seq_len: int, seed: int, rank: int, index: int):
+    """Same stream as the other arm's generator: block ``index`` of ``rank`` depends on
+    (seed, rank, index) only; ids are inverse-CDF samples of Zipf(1.1)."""
+    import torch
+
+    rng = np.random.default_rng([seed, rank, index])
+    u = rng.random((batch, seq_len + 1))
+    ids = np.searchsorted(cdf, u, side="right").astype(np.int64)
+    np.minimum(ids, vocab - 1, out=ids)
+    t = torch.from_numpy(ids)
+    return t.pin_memory() if torch.cuda.is_available() else t
+
+
+def run(args, sampler_cls) -> dict | None:
+    """Runs warm-up + device-timed + end-to-end regions and returns the JSON record (rank 0) or None."""
+    sys.path.insert(0, REF_ROOT)
+    for name in list(sys.modules):
+        if name == "archlab_b200" or name.startswith("archlab_b200."):
+            raise RuntimeError("the reference arm must not share a process with this repository's package")
+
+    import torch
+    import torch.distributed as dist
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    from archlab.model_factory import build_model_config, instantiate_model
+    from archlab.optimizers.speedrun import setup_model_optimizer
+    from archlab.speedrun import attention as ref_attention
+    from archlab.speedrun.precision import resolve_precision_backend
+    from archlab.speedrun.runtime import COMPUTE_DTYPE, compute_init
+
+    # CPU is accepted only so that the wiring can be checked without a GPU (tiny sizes, fp32).
+    device_type = "cuda" if torch.cuda.is_available() else "cpu"
+    ddp, rank, local_rank, world, device = compute_init(device_type)
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    on_gpu = device_type == "cuda"
+    if on_gpu and not ddp:
+        device = torch.device("cuda", local_rank)
+        torch.cuda.set_device(device)
+    precision = resolve_precision_backend(
+        "bf16", device_type=device_type, gpu_name=torch.cuda.get_device_name(device) if on_gpu else None)
+
+    cfg = build_model_config(arch_family="nanochat", depth=args.depth, aspect_ratio=64, head_dim=128,
+                             max_seq_len=args.seq_len, vocab_size=args.vocab,
+                             window_pattern=args.window_pattern, fog_variant="fog_opt")
+    with torch.device("meta"):
+        model = instantiate_model(cfg, runtime_backend=precision.runtime_backend)
+    model.to_empty(device=device)
+    model.init_weights()
+    # The benchmark's stated initialisation is N(0, 0.02) on the block matrices (the stock recipe
+    # zeroes the output projections); values only, the module code is untouched.
+    with torch.no_grad():
+        for block in model.transformer.h:
+            for lin in (block.attn.c_q, block.attn.c_k, block.attn.c_v, block.attn.c_proj,
+                        block.mlp.c_fc, block.mlp.c_proj):
+                lin.weight.normal_(0.0, 0.02)
+    orig_model = model
+    compiled = "torch.compile(dynamic=False)"
+    if args.no_compile:
+        compiled = "eager (--no-compile)"
+    else:
+        model = torch.compile(model, dynamic=False)
+
+    num_iterations = 10000
+    optimizer = setup_model_optimizer(orig_model, unembedding_lr=args.unembedding_lr,
+                                      embedding_lr=args.embedding_lr, scalar_lr=args.scalar_lr,
+                                      matrix_lr=args.matrix_lr, weight_decay=args.weight_decay)
+
+    warmup_steps, warmdown_ratio, final_lr_frac = 40, 0.65, 0.05
+
+    def lr_multiplier(it):
+        warmdown = round(warmdown_ratio * num_iterations)
+        if it < warmup_steps:
+            return (it + 1) / warmup_steps
+        if it <= num_iterations - warmdown:
+            return 1.0
+        progress = (num_iterations - it) / warmdown
+        return progress + (1 - progress) * final_lr_frac
+
+    def muon_momentum(it):
+        return (1 - it / 400) * 0.85 + (it / 400) * 0.97 if it < 400 else 0.97
+
+    def muon_weight_decay(it):
+        return args.weight_decay * 0.5 * (1 + math.cos(math.pi * it / num_iterations))
+
+    step_index = 0
+
+    def train_step_device(tok):
+        """One iteration of the reference loop on a device-resident block (grad_accum_steps = 1:
+        the local batch equals the script's default --device-batch-size of 32 sequences)."""
+        nonlocal step_index
+        x, y = tok[:, :-1], tok[:, 1:]
+        loss = None
+        for s in range(0, x.size(0), args.micro_batch):
+            with precision.training_context():
+                loss = model(x[s:s + args.micro_batch].contiguous(), y[s:s + args.micro_batch].contiguous())
+            train_loss = loss.detach()
+            (loss / accum).backward()
+        lrm = lr_multiplier(step_index)
+        for group in optimizer.param_groups:
+            group["lr"] = group["initial_lr"] * lrm
+            if group["kind"] == "muon":
+                group["momentum"] = muon_momentum(step_index)
+                group["weight_decay"] = muon_weight_decay(step_index)
+        optimizer.step()
+        model.zero_grad(set_to_none=True)
+        step_index += 1
+        return train_loss
+
+    accum = max(1, args.local_batch // args.micro_batch)
+    ranks = np.arange(1, args.vocab + 1, dtype=np.float64) ** (-1.1)
+    cdf = np.cumsum(ranks / ranks.sum())
+    cdf[-1] = 1.0
+    n_blocks = args.warmup + 2 * args.steps
+    host_blocks = [zipf_block(cdf, args.vocab, args.local_batch, args.seq_len, 0, rank, i) for i in range(n_blocks)]
+    dev_blocks = [b.to(device) for b in host_blocks[: args.warmup + args.steps]]
+    staging = torch.empty_like(dev_blocks[0])
+
+    def sync():
+        if on_gpu:
+            torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        sync()
+
+    compile_note = None
+    try:
+        for i in range(args.warmup):
+            train_step_device(dev_blocks[i])
+    except Exception as exc:  # inductor / triton failure on this box: the reference's eager module
+        if args.no_compile:
+            raise
+        compile_note = f"torch.compile failed ({type(exc).__name__}: {str(exc)[:160]}); eager module used"
+        compiled = "eager (compile failed)"
+        model = orig_model
+        model.zero_grad(set_to_none=True)
+        for i in range(args.warmup):
+            train_step_device(dev_blocks[i])
+    barrier()
+
+    sampler = sampler_cls(local_rank)
+    sampler.start()
+    barrier()
+    if on_gpu:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        train_step_device(dev_blocks[args.warmup + i])
+    if on_gpu:
+        e1.record()
+    barrier()
+    dev_ms = e0.elapsed_time(e1) if on_gpu else (time.perf_counter() - t0) * 1e3
+
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        staging.copy_(host_blocks[args.warmup + args.steps + i], non_blocking=True)
+        last_loss = float(train_step_device(staging).item())
+    sync()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    barrier()
+    clocks = sampler.stop()
+
+    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = float(times[0]), float(times[1])
+    tokens_per_step = args.local_batch * args.seq_len * world
+    out = None
+    if rank == 0:
+        mc = orig_model.config
+        out = {
+            "metric": "train tokens/sec/box", "value": tokens_per_step * args.steps / (dev_ms / 1e3),
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": str(COMPUTE_DTYPE).replace("torch.", "").replace("bfloat16", "bf16"),
+            "data": "synthetic: Zipf(1.1) token ids from seed 0, random-init weights",
+            "impl": "reference",
+            "config": {
+                "model": f"nanochat-speedrun-d{args.depth} ({mc.n_layer}L, d_model {mc.n_embd}, "
+                         f"{mc.n_head}x{mc.n_embd // mc.n_head} heads, vocab {args.vocab})",
+                "global_batch": tokens_per_step, "seq_len": args.seq_len,
+                "parallelism": f"dp{world} ({type(optimizer).__name__})",
+                "micro_batch_sequences": args.micro_batch, "window_pattern": args.window_pattern,
+                "l2": "working set per step far exceeds the 126 MB L2; no explicit flush",
+                "reference": {"package": "unmodified file copy of src/archlab under baseline/_ref",
+                              "model_call": compiled,
+                              "attention_backend": ref_attention.ATTENTION_BACKEND,
+                              "attention_backend_reason": ref_attention.ATTENTION_BACKEND_REASON,
+                              "note": compile_note},
+            },
+            "clocks": clocks,
+            "e2e": {"value": tokens_per_step * args.steps / (e2e_ms / 1e3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": host_blocks[0].numel() * host_blocks[0].element_size(),
+                    "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms / args.steps},
+            "final_loss": last_loss,
+        }
+    if world > 1:
+        dist.destroy_process_group()
+    return out

@@ -27,11 +27,6 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-REFERENCE_UNAVAILABLE = (
-    "pip install --no-index of the reference fails: its build backend (hatchling) and its "
-    "dependencies omegaconf / hydra-core are not in the offline wheelhouse"
-)
-
 
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
@@ -84,15 +79,40 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference", "eager"])
     ap.add_argument("--local-batch", type=int, default=32, help="sequences per GPU per step")
-    ap.add_argument("--micro-batch", type=int, default=16)
+    ap.add_argument("--micro-batch", type=int, default=None,
+                    help="sequences per forward/backward (default: 16 here, 32 = the stock "
+                         "--device-batch-size in the reference arm)")
     ap.add_argument("--depth", type=int, default=20)
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--vocab", type=int, default=65536)
+    ap.add_argument("--window-pattern", default="SSSL", help="the speedrun script's default in both arms")
+    ap.add_argument("--no-compile", action="store_true", help="reference arm: skip torch.compile")
+    # optimizer settings shared by both arms (the reference script's defaults, base_train.py:499-522)
+    ap.add_argument("--matrix-lr", type=float, default=0.02)
+    ap.add_argument("--embedding-lr", type=float, default=0.3)
+    ap.add_argument("--unembedding-lr", type=float, default=0.008)
+    ap.add_argument("--scalar-lr", type=float, default=0.5)
+    ap.add_argument("--weight-decay", type=float, default=0.28)
     args = ap.parse_args()
+    if args.warmup < 3:
+        raise SystemExit("at least 3 warm-up steps are required")
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import reference_arm
+
+        if args.micro_batch is None:
+            args.micro_batch = min(32, args.local_batch)
+        why = reference_arm.ensure_reference_tree()
+        if why is not None:
+            print(json.dumps({"impl": "reference", "unavailable": why}))
+            return
+        out = reference_arm.run(args, ClockSampler)
+        if out is not None:
+            print(json.dumps(out))
         return
+    if args.micro_batch is None:
+        args.micro_batch = min(16, args.local_batch)
 
     import torch
     import torch.distributed as dist
@@ -102,8 +122,6 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
-    if args.warmup < 3:
-        raise SystemExit("at least 3 warm-up steps are required")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -116,8 +134,12 @@ def main() -> None:
     from archlab_b200.train.speedrun import Trainer, TrainerConfig
 
     mcfg = GPTConfig.from_depth(args.depth, sequence_len=args.seq_len, vocab_size=args.vocab,
-                                compute_dtype=torch.bfloat16, matrix_init_recipe="normal-0.02")
-    tcfg = TrainerConfig(model=mcfg, micro_batch=args.micro_batch, num_iterations=10000)
+                                compute_dtype=torch.bfloat16, matrix_init_recipe="normal-0.02",
+                                window_pattern=args.window_pattern)
+    tcfg = TrainerConfig(model=mcfg, micro_batch=args.micro_batch, num_iterations=10000,
+                         matrix_lr=args.matrix_lr, embedding_lr=args.embedding_lr,
+                         unembedding_lr=args.unembedding_lr, scalar_lr=args.scalar_lr,
+                         weight_decay=args.weight_decay)
     trainer = Trainer(tcfg, device=dev)
     if args.impl == "eager":
         trainer.engine = None   # cuBLAS + SDPA + autograd on the same parameters
@@ -185,7 +207,7 @@ def main() -> None:
                          f"{mcfg.n_head}x{mcfg.head_dim} heads, vocab {args.vocab})",
                 "global_batch": tokens_per_step, "seq_len": args.seq_len,
                 "parallelism": f"dp{world} (ZeRO-1 Muon/AdamW inside the optimizer)",
-                "micro_batch_sequences": args.micro_batch,
+                "micro_batch_sequences": args.micro_batch, "window_pattern": args.window_pattern,
                 "l2": "working set per step far exceeds the 126 MB L2; no explicit flush",
             },
             "clocks": clocks,

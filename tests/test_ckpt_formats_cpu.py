@@ -74,7 +74,29 @@ def test_v41_sharded_inventory_and_reconstruction(tmp_path):
     man.write_text(json.dumps(data))
     with pytest.raises(ValueError):
         F.V41CheckpointInventory(tmp_path)
-    assert F.shard_extent(37, 16, 0) == (0, 3) and F.shard_extent(37, 16, 15) == (35, 2)
+    assert F.shard_extent(37, 16, 0) == (0, 3) and F.shard_extent(37, 16, 12) == (36, 1)
+    assert F.shard_extent(37, 16, 15) == (37, 0)
+
+
+def test_v41_shard_extents_of_axes_the_piece_count_does_not_divide(tmp_path):
+    """Ceil-width pieces with a short or empty tail, which is the placement a reference-written
+    checkpoint has (src/archlab/serving/v41_checkpoint_inventory.py:20-23)."""
+    assert [F.shard_extent(10, 4, i) for i in range(4)] == [(0, 3), (3, 3), (6, 3), (9, 1)]
+    assert [F.shard_extent(3, 2, i) for i in range(2)] == [(0, 2), (2, 1)]
+    assert [F.shard_extent(5, 4, i) for i in range(4)] == [(0, 2), (2, 2), (4, 1), (5, 0)]
+    g = torch.Generator().manual_seed(3)
+    state = {"embed_tokens.weight": torch.randn(10, 4, generator=g),
+             "layers.0.ffn.experts.gate_and_up_projs": torch.randn(3, 5, 6, generator=g),
+             "layers.0.ffn.experts.down_projs": torch.randn(3, 3, 5, generator=g)}
+    F.write_v41_sharded(tmp_path, state, cursor={"step": 1, "tokens": 8}, world_size=4, ep_size=2,
+                        expert_fsdp_size=2, engram_owners=4, chunk_elements=5)
+    inv = F.V41CheckpointInventory(tmp_path)
+    rows = [e["shape"][0] for e in inv.entries["embed_tokens.weight"]]
+    assert rows == [3, 3, 3, 1]
+    experts = [e["shape"][:2] for e in inv.entries["layers.0.ffn.experts.gate_and_up_projs"]]
+    assert experts == [[2, 3], [1, 3], [2, 2], [1, 2]]      # rank = ep index + 2 * fsdp index
+    for name, t in state.items():
+        assert torch.equal(inv.read_tensor(name), t), name
 
 
 def test_v41_released_name_export(tmp_path):

@@ -132,6 +132,15 @@ def test_stop_request_checkpoints_and_leaves_cleanly(tmp_path, monkeypatch):
     assert len(losses) == 2
     assert json.loads((run / "STOPPED.json").read_text())["step"] == 2
     assert (run / "checkpoints" / "latest_checkpointed_iteration.txt").read_text().strip() == "2" and (run / "HEARTBEAT.json").exists()
+    # a stopped run is not a completed one: no completion marker, the partial result says so
+    assert not (run / "COMPLETE.json").exists() and not (run / "RUNNING.json").exists()
+    assert json.loads((run / "result.json").read_text()) ["outcome"] == "stopped"
+    # ... and it resumes where it stopped, reproducing the uninterrupted run
+    full = mesh_train.train(mesh_train.parse_args(argv[:-1] + [f"--run-dir={tmp_path / 'full'}"]))
+    rest = mesh_train.train(mesh_train.parse_args(argv + ["--resume"]))
+    assert len(rest) == 4 and losses + rest == pytest.approx(full, abs=1e-6)
+    assert (run / "COMPLETE.json").exists() and not (run / "STOPPED.json").exists()
+    assert json.loads((run / "result.json").read_text())["steps"] == 6
 
 
 def test_fully_sharded_linears_follow_the_replicated_run(tmp_path):
