@@ -21,7 +21,9 @@ int nga_attn_bwd(const void* qkv, const void* out, const void* dout, const float
 // allocate once running.  Accepts B*T*Hq*128 <= nga_attn_bwd_static_max_elems() (4 Mi fp32 elements,
 // 16 MiB); returns -20 beyond that.  Calls that may overlap on one device race on the shared
 // scratch; order them.  The first call per device resolves the arrays' addresses and should be made
-// outside stream capture.  This entry point has no counterpart in the reference project.
+// outside stream capture.  The current device must be the one that owns the buffers and the stream
+// (the scratch used is the current device's; a dqkv that lives on another device returns -22).
+// This entry point has no counterpart in the reference project.
 int nga_attn_bwd_static(const void* qkv, const void* out, const void* dout, const float* lse2,
                         void* dqkv, int B, int T, int Hq, int Hkv, int D, int window, float scale,
                         int* status, void* stream);

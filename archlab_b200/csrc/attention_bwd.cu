@@ -446,7 +446,8 @@ extern "C" int nga_attn_bwd(const void* qkv, const void* out, const void* dout, 
   rc = make_tmap_3d(&tm_dq, dq_acc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ocols, rows, 1, ocols * 4,
                     rows * ocols * 4, 128, 64, false);
   if (rc) return rc;
-  static bool attr_done = false;
+  static nga::PerDevice<bool> attr_flags;
+  bool& attr_done = attr_flags.here();
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          AttnBwdSmem::kTotal);
@@ -525,6 +526,12 @@ extern "C" int nga_attn_bwd_static(const void* qkv, const void* out, const void*
   if ((long long)B * T * Hq * D > kStaticDqElems || (long long)B * Hq * T > kStaticDeltaElems) return -20;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices) return -21;
+  // The scratch handed to the kernel is the CURRENT device's copy of the arrays: the caller's
+  // buffers (and hence its stream) must live on that device, or another GPU's scratch would be
+  // paired with them.  A query of the output pointer catches the mismatch (no allocation).
+  cudaPointerAttributes where = {};
+  if (cudaPointerGetAttributes(&where, dqkv) != cudaSuccess) { cudaGetLastError(); return -22; }
+  if (where.type == cudaMemoryTypeDevice && where.device != dev) return -22;
   float *dq = nullptr, *dl = nullptr;
   {
     std::lock_guard<std::mutex> lock(g_static_mu);

@@ -374,7 +374,8 @@ extern "C" int nga_attn_fwd(const void* qkv, void* out, float* lse2, int B, int 
   int rc = make_tmap_3d(&tm, qkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, cols, (long long)B * T, 1,
                         cols * 2, (long long)B * T * cols * 2, 64, 128, true);
   if (rc) return rc;
-  static bool attr_done = false;
+  static nga::PerDevice<bool> attr_flags;
+  bool& attr_done = attr_flags.here();
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          AttnFwdSmem::kTotal);

@@ -544,7 +544,8 @@ extern "C" int nga_gdn_fwd(const void* q, const void* k, const void* v, const fl
   using namespace nga;
   if (D != DR_D || B <= 0 || H <= 0 || T <= 0 || (T % DR_C)) return -1;
   const int chunks = T / DR_C;
-  static bool attr_done = false;
+  static nga::PerDevice<bool> attr_flags;
+  bool& attr_done = attr_flags.here();
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(delta_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DeltaPrepSmem::kTotal);
     if (e == cudaSuccess)

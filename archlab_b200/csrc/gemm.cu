@@ -224,7 +224,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
                        cudaStream_t stream) {
   using S = GemmSmem<BN>;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
-  static bool attr_done = false;
+  static nga::PerDevice<bool> attr_flags;
+  bool& attr_done = attr_flags.here();
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) return -1000 - (int)e;

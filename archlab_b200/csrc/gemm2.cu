@@ -496,7 +496,8 @@ template <int A_MN, int B_MN, int TP, int F8 = 0>
 static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream,
                         const CUtensorMap& ta2, const TpParams& tp, const TpMaps& tpm) {
   auto kern = gemm2_bf16_kernel<A_MN, B_MN, TP, F8>;
-  static int max_clusters = 0;
+  static nga::PerDevice<int> max_clusters_by_device;
+  int& max_clusters = max_clusters_by_device.here();
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;

@@ -48,11 +48,15 @@ int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, 
   return r == CUDA_SUCCESS ? 0 : -4000 - (int)r;
 }
 
-int sm_count() {
-  static int n[64] = {0};
+int current_device_slot() {
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
+  return (dev < 0 || dev >= kMaxDevices) ? 0 : dev;
+}
+
+int sm_count() {
+  static int n[kMaxDevices] = {0};
+  const int dev = current_device_slot();
   if (n[dev] == 0) {
     cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
     if (n[dev] <= 0) n[dev] = 148;

@@ -18,6 +18,18 @@ int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, 
 
 void count_launch();
 int sm_count();
+int current_device_slot();   // cudaGetDevice() clamped to [0, kMaxDevices)
+
+// Function attributes (the opt-in to more than 48 KB of dynamic shared memory, occupancy results)
+// belong to a device, not to the process: one slot per device, indexed by the CURRENT device, so a
+// process that drives several GPUs sets them up on each.  The caller's buffers and stream must
+// belong to the current device.
+constexpr int kMaxDevices = 64;
+template <typename T>
+struct PerDevice {
+  T v[kMaxDevices] = {};
+  T& here() { return v[current_device_slot()]; }
+};
 
 #define NGA_CHECK_LAUNCH()                              \
   do {                                                  \

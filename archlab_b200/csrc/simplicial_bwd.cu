@@ -869,7 +869,8 @@ extern "C" int nga_simplicial_bwd(const void* q, const void* k1, const void* k2,
   if (rc) return rc;
   rc = make_tmap_3d(&tv128, v2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, kvcols, rows, 1, ldv2 * 2, rows * ldv2 * 2, 64, 128, true);
   if (rc) return rc;
-  static bool attr_done = false;
+  static nga::PerDevice<bool> attr_flags;
+  bool& attr_done = attr_flags.here();
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(simplicial_bwd_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SimpBwdQSmem::kTotal);

@@ -465,7 +465,8 @@ extern "C" int nga_simplicial_fwd(const void* q, const void* k1, const void* k2,
   rc = make_tmap_3d(&tv, v2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)Hkv * D, rows, 1, ldv2 * 2,
                     rows * ldv2 * 2, 64, 128, true);
   if (rc) return rc;
-  static bool attr_done = false;
+  static nga::PerDevice<bool> attr_flags;
+  bool& attr_done = attr_flags.here();
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(simplicial_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SimpFwdSmem::kTotal);
@@ -513,7 +514,8 @@ extern "C" int nga_simplicial_decode(const void* q, const void* k1c, const void*
   rc = make_tmap_3d(&tv, v2c, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)Hkv * D, rows, 1, ldc * 2, rows * ldc * 2, 64, 128,
                     true);
   if (rc) return rc;
-  static bool attr_done = false;
+  static nga::PerDevice<bool> attr_flags;
+  bool& attr_done = attr_flags.here();
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(simplicial_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          SimpFwdSmem::kTotal);

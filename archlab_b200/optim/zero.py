@@ -9,6 +9,12 @@ which is the part of the reference's FSDP/distributed-optimizer arrangement that
 (src/archlab/megatron/qwen38_flash_next_config.py:216-221 enables the distributed optimizer with
 overlapped parameter gather).
 
+Gradients: with fp32 parameters (CPU tests) ``p.grad`` is a view of the flat gradient buffer.  With
+bf16 / fp16 parameters the flat gradient buffer is fp32 ("main grads"): a post-accumulate hook adds every
+micro-batch's low-precision ``p.grad`` into the fp32 view and drops it, so micro-batch accumulation, the
+tensor- / context-parallel all-reduces over replicated ranges and the data-parallel reduce-scatter all
+sum in fp32, and the gradient norm is taken from that sum (Megatron's bf16 path does the same).
+
 Parameters with two or more dimensions are decayed; they are laid out first so that a slice meets at
 most one boundary between decayed and undecayed ranges.
 """
@@ -22,7 +28,7 @@ from ..parallel import collectives as coll
 
 class ZeroAdamW:
     def __init__(self, params, *, lr: float, weight_decay: float = 0.0, betas=(0.9, 0.95), eps: float = 1e-8,
-                 group=None, align: int = 128):
+                 group=None, align: int = 128, main_grads_fp32: bool | None = None):
         params = [p for p in params if p.requires_grad]
         self.group = group
         self.world, self.rank = coll.world_size(group), coll.rank(group)
@@ -37,7 +43,11 @@ class ZeroAdamW:
         n_all = pad(n_dec + sum(p.numel() for p in plain), align * self.world)
         self.n_decayed, self.numel = n_dec, n_all
         self.flat_p = torch.zeros(n_all, dtype=dt, device=dev)
-        self.flat_g = torch.zeros(n_all, dtype=dt, device=dev)
+        if main_grads_fp32 is None:
+            main_grads_fp32 = dt in (torch.bfloat16, torch.float16)
+        self.main_grads = bool(main_grads_fp32) and dt != torch.float32
+        gdt = torch.float32 if self.main_grads else dt
+        self.flat_g = torch.zeros(n_all, dtype=gdt, device=dev)
         off = 0
         for i, p in enumerate(self.params):
             if i == len(decayed):
@@ -45,7 +55,11 @@ class ZeroAdamW:
             n = p.numel()
             self.flat_p[off:off + n].copy_(p.detach().reshape(-1))
             p.data = self.flat_p[off:off + n].view_as(p)
-            p.grad = self.flat_g[off:off + n].view_as(p)
+            if self.main_grads:
+                p.grad = None
+                p.register_post_accumulate_grad_hook(self._fold_into_main_grad(self.flat_g[off:off + n].view_as(p)))
+            else:
+                p.grad = self.flat_g[off:off + n].view_as(p)
             off += n
         self.shard = n_all // self.world
         lo = self.rank * self.shard
@@ -53,12 +67,23 @@ class ZeroAdamW:
         self.master = self.flat_p[lo:self.hi].float()
         self.m, self.v = torch.zeros_like(self.master), torch.zeros_like(self.master)
         self.g32 = torch.empty_like(self.master)
-        self.g_shard = torch.empty(self.shard, dtype=dt, device=dev)
+        self.g_shard = torch.empty(self.shard, dtype=gdt, device=dev)
         self.lr, self.wd, self.betas, self.eps, self.t = lr, weight_decay, betas, eps, 0
 
     # -- gradient pieces ---------------------------------------------------------------------------
+    @staticmethod
+    def _fold_into_main_grad(main):
+        def hook(param):
+            main.add_(param.grad)
+            param.grad = None
+        return hook
+
     def zero_grad(self) -> None:
         self.flat_g.zero_()
+        if self.main_grads:
+            for p in self.params:
+                p.grad = None
+            return
         for p in self.params:                                    # autograd may have replaced the views
             if p.grad is None or p.grad.data_ptr() != self._grad_ptr(p):
                 p.grad = self._grad_view(p)
