@@ -101,6 +101,29 @@ def bench_fp8(t: Timer, small: bool):
         _emit(f"fp8_gemm_{name}", ms, flops=2.0 * M * N * K, extra={"M": M, "N": N, "K": K})
 
 
+def bench_blockscaled(t: Timer, small: bool):
+    """Block-scaled GEMMs (scale factors in TMEM) and their quantisers; fractions are against the bf16 peak."""
+    from .ops import blockscaled as bs
+
+    cases = [("8192", 8192, 8192, 8192), ("fc_fwd", 32768, 5120, 1280), ("dgrad", 32768, 1280, 5120), ("moe_up", 16384, 2816, 2048)]
+    if small:
+        cases = [("small", 4096, 4096, 4096)]
+    for name, M, N, K in cases:
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        b = torch.randn(N, K, device="cuda").bfloat16()
+        qa, qb = bs.quantize_fp8(a, 128), bs.quantize_fp8(b, -128)
+        ms = t(lambda: bs.gemm(qa, qb))
+        _emit(f"mxfp8_gemm_{name}", ms, flops=2.0 * M * N * K, extra={"M": M, "N": N, "K": K, "scales": "1x128 / 128x128"})
+        ms = t(lambda: bs.quantize_fp8(a, 128))
+        _emit(f"mxfp8_quant_rows_{name}", ms, bytes_=3.0 * M * K)
+        fa, fb = bs.quantize_nvfp4(a), bs.quantize_nvfp4(b, two_d=True)
+        ms = t(lambda: bs.gemm(fa, fb))
+        _emit(f"nvfp4_gemm_{name}", ms, flops=2.0 * M * N * K, extra={"M": M, "N": N, "K": K})
+        amax = a.abs().amax().float()
+        ms = t(lambda: bs.quantize_nvfp4(a, hadamard_seed=3, sr_seed=5, amax=amax))
+        _emit(f"nvfp4_quant_rht_sr_{name}", ms, bytes_=2.5 * M * K)
+
+
 def bench_attention(t: Timer, small: bool):
     from .ops import trunk
 
@@ -176,14 +199,14 @@ def bench_trunk(t: Timer, small: bool):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="gemm", choices=["gemm", "fp8", "attention", "simplicial", "trunk", "delta", "all"])
+    ap.add_argument("--op", default="gemm", choices=["gemm", "fp8", "blockscaled", "attention", "simplicial", "trunk", "delta", "all"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
     from .ops import native
 
     t = Timer(a.iters)
-    ops = {"gemm": bench_gemm, "fp8": bench_fp8, "attention": bench_attention, "simplicial": bench_simplicial, "trunk": bench_trunk, "delta": bench_delta}
+    ops = {"gemm": bench_gemm, "fp8": bench_fp8, "blockscaled": bench_blockscaled, "attention": bench_attention, "simplicial": bench_simplicial, "trunk": bench_trunk, "delta": bench_delta}
     for name, fn in ops.items():
         if a.op in (name, "all"):
             fn(t, a.small)

@@ -1,0 +1,273 @@
+// Quantisers for the block-scaled GEMM operand format (see gemm_bs.h): bf16 -> fp8 + ue8m0 scales and
+// bf16 -> e2m1 + ue4m3 scales, written straight in the 512-byte chunk layout the tensor core's scale copy
+// expects.  Memory-bound elementwise kernels: every input byte is read once.
+#include <cuda_bf16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+#include "gemm_bs.h"
+#include "host_util.h"
+
+namespace nga {
+
+__device__ __forceinline__ long long sf_offset(long long r, long long sfi, long long chunks_k) {
+  const long long tile = r >> 7, chunk = sfi >> 2;
+  const int rr = int(r & 127);
+  return (tile * chunks_k + chunk) * 512 + (rr & 31) * 16 + (rr >> 5) * 4 + int(sfi & 3);
+}
+
+// power-of-two scale: smallest 2^e with amax / 2^e <= fmax; returns the biased ue8m0 byte and 2^-e
+__device__ __forceinline__ uint8_t pow2_scale(float amax, float fmax, float& inv) {
+  int e = 0;
+  if (amax > 0.f) {
+    e = int(ceilf(log2f(amax / fmax)));
+    // log2f may be off by an ulp at exact powers of two: make sure the block fits
+    if (ldexpf(fmax, e) < amax) ++e;
+    else if (ldexpf(fmax, e - 1) >= amax) --e;
+    e = max(-127, min(127, e));
+  }
+  inv = ldexpf(1.f, -e);
+  return uint8_t(e + 127);
+}
+
+// One warp per (row, 128-element segment); lane holds 4 consecutive elements.
+template <int BLOCK>
+__global__ void quant_mxfp8_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                                        long long rows, long long K, long long ldx, long long ldq, int e5m2) {
+  const long long segs = (K + 127) / 128;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= rows * segs) return;
+  const int lane = threadIdx.x & 31;
+  const long long r = w / segs, seg = w - r * segs;
+  const long long k0 = seg * 128 + lane * 4;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  if (k0 + 4 <= K) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(x + r * ldx + k0);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+  } else {
+    for (int i = 0; i < 4; ++i)
+      if (k0 + i < K) v[i] = __bfloat162float(x[r * ldx + k0 + i]);
+  }
+  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+  for (int o = 1; o < (BLOCK == 32 ? 8 : 32); o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  float inv;
+  const uint8_t sb = pow2_scale(amax, e5m2 ? 57344.f : 448.f, inv);
+  const __nv_fp8_interpretation_t kind = e5m2 ? __NV_E5M2 : __NV_E4M3;
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv, v[1] * inv), __NV_SATFINITE, kind);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv, v[3] * inv), __NV_SATFINITE, kind);
+  if (k0 + 4 <= K) {
+    *reinterpret_cast<uint32_t*>(q + r * ldq + k0) = lo | (hi << 16);
+  } else {
+    const uint32_t pk = lo | (hi << 16);
+    for (int i = 0; i < 4; ++i)
+      if (k0 + i < K) q[r * ldq + k0 + i] = uint8_t(pk >> (8 * i));
+  }
+  if ((lane & 7) == 0) sf[sf_offset(r, seg * 4 + (lane >> 3), segs)] = sb;
+}
+
+// One CTA (256 threads) per 128 x 128 block: block maximum, one power-of-two scale for the whole block.
+__global__ void quant_mxfp8_block128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                                            long long rows, long long K, long long ldx, long long ldq, int e5m2) {
+  __shared__ float red[8];
+  const long long segs = (K + 127) / 128;
+  const long long r0 = (long long)blockIdx.y * 128, k0 = (long long)blockIdx.x * 128;
+  const int tr = threadIdx.x >> 3, tc = (threadIdx.x & 7) * 16;      // 32 rows x 8 column groups per pass
+  float v[4][16];
+  float amax = 0.f;
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const long long r = r0 + pass * 32 + tr;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const long long k = k0 + tc + i;
+      v[pass][i] = (r < rows && k < K) ? __bfloat162float(x[r * ldx + k]) : 0.f;
+      amax = fmaxf(amax, fabsf(v[pass][i]));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+  float inv;
+  const uint8_t sb = pow2_scale(amax, e5m2 ? 57344.f : 448.f, inv);
+  const __nv_fp8_interpretation_t kind = e5m2 ? __NV_E5M2 : __NV_E4M3;
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const long long r = r0 + pass * 32 + tr;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const long long k = k0 + tc + i;
+      if (k < K) q[r * ldq + k] = uint8_t(__nv_cvt_float_to_fp8(v[pass][i] * inv, __NV_SATFINITE, kind));
+    }
+  }
+  // the chunk of this (row tile, k segment): all 512 bytes carry the block's scale
+  uint8_t* chunk = sf + ((long long)blockIdx.y * segs + blockIdx.x) * 512;
+  const uint32_t rep = 0x01010101u * sb;
+  if (threadIdx.x < 128) reinterpret_cast<uint32_t*>(chunk)[threadIdx.x] = rep;
+}
+
+__device__ __forceinline__ uint32_t hash_u32(uint32_t a, uint32_t b) {
+  uint32_t h = a * 0x9E3779B1u ^ (b + 0x7F4A7C15u + (a << 6) + (a >> 2));
+  h ^= h >> 16; h *= 0x85EBCA6Bu; h ^= h >> 13; h *= 0xC2B2AE35u; h ^= h >> 16;
+  return h;
+}
+
+// e2m1 code of |v| (v >= 0, already scaled), round to nearest even on the grid {0, .5, 1, 1.5, 2, 3, 4, 6}
+// or stochastically with a uniform u in [0, 1).
+__device__ __forceinline__ uint32_t e2m1_code(float v, bool stochastic, float u) {
+  const float grid[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  v = fminf(v, 6.f);
+  int lo = 0;
+#pragma unroll
+  for (int i = 1; i < 8; ++i) lo = v >= grid[i] ? i : lo;
+  if (lo == 7) return 7;
+  const float frac = (v - grid[lo]) / (grid[lo + 1] - grid[lo]);
+  if (stochastic) return uint32_t(lo + (u < frac ? 1 : 0));
+  if (frac > 0.5f) return uint32_t(lo + 1);
+  if (frac < 0.5f) return uint32_t(lo);
+  return uint32_t(lo + (lo & 1));               // tie: even mantissa
+}
+
+// Thread = one 16-element block of one row.  Lanes 0..15 of a half-warp hold 16 consecutive rows of the same block
+// column (so that the 16 x 16 mode reduces over them with shuffles).
+__global__ void quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                                   const float* __restrict__ amax_ptr, long long rows, long long K, long long ldx,
+                                   long long ldq, int two_d, uint32_t hseed, uint32_t sr_seed) {
+  const long long nblk = (K + 15) / 16, chunks_k = (nblk + 3) / 4;
+  const long long rgroups = (rows + 15) / 16;
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long grp = t >> 4;
+  const int rr = int(t & 15);
+  // threads past the end stay for the warp shuffles below (full mask) and store nothing
+  const bool in_range = grp < rgroups * nblk;
+  if (!in_range) grp = rgroups * nblk - 1;
+  const long long rg = grp / nblk, kb = grp - rg * nblk;
+  const long long r = rg * 16 + rr, k0 = kb * 16;
+  const bool live = in_range && r < rows;
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = 0.f;
+  if (live) {
+    if (k0 + 16 <= K) {
+      const uint4* src = reinterpret_cast<const uint4*>(x + r * ldx + k0);
+      const uint4 a = src[0], b = src[1];
+      const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+      const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 fa = __bfloat1622float2(ha[i]), fb = __bfloat1622float2(hb[i]);
+        v[2 * i] = fa.x; v[2 * i + 1] = fa.y; v[8 + 2 * i] = fb.x; v[8 + 2 * i + 1] = fb.y;
+      }
+    } else {
+      for (int i = 0; i < 16; ++i)
+        if (k0 + i < K) v[i] = __bfloat162float(x[r * ldx + k0 + i]);
+    }
+  }
+  if (hseed != 0u) {
+    // y = H (d * v) / 4 with d a fixed random sign vector: orthogonal, so applying it to both operands of a
+    // product over K leaves the product unchanged while spreading outliers over the block
+    const uint32_t signs = hash_u32(hseed, 0x5EEDu);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = (signs >> i) & 1u ? -v[i] : v[i];
+#pragma unroll
+    for (int s = 1; s < 16; s <<= 1)
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if ((i & s) == 0) {
+          const float a = v[i], b = v[i | s];
+          v[i] = a + b;
+          v[i | s] = a - b;
+        }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] *= 0.25f;
+  }
+  float bmax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(v[i]));
+  if (two_d) {
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
+  }
+  const float tmax = *amax_ptr;
+  const float s_enc = tmax > 0.f ? 2688.f / tmax : 1.f;               // 448 * 6 / amax
+  // block decode scale in e4m3 (round to nearest, saturating), then the encode factor that matches it exactly
+  const __nv_fp8_storage_t sbyte = __nv_cvt_float_to_fp8(bmax / 6.f * s_enc, __NV_SATFINITE, __NV_E4M3);
+  const float sdec = __half2float(__half(__nv_cvt_fp8_to_halfraw(sbyte, __NV_E4M3)));
+  const float enc = sdec > 0.f ? s_enc / sdec : 0.f;
+  if (!live) return;
+  uint32_t words[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float a = v[i] * enc;
+    float u = 0.f;
+    if (sr_seed != 0u) u = float(hash_u32(sr_seed, uint32_t(r * K + k0 + i)) >> 8) * (1.f / 16777216.f);
+    const uint32_t code = e2m1_code(fabsf(a), sr_seed != 0u, u) | (a < 0.f ? 8u : 0u);
+    words[i >> 3] |= code << (4 * (i & 7));
+  }
+  if (k0 + 16 <= K) {
+    *reinterpret_cast<uint2*>(q + r * ldq + k0 / 2) = make_uint2(words[0], words[1]);
+  } else {
+    for (int i = 0; i < 16 && k0 + i < K; i += 2)
+      q[r * ldq + (k0 + i) / 2] = uint8_t((words[i >> 3] >> (4 * (i & 7))) & 0xFFu);
+  }
+  sf[sf_offset(r, kb, chunks_k)] = sbyte;
+}
+
+}  // namespace nga
+
+extern "C" long long nga_sf_bytes(int kind, long long rows, long long K) {
+  const long long per_chunk = kind == 1 ? 128 : 64;
+  const long long kblock = kind == 1 ? 128 : 256;               // the GEMM loads whole k-blocks of chunks
+  const long long chunks_k = ((K + kblock - 1) / kblock) * (kblock / per_chunk);
+  return ((rows + 127) / 128) * chunks_k * 512;
+}
+
+extern "C" int nga_quant_mxfp8(const void* x, void* q, void* sf, long long rows, long long K, long long ldx, long long ldq_bytes,
+                               int block, int e5m2, void* stream) {
+  using namespace nga;
+  if (rows <= 0 || K <= 0 || x == nullptr || q == nullptr || sf == nullptr) return -1;
+  if ((ldx & 3) || (ldq_bytes & 3) || (reinterpret_cast<uintptr_t>(x) & 7) || (reinterpret_cast<uintptr_t>(q) & 3)) return -5;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const long long segs = (K + 127) / 128;
+  auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto qb = reinterpret_cast<uint8_t*>(q);
+  auto sb = reinterpret_cast<uint8_t*>(sf);
+  if (block == -128) {
+    dim3 grid((unsigned)segs, (unsigned)((rows + 127) / 128));
+    quant_mxfp8_block128_kernel<<<grid, 256, 0, st>>>(xb, qb, sb, rows, K, ldx, ldq_bytes, e5m2);
+  } else if (block == 32 || block == 128) {
+    const long long warps = rows * segs;
+    const unsigned blocks = (unsigned)((warps + 7) / 8);
+    if (block == 32) quant_mxfp8_rows_kernel<32><<<blocks, 256, 0, st>>>(xb, qb, sb, rows, K, ldx, ldq_bytes, e5m2);
+    else quant_mxfp8_rows_kernel<128><<<blocks, 256, 0, st>>>(xb, qb, sb, rows, K, ldx, ldq_bytes, e5m2);
+  } else {
+    return -2;
+  }
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int nga_quant_nvfp4(const void* x, void* q, void* sf, const float* amax, long long rows, long long K, long long ldx,
+                               long long ldq_bytes, int two_d, unsigned hadamard_seed, unsigned sr_seed, void* stream) {
+  using namespace nga;
+  if (rows <= 0 || K <= 0 || x == nullptr || q == nullptr || sf == nullptr || amax == nullptr) return -1;
+  if ((K & 1) || (ldx & 7) || (ldq_bytes & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 7))
+    return -5;
+  if (two_d && (rows & 15)) return -2;
+  const long long nblk = (K + 15) / 16, rgroups = (rows + 15) / 16;
+  const long long threads = rgroups * nblk * 16;
+  quant_nvfp4_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<uint8_t*>(q), reinterpret_cast<uint8_t*>(sf), amax, rows, K,
+      ldx, ldq_bytes, two_d, hadamard_seed, sr_seed);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}
