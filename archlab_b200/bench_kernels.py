@@ -141,6 +141,27 @@ def bench_attention(t: Timer, small: bool):
         _emit(f"attn_bwd_B{B}_T{T}_w{window}", ms, flops=10.0 * D * pairs)
 
 
+def simplicial_headline(iters: int = 5) -> dict:
+    """2-simplicial attention forward + backward at the headline shape (one sequence of 8192, 16 query / 4 KV heads
+    of 128, windows 32 x 512): TFLOP/s over the useful (query, short key, long key) triples."""
+    from .ops.simplicial_bwd import simplicial_bwd
+    from .ops.simplicial_cuda import simplicial_fwd
+
+    B, N, Hq, Hkv, w1, w2, D = 1, 8192, 16, 4, 32, 512, 128
+    t = Timer(iters)
+    mk = lambda H: (torch.randn(B, N, H, D, device="cuda") * 0.7).bfloat16()
+    q, k1, k2, v1, v2 = mk(Hq), mk(Hkv), mk(Hkv), mk(Hkv), mk(Hkv)
+    dout = (torch.randn(B, N, Hq, D, device="cuda") * 0.3).bfloat16()
+    i = torch.arange(N, dtype=torch.float64)
+    triples = float((torch.clamp(i + 1, max=w1) * torch.clamp(i + 1, max=w2)).sum()) * B * Hq
+    out, lse2 = simplicial_fwd(q, k1, k2, v1, v2, w1, w2, D ** -0.5)
+    ms_f = t(lambda: simplicial_fwd(q, k1, k2, v1, v2, w1, w2, D ** -0.5))
+    ms_b = t(lambda: simplicial_bwd(q, k1, k2, v1, v2, out, dout, lse2, w1, w2, D ** -0.5))
+    return {"simplicial_fwd_bwd_tflops": round(14.0 * D * triples / (ms_f + ms_b) / 1e9, 1),
+            "simplicial_fwd_ms": round(ms_f, 3), "simplicial_bwd_ms": round(ms_b, 3),
+            "simplicial_shape": f"N{N} H{Hq}/{Hkv} D{D} windows {w1}x{w2}, bf16, L2 flushed between iterations"}
+
+
 def bench_simplicial(t: Timer, small: bool):
     from .ops.simplicial_bwd import simplicial_bwd
     from .ops.simplicial_cuda import simplicial_fwd

@@ -17,8 +17,10 @@
 // k-blocks (128 fp8 or 256 fp4 elements), each CTA stages its 128 rows of A, its half of B, the scale
 // chunks of its A rows and those of all 256 B rows; every load completes on the leader's barrier.  TMEM
 // holds ONE 256-column accumulator plus the scale columns (512 columns cannot hold two accumulators and
-// scales), so the epilogue of a tile does not overlap the next tile's main loop; the TMA producer keeps
-// prefetching meanwhile.  All waits are bounded.
+// scales).  The plain epilogues (scale, ReLU^2 to bf16) therefore pull the accumulator into registers as
+// packed bf16, hand TMEM back to the MMA warp at once and only then stage and store the tile, so that
+// all but the TMEM reads overlaps the next tile's main loop; epilogues with an aux operand release TMEM
+// after their stores.  The TMA producer prefetches throughout.  All waits are bounded.
 #include <cstdlib>
 #include "gemm_common.cuh"
 #include "pair_ptx.cuh"
@@ -29,13 +31,13 @@
 namespace nga {
 
 constexpr int BS_BN = 256;
-constexpr int BS_STAGES = 5;
+constexpr int BS_STAGES = 4;
 constexpr int BS_TILE_BYTES = 16384;                       // 128 rows x 128 bytes
 constexpr int BS_SFA_OFF = 2 * BS_TILE_BYTES;              // scale chunks of this CTA's A rows (up to 4)
 constexpr int BS_SFB_OFF = BS_SFA_OFF + 2048;              // scale chunks of the 256 B rows ([half][chunk])
 constexpr int BS_STAGE_BYTES = BS_SFB_OFF + 4096;          // 38912 = 38 KB
 constexpr int BS_OUT_OFFSET = BS_STAGES * BS_STAGE_BYTES;
-constexpr int BS_OUT_BYTES = 8 * 4096;
+constexpr int BS_OUT_BYTES = 16 * 4096;                    // 8 epilogue warps x two 32 x 64 bf16 staging tiles
 constexpr int BS_BAR_OFFSET = BS_OUT_OFFSET + BS_OUT_BYTES;
 constexpr int BS_SMEM = BS_BAR_OFFSET + (2 * BS_STAGES + 2) * 8 + 16 + 1024;
 constexpr int BS_THREADS = 320;                            // TMA warp, MMA warp, 8 epilogue warps
@@ -82,6 +84,17 @@ __device__ __forceinline__ void umma2_nvf4_ss(uint32_t tmem_d, uint64_t da, uint
 __device__ __forceinline__ uint32_t umma_idesc_bs(int m, int n, int a_fmt, int b_fmt, int ue8m0, int a_sf, int b_sf) {
   return (uint32_t(b_sf & 3) << 4) | (uint32_t(a_fmt & 7) << 7) | (uint32_t(b_fmt & 7) << 10) |
          (uint32_t(n >> 3) << 17) | (uint32_t(ue8m0 & 1) << 23) | (uint32_t(m >> 4) << 24) | (uint32_t(a_sf & 3) << 29);
+}
+
+// Epilogue arithmetic on one 64-column piece of an accumulator row, packed to bf16 pairs (register i = columns 2i, 2i+1).
+template <int EPI>
+__device__ __forceinline__ void pack_piece(const uint32_t (&r)[2][32], uint32_t (&pk)[32], float alpha) {
+#pragma unroll
+  for (int hc = 0; hc < 2; ++hc)
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      pk[hc * 16 + i] = pack_bf16(epi_apply<EPI>(__uint_as_float(r[hc][2 * i]), 0.f, alpha, 0.f),
+                                  epi_apply<EPI>(__uint_as_float(r[hc][2 * i + 1]), 0.f, alpha, 0.f));
 }
 
 struct BsExtra {
@@ -227,6 +240,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const bool vec_ok = epilogue_vec_ok(p);
     const bool need_aux = (p.epi == kEpiAxpby || p.epi == kEpiMulDRelu2);
     const bool aux_fast = aux_prefetchable(p);
+    const bool fast_epi = p.tma_store && (p.epi == kEpiScale || p.epi == kEpiRelu2);
     GemmParams pe = p;
     if (x.amax_a != nullptr) { const float a = *x.amax_a; pe.alpha *= a > 0.f ? a * (1.f / 2688.f) : 1.f; }
     if (x.amax_b != nullptr) { const float a = *x.amax_b; pe.alpha *= a > 0.f ? a * (1.f / 2688.f) : 1.f; }
@@ -240,6 +254,45 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16);
+      if (fast_epi) {
+        // accumulator -> packed bf16 in registers, TMEM handed back, then staging + TMA stores
+        uint32_t pk[2][32];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          uint32_t r2[2][32];
+          tmem_ld_32x32(taddr + uint32_t((chalf * 2 + j) * 64), r2[0]);
+          tmem_ld_32x32(taddr + uint32_t((chalf * 2 + j) * 64 + 32), r2[1]);
+          tmem_ld_wait();
+          if (pe.epi == kEpiRelu2) pack_piece<kEpiRelu2>(r2, pk[j], pe.alpha);
+          else pack_piece<kEpiScale>(r2, pk[j], pe.alpha);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(tempty_bar), 0));
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int col0 = nb * BS_BN + (chalf * 2 + j) * 64;
+          if (col0 >= p.N) {        // warp-uniform; an empty group keeps the two-groups-per-tile cadence the wait counts on
+            if (lane == 0) tma_store_commit();
+            continue;
+          }
+          uint8_t* buf = smem + BS_OUT_OFFSET + ((chalf * 4 + quarter) * 2 + j) * 4096;
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the store that last read this tile
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<uint4*>(buf + lane * 128 + ((q ^ (lane & 7)) * 16)) =
+                make_uint4(pk[j][4 * q], pk[j][4 * q + 1], pk[j][4 * q + 2], pk[j][4 * q + 3]);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_3d(&tmD, buf, col0, mb * 2 * BM + int(rank) * BM + quarter * 32, 0);
+            tma_store_commit();
+          }
+        }
+        acc_phase ^= 1u;
+        continue;
+      }
 #pragma unroll 1
       for (int c2 = chalf * 2; c2 < chalf * 2 + 2; ++c2) {
         const int col0 = nb * BS_BN + c2 * 64;

@@ -35,7 +35,8 @@ __device__ __forceinline__ int ld_acquire_sys(const int* addr) {
 
 // Each rank writes `epoch` into slot [rank] of every peer's flag array, then waits until all slots
 // of its own array have reached `epoch`.  One block, `world` active threads.
-__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, int* status) {
+__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, int* status,
+                                    unsigned long long budget_ns) {
   const int t = threadIdx.x;
   __threadfence_system();
   if (t < world) {
@@ -44,7 +45,7 @@ __global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int epo
     const unsigned long long t0 = globaltimer_ns();
     unsigned it = 0;
     while (ld_acquire_sys(mine) < epoch) {
-      if ((++it & 255u) == 0u && globaltimer_ns() - t0 > kWaitBudgetNs) {
+      if ((++it & 255u) == 0u && globaltimer_ns() - t0 > budget_ns) {
         atomicCAS(status, 0, kErrPeerTimeout);
         break;
       }
@@ -183,10 +184,17 @@ static PeerPtrs make_ptrs(const long long* host_ptrs, int world) {
 using namespace nga;
 #define ST(s) reinterpret_cast<cudaStream_t>(s)
 
+// How long a kernel waits for a flag another GPU writes before it gives up and reports kErrPeerTimeout through the
+// status word (default 2 s).  A launch parameter, so a health check or a test can ask for a short wait.
+static unsigned long long g_peer_wait_budget_ns = kWaitBudgetNs;
+extern "C" void nga_set_peer_wait_budget_ns(unsigned long long ns) { g_peer_wait_budget_ns = ns ? ns : kWaitBudgetNs; }
+extern "C" unsigned long long nga_peer_wait_budget_ns(void) { return g_peer_wait_budget_ns; }
+
 extern "C" int nga_peer_barrier(const long long* flag_ptrs, int rank, int world, int epoch, int* status,
                                 void* stream) {
   if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) return -1;
-  peer_barrier_kernel<<<1, 32, 0, ST(stream)>>>(make_ptrs(flag_ptrs, world), rank, world, epoch, status);
+  peer_barrier_kernel<<<1, 32, 0, ST(stream)>>>(make_ptrs(flag_ptrs, world), rank, world, epoch, status,
+                                                g_peer_wait_budget_ns);
   count_launch();
   NGA_CHECK_LAUNCH();
   return 0;

@@ -5,6 +5,10 @@
 extern "C" {
 #endif
 int nga_peer_barrier(const long long* flag_ptrs, int rank, int world, int epoch, int* status, void* stream);
+// Budget of the barrier's wait for the other ranks' flags (nanoseconds; 0 restores the 2 s default).  When it runs
+// out the kernel returns and the status word reads 2; nothing hangs and the context stays usable.
+void nga_set_peer_wait_budget_ns(unsigned long long ns);
+unsigned long long nga_peer_wait_budget_ns(void);
 int nga_peer_adamw(const long long* grad_ptrs, const long long* shadow_ptrs, float* p, float* m, float* v,
                    long long e0, long long n, int world, float lr, float beta1, float beta2, float eps, float wd,
                    int step, int cautious, void* stream);

@@ -30,42 +30,57 @@ __device__ __forceinline__ uint8_t pow2_scale(float amax, float fmax, float& inv
   return uint8_t(e + 127);
 }
 
-// One warp per (row, 128-element segment); lane holds 4 consecutive elements.
+// One warp per (row, 256-element span); a lane holds 8 consecutive elements (16-byte load, 8-byte store), so a
+// 32-element scale block is 4 lanes and a 128-element one 16 lanes.
 template <int BLOCK>
 __global__ void quant_mxfp8_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
                                         long long rows, long long K, long long ldx, long long ldq, int e5m2) {
-  const long long segs = (K + 127) / 128;
+  const long long segs = (K + 127) / 128, spans = (K + 255) / 256;
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (w >= rows * segs) return;
+  if (w >= rows * spans) return;                                   // warp-uniform
   const int lane = threadIdx.x & 31;
-  const long long r = w / segs, seg = w - r * segs;
-  const long long k0 = seg * 128 + lane * 4;
-  float v[4] = {0.f, 0.f, 0.f, 0.f};
-  if (k0 + 4 <= K) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(x + r * ldx + k0);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
-    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-  } else {
-    for (int i = 0; i < 4; ++i)
-      if (k0 + i < K) v[i] = __bfloat162float(x[r * ldx + k0 + i]);
-  }
-  float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+  const long long r = w / spans, sp = w - r * spans;
+  const long long k0 = sp * 256 + lane * 8;
+  float v[8];
 #pragma unroll
-  for (int o = 1; o < (BLOCK == 32 ? 8 : 32); o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  for (int i = 0; i < 8; ++i) v[i] = 0.f;
+  const __nv_bfloat16* src = x + r * ldx + k0;
+  if (k0 + 8 <= K && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  } else {
+    for (int i = 0; i < 8; ++i)
+      if (k0 + i < K) v[i] = __bfloat162float(src[i]);
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+  for (int o = 1; o < BLOCK / 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   float inv;
   const uint8_t sb = pow2_scale(amax, e5m2 ? 57344.f : 448.f, inv);
   const __nv_fp8_interpretation_t kind = e5m2 ? __NV_E5M2 : __NV_E4M3;
-  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv, v[1] * inv), __NV_SATFINITE, kind);
-  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv, v[3] * inv), __NV_SATFINITE, kind);
-  if (k0 + 4 <= K) {
-    *reinterpret_cast<uint32_t*>(q + r * ldq + k0) = lo | (hi << 16);
-  } else {
-    const uint32_t pk = lo | (hi << 16);
-    for (int i = 0; i < 4; ++i)
-      if (k0 + i < K) q[r * ldq + k0 + i] = uint8_t(pk >> (8 * i));
+  uint32_t pk[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * h] * inv, v[4 * h + 1] * inv), __NV_SATFINITE, kind);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * h + 2] * inv, v[4 * h + 3] * inv), __NV_SATFINITE, kind);
+    pk[h] = lo | (hi << 16);
   }
-  if ((lane & 7) == 0) sf[sf_offset(r, seg * 4 + (lane >> 3), segs)] = sb;
+  uint8_t* dst = q + r * ldq + k0;
+  if (k0 + 8 <= K && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+    *reinterpret_cast<uint2*>(dst) = make_uint2(pk[0], pk[1]);
+  } else {
+    for (int i = 0; i < 8; ++i)
+      if (k0 + i < K) dst[i] = uint8_t(pk[i >> 2] >> (8 * (i & 3)));
+  }
+  if ((lane & 3) == 0 && k0 < segs * 128) sf[sf_offset(r, k0 >> 5, segs)] = sb;
 }
 
 // One CTA (256 threads) per 128 x 128 block: block maximum, one power-of-two scale for the whole block.
@@ -119,45 +134,55 @@ __device__ __forceinline__ uint32_t hash_u32(uint32_t a, uint32_t b) {
   return h;
 }
 
-// e2m1 code of |v| (v >= 0, already scaled), round to nearest even on the grid {0, .5, 1, 1.5, 2, 3, 4, 6}
-// or stochastically with a uniform u in [0, 1).
-__device__ __forceinline__ uint32_t e2m1_code(float v, bool stochastic, float u) {
-  const float grid[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
-  v = fminf(v, 6.f);
-  int lo = 0;
-#pragma unroll
-  for (int i = 1; i < 8; ++i) lo = v >= grid[i] ? i : lo;
-  if (lo == 7) return 7;
-  const float frac = (v - grid[lo]) / (grid[lo + 1] - grid[lo]);
-  if (stochastic) return uint32_t(lo + (u < frac ? 1 : 0));
-  if (frac > 0.5f) return uint32_t(lo + 1);
-  if (frac < 0.5f) return uint32_t(lo);
-  return uint32_t(lo + (lo & 1));               // tie: even mantissa
+// Two scaled values -> one byte of e2m1 codes (first value in the low nibble), round to nearest even in hardware.
+__device__ __forceinline__ uint32_t e2m1_pair(float a, float b) {
+  return uint32_t(__nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest)) & 0xFFu;
+}
+// Stochastic rounding onto the e2m1 grid {0, .5, 1, 1.5, 2, 3, 4, 6}: the grid step is .5 below 2, 1 below 4, 2
+// above; floor(|a| / step + u) * step with u uniform in [0, 1) lands on a grid point and is unbiased.
+__device__ __forceinline__ float e2m1_stochastic(float a, float u) {
+  const float m = fminf(fabsf(a), 6.f);
+  const float step = m < 2.f ? 0.5f : (m < 4.f ? 1.f : 2.f);
+  const float qv = fminf(floorf(__fmaf_rn(m, 1.f / step, u)) * step, 6.f);
+  return copysignf(qv, a);
 }
 
-// Thread = one 16-element block of one row.  Lanes 0..15 of a half-warp hold 16 consecutive rows of the same block
-// column (so that the 16 x 16 mode reduces over them with shuffles).
+// Thread = one 16-element block of one row.  Row mode: consecutive lanes take consecutive blocks of a row (coalesced).
+// 16 x 16 mode: the 16 lanes of a half-warp hold 16 consecutive rows of one block column and share their maximum
+// through shuffles.
+template <int TWO_D>
 __global__ void quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
                                    const float* __restrict__ amax_ptr, long long rows, long long K, long long ldx,
-                                   long long ldq, int two_d, uint32_t hseed, uint32_t sr_seed) {
-  const long long nblk = (K + 15) / 16, chunks_k = (nblk + 3) / 4;
-  const long long rgroups = (rows + 15) / 16;
+                                   long long ldq, uint32_t hseed, uint32_t sr_seed) {
+  const long long nblk = (K + 15) / 16;
+  const long long chunks_k = ((K + 255) / 256) * 4;      // whole k-blocks of four chunks, as the GEMM loads them
   const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  long long grp = t >> 4;
-  const int rr = int(t & 15);
-  // threads past the end stay for the warp shuffles below (full mask) and store nothing
-  const bool in_range = grp < rgroups * nblk;
-  if (!in_range) grp = rgroups * nblk - 1;
-  const long long rg = grp / nblk, kb = grp - rg * nblk;
-  const long long r = rg * 16 + rr, k0 = kb * 16;
-  const bool live = in_range && r < rows;
+  long long r, kb;
+  bool live;
+  if (TWO_D) {
+    const long long rgroups = (rows + 15) / 16;
+    long long grp = t >> 4;
+    // threads past the end stay for the warp shuffles below (full mask) and store nothing
+    const bool in_range = grp < rgroups * nblk;
+    if (!in_range) grp = rgroups * nblk - 1;
+    const long long rg = grp / nblk;
+    kb = grp - rg * nblk;
+    r = rg * 16 + (t & 15);
+    live = in_range && r < rows;
+  } else {
+    r = t / nblk;
+    kb = t - r * nblk;
+    live = r < rows;
+    if (!live) return;
+  }
+  const long long k0 = kb * 16;
   float v[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = 0.f;
   if (live) {
-    if (k0 + 16 <= K) {
-      const uint4* src = reinterpret_cast<const uint4*>(x + r * ldx + k0);
-      const uint4 a = src[0], b = src[1];
+    const __nv_bfloat16* src = x + r * ldx + k0;
+    if (k0 + 16 <= K && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+      const uint4 a = __ldg(reinterpret_cast<const uint4*>(src)), b = __ldg(reinterpret_cast<const uint4*>(src) + 1);
       const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
       const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
 #pragma unroll
@@ -167,7 +192,7 @@ __global__ void quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, uint8_t*
       }
     } else {
       for (int i = 0; i < 16; ++i)
-        if (k0 + i < K) v[i] = __bfloat162float(x[r * ldx + k0 + i]);
+        if (k0 + i < K) v[i] = __bfloat162float(src[i]);
     }
   }
   if (hseed != 0u) {
@@ -191,7 +216,7 @@ __global__ void quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, uint8_t*
   float bmax = 0.f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(v[i]));
-  if (two_d) {
+  if (TWO_D) {
 #pragma unroll
     for (int o = 1; o < 16; o <<= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
   }
@@ -204,18 +229,20 @@ __global__ void quant_nvfp4_kernel(const __nv_bfloat16* __restrict__ x, uint8_t*
   if (!live) return;
   uint32_t words[2] = {0u, 0u};
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float a = v[i] * enc;
-    float u = 0.f;
-    if (sr_seed != 0u) u = float(hash_u32(sr_seed, uint32_t(r * K + k0 + i)) >> 8) * (1.f / 16777216.f);
-    const uint32_t code = e2m1_code(fabsf(a), sr_seed != 0u, u) | (a < 0.f ? 8u : 0u);
-    words[i >> 3] |= code << (4 * (i & 7));
+  for (int i = 0; i < 16; i += 2) {
+    float a = __fmul_rn(v[i], enc), b = __fmul_rn(v[i + 1], enc);
+    if (sr_seed != 0u) {
+      const uint32_t h = hash_u32(sr_seed, uint32_t(r * K + k0 + i));
+      a = e2m1_stochastic(a, float(h >> 16) * (1.f / 65536.f));
+      b = e2m1_stochastic(b, float(h & 0xFFFFu) * (1.f / 65536.f));
+    }
+    words[i >> 3] |= e2m1_pair(a, b) << (4 * (i & 7));
   }
-  if (k0 + 16 <= K) {
-    *reinterpret_cast<uint2*>(q + r * ldq + k0 / 2) = make_uint2(words[0], words[1]);
+  uint8_t* dst = q + r * ldq + k0 / 2;
+  if (k0 + 16 <= K && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+    *reinterpret_cast<uint2*>(dst) = make_uint2(words[0], words[1]);
   } else {
-    for (int i = 0; i < 16 && k0 + i < K; i += 2)
-      q[r * ldq + (k0 + i) / 2] = uint8_t((words[i >> 3] >> (4 * (i & 7))) & 0xFFu);
+    for (int i = 0; i < 16 && k0 + i < K; i += 2) dst[i / 2] = uint8_t((words[i >> 3] >> (4 * (i & 7))) & 0xFFu);
   }
   sf[sf_offset(r, kb, chunks_k)] = sbyte;
 }
@@ -233,7 +260,7 @@ extern "C" int nga_quant_mxfp8(const void* x, void* q, void* sf, long long rows,
                                int block, int e5m2, void* stream) {
   using namespace nga;
   if (rows <= 0 || K <= 0 || x == nullptr || q == nullptr || sf == nullptr) return -1;
-  if ((ldx & 3) || (ldq_bytes & 3) || (reinterpret_cast<uintptr_t>(x) & 7) || (reinterpret_cast<uintptr_t>(q) & 3)) return -5;
+  if (ldx < K || ldq_bytes < K) return -5;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const long long segs = (K + 127) / 128;
   auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
@@ -243,7 +270,7 @@ extern "C" int nga_quant_mxfp8(const void* x, void* q, void* sf, long long rows,
     dim3 grid((unsigned)segs, (unsigned)((rows + 127) / 128));
     quant_mxfp8_block128_kernel<<<grid, 256, 0, st>>>(xb, qb, sb, rows, K, ldx, ldq_bytes, e5m2);
   } else if (block == 32 || block == 128) {
-    const long long warps = rows * segs;
+    const long long warps = rows * ((K + 255) / 256);
     const unsigned blocks = (unsigned)((warps + 7) / 8);
     if (block == 32) quant_mxfp8_rows_kernel<32><<<blocks, 256, 0, st>>>(xb, qb, sb, rows, K, ldx, ldq_bytes, e5m2);
     else quant_mxfp8_rows_kernel<128><<<blocks, 256, 0, st>>>(xb, qb, sb, rows, K, ldx, ldq_bytes, e5m2);
@@ -259,14 +286,22 @@ extern "C" int nga_quant_nvfp4(const void* x, void* q, void* sf, const float* am
                                long long ldq_bytes, int two_d, unsigned hadamard_seed, unsigned sr_seed, void* stream) {
   using namespace nga;
   if (rows <= 0 || K <= 0 || x == nullptr || q == nullptr || sf == nullptr || amax == nullptr) return -1;
-  if ((K & 1) || (ldx & 7) || (ldq_bytes & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(q) & 7))
-    return -5;
+  if ((K & 1) || ldx < K || ldq_bytes * 2 < K) return -5;
   if (two_d && (rows & 15)) return -2;
   const long long nblk = (K + 15) / 16, rgroups = (rows + 15) / 16;
-  const long long threads = rgroups * nblk * 16;
-  quant_nvfp4_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<uint8_t*>(q), reinterpret_cast<uint8_t*>(sf), amax, rows, K,
-      ldx, ldq_bytes, two_d, hadamard_seed, sr_seed);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto qb = reinterpret_cast<uint8_t*>(q);
+  auto sb = reinterpret_cast<uint8_t*>(sf);
+  if (two_d) {
+    const long long threads = rgroups * nblk * 16;
+    quant_nvfp4_kernel<1><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(xb, qb, sb, amax, rows, K, ldx, ldq_bytes,
+                                                                             hadamard_seed, sr_seed);
+  } else {
+    const long long threads = rows * nblk;
+    quant_nvfp4_kernel<0><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(xb, qb, sb, amax, rows, K, ldx, ldq_bytes,
+                                                                             hadamard_seed, sr_seed);
+  }
   count_launch();
   NGA_CHECK_LAUNCH();
   return 0;

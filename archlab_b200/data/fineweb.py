@@ -1,14 +1,21 @@
 """FineWeb ``.bin`` token shards (llm.c / modded-nanogpt format) with deterministic rank slicing.
 
-File format: 256 int32 header words (magic 20240520, version 1, token count), then uint16 tokens.
-One global batch is one contiguous token range split into equal rank-local ranges; each range
-carries one extra trailing token so labels are the inputs shifted by one.  ``seek_batch(i)``
-reaches an exact distributed-batch cursor without reading payloads, which is how a resumed run
-derives its data position from the restored iteration.  Behaviour follows
-src/archlab/fineweb.py:16-246.
+File format (fixed by the published shards): 256 int32 header words (magic 20240520, version 1, token count),
+then uint16 tokens.  Batch geometry (fixed by the reference's loader, src/archlab/fineweb.py:96-246, because a
+resumed run must land on the same tokens): one distributed batch is one contiguous range of
+``world x local_batch x T`` tokens inside a shard, cut into equal rank-local ranges, each read with one extra
+trailing token so that labels are the inputs shifted by one; a shard is left as soon as it cannot supply a
+whole distributed batch plus that one token, and the shard list wraps around.
+
+Structure here: a ``ShardTable`` is built once from the headers (token count and number of whole batches per
+shard, prefix sums over an epoch).  A batch index maps to (shard, offset) in closed form, so ``seek_batch`` touches
+no payload and no shard in between, and the loader itself is a cursor over that table holding one memory map.
 """
 from __future__ import annotations
 
+import bisect
+import struct
+from dataclasses import dataclass
 from pathlib import Path
 
 import numpy as np
@@ -18,136 +25,159 @@ HEADER_INTS = 256
 HEADER_BYTES = HEADER_INTS * 4
 MAGIC = 20_240_520
 VERSION = 1
+TRAIN_SHARDS = 103                       # the complete published inventory: fineweb_train_000001 .. 000103
 
 
-def write_fineweb_shard(path: str | Path, tokens: np.ndarray) -> None:
+def write_fineweb_shard(path: str | Path, tokens) -> None:
     """Writer for tests and synthetic corpora."""
-    tokens = np.asarray(tokens, dtype=np.uint16)
-    header = np.zeros(HEADER_INTS, dtype=np.int32)
-    header[0], header[1], header[2] = MAGIC, VERSION, tokens.size
-    with Path(path).open("wb") as f:
-        f.write(header.tobytes())
-        f.write(tokens.tobytes())
+    payload = np.ascontiguousarray(tokens, dtype=np.uint16)
+    head = struct.pack("<3i", MAGIC, VERSION, payload.size) + bytes(HEADER_BYTES - 12)
+    Path(path).write_bytes(head + payload.tobytes())
 
 
-def inspect_fineweb_shard(path: Path) -> int:
-    with Path(path).open("rb") as f:
-        raw = f.read(HEADER_BYTES)
-    if len(raw) != HEADER_BYTES:
-        raise ValueError(f"truncated FineWeb header: {path}")
-    header = np.frombuffer(raw, dtype=np.int32)
-    if int(header[0]) != MAGIC:
-        raise ValueError(f"FineWeb magic mismatch in {path}")
-    if int(header[1]) != VERSION:
-        raise ValueError(f"unsupported FineWeb shard version in {path}: {int(header[1])}")
-    n = int(header[2])
-    if Path(path).stat().st_size != HEADER_BYTES + 2 * n:
-        raise ValueError(f"FineWeb shard length mismatch in {path}: {Path(path).stat().st_size} != {HEADER_BYTES + 2 * n}")
-    return n
+def inspect_fineweb_shard(path) -> int:
+    """Token count of a shard after checking header and file length."""
+    path = Path(path)
+    with path.open("rb") as f:
+        head = f.read(HEADER_BYTES)
+    if len(head) < HEADER_BYTES:
+        raise ValueError(f"{path}: header is shorter than {HEADER_BYTES} bytes")
+    magic, version, count = struct.unpack_from("<3i", head)
+    problems = []
+    if magic != MAGIC:
+        problems.append(f"magic {magic} != {MAGIC}")
+    elif version != VERSION:
+        problems.append(f"version {version} is not supported")
+    elif path.stat().st_size != HEADER_BYTES + 2 * count:
+        problems.append(f"length {path.stat().st_size} does not match {count} tokens")
+    if problems:
+        raise ValueError(f"{path}: {problems[0]}")
+    return count
 
 
-def inspect_fineweb_dataset(root, *, expected_train_shards: int = 103, required_train_tokens: int | None = None) -> dict:
+def _shard_number(path: Path) -> int:
+    return int(path.stem.rsplit("_", 1)[1])
+
+
+def inspect_fineweb_dataset(root, *, expected_train_shards: int = TRAIN_SHARDS, required_train_tokens: int | None = None) -> dict:
+    """Inventory check before a run.  Without ``required_train_tokens`` the complete numbered inventory must be
+    present; with it, the numbered prefix 1, 2, ... is validated until it holds that many tokens."""
     root = Path(root)
-    train = sorted(root.glob("fineweb_train_*.bin"))
-    val = sorted(root.glob("fineweb_val_*.bin"))
+    train = {_shard_number(p): p for p in root.glob("fineweb_train_*.bin")}
+    val = sorted(p.name for p in root.glob("fineweb_val_*.bin"))
     if not train:
-        raise ValueError("FineWeb has no visible train shards")
-    if val != [root / "fineweb_val_000000.bin"]:
-        raise ValueError("FineWeb requires exactly fineweb_val_000000.bin")
+        raise ValueError(f"{root}: no train shards")
+    if val != ["fineweb_val_000000.bin"]:
+        raise ValueError(f"{root}: the validation split must be exactly fineweb_val_000000.bin, found {val}")
     if required_train_tokens is None and len(train) != expected_train_shards:
-        raise ValueError(f"complete FineWeb inventory requires {expected_train_shards} train shards; found {len(train)}")
-    need = required_train_tokens or 0
-    paths = ([root / f"fineweb_train_{i:06d}.bin" for i in range(1, expected_train_shards + 1)] if need == 0 else train)
-    tokens = validated = 0
-    for idx, p in enumerate(paths, start=1):
-        if p.name != f"fineweb_train_{idx:06d}.bin" or not p.is_file():
-            raise ValueError(f"FineWeb is missing required train shard {idx:06d}")
-        tokens += inspect_fineweb_shard(p)
-        validated += 1
-        if need and tokens >= need:
+        raise ValueError(f"{root}: {len(train)} train shards visible, the complete inventory has {expected_train_shards}")
+    wanted = required_train_tokens or 0
+    last = expected_train_shards if not wanted else max(train)
+    counted = tokens = 0
+    for number in range(1, last + 1):
+        if number not in train:
+            raise ValueError(f"{root}: train shard {number:06d} is missing")
+        tokens += inspect_fineweb_shard(train[number])
+        counted += 1
+        if wanted and tokens >= wanted:
             break
-    if tokens < need:
-        raise ValueError(f"FineWeb prefix has {tokens} validated tokens, fewer than the required {need}")
-    return {"visible_train_shards": len(train), "validated_train_shards": validated, "validation_shards": len(val),
-            "validated_train_tokens": tokens, "validation_tokens": sum(inspect_fineweb_shard(p) for p in val),
+    if tokens < wanted:
+        raise ValueError(f"{root}: the shard prefix holds {tokens} tokens, {wanted} are required")
+    return {"visible_train_shards": len(train), "validated_train_shards": counted, "validation_shards": len(val),
+            "validated_train_tokens": tokens, "validation_tokens": inspect_fineweb_shard(root / val[0]),
             "complete_inventory": len(train) == expected_train_shards}
 
 
+@dataclass(frozen=True)
+class ShardTable:
+    """Headers of a split and the batch arithmetic over them."""
+    paths: tuple[Path, ...]
+    tokens: tuple[int, ...]
+    batch_tokens: int                     # tokens of one distributed batch
+    batches: tuple[int, ...]              # whole batches each shard supplies (one spare token for the labels)
+    first_batch: tuple[int, ...]          # epoch-relative index of each shard's first batch
+
+    @classmethod
+    def scan(cls, root, split: str, batch_tokens: int) -> "ShardTable":
+        paths = tuple(sorted(Path(root).glob(f"fineweb_{split}_*.bin")))
+        if not paths:
+            raise FileNotFoundError(f"no FineWeb {split} shards under {Path(root)}")
+        tokens = tuple(inspect_fineweb_shard(p) for p in paths)
+        batches = tuple(max(0, (n - 1) // batch_tokens) for n in tokens)
+        if not any(batches):
+            raise ValueError("no shard is large enough for one distributed batch")
+        starts, run = [], 0
+        for b in batches:
+            starts.append(run)
+            run += b
+        return cls(paths, tokens, batch_tokens, batches, tuple(starts))
+
+    @property
+    def epoch_batches(self) -> int:
+        return self.first_batch[-1] + self.batches[-1]
+
+    def locate(self, batch_index: int) -> tuple[int, int]:
+        """(shard, token offset of the batch inside it) of the ``batch_index``-th batch from the start."""
+        within = batch_index % self.epoch_batches
+        shard = bisect.bisect_right(self.first_batch, within) - 1
+        while self.batches[shard] == 0:                 # shards too small for a batch sort equal to their successor
+            shard -= 1
+        return shard, (within - self.first_batch[shard]) * self.batch_tokens
+
+
 class FineWebBinaryLoader:
+    """Iterator over this rank's ``(inputs, labels)`` of successive distributed batches."""
+
     def __init__(self, root, split: str, local_batch_size: int, sequence_length: int, *, rank: int, world_size: int,
                  device="cuda", start_batch_index: int = 0):
-        if split not in {"train", "val"}:
+        if split not in ("train", "val"):
             raise ValueError("split must be 'train' or 'val'")
-        if local_batch_size <= 0 or sequence_length <= 0:
-            raise ValueError("batch size and sequence length must be positive")
-        if world_size <= 0 or not 0 <= rank < world_size:
-            raise ValueError("rank must be inside a positive world size")
-        if start_batch_index < 0:
-            raise ValueError("start batch index must be non-negative")
-        self.files = sorted(Path(root).glob(f"fineweb_{split}_*.bin"))
-        if not self.files:
-            raise FileNotFoundError(f"no FineWeb {split} shards under {Path(root)}")
+        for name, value in (("local_batch_size", local_batch_size), ("sequence_length", sequence_length), ("world_size", world_size)):
+            if value <= 0:
+                raise ValueError(f"{name} must be positive")
+        if not 0 <= rank < world_size:
+            raise ValueError("rank must lie inside the world size")
         self.local_batch_size, self.sequence_length = local_batch_size, sequence_length
+        self.rank, self.world_size = rank, world_size
         self.local_tokens = local_batch_size * sequence_length
         self.global_tokens = self.local_tokens * world_size
-        self.rank, self.world_size = rank, world_size
+        self.table = ShardTable.scan(root, split, self.global_tokens)
+        self.files = list(self.table.paths)
         self.device = torch.device(device)
-        self.shard_index = self.global_position = self.batch_index = 0
-        self.tokens = None
-        self.token_count = 0
-        self._open()
-        if not any(inspect_fineweb_shard(p) > self.global_tokens for p in self.files):
-            raise ValueError("no FineWeb shard is large enough for one distributed batch")
+        self._mapped = (-1, None)
         self.seek_batch(start_batch_index)
 
-    def _open(self) -> None:
-        p = self.files[self.shard_index]
-        self.token_count = inspect_fineweb_shard(p)
-        self.tokens = np.memmap(p, dtype=np.uint16, mode="r", offset=HEADER_BYTES, shape=(self.token_count,))
-        self.global_position = 0
-
-    def _advance(self) -> None:
-        self.shard_index = (self.shard_index + 1) % len(self.files)
-        self._open()
-
+    # -- cursor --------------------------------------------------------------------------------------
     def seek_batch(self, batch_index: int) -> None:
         if batch_index < 0:
             raise ValueError("batch index must be non-negative")
-        self.shard_index = 0
-        self._open()
-        self.batch_index = 0
-        remaining = batch_index
-        while remaining:
-            available = max(0, (self.token_count - self.global_position - 1) // self.global_tokens)
-            if remaining < available:
-                self.global_position += remaining * self.global_tokens
-                self.batch_index += remaining
-                return
-            remaining -= available
-            self.batch_index += available
-            self._advance()
+        self.batch_index = batch_index
+        self.shard_index, self.global_position = self.table.locate(batch_index)
 
     def state_dict(self) -> dict[str, int]:
-        return {"shard_index": self.shard_index, "global_position": self.global_position,
-                "batch_index": self.batch_index}
+        return {"shard_index": self.shard_index, "global_position": self.global_position, "batch_index": self.batch_index}
+
+    def _payload(self, shard: int) -> np.memmap:
+        if self._mapped[0] != shard:
+            self._mapped = (shard, np.memmap(self.table.paths[shard], dtype=np.uint16, mode="r", offset=HEADER_BYTES,
+                                             shape=(self.table.tokens[shard],)))
+        return self._mapped[1]
+
+    # -- reading -------------------------------------------------------------------------------------
+    def next_block(self) -> torch.Tensor:
+        """This rank's ``local_tokens + 1`` int64 ids of the current batch; advances the cursor."""
+        lo = self.global_position + self.rank * self.local_tokens
+        ids = self._payload(self.shard_index)[lo:lo + self.local_tokens + 1].astype(np.int64)
+        self.seek_batch(self.batch_index + 1)
+        return torch.from_numpy(ids)
 
     def __iter__(self):
         return self
 
-    def next_block(self) -> torch.Tensor:
-        """This rank's ``[local_batch, T + 1]``-equivalent flat block (local_tokens + 1 int64 ids)."""
-        while self.global_position + self.global_tokens + 1 > self.token_count:
-            self._advance()
-        start = self.global_position + self.rank * self.local_tokens
-        buf = torch.from_numpy(np.array(self.tokens[start:start + self.local_tokens + 1], dtype=np.int64, copy=True))
-        self.global_position += self.global_tokens
-        self.batch_index += 1
-        return buf
-
     def __next__(self):
-        buf = self.next_block()
-        x = buf[:-1].view(self.local_batch_size, self.sequence_length)
-        y = buf[1:].view(self.local_batch_size, self.sequence_length)
+        block = self.next_block()
+        shape = (self.local_batch_size, self.sequence_length)
+        x, y = block[:-1].view(shape), block[1:].view(shape)
         if self.device.type == "cuda":
             return x.pin_memory().to(self.device, non_blocking=True), y.pin_memory().to(self.device, non_blocking=True)
         return x.to(self.device), y.to(self.device)
@@ -155,11 +185,11 @@ class FineWebBinaryLoader:
 
 def fixed_fineweb_validation_loader(root, local_batch_size: int, sequence_length: int, *, window_batches: int,
                                     rank: int = 0, world_size: int = 1, device="cuda"):
-    """Replays the identical first ``window_batches`` validation batches at every evaluation."""
+    """Endless generator that replays the same first ``window_batches`` validation batches at every evaluation."""
     if window_batches < 1:
         raise ValueError("window_batches must be positive")
+    loader = FineWebBinaryLoader(root, "val", local_batch_size, sequence_length, rank=rank, world_size=world_size, device=device)
     while True:
-        loader = FineWebBinaryLoader(root, "val", local_batch_size, sequence_length, rank=rank,
-                                     world_size=world_size, device=device)
+        loader.seek_batch(0)
         for _ in range(window_batches):
             yield next(loader)

@@ -40,6 +40,7 @@ class TrainerConfig:
     seed: int = 0
     head_chunk: int = 8192
     zero_impl: str = "auto"         # "nccl" (decomposed baseline) | "fused" (peer-memory kernels) | "auto"
+    use_engine: bool = True         # False: module forward + autograd on CUDA too (the library-kernel baseline)
 
 
 class Trainer:
@@ -53,7 +54,7 @@ class Trainer:
         model.init_weights()
         self.model = model
         self.engine = None
-        if self.device.type == "cuda" and not cfg.model.simplicial_layers:
+        if self.device.type == "cuda" and cfg.use_engine and not cfg.model.simplicial_layers:
             from ..models.nanochat_engine import FusedGPTEngine
 
             ws = coll.world_size()

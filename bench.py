@@ -3,6 +3,7 @@
     python bench.py --gpus N --steps K --warmup W            (N > 1: launched under torchrun)
     python bench.py --impl reference ...                      (the reference arm)
     python bench.py --impl eager ...                          (this repo's cuBLAS/SDPA/NCCL decomposition)
+    python bench.py --config qwen35_4b_simplicial | v41_moe   (the mesh trainer's step on the larger configurations)
 
 Config (BASELINE.json, config 2): 20 layers, d_model 1280, 10 heads x 128, QK-norm, vocab 65536,
 seq 2048, bf16, Muon + AdamW, ZeRO-1 style gradient sync inside the optimizer.  Weak scaling:
@@ -93,6 +94,9 @@ def main() -> None:
     ap.add_argument("--unembedding-lr", type=float, default=0.008)
     ap.add_argument("--scalar-lr", type=float, default=0.5)
     ap.add_argument("--weight-decay", type=float, default=0.28)
+    ap.add_argument("--config", default="d20", choices=["d20", "qwen35_4b_simplicial", "v41_moe"],
+                    help="d20: the speedrun GPT (headline); the others time the mesh trainer's step")
+    ap.add_argument("--no-extra", action="store_true", help="skip the kernel metrics appended to the d20 line")
     args = ap.parse_args()
     if args.warmup < 3:
         raise SystemExit("at least 3 warm-up steps are required")
@@ -111,6 +115,8 @@ def main() -> None:
         if out is not None:
             print(json.dumps(out))
         return
+    if args.config != "d20":
+        return mesh_config(args)
     if args.micro_batch is None:
         args.micro_batch = min(16, args.local_batch)
 
@@ -139,10 +145,10 @@ def main() -> None:
     tcfg = TrainerConfig(model=mcfg, micro_batch=args.micro_batch, num_iterations=10000,
                          matrix_lr=args.matrix_lr, embedding_lr=args.embedding_lr,
                          unembedding_lr=args.unembedding_lr, scalar_lr=args.scalar_lr,
-                         weight_decay=args.weight_decay)
+                         weight_decay=args.weight_decay,
+                         # eager arm: module forward / autograd (cuBLAS + SDPA) and the NCCL optimizer from the start
+                         use_engine=args.impl != "eager", zero_impl="nccl" if args.impl == "eager" else "auto")
     trainer = Trainer(tcfg, device=dev)
-    if args.impl == "eager":
-        trainer.engine = None   # cuBLAS + SDPA + autograd on the same parameters
     data = ZipfTokens(args.vocab, args.seq_len, args.local_batch, s=1.1, seed=0, rank=rank, pin=True)
     n_blocks = args.warmup + 2 * args.steps
     host_blocks = [data.block(i) for i in range(n_blocks)]
@@ -216,9 +222,82 @@ def main() -> None:
             "gpu_launches": int(launches),
             "final_loss": last_loss,
         }
+        if args.impl == "native" and not args.no_extra:
+            from archlab_b200.bench_kernels import simplicial_headline
+
+            del trainer
+            torch.cuda.empty_cache()
+            out["extra_metrics"] = simplicial_headline()
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
+
+
+def mesh_config(args) -> None:
+    """Configurations 3 and 4 through the mesh trainer (``archlab_b200.train.mesh_train.train``, the call a user
+    makes): per-GPU work is fixed (16 resp. 4 sequences per GPU per step), every step copies its token block from the
+    host and reads the loss back.  ``value`` sums the trainer's own per-step device times (CUDA events, max over
+    ranks); ``e2e`` is the wall clock around the same steps."""
+    import tempfile
+
+    import torch
+
+    from archlab_b200.ops import native
+    from archlab_b200.train import mesh_train
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    total = args.warmup + args.steps
+    run_dir = tempfile.mkdtemp(prefix="bench-mesh-") if rank == 0 else ""
+    if args.config == "qwen35_4b_simplicial":
+        tp = 2 if world >= 2 else 1
+        seq, per_gpu = 8192, 16
+        argv = ["--model=qwen35_4b", f"--tp={tp}", "--seq-len=8192", f"--global-batch={per_gpu * world}"]
+        if tp > 1:
+            argv.append("--sequence-parallel")
+        par = f"tp{tp}+sp x zero-dp{world // tp}"
+        model = "Qwen3.5-4B-like dense (36L, hidden 2560, 32/8 heads x 128, FFN 9728, vocab 151936), every 4th layer 2-simplicial 32x512"
+    else:
+        seq, per_gpu = 4096, 4
+        argv = ["--model=v41_moe", f"--ep={world}", "--seq-len=4096", "--micro-batch=1", f"--global-batch={per_gpu * world}"]
+        par = f"ep{world} (= dp{world})"
+        model = "DeepSeek-V4.1-style MoE (24L, hidden 2048, 64 routed experts FFN 1408 top-6 + 2 shared, DSA top-2048, 4 HC streams)"
+    argv += [f"--steps={total}", f"--run-dir={run_dir or tempfile.gettempdir() + '/bench-mesh-other'}"]
+    marks = {}
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+
+    def on_step(step, loss):
+        if step + 1 == args.warmup:
+            torch.cuda.synchronize()
+            sampler.start()
+            marks["t0"], marks["l0"] = time.perf_counter(), native.launch_count()
+        if step + 1 == total:
+            torch.cuda.synchronize()
+            marks["t1"], marks["l1"], marks["loss"] = time.perf_counter(), native.launch_count(), loss
+
+    mesh_train.train(mesh_train.parse_args(argv), on_step=on_step)
+    clocks = sampler.stop()
+    if rank != 0:
+        return
+    rows = [json.loads(line) for line in open(os.path.join(run_dir, "metrics_rank0.jsonl"))]
+    dev_s = sum(r["step_seconds"] for r in rows[args.warmup:total])
+    tokens = per_gpu * world * seq
+    e2e_s = marks["t1"] - marks["t0"]
+    print(json.dumps({
+        "metric": "train tokens/sec/box", "value": tokens * args.steps / dev_s, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: Zipf(1.1) token ids from seed 0, random-init weights", "impl": "native",
+        "config": {"model": model, "global_batch": tokens, "seq_len": seq, "parallelism": par,
+                   "l2": "working set per step far exceeds the 126 MB L2; no explicit flush"},
+        "clocks": clocks,
+        "e2e": {"value": tokens * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": per_gpu * (seq + 1) * 8,
+                "d2h_bytes_per_step": 4, "ms_per_step": e2e_s / args.steps * 1e3},
+        "gpu_launches": int(marks["l1"] - marks["l0"]), "final_loss": marks["loss"],
+        "peak_mem_gib": rows[-1].get("peak_mem_gib")}))
 
 
 if __name__ == "__main__":

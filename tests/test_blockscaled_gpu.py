@@ -36,7 +36,8 @@ def test_nvfp4_quantiser_matches_the_reference_bytes(two_d, seed):
     ref = bs.quantize_nvfp4_reference(x, two_d=two_d, hadamard_seed=seed)
     idx = bs.sf_index(rows, K // 16, ref.chunks_k, "cuda")
     if seed == 0:
-        assert torch.equal(got.sf[idx], ref.sf[idx]) and torch.equal(got.data, ref.data)
+        assert torch.equal(got.sf[idx], ref.sf[idx])
+        assert int((got.data != ref.data).sum()) == 0, f"{int((got.data != ref.data).sum())} of {ref.data.numel()} bytes differ"
     else:       # the transform's sums round differently in the two orders of addition: compare decoded values
         assert _rel(bs.decode(got), bs.decode(ref)) < 0.02
 

@@ -29,8 +29,37 @@ def test_fineweb_rank_slices_and_seek(tmp_path):
         assert torch.equal(next(seek)[0], batches[k])
     bad = tmp_path / "fineweb_val_000000.bin"
     bad.write_bytes(b"\0" * 100)
-    with pytest.raises(ValueError, match="truncated"):
+    with pytest.raises(ValueError, match="header is shorter"):
         inspect_fineweb_shard(bad)
+    # the cursor wraps around the epoch and a seek is closed-form (no shard in between is opened)
+    table = stream.table
+    assert table.batches == ((5000 - 1) // 256, (7000 - 1) // 256) and table.epoch_batches == 19 + 27
+    wrapped = FineWebBinaryLoader(tmp_path, "train", 2, 64, rank=1, world_size=2, device="cpu", start_batch_index=46 + 17)
+    assert torch.equal(next(wrapped)[0], batches[17]) and wrapped.state_dict()["batch_index"] == 64
+
+
+def test_fineweb_inventory(tmp_path):
+    from archlab_b200.data.fineweb import fixed_fineweb_validation_loader, inspect_fineweb_dataset
+
+    rng = np.random.default_rng(2)
+    for i in (1, 2, 3):
+        write_fineweb_shard(tmp_path / f"fineweb_train_{i:06d}.bin", rng.integers(0, 50000, 1000 * i))
+    write_fineweb_shard(tmp_path / "fineweb_val_000000.bin", rng.integers(0, 50000, 900))
+    with pytest.raises(ValueError, match="complete inventory"):
+        inspect_fineweb_dataset(tmp_path)
+    rep = inspect_fineweb_dataset(tmp_path, expected_train_shards=3)
+    assert rep["validated_train_tokens"] == 6000 and rep["complete_inventory"] and rep["validation_tokens"] == 900
+    part = inspect_fineweb_dataset(tmp_path, required_train_tokens=2500)
+    assert part["validated_train_shards"] == 2 and not part["complete_inventory"]
+    with pytest.raises(ValueError, match="are required"):
+        inspect_fineweb_dataset(tmp_path, required_train_tokens=7000)
+    (tmp_path / "fineweb_train_000002.bin").unlink()
+    with pytest.raises(ValueError, match="000002 is missing"):
+        inspect_fineweb_dataset(tmp_path, required_train_tokens=2500)
+    gen = fixed_fineweb_validation_loader(tmp_path, 2, 32, window_batches=3, device="cpu")
+    first = [next(gen)[0] for _ in range(3)]
+    again = [next(gen)[0] for _ in range(3)]
+    assert all(torch.equal(a, b) for a, b in zip(first, again))
 
 
 def test_token_batches_python_and_native_agree(tmp_path):
