@@ -16,16 +16,15 @@ __device__ __forceinline__ long long sf_offset(long long r, long long sfi, long 
   return (tile * chunks_k + chunk) * 512 + (rr & 31) * 16 + (rr >> 5) * 4 + int(sfi & 3);
 }
 
-// power-of-two scale: smallest 2^e with amax / 2^e <= fmax; returns the biased ue8m0 byte and 2^-e
+// power-of-two scale: smallest 2^e with max(amax, 1e-4) / 2^e <= fmax (the floor keeps all-zero blocks at a
+// finite scale, as the DeepSeek-V4.1 quantiser does); returns the biased ue8m0 byte and 2^-e
 __device__ __forceinline__ uint8_t pow2_scale(float amax, float fmax, float& inv) {
-  int e = 0;
-  if (amax > 0.f) {
-    e = int(ceilf(log2f(amax / fmax)));
-    // log2f may be off by an ulp at exact powers of two: make sure the block fits
-    if (ldexpf(fmax, e) < amax) ++e;
-    else if (ldexpf(fmax, e - 1) >= amax) --e;
-    e = max(-127, min(127, e));
-  }
+  amax = fmaxf(amax, 1e-4f);
+  int e = int(ceilf(log2f(amax / fmax)));
+  // log2f may be off by an ulp at exact powers of two: make sure the block fits, and fits tightly
+  if (ldexpf(fmax, e) < amax) ++e;
+  else if (ldexpf(fmax, e - 1) >= amax) --e;
+  e = max(-127, min(127, e));
   inv = ldexpf(1.f, -e);
   return uint8_t(e + 127);
 }

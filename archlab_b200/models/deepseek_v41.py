@@ -18,7 +18,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops import dsa, dsa_cuda, quant, stream_mix
+from ..ops import blockscaled, dsa, dsa_cuda, quant, stream_mix
 from . import moe
 from .blocks import RMSNorm, apply_rope, hc_split_sinkhorn, rms_norm, rope_tables
 
@@ -74,7 +74,9 @@ class QuantLinear(nn.Linear):
 
     def forward(self, x):
         if not self.fp8 or x.size(-1) % self.block:
-            return F.linear(x, self.weight.to(x.dtype))
+            return moe.dense_linear(x, self.weight)                  # tcgen05 kernels on a GPU, F.linear otherwise
+        if self.block == 128 and blockscaled.block_fp8_supported(x, self.weight):
+            return blockscaled.block_fp8_linear(x, self.weight)      # the product itself runs in FP8 on the tensor core
         xq = quant.rounded_activation(x, bits=8, block_size=self.block)
         with torch.no_grad():
             wq, ws = quant.fp8_weight_quantize_2d(self.weight, self.block)
@@ -210,7 +212,7 @@ class V41Block(nn.Module):
 
             self.ffn = FusedExpertParallelMoE(c.hidden_size, c.moe_inter, c.n_routed_experts, c.experts_top_k, ep_buffers,
                                               score=c.router_score, route_scale=c.route_scale, swiglu_limit=c.swiglu_limit,
-                                              n_shared=c.n_shared_experts)
+                                              n_shared=c.n_shared_experts, fp8=c.fp8 and c.fp8_block == 128)
         elif ep_group is not None:
             self.ffn = moe.ExpertParallelMoE(c.hidden_size, c.moe_inter, c.n_routed_experts, c.experts_top_k, ep_group,
                                              score=c.router_score, route_scale=c.route_scale, swiglu_limit=c.swiglu_limit,

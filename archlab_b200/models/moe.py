@@ -94,17 +94,34 @@ class GroupedExperts(nn.Module):
         return res
 
 
+def dense_linear(x: torch.Tensor, weight: torch.Tensor, fp8: bool = False) -> torch.Tensor:
+    """Bias-free linear of the MoE blocks: on a GPU in bf16 the tcgen05 kernels (block-scaled FP8 forward when ``fp8``
+    and the reduction width is a multiple of 128), otherwise ``F.linear``."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and weight.size(1) % 8 == 0 and weight.size(0) % 8 == 0:
+        from ..ops import blockscaled, native_linear
+
+        if fp8 and blockscaled.block_fp8_supported(x, weight):
+            return blockscaled.block_fp8_linear(x, weight)
+        return native_linear.native_linear(x, weight)
+    return F.linear(x, weight.to(x.dtype))
+
+
 class SwiGLU(nn.Module):
-    def __init__(self, dim: int, inter: int, limit: float | None = None):
+    def __init__(self, dim: int, inter: int, limit: float | None = None, fp8: bool = False):
         super().__init__()
         self.gate_up = nn.Linear(dim, 2 * inter, bias=False)
         self.down = nn.Linear(inter, dim, bias=False)
-        self.inter, self.limit = inter, limit
+        self.inter, self.limit, self.fp8 = inter, limit, fp8
 
     def forward(self, x):
-        h = F.linear(x, self.gate_up.weight.to(x.dtype))
-        a = swiglu_clamped(h[..., : self.inter], h[..., self.inter:], self.limit)
-        return F.linear(a.to(x.dtype), self.down.weight.to(x.dtype))
+        h = dense_linear(x, self.gate_up.weight, self.fp8)
+        if h.is_cuda and h.dtype == torch.bfloat16:
+            from ..ops import block_ops
+
+            a = block_ops.swiglu(h.reshape(-1, h.size(-1)), self.limit).reshape(*h.shape[:-1], self.inter)
+        else:
+            a = swiglu_clamped(h[..., : self.inter], h[..., self.inter:], self.limit).to(x.dtype)
+        return dense_linear(a, self.down.weight, self.fp8)
 
 
 class SparseMoE(nn.Module):

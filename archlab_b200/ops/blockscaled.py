@@ -73,12 +73,12 @@ def sf_index(rows: int, n_sf: int, chunks_k: int, device=None) -> torch.Tensor:
 
 
 def _pow2_scale_exponent(amax: torch.Tensor, fmax: float) -> torch.Tensor:
-    """Smallest integer e with amax / 2^e <= fmax (0 for an all-zero block), clamped to ue8m0's range."""
-    safe = amax.double().clamp_min(1e-300)
+    """Smallest integer e with max(amax, 1e-4) / 2^e <= fmax, clamped to ue8m0's range; the floor is the one of the
+    DeepSeek-V4.1 quantiser (src/archlab/automodel/deepseek_v41_native_quantization.py:31)."""
+    safe = amax.float().clamp_min(1e-4).double()
     e = torch.ceil(torch.log2(safe / fmax))
     e = torch.where(torch.ldexp(torch.full_like(safe, fmax), e.int()) < safe, e + 1, e)
     e = torch.where(torch.ldexp(torch.full_like(safe, fmax), e.int() - 1) >= safe, e - 1, e)
-    e = torch.where(amax > 0, e, torch.zeros_like(e))
     return e.clamp(-127, 127).to(torch.int32)
 
 
@@ -164,8 +164,9 @@ def quantize_nvfp4_reference(x: torch.Tensor, *, two_d: bool = False, hadamard_s
         padded = torch.zeros(Rp, Kp // 16, device=x.device)
         padded[:rows] = bmax
         bmax = padded.view(Rp // 16, 16, -1).amax(1).repeat_interleave(16, 0)[:rows]
-    s_enc = torch.where(amax > 0, NVFP4_RANGE / amax, torch.ones_like(amax))
-    sbyte = (bmax / 6.0 * s_enc).clamp(max=448.0).to(torch.float8_e4m3fn)
+    # tensor / tensor: true IEEE divisions, as in the kernel (a Python-scalar operand would multiply by a reciprocal)
+    s_enc = torch.where(amax > 0, torch.full_like(amax, NVFP4_RANGE) / amax, torch.ones_like(amax))
+    sbyte = (bmax / torch.full_like(bmax, 6.0) * s_enc).clamp(max=448.0).to(torch.float8_e4m3fn)
     sdec = sbyte.float()
     enc = torch.where(sdec > 0, s_enc / sdec, torch.zeros_like(sdec))
     a = blocks * enc.unsqueeze(-1)
@@ -304,3 +305,46 @@ def grouped_gemm(a: ScaledOperand, b: ScaledOperand, group_of_mtile: torch.Tenso
                                           native.status_word(a.data.device).data_ptr(), native.stream_ptr())
     native.check(rc, "nga_gemm_grouped_bs")
     return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Linear layer: block-FP8 forward, straight-through backward
+# ------------------------------------------------------------------------------------------------
+class _BlockFp8Linear(torch.autograd.Function):
+    """``y = Q(x) Q(W)^T`` on the block-scaled FP8 GEMM (activations 1 x 128, weights 128 x 128, power-of-two
+    scales); the gradients pass straight through the rounding and are taken against the unrounded bf16 operands,
+    which is how the reference trains its V4.1 linears (``rounded_activation`` with an identity gradient in front
+    of a bf16 linear, src/archlab/architectures/deepseek_v41_torch.py:80-121)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        from . import gemm as G  # noqa: F401  (kernels for the backward)
+
+        x2 = x.reshape(-1, x.size(-1)).to(torch.bfloat16).contiguous()
+        wb = w.to(torch.bfloat16)
+        ctx.save_for_backward(x2, wb)
+        ctx.lead, ctx.dtypes = x.shape[:-1], (x.dtype, w.dtype)
+        y = gemm(quantize_fp8(x2, 128), quantize_fp8(wb, -128), out_dtype=torch.bfloat16)
+        return y.reshape(*x.shape[:-1], w.size(0)).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import gemm as G
+
+        x2, wb = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.size(-1)).to(torch.bfloat16).contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = G.gemm(dy2, wb, b_mn=True, out_dtype=torch.bfloat16).reshape(*ctx.lead, wb.size(1)).to(ctx.dtypes[0])
+        if ctx.needs_input_grad[1]:
+            dw = G.gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.bfloat16).to(ctx.dtypes[1])
+        return dx, dw
+
+
+def block_fp8_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """Bias-free linear with both operands rounded to block-scaled FP8 in the forward product."""
+    return _BlockFp8Linear.apply(x, weight)
+
+
+def block_fp8_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return _on_gpu(x) and weight.size(1) % 128 == 0 and weight.size(0) % 8 == 0 and x.size(-1) == weight.size(1)

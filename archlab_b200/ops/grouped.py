@@ -37,10 +37,16 @@ def _launch(a, w_stack, tile_group, groups, n_out, k_red, b_mn):
 
 class _GroupedLinear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, tile_group, real, padded):
+    def forward(ctx, x, w, tile_group, real, padded, fp8=False):
         E, N, K = w.shape
         ctx.save_for_backward(x, w, tile_group)
         ctx.seg = (real, padded)
+        if fp8:
+            # forward product in block-scaled FP8 (rows 1 x 128, expert weights 128 x 128 blocks); the backward below
+            # is taken straight through the rounding against the bf16 operands
+            from . import blockscaled as bs
+
+            return bs.grouped_gemm(bs.quantize_fp8(x, 128), bs.quantize_fp8(w.view(E * N, K), -128), tile_group, E, N)
         return _launch(x, w.view(E * N, K), tile_group, E, N, K, False)
 
     @staticmethod
@@ -56,17 +62,20 @@ class _GroupedLinear(torch.autograd.Function):
             if n:
                 dw[e] = G.gemm(dy[s0:s0 + n], x[s0:s0 + n], a_mn=True, b_mn=True)     # dY_e^T X_e
             s0 += npad
-        return dx, dw, None, None, None
+        return dx, dw, None, None, None, None
 
 
-def grouped_linear(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, real: list[int], padded: list[int]) -> torch.Tensor:
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, real: list[int], padded: list[int],
+                   fp8: bool = False) -> torch.Tensor:
     """x [sum(padded), K] (rows sorted by expert, segments padded to 256), w [E, N, K] -> [sum(padded), N].
-    Rows in the padding produce unspecified values."""
+    Rows in the padding produce unspecified values.  ``fp8``: the forward product runs on the block-scaled FP8 GEMM
+    (needs N and K to be multiples of 128); gradients are straight-through in bf16."""
     E, N, K = w.shape
     if x.size(0) == 0:
         return x.new_zeros(0, N) + 0 * w.sum().to(x.dtype)            # keeps the weights in the graph
     if x.is_cuda and x.dtype == torch.bfloat16 and native.available() and K % 8 == 0 and N % 64 == 0 and K % 64 == 0:
-        return _GroupedLinear.apply(x.contiguous(), w.to(x.dtype).contiguous(), tile_group, real, padded)
+        return _GroupedLinear.apply(x.contiguous(), w.to(x.dtype).contiguous(), tile_group, real, padded,
+                                    bool(fp8 and N % 128 == 0 and K % 128 == 0))
     outs, s0 = [], 0
     for e, npad in enumerate(padded):
         outs.append(x[s0:s0 + npad] @ w[e].to(x.dtype).t())

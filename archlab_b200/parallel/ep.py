@@ -126,9 +126,10 @@ class FusedExpertParallelMoE(nn.Module):
     """Same parameters and semantics as ``models.moe.ExpertParallelMoE``; bf16 CUDA only."""
 
     def __init__(self, dim, inter, n_experts, top_k, buffers: EPBuffers, *, score="sqrt_softplus", route_scale=1.0,
-                 swiglu_limit=None, n_shared=1):
+                 swiglu_limit=None, n_shared=1, fp8: bool = False):
         super().__init__()
         self.buf = buffers
+        self.fp8 = fp8                      # forward products of the expert and shared projections in block-scaled FP8
         self.size, self.rank = buffers.world, buffers.rank
         if n_experts % self.size:
             raise ValueError("expert count must divide EP size")
@@ -139,7 +140,7 @@ class FusedExpertParallelMoE(nn.Module):
         self.router = nn.Parameter(torch.empty(n_experts, dim))
         self.register_buffer("e_score_correction_bias", torch.zeros(n_experts, dtype=torch.float32))
         self.experts = GroupedExperts(self.local_experts, dim, inter, swiglu_limit=swiglu_limit)
-        self.shared = SwiGLU(dim, inter * n_shared, swiglu_limit) if n_shared else None
+        self.shared = SwiGLU(dim, inter * n_shared, swiglu_limit, fp8=fp8) if n_shared else None
         self._cumulative_expert_load = None
 
     def plan(self, idx: torch.Tensor):
@@ -180,8 +181,8 @@ class FusedExpertParallelMoE(nn.Module):
         recv = _Dispatch.apply(x2, src_row, dst_rank, dst_row, n_recv, k, self.buf)
         # all local experts in ONE grouped GEMM per projection (rows in the 256-row padding are never read back)
         tiles = grouped.tile_groups(seg_pad, x.device)
-        h = grouped.grouped_linear(recv, self.experts.gate_up, tiles, seg, seg_pad)
-        y_local = grouped.grouped_linear(block_ops.swiglu(h, self.limit), self.experts.down, tiles, seg, seg_pad)
+        h = grouped.grouped_linear(recv, self.experts.gate_up, tiles, seg, seg_pad, fp8=self.fp8)
+        y_local = grouped.grouped_linear(block_ops.swiglu(h, self.limit), self.experts.down, tiles, seg, seg_pad, fp8=self.fp8)
         # ascending expert id per token: deterministic summation order
         eo = idx.argsort(dim=-1)
         slots = (torch.arange(T, device=x.device) * k).unsqueeze(1) + eo

@@ -109,3 +109,40 @@ def test_grouped_block_scaled_gemm(kind):
     da, dw = bs.decode(qa), bs.decode(qw).view(G, Nw, K)
     ref = torch.cat([da[t * 256:(t + 1) * 256] @ dw[g].t() for t, g in enumerate(groups.tolist())])
     assert _rel(out, ref) < 5e-3
+
+
+def test_block_fp8_linear_forward_and_straight_through_backward():
+    from archlab_b200.ops import blockscaled as bs, native
+
+    torch.manual_seed(5)
+    x = torch.randn(4, 96, 1024, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(768, 1024, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    g = torch.randn(4, 96, 768, device="cuda").bfloat16()
+    y = bs.block_fp8_linear(x, w)
+    y.backward(g)
+    torch.cuda.synchronize()
+    native.check_status()
+    xf, wf = x.detach().float(), w.detach().float()
+    assert _rel(y, xf @ wf.t()) < 0.05
+    # the gradients ignore the rounding: they are the bf16 products against the unrounded operands
+    assert _rel(x.grad, g.float() @ wf) < 0.01
+    assert _rel(w.grad, g.float().reshape(-1, 768).t() @ xf.reshape(-1, 1024)) < 0.01
+
+
+def test_grouped_linear_fp8_forward_matches_bf16_path():
+    from archlab_b200.ops import grouped, native
+
+    torch.manual_seed(6)
+    E, N, K = 3, 256, 512
+    seg, seg_pad = [200, 0, 300], [256, 0, 512]
+    x = torch.randn(sum(seg_pad), K, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(E, N, K, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    tiles = grouped.tile_groups(seg_pad, "cuda")
+    y8 = grouped.grouped_linear(x, w, tiles, seg, seg_pad, fp8=True)
+    y16 = grouped.grouped_linear(x, w, tiles, seg, seg_pad)
+    torch.cuda.synchronize()
+    native.check_status()
+    live = torch.cat([torch.arange(0, 200), torch.arange(256, 556)]).cuda()
+    assert _rel(y8[live], y16[live]) < 0.05
+    y8[live].float().square().sum().backward()
+    assert torch.isfinite(x.grad[live]).all() and torch.isfinite(w.grad).all()
