@@ -43,6 +43,10 @@ int nga_quant_mxfp8(const void* x, void* q, void* sf, long long rows, long long 
 // out).  sr_seed != 0: stochastic rounding.
 int nga_quant_nvfp4(const void* x, void* q, void* sf, const float* amax, long long rows, long long K, long long ldx,
                     long long ldq_bytes, int two_d, unsigned hadamard_seed, unsigned sr_seed, void* stream);
+// out [n, dim] bf16 = rows idx[i] (int64, inside [0, rows)) of a frozen e4m3 table [rows, dim] times its ue8m0 scales
+// [rows, dim / 32] (one per 32 columns); dim a multiple of 32.
+int nga_gather_dequant_fp8(const void* weight, const void* scale, const void* idx, void* out, long long n, long long rows,
+                           int dim, void* stream);
 #ifdef __cplusplus
 }
 #endif

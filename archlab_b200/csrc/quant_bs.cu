@@ -305,3 +305,49 @@ extern "C" int nga_quant_nvfp4(const void* x, void* q, void* sf, const float* am
   NGA_CHECK_LAUNCH();
   return 0;
 }
+
+// Row gather with de-quantisation for frozen fp8 tables with one ue8m0 scale per 32 columns (row-sharded Engram
+// memories): out[i, :] = e4m3(weight[idx[i], :]) * 2^(scale[idx[i], c / 32] - 127) in bf16.  One warp per output row;
+// a lane converts 8 columns per step (8-byte load, 16-byte store).
+namespace nga {
+__global__ void gather_dequant_fp8_kernel(const uint8_t* __restrict__ weight, const uint8_t* __restrict__ scale,
+                                          const long long* __restrict__ idx, __nv_bfloat16* __restrict__ out, long long n,
+                                          long long rows, int dim) {
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= n) return;
+  const int lane = threadIdx.x & 31;
+  long long r = idx[w];
+  r = r < 0 ? 0 : (r >= rows ? rows - 1 : r);             // ids are validated on the host; never read outside the shard
+  const uint8_t* src = weight + r * dim;
+  const uint8_t* sc = scale + r * (dim / 32);
+  for (int c = lane * 8; c < dim; c += 256) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(src + c);
+    const float s = ldexpf(1.f, int(sc[c >> 5]) - 127);
+    const uint32_t words[2] = {raw.x, raw.y};
+    uint32_t o[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const __half2_raw pr = __nv_cvt_fp8x2_to_halfraw2(__nv_fp8x2_storage_t((words[h] >> (16 * j)) & 0xFFFFu), __NV_E4M3);
+        const float2 f = __half22float2(__half2(pr));
+        const __nv_bfloat162 b = __floats2bfloat162_rn(f.x * s, f.y * s);
+        o[h * 2 + j] = *reinterpret_cast<const uint32_t*>(&b);
+      }
+    *reinterpret_cast<uint4*>(out + w * dim + c) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+}  // namespace nga
+
+extern "C" int nga_gather_dequant_fp8(const void* weight, const void* scale, const void* idx, void* out, long long n,
+                                      long long rows, int dim, void* stream) {
+  using namespace nga;
+  if (n <= 0 || rows <= 0 || dim <= 0 || (dim % 32)) return -1;
+  if ((reinterpret_cast<uintptr_t>(weight) & 7) || (reinterpret_cast<uintptr_t>(out) & 15)) return -5;
+  gather_dequant_fp8_kernel<<<(unsigned)((n + 7) / 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint8_t*>(weight), reinterpret_cast<const uint8_t*>(scale), reinterpret_cast<const long long*>(idx),
+      reinterpret_cast<__nv_bfloat16*>(out), n, rows, dim);
+  count_launch();
+  NGA_CHECK_LAUNCH();
+  return 0;
+}
