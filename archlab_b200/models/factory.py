@@ -78,6 +78,8 @@ def build_model(arch_family: str, config: dict[str, Any] | None = None, *, devic
         with torch.device("meta"):
             model = model_cls(cfg, **model_kwargs)
         model.to_empty(device=device)
+        if hasattr(model, "_tag"):           # materialisation made new Parameter objects: optimizer tags go on again
+            model._tag()
     if init and hasattr(model, "init_weights"):
         model.init_weights()
     return model

@@ -284,9 +284,15 @@ class Qwen38LM(nn.Module):
         for blk in blocks:
             att = blk.attention
             names = ("qkv", "out") if isinstance(att, GatedDeltaNet) else ("q_gate", "k", "v", "out")
+            # logical Muon matrices of the fused projections (src/archlab/architectures/qwen38_flash_next.py:995-1029):
+            # the GDN q/k/v projection per head (key_dim rows each), the gated attention query per head
+            split = {"qkv": att.kd} if isinstance(att, GatedDeltaNet) else {"q_gate": att.d}
             for n in names:
                 w = getattr(att, n).weight
                 w.archlab_optimizer, w.archlab_optimizer_category = "muon", f"{blk.attention_kind}_{n}"
+                rows = split.get(n)
+                if rows and w.shape[0] % rows == 0:
+                    w.archlab_muon_split_rows = rows
             if isinstance(blk.mlp, DenseMLP):
                 for n in ("gate", "up", "down"):
                     w = getattr(blk.mlp, n).weight
@@ -294,6 +300,7 @@ class Qwen38LM(nn.Module):
             else:
                 for n, w in (("experts_gate_up", blk.mlp.experts.gate_up), ("experts_down", blk.mlp.experts.down)):
                     w.archlab_optimizer, w.archlab_optimizer_category = "muon", n
+                blk.mlp.experts.gate_up.archlab_muon_split_rows = blk.mlp.experts.gate_up.shape[-2] // 2   # gate / up halves
         if self.mtp is not None and self.mtp.fusion:
             self.mtp.fc.weight.archlab_optimizer = "muon"
             self.mtp.fc.weight.archlab_optimizer_category = "mtp_fusion"

@@ -128,6 +128,10 @@ def parse_args(argv=None):
     ap.add_argument("--fsdp-min-features", type=int, default=256, help="smallest linear side that is sharded")
     ap.add_argument("--fsdp-keep-gathered", action="store_true",
                     help="keep every gathered weight from the forward to the backward pass (no second gather)")
+    ap.add_argument("--optimizer", default="adamw", choices=["adamw", "muon_split"],
+                    help="muon_split: layer-wise distributed Muon with logical row splits on the parameters a model tags "
+                         "for it (archlab_optimizer == 'muon'), sharded AdamW on the rest")
+    ap.add_argument("--muon-lr", type=float, default=0.02)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--weight-decay", type=float, default=0.1)
@@ -168,7 +172,7 @@ class _Job:
     of ``parallel.pp.run_1f1b``."""
 
     def __init__(self, a, mesh: Mesh, groups: dict, device):
-        self.mesh, self.groups, self.device = mesh, groups, device
+        self.mesh, self.groups, self.device, self.args = mesh, groups, device, a
         fam = a.model.split("_")[0]
         if a.model.startswith("factory:"):
             fam = "factory"
@@ -408,6 +412,17 @@ class MeshOptimizer:
         self.job = job
         experts = job.expert_params()
         shared = [p for p in job.model.parameters() if p not in experts and p.requires_grad]
+        self.muon = None
+        if getattr(job.args, "optimizer", "adamw") == "muon_split":
+            from ..optim.split_muon import SplitRowsMuon
+
+            if job.kind != "dp":
+                raise ValueError("--optimizer muon_split runs on data-parallel (factory) models")
+            # sums over the data group like the sharded AdamW: the step applies 1 / (accumulation x data ranks) to both
+            self.muon = SplitRowsMuon(job.model.named_parameters(), lr=job.args.muon_lr, weight_decay=weight_decay,
+                                      group=job.groups["dp"], average=False)
+            taken = {id(p) for p in self.muon.params}
+            shared = [p for p in shared if id(p) not in taken]
         is_repl = lambda p: not getattr(p, "tensor_model_parallel", False)
         shared.sort(key=lambda p: (p.dim() < 2, not is_repl(p)))      # decayed replicated | decayed sharded | plain
         self.zero = ZeroAdamW(shared, lr=lr, weight_decay=weight_decay, group=job.groups["dp"])
@@ -428,6 +443,9 @@ class MeshOptimizer:
         sq_all, sq_repl = z.grad_sq_norm(), z.grad_sq_norm(self.repl_ranges)
         both = torch.stack([sq_all, sq_repl])
         _allreduce(both, g["dp"])
+        if self.muon is not None:                                       # identical on every rank after its reduction
+            self.muon.reduce_gradients()
+            both[0] = both[0] + self.muon.grad_sq_norm()
         sharded = both[0] - both[1]
         if self.experts is not None:
             e = torch.stack([p.grad.float().pow(2).sum() for p in self.experts.params if p.grad is not None]).sum()
@@ -444,6 +462,8 @@ class MeshOptimizer:
         if fsdp is not None:
             fsdp.sync()                                   # no peer still reads the shards this step rewrites
         self.zero.step(lr_scale=lr_scale, grad_scale=grad_scale)
+        if self.muon is not None:
+            self.muon.step(lr_scale=lr_scale, grad_scale=grad_scale)
         if self.experts is not None:
             self.experts.step(lr_scale=lr_scale, grad_scale=grad_scale)
         if fsdp is not None:
