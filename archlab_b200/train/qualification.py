@@ -238,6 +238,17 @@ def qualify(experiment: Experiment, config: dict, output, *, run_gates: bool = T
                    _check("model_export", lambda: check_model(experiment, config))]
     checks.append(_check("native_model_fixture", lambda: run_pytest(
         ["tests/test_contracts.py"], output / "native_fixture", deployment=None)))
+    if run_gates and "simplicial" in json.dumps(asdict(experiment), default=str).lower():
+        # kernel preflight before anything trains with the 2-simplicial op: FP64 ladder + causality (+ timing on a GPU)
+        from .preflight_simplicial import run as simplicial_preflight
+
+        def preflight():
+            receipt = output / "simplicial_preflight.json"
+            receipt.unlink(missing_ok=True)
+            ev = simplicial_preflight(receipt, repetitions=5)
+            return {"receipt": receipt.name, "cases": len(ev["correctness"]), "benchmarks": len(ev["benchmarks"])}
+
+        checks.append(_check("simplicial_kernel_preflight", preflight))
     ready = all(r["status"] == "passed" for r in checks)
     if speedrun:
         plan = {k: (v[0], v[1]) for k, v in SPEEDRUN_TESTS.items()}
