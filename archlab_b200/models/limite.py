@@ -212,7 +212,25 @@ def set_trainable_mode(model, mode: str) -> int:
 @dataclass(frozen=True)
 class ConversionConfig:
     short_window: int = 8
-    backend: str = "auto"                     # auto: sm_100a kernel when the shape allows, else the PyTorch statement
+    # Which implementation reduces the converted layers (the reference's conversion.backend tri-state,
+    # src/archlab/architectures/limite_conversion.py:65-120):
+    #   "auto"       sm_100a kernel when dtype / head width allow, else the PyTorch statement
+    #   "kernel"     the sm_100a kernel or an error (a run that must not silently fall back)
+    #   "reference"  the PyTorch statement with fp32 queries (oracle runs)
+    backend: str = "auto"
+    scaling: float | None = None              # softmax scale of the reduction; None = head_dim ** -0.5
+
+    def __post_init__(self):
+        if self.backend not in ("auto", "kernel", "reference"):
+            raise ValueError(f"unknown conversion backend {self.backend!r}")
+
+
+def query_for_fixed_scale(q: torch.Tensor, scaling: float, kernel_scale: float) -> torch.Tensor:
+    """A reduction backend that hard-codes its own softmax scale (the reference's packed kernels apply D ** -0.5)
+    still realises the model's ``scaling`` when the query is multiplied by ``scaling / kernel_scale`` first, in
+    fp32 (fp64 stays fp64) so that the factor is not rounded into the bf16 query."""
+    work = torch.float64 if q.dtype == torch.float64 else torch.float32
+    return q.to(work) * (scaling / kernel_scale)
 
 
 class LimiteSimplicialAttention(nn.Module):
@@ -234,7 +252,17 @@ class LimiteSimplicialAttention(nn.Module):
         v1 = 1 + dv.view(B, T, c.num_key_value_heads, c.head_dim)
         w2 = T if n.is_global else c.window_span
         w1 = min(self.conversion.short_window, w2)
-        y = sx.simplicial_attention(q, k1.to(q.dtype), k2, v1.to(q.dtype), v2, w1, w2)
+        scaling, backend = self.conversion.scaling, self.conversion.backend
+        if backend == "reference":
+            y = sx.simplicial_attention_reference(q.float(), k1.float(), k2.float(), v1.float(), v2.float(), w1, w2, scale=scaling)
+        else:
+            if backend == "kernel":
+                from ..ops.simplicial_cuda import kernel_supports
+
+                if not (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 128 and kernel_supports(q, k1, v1, w1, w2)):
+                    raise RuntimeError("conversion.backend = 'kernel' but the sm_100a simplicial kernel does not take this "
+                                       f"input (device {q.device}, dtype {q.dtype}, head_dim {q.shape[-1]}, windows {w1} x {w2})")
+            y = sx.simplicial_attention(q, k1.to(q.dtype), k2, v1.to(q.dtype), v2, w1, w2, scale=scaling)
         return n.finish(h, y.to(h.dtype))
 
 

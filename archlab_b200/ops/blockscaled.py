@@ -348,3 +348,105 @@ def block_fp8_linear(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
 
 def block_fp8_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
     return _on_gpu(x) and weight.size(1) % 128 == 0 and weight.size(0) % 8 == 0 and x.size(-1) == weight.size(1)
+
+
+# ------------------------------------------------------------------------------------------------
+# Linear layer: NVFP4 training (forward, data gradient and weight gradient all on the FP4 tensor-core path)
+# ------------------------------------------------------------------------------------------------
+NVFP4_ALIGNMENT = 128          # both sides of a dense weight: keeps the reduction of all three GEMMs Hadamard-tile aligned
+
+
+class _Nvfp4Linear(torch.autograd.Function):
+    """The controls of the reference's NVFP4 recipe (src/archlab/speedrun/precision.py:170-205): weights in 16 x 16
+    blocks (so the transposed weight carries the same scales), stochastic rounding on gradients, a random Hadamard
+    transform on both operands of the weight-gradient product (it cancels in the product and spreads outliers).
+    Every product is ``A B^T`` with K contiguous, so the backward quantises transposed copies."""
+
+    @staticmethod
+    def forward(ctx, x, w, seed):
+        x2 = x.reshape(-1, x.size(-1)).to(torch.bfloat16).contiguous()
+        wb = w.to(torch.bfloat16).contiguous()
+        ctx.save_for_backward(x2, wb)
+        ctx.lead, ctx.dtypes, ctx.seed = x.shape[:-1], (x.dtype, w.dtype), int(seed)
+        y = gemm(quantize_nvfp4(x2), quantize_nvfp4(wb, two_d=True), out_dtype=torch.bfloat16)
+        return y.reshape(*x.shape[:-1], w.size(0)).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, wb = ctx.saved_tensors
+        seed = ctx.seed
+        dy2 = dy.reshape(-1, dy.size(-1)).to(torch.bfloat16).contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            # dX [M, K] = dY [M, N] W [N, K]: reduction over N -> B operand is W^T [K, N]
+            dx = gemm(quantize_nvfp4(dy2, sr_seed=seed), quantize_nvfp4(wb.t().contiguous(), two_d=True), out_dtype=torch.bfloat16)
+            dx = dx.reshape(*ctx.lead, wb.size(1)).to(ctx.dtypes[0])
+        if ctx.needs_input_grad[1]:
+            # dW [N, K] = dY^T [N, M] X^T[K, M]^T: reduction over the tokens, both operands Hadamard-transformed along it
+            M = dy2.size(0)
+            pad = (-M) % 16
+            dyt, xt = dy2.t().contiguous(), x2.t().contiguous()
+            if pad:
+                dyt, xt = torch.nn.functional.pad(dyt, (0, pad)), torch.nn.functional.pad(xt, (0, pad))
+            dw = gemm(quantize_nvfp4(dyt, hadamard_seed=seed | 1, sr_seed=seed + 1),
+                      quantize_nvfp4(xt, hadamard_seed=seed | 1), out_dtype=torch.float32).to(ctx.dtypes[1])
+        return dx, dw, None
+
+
+def nvfp4_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (weight.size(0) % NVFP4_ALIGNMENT == 0 and weight.size(1) % NVFP4_ALIGNMENT == 0 and x.size(-1) == weight.size(1)
+            and x.numel() // x.size(-1) % 64 == 0)
+
+
+def nvfp4_linear(x: torch.Tensor, weight: torch.Tensor, seed: int = 1) -> torch.Tensor:
+    """Bias-free linear whose three products run in NVFP4; ``seed`` drives stochastic rounding and the Hadamard signs
+    (pass the step number for fresh rounding noise every step)."""
+    return _Nvfp4Linear.apply(x, weight, seed)
+
+
+class BlockScaledLinear(torch.nn.Linear):
+    """``nn.Linear`` (no bias) re-classed onto a block-scaled recipe: ``recipe`` is "nvfp4" or "fp8_block".  Shapes the
+    recipe does not cover (a side not divisible by 128, a ragged token count) run in bf16 on the tcgen05 kernels -
+    the BF16 exceptions of the reference's FP4 contract (src/archlab/architectures/qwen38_flash_next.py:160-175)."""
+
+    recipe = "nvfp4"
+    step = 0
+
+    def forward(self, x):
+        w = self.weight
+        if self.recipe == "nvfp4" and nvfp4_supported(x, w):
+            return nvfp4_linear(x, w, seed=2 * self.step + 1)
+        if self.recipe == "fp8_block" and (block_fp8_supported(x, w) or not x.is_cuda) and w.size(1) % 128 == 0:
+            return block_fp8_linear(x, w)
+        from .native_linear import native_linear
+
+        return native_linear(x, w)
+
+
+def convert_linears(module: torch.nn.Module, recipe: str, *, skip: tuple[str, ...] = ("lm_head", "router", "gate")) -> dict:
+    """Re-classes the eligible bias-free linears of ``module`` in place and reports what ran where:
+    ``{"converted": [...], "bf16_exceptions": {name: reason}}``.  Routing logits, scalar gates and the output head stay
+    in bf16 by name; a weight side not divisible by 128 stays in bf16 by shape."""
+    if recipe not in ("nvfp4", "fp8_block"):
+        raise ValueError("recipe must be 'nvfp4' or 'fp8_block'")
+    report = {"recipe": recipe, "converted": [], "bf16_exceptions": {}}
+    for name, layer in module.named_modules():
+        if type(layer) is not torch.nn.Linear and type(layer).__name__ != "CastLinear":
+            continue
+        if layer.bias is not None:
+            report["bf16_exceptions"][name] = "bias"
+        elif any(part in name.split(".")[-1] for part in skip):
+            report["bf16_exceptions"][name] = "kept in bf16 by role"
+        elif layer.in_features % NVFP4_ALIGNMENT or layer.out_features % NVFP4_ALIGNMENT:
+            report["bf16_exceptions"][name] = f"{layer.out_features} x {layer.in_features} is not 128-aligned"
+        else:
+            layer.__class__ = type("BlockScaledLinear_" + recipe, (BlockScaledLinear,), {"recipe": recipe})
+            report["converted"].append(name)
+    return report
+
+
+def set_step(module: torch.nn.Module, step: int) -> None:
+    """Advances the rounding-noise seed of every converted layer (call once per optimizer step)."""
+    for layer in module.modules():
+        if isinstance(layer, BlockScaledLinear):
+            layer.step = step

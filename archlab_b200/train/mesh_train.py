@@ -116,8 +116,9 @@ def parse_args(argv=None):
     ap.add_argument("--global-batch", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=8192)
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8_block", "fp8_tensor", "nvfp4"],
-                    help="fp8_block: 1x128 / 128x128 block rounding with straight-through gradients (bf16 GEMMs); "
-                         "fp8_tensor: tensor-scaled e4m3 / e5m2 GEMMs on the 8-bit tensor-core path")
+                    help="fp8_block: 1x128 / 128x128 power-of-two block scales, forward products on the block-scaled FP8 GEMM, "
+                         "straight-through bf16 gradients; fp8_tensor: tensor-scaled e4m3 / e5m2 GEMMs; nvfp4: forward, "
+                         "data- and weight-gradient products in NVFP4 (2-D weight blocks, stochastic rounding, Hadamard)")
     ap.add_argument("--model-set", action="append", default=[], metavar="KEY=VALUE",
                     help="factory models: override a field of the family's config (repeatable; values parse as JSON)")
     ap.add_argument("--native-linears", action="store_true",
@@ -247,6 +248,11 @@ class _Job:
             from ..ops.fp8 import convert_linears
 
             self.fp8_layers = convert_linears(self.model)        # dense nn.Linear layers; expert and TP GEMMs stay bf16
+        if a.precision == "nvfp4" or (a.precision == "fp8_block" and fam != "v41"):
+            # block-scaled tensor-core products for the dense linears; what stays in BF16 and why is recorded
+            from ..ops.blockscaled import convert_linears as to_block_scaled
+
+            self.precision_report = to_block_scaled(self.model, "nvfp4" if a.precision == "nvfp4" else "fp8_block")
         if getattr(a, "native_linears", False) and not getattr(a, "fsdp", False):
             from ..ops.native_linear import convert_linears as to_native
 
@@ -329,7 +335,10 @@ CONTRACT_KEYS = ("model", "tp", "pp", "cp", "ep", "micro_batch", "global_batch",
 
 def run_contract(a, world: int) -> dict:
     """What must not change between the attempts of one run (a resume under a different contract is refused)."""
-    return {"format": "archlab-mesh-run-v1", "world_size": world, **{k: getattr(a, k) for k in CONTRACT_KEYS}}
+    from .precision_contract import FLAG_TO_PRECISION, precision_contract
+
+    return {"format": "archlab-mesh-run-v1", "world_size": world, **{k: getattr(a, k) for k in CONTRACT_KEYS},
+            "optimizer": getattr(a, "optimizer", "adamw"), "precision_contract": precision_contract(FLAG_TO_PRECISION[a.precision])}
 
 
 def check_contract(run_dir: Path, contract: dict, resume: bool) -> int:

@@ -146,3 +146,47 @@ def test_grouped_linear_fp8_forward_matches_bf16_path():
     assert _rel(y8[live], y16[live]) < 0.05
     y8[live].float().square().sum().backward()
     assert torch.isfinite(x.grad[live]).all() and torch.isfinite(w.grad).all()
+
+
+def test_nvfp4_linear_three_products_on_the_fp4_path():
+    from archlab_b200.ops import blockscaled as bs, native
+
+    torch.manual_seed(7)
+    x = torch.randn(512, 1024, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(768, 1024, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    g = torch.randn(512, 768, device="cuda").bfloat16()
+    assert bs.nvfp4_supported(x, w)
+    y = bs.nvfp4_linear(x, w, seed=3)
+    y.backward(g)
+    torch.cuda.synchronize()
+    native.check_status()
+    xf, wf, gf = x.detach().float(), w.detach().float(), g.float()
+    assert _rel(y, xf @ wf.t()) < 0.2
+    assert _rel(x.grad, gf @ wf) < 0.25
+    assert _rel(w.grad, gf.t() @ xf) < 0.25
+    # stochastic rounding: another seed gives other gradients with the same expectation
+    x2 = x.detach().clone().requires_grad_(True)
+    bs.nvfp4_linear(x2, w.detach(), seed=5).backward(g)
+    assert not torch.equal(x2.grad, x.grad) and _rel(x2.grad, gf @ wf) < 0.25
+
+
+def test_converted_model_trains_a_few_steps_in_nvfp4():
+    from archlab_b200.ops import blockscaled as bs
+
+    torch.manual_seed(8)
+    # fp32 master weights (the layers cast to bf16 and quantise per call), bf16 activations
+    net = torch.nn.Sequential(torch.nn.Linear(256, 512, bias=False), torch.nn.GELU(), torch.nn.Linear(512, 256, bias=False)).cuda()
+    rep = bs.convert_linears(net, "nvfp4")
+    assert len(rep["converted"]) == 2
+    opt = torch.optim.Adam(net.parameters(), lr=3e-3)
+    x = torch.randn(256, 256, device="cuda").bfloat16()
+    target = (x.float() @ torch.randn(256, 256, device="cuda") * 0.05).tanh()
+    losses = []
+    for step in range(60):
+        bs.set_step(net, step)
+        loss = (net(x).float() - target).square().mean()
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        losses.append(float(loss))
+    assert losses[-1] < 0.7 * losses[0], losses[::10]

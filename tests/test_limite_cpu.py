@@ -83,3 +83,38 @@ def test_static_cache_decoding_matches_full_forward():
         for t in range(12, 30):                                # crosses the sliding window (span 8) several times
             out = dec(ids[:, t:t + 1])
             assert torch.allclose(out, full[:, t], atol=1e-4), t
+
+
+def test_conversion_backend_tri_state_and_fixed_scale_query_rule():
+    import math
+
+    import pytest
+
+    torch.manual_seed(0)
+    with pytest.raises(ValueError):
+        L.ConversionConfig(backend="triton")
+    ids = torch.randint(0, 128, (1, 10))
+    outs = {}
+    for backend in ("auto", "reference"):
+        torch.manual_seed(1)
+        m = L.LimiteLM(L.LimiteConfig.tiny())
+        m.init_weights()
+        L.replace_limite_attention(m, L.ConversionConfig(short_window=4, backend=backend))
+        outs[backend] = m(ids)
+    torch.testing.assert_close(outs["auto"], outs["reference"], rtol=1e-4, atol=1e-4)
+    torch.manual_seed(1)
+    m = L.LimiteLM(L.LimiteConfig.tiny())
+    m.init_weights()
+    L.replace_limite_attention(m, L.ConversionConfig(short_window=4, backend="kernel"))
+    with pytest.raises(RuntimeError, match="kernel"):
+        m(ids)                                           # CPU, fp32: the kernel backend must refuse, not fall back
+    # a backend with a hard-coded D ** -0.5 realises `scaling` through a pre-scaled fp32 query
+    from archlab_b200.ops.simplicial import simplicial_attention_reference as ref
+
+    q, k = torch.randn(1, 6, 2, 16).bfloat16(), torch.randn(1, 6, 2, 16)
+    scaling, fixed = 0.31, 1 / math.sqrt(16)
+    pre = L.query_for_fixed_scale(q, scaling, fixed)
+    assert pre.dtype == torch.float32
+    a = ref(pre, k, k, k, k, 2, 4, scale=fixed)
+    b = ref(q.float(), k, k, k, k, 2, 4, scale=scaling)
+    torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
