@@ -141,6 +141,8 @@ def parse_args(argv=None):
     ap.add_argument("--run-dir", default="runs/mesh")
     ap.add_argument("--n-layer", type=int, default=0, help="override the preset's depth (0 keeps it)")
     ap.add_argument("--save-every", type=int, default=0, help="write a per-rank checkpoint every N steps (0: never)")
+    ap.add_argument("--bounded-staging", action="store_true",
+                    help="checkpoints: the local ranks of a host stage and write one at a time (bounds host memory)")
     ap.add_argument("--resume", action="store_true", help="continue from the newest checkpoint in --run-dir")
     return ap.parse_args(argv)
 
@@ -364,17 +366,42 @@ def check_contract(run_dir: Path, contract: dict, resume: bool) -> int:
     return attempt
 
 
-def save_checkpoint(run_dir: Path, step: int, rank: int, job, opt) -> None:
+def staged_by_local_rank(write, *, local_rank: int, local_world: int, barrier) -> None:
+    """Runs ``write()`` on one local rank of a host at a time.  Staging a rank's optimizer state for serialisation
+    copies it to host memory; with large owner-sharded tables, all local ranks staging at once can exceed the host's
+    memory, so the per-host order is bounded while every rank still writes its own file
+    (src/archlab/megatron/checkpoint_staging.py:15-64)."""
+    if local_world < 1 or not 0 <= local_rank < local_world:
+        raise RuntimeError(f"invalid local checkpoint topology: rank={local_rank}, world={local_world}")
+    import gc
+
+    for turn in range(local_world):
+        if turn == local_rank:
+            write()
+            gc.collect()                      # hand the staged host copies back before the next rank takes its turn
+        barrier()
+
+
+def save_checkpoint(run_dir: Path, step: int, rank: int, job, opt, *, bounded_staging: bool = False) -> None:
     """Every rank writes its own model shard and optimizer slice; rank 0 writes the step marker LAST."""
     d = run_dir / "checkpoints" / f"step_{step:07d}"
     d.mkdir(parents=True, exist_ok=True)
-    state = {"step": step, "model": job.model.state_dict(), "zero": opt.zero.state_dict(),
-             "experts": None if opt.experts is None else {"t": opt.experts.t, "master": opt.experts.master, "m": opt.experts.m,
-                                                          "v": opt.experts.v},
-             "rng": torch.get_rng_state()}
-    tmp = d / f".rank{rank:03d}.pt.tmp"
-    torch.save(state, tmp)
-    os.replace(tmp, d / f"rank{rank:03d}.pt")
+
+    def write():
+        state = {"step": step, "model": job.model.state_dict(), "zero": opt.zero.state_dict(),
+                 "experts": None if opt.experts is None else {"t": opt.experts.t, "master": opt.experts.master, "m": opt.experts.m,
+                                                              "v": opt.experts.v},
+                 "muon": None if getattr(opt, "muon", None) is None else opt.muon.state_dict(),
+                 "rng": torch.get_rng_state()}
+        tmp = d / f".rank{rank:03d}.pt.tmp"
+        torch.save(state, tmp)
+        os.replace(tmp, d / f"rank{rank:03d}.pt")
+
+    if bounded_staging and dist.is_initialized():
+        staged_by_local_rank(write, local_rank=int(os.environ.get("LOCAL_RANK", rank)),
+                             local_world=int(os.environ.get("LOCAL_WORLD_SIZE", dist.get_world_size())), barrier=dist.barrier)
+    else:
+        write()
     if dist.is_initialized():
         dist.barrier()
     if rank == 0:
@@ -394,6 +421,8 @@ def load_checkpoint(run_dir: Path, rank: int, job, opt) -> int:
         for name, b in job.model.named_buffers():
             if name in state["model"]:
                 b.copy_(state["model"][name])
+    if getattr(opt, "muon", None) is not None and state.get("muon") is not None:
+        opt.muon.load_state_dict(state["muon"])
     if opt.experts is not None and state["experts"] is not None:
         e = state["experts"]
         opt.experts.t = e["t"]
@@ -593,7 +622,7 @@ def train(a, *, on_step=None) -> list[float]:
             on_step(step, losses[-1])
         stopping = stop.should_stop()
         if (a.save_every and ((step + 1) % a.save_every == 0 or step + 1 == a.steps)) or stopping:
-            save_checkpoint(run_dir, step + 1, rank, job, opt)
+            save_checkpoint(run_dir, step + 1, rank, job, opt, bounded_staging=getattr(a, "bounded_staging", False))
         reached = step + 1
         if stopping:                                             # every rank leaves at the same step, after the checkpoint
             stop.acknowledge(step + 1, rank)
