@@ -20,6 +20,11 @@ int nga_simplicial_bwd(const void* q, const void* k1, const void* k2, const void
                        long long ldk1, long long ldk2, long long ldv1, long long ldv2, long long ldo, long long lddo,
                        long long lddq, long long lddk1, long long lddk2, long long lddv1, long long lddv2, int B,
                        int N, int Hq, int Hkv, int D, int w1, int w2, float scale, int* status, void* stream);
+// Atomic-free, bit-reproducible mode for the next nga_simplicial_bwd call of the calling thread: fp32 scratch for the
+// per-row short-key contributions ([B*N * w1 * Hq, 128] each) and, when Hq > Hkv, for the per-head planes of the long-key
+// gradients ([Hq / Hkv][B*N, Hkv*128] each; null otherwise).  Without this call dk1 / dv1 (and dk2 / dv2 under GQA)
+// are accumulated with fp32 vector atomics, whose order varies from run to run.
+void nga_simplicial_bwd_set_deterministic(float* dk1_part, float* dv1_part, float* dk2_part, float* dv2_part);
 #ifdef __cplusplus
 }
 #endif

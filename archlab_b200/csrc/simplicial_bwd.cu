@@ -38,6 +38,11 @@ struct SimpBwdParams {
   float* dv1;                  // [B*N, Hkv*D] fp32, zeroed by the launcher
   float* dk2;                  // [B*N, Hkv*D] fp32, zeroed by the launcher
   float* dv2;
+  // Deterministic mode (null otherwise): every (query, short key, query head) row stores its dk1 / dv1 contribution
+  // at [(query row * w1 + short-key slot) * Hq + head][D] instead of adding it atomically; a second kernel sums the
+  // contributions of a key in a fixed order.
+  float* dk1_part;
+  float* dv1_part;
   long long ldq, ldk1, ldv1, lddo, lddq;
   int B, N, Hq, Hkv, w1, w2;
   float scale, scale_log2;
@@ -78,6 +83,52 @@ __global__ void simp_cast_kernel(const float* __restrict__ acc, __nv_bfloat16* _
   uint2 u;
   u.x = pack_bf16(v.x, v.y);
   u.y = pack_bf16(v.z, v.w);
+  *reinterpret_cast<uint2*>(dst + row * ld + c) = u;
+}
+
+// Deterministic reductions.  dk1[b, j, hk, :] = sum over short-key slots jj (ascending) and the query heads of the
+// group (ascending) of the contribution stored by query i = j + w1 - 1 - jj; one thread per 4 channels.
+__global__ void simp_reduce_short_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ dst, int B, int N, int Hq,
+                                         int Hkv, int w1, long long ld) {
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int cols4 = Hkv * SB_D / 4;
+  if (t >= (long long)B * N * cols4) return;
+  const long long row = t / cols4;
+  const int c4 = int(t - row * cols4);
+  const int hk = (c4 * 4) / SB_D, d = (c4 * 4) % SB_D;
+  const int b = int(row / N), j = int(row - (long long)b * N);
+  const int group = Hq / Hkv;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int jj = 0; jj < w1; ++jj) {
+    const int i = j + w1 - 1 - jj;
+    if (i >= N) continue;
+    const long long qrow = (long long)b * N + i;
+    for (int g = 0; g < group; ++g) {
+      const float4 v = *reinterpret_cast<const float4*>(part + ((qrow * w1 + jj) * Hq + hk * group + g) * (long long)SB_D + d);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+  }
+  uint2 u;
+  u.x = pack_bf16(acc.x, acc.y);
+  u.y = pack_bf16(acc.z, acc.w);
+  *reinterpret_cast<uint2*>(dst + row * ld + c4 * 4) = u;
+}
+
+// dst[row, c] = bf16(sum over planes g = 0 .. group-1, ascending, of part[g][row, c]).
+__global__ void simp_reduce_planes_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ dst, long long rows, int cols,
+                                          int group, long long ld) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= rows * cols) return;
+  const long long row = i / cols;
+  const int c = int(i % cols);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int g = 0; g < group; ++g) {
+    const float4 v = *reinterpret_cast<const float4*>(part + (long long)g * rows * cols + i);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  uint2 u;
+  u.x = pack_bf16(acc.x, acc.y);
+  u.y = pack_bf16(acc.z, acc.w);
   *reinterpret_cast<uint2*>(dst + row * ld + c) = u;
 }
 
@@ -376,6 +427,7 @@ simplicial_bwd_q_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
       float* red = reinterpret_cast<float*>(smem + S::kK);
       float* dk1row = p.dk1 + krow_idx * ((long long)p.Hkv * SB_D) + hk * SB_D;
       float* dv1row = p.dv1 + krow_idx * ((long long)p.Hkv * SB_D) + hk * SB_D;
+      const long long part_off = ((qrow_idx * p.w1 + jj) * p.Hq + h) * (long long)SB_D;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint4 kk[4], qq[4], gg[4];                         // loads first: the atomics below would pin them in place
@@ -408,7 +460,14 @@ simplicial_bwd_q_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
             dvv[2 * e] = o0 * gf.x;
             dvv[2 * e + 1] = o1 * gf.y;
           }
-          if (row_valid) {
+          if (row_valid && p.dk1_part != nullptr) {
+            float* pk1 = p.dk1_part + part_off + c * 32 + g * 8;
+            float* pv1 = p.dv1_part + part_off + c * 32 + g * 8;
+            *reinterpret_cast<float4*>(pk1) = make_float4(dk[0], dk[1], dk[2], dk[3]);
+            *reinterpret_cast<float4*>(pk1 + 4) = make_float4(dk[4], dk[5], dk[6], dk[7]);
+            *reinterpret_cast<float4*>(pv1) = make_float4(dvv[0], dvv[1], dvv[2], dvv[3]);
+            *reinterpret_cast<float4*>(pv1 + 4) = make_float4(dvv[4], dvv[5], dvv[6], dvv[7]);
+          } else if (row_valid) {
             atomicAdd(reinterpret_cast<float4*>(dk1row + c * 32 + g * 8), make_float4(dk[0], dk[1], dk[2], dk[3]));
             atomicAdd(reinterpret_cast<float4*>(dk1row + c * 32 + g * 8 + 4), make_float4(dk[4], dk[5], dk[6], dk[7]));
             atomicAdd(reinterpret_cast<float4*>(dv1row + c * 32 + g * 8), make_float4(dvv[0], dvv[1], dvv[2], dvv[3]));
@@ -472,6 +531,8 @@ struct SimpBwdKParams {
   long long lddk2, lddv2;
   float* dk2_acc;              // [B*N, Hkv*D] fp32, zeroed by the launcher: target of the per-query-head CTAs'
   float* dv2_acc;              //   vector atomics when a KV head serves several query heads
+  float* dk2_part;             // deterministic mode: [group][B*N, Hkv*D] fp32, one plane per query head of a KV group
+  float* dv2_part;             //   (plain stores; summed in head order afterwards)
 };
 
 // Optional phase cycle counters (16 slots), written by CTA (0,0,0) of the key-owned kernel.
@@ -810,6 +871,17 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
               *reinterpret_cast<uint4*>(dkrow + c * 32 + gq * 8) = u;
               *reinterpret_cast<uint4*>(dvrow + c * 32 + gq * 8) = w;
             }
+          } else if (pk.dk2_part != nullptr) {
+            const long long plane = (long long)(hq % group) * p.B * p.N * ((long long)p.Hkv * SB_D);
+            float* pkd = pk.dk2_part + plane + krow * ((long long)p.Hkv * SB_D) + hk * SB_D + c * 32;
+            float* pvd = pk.dv2_part + plane + krow * ((long long)p.Hkv * SB_D) + hk * SB_D + c * 32;
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4) {
+              *reinterpret_cast<float4*>(pkd + q4 * 4) = make_float4(__uint_as_float(a[4 * q4]), __uint_as_float(a[4 * q4 + 1]),
+                                                                     __uint_as_float(a[4 * q4 + 2]), __uint_as_float(a[4 * q4 + 3]));
+              *reinterpret_cast<float4*>(pvd + q4 * 4) = make_float4(__uint_as_float(v[4 * q4]), __uint_as_float(v[4 * q4 + 1]),
+                                                                     __uint_as_float(v[4 * q4 + 2]), __uint_as_float(v[4 * q4 + 3]));
+            }
           } else {
 #pragma unroll
             for (int q4 = 0; q4 < 8; ++q4) {
@@ -840,6 +912,14 @@ simplicial_bwd_k_kernel(const __grid_constant__ CUtensorMap tm_k2, const __grid_
 
 extern "C" void nga_simplicial_bwd_set_prof(long long* device_ptr) { nga::g_simp_prof = device_ptr; }
 
+// Deterministic (atomic-free, bit-reproducible) mode for the NEXT call of nga_simplicial_bwd on this thread: scratch for
+// the per-row short-key contributions, [B*N * w1 * Hq, 128] fp32 each, and (only when Hq > Hkv, else null) the per-head
+// planes of the long-key gradients, [Hq / Hkv][B*N, Hkv*128] fp32 each.  The pointers are consumed by that call.
+static thread_local float* g_det[4] = {nullptr, nullptr, nullptr, nullptr};
+extern "C" void nga_simplicial_bwd_set_deterministic(float* dk1_part, float* dv1_part, float* dk2_part, float* dv2_part) {
+  g_det[0] = dk1_part; g_det[1] = dv1_part; g_det[2] = dk2_part; g_det[3] = dv2_part;
+}
+
 // Backward of nga_simplicial_fwd.  `out`, `lse2` come from the forward pass.  dq / dk2 / dv2 are
 // written as bf16 (strided like their inputs); dk1 / dv1 are accumulated in the fp32 scratch
 // buffers `dk1_acc` / `dv1_acc` ([B*N, Hkv*128], zeroed here) and cast into dk1 / dv1; `dk2_acc` /
@@ -860,6 +940,10 @@ extern "C" int nga_simplicial_bwd(const void* q, const void* k1, const void* k2,
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const long long rows = (long long)B * N;
   const long long kvcols = (long long)Hkv * D;
+  float* det[4] = {g_det[0], g_det[1], g_det[2], g_det[3]};
+  g_det[0] = g_det[1] = g_det[2] = g_det[3] = nullptr;
+  const bool deterministic = det[0] != nullptr && det[1] != nullptr;
+  if (deterministic && Hq != Hkv && (det[2] == nullptr || det[3] == nullptr)) return -7;
   CUtensorMap tk64, tv64, tk128, tv128;
   int rc = make_tmap_3d(&tk64, k2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, kvcols, rows, 1, ldk2 * 2, rows * ldk2 * 2, 64, 64, true);
   if (rc) return rc;
@@ -888,8 +972,10 @@ extern "C" int nga_simplicial_bwd(const void* q, const void* k1, const void* k2,
         N, Hq);
     count_launch();
   }
-  cudaMemsetAsync(dk1_acc, 0, sizeof(float) * rows * kvcols, st);
-  cudaMemsetAsync(dv1_acc, 0, sizeof(float) * rows * kvcols, st);
+  if (!deterministic) {
+    cudaMemsetAsync(dk1_acc, 0, sizeof(float) * rows * kvcols, st);
+    cudaMemsetAsync(dv1_acc, 0, sizeof(float) * rows * kvcols, st);
+  }
   SimpBwdParams p;
   p.q = reinterpret_cast<const __nv_bfloat16*>(q);
   p.k1 = reinterpret_cast<const __nv_bfloat16*>(k1);
@@ -902,6 +988,8 @@ extern "C" int nga_simplicial_bwd(const void* q, const void* k1, const void* k2,
   p.dv1 = dv1_acc;
   p.dk2 = nullptr;
   p.dv2 = nullptr;
+  p.dk1_part = deterministic ? det[0] : nullptr;
+  p.dv1_part = deterministic ? det[1] : nullptr;
   p.ldq = ldq; p.ldk1 = ldk1; p.ldv1 = ldv1; p.lddo = lddo; p.lddq = lddq;
   p.B = B; p.N = N; p.Hq = Hq; p.Hkv = Hkv; p.w1 = w1; p.w2 = w2;
   p.scale = scale;
@@ -921,7 +1009,9 @@ extern "C" int nga_simplicial_bwd(const void* q, const void* k1, const void* k2,
     pk.lddk2 = lddk2; pk.lddv2 = lddv2;
     pk.dk2_acc = dk2_acc; pk.dv2_acc = dv2_acc;
     pk.prof = g_simp_prof;
-    if (Hq != Hkv) {
+    pk.dk2_part = (deterministic && Hq != Hkv) ? det[2] : nullptr;
+    pk.dv2_part = (deterministic && Hq != Hkv) ? det[3] : nullptr;
+    if (Hq != Hkv && pk.dk2_part == nullptr) {
       if (dk2_acc == nullptr || dv2_acc == nullptr) return -7;
       cudaMemsetAsync(dk2_acc, 0, sizeof(float) * rows * kvcols, st);
       cudaMemsetAsync(dv2_acc, 0, sizeof(float) * rows * kvcols, st);
@@ -930,7 +1020,15 @@ extern "C" int nga_simplicial_bwd(const void* q, const void* k1, const void* k2,
     auto kern = w1 == 8 ? simplicial_bwd_k_kernel<8> : (w1 == 16 ? simplicial_bwd_k_kernel<16> : simplicial_bwd_k_kernel<32>);
     kern<<<grid, SK_THREADS, SimpBwdKSmem::kTotal, st>>>(tk128, tv128, pk);
     count_launch();
-    if (Hq != Hkv) {
+    if (Hq != Hkv && pk.dk2_part != nullptr) {
+      const long long n4 = rows * kvcols / 4;
+      simp_reduce_planes_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(pk.dk2_part, reinterpret_cast<__nv_bfloat16*>(dk2), rows,
+                                                                             (int)kvcols, Hq / Hkv, lddk2);
+      count_launch();
+      simp_reduce_planes_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(pk.dv2_part, reinterpret_cast<__nv_bfloat16*>(dv2), rows,
+                                                                             (int)kvcols, Hq / Hkv, lddv2);
+      count_launch();
+    } else if (Hq != Hkv) {
       const long long n4 = rows * kvcols / 4;
       simp_cast_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dk2_acc, reinterpret_cast<__nv_bfloat16*>(dk2), rows,
                                                                     (int)kvcols, lddk2);
@@ -940,7 +1038,15 @@ extern "C" int nga_simplicial_bwd(const void* q, const void* k1, const void* k2,
       count_launch();
     }
   }
-  {
+  if (deterministic) {
+    const long long n4 = rows * kvcols / 4;
+    simp_reduce_short_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(det[0], reinterpret_cast<__nv_bfloat16*>(dk1), B, N, Hq, Hkv,
+                                                                          w1, lddk1);
+    count_launch();
+    simp_reduce_short_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(det[1], reinterpret_cast<__nv_bfloat16*>(dv1), B, N, Hq, Hkv,
+                                                                          w1, lddv1);
+    count_launch();
+  } else {
     const long long n4 = rows * kvcols / 4;
     simp_cast_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(dk1_acc, reinterpret_cast<__nv_bfloat16*>(dk1), rows,
                                                                   (int)kvcols, lddk1);
