@@ -69,6 +69,8 @@ class ParamStore:
             attn, mlp = block.attn, block.mlp
             mats = [attn.c_q.weight, attn.c_k.weight, attn.c_v.weight, attn.c_proj.weight,
                     mlp.c_fc.weight, mlp.c_proj.weight]
+            if hasattr(attn, "c_k2"):                      # 2-simplicial layer: second key / value branch
+                mats += [attn.c_k2.weight, attn.c_v2.weight]
             if attn.ve_gate is not None:
                 mats.append(attn.ve_gate.weight)
             for p in mats:
@@ -150,8 +152,6 @@ class FusedGPTEngine:
         cfg = model.config
         if cfg.head_dim != 128:
             raise ValueError("the fused engine supports head_dim 128")
-        if cfg.simplicial_layers:
-            raise ValueError("simplicial layers run through the eager model")
         if cfg.n_embd % 8 or cfg.padded_vocab != cfg.vocab_size:
             raise ValueError("n_embd must be a multiple of 8 and the vocabulary a multiple of 64")
         if model.lm_head.weight.device.type != "cuda":
@@ -159,6 +159,15 @@ class FusedGPTEngine:
         native.lib()   # fail loudly if the native library is missing
         self.model, self.cfg = model, cfg
         self.store = ParamStore(model, world, symmetric, group)
+        # A 2-simplicial layer keeps its module as the statement of the mixer (five projections, RoPE + norms, the
+        # simplicial kernels) and runs under autograd inside the otherwise hand-written step: its linears go onto the
+        # tcgen05 GEMMs, its weight gradients accumulate into the store's fp32 buffers through ``p.grad``.
+        self.simplicial = set(cfg.simplicial_layers)
+        if self.simplicial:
+            from ..ops.native_linear import convert_linears
+
+            for i in self.simplicial:
+                convert_linears(model.transformer.h[i].attn, min_features=64)
         self.head_chunk = head_chunk
         dev = model.lm_head.weight.device
         self.dev = dev
@@ -230,6 +239,20 @@ class FusedGPTEngine:
         x = x0
         for i, block in enumerate(m.transformer.h):
             x1, n1 = trunk.mix_norm_fwd(x, x0, m.resid_lambdas.data[i:i + 1], m.x0_lambdas.data[i:i + 1])
+            if i in self.simplicial:
+                leaf = n1.detach().requires_grad_(True)
+                with torch.enable_grad():
+                    mixed = block.attn(leaf.view(B, T, C), None, m.cos[:T].to(n1.dtype), m.sin[:T].to(n1.dtype), m.window_sizes[i])
+                x2 = x1 + mixed.detach().reshape(-1, C)
+                sv.setdefault("simplicial", {})[i] = (leaf, mixed)
+                _, n2 = trunk.mix_norm_fwd(x2)
+                act = gemm(n2, st.shadow_of(block.mlp.c_fc.weight), epi=EPI_RELU2)
+                x3 = gemm(act, st.shadow_of(block.mlp.c_proj.weight), aux=x2, epi=EPI_AXPBY, alpha=1.0, beta=1.0)
+                for lst, v in ((xs, x3), (x1s, x1), (n1s, n1), (qkvs, None), (ys, None), (lses, None), (x2s, x2),
+                               (n2s, n2), (acts, act), (rstds, None), (gps, None)):
+                    lst.append(v)
+                x = x3
+                continue
             wqkv, _ = self._wqkv(i)
             qkv = gemm(n1, wqkv)
             ve_name = f"ve{i}"
@@ -311,6 +334,17 @@ class FusedGPTEngine:
             gemm(dh, n2, a_mn=True, b_mn=True, out=g_fc, epi=EPI_ATOMIC_ADD)
             del dh
             dx2 = trunk.norm_bwd(x2, dn2, dx)
+            if i in self.simplicial:
+                leaf, mixed = sv["simplicial"].pop(i)
+                with torch.enable_grad():
+                    mixed.backward(dx2.view_as(mixed))        # weight gradients land in the store through p.grad
+                dn1 = leaf.grad
+                dx = trunk.norm_bwd_mix(sv["x1"][i], dn1, dx2, m.resid_lambdas.data[i:i + 1],
+                                        m.x0_lambdas.data[i:i + 1], xs[i], x0, dx0, i == L - 1,
+                                        m.resid_lambdas.grad[i:i + 1], m.x0_lambdas.grad[i:i + 1])
+                for k in ("act", "n2", "x2", "n1", "x1"):
+                    sv[k][i] = None
+                continue
             # ---- attention
             dy = gemm(dx2, w_o, b_mn=True)
             gemm(dx2, y, a_mn=True, b_mn=True, out=g_o, epi=EPI_ATOMIC_ADD)

@@ -54,7 +54,7 @@ class Trainer:
         model.init_weights()
         self.model = model
         self.engine = None
-        if self.device.type == "cuda" and cfg.use_engine and not cfg.model.simplicial_layers:
+        if self.device.type == "cuda" and cfg.use_engine and cfg.model.head_dim == 128:
             from ..models.nanochat_engine import FusedGPTEngine
 
             ws = coll.world_size()

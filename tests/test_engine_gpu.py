@@ -70,3 +70,47 @@ def test_trainer_loss_decreases():
     tok = torch.randint(0, 64, (4, 257), generator=g).pin_memory()
     losses = [tr.train_step(tok) for _ in range(12)]
     assert losses[-1] < losses[0] - 0.5, losses
+
+
+def test_engine_runs_a_simplicial_layer_and_matches_eager():
+    """A 2-simplicial layer inside the fused engine (module under autograd, kernels for the mixer and its linears)
+    against the eager fp32 model: loss and every gradient, including the second key / value branch."""
+    from archlab_b200.models.nanochat import GPT, GPTConfig
+    from archlab_b200.models.nanochat_engine import FusedGPTEngine
+    from archlab_b200.ops import native
+
+    cfg = GPTConfig(sequence_len=256, vocab_size=1024, n_layer=4, n_head=2, n_kv_head=2, n_embd=256, compute_dtype=torch.float32,
+                    matrix_init_recipe="normal-0.02", simplicial_layers=(2,), simplicial_w1=16, simplicial_w2=64)
+    torch.manual_seed(0)
+    m = GPT(cfg).to("cuda")
+    m.init_weights()
+    with torch.no_grad():
+        m.smear_lambda.fill_(0.3)                       # with the gate closed its weight has no gradient to compare
+        m.lm_head.weight.normal_(0, 0.05)
+        for p in m.parameters():
+            if p.ndim >= 2:
+                p.copy_(p.bfloat16().float())
+    idx = torch.randint(0, cfg.vocab_size, (2, cfg.sequence_len), device="cuda")
+    tgt = idx.roll(-1, 1).clone()
+    tgt[:, -1] = -1
+    m.train()
+    loss = m(idx, tgt, loss_reduction="sum")
+    loss.backward()
+    ref = {n: p.grad.detach().float().clone() for n, p in m.named_parameters()}
+    for p in m.parameters():
+        p.grad = None
+    eng = FusedGPTEngine(m, head_chunk=256)
+    eng.store.zero_grads()
+    got = eng.forward_backward(idx, tgt, 1.0)
+    eng.finish_step()
+    torch.cuda.synchronize()
+    native.check_status()
+    assert abs(got.item() - loss.item()) / loss.item() < 3e-3
+    names = [n for n, _ in m.named_parameters() if ".2.attn." in n]
+    assert any("c_k2" in n for n in names) and any("c_v2" in n for n in names)
+    for n, p in m.named_parameters():
+        if p.ndim < 2:
+            continue
+        g, r = p.grad.float(), ref[n]
+        cos = torch.nn.functional.cosine_similarity(g.flatten(), r.flatten(), dim=0).item()
+        assert cos > 0.995, (n, cos)
