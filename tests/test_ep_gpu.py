@@ -59,16 +59,17 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_fused_ep_moe_matches_all_to_all(tmp_path):
+@pytest.mark.parametrize("world", [pytest.param(w, marks=pytest.mark.skipif(torch.cuda.device_count() < w, reason=f"needs {w} GPUs"))
+                                   for w in (2, 4, 8)])
+def test_fused_ep_moe_matches_all_to_all(tmp_path, world):
     ctx = mp.get_context("spawn")
-    procs = [ctx.Process(target=_worker, args=(r, 2, 29641, str(tmp_path))) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, 29641 + world, str(tmp_path))) for r in range(world)]
     for p in procs:
         p.start()
     from conftest import join_ranks
 
     join_ranks(procs)
-    for r in range(2):
+    for r in range(world):
         res = torch.load(tmp_path / f"ep_rank{r}.pt")
         for key, v in res.items():
             assert v < 3e-2, (r, key, v)

@@ -77,16 +77,17 @@ def _check_group(grp, tag, res, rank, world, dev):
             lay.weight.grad = None
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_fused_weight_gather_gemms(tmp_path):
+@pytest.mark.parametrize("world", [pytest.param(w, marks=pytest.mark.skipif(torch.cuda.device_count() < w, reason=f"needs {w} GPUs"))
+                                   for w in (2, 4, 8)])
+def test_fused_weight_gather_gemms(tmp_path, world):
     ctx = mp.get_context("spawn")
-    procs = [ctx.Process(target=_worker, args=(r, 2, 29661, str(tmp_path))) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, 29661 + world, str(tmp_path))) for r in range(world)]
     for p in procs:
         p.start()
     from conftest import join_ranks
 
     join_ranks(procs, timeout=300)
-    for r in range(2):
+    for r in range(world):
         res = torch.load(tmp_path / f"fsdp_rank{r}.pt")
         for k, v in res.items():
             tol = 1e-6 if k.startswith(("w", "pad")) else 1.5e-2

@@ -9,6 +9,7 @@ import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+WORLDS = [pytest.param(w, marks=pytest.mark.skipif(torch.cuda.device_count() < w, reason=f"needs {w} GPUs")) for w in (2, 4, 8)]
 
 
 def _worker(rank, world, port, out_dir):
@@ -53,16 +54,16 @@ def _worker(rank, world, port, out_dir):
     dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_fused_tp_gemms_match_decomposed(tmp_path):
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_tp_gemms_match_decomposed(tmp_path, world):
     ctx = mp.get_context("spawn")
-    procs = [ctx.Process(target=_worker, args=(r, 2, 29631, str(tmp_path))) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, 29631 + world, str(tmp_path))) for r in range(world)]
     for p in procs:
         p.start()
     from conftest import join_ranks
 
     join_ranks(procs)
-    for r in range(2):
+    for r in range(world):
         res = torch.load(tmp_path / f"tp_rank{r}.pt")
         for k, v in res.items():
             assert v < (1e-6 if k.startswith("gathered") else 1e-2), (r, k, v)
