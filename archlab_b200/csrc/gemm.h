@@ -34,6 +34,16 @@ int nga_gemm2_bf16(const void* A, const void* B, void* D, const void* aux, int M
                    int epi, int out_fp32, int aux_fp32, float alpha, float beta, int splits,
                    int* status, void* stream);
 
+// Owner-push all-gather -> GEMM and GEMM -> reduce-scatter finished in the kernel (gemm2.cu; no barrier kernels, no copy
+// clusters, no separate reduction pass).  `*_ptrs` are HOST arrays of `world` device addresses of symmetric buffers.
+int nga_tp_gemm_push_bf16(const void* x_local, const void* B, void* D, int M, int N, int K, long long ldb, long long ldd,
+                          int b_mn, int rank, int world, int rows_per_rank, const long long* gathered_ptrs,
+                          const long long* flag_ptrs, int epoch, int* status, void* stream);
+int nga_tp_gemm_rs_reduce_bf16(const void* A, const void* B, void* out, const void* resid, int M, int N, int K, long long ldb,
+                               long long ld_out, long long ld_resid, int b_mn, int rank, int world, int rows_per_rank,
+                               const long long* slot_ptrs, const long long* counter_ptrs, int call_index, int* status,
+                               void* stream);
+
 // Tensor-parallel GEMM fused with its collective over NVLink peer memory (CTA-pair kernel).
 // mode 1: all-gather of A row shards -> GEMM; mode 2: GEMM -> reduce-scatter of D row blocks into the
 // owners' staging slots, summed by nga_tp_reduce_slots after a cross-rank barrier.  See gemm2.cu.

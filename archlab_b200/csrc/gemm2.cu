@@ -61,10 +61,11 @@ __device__ __forceinline__ int ld_acquire_sys(const int* addr) {
   return v;
 }
 // Bounded wait for a gathered 128-row block; false (and the abort word set) when the budget runs out.
-__device__ __forceinline__ bool wait_block_ready(const int* flag, int epoch, volatile int* abort_word) {
-  if (ld_acquire_gpu(flag) >= epoch) return true;
+// `sys`: the flag is written by another GPU (owner-push), so the acquire has system scope.
+__device__ __forceinline__ bool wait_block_ready(const int* flag, int epoch, volatile int* abort_word, bool sys = false) {
+  if ((sys ? ld_acquire_sys(flag) : ld_acquire_gpu(flag)) >= epoch) return true;
   const long long t0 = clock64();
-  while (ld_acquire_gpu(flag) < epoch) {
+  while ((sys ? ld_acquire_sys(flag) : ld_acquire_gpu(flag)) < epoch) {
     if (*abort_word != 0) return false;
     if (clock64() - t0 > kWaitBudgetCycles) {
       *abort_word = kErrPeerTimeout;
@@ -121,6 +122,37 @@ __device__ __forceinline__ void tp_copy_role(const TpParams& tp, int K, uint8_t*
   }
 }
 
+__device__ __forceinline__ void red_release_sys_add(int* addr, int v) {
+  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+// Owner-push all-gather, run by the 256 epilogue threads of a CTA (`tid` 0..255) before their tile loop.  Work item =
+// (destination rank, 128-row block, one of `tp.push_parts` row slices of it); remote ranks first.  Every finished
+// slice adds one to the destination's counter of that block, which therefore reads epoch * push_parts when the
+// block of this call is complete.
+__device__ __forceinline__ void tp_push_role(const TpParams& tp, int tid, int cta, int num_ctas) {
+  const int bpr = tp.rows_per_rank / BM;
+  const int parts = tp.push_parts;
+  const int items = tp.world * bpr * parts;
+  const long long part_bytes = (long long)(BM / parts) * tp.row_elems * 2;
+  const int n16 = int(part_bytes >> 4);
+  for (int it = cta; it < items; it += num_ctas) {
+    const int peer = (tp.rank + 1 + it / (bpr * parts)) % tp.world;
+    const int sub = it % (bpr * parts);                     // slice index inside this rank's shard
+    const int blk = sub / parts;
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(tp.push_src) + sub * part_bytes);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(tp.peer_dst[peer]) +
+                                          (long long)tp.rank * tp.rows_per_rank * tp.row_elems * 2 + sub * part_bytes);
+    int i = tid;
+    for (; i + 768 < n16; i += 1024) {                       // four loads in flight per thread
+      const uint4 a = __ldg(src + i), b = __ldg(src + i + 256), c = __ldg(src + i + 512), d = __ldg(src + i + 768);
+      dst[i] = a; dst[i + 256] = b; dst[i + 512] = c; dst[i + 768] = d;
+    }
+    for (; i < n16; i += 256) dst[i] = __ldg(src + i);
+    __threadfence_system();                                   // this thread's stores before the counter, at system scope
+    asm volatile("bar.sync 1, 256;" ::: "memory");           // all 256 pushing threads have fenced
+    if (tid == 0) red_release_sys_add(tp.peer_flags[peer] + tp.rank * bpr + blk, 1);
+  }
+}
 // F8: 0 = bf16 operands; 1 + 2 * (A is e5m2) + 4 * (B is e5m2) = 8-bit operands (K-major only, 128 per k-block).
 template <int A_MN, int B_MN, int TP, int F8 = 0>
 __global__ void __launch_bounds__(G2_THREADS, 1)
@@ -139,7 +171,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();          // 0 = leader
   // With the all-gather fused in, the first `copy_clusters` clusters only move data.
-  const int copy_clusters = (TP && (tp.mode & kTpGatherAny)) ? tp.copy_clusters : 0;
+  const int copy_clusters = (TP && (tp.mode & kTpGatherAny) && !(tp.mode & kTpPush)) ? tp.copy_clusters : 0;
   const bool copy_role = TP && int(blockIdx.x >> 1) < copy_clusters;
   const int cluster_id = int(blockIdx.x >> 1) - copy_clusters;
   const int num_clusters = int(gridDim.x >> 1) - copy_clusters;
@@ -222,7 +254,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             mapA = &tmA2;
             m0 -= owner * tp.rows_per_rank;
           } else {
-            ok = wait_block_ready(tp.flags + m0 / BM, tp.epoch, abort_word);
+            ok = (tp.mode & kTpPush) ? wait_block_ready(tp.flags + m0 / BM, tp.epoch * tp.push_parts, abort_word, true)
+                                     : wait_block_ready(tp.flags + m0 / BM, tp.epoch, abort_word);
             if (!ok) break;
             fence_proxy_async_all();
           }
@@ -334,6 +367,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const bool need_aux = (p.epi == kEpiAxpby || p.epi == kEpiMulDRelu2);
     const bool aux_fast = aux_prefetchable(p);
     uint32_t out_cnt = 0;
+    if (TP && (tp.mode & kTpPush)) tp_push_role(tp, int(threadIdx.x) - 64, int(blockIdx.x), int(gridDim.x));
+    const bool reduce_mode = TP && (tp.mode & kTpScatter) && (tp.mode & kTpReduce);
     for (int it = 0, tile = seq.at(0); tile < num_tiles && ok; tile = seq.at(++it)) {
       int b, mb, nb, otile, kb0, kb1;
       split_range(tile, p.splits, num_kb, otile, kb0, kb1);
@@ -353,7 +388,57 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tc_fence_after();
       const uint32_t taddr = tmem_base + uint32_t(acc * G2_BN) + (uint32_t(quarter * 32) << 16);
       const bool scatter = TP && (tp.mode & kTpScatter);
-      if (scatter || p.tma_store) {
+      int signal_owner = -1;
+      if (reduce_mode && (mb * 2 * BM) / tp.rows_per_rank == tp.rank) {
+        // a tile this rank owns: wait for the partial tiles of the other ranks, then sum and write the final rows
+        const int per = tp.rows_per_rank / (2 * BM);
+        const int* counter = tp.flags + (mb - tp.rank * per) * num_n + nb;
+        bool arrived = true;
+        if (lane == 0) arrived = wait_block_ready(counter, tp.arrivals, abort_word, true);
+        ok = __all_sync(0xffffffffu, arrived);
+        if (!ok) break;
+        const int lrow = row - tp.rank * tp.rows_per_rank;               // row inside this rank's slice
+        const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(tp.peer_dst[tp.rank]);
+        const __nv_bfloat16* resid = reinterpret_cast<const __nv_bfloat16*>(tp.resid);
+        __nv_bfloat16* outp = reinterpret_cast<__nv_bfloat16*>(tp.reduce_out);
+#pragma unroll 1
+        for (int c = chalf * 4; c < chalf * 4 + 4; ++c) {                 // 32-column chunks of this warp's half
+          const int col0 = nb * G2_BN + c * 32;
+          if (col0 >= p.N) break;   // warp-uniform
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + uint32_t(c * 32), r);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = p.alpha * __uint_as_float(r[i]);
+          auto add_row = [&](const __nv_bfloat16* src) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 pk = *reinterpret_cast<const uint4*>(src + q * 8);
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(h[e]);
+                v[q * 8 + 2 * e] += f.x;
+                v[q * 8 + 2 * e + 1] += f.y;
+              }
+            }
+          };
+          for (int s = 0; s < tp.world; ++s)                                 // ascending source rank: a fixed order
+            if (s != tp.rank) add_row(slots + ((long long)s * tp.rows_per_rank + lrow) * tp.ld_slot + col0);
+          if (resid != nullptr) add_row(resid + (long long)lrow * tp.ld_resid + col0);
+          __nv_bfloat16* d = outp + (long long)lrow * tp.ld_out + col0;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            o.x = pack_bf16(v[8 * q], v[8 * q + 1]);
+            o.y = pack_bf16(v[8 * q + 2], v[8 * q + 3]);
+            o.z = pack_bf16(v[8 * q + 4], v[8 * q + 5]);
+            o.w = pack_bf16(v[8 * q + 6], v[8 * q + 7]);
+            *reinterpret_cast<uint4*>(d + q * 8) = o;
+          }
+        }
+      } else if (scatter || p.tma_store) {
         // bf16 tile -> swizzled staging tile -> one TMA store: into the owner's slot (reduce-scatter) or into D
         const int owner = scatter ? (mb * 2 * BM) / tp.rows_per_rank : 0;
         const int row0 = mb * 2 * BM + int(rank) * BM + quarter * 32 + int(pt.row_shift);
@@ -381,6 +466,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           }
           ++out_cnt;
         }
+        if (reduce_mode) signal_owner = owner;
       } else
 #pragma unroll 1
       for (int c2 = chalf * 2; c2 < chalf * 2 + 2; ++c2) {
@@ -402,6 +488,17 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty_bar[acc]), 0));
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      if (signal_owner >= 0) {
+        // this warp's part of a remote owner's tile has been handed to the TMA engine and TMEM is released: once the
+        // writes are complete, count one arrival on the owner's tile counter (16 warps of the pair make a tile)
+        if (lane == 0) {
+          tma_store_wait0();
+          fence_proxy_async_all();                         // the engine's writes before the generic-proxy release below
+          const int per = tp.rows_per_rank / (2 * BM);
+          red_release_sys_add(tp.peer_flags[signal_owner] + (mb - signal_owner * per) * num_n + nb, 1);
+        }
+        __syncwarp();
+      }
     }
     if (((TP && (tp.mode & kTpScatter)) || p.tma_store) && lane == 0) tma_store_wait0();   // every tile has landed
   }
@@ -469,7 +566,7 @@ static int launch_gemm2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
   }
   const int num_tiles = ((p.M + 255) / 256) * ((p.N + 255) / 256) * p.batch * p.splits;
   int clusters = num_tiles < max_clusters ? num_tiles : max_clusters;
-  if (TP && (tp.mode & kTpGatherAny)) {
+  if (TP && (tp.mode & kTpGatherAny) && !(tp.mode & kTpPush)) {
     // every cluster must be resident at once: the GEMM clusters wait for the copy clusters
     if (tp.copy_clusters < 1 || tp.copy_clusters >= max_clusters) return -9;
     const int gemm_clusters = num_tiles < max_clusters - tp.copy_clusters ? num_tiles : max_clusters - tp.copy_clusters;
@@ -711,6 +808,124 @@ extern "C" int nga_tp_gemm_bf16(const void* A, const void* B, void* D, int M, in
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (b_mn) return launch_gemm2<0, 1, 1>(ta, tb, p, st, ta2, tp, tpm);
   return launch_gemm2<0, 0, 1>(ta, tb, p, st, ta2, tp, tpm);
+}
+
+// Owner-push all-gather -> GEMM (kTpGather | kTpPush): D [M = world * rows_per_rank, N] = gather(X) . B^T (or . B with b_mn).
+//   x_local         this rank's row shard [rows_per_rank, K] (any local memory; read directly for this rank's tiles)
+//   gathered_ptrs   HOST array: the [M, K] gathered buffer of every rank for this call (symmetric memory; callers alternate
+//                   between two buffers from call to call, which is all the ordering two consecutive calls need)
+//   flag_ptrs       HOST array: every rank's flag array (symmetric, one int per 128 gathered rows, zero-initialised once);
+//                   `epoch` grows by one per call
+// No barrier precedes the call: a rank can run ahead by at most one call, because finishing a call needs every
+// peer's shard of that call.
+extern "C" int nga_tp_gemm_push_bf16(const void* x_local, const void* B, void* D, int M, int N, int K, long long ldb,
+                                     long long ldd, int b_mn, int rank, int world, int rows_per_rank,
+                                     const long long* gathered_ptrs, const long long* flag_ptrs, int epoch, int* status,
+                                     void* stream) {
+  using namespace nga;
+  if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > kTpMaxWorld || rank < 0 || rank >= world) return -1;
+  if (rows_per_rank <= 0 || rows_per_rank % 256 || M != world * rows_per_rank) return -2;
+  if ((K & 63) || (ldb & 7) || (ldd & 7)) return -5;
+  if (x_local == nullptr || gathered_ptrs == nullptr || flag_ptrs == nullptr) return -4;
+  TpParams tp = {};
+  tp.mode = kTpGather | kTpPush;
+  tp.rank = rank; tp.world = world; tp.rows_per_rank = rows_per_rank;
+  tp.copy_clusters = 0; tp.epoch = epoch; tp.row_elems = K; tp.early_rounds = 0;
+  tp.push_src = x_local;
+  // slices per 128-row block: enough work items for about two per CTA, so that every SM stores for a few microseconds only
+  // One 128-row block per push item measured fastest at two ranks (0.133 ms against 0.138 / 0.147 ms with the block cut
+  // in two / four slices): more pushing CTAs put peer stores on more SMs and slow every main loop.
+  tp.push_parts = 1;
+  {
+    static int forced = -1;                                  // NGA_TP_PUSH_PARTS = 1 | 2 | 4 for measurements
+    if (forced < 0) {
+      const char* e = getenv("NGA_TP_PUSH_PARTS");
+      forced = e ? atoi(e) : 0;
+    }
+    if (forced == 1 || forced == 2 || forced == 4) tp.push_parts = forced;
+  }
+  for (int r = 0; r < world; ++r) {
+    tp.peer_dst[r] = reinterpret_cast<void*>(gathered_ptrs[r]);
+    tp.peer_flags[r] = reinterpret_cast<int*>(flag_ptrs[r]);
+    if (tp.peer_dst[r] == nullptr || tp.peer_flags[r] == nullptr) return -4;
+  }
+  tp.flags = tp.peer_flags[rank];
+  tp.gathered = tp.peer_dst[rank];
+  CUtensorMap ta, ta2, tb;
+  int rc = make_tmap_3d(&ta, tp.gathered, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, 1, (long long)K * 2, (long long)M * K * 2, 64,
+                        128, true);
+  if (rc) return rc;
+  rc = make_tmap_3d(&ta2, x_local, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, rows_per_rank, 1, (long long)K * 2,
+                    (long long)rows_per_rank * K * 2, 64, 128, true);
+  if (rc) return rc;
+  if (b_mn)
+    rc = make_tmap_3d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, 1, ldb * 2, (long long)K * ldb * 2, 64, 64, true);
+  else
+    rc = make_tmap_3d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, 1, ldb * 2, (long long)N * ldb * 2, 64, 128, true);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.batch = 1;
+  p.D = D; p.aux = nullptr; p.ldd = ldd; p.ldaux = 0; p.sD = 0; p.sAux = 0;
+  p.epi = kEpiScale; p.out_fp32 = 0; p.aux_fp32 = 0; p.alpha = 1.f; p.beta = 0.f; p.splits = 1;
+  p.status = status; p.row_shift = 0;
+  p.group_of_mtile = nullptr; p.group_rows = 0;
+  TpMaps tpm = {};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (b_mn) return launch_gemm2<0, 1, 1>(ta, tb, p, st, ta2, tp, tpm);
+  return launch_gemm2<0, 0, 1>(ta, tb, p, st, ta2, tp, tpm);
+}
+
+// GEMM -> reduce-scatter finished in the kernel (kTpScatter | kTpReduce): out [rows_per_rank, N] = this rank's rows of
+// sum over ranks (A . B^T) (+ resid).  A [M, K] local.
+//   slot_ptrs     HOST array: every rank's staging buffer [world][rows_per_rank, N] bf16 for this call (symmetric; callers
+//                 alternate between two buffers from call to call)
+//   counter_ptrs  HOST array: every rank's arrival counters (symmetric int array, one per owned 256 x 256 tile,
+//                 zero-initialised once; never reset) and `call_index` = number of calls made on them so far + 1
+// No barrier and no separate reduction kernel: see kTpReduce.
+extern "C" int nga_tp_gemm_rs_reduce_bf16(const void* A, const void* B, void* out, const void* resid, int M, int N, int K,
+                                          long long ldb, long long ld_out, long long ld_resid, int b_mn, int rank, int world,
+                                          int rows_per_rank, const long long* slot_ptrs, const long long* counter_ptrs,
+                                          int call_index, int* status, void* stream) {
+  using namespace nga;
+  if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > kTpMaxWorld || rank < 0 || rank >= world) return -1;
+  if (rows_per_rank <= 0 || rows_per_rank % 256 || M != world * rows_per_rank) return -2;
+  if ((K & 63) || (ldb & 7) || (N & 31) || (ld_out & 7) || (ld_resid & 7)) return -5;
+  if (A == nullptr || out == nullptr || slot_ptrs == nullptr || counter_ptrs == nullptr || call_index < 1) return -4;
+  TpParams tp = {};
+  tp.mode = kTpScatter | kTpReduce;
+  tp.rank = rank; tp.world = world; tp.rows_per_rank = rows_per_rank;
+  tp.row_elems = K;
+  tp.resid = resid; tp.reduce_out = out; tp.ld_resid = ld_resid; tp.ld_out = ld_out; tp.ld_slot = N;
+  tp.arrivals = call_index * 16 * (world - 1);
+  for (int r = 0; r < world; ++r) {
+    tp.peer_dst[r] = reinterpret_cast<void*>(slot_ptrs[r]);
+    tp.peer_flags[r] = reinterpret_cast<int*>(counter_ptrs[r]);
+    if (tp.peer_dst[r] == nullptr || tp.peer_flags[r] == nullptr) return -4;
+  }
+  tp.flags = tp.peer_flags[rank];
+  CUtensorMap ta, tb;
+  int rc = make_tmap_3d(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, 1, (long long)K * 2, (long long)M * K * 2, 64, 128, true);
+  if (rc) return rc;
+  if (b_mn)
+    rc = make_tmap_3d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, 1, ldb * 2, (long long)K * ldb * 2, 64, 64, true);
+  else
+    rc = make_tmap_3d(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, 1, ldb * 2, (long long)N * ldb * 2, 64, 128, true);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.batch = 1;
+  p.D = nullptr; p.aux = nullptr; p.ldd = N; p.ldaux = 0; p.sD = 0; p.sAux = 0;
+  p.epi = kEpiScale; p.out_fp32 = 0; p.aux_fp32 = 0; p.alpha = 1.f; p.beta = 0.f; p.splits = 1;
+  p.status = status; p.row_shift = 0;
+  p.group_of_mtile = nullptr; p.group_rows = 0;
+  TpMaps tpm = {};
+  for (int r = 0; r < world; ++r) {
+    rc = make_tmap_3d(&tpm.d[r], tp.peer_dst[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, (long long)world * rows_per_rank, 1,
+                      (long long)N * 2, (long long)world * rows_per_rank * N * 2, 64, 32, true);
+    if (rc) return rc;
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (b_mn) return launch_gemm2<0, 1, 1>(ta, tb, p, st, ta, tp, tpm);
+  return launch_gemm2<0, 0, 1>(ta, tb, p, st, ta, tp, tpm);
 }
 
 // GEMMs against a fully-sharded weight W [w_rows = world * rows_per_rank, w_cols] that lives as row shards on the

@@ -52,6 +52,19 @@ constexpr int kTpGatherB = 4;
 //               own shard and waits (bounded) for each block of the others the first time it needs it.
 constexpr int kTpGatherBk = 8;
 constexpr int kTpGatherAny = kTpGather | kTpGatherB | kTpGatherBk;
+// kTpPush (with kTpGather): owner-push all-gather.  No copy clusters: at kernel start the epilogue warps of every CTA
+//               STORE this rank's row shard, 128-row block by block, into every rank's gathered buffer (`peer_dst`,
+//               remote ranks first) and publish each block with a release store to that rank's flag array
+//               (`peer_flags`).  Posted stores need no round trip, so a few dozen SMs fill the link, and they run under
+//               the main loops of the first tiles, which are this rank's own rows (read straight from the shard).
+constexpr int kTpPush = 16;
+// kTpReduce (with kTpScatter): the reduce-scatter is finished inside the GEMM kernel.  Tiles of remote owners come
+//               first: stored into the owner's slot as before, then every epilogue warp adds one to the owner's
+//               arrival counter of that tile (`peer_flags`, release at system scope, after its bulk stores have
+//               completed).  Tiles this rank owns come last: their epilogue waits (bounded) until the counter shows all
+//               remote partial tiles, then adds them (and the residual) to the accumulator and writes the final rows -
+//               no barrier kernels and no separate reduction pass.
+constexpr int kTpReduce = 32;
 struct TpParams {
   int mode, rank, world, rows_per_rank;
   int copy_clusters, epoch;
@@ -61,7 +74,14 @@ struct TpParams {
   int* flags;                          // one per 128-row block of the gathered matrix; value = epoch when ready
   const void* peer_src[kTpMaxWorld];   // row shard of every rank (bf16, contiguous rows of K elements, symmetric)
   void* gathered;                      // local [world * rows_per_rank, K] bf16
-  void* peer_dst[kTpMaxWorld];         // reduce-scatter staging buffer of every rank
+  void* peer_dst[kTpMaxWorld];         // reduce-scatter staging buffer of every rank; kTpPush: gathered buffer of every rank
+  int* peer_flags[kTpMaxWorld];        // kTpPush: block flags of every rank; kTpReduce: tile arrival counters of every rank
+  const void* push_src;                // kTpPush: this rank's row shard [rows_per_rank, row_elems]
+  int push_parts;                      // kTpPush: row slices per 128-row block (1, 2 or 4); a block counter reads epoch * parts
+  const void* resid;                   // kTpReduce: optional residual [rows_per_rank, ld_resid] added to the owned rows
+  void* reduce_out;                    // kTpReduce: final [rows_per_rank, ld_out] bf16 rows of this rank
+  long long ld_resid, ld_out, ld_slot; // row pitches (elements) of residual, output and staging slots
+  int arrivals;                        // kTpReduce: counter value at which a tile of this call is complete
 };
 
 // Tensor maps of the reduce-scatter staging buffer on every rank ([world * rows_per_rank, ldd] bf16,

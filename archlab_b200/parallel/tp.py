@@ -29,14 +29,19 @@ _vp, _i, _ll = C.c_void_p, C.c_int, C.c_longlong
 native.register_signature("nga_tp_gemm_bf16", [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _i, _i, _i, _i, _vp, _vp, _vp,
                                                _i, _i, _vp, _vp, _vp])
 native.register_signature("nga_tp_reduce_slots", [_vp, _vp, _vp, _i, _ll, _i, _ll, _ll, _ll, _vp])
+native.register_signature("nga_tp_gemm_push_bf16", [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp])
+native.register_signature("nga_tp_gemm_rs_reduce_bf16", [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i, _vp, _vp,
+                                                         _i, _vp, _vp])
 
 
 class TPGroup:
     """Symmetric buffers and barriers of one tensor-parallel group for a fixed problem geometry:
     ``rows`` sequence rows per rank, activations up to ``max_k`` wide, outputs up to ``max_n`` wide."""
 
-    def __init__(self, rows: int, max_k: int, max_n: int, device, group=None, copy_clusters: int = 12):
-        from .symm import PeerBarrier, symm_empty
+    def __init__(self, rows: int, max_k: int, max_n: int, device, group=None, copy_clusters: int = 12, push: bool = True):
+        """``push``: owner-push all-gather and in-kernel reduce-scatter (one launch per op, no barrier kernels); False
+        selects the pull form (copy clusters, barrier + separate slot reduction), kept for comparison."""
+        from .symm import PeerBarrier, symm_empty, symm_zeros
 
         self.group = group or dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
@@ -52,6 +57,20 @@ class TPGroup:
         self.flags = torch.zeros(self.world * rows // 128, dtype=torch.int32, device=device)
         self.epoch = 0
         self.barrier = PeerBarrier(device, self.group)
+        self.push = push
+        if push:
+            # both directions alternate between two buffers from call to call: a rank can be at most one call ahead of a
+            # peer (finishing a call needs every peer's data of that call), so the buffer of call k is free at call k + 2
+            self.gathered2 = symm_empty((2 * self.world * rows * max_k,), torch.bfloat16, device, self.group)
+            self.block_flags = symm_zeros((self.world * rows // 128,), torch.int32, device, self.group)
+            self.stage2 = symm_empty((2 * self.world * rows * max_n,), torch.bfloat16, device, self.group)
+            self.counters = symm_zeros((rows // 256 * ((max_n + 255) // 256 + 1),), torch.int32, device, self.group)
+            self.push_epoch = 0
+            self.rs_calls = 0
+            self._rs_shape = None
+            torch.cuda.synchronize(device)
+            self.barrier()                       # every rank's flags and counters are zero before anyone writes to them
+            torch.cuda.synchronize(device)
 
     def shard_view(self, k: int, epoch: int | None = None) -> torch.Tensor:
         """The shard buffer the call with this epoch (default: the next call) reads; a producer can write
@@ -61,6 +80,9 @@ class TPGroup:
         return self.x_shard.tensor[base: base + self.rows * k].view(self.rows, k)
 
     def gathered_view(self, k: int) -> torch.Tensor:
+        if self.push:                            # the buffer the latest call filled
+            base = (self.push_epoch & 1) * self.world * self.rows * self.max_k
+            return self.gathered2.tensor[base: base + self.world * self.rows * k].view(self.world * self.rows, k)
         return self.gathered[: self.world * self.rows * k].view(self.world * self.rows, k)
 
 
@@ -74,6 +96,18 @@ def ag_gemm(tp: TPGroup, x_shard: torch.Tensor, w: torch.Tensor, *, w_mn: bool =
     M = tp.world * rows
     if rows != tp.rows or K > tp.max_k:
         raise ValueError("geometry does not match the TP group")
+    if tp.push:
+        if out is None:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=x_shard.device)
+        x_shard = x_shard.contiguous()
+        tp.push_epoch += 1
+        base = (tp.push_epoch & 1) * tp.world * tp.rows * tp.max_k
+        rc = native.lib().nga_tp_gemm_push_bf16(
+            x_shard.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, w.stride(0), out.stride(0), int(w_mn), tp.rank, tp.world,
+            rows, tp.gathered2.ptr_array(base), tp.block_flags.ptr_array(), tp.push_epoch,
+            native.status_word(x_shard.device).data_ptr(), native.stream_ptr())
+        native.check(rc, "nga_tp_gemm_push_bf16")
+        return out
     src = tp.shard_view(K)
     if x_shard.data_ptr() != src.data_ptr():
         src.copy_(x_shard)
@@ -98,6 +132,19 @@ def gemm_rs(tp: TPGroup, a: torch.Tensor, w: torch.Tensor, *, w_mn: bool = False
         raise ValueError("geometry does not match the TP group")
     if out is None:
         out = torch.empty(tp.rows, N, dtype=torch.bfloat16, device=a.device)
+    if tp.push and N % 32 == 0 and (resid is None or resid.stride(0) % 8 == 0):
+        if tp._rs_shape not in (None, N):
+            raise ValueError("one TP group reduces outputs of one width (the arrival counters are indexed by tile)")
+        tp._rs_shape = N
+        tp.rs_calls += 1
+        base = (tp.rs_calls & 1) * tp.world * tp.rows * tp.max_n
+        rc = native.lib().nga_tp_gemm_rs_reduce_bf16(
+            a.data_ptr(), w.data_ptr(), out.data_ptr(), None if resid is None else resid.data_ptr(), M, N, K, w.stride(0),
+            out.stride(0), 0 if resid is None else resid.stride(0), int(w_mn), tp.rank, tp.world, tp.rows,
+            tp.stage2.ptr_array(base), tp.counters.ptr_array(), tp.rs_calls, native.status_word(a.device).data_ptr(),
+            native.stream_ptr())
+        native.check(rc, "nga_tp_gemm_rs_reduce_bf16")
+        return out
     tp.barrier()                                   # every owner has consumed its slots from the previous call
     rc = native.lib().nga_tp_gemm_bf16(
         a.data_ptr(), w.data_ptr(), None, M, N, K, w.stride(0), N, int(w_mn), 2, tp.rank, tp.world, tp.rows,

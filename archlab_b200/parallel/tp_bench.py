@@ -55,7 +55,8 @@ def main(argv=None):
 
     world = dist.get_world_size()
     dev = torch.device("cuda", rank)
-    grp = T.TPGroup(a.rows, a.k, max(a.n, a.k), dev, copy_clusters=a.copy_clusters)
+    grp = T.TPGroup(a.rows, a.k, max(a.n, a.k), dev, copy_clusters=a.copy_clusters, push=False)      # pull form (copy clusters)
+    grp_push = T.TPGroup(a.rows, a.k, max(a.n, a.k), dev)                                             # owner-push / in-kernel reduce
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     M = world * a.rows
     x = torch.randn(a.rows, a.k, device=dev).bfloat16()
@@ -81,7 +82,8 @@ def main(argv=None):
         ms = _time(fn, a.iters, flush)
         rows.append({"op": name, "ms": ms})
     grp.copy_clusters = a.copy_clusters
-    for name, fn in (("ag_gemm_fused", lambda: T.ag_gemm(grp, x, w, out=out)), ("ag_gemm_nccl", nccl_ag)):
+    for name, fn in (("ag_gemm_push", lambda: T.ag_gemm(grp_push, x, w, out=out)), ("ag_gemm_fused", lambda: T.ag_gemm(grp, x, w, out=out)),
+                     ("ag_gemm_nccl", nccl_ag)):
         ms = _time(fn, a.iters, flush)
         rows.append({"op": name, "ms": ms, "tflops": flops / ms / 1e9, "roofline_ms": roof, "of_roofline": roof / ms})
     # row-parallel: local K slice a.k, output width a.k (o-proj / FC2 shape family), reduce-scatter over rows
@@ -97,7 +99,9 @@ def main(argv=None):
     flops2 = 2.0 * M * a.k * a.n
     link2 = (world - 1) * a.rows * a.k * 2
     roof2 = max(flops2 / (a.gemm_peak_tflops * 1e12), link2 / (a.link_gbs * 1e9)) * 1e3
-    for name, fn in (("gemm_rs_fused", lambda: T.gemm_rs(grp, act, w2, out=ys)), ("gemm_rs_nccl", nccl_rs)):
+    for name, fn in (("gemm_rs_reduce_in_kernel", lambda: T.gemm_rs(grp_push, act, w2, out=ys)),
+                     ("gemm_rs_fused", lambda: T.gemm_rs(grp, act, w2, out=ys)), ("gemm_rs_nccl", nccl_rs),
+                     ("gemm_only_rs_shape", lambda: G.gemm(act, w2, out=y))):
         ms = _time(fn, a.iters, flush)
         rows.append({"op": name, "ms": ms, "tflops": flops2 / ms / 1e9, "roofline_ms": roof2, "of_roofline": roof2 / ms})
     if a.fsdp:

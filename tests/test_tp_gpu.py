@@ -25,8 +25,20 @@ def _worker(rank, world, port, out_dir):
 
     dev = torch.device("cuda", rank)
     rows, K, N = 512, 320, 384
-    grp = T.TPGroup(rows, max_k=512, max_n=512, device=dev, copy_clusters=2)
     res = {}
+    for form, push in (("push", True), ("pull", False)):
+        grp = T.TPGroup(rows, max_k=512, max_n=512, device=dev, copy_clusters=2, push=push)
+        _check_forms(T, grp, dev, rank, world, rows, K, N, res, form)
+    torch.cuda.synchronize()
+    native.check_status()
+    torch.save(res, os.path.join(out_dir, f"tp_rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _check_forms(T, grp, dev, rank, world, rows, K, N, res, form):
+    import torch.distributed as dist
+
     for it in range(3):                               # several epochs: flags, double buffering, slot reuse
         g = torch.Generator(device=dev).manual_seed(100 * it + rank)
         x = (torch.randn(rows, K, device=dev, generator=g) * 0.5).bfloat16()
@@ -34,24 +46,19 @@ def _worker(rank, world, port, out_dir):
         w = (torch.randn(N, K, device=dev, generator=gw) * 0.1).bfloat16()
         y = T.ag_gemm(grp, x, w)
         ref = T.ag_gemm_reference(x, w)
-        res[f"ag{it}"] = ((y.float() - ref.float()).norm() / ref.float().norm()).item()
+        res[f"{form}_ag{it}"] = ((y.float() - ref.float()).norm() / ref.float().norm()).item()
         wt = w.t().contiguous()                       # [K, N] MN-major operand
         y2 = T.ag_gemm(grp, x, wt, w_mn=True)
-        res[f"ag_mn{it}"] = ((y2.float() - ref.float()).norm() / ref.float().norm()).item()
+        res[f"{form}_ag_mn{it}"] = ((y2.float() - ref.float()).norm() / ref.float().norm()).item()
         gathered = grp.gathered_view(K)
         parts = [torch.empty_like(x) for _ in range(world)]
         dist.all_gather(parts, x)
-        res[f"gathered{it}"] = float((gathered.float() - torch.cat(parts).float()).abs().max())   # own rows included
+        res[f"gathered_{form}{it}"] = float((gathered.float() - torch.cat(parts).float()).abs().max())   # own rows included
         a = (torch.randn(world * rows, K, device=dev, generator=g) * 0.5).bfloat16()
         resid = (torch.randn(rows, N, device=dev, generator=g)).bfloat16()
         z = T.gemm_rs(grp, a, w, resid=resid)
         zref = T.gemm_rs_reference(a, w, resid=resid)
-        res[f"rs{it}"] = ((z.float() - zref.float()).norm() / zref.float().norm()).item()
-    torch.cuda.synchronize()
-    native.check_status()
-    torch.save(res, os.path.join(out_dir, f"tp_rank{rank}.pt"))
-    dist.barrier()
-    dist.destroy_process_group()
+        res[f"{form}_rs{it}"] = ((z.float() - zref.float()).norm() / zref.float().norm()).item()
 
 
 @pytest.mark.parametrize("world", WORLDS)
