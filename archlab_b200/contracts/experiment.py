@@ -305,172 +305,8 @@ def compose_trainer(experiment: Experiment, config_root: Path | None = None, *, 
 
 
 def validate_science(experiment: Experiment, config: dict) -> None:
-    """Fail-closed invariants of the agentic RL pilots (reference :149-229); each message names the
-    violated rule.  The MFU device name must say which accelerator the job really runs on: B200."""
-    c = Tree(config)
-    actor, rollout = c.actor_rollout_ref.actor, c.actor_rollout_ref.rollout
-    strategy = "fsdp2" if experiment.engine == "dp" else "megatron"
-    if c.model_engine != experiment.engine or actor.strategy != strategy:
-        raise ValueError("resolved learner strategy differs from the experiment engine")
-    if c.algorithm.adv_estimator != "grpo":
-        raise ValueError("the agentic code pilot requires GRPO")
-    if experiment.family == "muse_glimmer":
-        _validate_muse_science(experiment, c)
-    elif experiment.engine == "megatron":
-        if actor.megatron.dtype != "bfloat16":
-            raise ValueError("native mixed precision requires the bfloat16 Megatron contract")
-        if actor.megatron.patch_recomputation_backward:
-            raise ValueError("native Limite owns checkpointing; runtime Megatron patches must be disabled")
-    if experiment.family == "limite" and c.actor_rollout_ref.model.override_config:
-        raise ValueError("model geometry overrides require a new verified export")
-    if experiment.intervention == "replace_attention":
-        _validate_conversion_science(experiment, c)
-    if experiment.family == "limite" and not rollout.enforce_eager:
-        comp = rollout.engine_kwargs.vllm.get("compilation_config", {}) or {}
-        if (rollout.max_num_seqs != 1 or comp.get("mode") != 0 or comp.get("cudagraph_mode") != "FULL_DECODE_ONLY"
-                or comp.get("cudagraph_capture_sizes") != [1] or comp.get("max_cudagraph_capture_size") != 1):
-            raise ValueError("native serving requires eager execution or explicit single-sequence decode graphs")
-    if experiment.family == "limite" and experiment.attention == "native":
-        att = rollout.engine_kwargs.vllm.attention_config
-        if experiment.variant != "normal" or att.backend != "FLASH_ATTN" or att.flash_attn_version != 2:
-            raise ValueError("native normal RL requires explicit FlashAttention-2 serving")
-    if rollout.checkpoint_engine.backend != "naive":
-        raise ValueError("native mixed precision requires qualified full-weight synchronization")
-    if rollout.max_model_len != experiment.native_context:
-        raise ValueError("rollout must retain the model's native context")
-    if rollout.prompt_length + rollout.response_length != experiment.native_context:
-        raise ValueError("prompt and response allocation must cover native context")
-    if c.data.max_prompt_length != rollout.prompt_length or c.data.max_response_length != rollout.response_length:
-        raise ValueError("dataset and agent context geometry differ")
-    if c.data.truncation != "error":
-        raise ValueError("silently truncating agentic task prompts is not allowed")
-    if not rollout.multi_turn.enable or not rollout.calculate_log_probs:
-        raise ValueError("agentic RL requires multi-turn rollout and behavior log probabilities")
-    if rollout.n < 2:
-        raise ValueError("GRPO requires multiple responses and recorded behavior probabilities")
-    cor = c.algorithm.rollout_correction
-    if cor.bypass_mode or cor.rollout_is != "token" or cor.rollout_is_threshold != 2.0 or cor.rollout_is_batch_normalize:
-        raise ValueError("the pilot requires one upstream token importance correction, capped at 2")
-    if actor.use_kl_loss or c.algorithm.use_kl_in_reward:
-        raise ValueError("this controlled code pilot does not include a reference-policy KL")
-    if (experiment.family == "limite" and experiment.intervention != "replace_attention"
-            and rollout.custom.agent_framework.mask_unfinished_episode):
-        raise ValueError("unfinished trajectories must remain visible in this pilot")
-    if not 0 <= c.trainer.v1.sampler.max_off_policy_threshold <= experiment.maximum_policy_lag:
-        raise ValueError("policy lag exceeds the explicit experiment contract")
-    if experiment.resume_checkpoint:
-        if c.trainer.resume_mode != "resume_path" or c.trainer.resume_from_path != experiment.resume_checkpoint:
-            raise ValueError("resume must use the explicit checkpoint lineage")
-    elif c.trainer.resume_mode != "disable":
-        raise ValueError("fresh RL must reset the optimizer, RNG and training counters")
-    if (rollout.custom.agent_framework.get("trajectory_validator") != "archlab_b200.train.rollout.RolloutContract"
-            or c.trainer.get("metrics_extension") != "archlab_b200.train.metrics.step_metrics"):
-        raise ValueError("the primary pilot requires validated rollout and performance contracts")
-    if c.ray_kwargs.ray_init.runtime_env.env_vars.get("VERL_MFU_DEVICE_NAME") != "B200":
-        raise ValueError("MFU hardware must reflect the actual B200 allocation")
-    if experiment.family == "qwen3_5":
-        model = c.actor_rollout_ref.model
-        if (model.path != experiment.parent_checkpoint or model.external_lib or model.trust_remote_code
-                or model.custom_chat_template
-                or dict(model.override_config) != {"attn_implementation": "flash_attention_2"}
-                or dict(c.data.apply_chat_template_kwargs) != {"enable_thinking": False}
-                or actor.fsdp_config.dtype != "bfloat16" or actor.fsdp_config.model_dtype != "fp32"
-                or rollout.multi_turn.format != "qwen3_coder" or rollout.logprobs_mode != "processed_logprobs"):
-            raise ValueError("Qwen native control requires its declared model, codec and mixed precision")
+    """Fail-closed invariants of the agentic RL pilots; the rules are the table in ``science_rules`` and the raised
+    ``ValueError`` carries the violated rule's message (and the offending path as ``violated_path``)."""
+    from . import science_rules
 
-
-def _validate_muse_science(e: Experiment, c: Tree) -> None:
-    actor, model, rollout = c.actor_rollout_ref.actor, c.actor_rollout_ref.model, c.actor_rollout_ref.rollout
-    if (model.path != e.parent_checkpoint or model.external_lib or model.trust_remote_code
-            or model.custom_chat_template or model.hf_config_path or model.tokenizer_path):
-        raise ValueError("Muse must load its unchanged publisher checkpoint, tokenizer and template together")
-    if dict(model.override_config) != {"attn_implementation": "flash_attention_4"}:
-        raise ValueError("Muse permits only its explicit native FlashAttention-4 kernel override, without geometry changes")
-    f = actor.fsdp_config
-    if (f.strategy != "fsdp2" or f.dtype != "bfloat16" or f.model_dtype != "fp32" or f.ulysses_sequence_parallel_size != 1
-            or f.fsdp_size != 8 or f.param_offload or f.optimizer_offload or c.trainer.nnodes != 1
-            or c.trainer.n_gpus_per_node != 8):
-        raise ValueError("Muse requires GPU-resident DP8 FSDP2 with FP32 master weights and BF16 compute")
-    if (model.use_remove_padding or model.use_fused_kernels or model.use_liger or model.lora_rank or model.lora.rank
-            or model.lora_adapter_path or not model.enable_gradient_checkpointing or model.mtp.enable
-            or actor.ppo_micro_batch_size_per_gpu != 1 or actor.use_dynamic_bsz or actor.use_torch_compile
-            or f.use_torch_compile or f.qat.enable):
-        raise ValueError("Muse admission requires native full-weight microbatches without unqualified kernels or quantization")
-    o = actor.optim
-    if (o.optimizer != "Adam" or o.optimizer_impl != "torch.optim" or o.lr != 1e-6 or list(o.betas) != [.9, .95]
-            or o.weight_decay != 0 or o.override_optimizer_config):
-        raise ValueError("Muse control requires explicit torch Adam at 1e-6 with betas (0.9, 0.95)")
-    if (e.execution != "colocate_async" or e.native_context != 131072 or rollout.name != "vllm"
-            or not rollout.enforce_eager or rollout.ignore_eos or rollout.prompt_length != 16384
-            or rollout.response_length != 114688 or rollout.quantization or rollout.quantization_config_file
-            or rollout.tensor_model_parallel_size != 1 or rollout.pipeline_model_parallel_size != 1
-            or rollout.data_parallel_size != 1 or rollout.max_num_seqs != 1 or rollout.gpu_memory_utilization != .3
-            or rollout.multi_turn.format != "muse_glimmer"
-            or dict(rollout.engine_kwargs.vllm) != {"model_impl": "vllm", "limit_mm_per_prompt": {"image": 0, "video": 0}}
-            or dict(c.data.apply_chat_template_kwargs) != {"reasoning_strength": "high"}):
-        raise ValueError("Muse control requires native eager vLLM serving and the publisher's reasoning/tool protocol")
-    v = rollout.val_kwargs
-    if (rollout.temperature != 1. or not rollout.do_sample or rollout.top_p != 1. or rollout.top_k != -1
-            or rollout.logprobs_mode != "processed_logprobs" or not v.do_sample
-            or any(v[k] != rollout[k] for k in ("temperature", "top_p", "top_k"))):
-        raise ValueError("Muse control requires full-support processed behavior probabilities")
-    if (c.data.train_batch_size != 2 or actor.ppo_mini_batch_size != 2 or rollout.n != 4
-            or c.algorithm.filter_groups.enable or not c.algorithm.norm_adv_by_std_in_grpo
-            or not rollout.custom.agent_framework.mask_unfinished_episode):
-        raise ValueError("Muse control requires two stock GRPO groups of four and unfinished-episode masking")
-    p = e.pilot
-    if (p is None or p.max_turn_tokens != 8192 or p.step_limit != 500 or p.minimum_prompt_groups != 2
-            or p.minimum_completed_verifiers != 8
-            or min(p.minimum_tool_calls, p.minimum_observation_tokens, p.minimum_reward_contrast_groups) < 1
-            or p.maximum_truncated_trajectories != 0):
-        raise ValueError("Muse admission requires complete agentic traces, executable rewards and reward contrast")
-
-
-def _validate_conversion_science(e: Experiment, c: Tree) -> None:
-    actor, model, rollout = c.actor_rollout_ref.actor, c.actor_rollout_ref.model, c.actor_rollout_ref.rollout
-    t = rollout.temperature
-    if (type(t) not in (float, int) or not math.isfinite(t) or t <= 0 or not rollout.do_sample
-            or rollout.top_p != 1. or rollout.top_k != -1 or rollout.logprobs_mode != "processed_logprobs"):
-        raise ValueError("replacement RL requires positive-temperature full-support processed behavior probabilities")
-    v = rollout.val_kwargs
-    if not v.do_sample or any(v[k] != rollout[k] for k in ("temperature", "top_p", "top_k")):
-        raise ValueError("replacement validation and training must use the declared harness sampling distribution")
-    if (e.parent_stage != "package_sft" or e.parent_tokens is not None or e.variant != "simplicial"
-            or e.attention != "tilelang" or e.execution != "colocate_async"):
-        raise ValueError("replacement RL requires package SFT lineage and bounded async TileLang execution")
-    mg = actor.megatron
-    if (model.external_lib != "archlab_b200.train.learner" or model.use_remove_padding or model.use_fused_kernels
-            or model.lora_rank or model.lora.rank or mg.use_remove_padding or mg.pad_bshd_to_minibatch_max
-            or actor.ppo_micro_batch_size_per_gpu != 1 or actor.use_dynamic_bsz):
-        raise ValueError("replacement RL requires full-weight native BSHD microbatches of one")
-    if (any(mg[n] != 1 for n in ("tensor_model_parallel_size", "pipeline_model_parallel_size",
-                                 "context_parallel_size", "expert_model_parallel_size"))
-            or mg.sequence_parallel or mg.dynamic_context_parallel
-            or mg.virtual_pipeline_model_parallel_size is not None or c.trainer.nnodes != 1
-            or c.trainer.n_gpus_per_node != 8):
-        raise ValueError("replacement learner requires DP8 with TP=PP=CP=EP=1")
-    att = rollout.engine_kwargs.vllm.attention_config
-    if (rollout.name != "vllm" or not rollout.enforce_eager or rollout.max_num_seqs != 1
-            or rollout.enable_prefix_caching or rollout.enable_chunked_prefill
-            or rollout.max_num_batched_tokens < e.native_context or rollout.tensor_model_parallel_size != 1
-            or rollout.pipeline_model_parallel_size != 1 or rollout.data_parallel_size != 1
-            or att.backend != "FLASH_ATTN" or att.flash_attn_version != 2):
-        raise ValueError("replacement serving requires eager FA2, one request, TP=PP=1 and no prefix/chunked prefill")
-    conflicting = {"enforce_eager", "max_num_seqs", "enable_prefix_caching", "enable_chunked_prefill",
-                   "tensor_parallel_size", "pipeline_parallel_size", "decode_context_parallel_size",
-                   "prefill_context_parallel_size", "quantization", "kv_cache_dtype", "speculative_config",
-                   "hf_overrides", "model", "logprobs_mode"} & set(rollout.engine_kwargs.vllm)
-    if conflicting:
-        raise ValueError("replacement engine kwargs override the serving contract: " + ", ".join(sorted(conflicting)))
-    if not actor.optim.use_checkpoint_opt_param_scheduler:
-        raise ValueError("replacement checkpoints must restore the optimizer parameter scheduler")
-    ov = actor.optim.override_optimizer_config or {}
-    if ov.get("adam_beta1") != .9 or ov.get("adam_beta2") != .95:
-        raise ValueError("replacement Adam requires explicit Megatron beta overrides (0.9, 0.95)")
-    p = e.pilot
-    if (p is None or not 0 < p.max_turn_tokens <= 8192 or p.step_limit != 500 or p.minimum_prompt_groups < 2
-            or p.minimum_completed_verifiers < p.minimum_prompt_groups * rollout.n
-            or min(p.minimum_tool_calls, p.minimum_observation_tokens, p.minimum_reward_contrast_groups) < 1
-            or p.maximum_truncated_trajectories != 0 or c.data.train_batch_size < p.minimum_prompt_groups
-            or actor.ppo_mini_batch_size * rollout.n < 8 or not rollout.custom.agent_framework.mask_unfinished_episode):
-        raise ValueError("replacement pilot requires explicit short turns, usable traces and stock truncation masking")
+    science_rules.validate(experiment, config)

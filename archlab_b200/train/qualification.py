@@ -131,84 +131,109 @@ def check_model(experiment: Experiment, config: dict) -> dict:
     return detail
 
 
+GATE_SWITCHES = ("DISTRIBUTED", "ENGINE", "NATIVE_CONTEXT", "THROUGHPUT", "AGENTIC_PIPELINE")   # ARCHLAB_RUN_<switch>=1
+DEPLOYMENT_FILES = {"resolved.yaml": "ARCHLAB_QUALIFICATION_CONFIG", "experiment.json": "ARCHLAB_QUALIFICATION_EXPERIMENT"}
+_NOT_A_PASS = ("failure", "error", "skipped")
+
+
+class _PytestGate:
+    """One subprocess run of pytest nodes of this checkout, one process per GPU when ``world_size`` > 1.
+
+    Every rank writes its own junit report (the test session reads ``ARCHLAB_JUNIT_PER_RANK``); a gate passes only when
+    every report exists, holds at least one test case, and no case failed, errored or was skipped."""
+
+    def __init__(self, nodes, output: Path, world_size: int, root: Path):
+        self.nodes, self.output, self.world, self.root = list(nodes), output, world_size, root
+        self.reports = [output / f"pytest-rank-{r}.xml" for r in range(world_size)] if world_size > 1 else [output / "pytest.xml"]
+
+    def unimplemented(self):
+        return next((n for n in self.nodes if not (self.root / n.partition("::")[0]).is_file()), None)
+
+    def command(self) -> list[str]:
+        launcher = ["-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1", "--nnodes=1",
+                    f"--nproc_per_node={self.world}"] if self.world > 1 else []
+        return [sys.executable, *launcher, "-m", "pytest", "-q", *self.nodes,
+                f"--basetemp={self.output.resolve() / 'artifacts'}", f"--junitxml={self.output / 'pytest.xml'}"]
+
+    def environment(self, deployment, extra) -> dict:
+        env = {**os.environ, **(extra or {}), "ARCHLAB_JUNIT_PER_RANK": str(int(self.world > 1))}
+        if deployment is not None:                       # the gate reads the frozen copy, not the caller's files
+            for name, variable in DEPLOYMENT_FILES.items():
+                (self.output / name).write_bytes((Path(deployment) / name).read_bytes())
+                env[variable] = str((self.output / name).resolve())
+            env.update({f"ARCHLAB_RUN_{switch}": "1" for switch in GATE_SWITCHES})
+            env["ARCHLAB_LEARNER_WORK"] = str(self.output / "learner")
+        return env
+
+    def verdict(self, exit_code: int) -> int:
+        log = self.output / "pytest.log"
+        if absent := [p.name for p in self.reports if not p.exists()]:
+            raise RuntimeError(f"pytest did not produce a report (exit {exit_code}; missing {absent}); see {log}")
+        per_rank = [list(ET.parse(p).iter("testcase")) for p in self.reports]
+        if not all(per_rank):
+            raise RuntimeError(f"qualification tests failed or skipped: empty rank report; see {log}")
+        not_passed = [case.get("name") for cases in per_rank for case in cases if any(case.find(t) is not None for t in _NOT_A_PASS)]
+        if exit_code or not_passed:
+            raise RuntimeError(f"qualification tests failed or skipped: {not_passed}; see {log}")
+        return sum(map(len, per_rank))
+
+
 def run_pytest(nodes, output, *, deployment=None, timeout: int = 1800, world_size: int = 1, env_extra=None,
                root: Path = ROOT) -> dict:
     """Run concrete pytest nodes of this checkout; a missing, failed or SKIPPED test never passes."""
     output = Path(output)
     output.mkdir(parents=True, exist_ok=True)
-    for node in nodes:
-        if not (root / node.split("::", 1)[0]).is_file():
-            return dict(status="pending", reason="concrete integration test not implemented", node=node)
-    report = output / "pytest.xml"
-    reports = [output / f"pytest-rank-{r}.xml" for r in range(world_size)] if world_size > 1 else [report]
-    for path in reports:
-        path.unlink(missing_ok=True)
-    cmd = [sys.executable]
-    if world_size > 1:
-        cmd += ["-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1", "--nnodes=1",
-                f"--nproc_per_node={world_size}"]
-    cmd += ["-m", "pytest", "-q", *nodes, f"--basetemp={output.resolve() / 'artifacts'}", f"--junitxml={report}"]
-    env = os.environ.copy()
-    env.update(env_extra or {})
-    if deployment is not None:
-        for name in ("resolved.yaml", "experiment.json"):
-            (output / name).write_bytes((Path(deployment) / name).read_bytes())
-        env["ARCHLAB_QUALIFICATION_CONFIG"] = str((output / "resolved.yaml").resolve())
-        env["ARCHLAB_QUALIFICATION_EXPERIMENT"] = str((output / "experiment.json").resolve())
-        env.update(ARCHLAB_RUN_DISTRIBUTED="1", ARCHLAB_RUN_ENGINE="1", ARCHLAB_RUN_NATIVE_CONTEXT="1",
-                   ARCHLAB_RUN_THROUGHPUT="1", ARCHLAB_RUN_AGENTIC_PIPELINE="1",
-                   ARCHLAB_LEARNER_WORK=str(output / "learner"))
-    env["ARCHLAB_JUNIT_PER_RANK"] = "1" if world_size > 1 else "0"
-    sources = source_manifest(root)
-    atomic_write_json(output / "source.json", sources)
+    gate = _PytestGate(nodes, output, world_size, root)
+    if (node := gate.unimplemented()) is not None:
+        return dict(status="pending", reason="concrete integration test not implemented", node=node)
+    for stale in gate.reports:
+        stale.unlink(missing_ok=True)
+    env = gate.environment(deployment, env_extra)
+    before = source_manifest(root)
+    atomic_write_json(output / "source.json", before)
     with (output / "pytest.log").open("w") as log:
-        done = subprocess.run(cmd, cwd=root, env=env, stdout=log, stderr=subprocess.STDOUT, timeout=timeout)
-    source = check_source_unchanged(sources, root)
-    if not all(p.exists() for p in reports):
-        raise RuntimeError(f"pytest did not produce a report (exit {done.returncode}); see {output / 'pytest.log'}")
-    cases = [c for p in reports for c in ET.parse(p).iter("testcase")]
-    if any(not list(ET.parse(p).iter("testcase")) for p in reports):
-        raise RuntimeError(f"qualification tests failed or skipped: empty rank report; see {output / 'pytest.log'}")
-    bad = [c.attrib.get("name") for c in cases
-           if any(c.find(tag) is not None for tag in ("failure", "error", "skipped"))]
-    if done.returncode or not cases or bad:
-        raise RuntimeError(f"qualification tests failed or skipped: {bad}; see {output / 'pytest.log'}")
-    return dict(status="passed", tests=len(cases), world_size=world_size, source=source,
-                deployment_sha256=({n: sha256_file(output / n) for n in ("resolved.yaml", "experiment.json")}
-                                   if deployment is not None else None),
-                reports={str(p): sha256_file(p) for p in reports})
+        exit_code = subprocess.run(gate.command(), cwd=root, env=env, stdout=log, stderr=subprocess.STDOUT, timeout=timeout).returncode
+    source = check_source_unchanged(before, root)
+    tests = gate.verdict(exit_code)
+    frozen = {n: sha256_file(output / n) for n in DEPLOYMENT_FILES} if deployment is not None else None
+    return dict(status="passed", tests=tests, world_size=world_size, source=source, deployment_sha256=frozen,
+                reports={str(p): sha256_file(p) for p in gate.reports})
+
+
+# pilot threshold field -> observed counter it bounds from below
+PILOT_FLOORS = {"minimum_completed_verifiers": "completed_verifiers", "minimum_prompt_groups": "prompt_groups",
+                "minimum_tool_calls": "tool_calls", "minimum_observation_tokens": "masked_observation_tokens",
+                "minimum_reward_contrast_groups": "reward_contrast_groups"}
 
 
 def check_learning_signal(output, pilot=None) -> dict:
-    """A completed tool loop alone does not establish a useful policy update."""
-    receipts = list((Path(output) / "artifacts").rglob("pipeline-evidence.json"))
-    if len(receipts) != 1:
+    """A completed tool loop alone does not establish a useful policy update: the update's receipt must show a finite,
+    positive gradient norm and reward contrast, and - with pilot thresholds - enough verifiers, groups, tool calls and
+    observation tokens and few enough truncations."""
+    found = list((Path(output) / "artifacts").rglob("pipeline-evidence.json"))
+    if len(found) != 1:
         raise ValueError("real policy update must write exactly one learning-signal receipt")
-    ev = json.loads(receipts[0].read_text())
-    contrast, grad_norm = ev["reward_contrast_groups"], ev["grad_norm"]
+    evidence = json.loads(found[0].read_text())
+    contrast, grad_norm = evidence["reward_contrast_groups"], evidence["grad_norm"]
     if not isinstance(grad_norm, (int, float)) or not math.isfinite(grad_norm):
         raise ValueError("real policy update did not record a finite gradient norm")
-    result = dict(receipt=str(receipts[0]), receipt_sha256=sha256_file(receipts[0]),
-                  reward_contrast_groups=contrast, grad_norm=grad_norm)
+    result = dict(receipt=str(found[0]), receipt_sha256=sha256_file(found[0]), reward_contrast_groups=contrast, grad_norm=grad_norm)
     if pilot is None:
-        if contrast <= 0 or grad_norm <= 0:
+        if min(contrast, grad_norm) <= 0:
             result.update(status="pending", reason="execution passed but this pilot has no nonzero GRPO learning signal")
         return result
-    obs = {k: ev.get(k, 0) for k in ("completed_verifiers", "tool_calls", "masked_observation_tokens",
-                                     "truncated_trajectories")}
-    obs["prompt_groups"] = len({uid.rsplit("_", 2)[0] for uid in ev.get("consumed_rollout_uids", [])})
-    obs["reward_contrast_groups"] = contrast
-    limits = dict(completed_verifiers=pilot.minimum_completed_verifiers, prompt_groups=pilot.minimum_prompt_groups,
-                  tool_calls=pilot.minimum_tool_calls, masked_observation_tokens=pilot.minimum_observation_tokens,
-                  reward_contrast_groups=pilot.minimum_reward_contrast_groups)
-    failed = [k for k, lo in limits.items() if type(obs[k]) is not int or obs[k] < lo]
-    if type(obs["truncated_trajectories"]) is not int or obs["truncated_trajectories"] > pilot.maximum_truncated_trajectories:
-        failed.append("truncated_trajectories")
+    groups = {uid.rsplit("_", 2)[0] for uid in evidence.get("consumed_rollout_uids", [])}
+    observed = {counter: evidence.get(counter, 0) for counter in (*PILOT_FLOORS.values(), "truncated_trajectories")}
+    observed.update(prompt_groups=len(groups), reward_contrast_groups=contrast)
+    whole = lambda v: type(v) is int
+    short = [counter for floor, counter in PILOT_FLOORS.items() if not whole(observed[counter]) or observed[counter] < getattr(pilot, floor)]
+    if not whole(observed["truncated_trajectories"]) or observed["truncated_trajectories"] > pilot.maximum_truncated_trajectories:
+        short.append("truncated_trajectories")
     if grad_norm <= 0:
-        failed.append("positive_gradient")
-    result.update(observed=obs, thresholds=asdict(pilot))
-    if failed:
-        result.update(status="failed", reason="bootstrap pilot health thresholds not met: " + ", ".join(failed))
+        short.append("positive_gradient")
+    result.update(observed=observed, thresholds=asdict(pilot))
+    if short:
+        result.update(status="failed", reason="bootstrap pilot health thresholds not met: " + ", ".join(short))
     return result
 
 

@@ -96,6 +96,9 @@ def main() -> None:
     ap.add_argument("--weight-decay", type=float, default=0.28)
     ap.add_argument("--config", default="d20", choices=["d20", "qwen35_4b_simplicial", "v41_moe"],
                     help="d20: the speedrun GPT (headline); the others time the mesh trainer's step")
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8_block", "nvfp4"],
+                    help="configurations 3 and 4 only: compute precision of the linear layers (the d20 headline is bf16)")
+    ap.add_argument("--per-gpu-batch", type=int, default=0, help="configurations 3 and 4: sequences per GPU per step (0: 16 / 4)")
     ap.add_argument("--no-extra", action="store_true", help="skip the kernel metrics appended to the d20 line")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -254,18 +257,21 @@ def mesh_config(args) -> None:
     run_dir = tempfile.mkdtemp(prefix="bench-mesh-") if rank == 0 else ""
     if args.config == "qwen35_4b_simplicial":
         tp = 2 if world >= 2 else 1
-        seq, per_gpu = 8192, 16
+        seq, per_gpu = 8192, args.per_gpu_batch or 16
         argv = ["--model=qwen35_4b", f"--tp={tp}", "--seq-len=8192", f"--global-batch={per_gpu * world}"]
         if tp > 1:
             argv.append("--sequence-parallel")
         par = f"tp{tp}+sp x zero-dp{world // tp}"
         model = "Qwen3.5-4B-like dense (36L, hidden 2560, 32/8 heads x 128, FFN 9728, vocab 151936), every 4th layer 2-simplicial 32x512"
     else:
-        seq, per_gpu = 4096, 4
+        if world < 4:
+            raise SystemExit("v41_moe keeps 64 experts' weights, gradients and optimizer state on the expert-parallel group: "
+                             "it needs at least 4 GPUs of 180 GB")
+        seq, per_gpu = 4096, args.per_gpu_batch or 4
         argv = ["--model=v41_moe", f"--ep={world}", "--seq-len=4096", "--micro-batch=1", f"--global-batch={per_gpu * world}"]
         par = f"ep{world} (= dp{world})"
         model = "DeepSeek-V4.1-style MoE (24L, hidden 2048, 64 routed experts FFN 1408 top-6 + 2 shared, DSA top-2048, 4 HC streams)"
-    argv += [f"--steps={total}", f"--run-dir={run_dir or tempfile.gettempdir() + '/bench-mesh-other'}"]
+    argv += [f"--precision={args.precision}", f"--steps={total}", f"--run-dir={run_dir or tempfile.gettempdir() + '/bench-mesh-other'}"]
     marks = {}
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
 
@@ -289,7 +295,7 @@ def mesh_config(args) -> None:
     print(json.dumps({
         "metric": "train tokens/sec/box", "value": tokens * args.steps / dev_s, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_s / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "scaling": "weak", "vs_baseline": None, "dtype": args.precision,
         "data": "synthetic: Zipf(1.1) token ids from seed 0, random-init weights", "impl": "native",
         "config": {"model": model, "global_batch": tokens, "seq_len": seq, "parallelism": par,
                    "l2": "working set per step far exceeds the 126 MB L2; no explicit flush"},
