@@ -1,8 +1,7 @@
-"""Storage hygiene: verified bulk offload with a SQLite journal, and newest-complete checkpoint
-retention (src/archlab/storage/bulk_offload.py:17-108, checkpoint_retention.py:29-250)."""
+"""Storage hygiene: verified bulk offload with a SQLite journal (src/archlab/storage/bulk_offload.py:17-108).
+Checkpoint retention is the service in ``services.retention``."""
 from __future__ import annotations
 
-import json
 import os
 import shutil
 import sqlite3
@@ -63,30 +62,3 @@ def transfer(source, destination, journal: OffloadJournal, *, link: bool = False
     if delete_source:
         source.unlink()
     return {"source": str(source), "state": "verified", "sha256": src_sha}
-
-
-def complete_checkpoints(root) -> list[Path]:
-    """Checkpoint directories under ``root`` that carry a completion marker, oldest first."""
-    out = []
-    for d in sorted(Path(root).iterdir()):
-        if d.is_dir() and any((d / m).is_file() for m in ("COMPLETE.json", "EXPORT_COMPLETE.json", ".metadata")):
-            out.append(d)
-    return sorted(out, key=lambda p: p.stat().st_mtime)
-
-
-def sweep(root, *, keep: int = 2, apply: bool = False, audit=None) -> dict:
-    """Keep the newest ``keep`` COMPLETE checkpoints; incomplete directories are never touched (they may be
-    in flight).  ``apply=False`` only reports."""
-    done = complete_checkpoints(root)
-    doomed = done[:-keep] if keep > 0 else done
-    removed = []
-    for d in doomed:
-        newest = done[-1]
-        record = {"removed": str(d), "replacement": str(newest), "bytes": sum(f.stat().st_size for f in d.rglob("*") if f.is_file())}
-        if apply:
-            shutil.rmtree(d)
-        removed.append(record)
-        if audit is not None:
-            with open(audit, "a") as f:
-                f.write(json.dumps({**record, "applied": apply, "time": time.time()}) + "\n")
-    return {"kept": [str(d) for d in done[len(doomed):]], "removed": removed, "applied": apply}

@@ -57,19 +57,6 @@ def test_offload_verifies_and_retention_keeps_newest_complete(tmp_path):
         storage.transfer(src, tmp_path / "dst" / "b.bin", j, expected_sha="0" * 64)
     with pytest.raises(ValueError):
         storage.confined(tmp_path, "../x")
-    root = tmp_path / "ckpt"
-    for i in range(4):
-        d = root / f"step{i}"
-        d.mkdir(parents=True)
-        (d / "w.pt").write_bytes(b"x" * 10)
-        if i != 2:
-            (d / "COMPLETE.json").write_text("{}")
-        os.utime(d, (i, i))
-    rep = storage.sweep(root, keep=2, apply=False)
-    assert [os.path.basename(r["removed"]) for r in rep["removed"]] == ["step0"] and (root / "step0").exists()
-    storage.sweep(root, keep=2, apply=True, audit=tmp_path / "audit.jsonl")
-    assert not (root / "step0").exists() and (root / "step2").exists()      # incomplete one is never touched
-    assert json.loads((tmp_path / "audit.jsonl").read_text())["applied"] is True
 
 
 def test_math_rewards_are_exact():
