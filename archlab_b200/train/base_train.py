@@ -71,6 +71,23 @@ def parse_args(argv=None):
     ap.add_argument("--max-training-tokens", type=int, default=0, help="refuse a horizon longer than this many tokens")
     ap.add_argument("--initialization-hash", default=None,
                     help="sha256 over the initial weights (contracts.provenance.hash_named_tensors); a mismatch is refused")
+    # horizon, evaluation cadence and artifact policy of the speedrun script (src/archlab/speedrun/base_train.py:466-642)
+    ap.add_argument("--target-flops", type=float, default=-1.0, help="derive the step count from a training-FLOP budget (-1: off)")
+    ap.add_argument("--exact-global-batch-replay", action=argparse.BooleanOptionalAction, default=False,
+                    help="evaluation consumes whole global batches, so any world size sees the same held-out tokens")
+    ap.add_argument("--core-metric-every", type=int, default=-1, help="multiple-choice task suite every N steps (-1: off)")
+    ap.add_argument("--core-metric-max-per-task", type=int, default=500)
+    ap.add_argument("--core-tasks", default=None, help="JSON task bundle for --core-metric-every (see train.evaluation.load_task_bundle)")
+    ap.add_argument("--sample-every", type=int, default=-1, help="greedy samples from the prompt set every N steps (-1: off)")
+    ap.add_argument("--prompt-file", default=None, help="YAML / JSON prompt set: a list of strings or of token-id lists")
+    ap.add_argument("--tokenizer-dir", default=None, help="tokenizer for byte counts, prompts and task text")
+    ap.add_argument("--artifact-policy", choices=("metrics_only", "research", "frozen_historical"), default="metrics_only",
+                    help="research requires pinned data, an initialization identity and checkpoints")
+    ap.add_argument("--data-manifest", default=None, help="content manifest of --data-dir, verified before the first step")
+    ap.add_argument("--data-verification", choices=("metadata", "full"), default="metadata")
+    ap.add_argument("--precision-recipe", choices=("bf16", "fp8_block", "nvfp4"), default="bf16",
+                    help="bf16 runs the fused engine; the block-scaled recipes run the module path on the block-scaled GEMMs")
+    ap.add_argument("--device-type", default="", help="cuda | cpu (empty: autodetect)")
     ap.add_argument("--throughput-warmup-steps", type=int, default=10)
     ap.add_argument("--throughput-measurement-steps", type=int, default=0)
     _add_arm_flags(ap)
@@ -136,11 +153,12 @@ def run_arm(a) -> int:
     return 0
 
 
-def _init_distributed():
+def _init_distributed(device_type: str = ""):
+    use_cuda = torch.cuda.is_available() if not device_type else device_type == "cuda"
     if "RANK" not in os.environ:
-        return 0, 1, torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+        return 0, 1, torch.device("cuda", 0) if use_cuda else torch.device("cpu")
     rank, local = int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", 0))
-    if torch.cuda.is_available():
+    if use_cuda:
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         return rank, dist.get_world_size(), torch.device("cuda", local)
@@ -148,29 +166,159 @@ def _init_distributed():
     return rank, dist.get_world_size(), torch.device("cpu")
 
 
+def check_artifact_policy(a) -> None:
+    """``research`` runs must be reproducible from their artifacts: pinned data, a declared initialization, checkpoints."""
+    if a.artifact_policy != "research":
+        return
+    missing = [what for what, ok in (("--data-dir with --data-manifest", bool(a.data_dir and a.data_manifest)),
+                                     ("--initialization-hash", bool(a.initialization_hash)),
+                                     ("a final checkpoint", a.save_final_checkpoint)) if not ok]
+    if missing:
+        raise SystemExit("artifact policy 'research' requires " + ", ".join(missing))
+
+
+def verify_data(a) -> dict | None:
+    """Checks --data-dir against --data-manifest before a single token is read; returns the dataset identity."""
+    if not a.data_manifest:
+        return None
+    if not a.data_dir:
+        raise SystemExit("--data-manifest needs --data-dir")
+    from ..contracts.provenance import verify_dataset_manifest
+
+    return verify_dataset_manifest(a.data_dir, a.data_manifest, mode=a.data_verification)
+
+
+def horizon(a, model) -> int:
+    """Step count: explicit, from a FLOP budget, or from the tokens-per-parameter ratio (in that order)."""
+    if a.num_iterations > 0:
+        return a.num_iterations
+    if a.target_flops > 0:
+        return max(1, round(a.target_flops / (model.estimate_flops() * a.total_batch_size)))
+    scaling = model.num_scaling_params()
+    n_params = scaling["total"] if isinstance(scaling, dict) else int(scaling)
+    return max(1, int(a.target_param_data_ratio * n_params) // a.total_batch_size)
+
+
+class EvalCadence:
+    """What the loop does between optimizer steps: validation bits per byte, the task suite, samples."""
+
+    def __init__(self, a, trainer: Trainer, rank: int, world: int, device, log):
+        self.a, self.trainer, self.rank, self.world, self.device, self.log = a, trainer, rank, world, device, log
+        self.tokenizer = None
+        if a.tokenizer_dir:
+            from ..data.tokenizer import BPETokenizer
+
+            self.tokenizer = BPETokenizer.load(Path(a.tokenizer_dir))
+        vocab = trainer.model.config.vocab_size
+        if self.tokenizer is not None:
+            table = list(self.tokenizer.token_bytes())[:vocab]
+            self.token_bytes = torch.tensor(table + [0] * (vocab - len(table)), dtype=torch.int64, device=device)
+        else:
+            self.token_bytes = torch.ones(vocab, dtype=torch.int64, device=device)    # no tokenizer: bits per token
+        self.tasks = None
+        if a.core_metric_every > 0:
+            if not a.core_tasks:
+                raise SystemExit("--core-metric-every needs --core-tasks")
+            from .evaluation import load_task_bundle
+
+            self.tasks = load_task_bundle(a.core_tasks, self.tokenizer)
+        self.prompts = None
+        if a.sample_every > 0:
+            if not a.prompt_file:
+                raise SystemExit("--sample-every needs --prompt-file")
+            from .evaluation import load_prompts
+
+            self.prompts = load_prompts(a.prompt_file, self.tokenizer)
+        self.min_val_bpb, self.val_bpb = float("inf"), None
+
+    def due(self, every: int, step: int, last: bool, *, at_zero: bool) -> bool:
+        return every > 0 and (last or (step % every == 0 and (at_zero or step > 0)))
+
+    def eval_steps(self) -> int:
+        a = self.a
+        if a.exact_global_batch_replay:
+            if a.eval_tokens % a.total_batch_size:
+                raise ValueError("exact replay requires eval tokens divisible by total batch tokens")
+            return a.eval_tokens // a.total_batch_size * (a.total_batch_size // (a.device_batch_size * a.max_seq_len * self.world))
+        return a.eval_tokens // (a.device_batch_size * a.max_seq_len * self.world)
+
+    def _val_batches(self, steps: int):
+        a = self.a
+        if a.data_dir:
+            from ..data.fineweb import FineWebBinaryLoader
+
+            loader = FineWebBinaryLoader(a.data_dir, "val", a.device_batch_size, a.max_seq_len, rank=self.rank, world_size=self.world,
+                                         device=self.device)
+            for _ in range(steps):
+                yield next(loader)
+        else:                                   # held-out synthetic stream: same law, a seed the training stream never uses
+            gen = ZipfTokens(a.vocab_size, a.max_seq_len, a.device_batch_size, seed=a.seed + 7919, rank=self.rank, pin=False)
+            for i in range(steps):
+                block = gen.block(i).to(self.device)
+                yield block[:, :-1], block[:, 1:]
+
+    def run(self, step: int, last: bool, flops_per_token: int) -> None:
+        a, model = self.a, self.trainer.model
+        if self.due(a.eval_every, step, last, at_zero=True) and a.eval_tokens > 0:
+            from .evaluation import evaluate_bpb
+
+            with torch.autocast(self.device.type, dtype=torch.bfloat16, enabled=self.device.type == "cuda"):
+                bpb = evaluate_bpb(model, self._val_batches(self.eval_steps()), self.token_bytes)
+            if bpb != bpb or bpb in (float("inf"), float("-inf")):
+                raise FloatingPointError(f"non-finite validation BPB at step {step}")
+            self.val_bpb, self.min_val_bpb = bpb, min(self.min_val_bpb, bpb)
+            self._emit({"kind": "validation", "step": step, "tokens": a.total_batch_size * step, "bpb": bpb, "eval_tokens": a.eval_tokens,
+                        "total_training_flops": flops_per_token * a.total_batch_size * step})
+        if self.tasks is not None and self.due(a.core_metric_every, step, last, at_zero=False):
+            from .evaluation import evaluate_core
+
+            res = evaluate_core(model, self.tasks, max_per_task=a.core_metric_max_per_task, rank=self.rank, world=self.world)
+            self._emit({"kind": "core", "step": step, "core_metric": res["core_metric"], "centered_results": res["centered_results"]})
+        if self.prompts is not None and self.rank == 0 and self.due(a.sample_every, step, last, at_zero=False):
+            from .evaluation import generate_batch
+
+            was = model.training
+            model.eval()
+            outs = generate_batch(model, self.prompts, 16, temperature=0.0, seed=a.seed)
+            model.train(was)
+            shown = [self.tokenizer.decode(p + o) if self.tokenizer is not None else o for p, o in zip(self.prompts, outs)]
+            self._emit({"kind": "samples", "step": step, "samples": shown})
+
+    def _emit(self, row: dict) -> None:
+        if self.log is not None:
+            self.log.write(json.dumps(row) + "\n")
+            self.log.flush()
+        if self.rank == 0:
+            print(json.dumps({k: v for k, v in row.items() if k != "samples"} if row["kind"] != "samples" else row), flush=True)
+
+
 def main(argv=None) -> int:
     a = parse_args(argv)
     if a.arch_family not in (None, "nanochat"):
         return run_arm(a)
-    rank, world, device = _init_distributed()
-    model_cfg = GPTConfig.from_depth(a.depth, sequence_len=a.max_seq_len, vocab_size=a.vocab_size)
+    rank, world, device = _init_distributed(a.device_type)
+    check_artifact_policy(a)
+    data_identity = verify_data(a) if rank == 0 or world == 1 else None
+    model_cfg = GPTConfig.from_depth(a.depth, sequence_len=a.max_seq_len, vocab_size=a.vocab_size, aspect_ratio=a.aspect_ratio,
+                                     head_dim=a.head_dim, window_pattern=a.window_pattern)
     tokens_per_micro = a.device_batch_size * a.max_seq_len * world
     if a.total_batch_size % tokens_per_micro:
         raise SystemExit("total batch must be a multiple of device batch x sequence length x world size")
     accum = a.total_batch_size // tokens_per_micro
     local_batch = a.device_batch_size * accum
-    probe = Trainer.__new__(Trainer)                       # parameter count decides the horizon
-    iters = a.num_iterations
-    cfg = TrainerConfig(model=model_cfg, micro_batch=a.device_batch_size, num_iterations=max(iters, 1), matrix_lr=a.matrix_lr,
-                        embedding_lr=a.embedding_lr, unembedding_lr=a.unembedding_lr, weight_decay=a.weight_decay,
-                        warmup_steps=a.warmup_steps, warmdown_ratio=a.warmdown_ratio, seed=a.seed, zero_impl=a.zero_impl)
+    cfg = TrainerConfig(model=model_cfg, micro_batch=a.device_batch_size, num_iterations=max(a.num_iterations, 1), matrix_lr=a.matrix_lr,
+                        embedding_lr=a.embedding_lr, unembedding_lr=a.unembedding_lr, scalar_lr=a.scalar_lr, weight_decay=a.weight_decay,
+                        warmup_steps=a.warmup_steps, warmdown_ratio=a.warmdown_ratio, final_lr_frac=a.final_lr_frac, seed=a.seed,
+                        zero_impl=a.zero_impl, use_engine=a.precision_recipe == "bf16")
     trainer = Trainer(cfg, device=device)
-    del probe
-    if iters <= 0:
-        scaling = trainer.model.num_scaling_params()
-        n_params = scaling["total"] if isinstance(scaling, dict) else int(scaling)
-        iters = max(1, int(a.target_param_data_ratio * n_params) // a.total_batch_size)
-        trainer.schedule.num_iterations = iters
+    precision_report = None
+    if a.precision_recipe != "bf16":
+        from ..ops.blockscaled import convert_linears
+
+        precision_report = convert_linears(trainer.model, a.precision_recipe)
+    iters = horizon(a, trainer.model)
+    trainer.schedule.num_iterations = iters
+    flops_per_token = trainer.model.estimate_flops()
     n_scaling = trainer.model.num_scaling_params()
     n_scaling = n_scaling["total"] if isinstance(n_scaling, dict) else int(n_scaling)
     if a.max_parameters and n_scaling > a.max_parameters:
@@ -187,41 +335,56 @@ def main(argv=None) -> int:
     ckpt_dir = Path(a.checkpoint_dir) if a.checkpoint_dir else run_dir / "checkpoints"
     if rank == 0:
         run_dir.mkdir(parents=True, exist_ok=True)
-        (run_dir / "config.json").write_text(json.dumps({"args": vars(a), "world_size": world, "grad_accum_steps": accum,
-                                                         "num_iterations": iters}, indent=2, default=str))
-    start = 0
+        (run_dir / "config.json").write_text(json.dumps({
+            "args": vars(a), "world_size": world, "grad_accum_steps": accum, "num_iterations": iters, "flops_per_token": flops_per_token,
+            "artifact_policy": a.artifact_policy, "data_identity": data_identity, "precision": precision_report}, indent=2, default=str))
+    start, loop_state = 0, {}
     if a.resume_from_step >= 0:
-        start = resume(trainer, ckpt_dir, a.resume_from_step, rank, world, device)
+        start, loop_state = resume(trainer, ckpt_dir, a.resume_from_step, rank, world, device)
     if a.data_dir:
         from ..data.fineweb import FineWebBinaryLoader
 
-        loader = FineWebBinaryLoader(a.data_dir, local_batch, a.max_seq_len, rank=rank, world_size=world)
-        loader.seek(start) if hasattr(loader, "seek") else None
-        next_block = lambda i: loader.next_batch_tokens() if hasattr(loader, "next_batch_tokens") else loader.block(i)
-        data_tag = "fineweb"
+        loader = FineWebBinaryLoader(a.data_dir, "train", local_batch, a.max_seq_len, rank=rank, world_size=world, device="cpu",
+                                     start_batch_index=start)
+        next_block = lambda i: loader.next_block().view(1, -1).unfold(1, a.max_seq_len + 1, a.max_seq_len)[0].contiguous()
+        data_tag, data_state = "fineweb", loader.state_dict
     else:
         gen = ZipfTokens(a.vocab_size, a.max_seq_len, local_batch, seed=a.seed, rank=rank, pin=device.type == "cuda")
-        next_block = gen.block
-        data_tag = "synthetic-zipf"
+        next_block, data_tag, data_state = gen.block, "synthetic-zipf", (lambda: {"batch_index": trainer.step_index})
     log = open(a.metrics_path or run_dir / f"metrics_rank{rank}.jsonl", "a") if rank == 0 else None
-    t_last = time.perf_counter()
-    stamps, paused = [t_last], 0.0
-    for step in range(start, iters):
+    cadence = EvalCadence(a, trainer, rank, world, device, log)
+    cadence.min_val_bpb = loop_state.get("min_val_bpb", cadence.min_val_bpb)
+    smooth, total_time = loop_state.get("smooth_train_loss", 0.0), loop_state.get("total_training_time", 0.0)
+    stamps, paused = [time.perf_counter()], 0.0
+    step = start
+    while True:                                   # iters + 1 passes: evaluation and the final checkpoint follow the last update
+        last = step == iters
+        cadence.run(step, last, flops_per_token)
+        due_save = step > start and a.save_every > 0 and step % a.save_every == 0
+        if (last and a.save_final_checkpoint) or due_save:
+            t_save = time.perf_counter()
+            extra = {"artifact_policy": a.artifact_policy, "data_identity": data_identity, "val_bpb": cadence.val_bpb,
+                     "dataloader_state_dict": data_state(),
+                     "loop_state": {"min_val_bpb": cadence.min_val_bpb, "smooth_train_loss": smooth, "total_training_time": total_time}}
+            save(trainer, ckpt_dir, step, rank, model_cfg, a, extra)
+            paused += time.perf_counter() - t_save                               # a checkpoint is not a training interval
+        if last:
+            break
+        t0 = time.perf_counter()
         loss = trainer.train_step(next_block(step))
-        if a.finite_check_every > 0 and (step + 1) % a.finite_check_every == 0 and loss != loss:
-            raise FloatingPointError(f"non-finite loss at step {step + 1}")        # classified as a numerical failure
+        step += 1
+        if a.finite_check_every > 0 and step % a.finite_check_every == 0 and loss != loss:
+            raise FloatingPointError(f"non-finite loss at step {step}")          # classified as a numerical failure
         now = time.perf_counter()
         stamps.append(now - paused)
-        if log is not None and (a.metrics_every <= 1 or (step + 1) % a.metrics_every == 0 or step + 1 == iters):
-            log.write(json.dumps({"step": step + 1, "loss": loss, "tokens_per_second": a.total_batch_size / (now - t_last),
-                                  "data": data_tag}) + "\n")
+        smooth = 0.9 * smooth + 0.1 * loss
+        if step - start > 10:
+            total_time += now - t0                                               # the first steps carry one-off set-up cost
+        if log is not None and (a.metrics_every <= 1 or step % a.metrics_every == 0 or step == iters):
+            log.write(json.dumps({"kind": "train", "step": step, "loss": loss, "smooth_loss": smooth / (1 - 0.9 ** (step - start)),
+                                  "tokens_per_second": a.total_batch_size / (now - t0), "total_training_time": total_time,
+                                  "total_training_flops": flops_per_token * a.total_batch_size * step, "data": data_tag}) + "\n")
             log.flush()
-        t_last = now
-        last = step + 1 == iters
-        if (a.save_every > 0 and (step + 1) % a.save_every == 0) or (last and a.save_final_checkpoint):
-            save(trainer, ckpt_dir, step + 1, rank, model_cfg, a)
-            paused += time.perf_counter() - now                                  # a checkpoint is not a training interval
-            t_last = time.perf_counter()
     if rank == 0 and len(stamps) > 1:
         from ..contracts.performance import ThroughputProtocol, summarize_step_timestamps
         from ..contracts.substrate import atomic_write_json
@@ -235,11 +398,11 @@ def main(argv=None) -> int:
     return 0
 
 
-def save(trainer: Trainer, ckpt_dir, step: int, rank: int, model_cfg: GPTConfig, args) -> None:
+def save(trainer: Trainer, ckpt_dir, step: int, rank: int, model_cfg: GPTConfig, args, extra: dict | None = None) -> None:
     if hasattr(trainer.optimizer, "gather_master"):
         trainer.optimizer.gather_master()                    # full fp32 weights on every rank before the write
     meta = {"step": step, "model_config": {k: (str(v) if isinstance(v, torch.dtype) else v) for k, v in asdict(model_cfg).items()},
-            "user_config": {k: v for k, v in vars(args).items()}, "world_size": trainer.world}
+            "user_config": {k: v for k, v in vars(args).items()}, "world_size": trainer.world, **(extra or {})}
     ckpt.save_checkpoint(ckpt_dir, step, trainer.model.state_dict(), trainer.optimizer.state_dict(), meta, rank=rank,
                          rng_data=ckpt.capture_rng_state())
     if trainer.world > 1:
@@ -248,7 +411,7 @@ def save(trainer: Trainer, ckpt_dir, step: int, rank: int, model_cfg: GPTConfig,
         ckpt.verify_checkpoint_bundle(ckpt_dir, step, world_size=trainer.world, require_rng=True)
 
 
-def resume(trainer: Trainer, ckpt_dir, step: int, rank: int, world: int, device) -> int:
+def resume(trainer: Trainer, ckpt_dir, step: int, rank: int, world: int, device) -> tuple[int, dict]:
     ckpt.verify_checkpoint_bundle(ckpt_dir, step, world_size=world, require_rng=True)
     state, optim, meta = ckpt.load_checkpoint(ckpt_dir, step, device, load_optimizer=True, rank=rank)
     if int(meta.get("world_size", world)) != world:
@@ -262,7 +425,7 @@ def resume(trainer: Trainer, ckpt_dir, step: int, rank: int, world: int, device)
     if rng is not None:
         ckpt.restore_rng_state(rng)
     trainer.step_index = step
-    return step
+    return step, dict(meta.get("loop_state") or {})
 
 
 if __name__ == "__main__":

@@ -24,7 +24,7 @@ def evaluate_bpb(model, batches: Iterable[tuple[torch.Tensor, torch.Tensor]], to
         valid = y >= 0
         nbytes = torch.where(valid, token_bytes[y.clamp_min(0)], torch.zeros_like(y))
         counted = nbytes > 0
-        total_nats += (loss.double() * counted).sum()
+        total_nats += (loss.double().reshape(y.shape) * counted).sum()
         total_bytes += nbytes.sum()
     if dist.is_available() and dist.is_initialized():
         dist.all_reduce(total_nats, group=group)
@@ -82,3 +82,78 @@ def generate_batch(model, prompts: list[list[int]], max_tokens: int, *, temperat
                 break
         ids = torch.cat([ids, nxt], 1)
     return outs
+
+
+# ---- task suite and prompt sets of the training loop -----------------------------------------------------------------
+def load_task_bundle(path, tokenizer=None) -> dict[str, dict]:
+    """A JSON task bundle: ``{task: {"random_baseline": b, "items": [{"prefix": ..., "choices": [...], "gold": i}, ...]}}``.
+    ``prefix`` / ``choices`` are token-id lists, or strings when a tokenizer is given (the prefix is encoded with a
+    leading BOS, each choice as the continuation of the prefix text)."""
+    import json
+    from pathlib import Path
+
+    bundle = json.loads(Path(path).read_text())
+    out = {}
+    for task, body in bundle.items():
+        items = []
+        for it in body["items"]:
+            prefix, choices = it["prefix"], it["choices"]
+            if isinstance(prefix, str):
+                if tokenizer is None:
+                    raise ValueError(f"task {task} holds text; a tokenizer is needed")
+                base = tokenizer.encode(prefix, prepend_bos=True)
+                choices = [tokenizer.encode(prefix + c, prepend_bos=True)[len(base):] for c in choices]
+                prefix = base
+            if not 0 <= int(it["gold"]) < len(choices) or any(len(c) == 0 for c in choices) or len(prefix) == 0:
+                raise ValueError(f"malformed item in task {task}")
+            items.append({"prefix": list(prefix), "choices": [list(c) for c in choices], "gold": int(it["gold"])})
+        if not items or not 0 <= body["random_baseline"] < 1:
+            raise ValueError(f"task {task} needs items and a baseline in [0, 1)")
+        out[task] = {"random_baseline": float(body["random_baseline"]), "items": items}
+    return out
+
+
+@torch.no_grad()
+def evaluate_core(model, tasks: dict[str, dict], *, max_per_task: int = -1, rank: int = 0, world: int = 1, group=None) -> dict:
+    """Accuracy per task (items strided over the ranks, counts all-reduced), centred accuracies and their mean."""
+    from ..data.tokenizer import core_metric
+
+    dev = next(model.parameters()).device
+    was_training = model.training
+    model.eval()
+    acc = {}
+    for task, body in tasks.items():
+        items = body["items"][:max_per_task] if max_per_task > 0 else body["items"]
+        hits = torch.zeros(2, dtype=torch.float64, device=dev)
+        for it in items[rank::world]:
+            hits[0] += score_multiple_choice(model, it["prefix"], it["choices"]) == it["gold"]
+            hits[1] += 1
+        if world > 1:
+            dist.all_reduce(hits, group=group)
+        acc[task] = float(hits[0] / hits[1].clamp_min(1))
+    model.train(was_training)
+    base = {t: tasks[t]["random_baseline"] for t in tasks}
+    centered = {t: (acc[t] - base[t]) / (1.0 - base[t]) for t in tasks}
+    return {"results": acc, "centered_results": centered, "core_metric": core_metric(acc, base)}
+
+
+def load_prompts(path, tokenizer=None) -> list[list[int]]:
+    """A YAML or JSON list of prompts: strings (encoded with a leading BOS) or token-id lists."""
+    from pathlib import Path
+
+    import yaml
+
+    doc = yaml.safe_load(Path(path).read_text())
+    prompts = doc.get("prompts") if isinstance(doc, dict) else doc
+    if not isinstance(prompts, list) or not prompts:
+        raise ValueError("the prompt file holds no prompts")
+    out = []
+    for p in prompts:
+        if isinstance(p, str):
+            if tokenizer is None:
+                raise ValueError("text prompts need a tokenizer")
+            p = tokenizer.encode(p, prepend_bos=True)
+        if not p or not all(isinstance(t, int) for t in p):
+            raise ValueError("a prompt must be text or a non-empty list of token ids")
+        out.append(list(p))
+    return out
