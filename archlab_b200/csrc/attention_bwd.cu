@@ -6,6 +6,10 @@
 //     S^T  = K Q^T            P^T  = exp2(S^T * scale*log2e - lse2[q])
 //     dP^T = V dO^T           dS^T = P^T * (dP^T - delta[q]) * scale
 //     dV  += P^T dO           dK  += dS^T Q           dQ^T = K^T dS^T   (-> fp32 atomics)
+// Warps: TMA producer, MMA issuer, eight compute warps (P^T / dS^T of a step), four dQ warps that carry dQ^T of the
+// previous step from TMEM through a shared staging tile into the fp32 accumulator with one bulk tensor reduction, so
+// that the compute warps go straight to the next step (a completed S^T of step i+1 implies that the products of step
+// i have finished reading P^T / dS^T, because one thread's tcgen05.mma operations complete in issue order).
 // dK / dV stay in TMEM for the whole CTA lifetime and are written once: no atomics on them and a
 // bit-reproducible result; only dQ uses floating-point atomics (the reference's key-owned TileLang
 // backward, src/archlab/architectures/tilelang_gqa.py:64-152, makes the same choice).
@@ -14,13 +18,14 @@
 #include "attention.h"
 #include <cuda.h>
 #include <mutex>
+#include <cstdlib>
 
 namespace nga {
 
 constexpr int AB_D = 128;
 constexpr int AB_BK = 128;   // keys per CTA
 constexpr int AB_BQ = 64;    // queries per inner step
-constexpr int AB_THREADS = 320;   // TMA warp, MMA warp, 8 compute warps
+constexpr int AB_THREADS = 448;   // TMA warp, MMA warp, 8 compute warps, 4 dQ warps
 
 struct AttnBwdParams {
   __nv_bfloat16* dqkv;   // [B*T, (Hq+2Hkv)*D]
@@ -31,6 +36,7 @@ struct AttnBwdParams {
   float scale, scale_log2;
   int* status;
   long long* prof;       // optional phase cycle counters written by CTA (0,0,0)
+  int debug_skip_dq;     // measurement aid: leave the dQ reduction out
   const uint32_t* selT;  // optional key-major selection bits [B, T(key), T/32] (bit q of row k)
 };
 
@@ -46,6 +52,14 @@ struct AttnBwdSmem {
   static constexpr int kBar = kVec + 8 * 128 * 4;
   static constexpr int kTotal = kBar + 16 * 8 + 16 + 1024;
 };
+
+// Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completion on an mbarrier.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 
 // delta[b, h, t] = sum_d O * dO   (one warp per (token, head))
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out,
@@ -104,8 +118,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
   uint64_t* pds_full = bars + 6;
   uint64_t* mma2_done = bars + 7;
   uint64_t* dq_free = bars + 8;
-  uint64_t* dqs_full = bars + 9;    // dQ staging tile written by all compute warps
-  uint64_t* dqs_free = bars + 10;   // previous bulk reduction has finished reading the tile
+  uint64_t* all_done = bars + 9;    // every product of the CTA has completed (dK / dV are final)
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
   float* s_vec = reinterpret_cast<float*>(smem + S::kVec);
@@ -122,6 +135,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
   const int niter = nq * group;
   const int k_col = (p.Hq + hk) * AB_D;
   const int v_col = (p.Hq + p.Hkv + hk) * AB_D;
+  // full 64-query steps everywhere: the per-query vectors can come in by bulk copy (16-byte aligned, in bounds)
+  const bool fast_vec = (p.T % AB_BQ) == 0;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -132,9 +147,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
     mbar_init(st_full, 1);
     mbar_init(pds_full, 8);
     mbar_init(mma2_done, 1);
-    mbar_init(dq_free, 8);
-    mbar_init(dqs_full, 8);
-    mbar_init(dqs_free, 1);
+    mbar_init(dq_free, 4);
+    mbar_init(all_done, 1);
     *abort_word = 0;
     fence_mbar_init();
   }
@@ -171,7 +185,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
         const int qrow = row_base + (qt_lo + it % nq) * AB_BQ;
         uint8_t* sQ = smem + S::kQ + st * 16384;
         uint8_t* sDO = smem + S::kDO + st * 16384;
-        mbar_expect_tx(&qdo_full[st], 32768);
+        mbar_expect_tx(&qdo_full[st], 32768 + (fast_vec ? 512 : 0));
+        if (fast_vec) {
+          // log-sum-exp and delta of the step's 64 queries ride on the same barrier (256 contiguous bytes each)
+          const long long vi = ((long long)b * p.Hq + h) * p.T + (qt_lo + it % nq) * AB_BQ;
+          bulk_load_1d(s_vec + st * 128, p.lse2 + vi, 256, &qdo_full[st]);
+          bulk_load_1d(s_vec + st * 128 + 64, p.delta + vi, 256, &qdo_full[st]);
+        }
         tma_load_3d(sQ, &tm_q, &qdo_full[st], h * AB_D, qrow, 0);
         tma_load_3d(sQ + 8192, &tm_q, &qdo_full[st], h * AB_D + 64, qrow, 0);
         tma_load_3d(sDO, &tm_do, &qdo_full[st], h * AB_D, qrow, 0);
@@ -238,6 +258,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
         }
         umma_commit(mma2_done);
         umma_commit(&qdo_empty[it & 1]);
+        if (it + 1 == niter) umma_commit(all_done);
         if (it + 1 < niter) {
           ok = mbar_wait(&qdo_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_word);
           if (!ok) break;
@@ -246,6 +267,46 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
         }
       }
     }
+  } else if (warp >= 10) {
+    // ---------------------------------------------------------------- dQ warps 10..13: thread = d (TMEM lane)
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_off = uint32_t(quarter * 32) << 16;
+    float* sDQ = reinterpret_cast<float*>(smem + S::kDQ);          // [64 q][128 d] fp32
+    const bool tma_thread = (warp == 10 && lane == 0);
+    bool ok = true;
+    for (int it = 0; it < niter && ok; ++it) {
+      const int h = hk * group + it / nq;
+      const int q0 = (qt_lo + it % nq) * AB_BQ;
+      ok = __all_sync(0xffffffffu, mbar_wait(mma2_done, it & 1, abort_word));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t qv[2][32];
+      tmem_ld_32x32(t_DQT + lane_off, qv[0]);
+      tmem_ld_32x32(t_DQT + lane_off + 32, qv[1]);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_free);
+      // the staging tile is free once the previous bulk reduction has read it (its issuer waited for that before
+      // it came to this barrier).  (Reducing straight from registers with scalar red.global was measured slower:
+      // 1.23 against 1.11 ms at B16 T2048 H10.)
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sDQ[(c * 32 + i) * AB_D + r] = __uint_as_float(qv[c][i]);
+      fence_proxy_async_smem();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (tma_thread && !p.debug_skip_dq) {
+        // one bulk tensor reduction adds the 64 x 128 fp32 tile into dq_acc (rows past the sequence end carry exact
+        // zeros, rows past the tensor end are clipped by the copy engine)
+        tma_reduce_add_3d(&tm_dq, sDQ, h * AB_D, row_base + q0, 0);
+        tma_store_commit();
+        tma_store_wait_read0();
+      }
+    }
+    if (tma_thread) tma_store_wait0();
   } else {
     // ---------------------------------------------------------------- compute warps 2..9
     // thread = key row (TMEM lane); warps 2..5 own query columns 0..31 of the step, warps 6..9 own
@@ -259,9 +320,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
     const uint32_t col_off = uint32_t(chalf * 32);
     uint8_t* rowPT = smem + S::kPT + r * 128;
     uint8_t* rowDST = smem + S::kDST + r * 128;
-    float* sDQ = reinterpret_cast<float*>(smem + S::kDQ);          // [64 q][128 d] fp32
     float* my_vec = s_vec + cw * 128;                              // [2][lse 32 | delta 32]
-    const bool tma_thread = (warp == 2 && lane == 0);
     bool ok = true;
     const bool prof_on = p.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 64;
     long long pc[6] = {0, 0, 0, 0, 0, 0};
@@ -279,21 +338,31 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
       nxt_l = q < p.T ? p.lse2[vi] : INFINITY;
       nxt_d = q < p.T ? p.delta[vi] : 0.f;
     };
-    if (niter > 0) fetch_vec(0);
+    if (niter > 0 && (!fast_vec || p.selT != nullptr)) fetch_vec(0);
     for (int it = 0; it < niter && ok; ++it) {
       const int h = hk * group + it / nq;
       const int q0 = (qt_lo + it % nq) * AB_BQ;
       const bool need_mask = (q0 < k0 + AB_BK - 1) || (p.window >= 0 && q0 + AB_BQ - 1 - k0 > p.window) ||
                              (q0 + AB_BQ > p.T);
-      float* lse_b = my_vec + (it & 1) * 64;
-      float* del_b = lse_b + 32;
-      lse_b[lane] = nxt_l;
-      del_b[lane] = nxt_d;
-      const uint32_t selw = nxt_sel;
+      float* lse_b = fast_vec ? s_vec + (it & 1) * 128 + chalf * 32 : my_vec + (it & 1) * 64;
+      float* del_b = fast_vec ? lse_b + 64 : lse_b + 32;
+      if (!fast_vec) {
+        lse_b[lane] = nxt_l;
+        del_b[lane] = nxt_d;
+      }
+      // queries of this warp's 32 columns that the key row may pair with: q in [key, min(T - 1, key + window)]
+      uint32_t vis = nxt_sel;
+      if (need_mask) {
+        const int qb = q0 + chalf * 32;
+        const int i_lo = max(key - qb, 0);
+        const int i_hi = min(min(p.T - 1, p.window >= 0 ? key + p.window : p.T - 1) - qb, 31);
+        vis &= (i_hi < i_lo) ? 0u : ((i_hi >= 31 ? ~0u : ((1u << (i_hi + 1)) - 1u)) & ~((1u << i_lo) - 1u));
+      }
       __syncwarp();
-      if (it + 1 < niter) fetch_vec(it + 1);     // global loads in flight during this step
+      if (it + 1 < niter && (!fast_vec || p.selT != nullptr)) fetch_vec(it + 1);     // global loads in flight during this step
       NGA_PROFB(0);
-      ok = __all_sync(0xffffffffu, mbar_wait(st_full, it & 1, abort_word));
+      if (fast_vec) ok = __all_sync(0xffffffffu, mbar_wait(&qdo_full[it & 1], (it >> 1) & 1, abort_word));   // vectors landed
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(st_full, it & 1, abort_word));
       if (!ok) break;
       NGA_PROFB(1);
       tc_fence_after();
@@ -306,11 +375,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           float e = ex2_fast(fmaf(__uint_as_float(sv[i]), p.scale_log2, -lse_b[i]));
-          if (need_mask) {
-            const int q = q0 + chalf * 32 + i;
-            if (key > q || q >= p.T || (p.window >= 0 && q - key > p.window)) e = 0.f;
-          }
-          if (!((selw >> i) & 1u)) e = 0.f;
+          if (!((vis >> i) & 1u)) e = 0.f;
           pr[i] = e;
           ds[i] = e * (__uint_as_float(dv[i]) - del_b[i]) * p.scale;
         }
@@ -335,43 +400,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
-      // dQ^T of this step: lane = d, this warp's 32 query columns
-      ok = __all_sync(0xffffffffu, mbar_wait(mma2_done, it & 1, abort_word));
-      if (!ok) break;
-      NGA_PROFB(3);
-      tc_fence_after();
-      uint32_t qv[32];
-      tmem_ld_32x32(t_DQT + lane_off + col_off, qv);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(dq_free);
-      // the staging tile is free once the previous step's bulk reduction has read it
-      if (it > 0) {
-        if (tma_thread) {
-          tma_store_wait_read0();
-          mbar_arrive(dqs_free);
-        }
-        ok = __all_sync(0xffffffffu, mbar_wait(dqs_free, (it - 1) & 1, abort_word));
-        if (!ok) break;
-      }
-#pragma unroll
-      for (int i = 0; i < 32; ++i) sDQ[(chalf * 32 + i) * AB_D + r] = __uint_as_float(qv[i]);
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(dqs_full);
-      if (tma_thread) {
-        // one bulk tensor reduction adds the 64 x 128 fp32 tile into dq_acc (rows past the
-        // sequence end carry exact zeros, rows past the tensor end are clipped by the copy engine)
-        if (mbar_wait(dqs_full, it & 1, abort_word)) {
-          tma_reduce_add_3d(&tm_dq, sDQ, h * AB_D, row_base + q0, 0);
-          tma_store_commit();
-        }
-      }
-      NGA_PROFB(4);
     }
-    if (tma_thread) tma_store_wait0();
     if (prof_on) { for (int i = 0; i < 6; ++i) p.prof[i] = pc[i]; p.prof[6] = niter; }
+    if (ok && niter > 0) ok = __all_sync(0xffffffffu, mbar_wait(all_done, 0, abort_word));
     // ---------------------------------------------------------------- dK / dV write-out
     // warps 2..5 write dK, warps 6..9 write dV (each thread: its key row, 128 columns)
     if (ok && niter > 0) {
@@ -472,6 +503,7 @@ extern "C" int nga_attn_bwd(const void* qkv, const void* out, const void* dout, 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
   p.prof = g_attn_bwd_prof;
+  p.debug_skip_dq = getenv("NGA_ATTN_BWD_SKIP_DQ") != nullptr;
   p.selT = g_attn_bwd_selT;
   g_attn_bwd_selT = nullptr;
   if (p.selT != nullptr && (T % 64)) return -7;
