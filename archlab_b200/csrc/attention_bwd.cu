@@ -61,43 +61,49 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
                : "memory");
 }
 
-// delta[b, h, t] = sum_d O * dO   (one warp per (token, head))
+// delta[b, h, t] = sum_d O * dO   (16 lanes per (token, head), 16 bytes per lane and tensor)
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out,
                                   const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta,
                                   int B, int T, int Hq) {
-  const int lane = threadIdx.x & 31;
-  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (w >= (long long)B * T * Hq) return;
-  const long long row = w / Hq;
-  const int h = int(w % Hq);
-  const long long off = row * (long long)(Hq * AB_D) + h * AB_D + lane * 4;
-  const uint2 a = *reinterpret_cast<const uint2*>(out + off);
-  const uint2 g = *reinterpret_cast<const uint2*>(dout + off);
-  const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
-  const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g);
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int sub = int(gid & 15);
+  const long long item = gid >> 4;
+  const bool active = item < (long long)B * T * Hq;
+  const long long row = active ? item / Hq : 0;
+  const int h = active ? int(item % Hq) : 0;
   float s = 0.f;
+  if (active) {
+    const long long off = row * (long long)(Hq * AB_D) + h * AB_D + sub * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(out + off);
+    const uint4 g = *reinterpret_cast<const uint4*>(dout + off);
+    const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g);
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    float2 x = __bfloat1622float2(ah[i]), y = __bfloat1622float2(gh[i]);
-    s += x.x * y.x + x.y * y.y;
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(ah[i]), y = __bfloat1622float2(gh[i]);
+      s += x.x * y.x + x.y * y.y;
+    }
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if (lane == 0) delta[((long long)(row / T) * Hq + h) * T + (row % T)] = s;
+  for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (active && sub == 0) delta[((long long)(row / T) * Hq + h) * T + (row % T)] = s;
 }
 
 // dqkv[:, q columns] = bf16(dq_acc)
 __global__ void attn_dq_cast_kernel(const float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dqkv,
                                     long long rows, int qcols, int allcols) {
-  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;      // qcols is a multiple of 128
   if (i >= rows * qcols) return;
   const long long row = i / qcols;
   const int c = int(i % qcols);
   const float4 v = *reinterpret_cast<const float4*>(dq_acc + i);
-  uint2 u;
+  const float4 w = *reinterpret_cast<const float4*>(dq_acc + i + 4);
+  uint4 u;
   u.x = pack_bf16(v.x, v.y);
   u.y = pack_bf16(v.z, v.w);
-  *reinterpret_cast<uint2*>(dqkv + row * allcols + c) = u;
+  u.z = pack_bf16(w.x, w.y);
+  u.w = pack_bf16(w.z, w.w);
+  *reinterpret_cast<uint4*>(dqkv + row * allcols + c) = u;
 }
 
 __global__ void __launch_bounds__(AB_THREADS, 1)
@@ -486,8 +492,8 @@ extern "C" int nga_attn_bwd(const void* qkv, const void* out, const void* dout, 
     attr_done = true;
   }
   {
-    const long long warps = rows * Hq;
-    attn_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(
+    const long long threads = rows * Hq * 16;
+    attn_delta_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(
         reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout),
         delta, B, T, Hq);
     count_launch();
@@ -511,8 +517,8 @@ extern "C" int nga_attn_bwd(const void* qkv, const void* out, const void* dout, 
   attn_bwd_kernel<<<grid, AB_THREADS, AttnBwdSmem::kTotal, st>>>(tm_kv, tm_q, tm_do, tm_dq, p);
   count_launch();
   {
-    const long long n4 = rows * ocols / 4;
-    attn_dq_cast_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(
+    const long long n8 = rows * ocols / 8;
+    attn_dq_cast_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(
         dq_acc, reinterpret_cast<__nv_bfloat16*>(dqkv), rows, (int)ocols, (int)cols);
     count_launch();
   }

@@ -5,6 +5,7 @@
 // Layout: activations are [tokens, C] bf16 row-major, C a multiple of 8.
 #include "ptx.cuh"
 #include "host_util.h"
+#include <cstdlib>
 #include "elementwise.h"
 
 namespace nga {
@@ -634,16 +635,19 @@ __global__ void gate_bwd_kernel(__nv_bfloat16* __restrict__ dn, const __nv_bfloa
 //   dl = gscale * (softmax(z) - onehot) * (1 - tanh^2)          written in place over the logits
 // |z| <= cap = 15, so exp(z) needs no running maximum in fp32.  target == -1 rows are ignored.
 // ------------------------------------------------------------------------------------------------
-// tanh through one ex2 and one rcp (about 1e-6 relative error); the libm tanhf / expf sequences made this
-// memory-sized kernel instruction-bound (two passes x 65536 columns x ~80 instructions per element).
+// The kernel is bound by the special-function unit (16 results per clock per SM): with tanh as ex2 + rcp and the
+// exponential as ex2 it needs six such results per logit over its two passes, which is exactly its measured time
+// (0.76 ms per 8192 x 65536 chunk).  tanh.approx.f32 is one result (relative error 2^-11, a quarter of the rounding of
+// the bf16 logit it is applied to), which brings that to four.
 __device__ __forceinline__ float fast_ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 __device__ __forceinline__ float fast_tanh(float x) {
-  const float e = fast_ex2(x * 2.885390081777927f);      // exp(2x)
-  return 1.f - __fdividef(2.f, e + 1.f);
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ float fast_exp(float x) { return fast_ex2(x * 1.4426950408889634f); }
 
@@ -855,7 +859,12 @@ extern "C" int nga_softcap_ce(void* logits, const long long* targets, float* los
   // (A one-CTA-per-row form that parks the row in shared memory between the passes, so that it is read once, was
   // measured slower: 8.6 against 7.2 ms per d20 step; with one 128 KB CTA per SM its load, math and store phases do not
   // overlap across rows, while eight small CTAs per SM do.)
-  softcap_ce_kernel<<<(unsigned)rows, 256, 0, ST(stream)>>>(BFW(logits), targets, loss_rows, cap,
+  static int pad_kb = -1;             // NGA_CE_SMEM_KB: unused dynamic shared memory per CTA, to lower the resident row count
+  if (pad_kb < 0) {
+    const char* e = getenv("NGA_CE_SMEM_KB");
+    pad_kb = e ? atoi(e) : 0;
+  }
+  softcap_ce_kernel<<<(unsigned)rows, 256, (size_t)pad_kb * 1024, ST(stream)>>>(BFW(logits), targets, loss_rows, cap,
                                                             gscale, ld, V);
   count_launch();
   NGA_CHECK_LAUNCH();
