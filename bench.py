@@ -99,6 +99,9 @@ def main() -> None:
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp8_block", "nvfp4"],
                     help="configurations 3 and 4 only: compute precision of the linear layers (the d20 headline is bf16)")
     ap.add_argument("--per-gpu-batch", type=int, default=0, help="configurations 3 and 4: sequences per GPU per step (0: 16 / 4)")
+    ap.add_argument("--kernel-times", action="store_true",
+                    help="after the timed runs: two more steps under the torch profiler's CUDA activity records, kernel "
+                         "durations summed by kernel to stderr (in-situ shares at the power-capped clock; never a bench value)")
     ap.add_argument("--no-extra", action="store_true", help="skip the kernel metrics appended to the d20 line")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -195,6 +198,8 @@ def main() -> None:
     clocks = sampler.stop()
     if trainer.engine is not None:
         native.check_status()
+    if args.kernel_times and rank == 0:
+        kernel_times(trainer, host_blocks)
 
     times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -234,6 +239,27 @@ def main() -> None:
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
+
+
+def kernel_times(trainer, host_blocks, steps: int = 2) -> None:
+    """Kernel durations of ``steps`` training steps, summed by kernel name, largest first, to stderr."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for i in range(steps):
+            trainer.train_step(host_blocks[i % len(host_blocks)])
+        torch.cuda.synchronize()
+    groups: dict[str, list] = {}
+    for e in prof.key_averages():
+        name = e.key.split("(")[0].split("<")[0].strip()[-64:]
+        g = groups.setdefault(name, [0.0, 0])
+        g[0] += e.self_device_time_total / 1e3 / steps
+        g[1] += e.count // steps
+    total = sum(ms for ms, _ in groups.values())
+    print(f"kernel time per step {total:.1f} ms", file=sys.stderr)
+    for name, (ms, n) in sorted(groups.items(), key=lambda kv: -kv[1][0])[:30]:
+        print(f"{ms:9.2f} ms {n:5d}x  {name}", file=sys.stderr)
 
 
 def mesh_config(args) -> None:
