@@ -271,7 +271,7 @@ extern "C" int nga_gemm_bf16(const void* A, const void* B, void* D, const void* 
   if (rc) return rc;
   GemmParams p;
   p.row_shift = 0;
-  p.group_of_mtile = nullptr; p.group_rows = 0;
+  p.group_of_mtile = nullptr; p.group_rows = 0; p.kb_range = nullptr;
   p.M = M; p.N = N; p.K = K; p.batch = batch;
   p.D = D; p.aux = aux; p.ldd = ldd; p.ldaux = ldaux; p.sD = sD; p.sAux = sAux;
   p.epi = epi; p.out_fp32 = out_fp32; p.aux_fp32 = aux_fp32; p.alpha = alpha; p.beta = beta;

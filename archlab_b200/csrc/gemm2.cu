@@ -244,6 +244,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         split_range(tile, p.splits, num_kb, otile, kb0, kb1);
         tile_coords(otile, num_m, num_n, b, mb, nb);
         if (TP) { mb = tp_remap_mb(tp, mb, num_m); nb = tp_remap_nb(tp, nb, num_n); }
+        if (!tile_has_work(p, b, mb, kb0, kb1)) continue;
         int m0 = mb * 2 * BM + int(rank) * BM;             // this CTA's 128 rows of A
         int n0 = nb * G2_BN + int(rank) * 128;             // this CTA's 128 N-rows of B
         const int grp_off = p.group_of_mtile ? p.group_of_mtile[mb] * p.group_rows : 0;   // rows of B before this tile's group
@@ -295,19 +296,20 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           uint8_t* sB = sA + G2_A_BYTES;
           const uint32_t leader_full = mapa_u32(smem_u32(&full_bar[stage]), 0);
           if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * G2_STAGE_BYTES);
+          const int bl = p.kb_range != nullptr ? 0 : b;    // variable-length reductions share one A / B row range
           if (A_MN) {
 #pragma unroll
             for (int j = 0; j < 2; ++j)
-              tma_load_3d_pair(sA + j * 8192, mapA, leader_full, m0 + j * 64, kb * BK, b);
+              tma_load_3d_pair(sA + j * 8192, mapA, leader_full, m0 + j * 64, kb * BK, bl);
           } else {
-            tma_load_3d_pair(sA, mapA, leader_full, kb * BKE, m0, b);
+            tma_load_3d_pair(sA, mapA, leader_full, kb * BKE, m0, bl);
           }
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < 2; ++j)
-              tma_load_3d_pair(sB + j * 8192, mapBk, leader_full, n0 + j * 64, brow + grp_off, b);
+              tma_load_3d_pair(sB + j * 8192, mapBk, leader_full, n0 + j * 64, brow + grp_off, bl);
           } else {
-            tma_load_3d_pair(sB, mapB, leader_full, kb * BKE, n0 + grp_off, b);
+            tma_load_3d_pair(sB, mapB, leader_full, kb * BKE, n0 + grp_off, bl);
           }
           if (++stage == G2_STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -325,12 +327,17 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int it = 0, tile = seq.at(0); tile < num_tiles && ok; tile = seq.at(++it)) {
+        int otile, kb0, kb1;
+        split_range(tile, p.splits, num_kb, otile, kb0, kb1);
+        if (p.group_of_mtile != nullptr || p.kb_range != nullptr) {
+          int b, mb, nb;
+          tile_coords(otile, num_m, num_n, b, mb, nb);
+          if (!tile_has_work(p, b, mb, kb0, kb1)) continue;
+        }
         ok = mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_word);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + uint32_t(acc * G2_BN);
-        int otile, kb0, kb1;
-        split_range(tile, p.splits, num_kb, otile, kb0, kb1);
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_word);
           if (!ok) break;
@@ -374,6 +381,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       split_range(tile, p.splits, num_kb, otile, kb0, kb1);
       tile_coords(otile, num_m, num_n, b, mb, nb);
       if (TP) { mb = tp_remap_mb(tp, mb, num_m); nb = tp_remap_nb(tp, nb, num_n); }
+      if (!tile_has_work(p, b, mb, kb0, kb1)) continue;
       const int row = mb * 2 * BM + int(rank) * BM + quarter * 32 + lane;
       GemmParams pt = p;
       if (TP && (tp.mode & kTpScatter)) {                   // this tile's rows live on rank `owner`
@@ -651,7 +659,7 @@ extern "C" int nga_gemm2_bf16(const void* A, const void* B, void* D, const void*
   if (epi == kEpiAtomicAdd && !out_fp32) return -8;
   p.status = status;
   p.row_shift = 0;
-  p.group_of_mtile = nullptr; p.group_rows = 0;
+  p.group_of_mtile = nullptr; p.group_rows = 0; p.kb_range = nullptr;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   TpParams tp = {};
   static const TpMaps no_maps = {};
@@ -687,13 +695,41 @@ extern "C" int nga_gemm2_grouped_bf16(const void* A, const void* B, void* D, con
   p.splits = 1;
   p.status = status;
   p.row_shift = 0;
-  p.group_of_mtile = group_of_mtile;
+  p.group_of_mtile = group_of_mtile; p.kb_range = nullptr;
   p.group_rows = b_mn ? K : N;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   TpParams tp = {};
   static const TpMaps no_maps = {};
   if (b_mn) return launch_gemm2<0, 1, 0>(ta, tb, p, st, ta, tp, no_maps);
   return launch_gemm2<0, 0, 0>(ta, tb, p, st, ta, tp, no_maps);
+}
+
+// Grouped weight gradient in one launch: dW[g] ([N_out, K_in] bf16, `groups` of them, contiguous) = dY_g^T X_g, where
+// group g owns the 64-row blocks [kb_range[2g], kb_range[2g + 1]) of dY [rows, N_out] and X [rows, K_in] (device int
+// array; rows are sorted by group and padded to 256 per group, rows of the padding must be zero in dY or X).  Groups
+// without rows are skipped: dW[g] keeps what the caller put there (zeros).
+extern "C" int nga_gemm2_grouped_wgrad_bf16(const void* dY, const void* X, void* dW, const int* kb_range, int groups, int rows,
+                                            int n_out, int k_in, long long ldy, long long ldx, int* status, void* stream) {
+  using namespace nga;
+  if (rows <= 0 || n_out <= 0 || k_in <= 0 || groups <= 0 || kb_range == nullptr) return -1;
+  if ((ldy & 7) || (ldx & 7) || (rows % BK)) return -5;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_3d(&ta, dY, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n_out, rows, 1, ldy * 2, (long long)rows * ldy * 2, 64, 64, true);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tb, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k_in, rows, 1, ldx * 2, (long long)rows * ldx * 2, 64, 64, true);
+  if (rc) return rc;
+  GemmParams p;
+  p.M = n_out; p.N = k_in; p.K = rows; p.batch = groups;
+  p.D = dW; p.aux = nullptr; p.ldd = k_in; p.ldaux = 0; p.sD = (long long)n_out * k_in; p.sAux = 0;
+  p.epi = kEpiScale; p.out_fp32 = 0; p.aux_fp32 = 0; p.alpha = 1.f; p.beta = 0.f;
+  p.splits = 1;
+  p.status = status;
+  p.row_shift = 0;
+  p.group_of_mtile = nullptr; p.group_rows = 0; p.kb_range = kb_range;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  TpParams tp = {};
+  static const TpMaps no_maps = {};
+  return launch_gemm2<1, 1, 0>(ta, tb, p, st, ta, tp, no_maps);
 }
 
 // D[M, N] (bf16 or fp32) = alpha * A[M, K] B[N, K]^T with 8-bit floating-point operands (row-major, K contiguous,
@@ -718,7 +754,7 @@ extern "C" int nga_gemm2_fp8(const void* A, const void* B, void* D, const void* 
   if (epi == kEpiAtomicAdd) return -8;
   p.status = status;
   p.row_shift = 0;
-  p.group_of_mtile = nullptr; p.group_rows = 0;
+  p.group_of_mtile = nullptr; p.group_rows = 0; p.kb_range = nullptr;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   TpParams tp = {};
   static const TpMaps no_maps = {};
@@ -796,7 +832,7 @@ extern "C" int nga_tp_gemm_bf16(const void* A, const void* B, void* D, int M, in
   p.D = D; p.aux = nullptr; p.ldd = ldd; p.ldaux = 0; p.sD = 0; p.sAux = 0;
   p.epi = kEpiScale; p.out_fp32 = 0; p.aux_fp32 = 0; p.alpha = 1.f; p.beta = 0.f; p.splits = 1;
   p.status = status; p.row_shift = 0;
-  p.group_of_mtile = nullptr; p.group_rows = 0;
+  p.group_of_mtile = nullptr; p.group_rows = 0; p.kb_range = nullptr;
   TpMaps tpm = {};
   if (mode == kTpScatter) {
     for (int r = 0; r < world; ++r) {
@@ -868,7 +904,7 @@ extern "C" int nga_tp_gemm_push_bf16(const void* x_local, const void* B, void* D
   p.D = D; p.aux = nullptr; p.ldd = ldd; p.ldaux = 0; p.sD = 0; p.sAux = 0;
   p.epi = kEpiScale; p.out_fp32 = 0; p.aux_fp32 = 0; p.alpha = 1.f; p.beta = 0.f; p.splits = 1;
   p.status = status; p.row_shift = 0;
-  p.group_of_mtile = nullptr; p.group_rows = 0;
+  p.group_of_mtile = nullptr; p.group_rows = 0; p.kb_range = nullptr;
   TpMaps tpm = {};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (b_mn) return launch_gemm2<0, 1, 1>(ta, tb, p, st, ta2, tp, tpm);
@@ -916,7 +952,7 @@ extern "C" int nga_tp_gemm_rs_reduce_bf16(const void* A, const void* B, void* ou
   p.D = nullptr; p.aux = nullptr; p.ldd = N; p.ldaux = 0; p.sD = 0; p.sAux = 0;
   p.epi = kEpiScale; p.out_fp32 = 0; p.aux_fp32 = 0; p.alpha = 1.f; p.beta = 0.f; p.splits = 1;
   p.status = status; p.row_shift = 0;
-  p.group_of_mtile = nullptr; p.group_rows = 0;
+  p.group_of_mtile = nullptr; p.group_rows = 0; p.kb_range = nullptr;
   TpMaps tpm = {};
   for (int r = 0; r < world; ++r) {
     rc = make_tmap_3d(&tpm.d[r], tp.peer_dst[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, (long long)world * rows_per_rank, 1,
@@ -971,7 +1007,7 @@ extern "C" int nga_fsdp_gemm_bf16(const void* A, void* D, int M, int w_rows, int
   p.D = D; p.aux = nullptr; p.ldd = ldd; p.ldaux = 0; p.sD = 0; p.sAux = 0;
   p.epi = kEpiScale; p.out_fp32 = 0; p.aux_fp32 = 0; p.alpha = 1.f; p.beta = 0.f; p.splits = 1;
   p.status = status; p.row_shift = 0;
-  p.group_of_mtile = nullptr; p.group_rows = 0;
+  p.group_of_mtile = nullptr; p.group_rows = 0; p.kb_range = nullptr;
   TpMaps tpm = {};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (transposed) return launch_gemm2<0, 1, 1>(ta, tb, p, st, tb_own, tp, tpm);

@@ -165,6 +165,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
         int b, mb, nb;
         tile_coords(tile, num_m, num_n, b, mb, nb);
+        if (p.group_of_mtile != nullptr && p.group_of_mtile[mb] < 0) continue;      // a tile of the row bound without rows
         const int m0 = mb * 2 * BM + int(rank) * BM;
         const int group = p.group_of_mtile ? p.group_of_mtile[mb] : 0;
         const int n0 = nb * BS_BN + int(rank) * 128 + group * p.group_rows;
@@ -193,6 +194,11 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        if (p.group_of_mtile != nullptr) {
+          int b, mb, nb;
+          tile_coords(tile, num_m, num_n, b, mb, nb);
+          if (p.group_of_mtile[mb] < 0) continue;
+        }
         ok = mbar_wait(tempty_bar, acc_phase ^ 1u, abort_word);      // the epilogue has drained the accumulator
         if (!ok) break;
         tc_fence_after();
@@ -247,6 +253,7 @@ gemm_bs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       int b, mb, nb;
       tile_coords(tile, num_m, num_n, b, mb, nb);
+      if (p.group_of_mtile != nullptr && p.group_of_mtile[mb] < 0) continue;
       const int row = mb * 2 * BM + int(rank) * BM + quarter * 32 + lane;
       AuxPre nxt;
       aux_prefetch(p, nxt, row, nb * BS_BN + chalf * 128, 0, aux_fast);
@@ -427,7 +434,7 @@ static int gemm_bs_common(int kind, const void* A, const void* sfa, const void* 
   p.D = D; p.aux = aux; p.ldd = ldd; p.ldaux = ldaux; p.sD = 0; p.sAux = 0;
   p.epi = epi; p.out_fp32 = out_fp32; p.aux_fp32 = aux_fp32; p.alpha = alpha; p.beta = beta;
   p.splits = 1; p.status = status; p.row_shift = 0;
-  p.group_of_mtile = group_of_mtile; p.group_rows = group_of_mtile ? N : 0;
+  p.group_of_mtile = group_of_mtile; p.group_rows = group_of_mtile ? N : 0; p.kb_range = nullptr;
   p.tma_store = 0;
   BsExtra x = {a_fmt, b_fmt, group_of_mtile ? N / 128 : 0, amax_a, amax_b};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

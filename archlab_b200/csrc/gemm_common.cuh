@@ -24,8 +24,13 @@ struct GemmParams {
   long long row_shift;           // added to the row index when addressing D (tensor-parallel staging slots)
   // grouped form (expert GEMMs in one launch): rows are sorted by group and every 256-row tile belongs to one
   // group; `group_of_mtile[mb]` names it and B is the stack of the groups' matrices, `group_rows` rows each
+  // A negative entry marks a tile of the (fixed, upper-bound) row range that holds no rows: every role skips it.
   const int* group_of_mtile;
   int group_rows;
+  // variable-length reductions (grouped weight gradients): batch element b reduces over the 64-row blocks
+  // [kb_range[2b], kb_range[2b + 1]) of the shared A / B row range; an empty range skips the tile (its output keeps
+  // what the caller put there)
+  const int* kb_range;
   int tma_store;                 // pair kernel, plain bf16 output: tiles leave through swizzled staging + TMA stores
 };
 
@@ -132,6 +137,18 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
 }
 
 // Work item -> (output tile index, k-block range) under split-K.
+// Grouped forms: whether this tile has anything to do, and (variable-length reductions) its range of 64-row blocks.
+// Every role of the kernel asks the same question of the same device tables, so they skip the same tiles.
+__device__ __forceinline__ bool tile_has_work(const GemmParams& p, int b, int mb, int& kb0, int& kb1) {
+  if (p.group_of_mtile != nullptr && p.group_of_mtile[mb] < 0) return false;
+  if (p.kb_range != nullptr) {
+    kb0 = p.kb_range[2 * b];
+    kb1 = p.kb_range[2 * b + 1];
+    return kb1 > kb0;
+  }
+  return true;
+}
+
 __device__ __forceinline__ void split_range(int item, int splits, int num_kb, int& tile, int& kb0, int& kb1) {
   const int sidx = item % splits;
   tile = item / splits;

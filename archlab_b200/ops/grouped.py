@@ -20,6 +20,7 @@ from . import native
 TILE = 256
 _vp, _i, _ll = C.c_void_p, C.c_int, C.c_longlong
 native.register_signature("nga_gemm2_grouped_bf16", [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp])
+native.register_signature("nga_gemm2_grouped_wgrad_bf16", [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _ll, _ll, _vp, _vp])
 
 
 def padded_sizes(counts: torch.Tensor) -> torch.Tensor:
@@ -86,3 +87,67 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, r
 def tile_groups(padded: list[int], device) -> torch.Tensor:
     reps = torch.tensor([p // TILE for p in padded], device=device)
     return torch.repeat_interleave(torch.arange(len(padded), device=device, dtype=torch.int32), reps).contiguous()
+
+
+# ------------------------------------------------------------------------------------------------
+# Device-planned form: nothing about the segment sizes is known on the host
+# ------------------------------------------------------------------------------------------------
+def device_plan(padded: torch.Tensor, bound_rows: int):
+    """From the padded segment sizes (device int tensor, multiples of 256) and a fixed row bound: the group of every
+    256-row tile of the bound (-1 past the used rows) and the [first, last) 64-row block of every group.  All on the
+    device; ``bound_rows`` is a host constant (a multiple of 256) that the caller guarantees (and checks) to suffice."""
+    if bound_rows % TILE:
+        raise ValueError("the row bound must be a multiple of 256")
+    ends = padded.cumsum(0)
+    starts = ends - padded
+    tile_first = torch.arange(bound_rows // TILE, device=padded.device, dtype=ends.dtype) * TILE
+    group = torch.searchsorted(ends, tile_first, right=True)
+    tile_group = torch.where(tile_first < ends[-1], group, torch.full_like(group, -1)).to(torch.int32).contiguous()
+    kb_range = torch.stack([starts // 64, ends // 64], 1).to(torch.int32).contiguous()
+    return tile_group, kb_range
+
+
+class _GroupedLinearDevice(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, tile_group, kb_range, fp8=False, out=None):
+        E, N, K = w.shape
+        ctx.save_for_backward(x, w, tile_group, kb_range)
+        if fp8:
+            from . import blockscaled as bs
+
+            y = bs.grouped_gemm(bs.quantize_fp8(x, 128), bs.quantize_fp8(w.view(E * N, K), -128), tile_group, E, N)
+            return y if out is None else out.copy_(y)
+        y = torch.empty(x.size(0), N, dtype=torch.bfloat16, device=x.device) if out is None else out
+        rc = native.lib().nga_gemm2_grouped_bf16(x.data_ptr(), w.data_ptr(), y.data_ptr(), tile_group.data_ptr(), E, x.size(0), N, K,
+                                                 x.stride(0), K, y.stride(0), 0, native.status_word(x.device).data_ptr(), native.stream_ptr())
+        native.check(rc, "nga_gemm2_grouped_bf16")
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, tile_group, kb_range = ctx.saved_tensors
+        E, N, K = w.shape
+        dy = dy.contiguous()
+        dx = torch.zeros(x.size(0), K, dtype=torch.bfloat16, device=x.device)       # skipped tiles stay zero
+        rc = native.lib().nga_gemm2_grouped_bf16(dy.data_ptr(), w.data_ptr(), dx.data_ptr(), tile_group.data_ptr(), E, dy.size(0), K, N,
+                                                 dy.stride(0), K, dx.stride(0), 1, native.status_word(x.device).data_ptr(), native.stream_ptr())
+        native.check(rc, "nga_gemm2_grouped_bf16")
+        dw = torch.zeros_like(w)                                                     # groups without rows are skipped
+        rc = native.lib().nga_gemm2_grouped_wgrad_bf16(dy.data_ptr(), x.data_ptr(), dw.data_ptr(), kb_range.data_ptr(), E, dy.size(0), N, K,
+                                                       dy.stride(0), x.stride(0), native.status_word(x.device).data_ptr(), native.stream_ptr())
+        native.check(rc, "nga_gemm2_grouped_wgrad_bf16")
+        return dx, dw, None, None, None, None
+
+
+def grouped_linear_device(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, kb_range: torch.Tensor, *, fp8: bool = False,
+                          out: torch.Tensor | None = None) -> torch.Tensor:
+    """``grouped_linear`` with the segment layout on the device (``device_plan``): ``x`` has the fixed bound of rows, tiles
+    past the used rows are skipped by the kernels (their output rows are unspecified in the forward and zero in the
+    data gradient) and the weight gradient is one launch whose reduction ranges come from ``kb_range``.  Rows of the
+    padding inside a segment must be finite in ``x`` and zero in the incoming gradient.  bf16 CUDA only; N and K
+    multiples of 256 resp. 64."""
+    E, N, K = w.shape
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and native.available() and K % 64 == 0 and N % 64 == 0 and x.size(0) % TILE == 0):
+        raise ValueError("grouped_linear_device needs bf16 CUDA operands, K and N multiples of 64 and a 256-row bound")
+    return _GroupedLinearDevice.apply(x.contiguous(), w.to(x.dtype).contiguous(), tile_group, kb_range,
+                                      bool(fp8 and N % 128 == 0 and K % 128 == 0), out)

@@ -46,7 +46,18 @@ class EPBuffers:
         self.capacity, self.dim = capacity, dim
         mk = lambda: symm_empty((capacity * dim,), torch.bfloat16, device, self.group)
         self.recv_x, self.y, self.g_y, self.g_x = mk(), mk(), mk(), mk()
+        for sym in (self.recv_x, self.y, self.g_y, self.g_x):
+            sym.tensor.zero_()             # rows of segment padding are read by the grouped GEMMs: they must be finite
         self.barrier = PeerBarrier(device, self.group)
+        # rows past the bound that a layer's grouped GEMMs run over (device flag, read once per step by the trainer)
+        self.overflow = torch.zeros((), dtype=torch.int64, device=device)
+
+    def check_overflow(self) -> None:
+        """One device -> host read: raises when some layer received more rows than its row bound since the last check."""
+        over = int(self.overflow)
+        if over:
+            self.overflow.zero_()
+            raise RuntimeError(f"expert receive bound exceeded by {over} rows: raise the capacity factor")
 
     def view(self, sym, n):
         return sym.tensor[: n * self.dim].view(n, self.dim)
@@ -110,6 +121,7 @@ class _Combine(torch.autograd.Function):
         T, k, buf = ctx.meta
         n = y_local.size(0)
         gout = gout.contiguous()
+        buf.view(buf.g_y, n).zero_()        # rows of segment padding must be zero for the grouped weight gradient
         buf.barrier()
         buf.view(buf.y, n).copy_(y_local)                        # expert rows again, for d(weight)
         buf.barrier()
@@ -126,9 +138,12 @@ class FusedExpertParallelMoE(nn.Module):
     """Same parameters and semantics as ``models.moe.ExpertParallelMoE``; bf16 CUDA only."""
 
     def __init__(self, dim, inter, n_experts, top_k, buffers: EPBuffers, *, score="sqrt_softplus", route_scale=1.0,
-                 swiglu_limit=None, n_shared=1, fp8: bool = False):
+                 swiglu_limit=None, n_shared=1, fp8: bool = False, capacity_factor: float | None = None):
         super().__init__()
         self.buf = buffers
+        # capacity_factor f: the grouped GEMMs run over a fixed bound of f x (tokens x top_k) + padding rows whose layout
+        # lives on the device, so the layer never synchronises with the host; None: exact sizes read back per call
+        self.capacity_factor = capacity_factor
         self.fp8 = fp8                      # forward products of the expert and shared projections in block-scaled FP8
         self.size, self.rank = buffers.world, buffers.rank
         if n_experts % self.size:
@@ -148,7 +163,7 @@ class FusedExpertParallelMoE(nn.Module):
         T, k = idx.shape
         E, El, W = self.n_experts, self.local_experts, self.size
         flat = idx.flatten()
-        counts = torch.bincount(flat, minlength=E)
+        counts = torch.zeros(E, dtype=torch.int64, device=idx.device).scatter_add_(0, flat, torch.ones_like(flat))   # bincount would sync
         allc = torch.empty(W, E, dtype=counts.dtype, device=idx.device)
         dist.all_gather_into_tensor(allc, counts, group=self.buf.group)
         per_e = allc.sum(0)                                                     # rows of expert e on its owner
@@ -173,6 +188,8 @@ class FusedExpertParallelMoE(nn.Module):
         dst_rank, dst_row, mine, counts = self.plan(idx)
         load = counts.float()
         self._cumulative_expert_load = load if self._cumulative_expert_load is None else self._cumulative_expert_load + load
+        if self.capacity_factor is not None and inter % 128 == 0 and self.dim % 256 == 0:
+            return self._forward_device_planned(x2, w, idx, dst_rank, dst_row, mine, shape)
         seg, seg_pad = mine.tolist()                                              # host needs the GEMM extents
         n_recv = sum(seg_pad)
         if n_recv > self.buf.capacity:
@@ -186,6 +203,25 @@ class FusedExpertParallelMoE(nn.Module):
         # ascending expert id per token: deterministic summation order
         eo = idx.argsort(dim=-1)
         slots = (torch.arange(T, device=x.device) * k).unsqueeze(1) + eo
+        rank_s, row_s, w_s = dst_rank[slots].contiguous(), dst_row[slots].contiguous(), w.gather(1, eo).float().contiguous()
+        out = _Combine.apply(y_local, w_s, rank_s, row_s, T, k, self.buf)
+        if self.shared is not None:
+            out = out + self.shared(x2).to(out.dtype)
+        return out.reshape(shape)
+
+    def _forward_device_planned(self, x2, w, idx, dst_rank, dst_row, mine, shape):
+        """No host synchronisation: a fixed row bound, tile -> expert and reduction-range tables on the device."""
+        T, k = x2.size(0), self.top_k
+        bound = int(self.capacity_factor * T * k) + grouped.TILE * self.local_experts
+        bound = min((bound + grouped.TILE - 1) // grouped.TILE * grouped.TILE, self.buf.capacity // grouped.TILE * grouped.TILE)
+        tiles, kb_range = grouped.device_plan(mine[1], bound)
+        self.buf.overflow += (mine[1].sum() - bound).clamp_min(0)
+        src_row = torch.arange(T, device=x2.device, dtype=torch.int32).repeat_interleave(k)
+        recv = _Dispatch.apply(x2, src_row, dst_rank, dst_row, bound, k, self.buf)
+        h = grouped.grouped_linear_device(recv, self.experts.gate_up, tiles, kb_range, fp8=self.fp8)
+        y_local = grouped.grouped_linear_device(block_ops.swiglu(h, self.limit), self.experts.down, tiles, kb_range, fp8=self.fp8)
+        eo = idx.argsort(dim=-1)
+        slots = (torch.arange(T, device=x2.device) * k).unsqueeze(1) + eo
         rank_s, row_s, w_s = dst_rank[slots].contiguous(), dst_row[slots].contiguous(), w.gather(1, eo).float().contiguous()
         out = _Combine.apply(y_local, w_s, rank_s, row_s, T, k, self.buf)
         if self.shared is not None:

@@ -32,7 +32,7 @@ def _worker(rank, world, port, out_dir):
     ref = ref.bfloat16()
     ref.e_score_correction_bias = ref.e_score_correction_bias.float()
     buf = ep.EPBuffers(capacity=T * k * world, dim=dim, device=dev)
-    fused = ep.FusedExpertParallelMoE(dim, inter, E, k, buf, swiglu_limit=7.0, n_shared=1).to(dev).bfloat16()
+    fused = ep.FusedExpertParallelMoE(dim, inter, E, k, buf, swiglu_limit=7.0, n_shared=1, capacity_factor=2.0).to(dev).bfloat16()
     fused.e_score_correction_bias = fused.e_score_correction_bias.float()
     fused.load_state_dict(ref.state_dict())
     res = {}
@@ -52,6 +52,43 @@ def _worker(rank, world, port, out_dir):
         res[f"drouter{it}"] = rel(ref.router.grad, fused.router.grad)
         res[f"ddown{it}"] = rel(ref.experts.down.grad, fused.experts.down.grad)
         res[f"dgate_up{it}"] = rel(ref.experts.gate_up.grad, fused.experts.gate_up.grad)
+    # the device-planned layer (fixed row bound, tile and reduction tables on the device) never waits for the GPU
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")
+    try:
+        xs = x.clone().requires_grad_(True)
+        ys = fused(xs)
+        ys.backward(go)
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    res["sync_free_out"] = ((ys.float() - yb.float()).abs().max()).item()          # same inputs as the last iteration
+    buf.check_overflow()
+    # the host-planned form (exact sizes read back) gives the same numbers
+    exact = ep.FusedExpertParallelMoE(dim, inter, E, k, buf, swiglu_limit=7.0, n_shared=1, capacity_factor=None).to(dev).bfloat16()
+    exact.e_score_correction_bias = exact.e_score_correction_bias.float()
+    exact.load_state_dict(fused.state_dict())
+    xe = x.clone().requires_grad_(True)
+    ye = exact(xe)
+    ye.backward(go)
+    res["host_planned_out"] = ((ye.float() - yb.float()).abs().max()).item()
+    res["host_planned_ddown"] = ((exact.experts.down.grad.float() - fused.experts.down.grad.float()).abs().max()).item()
+    res["host_planned_dgate_up"] = ((exact.experts.gate_up.grad.float() - fused.experts.gate_up.grad.float()).abs().max()).item()
+    # a bound that is too small is reported, not silently computed
+    local = E // world
+    shrink = -((local - 1) * 256) / (T * k)                              # leaves a bound of exactly one 256-row tile
+    tight = ep.FusedExpertParallelMoE(dim, inter, E, k, buf, swiglu_limit=7.0, n_shared=1, capacity_factor=shrink).to(dev).bfloat16()
+    tight.e_score_correction_bias = tight.e_score_correction_bias.float()
+    tight.load_state_dict(fused.state_dict())
+    with torch.no_grad():
+        tight.router.zero_()
+        tight.e_score_correction_bias[: k] += 10.0                       # every token to the first k experts: rank 0 overflows
+        tight(x)
+    raised = False
+    try:
+        buf.check_overflow()
+    except RuntimeError:
+        raised = True
+    res["overflow_reported"] = 0.0 if (raised or rank != 0) else 1.0
     torch.cuda.synchronize()
     native.check_status()
     torch.save(res, os.path.join(out_dir, f"ep_rank{rank}.pt"))
