@@ -51,6 +51,9 @@ class V41Config:
     hc_sinkhorn_iters: int = 20
     fp8: bool = False
     fp8_block: int = 128
+    # expert-parallel layers over peer memory: grouped GEMMs run over a fixed bound of factor x tokens x top-k rows whose
+    # layout lives on the device (no host synchronisation per layer); None reads the exact sizes back
+    expert_capacity_factor: float | None = 2.0
     rms_eps: float = 1e-6
 
     @classmethod
@@ -212,7 +215,8 @@ class V41Block(nn.Module):
 
             self.ffn = FusedExpertParallelMoE(c.hidden_size, c.moe_inter, c.n_routed_experts, c.experts_top_k, ep_buffers,
                                               score=c.router_score, route_scale=c.route_scale, swiglu_limit=c.swiglu_limit,
-                                              n_shared=c.n_shared_experts, fp8=c.fp8 and c.fp8_block == 128)
+                                              n_shared=c.n_shared_experts, fp8=c.fp8 and c.fp8_block == 128,
+                                              capacity_factor=c.expert_capacity_factor)
         elif ep_group is not None:
             self.ffn = moe.ExpertParallelMoE(c.hidden_size, c.moe_inter, c.n_routed_experts, c.experts_top_k, ep_group,
                                              score=c.router_score, route_scale=c.route_scale, swiglu_limit=c.swiglu_limit,

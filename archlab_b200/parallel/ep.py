@@ -15,6 +15,7 @@ baseline and the oracle.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 import torch.distributed as dist
@@ -143,7 +144,7 @@ class FusedExpertParallelMoE(nn.Module):
         self.buf = buffers
         # capacity_factor f: the grouped GEMMs run over a fixed bound of f x (tokens x top_k) + padding rows whose layout
         # lives on the device, so the layer never synchronises with the host; None: exact sizes read back per call
-        self.capacity_factor = capacity_factor
+        self.capacity_factor = None if os.environ.get("NGA_EP_HOST_PLAN") == "1" else capacity_factor
         self.fp8 = fp8                      # forward products of the expert and shared projections in block-scaled FP8
         self.size, self.rank = buffers.world, buffers.rank
         if n_experts % self.size:
@@ -188,7 +189,7 @@ class FusedExpertParallelMoE(nn.Module):
         dst_rank, dst_row, mine, counts = self.plan(idx)
         load = counts.float()
         self._cumulative_expert_load = load if self._cumulative_expert_load is None else self._cumulative_expert_load + load
-        if self.capacity_factor is not None and inter % 128 == 0 and self.dim % 256 == 0:
+        if self.capacity_factor is not None and self.experts.inter % 128 == 0 and self.dim % 256 == 0:
             return self._forward_device_planned(x2, w, idx, dst_rank, dst_row, mine, shape)
         seg, seg_pad = mine.tolist()                                              # host needs the GEMM extents
         n_recv = sum(seg_pad)

@@ -221,6 +221,7 @@ class _Job:
                 # come close); at 2 bytes x hidden per row the four buffers stay in the low GB range
                 slots = a.micro_batch * a.seq_len * cfg.experts_top_k
                 ep_buffers = EPBuffers(mesh.dp * slots, cfg.hidden_size, device, ep_group)
+            self.ep_buffers = ep_buffers
             self.model = V41LM(cfg, ep_group, ep_buffers).to(device)
             self.model.init_weights()
             if ep_group is not None:                          # shared weights agree; every rank keeps its own experts
@@ -609,6 +610,8 @@ def train(a, *, on_step=None) -> list[float]:
         else:
             dt = time.perf_counter() - t0
         losses.append(float(loss))
+        if getattr(job, "ep_buffers", None) is not None:
+            job.ep_buffers.check_overflow()                      # a layer received more rows than its bound: fail loudly
         guard.check(step + 1, losses[-1], gnorm)
         beat.beat(step=step + 1, loss=losses[-1])
         if log is not None:

@@ -55,6 +55,7 @@ def _worker(rank, world, port, out_dir):
     # the device-planned layer (fixed row bound, tile and reduction tables on the device) never waits for the GPU
     torch.cuda.synchronize()
     torch.cuda.set_sync_debug_mode("error")
+    fused.zero_grad()
     try:
         xs = x.clone().requires_grad_(True)
         ys = fused(xs)
