@@ -206,7 +206,7 @@ def chunked_kl_step(teacher_hidden_fn, student_hidden_fn, teacher_head, student_
         kl = _kl_rows(tl, sl) if direction == "forward" else _kl_rows(sl, tl)
         part = kl.sum() * (scale / n)
         part.backward()                                           # head parameters and `leaf.grad` accumulate
-        total += float(kl.sum())
+        total += float(kl.detach().sum())
     flat_s.backward(leaf.grad)
     return total / n
 
