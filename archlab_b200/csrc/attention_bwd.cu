@@ -37,6 +37,7 @@ struct AttnBwdParams {
   int* status;
   long long* prof;       // optional phase cycle counters written by CTA (0,0,0)
   int debug_skip_dq;     // measurement aid: leave the dQ reduction out
+  int pt_tmem;           // 1: P^T and dS^T reach the dV / dK products as TMEM A operands instead of shared tiles
   const uint32_t* selT;  // optional key-major selection bits [B, T(key), T/32] (bit q of row k)
 };
 
@@ -169,6 +170,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
   const uint32_t t_ST = tmem_base;          // 64 cols
   const uint32_t t_DPT = tmem_base + 64;    // 64 cols
   const uint32_t t_DQT = tmem_base + 128;   // 64 cols
+  const uint32_t t_PT = tmem_base + 192;    // 32 cols: P^T as packed bf16 pairs (TMEM A operand of dV)
+  const uint32_t t_DS = tmem_base + 224;    // 32 cols: dS^T as packed bf16 pairs (TMEM A operand of dK)
   const uint32_t t_DV = tmem_base + 256;    // 128 cols
   const uint32_t t_DK = tmem_base + 384;    // 128 cols
 
@@ -247,13 +250,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
         for (int k = 0; k < 4; ++k) {   // contraction over the 64 queries
           // A: P^T / dS^T, K-major (q contiguous), one 64-wide block.  B: dO / Q, MN-major:
           // rows are queries, d blocks 8 KB apart, 16 queries = 2048 B.
-          umma_bf16_ss(t_DV, umma_smem_desc(sPT + k * 32, 16, 1024),
-                       umma_smem_desc(sDO + k * 2048, 8192, 1024), id_dv, (it | k) != 0 ? 1u : 0u);
+          if (p.pt_tmem)
+            umma_bf16_ts(t_DV, t_PT + uint32_t(k * 8), umma_smem_desc(sDO + k * 2048, 8192, 1024), id_dv, (it | k) != 0 ? 1u : 0u);
+          else
+            umma_bf16_ss(t_DV, umma_smem_desc(sPT + k * 32, 16, 1024),
+                         umma_smem_desc(sDO + k * 2048, 8192, 1024), id_dv, (it | k) != 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          umma_bf16_ss(t_DK, umma_smem_desc(sDST + k * 32, 16, 1024),
-                       umma_smem_desc(sQ + k * 2048, 8192, 1024), id_dv, (it | k) != 0 ? 1u : 0u);
+          if (p.pt_tmem)
+            umma_bf16_ts(t_DK, t_DS + uint32_t(k * 8), umma_smem_desc(sQ + k * 2048, 8192, 1024), id_dv, (it | k) != 0 ? 1u : 0u);
+          else
+            umma_bf16_ss(t_DK, umma_smem_desc(sDST + k * 32, 16, 1024),
+                         umma_smem_desc(sQ + k * 2048, 8192, 1024), id_dv, (it | k) != 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {   // contraction over the 128 keys
@@ -385,20 +394,39 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box {64, 12
           pr[i] = e;
           ds[i] = e * (__uint_as_float(dv[i]) - del_b[i]) * p.scale;
         }
+        if (p.pt_tmem) {
+          // P^T and dS^T: 32 queries = 16 columns of packed pairs each, this warp's half of the 32-column operands
+          uint32_t pk[16], dk[16];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int chunk = (chalf * 4 + g) ^ (r & 7);
-          uint4 u, w;
-          u.x = pack_bf16(pr[8 * g + 0], pr[8 * g + 1]);
-          u.y = pack_bf16(pr[8 * g + 2], pr[8 * g + 3]);
-          u.z = pack_bf16(pr[8 * g + 4], pr[8 * g + 5]);
-          u.w = pack_bf16(pr[8 * g + 6], pr[8 * g + 7]);
-          w.x = pack_bf16(ds[8 * g + 0], ds[8 * g + 1]);
-          w.y = pack_bf16(ds[8 * g + 2], ds[8 * g + 3]);
-          w.z = pack_bf16(ds[8 * g + 4], ds[8 * g + 5]);
-          w.w = pack_bf16(ds[8 * g + 6], ds[8 * g + 7]);
-          *reinterpret_cast<uint4*>(rowPT + chunk * 16) = u;
-          *reinterpret_cast<uint4*>(rowDST + chunk * 16) = w;
+          for (int g = 0; g < 16; ++g) {
+            pk[g] = pack_bf16(pr[2 * g], pr[2 * g + 1]);
+            dk[g] = pack_bf16(ds[2 * g], ds[2 * g + 1]);
+          }
+          tmem_st_32x16(t_PT + lane_off + uint32_t(chalf * 16), pk);
+          tmem_st_32x16(t_DS + lane_off + uint32_t(chalf * 16), dk);
+          // dS^T is also the shared B operand of dQ^T = K^T dS^T
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int chunk = (chalf * 4 + g) ^ (r & 7);
+            *reinterpret_cast<uint4*>(rowDST + chunk * 16) = make_uint4(dk[4 * g], dk[4 * g + 1], dk[4 * g + 2], dk[4 * g + 3]);
+          }
+          tmem_st_wait();
+        } else {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int chunk = (chalf * 4 + g) ^ (r & 7);
+            uint4 u, w;
+            u.x = pack_bf16(pr[8 * g + 0], pr[8 * g + 1]);
+            u.y = pack_bf16(pr[8 * g + 2], pr[8 * g + 3]);
+            u.z = pack_bf16(pr[8 * g + 4], pr[8 * g + 5]);
+            u.w = pack_bf16(pr[8 * g + 6], pr[8 * g + 7]);
+            w.x = pack_bf16(ds[8 * g + 0], ds[8 * g + 1]);
+            w.y = pack_bf16(ds[8 * g + 2], ds[8 * g + 3]);
+            w.z = pack_bf16(ds[8 * g + 4], ds[8 * g + 5]);
+            w.w = pack_bf16(ds[8 * g + 6], ds[8 * g + 7]);
+            *reinterpret_cast<uint4*>(rowPT + chunk * 16) = u;
+            *reinterpret_cast<uint4*>(rowDST + chunk * 16) = w;
+          }
         }
       }
       NGA_PROFB(2);
@@ -510,6 +538,10 @@ extern "C" int nga_attn_bwd(const void* qkv, const void* out, const void* dout, 
   p.status = status;
   p.prof = g_attn_bwd_prof;
   p.debug_skip_dq = getenv("NGA_ATTN_BWD_SKIP_DQ") != nullptr;
+  {
+    const char* e = getenv("NGA_ATTN_BWD_PT_TMEM");          // 0: P^T / dS^T as shared A operands of the dV / dK products
+    p.pt_tmem = (e != nullptr && e[0] == '0') ? 0 : 1;       // TMEM operands: 1.105 against 1.125 ms (B16 T2048 H10)
+  }
   p.selT = g_attn_bwd_selT;
   g_attn_bwd_selT = nullptr;
   if (p.selT != nullptr && (T % 64)) return -7;

@@ -51,9 +51,10 @@ class V41Config:
     hc_sinkhorn_iters: int = 20
     fp8: bool = False
     fp8_block: int = 128
-    # expert-parallel layers over peer memory: grouped GEMMs run over a fixed bound of factor x tokens x top-k rows whose
-    # layout lives on the device (no host synchronisation per layer); None reads the exact sizes back
-    expert_capacity_factor: float | None = 2.0
+    # expert-parallel layers over peer memory: grouped GEMMs run over a fixed bound of rows whose layout lives on the
+    # device (no host synchronisation per layer): a factor x tokens x top-k, or "auto" (1.5 x the largest row count of the
+    # previous step, the worst case for the first step); None reads the exact sizes back per layer
+    expert_capacity_factor: float | str | None = "auto"
     rms_eps: float = 1e-6
 
     @classmethod

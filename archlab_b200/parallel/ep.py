@@ -50,14 +50,28 @@ class EPBuffers:
         for sym in (self.recv_x, self.y, self.g_y, self.g_x):
             sym.tensor.zero_()             # rows of segment padding are read by the grouped GEMMs: they must be finite
         self.barrier = PeerBarrier(device, self.group)
-        # rows past the bound that a layer's grouped GEMMs run over (device flag, read once per step by the trainer)
-        self.overflow = torch.zeros((), dtype=torch.int64, device=device)
+        # [rows past the bound that a layer's grouped GEMMs run over, most padded rows any layer received]: device
+        # counters, read once per step by the trainer
+        self.counters = torch.zeros(2, dtype=torch.int64, device=device)
+        self.adaptive_bound: int | None = None      # "auto" capacity: None = worst case until the first step was seen
 
-    def check_overflow(self) -> None:
-        """One device -> host read: raises when some layer received more rows than its row bound since the last check."""
-        over = int(self.overflow)
+    @property
+    def overflow(self):
+        return self.counters[0]
+
+    def note_rows(self, padded_rows: torch.Tensor, bound: int) -> None:
+        """Device-side bookkeeping of one layer call (no synchronisation)."""
+        self.counters[0] += (padded_rows - bound).clamp_min(0)
+        self.counters[1] = torch.maximum(self.counters[1], padded_rows)
+
+    def check_overflow(self, margin: float = 1.5) -> None:
+        """One device -> host read per step: raises when some layer received more rows than its bound since the last
+        check, and moves the adaptive bound to ``margin`` x the largest row count seen in the step."""
+        over, peak = self.counters.tolist()
+        self.counters.zero_()
+        if peak:
+            self.adaptive_bound = min(self.capacity // 256 * 256, (int(margin * peak) + 255) // 256 * 256)
         if over:
-            self.overflow.zero_()
             raise RuntimeError(f"expert receive bound exceeded by {over} rows: raise the capacity factor")
 
     def view(self, sym, n):
@@ -139,11 +153,13 @@ class FusedExpertParallelMoE(nn.Module):
     """Same parameters and semantics as ``models.moe.ExpertParallelMoE``; bf16 CUDA only."""
 
     def __init__(self, dim, inter, n_experts, top_k, buffers: EPBuffers, *, score="sqrt_softplus", route_scale=1.0,
-                 swiglu_limit=None, n_shared=1, fp8: bool = False, capacity_factor: float | None = None):
+                 swiglu_limit=None, n_shared=1, fp8: bool = False, capacity_factor: float | str | None = None):
         super().__init__()
         self.buf = buffers
         # capacity_factor f: the grouped GEMMs run over a fixed bound of f x (tokens x top_k) + padding rows whose layout
-        # lives on the device, so the layer never synchronises with the host; None: exact sizes read back per call
+        # lives on the device, so the layer never synchronises with the host; "auto": the bound follows the largest row
+        # count of the previous step (x 1.5; the worst case before the first step was seen); None: exact sizes read
+        # back per call
         self.capacity_factor = None if os.environ.get("NGA_EP_HOST_PLAN") == "1" else capacity_factor
         self.fp8 = fp8                      # forward products of the expert and shared projections in block-scaled FP8
         self.size, self.rank = buffers.world, buffers.rank
@@ -213,10 +229,14 @@ class FusedExpertParallelMoE(nn.Module):
     def _forward_device_planned(self, x2, w, idx, dst_rank, dst_row, mine, shape):
         """No host synchronisation: a fixed row bound, tile -> expert and reduction-range tables on the device."""
         T, k = x2.size(0), self.top_k
-        bound = int(self.capacity_factor * T * k) + grouped.TILE * self.local_experts
-        bound = min((bound + grouped.TILE - 1) // grouped.TILE * grouped.TILE, self.buf.capacity // grouped.TILE * grouped.TILE)
+        limit = self.buf.capacity // grouped.TILE * grouped.TILE
+        if self.capacity_factor == "auto":
+            bound = self.buf.adaptive_bound or limit
+        else:
+            bound = int(self.capacity_factor * T * k) + grouped.TILE * self.local_experts
+        bound = min((bound + grouped.TILE - 1) // grouped.TILE * grouped.TILE, limit)
         tiles, kb_range = grouped.device_plan(mine[1], bound)
-        self.buf.overflow += (mine[1].sum() - bound).clamp_min(0)
+        self.buf.note_rows(mine[1].sum(), bound)
         src_row = torch.arange(T, device=x2.device, dtype=torch.int32).repeat_interleave(k)
         recv = _Dispatch.apply(x2, src_row, dst_rank, dst_row, bound, k, self.buf)
         h = grouped.grouped_linear_device(recv, self.experts.gate_up, tiles, kb_range, fp8=self.fp8)

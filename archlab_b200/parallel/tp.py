@@ -38,7 +38,7 @@ class TPGroup:
     """Symmetric buffers and barriers of one tensor-parallel group for a fixed problem geometry:
     ``rows`` sequence rows per rank, activations up to ``max_k`` wide, outputs up to ``max_n`` wide."""
 
-    def __init__(self, rows: int, max_k: int, max_n: int, device, group=None, copy_clusters: int = 12, push: bool = True):
+    def __init__(self, rows: int, max_k: int, max_n: int, device, group=None, copy_clusters: int = 12, push: bool | None = None):
         """``push``: owner-push all-gather and in-kernel reduce-scatter (one launch per op, no barrier kernels); False
         selects the pull form (copy clusters, barrier + separate slot reduction), kept for comparison."""
         from .symm import PeerBarrier, symm_empty, symm_zeros
@@ -57,7 +57,9 @@ class TPGroup:
         self.flags = torch.zeros(self.world * rows // 128, dtype=torch.int32, device=device)
         self.epoch = 0
         self.barrier = PeerBarrier(device, self.group)
-        self.push = push
+        # owner-push / in-epilogue reduction measured faster than the copy-cluster forms at two ranks (0.13 / 0.147 against
+        # 0.154 / 0.157 ms) and slower at four (0.272 / 0.274 against 0.261 / 0.244 ms: three peers' pushes occupy every CTA)
+        self.push = push = (self.world == 2) if push is None else push
         if push:
             # both directions alternate between two buffers from call to call: a rank can be at most one call ahead of a
             # peer (finishing a call needs every peer's data of that call), so the buffer of call k is free at call k + 2
