@@ -64,15 +64,21 @@ class EPBuffers:
         self.counters[0] += (padded_rows - bound).clamp_min(0)
         self.counters[1] = torch.maximum(self.counters[1], padded_rows)
 
-    def check_overflow(self, margin: float = 1.5) -> None:
-        """One device -> host read per step: raises when some layer received more rows than its bound since the last
-        check, and moves the adaptive bound to ``margin`` x the largest row count seen in the step."""
-        over, peak = self.counters.tolist()
+    def check_overflow(self, margin: float = 1.5) -> dict:
+        """Once per step (a small collective and one device -> host read): how many rows arrived past a bound since the
+        last call (their tokens' expert contributions were dropped, as in capacity-factor routing) and the largest row
+        count any layer of any rank saw; the adaptive bound moves to ``margin`` x that, identically on every rank."""
+        if self.world > 1:
+            both = self.counters.clone()
+            dist.all_reduce(both[:1], group=self.group)
+            dist.all_reduce(both[1:], op=dist.ReduceOp.MAX, group=self.group)
+        else:
+            both = self.counters
+        over, peak = both.tolist()
         self.counters.zero_()
         if peak:
             self.adaptive_bound = min(self.capacity // 256 * 256, (int(margin * peak) + 255) // 256 * 256)
-        if over:
-            raise RuntimeError(f"expert receive bound exceeded by {over} rows: raise the capacity factor")
+        return {"dropped_rows": int(over), "peak_rows": int(peak), "bound": self.adaptive_bound}
 
     def view(self, sym, n):
         return sym.tensor[: n * self.dim].view(n, self.dim)
@@ -101,8 +107,8 @@ def pull_combine(sym, buf: EPBuffers, rank, row, weight, T, k, gout=None, want_d
 
 class _Dispatch(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, src_row, dst_rank, dst_row, n_recv, k, buf):
-        ctx.meta = (dst_rank, dst_row, x.size(0), k, buf, n_recv)
+    def forward(ctx, x, src_row, dst_rank, dst_row, n_recv, k, buf, keep=None):
+        ctx.meta = (dst_rank, dst_row, x.size(0), k, buf, n_recv, keep)
         buf.barrier()                                           # receive buffers are free everywhere
         push_rows(x, dst_rank, dst_row, buf.recv_x, buf, src_row=src_row)
         buf.barrier()                                           # every row has landed
@@ -110,17 +116,19 @@ class _Dispatch(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g_recv):
-        dst_rank, dst_row, T, k, buf, n_recv = ctx.meta
+        dst_rank, dst_row, T, k, buf, n_recv, keep = ctx.meta
         buf.barrier()
         buf.view(buf.g_x, n_recv).copy_(g_recv)
         buf.barrier()
-        dx, _ = pull_combine(buf.g_x, buf, dst_rank, dst_row, None, T, k)      # slots of a token are adjacent
-        return dx, None, None, None, None, None, None
+        # slots of a token are adjacent; slots dropped at the owner's row bound carry no gradient
+        dx, _ = pull_combine(buf.g_x, buf, dst_rank, dst_row, None if keep is None else keep.view(T, k), T, k)
+        return dx, None, None, None, None, None, None, None
 
 
 class _Combine(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, y_local, weight, rank_sorted, row_sorted, T, k, buf):
+    def forward(ctx, y_local, weight, rank_sorted, row_sorted, T, k, buf, masked=False):
+        ctx.masked = masked
         n = y_local.size(0)
         buf.barrier()
         buf.view(buf.y, n).copy_(y_local)
@@ -141,12 +149,14 @@ class _Combine(torch.autograd.Function):
         buf.view(buf.y, n).copy_(y_local)                        # expert rows again, for d(weight)
         buf.barrier()
         _, dw = pull_combine(buf.y, buf, rank_sorted, row_sorted, None, T, k, gout=gout, want_dweight=True, fp32_out=True)
+        if ctx.masked:
+            dw = dw * (weight != 0)                               # dropped slots read rows the owner never computed
         src_row = torch.arange(T, device=gout.device, dtype=torch.int32).repeat_interleave(k)
         push_rows(gout, rank_sorted.flatten(), row_sorted.flatten(), buf.g_y, buf, scale=weight.flatten().contiguous(),
                   src_row=src_row)
         buf.barrier()
         gy = buf.view(buf.g_y, n).clone()
-        return gy, dw, None, None, None, None, None
+        return gy, dw, None, None, None, None, None, None
 
 
 class FusedExpertParallelMoE(nn.Module):
@@ -212,7 +222,7 @@ class FusedExpertParallelMoE(nn.Module):
         if n_recv > self.buf.capacity:
             raise RuntimeError(f"expert receive buffer too small: {n_recv} rows > capacity {self.buf.capacity}")
         src_row = torch.arange(T, device=x.device, dtype=torch.int32).repeat_interleave(k)
-        recv = _Dispatch.apply(x2, src_row, dst_rank, dst_row, n_recv, k, self.buf)
+        recv = _Dispatch.apply(x2, src_row, dst_rank, dst_row, n_recv, k, self.buf, None)
         # all local experts in ONE grouped GEMM per projection (rows in the 256-row padding are never read back)
         tiles = grouped.tile_groups(seg_pad, x.device)
         h = grouped.grouped_linear(recv, self.experts.gate_up, tiles, seg, seg_pad, fp8=self.fp8)
@@ -221,7 +231,7 @@ class FusedExpertParallelMoE(nn.Module):
         eo = idx.argsort(dim=-1)
         slots = (torch.arange(T, device=x.device) * k).unsqueeze(1) + eo
         rank_s, row_s, w_s = dst_rank[slots].contiguous(), dst_row[slots].contiguous(), w.gather(1, eo).float().contiguous()
-        out = _Combine.apply(y_local, w_s, rank_s, row_s, T, k, self.buf)
+        out = _Combine.apply(y_local, w_s, rank_s, row_s, T, k, self.buf, False)
         if self.shared is not None:
             out = out + self.shared(x2).to(out.dtype)
         return out.reshape(shape)
@@ -237,14 +247,19 @@ class FusedExpertParallelMoE(nn.Module):
         bound = min((bound + grouped.TILE - 1) // grouped.TILE * grouped.TILE, limit)
         tiles, kb_range = grouped.device_plan(mine[1], bound)
         self.buf.note_rows(mine[1].sum(), bound)
+        # every rank uses the same bound (same token count, or the all-reduced adaptive bound), so the sender knows which
+        # of its slots land past it: those are dropped (weight 0, no gradient), as in capacity-factor routing
+        keep = (dst_row < bound).float()
         src_row = torch.arange(T, device=x2.device, dtype=torch.int32).repeat_interleave(k)
-        recv = _Dispatch.apply(x2, src_row, dst_rank, dst_row, bound, k, self.buf)
+        recv = _Dispatch.apply(x2, src_row, dst_rank, dst_row, bound, k, self.buf, keep)
         h = grouped.grouped_linear_device(recv, self.experts.gate_up, tiles, kb_range, fp8=self.fp8)
         y_local = grouped.grouped_linear_device(block_ops.swiglu(h, self.limit), self.experts.down, tiles, kb_range, fp8=self.fp8)
         eo = idx.argsort(dim=-1)
         slots = (torch.arange(T, device=x2.device) * k).unsqueeze(1) + eo
-        rank_s, row_s, w_s = dst_rank[slots].contiguous(), dst_row[slots].contiguous(), w.gather(1, eo).float().contiguous()
-        out = _Combine.apply(y_local, w_s, rank_s, row_s, T, k, self.buf)
+        rank_s, row_s = dst_rank[slots].contiguous(), dst_row[slots].contiguous()
+        w_s = (w.gather(1, eo).float() * keep[slots]).contiguous()
+        self._last_keep = keep.view(T, k)
+        out = _Combine.apply(y_local, w_s, rank_s, row_s, T, k, self.buf, True)
         if self.shared is not None:
             out = out + self.shared(x2).to(out.dtype)
         return out.reshape(shape)

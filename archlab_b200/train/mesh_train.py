@@ -610,12 +610,13 @@ def train(a, *, on_step=None) -> list[float]:
         else:
             dt = time.perf_counter() - t0
         losses.append(float(loss))
-        if getattr(job, "ep_buffers", None) is not None:
-            job.ep_buffers.check_overflow()                      # a layer received more rows than its bound: fail loudly
+        dropped = None
+        if getattr(job, "ep_buffers", None) is not None and getattr(job.model.config, "expert_capacity_factor", None) is not None:
+            dropped = job.ep_buffers.check_overflow()["dropped_rows"]      # rows past the expert row bound (tokens dropped)
         guard.check(step + 1, losses[-1], gnorm)
         beat.beat(step=step + 1, loss=losses[-1])
         if log is not None:
-            log.write(json.dumps({"step": step + 1, "loss": losses[-1], "grad_norm": gnorm, "step_seconds": dt,
+            log.write(json.dumps({"step": step + 1, "loss": losses[-1], "grad_norm": gnorm, "step_seconds": dt, "dropped_expert_rows": dropped,
                                   "tokens_per_second": a.global_batch * a.seq_len / dt,
                                   "timing": "cuda events, max over ranks" if cuda else "host clock",
                                   "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 2) if cuda else 0.0,

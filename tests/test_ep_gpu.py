@@ -63,7 +63,7 @@ def _worker(rank, world, port, out_dir):
     finally:
         torch.cuda.set_sync_debug_mode("default")
     res["sync_free_out"] = ((ys.float() - yb.float()).abs().max()).item()          # same inputs as the last iteration
-    buf.check_overflow()
+    res["ample_bound_drops_nothing"] = float(buf.check_overflow()["dropped_rows"])
     # the host-planned form (exact sizes read back) gives the same numbers
     exact = ep.FusedExpertParallelMoE(dim, inter, E, k, buf, swiglu_limit=7.0, n_shared=1, capacity_factor=None).to(dev).bfloat16()
     exact.e_score_correction_bias = exact.e_score_correction_bias.float()
@@ -83,13 +83,19 @@ def _worker(rank, world, port, out_dir):
     with torch.no_grad():
         tight.router.zero_()
         tight.e_score_correction_bias[: k] += 10.0                       # every token to the first k experts: rank 0 overflows
-        tight(x)
-    raised = False
-    try:
-        buf.check_overflow()
-    except RuntimeError:
-        raised = True
-    res["overflow_reported"] = 0.0 if (raised or rank != 0) else 1.0
+        exact.load_state_dict(tight.state_dict())
+        exact.e_score_correction_bias = tight.e_score_correction_bias.clone()
+        y_tight, y_exact = tight(x), exact(x)
+    info = buf.check_overflow()                                          # collective: the same verdict on every rank
+    res["overflow_reported"] = 0.0 if info["dropped_rows"] > 0 else 1.0
+    res["dropped_output_finite"] = 0.0 if bool(torch.isfinite(y_tight).all()) else 1.0
+    kept_all = tight._last_keep.bool().all(1)
+    res["some_tokens_dropped"] = 0.0 if (world == 1 or bool((~kept_all).any()) or rank != 0) else 1.0
+    if bool(kept_all.any()):                                              # tokens that lost no slot are computed exactly
+        res["kept_tokens_exact"] = (y_tight[kept_all].float() - y_exact[kept_all].float()).abs().max().item()
+    lost = ~kept_all
+    if bool(lost.any()):                                                  # the others lost (part of) their expert sum
+        res["dropped_tokens_differ"] = 0.0 if (y_tight[lost].float() - y_exact[lost].float()).abs().max().item() > 1e-3 else 1.0
     torch.cuda.synchronize()
     native.check_status()
     torch.save(res, os.path.join(out_dir, f"ep_rank{rank}.pt"))
