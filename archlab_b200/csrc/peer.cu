@@ -44,7 +44,10 @@ __global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int epo
     const int* mine = reinterpret_cast<const int*>(flags.p[rank]) + t;
     const unsigned long long t0 = globaltimer_ns();
     unsigned it = 0;
-    while (ld_acquire_sys(mine) < epoch) {
+    // once a wait of this process has expired the step is lost anyway: later barriers do not wait again, so the host
+    // reaches its next status check after one budget instead of one budget per barrier
+    const bool lost = *reinterpret_cast<volatile int*>(status) != 0;
+    while (!lost && ld_acquire_sys(mine) < epoch) {
       if ((++it & 255u) == 0u && globaltimer_ns() - t0 > budget_ns) {
         atomicCAS(status, 0, kErrPeerTimeout);
         break;

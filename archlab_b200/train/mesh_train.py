@@ -610,6 +610,11 @@ def train(a, *, on_step=None) -> list[float]:
         else:
             dt = time.perf_counter() - t0
         losses.append(float(loss))
+        if cuda:
+            from ..ops import native
+
+            if native.available():
+                native.check_status()                            # an expired device-side wait (peer barrier, flag) ends the run here
         dropped = None
         if getattr(job, "ep_buffers", None) is not None and getattr(job.model.config, "expert_capacity_factor", None) is not None:
             dropped = job.ep_buffers.check_overflow()["dropped_rows"]      # rows past the expert row bound (tokens dropped)
