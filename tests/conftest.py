@@ -24,7 +24,7 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
-def join_ranks(procs, timeout: float = 600.0) -> None:
+def join_ranks(procs, timeout: float = 300.0) -> None:
     """Waits for the child processes of a multi-rank test; a rank whose peer failed must not outlive the test
     (it would sit in a collective until the process-group timeout), so stragglers are terminated."""
     try:
