@@ -15,6 +15,7 @@ Plays the role of the reference's Megatron launches (``src/archlab/megatron/qwen
 from __future__ import annotations
 
 import argparse
+import faulthandler
 import json
 import os
 import time
@@ -144,6 +145,9 @@ def parse_args(argv=None):
     ap.add_argument("--bounded-staging", action="store_true",
                     help="checkpoints: the local ranks of a host stage and write one at a time (bounds host memory)")
     ap.add_argument("--resume", action="store_true", help="continue from the newest checkpoint in --run-dir")
+    ap.add_argument("--hang-dump-seconds", type=float, default=0.0,
+                    help="a step that takes longer than this writes the Python stack of every thread of the rank to stderr "
+                         "(re-armed every step; 0: off)")
     return ap.parse_args(argv)
 
 
@@ -573,8 +577,11 @@ def train(a, *, on_step=None) -> list[float]:
     scale = 1.0 / (accum * mesh.dp)
     cuda = device.type == "cuda"
     reached, stopped_early = start, False
+    watchdog = float(getattr(a, "hang_dump_seconds", 0.0) or 0.0)
     for step in range(start, a.steps):
         t0 = time.perf_counter()
+        if watchdog > 0:                                         # where is every thread if this step does not come back
+            faulthandler.dump_traceback_later(watchdog, repeat=True, exit=False)
         if cuda:
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()
@@ -637,6 +644,8 @@ def train(a, *, on_step=None) -> list[float]:
             stop.acknowledge(step + 1, rank)
             stopped_early = reached < a.steps
             break
+    if watchdog > 0:
+        faulthandler.cancel_dump_traceback_later()
     if receipts is not None:
         outcome = {"final_loss": losses[-1] if losses else None, "steps": reached, "step_budget": a.steps}
         if stopped_early:

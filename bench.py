@@ -297,7 +297,7 @@ def mesh_config(args) -> None:
         argv = ["--model=v41_moe", f"--ep={world}", "--seq-len=4096", "--micro-batch=1", f"--global-batch={per_gpu * world}"]
         par = f"ep{world} (= dp{world})"
         model = "DeepSeek-V4.1-style MoE (24L, hidden 2048, 64 routed experts FFN 1408 top-6 + 2 shared, DSA top-2048, 4 HC streams)"
-    argv += [f"--precision={args.precision}", f"--steps={total}", f"--run-dir={run_dir or tempfile.gettempdir() + '/bench-mesh-other'}"]
+    argv += [f"--precision={args.precision}", "--hang-dump-seconds=120", f"--steps={total}", f"--run-dir={run_dir or tempfile.gettempdir() + '/bench-mesh-other'}"]
     marks = {}
     sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
 

@@ -159,3 +159,21 @@ def test_fully_sharded_linears_follow_the_replicated_run(tmp_path):
     norms = [[json.loads(l)["grad_norm"] for l in open(tmp_path / d / "metrics_rank0.jsonl")] for d in ("plain", "fsdp")]
     assert all(abs(a - b) < 2e-2 * a for a, b in zip(*norms)), norms        # same gradient scale, not only the same direction
     assert all(abs(a - b) < 1e-6 for a, b in zip(shard[0], shard[1]))
+
+
+def test_hang_dump_writes_the_stacks_of_a_slow_step(tmp_path, capfd):
+    """A step slower than --hang-dump-seconds leaves the Python stack of every thread on stderr."""
+    import time
+
+    from archlab_b200.train import mesh_train
+
+    def slow(step, loss):
+        if step == 0:
+            time.sleep(1.6)
+
+    args = mesh_train.parse_args(["--model=qwen35_tiny", "--seq-len=32", "--global-batch=2", "--steps=2", f"--run-dir={tmp_path}",
+                                  "--hang-dump-seconds=0.5"])
+    # the hook runs inside the step, so the armed dump fires while it sleeps
+    mesh_train.train(args, on_step=slow)
+    err = capfd.readouterr().err
+    assert "Timeout (0:00:00.5" in err and "most recent call first" in err and "slow" in err
