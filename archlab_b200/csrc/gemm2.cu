@@ -67,7 +67,7 @@ __device__ __forceinline__ bool wait_block_ready(const int* flag, int epoch, vol
   const long long t0 = clock64();
   while ((sys ? ld_acquire_sys(flag) : ld_acquire_gpu(flag)) < epoch) {
     if (*abort_word != 0) return false;
-    if (clock64() - t0 > kWaitBudgetCycles) {
+    if (clock64() - t0 > kPeerWaitBudgetCycles) {
       *abort_word = kErrPeerTimeout;
       return false;
     }

@@ -19,8 +19,13 @@ enum : int {
   kErrBadShape = 3,
 };
 
-constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s (waits on other GPUs)
+// Waits on another GPU cover the skew between the ranks' host threads (a rank that compiles a kernel, grows its allocator
+// or writes a checkpoint can be seconds late): 30 s by default, settable (nga_set_peer_wait_budget_ns; tests use
+// milliseconds).  A 2 s default made a 4-rank run of the 24-layer MoE model fail at its fifth step (one rank was late,
+// three reported an expired peer wait).  Waits inside one GPU (mbarriers) keep ~2 s.
+constexpr unsigned long long kWaitBudgetNs = 30000000000ull;  // 30 s (waits on other GPUs)
 constexpr long long kWaitBudgetCycles = 4000000000ll;         // ~2 s of SM cycles (mbarrier waits)
+constexpr long long kPeerWaitBudgetCycles = 60000000000ll;    // ~30 s of SM cycles (flags written by another GPU)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
