@@ -73,7 +73,9 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, r
     (needs N and K to be multiples of 128); gradients are straight-through in bf16."""
     E, N, K = w.shape
     if x.size(0) == 0:
-        return x.new_zeros(0, N) + 0 * w.sum().to(x.dtype)            # keeps the weights in the graph
+        # keeps the weights AND the (empty) input in the graph: the input's producer may be a collective autograd function
+        # (expert dispatch) whose backward every rank must run, rows or no rows
+        return x.new_zeros(0, N) + (0 * w.sum() + 0 * x.sum()).to(x.dtype)
     if x.is_cuda and x.dtype == torch.bfloat16 and native.available() and K % 8 == 0 and N % 64 == 0 and K % 64 == 0:
         return _GroupedLinear.apply(x.contiguous(), w.to(x.dtype).contiguous(), tile_group, real, padded,
                                     bool(fp8 and N % 128 == 0 and K % 128 == 0))

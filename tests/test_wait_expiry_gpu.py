@@ -18,7 +18,7 @@ def test_barrier_wait_expires_and_reports_operational_failure():
     L.nga_set_peer_wait_budget_ns.argtypes, L.nga_set_peer_wait_budget_ns.restype = [C.c_ulonglong], None
     L.nga_peer_wait_budget_ns.restype = C.c_ulonglong
     default = L.nga_peer_wait_budget_ns()
-    assert default == 2_000_000_000
+    assert default == 30_000_000_000                                # inter-GPU waits tolerate a late rank by default
     mine = torch.zeros(16, dtype=torch.int32, device="cuda")       # this rank's flag array
     other = torch.zeros(16, dtype=torch.int32, device="cuda")      # stands in for rank 1's; rank 1 never runs
     table = (C.c_longlong * 2)(mine.data_ptr(), other.data_ptr())
