@@ -107,6 +107,8 @@ class _SwiGLU(torch.autograd.Function):
         (h,) = ctx.saved_tensors
         rows, inter, limit = ctx.meta
         dh = torch.empty_like(h)
+        if rows == 0:                      # a rank without expert rows still runs the backward of its (empty) branch
+            return dh, None
         native.check(native.lib().nga_swiglu_bwd(_p(h), _p(dout.contiguous()), _p(dh), rows, inter, limit, native.stream_ptr()),
                      "nga_swiglu_bwd")
         return dh, None
