@@ -55,3 +55,171 @@ def markdown_table(rows: list[dict], columns: list[str], *, digits: int = 4) -> 
     fmt = lambda v: f"{v:.{digits}f}" if isinstance(v, float) else str(v)
     head = "| " + " | ".join(columns) + " |\n|" + "|".join("---" for _ in columns) + "|\n"
     return head + "".join("| " + " | ".join(fmt(r.get(c, "")) for c in columns) + " |\n" for r in rows)
+
+
+# ======================================================================================================================
+# Token-matched comparison of two training runs from their append-only ledgers
+# (what the reference's paired report computes: src/archlab/reporting/runs.py:9-132, paired_curves.py:12-92)
+# ======================================================================================================================
+class TrainingLedger:
+    """Validated rows of a run's ``train-metrics.jsonl`` (preceded by ``prior-phase-metrics.jsonl`` when present).
+
+    A ledger is trusted only if its steps are contiguous, every row has a positive token count and a finite loss, and the
+    cumulative token cursor equals the running sum of the rows' token counts.  A last line without its newline belongs to
+    a writer that is still running and is left out; any other undecodable line is an error."""
+
+    def __init__(self, rows: list[dict], sources: list[dict] | None = None):
+        self.rows, self.sources = rows, sources or []
+        self._validate()
+
+    @staticmethod
+    def decode(raw: bytes) -> list[dict]:
+        rows, lines = [], raw.split(b"\n")                   # records are separated by LF only, never by Unicode separators
+        for i, line in enumerate(lines):
+            if not line.strip():
+                continue
+            try:
+                row = json.loads(line)
+            except json.JSONDecodeError:
+                if i == len(lines) - 1 and not raw.endswith(b"\n"):
+                    break
+                raise
+            if not isinstance(row, dict):
+                raise ValueError("a training ledger holds JSON objects")
+            rows.append(row)
+        return rows
+
+    @classmethod
+    def read(cls, directory, *, include_history: bool = True) -> "TrainingLedger":
+        import hashlib
+
+        directory = Path(directory)
+        files = [directory / "train-metrics.jsonl"]
+        if include_history and (directory / "prior-phase-metrics.jsonl").exists():
+            files.insert(0, directory / "prior-phase-metrics.jsonl")
+        rows, sources = [], []
+        for f in files:
+            raw = f.read_bytes()
+            part = cls.decode(raw)
+            rows += part
+            sources.append({"path": str(f.resolve()), "sha256": hashlib.sha256(raw).hexdigest(), "rows": len(part)})
+        return cls(rows, sources)
+
+    def _validate(self) -> None:
+        if not self.rows:
+            raise ValueError("empty training ledger")
+        step = self.rows[0]["step"] - 1
+        cursor = self.rows[0]["consumed_supervised_tokens"] - self.rows[0]["supervised_tokens"]
+        if cursor < 0:
+            raise ValueError("negative initial token cursor")
+        for r in self.rows:
+            if r["step"] != step + 1:
+                raise ValueError("non-contiguous training steps")
+            if r["supervised_tokens"] <= 0 or not math.isfinite(r["loss"]):
+                raise ValueError("invalid token count or nonfinite loss")
+            cursor += r["supervised_tokens"]
+            if r["consumed_supervised_tokens"] != cursor:
+                raise ValueError("token ledger differs from cumulative cursor")
+            step = r["step"]
+
+    @property
+    def token_interval(self) -> tuple[int, int]:
+        first, last = self.rows[0], self.rows[-1]
+        return first["consumed_supervised_tokens"] - first["supervised_tokens"], last["consumed_supervised_tokens"]
+
+    def window_mean(self, low: float, high: float) -> float:
+        """Token-weighted mean loss over the token interval [low, high)."""
+        if not (math.isfinite(low) and math.isfinite(high) and high > low):
+            raise ValueError("token window must have finite increasing bounds")
+        total = weight = 0.0
+        for r in self.rows:
+            end = r["consumed_supervised_tokens"]
+            overlap = max(0, min(end, high) - max(end - r["supervised_tokens"], low))
+            total, weight = total + overlap * r["loss"], weight + overlap
+        if weight <= 0:
+            raise ValueError("empty token window")
+        return total / weight
+
+    def smoothed(self, width: int) -> list[tuple[int, float]]:
+        """(token cursor, token-weighted mean loss of the trailing ``width`` tokens) after every update."""
+        if width <= 0:
+            raise ValueError("smoothing token count must be positive")
+        start = self.token_interval[0]
+        return [(r["consumed_supervised_tokens"], self.window_mean(max(start, r["consumed_supervised_tokens"] - width), r["consumed_supervised_tokens"]))
+                for r in self.rows]
+
+
+PAIRED_FIELDS = ("consumed_supervised_tokens", "supervised_tokens", "input_tokens", "window_cursor", "learning_rate")
+
+
+def matched_ledgers(first: TrainingLedger, second: TrainingLedger) -> tuple[TrainingLedger, TrainingLedger]:
+    """The common steps of two runs, refusing pairs whose data or schedule cursors differ at a common step: updates are
+    matched, never interpolated."""
+    left, right = ({r["step"]: r for r in ledger.rows} for ledger in (first, second))
+    steps = sorted(left.keys() & right.keys())
+    if not steps:
+        raise ValueError("runs have no common training steps")
+    for s in steps:
+        for f in PAIRED_FIELDS:
+            if (f in left[s]) != (f in right[s]) or left[s].get(f) != right[s].get(f):
+                raise ValueError(f"paired {f} differs at step {s}")
+    return TrainingLedger([left[s] for s in steps]), TrainingLedger([right[s] for s in steps])
+
+
+def paired_report(runs: dict[str, str], output, *, smoothing_tokens: int = 5_000_000, summary_tokens: int = 10_000_000,
+                  current_phase_only: bool = False) -> dict:
+    """Writes ``SUMMARY.json``, per-run snapshots and ``matched-training-curves.csv`` for exactly two labelled runs."""
+    import csv
+
+    from ..contracts.substrate import atomic_write_json
+
+    if len(runs) != 2:
+        raise ValueError("provide exactly two runs with distinct labels")
+    if min(smoothing_tokens, summary_tokens) <= 0:
+        raise ValueError("token windows must be positive")
+    labels = list(runs)
+    loaded = [TrainingLedger.read(runs[k], include_history=not current_phase_only) for k in labels]
+    paired = matched_ledgers(*loaded)
+    start, stop = paired[0].token_interval
+    low = max(start, stop - summary_tokens)
+    output = Path(output)
+    output.mkdir(parents=True, exist_ok=False)
+    summary = {"matched_steps": [paired[0].rows[0]["step"], paired[0].rows[-1]["step"]], "matched_token_interval": [start, stop],
+               "summary_token_interval": [low, stop], "smoothing_tokens": smoothing_tokens, "runs": {}}
+    for i, k in enumerate(labels):
+        summary["runs"][k] = {"directory": str(Path(runs[k]).resolve()), "sources": loaded[i].sources, "latest_step": loaded[i].rows[-1]["step"],
+                              "latest_tokens": loaded[i].rows[-1]["consumed_supervised_tokens"],
+                              "matched_token_weighted_ce": paired[i].window_mean(low, stop)}
+        (output / f"run-{i}-snapshot.jsonl").write_text("".join(json.dumps(r) + "\n" for r in loaded[i].rows))
+    summary["first_minus_second_ce"] = (summary["runs"][labels[0]]["matched_token_weighted_ce"]
+                                        - summary["runs"][labels[1]]["matched_token_weighted_ce"])
+    atomic_write_json(output / "SUMMARY.json", summary, allow_nan=False)
+    curves = [dict(p.smoothed(smoothing_tokens)) for p in paired]
+    with (output / "matched-training-curves.csv").open("w", newline="") as f:
+        w = csv.writer(f)
+        w.writerow(["step", "supervised_tokens", *labels, *(f"{k}_smoothed" for k in labels)])
+        for a, b in zip(paired[0].rows, paired[1].rows):
+            t = a["consumed_supervised_tokens"]
+            w.writerow([a["step"], t, a["loss"], b["loss"], curves[0][t], curves[1][t]])
+    return summary
+
+
+def main(argv=None) -> int:
+    import argparse
+
+    ap = argparse.ArgumentParser(description="Summarise two token-matched training runs.")
+    ap.add_argument("--run", nargs=2, action="append", required=True, metavar=("LABEL", "DIRECTORY"))
+    ap.add_argument("--output", type=Path, required=True)
+    ap.add_argument("--smoothing-tokens", type=int, default=5_000_000)
+    ap.add_argument("--summary-tokens", type=int, default=10_000_000)
+    ap.add_argument("--current-phase-only", action="store_true")
+    a = ap.parse_args(argv)
+    if len({label for label, _ in a.run}) != len(a.run):
+        ap.error("run labels must be distinct")
+    print(json.dumps(paired_report(dict(a.run), a.output, smoothing_tokens=a.smoothing_tokens, summary_tokens=a.summary_tokens,
+                                   current_phase_only=a.current_phase_only), indent=2))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
