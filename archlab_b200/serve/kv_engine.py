@@ -193,9 +193,20 @@ def answer_tickets(front, engine: "Engine", tokenizer, *, stop=None, idle_timeou
             room = engine.model.cos.size(0) - len(prompt)
             if room < 1:
                 raise ValueError("the conversation does not fit the model's context")
-            out = engine.generate_batch(prompt, max_tokens=min(req["max_tokens"], room), temperature=req["temperature"],
-                                        top_k=top_k, seed=req["seed"] % (2 ** 63), stop_tokens=(end,))[0]
-            ticket.finish(text=tokenizer.decode(out[len(prompt):]))
+            reply, shown = [], ""
+            for column, _ in engine.generate(prompt, max_tokens=min(req["max_tokens"], room), temperature=req["temperature"],
+                                             top_k=top_k, seed=req["seed"] % (2 ** 63), stop_tokens=(end,)):
+                if column[0] is None or column[0] == end:
+                    continue
+                reply.append(column[0])
+                if req.get("stream"):
+                    # a token may end inside a multi-byte character: only the text that is already stable goes out
+                    text = tokenizer.decode(reply)
+                    stable = text[:len(text) - 1] if text.endswith("\ufffd") else text
+                    if len(stable) > len(shown) and stable.startswith(shown):
+                        ticket.emit(stable[len(shown):])
+                        shown = stable
+            ticket.finish(text=tokenizer.decode(reply))
         except Exception as e:                                     # the front reports it as a 500 with this message
             ticket.finish(error=f"{type(e).__name__}: {e}")
         served += 1

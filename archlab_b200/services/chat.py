@@ -1,6 +1,12 @@
 """OpenAI-compatible chat front for a checkpoint under evaluation: strict request validation and a
 ticket queue that the generation loop drains at a collective boundary, so HTTP threads never touch
-the model (src/archlab/serving/openai_chat.py:23-300)."""
+the model (src/archlab/serving/openai_chat.py:23-300).
+
+``"stream": true`` is answered as server-sent events (``chat.completion.chunk`` objects, then ``data: [DONE]``): the
+generation loop calls ``Ticket.emit(piece)`` as text becomes available and the HTTP thread forwards every piece at once
+with buffering switched off for proxies, which is what a streaming playground needs from the server side (the
+reference patches the MLflow UI to consume such a stream, src/archlab/serving/mlflow_playground_overlay.py:1-156; the
+UI patch itself has no counterpart here, MLflow is not part of this framework)."""
 from __future__ import annotations
 
 import json
@@ -57,9 +63,16 @@ class Ticket:
     done: threading.Event = field(default_factory=threading.Event)
     text: str | None = None
     error: str | None = None
+    pieces: "queue.Queue[str | None]" = field(default_factory=queue.Queue)      # streamed text; None closes the stream
+
+    def emit(self, piece: str) -> None:
+        """Streaming: hand the next piece of generated text to the waiting HTTP thread."""
+        if piece:
+            self.pieces.put(piece)
 
     def finish(self, text: str | None = None, error: str | None = None) -> None:
         self.text, self.error = text, error
+        self.pieces.put(None)
         self.done.set()
 
 
@@ -84,6 +97,44 @@ class ChatFront:
                 self.end_headers()
                 self.wfile.write(body)
 
+            def _event(self, payload) -> None:
+                self.wfile.write(b"data: " + (payload if isinstance(payload, bytes) else json.dumps(payload).encode()) + b"\n\n")
+                self.wfile.flush()
+
+            def _stream(self, t, req):
+                """Server-sent events: a role chunk, one chunk per emitted piece, a finish chunk, ``[DONE]``."""
+                self.send_response(200)
+                self.send_header("Content-Type", "text/event-stream")
+                self.send_header("Cache-Control", "no-cache")
+                self.send_header("X-Accel-Buffering", "no")            # reverse proxies must not hold chunks back
+                self.send_header("Connection", "close")
+                self.end_headers()
+                chunk = lambda delta, finish=None: {"id": t.id, "object": "chat.completion.chunk", "created": int(time.time()),
+                                                    "model": req["model"], "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
+                self._event(chunk({"role": "assistant"}))
+                sent, deadline = "", time.monotonic() + front.timeout
+                try:
+                    while True:
+                        try:
+                            piece = t.pieces.get(timeout=max(0.0, deadline - time.monotonic()))
+                        except queue.Empty:
+                            self._event({"error": {"message": "generation timed out"}})
+                            break
+                        if piece is None:
+                            if t.error:
+                                self._event({"error": {"message": t.error}})
+                            else:
+                                rest = (t.text or "")[len(sent):] if (t.text or "").startswith(sent) else ""
+                                if rest:                                  # a loop that never called emit still streams once
+                                    self._event(chunk({"content": rest}))
+                                self._event(chunk({}, "stop"))
+                            break
+                        sent += piece
+                        self._event(chunk({"content": piece}))
+                    self._event(b"[DONE]")
+                except (BrokenPipeError, ConnectionResetError):
+                    pass                                                  # the client went away; the ticket finishes on its own
+
             def do_GET(self):
                 if self.path == "/v1/models":
                     self._send(200, {"object": "list", "data": [{"id": m, "object": "model"} for m in front.models]})
@@ -104,6 +155,8 @@ class ChatFront:
                     return self._send(400, {"error": {"message": str(e)}})
                 t = Ticket(req)
                 front.tickets.put(t)
+                if req["stream"]:
+                    return self._stream(t, req)
                 if not t.done.wait(front.timeout):
                     return self._send(504, {"error": {"message": "generation timed out"}})
                 if t.error:

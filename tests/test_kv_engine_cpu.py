@@ -90,3 +90,45 @@ def test_chat_front_is_answered_by_the_engine():
     front.server.shutdown()
     assert served == 1 and result["reply"]["object"] == "chat.completion"
     assert isinstance(result["reply"]["choices"][0]["message"]["content"], str)
+
+
+def test_streamed_reply_equals_the_whole_reply():
+    """With ``stream`` the engine's worker emits the reply piece by piece; the pieces concatenate to the same text the
+    non-streaming request returns for the same seed."""
+    import json
+    import threading
+    import urllib.request
+
+    from archlab_b200.data.tokenizer import BPETokenizer
+    from archlab_b200.serve.kv_engine import answer_tickets
+    from archlab_b200.services.chat import ChatFront
+
+    tok = BPETokenizer.train(["hello world, hello there. the quick brown fox"] * 4, vocab_size=280)
+    torch.manual_seed(0)
+    m = GPT(GPTConfig(sequence_len=128, vocab_size=300, n_layer=2, n_head=2, n_kv_head=2, n_embd=32, window_pattern="L"))
+    m.init_weights()
+    front = ChatFront("127.0.0.1", 0, "tok", {"tiny": "normal"})
+    port = front.server.server_address[1]
+    stop = threading.Event()
+    got = {}
+
+    def ask(stream):
+        body = json.dumps({"model": "tiny", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 8, "seed": 5,
+                           "stream": stream}).encode()
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/chat/completions", data=body,
+                                     headers={"Authorization": "Bearer tok", "Content-Type": "application/json"})
+        return urllib.request.urlopen(req, timeout=30).read().decode()
+
+    def client():
+        got["whole"] = json.loads(ask(False))["choices"][0]["message"]["content"]
+        events = [e[len("data: "):] for e in ask(True).split("\n\n") if e.startswith("data: ")]
+        got["pieces"] = [json.loads(e)["choices"][0]["delta"].get("content", "") for e in events[:-1]]
+        got["last"] = events[-1]
+        stop.set()
+
+    t = threading.Thread(target=client)
+    t.start()
+    served = answer_tickets(front, Engine(m), tok, stop=stop.is_set)
+    t.join(10)
+    front.server.shutdown()
+    assert served == 2 and got["last"] == "[DONE]" and "".join(got["pieces"]) == got["whole"]

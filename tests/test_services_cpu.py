@@ -112,3 +112,45 @@ def test_reporting_pairs_by_seed(tmp_path):
     rows = reporting.read_metrics(m)
     assert abs(reporting.final_value(rows) - 1.45) < 1e-9 and len(reporting.learning_curve(rows, ema=0.9)) == 20
     assert reporting.markdown_table([{"a": 1, "b": 0.5}], ["a", "b"]).count("|") == 9
+
+
+def test_chat_front_streams_server_sent_events():
+    import threading
+
+    models = {"ckpt-a": "normal"}
+    body = {"model": "ckpt-a", "messages": [{"role": "user", "content": "count"}], "max_tokens": 8, "stream": True}
+    front = chat.ChatFront("127.0.0.1", 0, "tok", models, timeout=5)
+    try:
+        def owner():
+            t = front.next_ticket(timeout=5)
+            for piece in ("one ", "two ", "three"):
+                t.emit(piece)
+            t.finish("one two three")
+            t = front.next_ticket(timeout=5)                      # a loop that never emits still streams its text once
+            t.finish("whole")
+            t = front.next_ticket(timeout=5)
+            t.emit("par")
+            t.finish(error="device lost")
+
+        threading.Thread(target=owner, daemon=True).start()
+
+        def events():
+            req = urllib.request.Request(f"http://127.0.0.1:{front.port}/v1/chat/completions", data=json.dumps(body).encode(),
+                                         headers={"Authorization": "Bearer tok", "Content-Type": "application/json"})
+            with urllib.request.urlopen(req, timeout=5) as resp:
+                assert resp.headers["Content-Type"] == "text/event-stream" and resp.headers["X-Accel-Buffering"] == "no"
+                raw = resp.read().decode()
+            return [line[len("data: "):] for line in raw.split("\n\n") if line.startswith("data: ")]
+
+        first = events()
+        assert first[-1] == "[DONE]"
+        chunks = [json.loads(e) for e in first[:-1]]
+        assert chunks[0]["choices"][0]["delta"] == {"role": "assistant"} and chunks[0]["object"] == "chat.completion.chunk"
+        assert [c["choices"][0]["delta"].get("content") for c in chunks[1:-1]] == ["one ", "two ", "three"]
+        assert chunks[-1]["choices"][0]["finish_reason"] == "stop" and len({c["id"] for c in chunks}) == 1
+        second = [json.loads(e) for e in events()[:-1]]
+        assert [c["choices"][0]["delta"].get("content") for c in second[1:-1]] == ["whole"]
+        third = events()
+        assert json.loads(third[-2]) == {"error": {"message": "device lost"}} and third[-1] == "[DONE]"
+    finally:
+        front.close()
