@@ -144,6 +144,10 @@ def load_prompts(path, tokenizer=None) -> list[list[int]]:
     import yaml
 
     doc = yaml.safe_load(Path(path).read_text())
+    if isinstance(doc, dict) and "schema_version" in doc:              # a versioned prompt set: rows with id / text / tags
+        from ..contracts.prompts import load_prompt_set
+
+        doc = [p.text for p in load_prompt_set(path)]
     prompts = doc.get("prompts") if isinstance(doc, dict) else doc
     if not isinstance(prompts, list) or not prompts:
         raise ValueError("the prompt file holds no prompts")
