@@ -20,6 +20,7 @@ import hashlib
 import json
 import math
 import re
+import shutil
 import time
 from collections import Counter
 from pathlib import Path
@@ -139,12 +140,30 @@ def state_sha256(state: dict[str, torch.Tensor]) -> str:
 
 
 def export_hf(out_dir, state: dict[str, torch.Tensor], config: dict, *, export_format: str = "archlab-hf-v1",
-              extra_files: dict[str, bytes] | None = None, lineage: dict | None = None) -> dict:
-    """Writes config.json + model.safetensors (+ assets), then EXPORT.json last, then re-loads to verify."""
+              extra_files: dict[str, bytes] | None = None, lineage: dict | None = None,
+              tokenizer_dir=None, tokenizer_identity_sha256: str | None = None) -> dict:
+    """Writes config.json + model.safetensors (+ assets), then EXPORT.json last, then re-loads to verify.
+
+    ``tokenizer_dir``: the tokenizer's files (``TOKENIZER_ASSETS``, those that exist) are copied beside the weights so
+    the export loads on its own; ``tokenizer.json`` or a sentencepiece model must be among them.  Their combined digest
+    (``tokenizer_identity``) goes into the receipt and must equal ``tokenizer_identity_sha256`` when that is given, so a
+    checkpoint is never shipped with another run's vocabulary (src/archlab/training/sft_export.py:24-40,219-244).
+    """
     from safetensors.torch import load_file, save_file
 
     out = Path(out_dir)
     out.mkdir(parents=True, exist_ok=True)
+    identity = None
+    if tokenizer_dir is not None:
+        identity = tokenizer_identity(tokenizer_dir)
+        if tokenizer_identity_sha256 is not None and identity != tokenizer_identity_sha256:
+            raise ValueError("the tokenizer directory is not the tokenizer the checkpoint was trained with")
+        vocab = config.get("vocab_size")
+        size = tokenizer_vocab_size(tokenizer_dir)
+        if vocab is not None and size is not None and size > vocab:
+            raise ValueError(f"tokenizer has {size} entries, the model's embedding only {vocab}")
+        for name in _present_assets(tokenizer_dir):
+            shutil.copyfile(Path(tokenizer_dir) / name, out / name)
     tensors = {k: v.detach().contiguous().cpu() for k, v in state.items()}
     (out / "config.json").write_text(json.dumps(config, indent=2, sort_keys=True))
     save_file(tensors, str(out / "model.safetensors"), metadata={"format": "pt"})
@@ -160,8 +179,40 @@ def export_hf(out_dir, state: dict[str, torch.Tensor], config: dict, *, export_f
              if p.is_file() and p.name != "EXPORT.json"}
     receipt = {"format": export_format, "state_sha256": digest, "files": files, "tensor_count": len(tensors),
                "lineage": lineage or {}}
+    if identity is not None:
+        receipt["tokenizer_identity_sha256"] = identity
     atomic_write_json(out / "EXPORT.json", receipt)
     return receipt
+
+
+TOKENIZER_ASSETS = ("tokenizer.json", "tokenizer.model", "tokenizer_config.json", "special_tokens_map.json", "added_tokens.json",
+                    "vocab.json", "merges.txt", "chat_template.jinja", "generation_config.json")
+
+
+def _present_assets(directory) -> list[str]:
+    names = [n for n in TOKENIZER_ASSETS if (Path(directory) / n).is_file()]
+    if not {"tokenizer.json", "tokenizer.model"} & set(names):
+        raise ValueError("a tokenizer directory needs tokenizer.json or tokenizer.model")
+    return names
+
+
+def tokenizer_identity(directory) -> str:
+    """One digest over the names and contents of the tokenizer's files, independent of where they are stored."""
+    h = hashlib.sha256()
+    for name in _present_assets(directory):
+        h.update(name.encode() + b"\0" + bytes.fromhex(sha256_file(Path(directory) / name)))
+    return h.hexdigest()
+
+
+def tokenizer_vocab_size(directory) -> int | None:
+    """Highest token id + 1 of a ``tokenizer.json`` (vocabulary and added tokens); None for other tokenizer kinds."""
+    path = Path(directory) / "tokenizer.json"
+    if not path.is_file():
+        return None
+    body = json.loads(path.read_text())
+    ids = [*body.get("model", {}).get("vocab", {}).values()] if isinstance(body.get("model", {}).get("vocab"), dict) else []
+    ids += [t["id"] for t in body.get("added_tokens", [])]
+    return max(ids) + 1 if ids else None
 
 
 def verify_hf_export(out_dir) -> dict:

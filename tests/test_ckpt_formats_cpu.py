@@ -129,3 +129,33 @@ def test_run_receipts(tmp_path):
     f.finish(error=RuntimeError("CUDA out of memory"))
     failed = json.loads((tmp_path / "b" / "FAILED.json").read_text())
     assert "out of memory" in failed["error"] and failed["classification"]
+
+
+def test_export_carries_the_tokenizer_and_checks_its_identity(tmp_path):
+    import json
+
+    import pytest
+    import torch
+
+    from archlab_b200.ckpt import formats
+
+    tok = tmp_path / "tok"
+    tok.mkdir()
+    (tok / "tokenizer.json").write_text(json.dumps({"model": {"vocab": {"a": 0, "b": 1}}, "added_tokens": [{"id": 5, "content": "<eod>"}]}))
+    (tok / "tokenizer_config.json").write_text("{}")
+    (tok / "unrelated.bin").write_bytes(b"x")
+    identity = formats.tokenizer_identity(tok)
+    assert formats.tokenizer_vocab_size(tok) == 6
+    state = {"w": torch.ones(2, 2)}
+    receipt = formats.export_hf(tmp_path / "out", state, {"vocab_size": 8}, tokenizer_dir=tok, tokenizer_identity_sha256=identity)
+    assert receipt["tokenizer_identity_sha256"] == identity
+    assert {"tokenizer.json", "tokenizer_config.json"} <= set(receipt["files"]) and "unrelated.bin" not in receipt["files"]
+    assert formats.tokenizer_identity(tmp_path / "out") == identity           # the export is self-contained
+    formats.verify_hf_export(tmp_path / "out")
+    with pytest.raises(ValueError, match="not the tokenizer"):
+        formats.export_hf(tmp_path / "o2", state, {"vocab_size": 8}, tokenizer_dir=tok, tokenizer_identity_sha256="0" * 64)
+    with pytest.raises(ValueError, match="embedding only"):
+        formats.export_hf(tmp_path / "o3", state, {"vocab_size": 4}, tokenizer_dir=tok)
+    (tok / "tokenizer.json").unlink()
+    with pytest.raises(ValueError, match="needs tokenizer.json"):
+        formats.export_hf(tmp_path / "o4", state, {"vocab_size": 8}, tokenizer_dir=tok)
