@@ -94,23 +94,47 @@ class StreamAdapter(nn.Module):
                         nn.init.zeros_(mod.bias)
             nn.init.zeros_(self.output.weight)
 
+    def project(self, x: torch.Tensor, offset: int = 0):
+        """Normalised, rotated queries and keys and the values of ``x`` [B, T, W] whose first token sits at absolute
+        position ``offset`` (the incremental serving form projects one chunk at a time).  The ``normal`` arm folds its
+        widening projections into its single key / value stream here."""
+        c = self.c
+        B, T, _ = x.shape
+        rot = int(c.head_dim * c.rotary_fraction) // 2 * 2
+        cos, sin = rope_tables(T, max(rot, 2), c.rope_theta, x.device, offset=offset)
+        rope = (lambda t: apply_rope(t, cos, sin, rot_dim=rot)) if rot else (lambda t: t)
+        q = rope(self.q_norm(self.q(x).view(B, T, c.heads, c.head_dim)))
+        ks = [rope(n(k(x).view(B, T, c.kv_heads, c.head_dim))) for k, n in zip(self.keys, self.k_norms)]
+        vs = [v(x).view(B, T, c.kv_heads, c.head_dim) for v in self.values]
+        if c.mechanism == "normal":
+            ek, ev = self.extra(x).view(B, T, 2, c.kv_heads, c.head_dim).unbind(2)     # the matched parameters widen K and V
+            ks, vs = [ks[0] + rope(self.k_norms[0](ek))], [vs[0] + ev]
+        return q, ks, vs
+
+    def attend(self, q, ks, vs):
+        """Windowed core of the ``simplicial`` and ``normal`` arms; keys may be longer than queries (cached prefix
+        first): the queries are the LAST ``q.shape[1]`` positions of the key sequence."""
+        c, T, S = self.c, q.shape[1], ks[0].shape[1]
+        if S != T:                                                             # left-pad queries; their rows are dropped below
+            q = torch.cat([q.new_zeros(q.shape[0], S - T, *q.shape[2:]), q], dim=1)
+        if c.mechanism == "simplicial":
+            w2 = min(S, c.long_window)
+            y = sx.simplicial_attention(q, ks[0], ks[1], vs[0], vs[1], min(c.short_window, w2), w2)
+        else:
+            y = local_attention.local_attention(q, ks[0], vs[0], min(S, c.long_window))
+        return y[:, S - T:]
+
+    def finish(self, x, y):
+        return self.output(y.reshape(x.shape[0], x.shape[1], -1).to(x.dtype) * torch.sigmoid(self.output_gate(x)))
+
     def branch(self, x: torch.Tensor) -> torch.Tensor:
         c, m = self.c, self.c.mechanism
         B, T, _ = x.shape
         if m == "mixer":
             return self.output(F.silu(self.gate_proj(x)) * self.up_proj(x))
-        rot = int(c.head_dim * c.rotary_fraction) // 2 * 2
-        cos, sin = rope_tables(T, max(rot, 2), c.rope_theta, x.device)
-        rope = (lambda t: apply_rope(t, cos, sin, rot_dim=rot)) if rot else (lambda t: t)
-        q = rope(self.q_norm(self.q(x).view(B, T, c.heads, c.head_dim)))
-        ks = [rope(n(k(x).view(B, T, c.kv_heads, c.head_dim))) for k, n in zip(self.keys, self.k_norms)]
-        vs = [v(x).view(B, T, c.kv_heads, c.head_dim) for v in self.values]
-        if m == "simplicial":
-            w2 = min(T, c.long_window)
-            y = sx.simplicial_attention(q, ks[0], ks[1], vs[0], vs[1], min(c.short_window, w2), w2)
-        elif m == "normal":
-            ek, ev = self.extra(x).view(B, T, 2, c.kv_heads, c.head_dim).unbind(2)     # the matched parameters widen K and V
-            y = local_attention.local_attention(q, ks[0] + rope(self.k_norms[0](ek)), vs[0] + ev, min(T, c.long_window))
+        q, ks, vs = self.project(x)
+        if m in ("simplicial", "normal"):
+            y = self.attend(q, ks, vs)
         elif m == "linsimp":
             y = linsimp.linsimp_attention(q, ks[0], ks[1], vs[0], vs[1], self.omega, window=min(T, c.short_window))
         else:
@@ -121,8 +145,7 @@ class StreamAdapter(nn.Module):
             g = -F.softplus(self.decay(x).float()).unsqueeze(-1).expand(B, T, c.heads, E)      # one decay per head, shared by its slices
             y = triadic.triadic_gdn_attention(F.normalize(q.float(), dim=-1), F.normalize(k.float(), dim=-1), v.float(), k2, q2, g,
                                               torch.sigmoid(self.beta(x).float())).to(x.dtype)
-        y = y.reshape(B, T, -1).to(x.dtype) * torch.sigmoid(self.output_gate(x))
-        return self.output(y)
+        return self.finish(x, y)
 
     def forward(self, packed: torch.Tensor) -> torch.Tensor:
         x, packed, w = self.read(packed)
