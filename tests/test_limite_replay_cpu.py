@@ -53,7 +53,7 @@ def test_replay_equals_the_plain_forward_and_retains_less():
     reference = {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None}
     model.zero_grad()
     got.backward(g)
-    assert all(torch.allclose(p.grad, reference[n], atol=1e-5, rtol=1e-5) for n, p in model.named_parameters() if n in reference)
+    assert all(float((p.grad - reference[n]).abs().max()) <= 1e-5 + 2e-6 * float(reference[n].abs().max()) for n, p in model.named_parameters() if n in reference)
     c = model.config
     assert retained_activation_bytes(c, 2, 48) < 0.25 * retained_activation_bytes(c, 2, 48, checkpoint_layers=False)
 
