@@ -243,13 +243,22 @@ class LimiteSimplicialAttention(nn.Module):
         w = native.qkv_proj.weight
         self.short_kv_delta = nn.Parameter(w.new_zeros(2 * native.kv_size, w.shape[1]))
 
-    def forward(self, h, value_embeds, cos, sin):
+    def operands(self, h, value_embeds, cos, sin):
+        """(q, k1, k2, v1, v2) of the tokens in ``h``; serving caches k1 / v1 (short) and k2 / v2 (long) per layer."""
         n, c = self.native, self.native.c
         q, k2, v2 = n.project(h, value_embeds, cos, sin)
         B, T = h.shape[:2]
         dk, dv = F.linear(h, self.short_kv_delta.to(h.dtype)).split(n.kv_size, -1)
         k1 = 1 + dk.view(B, T, c.num_key_value_heads, c.head_dim)
         v1 = 1 + dv.view(B, T, c.num_key_value_heads, c.head_dim)
+        return q, k1, k2, v1, v2
+
+    def forward(self, h, value_embeds, cos, sin):
+        return self.reduce(h, *self.operands(h, value_embeds, cos, sin))
+
+    def reduce(self, h, q, k1, k2, v1, v2):
+        n, c = self.native, self.native.c
+        T = h.shape[1]
         w2 = T if n.is_global else c.window_span
         w1 = min(self.conversion.short_window, w2)
         scaling, backend = self.conversion.scaling, self.conversion.backend
