@@ -132,6 +132,8 @@ class CheckpointAttachments:
         root = Path(spec["root"])
         attached, skipped = [], []
         with SingleWriterLock(self.state_path.with_suffix(".lock")):
+            if self.state_path.exists():                              # another instance may have attached checkpoints meanwhile
+                self.state = json.loads(self.state_path.read_text())
             done = self.state["attached"].setdefault(spec["run_id"], {})
             for checkpoint in self._candidates(root):
                 if checkpoint.name in done:
