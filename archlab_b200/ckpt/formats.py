@@ -215,6 +215,45 @@ def tokenizer_vocab_size(directory) -> int | None:
     return max(ids) + 1 if ids else None
 
 
+COPY_MARKER = "EXPORT_COPY_COMPLETE.json"
+
+
+def valid_hf_export(path) -> bool:
+    """What a loader needs at least: configuration, tokenizer and weights."""
+    path = Path(path)
+    return (path / "config.json").is_file() and ((path / "tokenizer.json").is_file() or (path / "tokenizer.model").is_file()) and (
+        any(path.glob("*.safetensors")) or any(path.glob("pytorch_model*.bin")))
+
+
+def copy_export(source, output) -> dict:
+    """Copies a complete export to storage that supports neither rename nor metadata copies (object-store mounts): plain
+    file copies, each re-hashed at the destination, then ``EXPORT_COPY_COMPLETE.json`` LAST with the per-file manifest.  A
+    destination that is valid and carries the marker is left alone; one without the marker is copied again
+    (src/archlab/megatron/export_eval.py:112-139)."""
+    source, output = Path(source), Path(output)
+    marker = output / COPY_MARKER
+    if valid_hf_export(output) and marker.is_file():
+        return json.loads(marker.read_text())
+    if not valid_hf_export(source):
+        raise RuntimeError(f"the source export is incomplete: {source}")
+    output.mkdir(parents=True, exist_ok=True)
+    manifest = []
+    for src in sorted(f for f in source.rglob("*") if f.is_file()):
+        rel = src.relative_to(source)
+        dst = output / rel
+        dst.parent.mkdir(parents=True, exist_ok=True)
+        shutil.copyfile(src, dst)
+        digest = sha256_file(src)
+        if sha256_file(dst) != digest:
+            raise RuntimeError(f"export copy hash mismatch: {rel}")
+        manifest.append({"path": str(rel), "bytes": src.stat().st_size, "sha256": digest})
+    if not valid_hf_export(output):
+        raise RuntimeError(f"the copied export is incomplete: {output}")
+    body = {"source": str(source), "files": manifest}
+    marker.write_text(json.dumps(body, sort_keys=True) + "\n")
+    return body
+
+
 def verify_hf_export(out_dir) -> dict:
     from safetensors.torch import load_file
 

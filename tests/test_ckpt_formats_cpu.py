@@ -159,3 +159,31 @@ def test_export_carries_the_tokenizer_and_checks_its_identity(tmp_path):
     (tok / "tokenizer.json").unlink()
     with pytest.raises(ValueError, match="needs tokenizer.json"):
         formats.export_hf(tmp_path / "o4", state, {"vocab_size": 8}, tokenizer_dir=tok)
+
+
+def test_export_copy_is_verified_and_marked_last(tmp_path):
+    import json
+
+    import pytest
+    import torch
+
+    from archlab_b200.ckpt import formats
+
+    tok = tmp_path / "tok"
+    tok.mkdir()
+    (tok / "tokenizer.json").write_text(json.dumps({"model": {"vocab": {"a": 0}}}))
+    formats.export_hf(tmp_path / "export", {"w": torch.ones(2, 2)}, {"vocab_size": 4}, tokenizer_dir=tok)
+    body = formats.copy_export(tmp_path / "export", tmp_path / "bulk" / "export")
+    names = {f["path"] for f in body["files"]}
+    assert {"config.json", "tokenizer.json", "model.safetensors", "EXPORT.json"} <= names
+    assert json.loads((tmp_path / "bulk" / "export" / formats.COPY_MARKER).read_text()) == body
+    formats.verify_hf_export(tmp_path / "bulk" / "export")
+    (tmp_path / "export" / "config.json").write_text("{}")                          # a later change of the source is not picked up:
+    assert formats.copy_export(tmp_path / "export", tmp_path / "bulk" / "export") == body      # the marked copy is final
+    (tmp_path / "bulk" / "export" / formats.COPY_MARKER).unlink()                  # an unmarked destination is copied again
+    again = formats.copy_export(tmp_path / "export", tmp_path / "bulk" / "export")
+    assert (tmp_path / "bulk" / "export" / "config.json").read_text() == "{}" and again != body
+    (tmp_path / "partial").mkdir()
+    (tmp_path / "partial" / "config.json").write_text("{}")
+    with pytest.raises(RuntimeError, match="source export is incomplete"):
+        formats.copy_export(tmp_path / "partial", tmp_path / "bulk" / "partial")
