@@ -126,9 +126,11 @@ def _publish(scratch: Path, destination: Path) -> None:
 
 
 def run_task(root, task_id: str, rows: Iterable[dict], render: Callable[[dict], str | None], tokenizer, *, eod: int,
-             group_of: Callable[[dict], str] = lambda row: str(row.get("id", "")), scratch=None) -> dict:
+             group_of: Callable[[dict], str] = lambda row: str(row.get("id", "")), scratch=None,
+             meta_of: Callable[[dict], dict] | None = None) -> dict:
     """Prepares one task.  ``rows`` yields exactly the task's row range; ``render`` returns the document text or None to
-    exclude the row (excluded rows are counted, so coverage stays checkable)."""
+    exclude the row (excluded rows are counted, so coverage stays checkable).  ``meta_of(row)`` adds fields to the
+    document's metadata line (a problem hash for later overlap audits, a source id)."""
     root = Path(root)
     contract = Contract.load(root)
     task = contract.task(task_id)
@@ -151,7 +153,7 @@ def run_task(root, task_id: str, rows: Iterable[dict], render: Callable[[dict], 
         p = parts[side]
         p["tokens"].extend(ids)
         p["ends"].append(len(p["tokens"]))
-        p["meta"].append({"row": task["row_start"] + offset, "tokens": len(ids)})
+        p["meta"].append({**(meta_of(row) if meta_of else {}), "row": task["row_start"] + offset, "tokens": len(ids)})
     if seen != task["rows"]:
         shutil.rmtree(work, ignore_errors=True)
         raise ValueError(f"task {task_id} expected {task['rows']} rows, the source gave {seen}")
