@@ -99,14 +99,23 @@ def forward_cached(model: GPT, idx: torch.Tensor, cache: KVCache) -> torch.Tenso
     return cfg.logit_softcap * torch.tanh(logits / cfg.logit_softcap)
 
 
-def sample_next(logits: torch.Tensor, temperature: float, top_k: int | None, rng) -> torch.Tensor:
-    """logits [B, V] -> token ids [B, 1]; temperature 0 is greedy."""
+def sample_next(logits: torch.Tensor, temperature: float, top_k: int | None, rng, top_p: float = 1.0) -> torch.Tensor:
+    """logits [B, V] -> token ids [B, 1]; temperature 0 is greedy.  ``top_p`` < 1 keeps the smallest set of most probable
+    tokens whose mass reaches ``top_p`` (the token that crosses the threshold is kept, so the set is never empty).
+    Non-finite logits are an error rather than a sample."""
+    if not torch.isfinite(logits).all():
+        raise RuntimeError("sampling logits contain non-finite values")
     if temperature <= 0:
         return logits.argmax(-1, keepdim=True)
     if top_k:
         kth = logits.topk(min(top_k, logits.size(-1)), dim=-1).values[:, -1:]
         logits = logits.masked_fill(logits < kth, float("-inf"))
-    return torch.multinomial(F.softmax(logits / temperature, dim=-1), 1, generator=rng)
+    probabilities = F.softmax(logits / temperature, dim=-1)
+    if top_p < 1.0:
+        ordered, index = probabilities.sort(descending=True, dim=-1)
+        ordered = ordered.masked_fill(ordered.cumsum(-1) - ordered > top_p, 0.0)       # mass BEFORE the token already exceeds top_p
+        return index.gather(-1, torch.multinomial(ordered, 1, generator=rng))
+    return torch.multinomial(probabilities, 1, generator=rng)
 
 
 class Engine:
@@ -117,7 +126,7 @@ class Engine:
 
     @torch.no_grad()
     def generate(self, tokens: list[int], *, num_samples: int = 1, max_tokens: int = 64, temperature: float = 1.0,
-                 top_k: int | None = None, seed: int = 42, stop_tokens: tuple[int, ...] = ()):
+                 top_k: int | None = None, seed: int = 42, stop_tokens: tuple[int, ...] = (), top_p: float = 1.0):
         """Yields ``(column, done)`` per step: ``column[r]`` is the token sample ``r`` produced (None once it has
         stopped) and ``done[r]`` whether it has stopped.  The prompt is prefilled once and shared by all samples."""
         model = self.model
@@ -133,7 +142,7 @@ class Engine:
         done = [False] * num_samples
         try:
             for _ in range(max_tokens):
-                nxt = sample_next(logits, temperature, top_k, rng)
+                nxt = sample_next(logits, temperature, top_k, rng, top_p)
                 column = []
                 for r, t in enumerate(nxt[:, 0].tolist()):
                     column.append(None if done[r] else t)
@@ -195,7 +204,7 @@ def answer_tickets(front, engine: "Engine", tokenizer, *, stop=None, idle_timeou
                 raise ValueError("the conversation does not fit the model's context")
             reply, shown = [], ""
             for column, _ in engine.generate(prompt, max_tokens=min(req["max_tokens"], room), temperature=req["temperature"],
-                                             top_k=top_k, seed=req["seed"] % (2 ** 63), stop_tokens=(end,)):
+                                             top_k=top_k, seed=req["seed"] % (2 ** 63), stop_tokens=(end,), top_p=req.get("top_p", 1.0)):
                 if column[0] is None or column[0] == end:
                     continue
                 reply.append(column[0])

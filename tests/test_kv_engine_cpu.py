@@ -132,3 +132,20 @@ def test_streamed_reply_equals_the_whole_reply():
     t.join(10)
     front.server.shutdown()
     assert served == 2 and got["last"] == "[DONE]" and "".join(got["pieces"]) == got["whole"]
+
+
+def test_nucleus_sampling_keeps_the_smallest_sufficient_set():
+    import pytest
+    import torch
+
+    from archlab_b200.serve.kv_engine import sample_next
+
+    logits = torch.log(torch.tensor([[0.5, 0.3, 0.15, 0.05]]))
+    rng = torch.Generator().manual_seed(0)
+    draws = {int(sample_next(logits, 1.0, None, rng, top_p=0.7)) for _ in range(200)}
+    assert draws == {0, 1}                                     # 0.5 alone is short of 0.7; 0.5 + 0.3 reaches it
+    assert {int(sample_next(logits, 1.0, None, rng, top_p=0.4)) for _ in range(50)} == {0}
+    assert {int(sample_next(logits, 1.0, None, rng, top_p=1.0)) for _ in range(400)} == {0, 1, 2, 3}
+    assert int(sample_next(logits, 0.0, None, None, top_p=0.1)) == 0
+    with pytest.raises(RuntimeError, match="non-finite"):
+        sample_next(torch.tensor([[0.0, float("nan")]]), 1.0, None, rng)
