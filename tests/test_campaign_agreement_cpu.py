@@ -5,7 +5,7 @@ import json
 import pytest
 
 from archlab_b200.contracts.campaigns import TEN_M_SEEDS, TEN_M_VARIANTS_BY_NAME
-from archlab_b200.services import campaign_compare as cc
+from archlab_b200.services import campaign_agreement as cc
 
 
 def row(backend, variant, seed, bpb, tps, steady=None):
