@@ -16,29 +16,40 @@ import yaml
 from .contracts.experiment import compose_trainer, read_experiment
 from .contracts.substrate import atomic_write_json
 
+ACTIONS = ("resolve", "qualify", "train")
 
-def main(argv=None) -> int:
-    parser = argparse.ArgumentParser(prog="archlab")
-    parser.add_argument("action", choices=("resolve", "qualify", "train"))
-    parser.add_argument("recipe", type=Path)
-    parser.add_argument("--config-root", type=Path, default=None,
-                        help="directory holding the trainer configuration trees (default: packaged)")
-    parser.add_argument("--output", type=Path, required=True)
-    parser.add_argument("--overlay", type=Path, action="append", default=[])
-    parser.add_argument("--skip-gates", action="store_true", help="qualify: readiness checks only")
-    parser.add_argument("overrides", nargs="*")
-    args = parser.parse_intermixed_args(argv)
+
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(prog="archlab", description="Resolve, qualify or launch one experiment recipe")
+    p.add_argument("action", choices=ACTIONS)
+    p.add_argument("recipe", type=Path)
+    p.add_argument("--output", type=Path, required=True)
+    p.add_argument("--overlay", type=Path, action="append", default=[])
+    p.add_argument("--config-root", type=Path, default=None, help="directory holding the trainer configuration trees (default: packaged)")
+    p.add_argument("--skip-gates", action="store_true", help="qualify: readiness checks only")
+    p.add_argument("overrides", nargs="*")
+    return p
+
+
+def resolve(args):
+    """Writes the resolved trainer configuration and the typed experiment; returns both."""
     experiment = read_experiment(args.recipe, args.overrides, overlays=args.overlay)
     config = compose_trainer(experiment, args.config_root)
     args.output.mkdir(parents=True, exist_ok=True)
     (args.output / "resolved.yaml").write_text(yaml.safe_dump(config, sort_keys=False))
     atomic_write_json(args.output / "experiment.json", asdict(experiment))
+    return experiment, config
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_intermixed_args(argv)
+    experiment, config = resolve(args)
     if args.action == "resolve":
         return 0
     from .train.qualification import qualify
 
-    result = qualify(experiment, config, args.output, run_gates=not args.skip_gates)
-    if not result["passed"]:
+    verdict = qualify(experiment, config, args.output, run_gates=not args.skip_gates)
+    if not verdict["passed"]:
         print("Qualification blocked; see", args.output / "qualification.json")
         return 1
     if args.action == "train":

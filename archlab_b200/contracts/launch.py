@@ -1,6 +1,9 @@
-"""Launch plans: an inspectable argv + environment + provenance bundle
-(src/archlab/launch.py:11-57).  ``env:NAME`` tokens render as ``"${NAME}"`` so a committed plan
-stays free of machine paths."""
+"""Launch plans: what a backend would run, kept inspectable -- the argument vector, the environment it adds and the
+provenance that explains both (src/archlab/launch.py:11-57).
+
+Arguments of the form ``env:NAME`` stand for a value the launching machine supplies; they render as ``"${NAME}"`` in
+the shell form, so a committed plan never contains a machine path, and every other token is shell-quoted.
+"""
 from __future__ import annotations
 
 import json
@@ -10,12 +13,15 @@ from collections.abc import Mapping
 from dataclasses import dataclass, field
 from typing import Any
 
-_ENV_TOKEN = re.compile(r"^env:([A-Z][A-Z0-9_]*)$")
+ENV_REFERENCE = re.compile(r"env:([A-Z][A-Z0-9_]*)")
+BACKENDS = {"speedrun": "SpeedrunBackend", "megatron": "MeshBackend"}      # single-mesh data parallel / TP-PP-CP-EP mesh
 
 
 def shell_token(token: str) -> str:
-    m = _ENV_TOKEN.fullmatch(token)
-    return f'"${{{m.group(1)}}}"' if m else shlex.quote(token)
+    reference = ENV_REFERENCE.fullmatch(token)
+    if reference is None:
+        return shlex.quote(token)
+    return '"${' + reference.group(1) + '}"'
 
 
 @dataclass(frozen=True)
@@ -25,24 +31,23 @@ class LaunchPlan:
     env: Mapping[str, str] = field(default_factory=dict)
     metadata: Mapping[str, Any] = field(default_factory=dict)
 
+    def environment_assignments(self) -> list[str]:
+        return [name + "=" + shlex.quote(self.env[name]) for name in sorted(self.env)]
+
     def shell(self) -> str:
-        prefix = [f"{k}={shlex.quote(v)}" for k, v in sorted(self.env.items())]
-        return " ".join([*prefix, *(shell_token(t) for t in self.argv)])
+        """One line: sorted ``NAME=value`` assignments, then the command."""
+        return " ".join(self.environment_assignments() + [shell_token(t) for t in self.argv])
 
     def as_dict(self) -> dict[str, Any]:
-        return {"backend": self.backend, "argv": list(self.argv), "env": dict(self.env),
-                "metadata": dict(self.metadata)}
+        return dict(backend=self.backend, argv=[*self.argv], env={**self.env}, metadata={**self.metadata})
 
     def json(self) -> str:
-        return json.dumps(self.as_dict(), indent=2, sort_keys=True) + "\n"
+        return json.dumps(self.as_dict(), sort_keys=True, indent=2) + "\n"
 
 
 def get_backend(name: str):
-    """``speedrun`` (single-mesh data parallel) or ``megatron`` (TP/PP/CP/EP mesh) launch renderers."""
+    if name not in BACKENDS:
+        raise ValueError(f"unknown backend: {name}")
     from ..train import backends
 
-    if name == "speedrun":
-        return backends.SpeedrunBackend()
-    if name == "megatron":
-        return backends.MeshBackend()
-    raise ValueError(f"unknown backend: {name}")
+    return getattr(backends, BACKENDS[name])()
