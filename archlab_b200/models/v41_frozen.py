@@ -132,3 +132,40 @@ def freeze_backbone(model: V41LM, *, carry_coefficients_bf16: bool = False) -> d
     return {"frozen_linears": linears, "frozen_hyper_connections": mixes, "coefficients_carried_as": "bf16-in-fp32" if carry_coefficients_bf16 else "fp32",
             "linear_backward": "dX = dY @ rounded(W); input not saved", "expert_sum": "fp32, rounded once" if sums_ok else "unverified",
             "parameters_preserved": True, "trainable_parameters": 0}
+
+
+class FrozenHeadCrossEntropy(torch.autograd.Function):
+    """Summed cross entropy through a FROZEN output head, chunk by chunk over tokens: the forward computes each chunk's
+    logits, its loss and -- because the head has no gradient of its own -- the chunk's d(loss)/d(hidden) right away,
+    then drops the logits.  Nothing vocabulary-sized survives the forward, and the backward is one multiplication by
+    the incoming scalar.  Labels of -100 are ignored; a batch without any target still yields a zero gradient of the
+    right shape, so every rank keeps taking part in the backward collectives
+    (src/archlab/automodel/deepseek_v41_loss.py:1-40)."""
+
+    @staticmethod
+    def forward(ctx, hidden, labels, weight, chunk_tokens):
+        if weight.requires_grad:
+            raise ValueError("the output head must be frozen")
+        flat, targets = hidden.reshape(-1, hidden.shape[-1]), labels.reshape(-1)
+        grad = torch.zeros_like(flat)
+        total = torch.zeros((), dtype=torch.float32, device=hidden.device)
+        for start in range(0, flat.shape[0], chunk_tokens):
+            y = targets[start:start + chunk_tokens]
+            keep = y != -100
+            if not bool(keep.any()):
+                continue
+            logits = F.linear(flat[start:start + chunk_tokens][keep], weight).float()
+            logp = torch.log_softmax(logits, -1)
+            total += -logp.gather(-1, y[keep, None]).sum()
+            dlogits = logp.exp_()
+            dlogits.scatter_add_(-1, y[keep, None], torch.full_like(dlogits[:, :1], -1.0))
+            rows = torch.nonzero(keep, as_tuple=True)[0] + start
+            grad[rows] = (dlogits.to(weight.dtype) @ weight).to(grad.dtype)
+        ctx.save_for_backward(grad)
+        ctx.shape = hidden.shape
+        return total
+
+    @staticmethod
+    def backward(ctx, upstream):
+        (grad,) = ctx.saved_tensors
+        return (grad * upstream.to(grad.dtype)).view(ctx.shape), None, None, None

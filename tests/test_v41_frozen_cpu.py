@@ -61,3 +61,24 @@ def test_frozen_backbone_trains_only_what_is_attached(fp8):
     assert all(p.grad is None for p in model.parameters())
     with pytest.raises(ValueError, match="already frozen"):
         freeze_backbone(model)
+
+
+@pytest.mark.parametrize("chunk", [1, 3, 128])
+def test_frozen_head_cross_entropy_matches_pytorch(chunk):
+    from archlab_b200.models.v41_frozen import FrozenHeadCrossEntropy
+
+    torch.manual_seed(3)
+    hidden = torch.randn(2, 5, 7, requires_grad=True)
+    twin = hidden.detach().clone().requires_grad_()
+    weight, labels = torch.randn(23, 7), torch.randint(0, 23, (2, 5))
+    labels[:, 1] = -100
+    got = FrozenHeadCrossEntropy.apply(hidden, labels, weight, chunk)
+    want = torch.nn.functional.cross_entropy((twin @ weight.T).flatten(0, 1), labels.flatten(), reduction="sum")
+    (2 * got).backward(), (2 * want).backward()
+    assert torch.allclose(got, want, atol=1e-5) and torch.allclose(hidden.grad, twin.grad, atol=1e-5)
+    empty = torch.randn(1, 5, 7, requires_grad=True)
+    loss = FrozenHeadCrossEntropy.apply(empty, torch.full((1, 5), -100), weight, 3)
+    loss.backward()
+    assert float(loss.detach()) == 0 and torch.equal(empty.grad, torch.zeros_like(empty))
+    with pytest.raises(ValueError, match="frozen"):
+        FrozenHeadCrossEntropy.apply(hidden, labels, weight.clone().requires_grad_(), 3)
