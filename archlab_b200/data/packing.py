@@ -80,3 +80,29 @@ def replicated_global_batch(packer: BestFitPacker, rank: int, world_size: int):
         x = torch.cat([x, x[:pad]], dim=0)
         y = torch.cat([y, torch.full_like(y[:pad], -1)], dim=0)
     return x[rank * per:(rank + 1) * per], y[rank * per:(rank + 1) * per], state
+
+
+def balanced_slice(global_batch: int, rank: int, world_size: int) -> tuple[int, int, int]:
+    """``(start, active, local_size)`` of one rank's share of an exact global batch.  Every rank gets the same static
+    shape ``ceil(global / world)``; when the world does not divide the batch the first ``global % world`` ranks hold one
+    more ACTIVE row than the rest and the others carry one ignored row, so no rank idles on several padded rows while
+    another is full (192 sequences on 15 ranks: twelve ranks with 13 active rows, three with 12, all of shape 13).
+    Active rows stay contiguous in the canonical one-rank stream (src/archlab/speedrun/dataloader.py:286-306)."""
+    if global_batch <= 0:
+        raise ValueError("global_batch must be positive")
+    if world_size <= 0 or not 0 <= rank < world_size:
+        raise ValueError("rank must lie inside a positive world size")
+    base, extra = divmod(global_batch, world_size)
+    return rank * base + min(rank, extra), base + (rank < extra), base + (extra > 0)
+
+
+def balanced_global_batch(packer: BestFitPacker, rank: int, world_size: int):
+    """Like ``replicated_global_batch`` with the balanced split: ignored rows repeat the rank's first row with ``-1``
+    targets, so shapes are static and the loss sees exactly the global batch."""
+    x, y, state = packer.next_batch()
+    start, active, local = balanced_slice(x.size(0), rank, world_size)
+    xs, ys = x[start:start + active], y[start:start + active]
+    if active < local:
+        xs = torch.cat([xs, xs[:local - active]], dim=0)
+        ys = torch.cat([ys, torch.full_like(ys[:local - active], -1)], dim=0)
+    return xs, ys, {**state, "active_rows": active}
