@@ -31,6 +31,7 @@ from typing import Callable, Protocol
 import torch
 
 from ..contracts.substrate import atomic_write_json
+from ..services.code_verdict import RewardInfrastructureError
 from .grpo import GRPOConfig, grpo_step
 
 
@@ -207,7 +208,7 @@ class AgenticGRPO:
         self.next_prompt = 0
         self.evidence_dir = Path(evidence_dir) if evidence_dir is not None else None
         self.totals = {"completed_verifiers": 0, "tool_calls": 0, "masked_observation_tokens": 0, "truncated_trajectories": 0,
-                       "reward_contrast_groups": 0, "wasted_groups": 0, "dropped_stale_groups": 0}
+                       "reward_contrast_groups": 0, "wasted_groups": 0, "dropped_stale_groups": 0, "infrastructure_failed_groups": 0}
         self.history: list[dict] = []
 
     def collect(self, groups: int) -> None:
@@ -215,8 +216,15 @@ class AgenticGRPO:
             group_id, prompt = self.prompts(self.next_prompt)
             self.next_prompt += 1
             group = self.actor.rollout_group(group_id, prompt)
-            for t in group:
-                t.reward = float(self.verifier(t))
+            try:
+                rewards = [float(self.verifier(t)) for t in group]
+            except RewardInfrastructureError:
+                # the verifier did not reach a verdict for some member: nothing of the group is learned from (a group with a
+                # member missing would shift its own baseline), and the failure is counted, not hidden as a zero reward
+                self.totals["infrastructure_failed_groups"] += 1
+                continue
+            for t, reward in zip(group, rewards):
+                t.reward = reward
                 if not math.isfinite(t.reward):
                     raise ValueError(f"verifier returned a non-finite reward for {t.uid}")
                 self.totals["completed_verifiers"] += 1
@@ -254,7 +262,8 @@ class AgenticGRPO:
             **{k: self.totals[k] for k in ("completed_verifiers", "tool_calls", "masked_observation_tokens", "truncated_trajectories",
                                            "reward_contrast_groups")},
             "grad_norm": last["grad_norm"], "loss": last["loss"], "learner_steps": self.version, "consumed_rollout_uids": consumed,
-            "dropped_stale_groups": self.totals["dropped_stale_groups"], "wasted_groups": self.totals["wasted_groups"]})
+            "dropped_stale_groups": self.totals["dropped_stale_groups"], "wasted_groups": self.totals["wasted_groups"],
+            "infrastructure_failed_groups": self.totals["infrastructure_failed_groups"]})
 
     def run(self) -> list[dict]:
         for _ in range(self.loop.steps):

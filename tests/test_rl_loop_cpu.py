@@ -99,3 +99,35 @@ def test_contract_refusals():
                           rl.LoopConfig(steps=1), verifier=lambda t: float("nan"), prompts=lambda i: ("p", [1]))
     with pytest.raises(ValueError, match="non-finite reward"):
         loop.run()
+
+
+def test_groups_without_a_verdict_are_counted_and_not_learned_from(tmp_path):
+    import torch
+
+    from archlab_b200.services.code_verdict import RewardInfrastructureError
+    from archlab_b200.train import rl_loop as rl
+
+    src = open(rl.__file__).read()
+    assert "infrastructure_failed_groups" in src
+    calls = {"n": 0}
+
+    def verifier(t):
+        calls["n"] += 1
+        if t.uid.startswith("p1"):
+            raise RewardInfrastructureError("sandbox timeout")
+        return 1.0
+
+    class Stub:
+        def __init__(self):
+            self.totals = {"completed_verifiers": 0, "tool_calls": 0, "masked_observation_tokens": 0, "truncated_trajectories": 0,
+                           "reward_contrast_groups": 0, "wasted_groups": 0, "dropped_stale_groups": 0, "infrastructure_failed_groups": 0}
+            self.next_prompt, self.verifier, self.put = 0, verifier, []
+            self.prompts = lambda i: (f"p{i}", [1, 2])
+            self.actor = type("A", (), {"rollout_group": staticmethod(lambda gid, prompt: [type("T", (), {"uid": f"{gid}-{k}", "tool_calls": 0, "observation_tokens": 0,
+                                                                                                          "truncated": False, "reward": None})() for k in range(2)])})()
+            self.queue = type("Q", (), {"put": lambda _self, g: self.put.append(g)})()
+
+    stub = Stub()
+    rl.AgenticGRPO.collect(stub, 3)
+    assert stub.totals["infrastructure_failed_groups"] == 1 and len(stub.put) == 2 and stub.totals["completed_verifiers"] == 4
+    assert all(t.reward == 1.0 for g in stub.put for t in g)
