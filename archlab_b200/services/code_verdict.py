@@ -1,4 +1,4 @@
-"""When is a software-engineering reward a VERDICT, and when is it an accident of the infrastructure?
+"""When is a software-engineering reward a verdict, and when is it an accident of the infrastructure?
 
 An executable verifier applies the hidden test patch after the rollout and runs the test command; exit code 0 means the
 task is solved (reward 1), a small positive exit code means the tests ran and failed (reward 0).  Everything else is not

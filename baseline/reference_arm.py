@@ -36,7 +36,8 @@ def ensure_reference_tree() -> str | None:
     --target`` cannot produce it)."""
     pkg = os.path.join(REF_ROOT, "archlab")
     if not os.path.isdir(pkg):
-        src = os.environ.get("ARCHLAB_REFERENCE_SRC", "/root/reference/src/archlab")
+        # the reference checkout is expected beside the repository unless ARCHLAB_REFERENCE_SRC says otherwise
+        src = os.environ.get("ARCHLAB_REFERENCE_SRC", os.path.normpath(os.path.join(HERE, "..", "..", "reference", "src", "archlab")))
         if os.path.isdir(src):
             import shutil
 
