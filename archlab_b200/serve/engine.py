@@ -39,8 +39,42 @@ class Request:
         return len(self.tokens) >= self.max_new_tokens or (self.eos is not None and self.tokens and self.tokens[-1] == self.eos)
 
 
+@dataclass(frozen=True)
+class ServingSettings:
+    """What a deployment asks of the engine; ``validate_serving`` refuses what the paged simplicial path does not implement."""
+    tensor_parallel: int = 1
+    pipeline_parallel: int = 1
+    chunked_prefill: bool = False
+    prefix_caching: bool = False
+    cache_dtype: str = "auto"
+    speculative: bool = False
+    quantization: str | None = None
+
+
+def validate_serving(model: L.LimiteLM, settings: ServingSettings, *, short_window: int | None = None) -> None:
+    """The engine prefills one COMPLETE prompt per request and owns private, unquantised pages per request: tensor /
+    pipeline splits, chunked prefill, prefix sharing, quantised caches or weights and speculative decoding are refused
+    rather than silently ignored, and so is a model that is not converted in every layer or still carries adapters
+    (the reference states the same admission rules for its engine bridge: src/archlab/training/serving_conversion.py:19-46)."""
+    if settings.tensor_parallel != 1 or settings.pipeline_parallel != 1:
+        raise ValueError("converted serving runs on one GPU per replica (TP = PP = 1)")
+    if settings.chunked_prefill:
+        raise ValueError("converted serving admits one complete prompt at a time (no chunked prefill)")
+    if settings.prefix_caching or settings.cache_dtype not in ("auto", "bfloat16", "float16", "float32"):
+        raise ValueError("converted serving needs private, unquantised K/V pages")
+    if settings.quantization is not None or settings.speculative:
+        raise ValueError("converted serving does not admit quantisation or speculative decoding")
+    layers = [b.attn for b in model.layers]
+    if not all(isinstance(a, L.LimiteSimplicialAttention) for a in layers) or any(b.prelude is not None for b in model.layers):
+        raise ValueError("converted serving needs the attention replacement in every layer and no adapters")
+    if short_window is not None and any(a.conversion.short_window != short_window for a in layers):
+        raise ValueError(f"converted serving was qualified for short window {short_window}")
+
+
 class SimplicialServingEngine:
-    def __init__(self, model: L.LimiteLM, *, num_pages: int, max_batch: int = 64, max_seq_len: int = 4096):
+    def __init__(self, model: L.LimiteLM, *, num_pages: int, max_batch: int = 64, max_seq_len: int = 4096, settings: ServingSettings | None = None):
+        if settings is not None:
+            validate_serving(model, settings)
         if not all(isinstance(b.attn, L.LimiteSimplicialAttention) for b in model.layers):
             raise ValueError("the engine serves models whose attention layers were converted")
         if any(b.prelude is not None for b in model.layers):

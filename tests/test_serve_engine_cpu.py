@@ -34,3 +34,28 @@ def test_engine_matches_full_recomputation_and_recycles_pages():
     for rid, p in zip(ids, prompts):
         assert out[rid] == _greedy(m, p, 6), rid
     assert len(eng.free) == 4 and not eng.running and not eng.waiting
+
+
+def test_serving_admission_rules():
+    import pytest
+    import torch
+
+    from archlab_b200.models import limite as L
+    from archlab_b200.serve.engine import ServingSettings, SimplicialServingEngine, validate_serving
+
+    torch.manual_seed(0)
+    m = L.LimiteLM(L.LimiteConfig.tiny())
+    plain = L.LimiteLM(L.LimiteConfig.tiny())
+    L.replace_limite_attention(m, L.ConversionConfig(short_window=3, backend="reference"))
+    validate_serving(m, ServingSettings())
+    for settings, message in ((ServingSettings(tensor_parallel=2), "TP = PP = 1"), (ServingSettings(chunked_prefill=True), "chunked prefill"),
+                              (ServingSettings(prefix_caching=True), "unquantised"), (ServingSettings(cache_dtype="fp8"), "unquantised"),
+                              (ServingSettings(speculative=True), "speculative"), (ServingSettings(quantization="awq"), "quantisation")):
+        with pytest.raises(ValueError, match=message):
+            validate_serving(m, settings)
+    with pytest.raises(ValueError, match="qualified for short window"):
+        validate_serving(m, ServingSettings(), short_window=16)
+    with pytest.raises(ValueError, match="attention replacement in every layer"):
+        validate_serving(plain, ServingSettings())
+    with pytest.raises(ValueError, match="chunked prefill"):
+        SimplicialServingEngine(m, num_pages=2, settings=ServingSettings(chunked_prefill=True))
