@@ -106,3 +106,32 @@ def balanced_global_batch(packer: BestFitPacker, rank: int, world_size: int):
         xs = torch.cat([xs, xs[:local - active]], dim=0)
         ys = torch.cat([ys, torch.full_like(ys[:local - active], -1)], dim=0)
     return xs, ys, {**state, "active_rows": active}
+
+
+def tokenizing_loader(data_dir, tokenizer, batch_size: int, seq_len: int, *, split: str = "train", rank: int = 0, world: int = 1,
+                      buffer_size: int = 1000, resume_state: dict | None = None, bos_token: int | None = None):
+    """Parquet shards -> tokenizer -> best-fit packer, yielding ``(inputs, targets, state)``.
+
+    ``state`` = ``{"batch_index", "shard", "row_group", "epoch"}``: the batch cursor plus the position of the document
+    stream when the batch was cut (for logs and sanity checks).  Resuming is EXACT: the packer's buffer contents are a
+    function of the whole document stream, so ``resume_state`` replays the stream to ``batch_index`` (tokenising again,
+    discarding batches) instead of guessing the buffer from a file cursor; the first batch after a resume is the batch
+    that was in flight when the state was saved (src/archlab/speedrun/dataloader.py:154-276)."""
+    from .parquet_shards import document_batches
+
+    cursor = {"shard": 0, "row_group": 0, "epoch": 1}
+    if bos_token is None:
+        bos_token = getattr(tokenizer, "special", {}).get("<|bos|>") if hasattr(tokenizer, "special") else None
+
+    def documents():
+        for texts, (shard, group, epoch) in document_batches(data_dir, split, rank=rank, world=world):
+            cursor.update(shard=shard, row_group=group, epoch=epoch)
+            for text in texts:
+                yield tokenizer.encode(text)
+
+    packer = BestFitPacker(documents(), batch_size, seq_len, buffer_size=buffer_size, bos_token=bos_token)
+    if resume_state is not None:
+        packer.seek(int(resume_state["batch_index"]))
+    while True:
+        x, y, state = packer.next_batch()
+        yield x, y, {**state, **cursor}

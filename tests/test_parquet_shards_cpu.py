@@ -40,3 +40,27 @@ def test_cursor_resumes_after_the_consumed_row_group_and_epochs_repeat(tmp_path)
     assert cursors[:4] == [(0, 1, 1), (0, 3, 1), (1, 1, 1), (1, 3, 1)] and cursors[4] == (0, 1, 2)
     resumed = list(itertools.islice(document_batches(root, "train", rank=1, world=2, resume=cursors[2]), 4))
     assert [c for _, c in resumed] == cursors[3:7] and [t for t, _ in resumed] == [t for t, _ in full[3:7]]
+
+
+def test_tokenizing_loader_resumes_exactly(tmp_path):
+    import torch
+
+    from archlab_b200.data.packing import tokenizing_loader
+
+    root = corpus(tmp_path / "data", shards=3, groups=6, rows=3)
+
+    class Tok:
+        special = {"<|bos|>": 1}
+
+        def encode(self, text):
+            return [2 + (ord(c) % 23) for c in text]
+
+    make = lambda **kw: tokenizing_loader(root, Tok(), 2, 8, buffer_size=6, **kw)
+    run = make()
+    history = [next(run) for _ in range(7)]
+    assert all(bool((x[:, 0] == 1).all()) for x, _, _ in history) and history[4][2]["batch_index"] == 4
+    assert history[-1][2]["shard"] >= history[0][2]["shard"] and history[0][2]["epoch"] == 1
+    resumed = make(resume_state=history[4][2])
+    x, y, state = next(resumed)
+    assert torch.equal(x, history[4][0]) and torch.equal(y, history[4][1]) and state["batch_index"] == 4
+    assert torch.equal(next(resumed)[0], history[5][0])
