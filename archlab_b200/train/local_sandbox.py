@@ -156,3 +156,34 @@ class LocalSandbox:
 
     def __exit__(self, *exc):
         self.close()
+
+
+@dataclass(frozen=True)
+class ExecutionResult:
+    """Outcome of running one generated program (code-benchmark grading)."""
+    success: bool
+    stdout: str
+    stderr: str
+    error: str | None = None
+    timeout: bool = False
+    memory_exceeded: bool = False
+
+
+def execute_code(code: str, *, timeout: float = 5.0, memory_mb: int = 256, allow_unisolated: bool = False) -> ExecutionResult:
+    """Runs ``code`` (a complete program: solution plus its tests) in a fresh sandbox and classifies the outcome: success
+    means exit code 0 within the time and memory limits.  A timeout kills the whole process group; an exhausted address
+    space shows up as ``MemoryError`` and is reported as such rather than as a plain failure, so a grader can tell "wrong"
+    from "too expensive".  The sandbox (and its directory) does not outlive the call.  Same role as the reference's
+    generated-code executor (src/archlab/speedrun/execution.py:38-358), with the isolation described at the top of this
+    module instead of in-process function patching."""
+    isolation = strongest_isolation()
+    with LocalSandbox(cpu_seconds=max(1, int(timeout) + 1), memory_mb=memory_mb, wall_seconds=timeout, isolation=isolation,
+                      allow_unisolated=allow_unisolated or isolation != "rlimits") as box:
+        r = box.run_python(code)
+    if r.timed_out:
+        return ExecutionResult(False, r.stdout, r.stderr, "execution timed out", timeout=True)
+    if r.returncode == 0:
+        return ExecutionResult(True, r.stdout, r.stderr)
+    last = r.stderr.strip().splitlines()[-1] if r.stderr.strip() else f"exit code {r.returncode}"
+    memory = "MemoryError" in r.stderr
+    return ExecutionResult(False, r.stdout, r.stderr, "memory limit exceeded" if memory else last, memory_exceeded=memory)
