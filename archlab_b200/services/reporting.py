@@ -223,3 +223,45 @@ def main(argv=None) -> int:
 
 if __name__ == "__main__":
     raise SystemExit(main())
+
+
+# ---- runs with different batch sizes on one token axis ---------------------------------------------------------------
+def token_blocks(rows: list[dict], *, tokens_per_step: int, block_tokens: int, key: str = "loss") -> list[dict]:
+    """Means of ``key`` over COMPLETE blocks of ``block_tokens`` consumed tokens.  Two runs whose optimizer steps hold
+    different numbers of tokens become comparable point by point; a block with a missing step is left out rather than
+    averaged over fewer steps.  (The reference aligns TensorBoard scalars the same way:
+    src/archlab/reporting/learning_curves.py:16-50; here the source is the run's ``metrics.jsonl``.)"""
+    if block_tokens % tokens_per_step:
+        raise ValueError("a comparison block must hold a whole number of optimizer steps")
+    per_block = block_tokens // tokens_per_step
+    by_step = {int(r["step"]): r for r in rows if key in r and math.isfinite(r[key])}
+    if not by_step:
+        raise ValueError("no finite measurements")
+    points = []
+    for block in range(1, max(by_step) // per_block + 1):
+        steps = range((block - 1) * per_block + 1, block * per_block + 1)
+        if all(s in by_step for s in steps):
+            points.append({"block": block, "step": steps[-1], "tokens": block * block_tokens,
+                           key: sum(by_step[s][key] for s in steps) / per_block})
+    if not points:
+        raise ValueError("no complete token blocks")
+    return points
+
+
+def trailing_means(values: list[float], window: int) -> list[float]:
+    return [sum(values[max(0, i + 1 - window):i + 1]) / (i + 1 - max(0, i + 1 - window)) for i in range(len(values))]
+
+
+def aligned_curves(runs: dict[str, tuple[list[dict], int]], *, block_tokens: int, smoothing_blocks: int = 20, key: str = "loss") -> dict:
+    """``runs``: label -> (ledger rows, tokens per optimizer step).  Returns per label the block means and their trailing
+    mean, plus the differences against the first label at every token count all runs reached."""
+    curves = {}
+    for label, (rows, tokens_per_step) in runs.items():
+        points = token_blocks(rows, tokens_per_step=tokens_per_step, block_tokens=block_tokens, key=key)
+        smooth = trailing_means([p[key] for p in points], smoothing_blocks)
+        curves[label] = [{**p, "smoothed": s} for p, s in zip(points, smooth)]
+    first, *others = list(curves)
+    base = {p["tokens"]: p for p in curves[first]}
+    differences = {label: [{"tokens": p["tokens"], "delta": p[key] - base[p["tokens"]][key], "delta_smoothed": p["smoothed"] - base[p["tokens"]]["smoothed"]}
+                           for p in curves[label] if p["tokens"] in base] for label in others}
+    return {"block_tokens": block_tokens, "smoothing_blocks": smoothing_blocks, "curves": curves, "differences_against": first, "differences": differences}

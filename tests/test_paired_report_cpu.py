@@ -59,3 +59,24 @@ def test_paired_report_matches_updates_and_refuses_different_cursors(tmp_path):
     with pytest.raises(ValueError, match="paired learning_rate differs"):
         rp.paired_report({"base": str(tmp_path / "base"), "x": str(tmp_path / "other_lr")}, tmp_path / "r3", current_phase_only=True)
     assert rp.main(["--run", "base", str(tmp_path / "base"), "--run", "arm", str(tmp_path / "arm"), "--output", str(tmp_path / "r4")]) == 0
+
+
+def test_runs_with_different_batch_sizes_share_a_token_axis():
+    import pytest
+
+    from archlab_b200.services.reporting import aligned_curves, token_blocks, trailing_means
+
+    small = [{"step": s, "loss": 4.0 - 0.01 * s} for s in range(1, 41)]                     # 100 tokens per step
+    large = [{"step": s, "loss": 3.9 - 0.04 * s} for s in range(1, 11) if s != 7]           # 400 tokens per step, step 7 lost
+    a = token_blocks(small, tokens_per_step=100, block_tokens=800)
+    assert [p["tokens"] for p in a] == [800, 1600, 2400, 3200, 4000] and a[0]["loss"] == pytest.approx(4.0 - 0.01 * 4.5)
+    b = token_blocks(large, tokens_per_step=400, block_tokens=800)
+    assert [p["block"] for p in b] == [1, 2, 3, 5]                                            # block 4 (steps 7-8) is incomplete and left out
+    with pytest.raises(ValueError, match="whole number"):
+        token_blocks(small, tokens_per_step=300, block_tokens=800)
+    with pytest.raises(ValueError, match="no complete"):
+        token_blocks(small[:3], tokens_per_step=100, block_tokens=800)
+    assert trailing_means([1.0, 3.0, 5.0, 7.0], 2) == [1.0, 2.0, 4.0, 6.0]
+    out = aligned_curves({"small": (small, 100), "large": (large, 400)}, block_tokens=800, smoothing_blocks=2)
+    deltas = out["differences"]["large"]
+    assert [d["tokens"] for d in deltas] == [800, 1600, 2400, 4000] and all(d["delta"] < 0 for d in deltas) and out["differences_against"] == "small"
