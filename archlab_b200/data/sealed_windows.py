@@ -111,3 +111,68 @@ class SealedWindows:
         if count != int((labels != IGNORE).sum()) or count != w["targets"]:
             raise ValueError("assistant targets were lost or counted twice")
         return inputs.to(device), labels.to(device), count
+
+
+# ---- selecting a pilot with an EXACT supervised-token budget -----------------------------------------------------------
+def shifted_window_spans(spans: list, start: int, length: int, *, limit: int | None = None) -> list[list[int]]:
+    """Assistant TOKEN spans of a document -> half-open LABEL spans of the input window ``[start, start + length)``.
+
+    Label ``t`` of a window is token ``start + t + 1``; a token at document position p is therefore label ``p - start - 1``
+    and is supervised by the window whose inputs cover ``p - 1``.  Consecutive windows overlap by that one boundary token,
+    so no assistant token is lost or counted twice.  ``limit`` cuts the selection after that many targets (the last
+    window of a pilot stops exactly on the budget)."""
+    out, left, previous = [], limit, 0
+    for lo, hi in spans:
+        if type(lo) is not int or type(hi) is not int or lo < previous or hi <= lo:
+            raise ValueError("assistant spans must be sorted, non-overlapping, non-empty ranges")
+        previous = hi
+        a, b = max(lo, start + 1), min(hi, start + length + 1)
+        if a >= b:
+            continue
+        if left is not None:
+            b = min(b, a + left)
+            left -= b - a
+        if b > a:
+            out.append([a - start - 1, b - start - 1])
+        if left == 0:
+            break
+    return out
+
+
+def select_pilot_windows(documents: list[dict], *, target_tokens: int, context: int, seed: int = 1234) -> tuple[list[dict], dict]:
+    """``documents``: ``{"part", "offset", "tokens", "assistant_token_spans", ...}`` (offset = position of the document's
+    first token in its part file).  Documents are shuffled deterministically; each selected document's windows are taken
+    in order (every window starts a fresh context); windows without any target are skipped and counted; the selection
+    stops on EXACTLY ``target_tokens`` targets or raises if the corpus is too small.  Returns the windows in the form
+    ``seal_pilot`` takes and a summary."""
+    if type(target_tokens) is not int or target_tokens < 1 or type(context) is not int or context < 2:
+        raise ValueError("a positive supervised budget and a context of at least 2 are required")
+    order = list(documents)
+    random.Random(seed).shuffle(order)
+    windows, targets, used_documents, skipped, resets = [], 0, 0, 0, 0
+    for doc in order:
+        spans = doc["assistant_token_spans"]
+        if any(hi > doc["tokens"] for _, hi in spans):
+            raise ValueError("supervision outside the source document")
+        used = False
+        for start in range(0, doc["tokens"] - 1, context):
+            length = min(context, doc["tokens"] - 1 - start)
+            selected = shifted_window_spans(spans, start, length, limit=target_tokens - targets)
+            count = sum(hi - lo for lo, hi in selected)
+            if not count:
+                skipped += 1
+                continue
+            windows.append({"part": doc["part"], "start": doc["offset"] + start, "length": length, "assistant_label_spans": selected, "targets": count,
+                            "context_reset": start > 0, **{k: doc[k] for k in ("problem_sha256", "mode", "has_tools") if k in doc}})
+            targets += count
+            resets += int(start > 0)
+            used_documents += int(not used)
+            used = True
+            if targets == target_tokens:
+                break
+        if targets == target_tokens:
+            break
+    if targets != target_tokens:
+        raise ValueError(f"the corpus holds only {targets} supervised tokens; {target_tokens} were requested")
+    return windows, {"supervised_tokens": targets, "windows": len(windows), "documents": used_documents, "zero_target_windows_skipped": skipped,
+                     "context_resets": resets, "seed": seed, "context": context}

@@ -59,3 +59,27 @@ def test_sealing_is_enforced(tmp_path):
         f.write("{}\n")
     with pytest.raises(ValueError, match="changed after sealing"):
         SealedWindows(tmp_path / "pilot", expected_split="train")
+
+
+def test_pilot_selection_hits_the_budget_exactly_and_counts_every_target_once(tmp_path):
+    from archlab_b200.data.sealed_windows import select_pilot_windows, shifted_window_spans
+
+    assert shifted_window_spans([[3, 12]], 0, 8) == [[2, 8]] and shifted_window_spans([[3, 12]], 8, 8) == [[0, 3]]      # tokens 3..8 | 9..11
+    assert shifted_window_spans([[3, 12]], 0, 8, limit=4) == [[2, 6]] and shifted_window_spans([[0, 2]], 0, 8) == [[0, 1]]   # token 0 has no predecessor
+    with pytest.raises(ValueError, match="sorted"):
+        shifted_window_spans([[5, 9], [2, 4]], 0, 8)
+    src = corpus(tmp_path / "corpus")
+    docs = [{"part": "part-00000.bin", "offset": 0, "tokens": 300, "assistant_token_spans": [[10, 40], [100, 290]]},
+            {"part": "part-00000.bin", "offset": 300, "tokens": 200, "assistant_token_spans": [[50, 200]]},
+            {"part": "part-00000.bin", "offset": 500, "tokens": 64, "assistant_token_spans": []}]
+    windows, summary = select_pilot_windows(docs, target_tokens=333, context=128, seed=3)
+    assert summary["supervised_tokens"] == 333 == sum(w["targets"] for w in windows) and summary["documents"] == 2
+    seal_pilot(tmp_path / "pilot", src, windows, split="train", context=128)
+    data = SealedWindows(tmp_path / "pilot", expected_split="train", expected_budget=333)
+    assert sum(data.batch(i)[2] for i in range(len(data))) == 333
+    all_windows, total = select_pilot_windows(docs, target_tokens=30 + 190 + 150, context=128)                           # every assistant token exactly once
+    positions = sorted(w["start"] + lo + 1 + k for w in all_windows for lo, hi in w["assistant_label_spans"] for k in range(hi - lo))
+    expected = sorted([p for a, b in [(10, 40), (100, 290)] for p in range(a, b)] + [300 + p for p in range(50, 200)])
+    assert positions == expected and total["zero_target_windows_skipped"] <= 1       # the document without assistant text, if it came first
+    with pytest.raises(ValueError, match="holds only"):
+        select_pilot_windows(docs, target_tokens=10_000, context=128)
