@@ -192,3 +192,58 @@ class TreeMigration:
         state.update(phase="complete", completed=time.time(), removed_bytes=state["bytes"])
         self._save(state)
         return state
+
+
+# ---- continuing offload as new finished payloads appear ----------------------------------------------------------------
+def grow_plan(plan_path, candidates: list[dict]) -> int:
+    """Adds tasks whose source is not in the plan yet (existing rows, with whatever state they carry, are kept);
+    the plan file is replaced atomically.  Returns how many were added."""
+    plan_path = Path(plan_path)
+    known = {}
+    if plan_path.exists():
+        known = {row["source"]: row for row in (json.loads(line) for line in plan_path.read_text().splitlines() if line.strip())}
+    added = 0
+    for row in candidates:
+        if row["source"] not in known:
+            known[row["source"]] = row
+            added += 1
+    if added:
+        tmp = plan_path.with_suffix(".tmp")
+        tmp.write_text("".join(json.dumps(r) + "\n" for r in known.values()))
+        tmp.replace(plan_path)
+    return added
+
+
+def offload_watch(source, destination, plan_path, journal_path, *, cycles: int | None = None, sleep_seconds: float = 120.0, minimum_bytes: int = 4 << 20,
+                  sleep=time.sleep) -> dict:
+    """Every cycle: re-plan the tree, append new finished payloads to the plan, transfer what the journal has not verified
+    yet (``services.storage.transfer``: copy, re-hash, journal), write the status file beside the journal.  A transfer
+    error stops the watcher with the status saying so -- nothing is retried blindly.  ``cycles=None`` runs until
+    interrupted.  (Reference: src/archlab/storage/offload_watch.py:15-95.)"""
+    from .storage import OffloadJournal, transfer
+
+    journal = OffloadJournal(journal_path)
+    status_path = Path(journal_path).parent / "OFFLOAD_WATCH_STATUS.json"
+    done = 0
+    last = {}
+    while cycles is None or done < cycles:
+        tasks, summary = offload_plan(source, destination, minimum_bytes=minimum_bytes)
+        added = grow_plan(plan_path, tasks)
+        moved, errors = 0, []
+        rows = [json.loads(line) for line in Path(plan_path).read_text().splitlines() if line.strip()] if Path(plan_path).exists() else []
+        for row in rows:
+            if journal.state(row["source"])[0] == "verified":
+                continue
+            try:
+                transfer(row["source"], row["destination"], journal)
+                moved += 1
+            except (OSError, ValueError, RuntimeError) as why:
+                errors.append({"source": row["source"], "error": str(why)})
+        last = {"state": "needs_attention" if errors else "caught_up", "new_files": added, "transferred": moved, "errors": errors, "scan": summary, "time": time.time()}
+        atomic_write_json(status_path, last)
+        if errors:
+            break
+        done += 1
+        if cycles is None or done < cycles:
+            sleep(sleep_seconds)
+    return last

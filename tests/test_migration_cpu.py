@@ -88,3 +88,25 @@ def test_refusals(tmp_path):
     (model / "config.json").write_text('{"changed": 1}')
     with pytest.raises(ValueError, match="source changed after verification"):
         m.commit()
+
+
+def test_watcher_picks_up_new_finished_payloads(tmp_path):
+    src, dst = tmp_path / "results", tmp_path / "bulk"
+    step = src / "run" / "checkpoints" / "step-10"
+    step.mkdir(parents=True)
+    (step / "w.pt").write_bytes(b"a" * 64)
+    (step / "COMPLETE.json").write_text("{}")
+    pending = src / "run" / "checkpoints" / "step-20"
+    pending.mkdir()
+    (pending / "w.pt").write_bytes(b"b" * 64)
+    kw = dict(cycles=1, minimum_bytes=16, sleep=lambda s: None)
+    first = mg.offload_watch(src, dst, tmp_path / "plan.jsonl", tmp_path / "journal.db", **kw)
+    assert first["state"] == "caught_up" and first["new_files"] == 1 and first["transferred"] == 1
+    assert (dst / "run" / "checkpoints" / "step-10" / "w.pt").read_bytes() == b"a" * 64 and not (dst / "run" / "checkpoints" / "step-20").exists()
+    (pending / "COMPLETE.json").write_text("{}")                                 # the second checkpoint finishes
+    second = mg.offload_watch(src, dst, tmp_path / "plan.jsonl", tmp_path / "journal.db", **kw)
+    assert second["new_files"] == 1 and second["transferred"] == 1 and (dst / "run" / "checkpoints" / "step-20" / "w.pt").exists()
+    third = mg.offload_watch(src, dst, tmp_path / "plan.jsonl", tmp_path / "journal.db", **kw)
+    assert third["new_files"] == 0 and third["transferred"] == 0
+    assert json.loads((tmp_path / "OFFLOAD_WATCH_STATUS.json").read_text())["state"] == "caught_up"
+    assert mg.grow_plan(tmp_path / "plan.jsonl", [{"source": str(step / "w.pt"), "destination": "x", "bytes": 1}]) == 0
