@@ -294,3 +294,35 @@ def main(argv=None) -> int:
 
 if __name__ == "__main__":
     raise SystemExit(main())
+
+
+def checkpoint_receipt(path, *, sample_tensors: tuple[str, ...] = (), sample_ranks: tuple[int, ...] = (0,)) -> dict:
+    """The structural verification plus REPRESENTATIVE content checks: for the named tensors (default: the first and the
+    last tensor of the manifest) the first chunk on each sampled rank is loaded and its SHA-256 compared with the
+    manifest.  Reading every payload of a multi-terabyte save is the restore's job; a receipt that proves lengths
+    everywhere and content somewhere is what an archive step can afford
+    (src/archlab/storage/v41_checkpoint_receipt.py:13-94)."""
+    import hashlib
+
+    import torch
+
+    path = Path(path)
+    base = verify_sharded(path)
+    marker = json.loads((path / "COMPLETE.json").read_text())
+    manifests = marker.get("manifests") or [f"rank-{r:02d}/MANIFEST.json" for r in range(marker["world_size"])]
+    samples = []
+    for rank in sample_ranks:
+        manifest_path = path / manifests[rank]
+        tensors = json.loads(manifest_path.read_text())["tensors"]
+        wanted = sample_tensors or tuple(dict.fromkeys((tensors[0]["name"], tensors[-1]["name"])))
+        for name in wanted:
+            entry = next((t for t in tensors if t["name"] == name), None)
+            if entry is None:
+                raise ValueError(f"sampled tensor is not in the checkpoint: {name}")
+            chunk = entry["chunks"][0]
+            value = torch.load(manifest_path.parent / chunk["file"], map_location="cpu", weights_only=True)
+            digest = hashlib.sha256(value.contiguous().view(torch.uint8).numpy().tobytes()).hexdigest()
+            if digest != chunk["sha256"]:
+                raise ValueError(f"payload checksum mismatch: rank {rank} {name}")
+            samples.append({"rank": rank, "name": name, "sha256": digest, "verified": True})
+    return {**base, "passed": True, "representative_checksums": samples, "all_payload_lengths_verified": True}

@@ -91,3 +91,26 @@ def test_cli_dry_run_and_lock(tmp_path, capsys):
     assert json.loads(capsys.readouterr().out)["groups"][0]["delete"] == [str(root / "step-1")]
     with pytest.raises(SystemExit):
         rt.main(["--config", str(cfg), "--audit", str(tmp_path / "audit"), "--interval", "0.1"])
+
+
+def test_checkpoint_receipt_samples_content(tmp_path):
+    import pytest
+    import torch
+
+    from archlab_b200.ckpt.formats import write_v41_sharded
+    from archlab_b200.services.retention import checkpoint_receipt
+
+    state = {"embed.weight": torch.arange(12, dtype=torch.float32).view(6, 2), "mid.weight": torch.ones(4, 2), "head.weight": torch.full((6, 2), 3.0)}
+    write_v41_sharded(tmp_path / "ck", state, cursor={"step": 5, "supervised_tokens": 50}, world_size=2, ep_size=2, expert_fsdp_size=1)
+    receipt = checkpoint_receipt(tmp_path / "ck", sample_ranks=(0, 1))
+    assert receipt["passed"] and [s["name"] for s in receipt["representative_checksums"]] == ["embed.weight", "head.weight"] * 2
+    manifest = tmp_path / "ck" / "rank-01" / "MANIFEST.json"
+    import json
+    body = json.loads(manifest.read_text())
+    chunk = next(t for t in body["tensors"] if t["name"] == "head.weight")["chunks"][0]
+    torch.save(torch.zeros(chunk["elements"]), manifest.parent / chunk["file"])                  # same length, other content
+    with pytest.raises(ValueError, match="payload checksum mismatch: rank 1 head.weight"):
+        checkpoint_receipt(tmp_path / "ck", sample_ranks=(0, 1))
+    assert checkpoint_receipt(tmp_path / "ck", sample_tensors=("mid.weight",))["representative_checksums"][0]["name"] == "mid.weight"
+    with pytest.raises(ValueError, match="not in the checkpoint"):
+        checkpoint_receipt(tmp_path / "ck", sample_tensors=("absent",))
