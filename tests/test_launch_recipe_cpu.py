@@ -43,3 +43,16 @@ def test_refusals(tmp_path):
     bad.write_text(yaml.safe_dump({"schema_version": 1, "family": "flash-next", "environment": {}, "extra": 1}))
     with pytest.raises(ValueError, match="exactly schema_version"):
         resolve_launch_recipe(bad, {})
+
+
+def test_every_profile_of_the_shipped_launch_catalog_resolves():
+    from pathlib import Path
+
+    catalog = Path(__file__).resolve().parents[1] / "recipes" / "qwen" / "launches.yaml"
+    profiles = yaml.safe_load(catalog.read_text())["profiles"]
+    assert profiles
+    for name in profiles:
+        out = resolve_launch_recipe(f"{catalog}#{name}", {})
+        assert out["NGA_LAUNCH_FAMILY"] in ("dense-27b", "flash-next") and int(out["NGA_EXPECTED_NODES"]) >= 1
+    one, other = list(profiles)[0], list(profiles)[-1]
+    assert resolve_launch_recipe(f"{catalog}#{one}", {})["NGA_LAUNCH_RECIPE_SHA256"] != resolve_launch_recipe(f"{catalog}#{other}", {})["NGA_LAUNCH_RECIPE_SHA256"]
