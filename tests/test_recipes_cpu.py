@@ -34,8 +34,8 @@ def test_rl_recipes_and_overlay(monkeypatch):
 
 
 def test_launch_catalog_and_study_contract():
-    cat = read_recipe(f"{ROOT / 'qwen/launches.yaml'}#flash-next-quarter-fp4")
-    assert cat["family"] == "flash-next" and cat["environment"]["NGA_PRECISION"] == "fp4"
+    cat = read_recipe(f"{ROOT / 'qwen/launches.yaml'}#flash_next_quarter")
+    assert cat["family"] == "flash-next" and cat["environment"]["NGA_FLASH_NEXT_MODEL_VARIANT"] == "quarter-depth48-no-mtp"
     with pytest.raises(ValueError):
         read_recipe(ROOT / "qwen/launches.yaml")
     assert read_recipe(ROOT / "deepseek_v41/scratch_w640_d20.yaml")["parallelism"]["expert"] == 8
