@@ -293,3 +293,8 @@ class V41LM(nn.Module):
         kl = torch.stack(kls).mean() if kls else ce.new_zeros(())
         self.last_loss_metrics = {"cross entropy": ce.detach(), "indexer kl": kl.detach()}
         return ce + c.indexer_kl_weight * kl
+
+
+from .protocol import attach_protocol  # noqa: E402  (after the classes it completes)
+
+attach_protocol(V41LM)

@@ -405,3 +405,8 @@ class FrontierLM(nn.Module):
             tgt = labels[:, off:]
             losses.append(F.cross_entropy(self._logits(state).flatten(0, 1), tgt.flatten(), ignore_index=-1))
         return torch.stack(losses).mean() if losses else hidden.new_zeros(())
+
+
+from .protocol import attach_protocol  # noqa: E402  (after the classes it completes)
+
+attach_protocol(FrontierLM)

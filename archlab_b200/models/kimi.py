@@ -211,3 +211,8 @@ class KimiLM(nn.Module):
         if labels is None:
             return logits
         return F.cross_entropy(logits.flatten(0, 1), labels.flatten(), ignore_index=-1)
+
+
+from .protocol import attach_protocol  # noqa: E402  (after the classes it completes)
+
+attach_protocol(KimiLM)

@@ -529,3 +529,8 @@ class GraphDecoderPool:
         if key not in self.pool:
             self.pool[key] = GraphDecoder(self.model, batch, capacity)
         return self.pool[key]
+
+
+from .protocol import attach_protocol  # noqa: E402  (after the classes it completes)
+
+attach_protocol(LimiteLM)

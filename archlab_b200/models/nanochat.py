@@ -343,3 +343,8 @@ class GPT(nn.Module):
                 nxt = torch.argmax(logits, dim=-1, keepdim=True)
             ids = torch.cat([ids, nxt], dim=1)
             yield int(nxt.item())
+
+
+from .protocol import attach_protocol  # noqa: E402  (after the classes it completes)
+
+attach_protocol(GPT)

@@ -378,3 +378,8 @@ class Qwen38LM(nn.Module):
         if loss_reduction not in ("sum", "mean"):
             raise ValueError(f"unsupported loss reduction: {loss_reduction}")
         return total + c.router_aux_weight * aux if self.routers() else total
+
+
+from .protocol import attach_protocol  # noqa: E402  (after the classes it completes)
+
+attach_protocol(Qwen38LM)

@@ -377,3 +377,8 @@ def combo_config(name: str, **kw) -> SotaConfig:
     if name not in PARETO_COMBOS:
         raise ValueError(f"unknown combination {name!r}")
     return SotaConfig(mechanisms=PARETO_COMBOS[name], **kw)
+
+
+from .protocol import attach_protocol  # noqa: E402  (after the classes it completes)
+
+attach_protocol(SotaLM)
