@@ -137,3 +137,67 @@ def compare(first: list[dict], second: list[dict], expected_ids: list[str]) -> d
         return [picked[p] for p in expected_ids]
 
     return paired_statistics(first_draws(first), first_draws(second))
+
+
+# ---- a report over several models' sampled exams ------------------------------------------------------------------------
+def completion_budget(prompt_tokens: int, requested: int, context: int) -> int:
+    """The completion may spend the REMAINING native context: the prompt is never truncated to make room."""
+    if not 0 < prompt_tokens < context or requested < 1:
+        raise ValueError("the prompt does not fit the model's native context")
+    return min(requested, context - prompt_tokens)
+
+
+def read_complete_rows(path) -> list[dict]:
+    """A live writer may have a half-written last line; a row counts only when its newline is there."""
+    import json
+    from pathlib import Path
+
+    return [json.loads(line) for line in Path(path).read_text().split("\n")[:-1] if line.strip()]
+
+
+def build_report(cases: list[dict], models: dict[str, dict], *, bootstrap_draws: int = 10_000) -> dict:
+    """``cases``: ``{"id", "task"}``; ``models``: name -> ``{"records": [...], "samples_per_problem": n}`` where every record
+    carries ``model``, ``problem_id``, ``sample_index``, ``correct``, ``finish_reason``, ``generated_tokens``.  Per model and
+    exam (each task, and all tasks together): the first-draw summary and the repeated-draw summary; per pair of models
+    whose first draws are complete: the paired test.  ``complete`` only when every repeated summary is."""
+    from itertools import combinations
+
+    exams = {task: [c["id"] for c in cases if c["task"] == task] for task in sorted({c["task"] for c in cases})}
+    exams["all"] = [c["id"] for c in cases]
+    report = {"format": "archlab-math-report-v1", "models": {}, "paired_first_draw": {}}
+    complete = True
+    for name, entry in models.items():
+        rows = entry["records"]
+        if any(r["model"] != name for r in rows):
+            raise ValueError("a benchmark record belongs to another model than its registered output")
+        per_exam = {}
+        for task, ids in exams.items():
+            subset = [r for r in rows if r["problem_id"] in set(ids)]
+            per_exam[task] = {"first_draw": summarize([r for r in subset if r["sample_index"] == 0], ids, 1, bootstrap_draws=bootstrap_draws),
+                              "repeated": summarize(subset, ids, entry["samples_per_problem"], bootstrap_draws=bootstrap_draws)}
+            complete &= per_exam[task]["repeated"]["complete"]
+        report["models"][name] = {"exams": per_exam, "recorded_samples": len(rows), "expected_samples": len(cases) * entry["samples_per_problem"]}
+    for left, right in combinations(models, 2):
+        pair = {}
+        for task, ids in exams.items():
+            if all(report["models"][m]["exams"][task]["first_draw"]["complete"] for m in (left, right)):
+                pick = lambda m: [r for r in models[m]["records"] if r["problem_id"] in set(ids)]
+                pair[task] = compare(pick(left), pick(right), ids)
+        if pair:
+            report["paired_first_draw"][f"{left} vs {right}"] = pair
+    report["complete"] = bool(complete and models)
+    return report
+
+
+def markdown_report(report: dict) -> str:
+    lines = ["# Sampled math evaluation", "", "Only completed exams are scored; partial response counts are progress, not accuracy.", "",
+             "| Model | Exam | Draws / expected | First-draw accuracy | pass@1 | pass@4 | Truncated |", "| --- | --- | --- | --- | --- | --- | --- |"]
+    for name, model in report["models"].items():
+        for task, res in model["exams"].items():
+            first, rep = res["first_draw"], res["repeated"]
+            done = rep.get("responses", rep.get("recorded_samples", 0))
+            expected = rep.get("expected_samples", rep.get("responses"))
+            pct = lambda d, k: f"{d[k]:.1%}" if d.get("complete") and k in d else "pending"
+            lines.append(f"| {name} | {task} | {done} / {expected} | {pct(first, 'first_draw_accuracy')} | {pct(rep, 'pass_at_1')} | {pct(rep, 'pass_at_4')} | {pct(rep, 'truncation_rate')} |")
+    lines += ["", "The JSON report holds problem-cluster bootstrap intervals, Wilson intervals, paired tests, truncation rates and token lengths.", ""]
+    return "\n".join(lines)

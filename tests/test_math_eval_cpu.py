@@ -76,3 +76,31 @@ def test_paired_comparison_uses_the_first_draw():
     assert out["gained"] == 2 and out["lost"] == 0 and out["difference"] == pytest.approx(2 / 3)
     with pytest.raises(ValueError, match="same complete"):
         me.compare(one, two[4:], ["a", "b", "c"])
+
+
+def test_multi_model_report_and_budget(tmp_path):
+    cases = [{"id": "a", "task": "exam24"}, {"id": "b", "task": "exam24"}, {"id": "c", "task": "exam25"}]
+
+    def records(model, pattern, drop=0):
+        rows = [{"model": model, **r} for r in _records(pattern)]
+        return rows[:len(rows) - drop]
+    models = {"base": {"records": records("base", {"a": [0, 0, 0, 0], "b": [0, 1, 0, 0], "c": [0, 0, 0, 0]}), "samples_per_problem": 4},
+              "tuned": {"records": records("tuned", {"a": [1, 1, 0, 1], "b": [1, 1, 1, 1], "c": [0, 0, 1, 0]}), "samples_per_problem": 4}}
+    report = me.build_report(cases, models, bootstrap_draws=100)
+    assert report["complete"] and set(report["models"]["base"]["exams"]) == {"exam24", "exam25", "all"}
+    assert report["models"]["tuned"]["exams"]["exam24"]["repeated"]["pass_at_1"] == pytest.approx((0.75 + 1.0) / 2)
+    assert report["paired_first_draw"]["base vs tuned"]["all"]["gained"] == 2
+    text = me.markdown_report(report)
+    assert "| tuned | exam24 | 8 / 8 | 100.0% | 87.5% | 100.0% | 25.0% |" in text
+    models["tuned"]["records"] = records("tuned", {"a": [1, 1, 0, 1], "b": [1, 1, 1, 1], "c": [0, 0, 1, 0]}, drop=1)
+    partial = me.build_report(cases, models, bootstrap_draws=50)
+    assert not partial["complete"] and "pending" in me.markdown_report(partial)
+    models["tuned"]["records"][0]["model"] = "other"
+    with pytest.raises(ValueError, match="another model"):
+        me.build_report(cases, models)
+    assert me.completion_budget(1000, 131072, 131072) == 130072 and me.completion_budget(10, 50, 1000) == 50
+    with pytest.raises(ValueError):
+        me.completion_budget(2000, 10, 1000)
+    live = tmp_path / "records.jsonl"
+    live.write_text('{"a": 1}\n{"a": 2}\n{"a": 3')
+    assert me.read_complete_rows(live) == [{"a": 1}, {"a": 2}]
