@@ -112,3 +112,51 @@ def evaluate_task(logits_fn, encode, data: list[dict], meta: dict, *, rank: int 
         correct += int(evaluate_item(logits_fn, encode, data[i], kind, delimiter=meta.get("continuation_delimiter", " "), fewshot=fewshot, **kw))
         done += 1
     return correct, done
+
+
+def read_bundle(bundle_dir) -> list[dict]:
+    """The published bundle layout: ``core.yaml`` (``icl_tasks``: label, icl_task_type, dataset_uri, num_fewshot list,
+    optional continuation_delimiter), ``eval_meta_data.csv`` (columns ``Eval Task`` and ``Random baseline`` in PERCENT)
+    and ``eval_data/<dataset_uri>`` JSON lines.  A task without a baseline row or a data file fails here, before any
+    model time is spent.  (Reference: src/archlab/speedrun/base_eval.py:121-190.)"""
+    import csv
+    import json
+    from pathlib import Path
+
+    import yaml
+
+    root = Path(bundle_dir)
+    with open(root / "eval_meta_data.csv", encoding="utf-8", newline="") as f:
+        baselines = {row["Eval Task"]: float(row["Random baseline"]) for row in csv.DictReader(f)}
+    tasks = []
+    for entry in yaml.safe_load((root / "core.yaml").read_text(encoding="utf-8"))["icl_tasks"]:
+        label, kind = entry["label"], entry["icl_task_type"]
+        if kind not in TASK_TYPES:
+            raise ValueError(f"task {label}: unknown task type {kind!r}")
+        if label not in baselines or not 0.0 <= baselines[label] < 100.0:
+            raise ValueError(f"task {label}: no random baseline in [0, 100) percent")
+        path = root / "eval_data" / entry["dataset_uri"]
+        data = [json.loads(line) for line in path.read_text(encoding="utf-8").splitlines() if line.strip()]
+        if not data:
+            raise ValueError(f"task {label}: no items in {path}")
+        tasks.append({"label": label, "data": data, "random_baseline": baselines[label] / 100.0,
+                      "meta": {"task_type": kind, "num_fewshot": int(entry["num_fewshot"][0]), "continuation_delimiter": entry.get("continuation_delimiter", " ")}})
+    return tasks
+
+
+def evaluate_bundle(logits_fn, encode, tasks: list[dict], *, max_per_task: int = -1, rank: int = 0, world: int = 1, group=None, shuffle_seed: int = 1337, **kw) -> dict:
+    """Accuracy, centred accuracy ``(acc - b) / (1 - b)`` and their mean over the bundle.  Items are shuffled with a fixed
+    seed BEFORE the ``max_per_task`` cut, so a subsample is the same on every run and every rank."""
+    results, centered = {}, {}
+    for task in tasks:
+        data = list(task["data"])
+        random.Random(shuffle_seed).shuffle(data)
+        if max_per_task > 0:
+            data = data[:max_per_task]
+        counts = torch.tensor(evaluate_task(logits_fn, encode, data, task["meta"], rank=rank, world=world, **kw), dtype=torch.float64,
+                              device=kw.get("device", "cpu"))
+        if world > 1:
+            torch.distributed.all_reduce(counts, group=group)
+        results[task["label"]] = float(counts[0] / counts[1].clamp_min(1))
+        centered[task["label"]] = (results[task["label"]] - task["random_baseline"]) / (1.0 - task["random_baseline"])
+    return {"results": results, "centered_results": centered, "core_metric": sum(centered.values()) / max(len(centered), 1)}

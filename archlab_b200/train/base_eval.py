@@ -32,12 +32,21 @@ def parse_modes(text: str) -> set[str]:
 
 def evaluate_checkpoint(model, modes: set[str], *, tasks: dict | None = None, max_per_task: int = -1, bpb_batches: dict[str, Iterable] | None = None,
                         token_bytes: torch.Tensor | None = None, prompts: list[list[int]] | None = None, sample_tokens: int = 16, decode=None,
-                        rank: int = 0, world: int = 1) -> dict:
+                        rank: int = 0, world: int = 1, core_encode=None, core_max_tokens: int | None = None) -> dict:
     out: dict = {}
     if "core" in modes:
         if tasks is None:
             raise ValueError("core evaluation needs a task bundle")
-        out["core"] = evaluate_core(model, tasks, max_per_task=max_per_task, rank=rank, world=world)
+        if isinstance(tasks, list):                                            # the published directory layout, all three task types
+            from ..evaluation.core_tasks import evaluate_bundle
+
+            device, was_training = next(model.parameters()).device, model.training
+            model.eval()
+            out["core"] = evaluate_bundle(lambda ids: model(ids), core_encode, tasks, max_per_task=max_per_task, rank=rank, world=world,
+                                          device=device, max_tokens=core_max_tokens)
+            model.train(was_training)
+        else:
+            out["core"] = evaluate_core(model, tasks, max_per_task=max_per_task, rank=rank, world=world)
     if "bpb" in modes:
         if not bpb_batches or token_bytes is None:
             raise ValueError("bpb evaluation needs batches per split and the tokenizer's token_bytes")
@@ -85,7 +94,13 @@ def main(argv=None) -> int:
     seq_len = meta["model_config"]["sequence_len"]
     kwargs: dict = {"decode": tokenizer.decode}
     if "core" in modes:
-        kwargs.update(tasks=load_task_bundle(a.task_bundle, tokenizer), max_per_task=a.max_per_task)
+        if Path(a.task_bundle).is_dir():
+            from ..evaluation.core_tasks import read_bundle
+
+            kwargs.update(tasks=read_bundle(a.task_bundle), max_per_task=a.max_per_task, core_max_tokens=seq_len,
+                          core_encode=lambda text: tokenizer.encode(text, prepend_bos=True))
+        else:
+            kwargs.update(tasks=load_task_bundle(a.task_bundle, tokenizer), max_per_task=a.max_per_task)
     if "bpb" in modes:
         part = torch.from_numpy(read_part(Path(a.data), 0).astype("int64"))
         kwargs.update(token_bytes=torch.load(Path(a.tokenizer) / "token_bytes.pt").to(device),

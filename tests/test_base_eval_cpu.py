@@ -38,3 +38,17 @@ def test_each_mode_runs_and_missing_inputs_are_errors():
             evaluate_checkpoint(m, modes)
     batches = list(part_batches(part, 2, 32, 200, "cpu"))
     assert len(batches) == 3 and torch.equal(batches[0][1][0, :-1], batches[0][0][0, 1:])
+
+
+def test_core_mode_accepts_the_published_bundle_layout(tmp_path):
+    import json
+
+    from archlab_b200.evaluation.core_tasks import read_bundle
+
+    (tmp_path / "eval_data").mkdir()
+    (tmp_path / "core.yaml").write_text("icl_tasks:\n- {label: t, icl_task_type: schema, dataset_uri: t.jsonl, num_fewshot: [1]}\n")
+    (tmp_path / "eval_meta_data.csv").write_text("Eval Task,Random baseline\nt,50\n")
+    (tmp_path / "eval_data" / "t.jsonl").write_text("\n".join(json.dumps({"context_options": [f"a{i}", f"b{i}"], "continuation": "cd", "gold": i % 2}) for i in range(4)) + "\n")
+    m = tiny()
+    out = evaluate_checkpoint(m, {"core"}, tasks=read_bundle(tmp_path), core_encode=lambda s: [1] + [2 + b % 60 for b in s.encode()], core_max_tokens=32)
+    assert set(out["core"]) == {"results", "centered_results", "core_metric"} and 0.0 <= out["core"]["results"]["t"] <= 1.0

@@ -81,3 +81,28 @@ def test_task_loop_strides_ranks_and_draws_fewshot_deterministically():
     assert seen == first[:3]                                                   # same few-shot draws on a re-run
     with pytest.raises(ValueError, match="unknown task type"):
         ct.evaluate_task(spy, encode, data, {"task_type": "cloze"})
+
+
+def test_bundle_directory_to_centred_metric(tmp_path):
+    import json
+
+    (tmp_path / "eval_data").mkdir()
+    (tmp_path / "core.yaml").write_text(
+        "icl_tasks:\n"
+        "- {label: sums, icl_task_type: multiple_choice, dataset_uri: sums.jsonl, num_fewshot: [0]}\n"
+        "- {label: capitals, icl_task_type: language_modeling, dataset_uri: cap.jsonl, num_fewshot: [0], continuation_delimiter: ' '}\n")
+    (tmp_path / "eval_meta_data.csv").write_text("Eval Task,Random baseline\nsums,50\ncapitals,0\n")
+    (tmp_path / "eval_data" / "sums.jsonl").write_text("\n".join(json.dumps({"query": "2+2=", "choices": ["5", "4"], "gold": g}) for g in (1, 0)) + "\n")
+    (tmp_path / "eval_data" / "cap.jsonl").write_text(json.dumps({"context": "Paris is in", "continuation": "France"}) + "\n")
+    tasks = ct.read_bundle(tmp_path)
+    assert [t["label"] for t in tasks] == ["sums", "capitals"] and tasks[0]["random_baseline"] == 0.5
+
+    both = oracle("2+2= 4")
+    out = ct.evaluate_bundle(both, encode, tasks)
+    assert out["results"] == {"sums": 0.5, "capitals": 0.0}                     # the model says 4: right for gold=1, wrong for gold=0
+    assert out["centered_results"] == {"sums": 0.0, "capitals": 0.0} and out["core_metric"] == 0.0
+    assert ct.evaluate_bundle(both, encode, tasks, max_per_task=1)["results"]["sums"] in (0.0, 1.0)
+
+    (tmp_path / "eval_meta_data.csv").write_text("Eval Task,Random baseline\nsums,50\n")
+    with pytest.raises(ValueError, match="capitals: no random baseline"):
+        ct.read_bundle(tmp_path)
