@@ -219,9 +219,16 @@ class EvalCadence:
         if a.core_metric_every > 0:
             if not a.core_tasks:
                 raise SystemExit("--core-metric-every needs --core-tasks")
-            from .evaluation import load_task_bundle
+            if Path(a.core_tasks).is_dir():                                   # published layout: three task types, percent baselines
+                from ..evaluation.core_tasks import read_bundle
 
-            self.tasks = load_task_bundle(a.core_tasks, self.tokenizer)
+                if self.tokenizer is None:
+                    raise SystemExit("a CORE bundle directory holds text: --core-tasks DIR needs a tokenizer")
+                self.tasks = read_bundle(a.core_tasks)
+            else:
+                from .evaluation import load_task_bundle
+
+                self.tasks = load_task_bundle(a.core_tasks, self.tokenizer)
         self.prompts = None
         if a.sample_every > 0:
             if not a.prompt_file:
@@ -270,9 +277,19 @@ class EvalCadence:
             self._emit({"kind": "validation", "step": step, "tokens": a.total_batch_size * step, "bpb": bpb, "eval_tokens": a.eval_tokens,
                         "total_training_flops": flops_per_token * a.total_batch_size * step})
         if self.tasks is not None and self.due(a.core_metric_every, step, last, at_zero=False):
-            from .evaluation import evaluate_core
+            if isinstance(self.tasks, list):
+                from ..evaluation.core_tasks import evaluate_bundle
 
-            res = evaluate_core(model, self.tasks, max_per_task=a.core_metric_max_per_task, rank=self.rank, world=self.world)
+                was = model.training
+                model.eval()
+                res = evaluate_bundle(lambda ids: model(ids), lambda text: self.tokenizer.encode(text, prepend_bos=True), self.tasks,
+                                      max_per_task=a.core_metric_max_per_task, rank=self.rank, world=self.world,
+                                      device=next(model.parameters()).device, max_tokens=a.max_seq_len)
+                model.train(was)
+            else:
+                from .evaluation import evaluate_core
+
+                res = evaluate_core(model, self.tasks, max_per_task=a.core_metric_max_per_task, rank=self.rank, world=self.world)
             self._emit({"kind": "core", "step": step, "core_metric": res["core_metric"], "centered_results": res["centered_results"]})
         if self.prompts is not None and self.rank == 0 and self.due(a.sample_every, step, last, at_zero=False):
             from .evaluation import generate_batch
